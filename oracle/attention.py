@@ -1,0 +1,131 @@
+"""Paged GQA attention of the Qwen3.5 decoder (CPU oracle; test infrastructure only).
+
+Page-table form of the reference's sgl line: paged_kv_cache [pages, 2, P, HKV, D] (K plane, V plane per page),
+indptr [B + 1], indices [pages used], last_page_len [B]
+(models/qwen35_35b_a3b/sgl/python/sgl_kernel_axera/attention/flash_attn.py:2549-2587).
+"""
+import math
+
+import torch
+import torch.nn.functional as F
+
+from .codecs import kv_dequant_fp8, kv_quant_fp8
+from .moe import bf, rmsnorm
+
+
+def valid_kv_len(indptr, last_page_len, page):
+    """(n_pages - 1) * P + last_page_len, 0 for a sequence without pages (flash_attn.py:2354-2358)."""
+    n = (indptr[1:] - indptr[:-1]).long()
+    return torch.where(n > 0, (n - 1) * page + last_page_len.long(), torch.zeros_like(n))
+
+
+def gather_kv(cache, indptr, indices, last_page_len, b, kv_scale=None):
+    """history K, V of sequence b as fp32 [ctx, HKV, D] (golden gather,
+    models/qwen35_35b_a3b/sgl/tests/test_qwen35_runtime.py:76-79)."""
+    P = cache.shape[2]
+    rows = indices[int(indptr[b]):int(indptr[b + 1])].long()
+    ctx = int(valid_kv_len(indptr, last_page_len, P)[b])
+    k = cache[rows, 0].reshape(-1, *cache.shape[3:])[:ctx]
+    v = cache[rows, 1].reshape(-1, *cache.shape[3:])[:ctx]
+    if cache.dtype == torch.float8_e4m3fn:
+        ks = vs = None
+        if kv_scale is not None:
+            ks, vs = kv_scale[0], kv_scale[1]
+        return kv_dequant_fp8(k, ks), kv_dequant_fp8(v, vs)
+    return k.float(), v.float()
+
+
+def paged_decode(q, cache, indptr, indices, last_page_len, sm_scale=None, kv_scale=None, k_new=None, v_new=None):
+    """One query token per sequence over its paged history (+ optionally the current token's own k / v row, which the
+    kernel takes from registers instead of the cache, flash_attn.py:2088-2124).
+
+    q [B, HQ, D] bf16; k_new / v_new [B, HKV, D] bf16; kv_scale [2, HKV] fp32 for a per-head-scaled FP8 cache (None with
+    an FP8 cache: the constant-8 form).  softmax(q k^T * sm_scale) v in fp32 -> bf16, query head h uses KV head
+    h // (HQ / HKV) (golden: scaled_dot_product_attention(enable_gqa=True),
+    models/qwen35_35b_a3b/sgl/tests/test_qwen35_runtime.py:80-85).  A sequence with no key at all gives zeros."""
+    B, HQ, D = q.shape
+    HKV = cache.shape[3]
+    G = HQ // HKV
+    scale = 1.0 / math.sqrt(D) if sm_scale is None else float(sm_scale)
+    out = torch.zeros((B, HQ, D))
+    for b in range(B):
+        k, v = gather_kv(cache, indptr, indices, last_page_len, b, kv_scale)
+        if k_new is not None:
+            k = torch.cat([k, k_new[b].float()[None]], 0)
+            v = torch.cat([v, v_new[b].float()[None]], 0)
+        if k.shape[0] == 0:
+            continue
+        qb = q[b].float().reshape(HKV, G, D)
+        s = torch.einsum("hgd,lhd->hgl", qb, k) * scale
+        p = torch.softmax(s, -1)
+        out[b] = torch.einsum("hgl,lhd->hgd", p, v).reshape(HQ, D)
+    return out.to(torch.bfloat16)
+
+
+def store_paged_kv(cache, cache_location, k_new, v_new, kv_scale=None):
+    """write the current token's K / V rows at (page, offset) per sequence (flash_attn.py:53-84); FP8 caches store
+    e4m3(x * 8) (models/qwen38_27b/decode/q35_group.py:244-249) or e4m3(x / scale_h) with kv_scale [2, HKV]."""
+    for b in range(k_new.shape[0]):
+        page, off = int(cache_location[b, 0]), int(cache_location[b, 1])
+        if cache.dtype == torch.float8_e4m3fn:
+            ks = vs = None
+            if kv_scale is not None:
+                ks, vs = kv_scale[0], kv_scale[1]
+            cache[page, 0, off] = kv_quant_fp8(k_new[b], ks)
+            cache[page, 1, off] = kv_quant_fp8(v_new[b], vs)
+        else:
+            cache[page, 0, off] = k_new[b].to(cache.dtype)
+            cache[page, 1, off] = v_new[b].to(cache.dtype)
+    return cache
+
+
+def rope_neox(x, cos, sin, rot):
+    """NeoX-style rotation of the first `rot` channels (halves rot/2 apart), the rest passed through
+    (attn_utils/common.py:248-301; golden test_qwen35_runtime.py:66-72).  x [..., D] bf16, cos / sin [..., rot/2]."""
+    a, b = x[..., : rot // 2].float(), x[..., rot // 2: rot].float()
+    c, s = cos.float(), sin.float()
+    y = x.clone()
+    y[..., : rot // 2] = (a * c - b * s).to(x.dtype)
+    y[..., rot // 2: rot] = (b * c + a * s).to(x.dtype)
+    return y
+
+
+def rope_cos_sin(pos, rot, theta):
+    """models/qwen35_2b/whole/src/q35_step.py:408-411 (fp32 here; the kernels take them as inputs)."""
+    inv = 1.0 / (theta ** (torch.arange(0, rot, 2, dtype=torch.int64).float() / rot))
+    f = torch.as_tensor(pos).float().reshape(-1, 1) * inv
+    return f.cos(), f.sin()
+
+
+def attn_layer_decode(x, w, cache, indptr, indices, last_page_len, cache_location, cos, sin, *, heads, kv_heads,
+                      head_dim, rot, gated=True, eps=1e-6, sm_scale=None, kv_scale=None):
+    """Decode attention sublayer on B sequences (one token each), golden of
+    models/qwen35_35b_a3b/sgl/tests/test_qwen35_runtime.py:57-93: RMSNorm -> q(+gate) / k / v projections (bf16) ->
+    q / k RMSNorm -> RoPE -> cache write -> attention over history + current token -> sigmoid gate -> o-proj ->
+    residual.  w: ln1 [H] f32, w_q [HQ * D * (2 if gated), H] (per head [q | gate], models/qwen35_2b/whole/src/
+    q35_step.py:192-194), w_k, w_v [HKV * D, H], q_norm, k_norm [D] f32, w_o [H, HQ * D] -- DEQUANTIZED fp32.
+    x [B, H] bf16.  Returns out [B, H] bf16 (cache updated in place)."""
+    B, H = x.shape
+    n = rmsnorm(x, w["ln1"], eps).float()
+    qg = bf(n @ w["w_q"].float().T).reshape(B, heads, -1)
+    q, gate = (qg[..., :head_dim], qg[..., head_dim:]) if gated else (qg, None)
+    k = bf(n @ w["w_k"].float().T).reshape(B, kv_heads, head_dim)
+    v = bf(n @ w["w_v"].float().T).reshape(B, kv_heads, head_dim).to(torch.bfloat16)
+    q = rmsnorm(q, w["q_norm"], eps)
+    k = rmsnorm(k, w["k_norm"], eps)
+    q = rope_neox(q, cos[:, None, :], sin[:, None, :], rot)
+    k = rope_neox(k, cos[:, None, :], sin[:, None, :], rot)
+    attn = paged_decode(q, cache, indptr, indices, last_page_len, sm_scale, kv_scale, k_new=k, v_new=v).float()
+    store_paged_kv(cache, cache_location, k, v, kv_scale)
+    if gated:
+        attn = bf(attn * torch.sigmoid(gate))
+    o = bf(attn.reshape(B, -1) @ w["w_o"].float().T)
+    return (x.float() + o).to(torch.bfloat16), q, k, v
+
+
+def sdpa_decode_reference(q, k_hist, v_hist):
+    """independent formulation used to cross-check paged_decode in the CPU tests: torch SDPA with GQA on one
+    sequence, q [HQ, D], k / v [L, HKV, D] (all fp32)."""
+    o = F.scaled_dot_product_attention(q[None, :, None, :].double(), k_hist.permute(1, 0, 2)[None].double(),
+                                       v_hist.permute(1, 0, 2)[None].double(), enable_gqa=True)
+    return o[0, :, 0].float()

@@ -1,0 +1,152 @@
+"""Generates the golden fixtures in this directory from the reference's OWN torch goldens.
+
+Run in a container that has the reference checkout (path in REF, default /root/reference):
+    python tests/golden/make_golden.py
+The reference's kernels need its NPU DSL package `axnn`, which is not installable; its pure-torch golden functions do
+not, so `axnn` (and `onnx`, imported by a board helper) are replaced by inert stub modules and the golden functions
+are imported and called unchanged.  Outputs: small .npz files (bf16 tensors stored as their int16 bit patterns with a
+`__bf16` suffix, fp8 as uint8 with `__e4m3`).  The tests only read the .npz files; nothing reads the reference at
+test time.
+"""
+import importlib.abc
+import importlib.machinery
+import json
+import os
+import sys
+import tempfile
+from unittest.mock import MagicMock
+
+import numpy as np
+import torch
+
+REF = os.environ.get("REF", "/root/reference")
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+class _Mod(MagicMock):
+    __path__ = []
+    __all__ = []
+
+
+def _builder(*a, **k):
+    return lambda fn: fn
+
+
+class _Finder(importlib.abc.MetaPathFinder, importlib.abc.Loader):
+    def find_spec(self, name, path, target=None):
+        if name.split(".")[0] in ("axnn", "onnx"):
+            return importlib.machinery.ModuleSpec(name, self, is_package=True)
+        return None
+
+    def create_module(self, spec):
+        m = _Mod()
+        m.__name__, m.__spec__, m.builder = spec.name, spec, _builder
+        return m
+
+    def exec_module(self, module):
+        pass
+
+
+def pack(d):
+    out = {}
+    for k, v in d.items():
+        if isinstance(v, torch.Tensor):
+            if v.dtype == torch.bfloat16:
+                out[k + "__bf16"] = v.contiguous().view(torch.int16).numpy()
+            elif v.dtype == torch.float8_e4m3fn:
+                out[k + "__e4m3"] = v.contiguous().view(torch.uint8).numpy()
+            elif v.dtype in (torch.float8_e8m0fnu, torch.float4_e2m1fn_x2):
+                out[k] = v.contiguous().view(torch.uint8).numpy()
+            else:
+                out[k] = v.contiguous().numpy()
+        else:
+            out[k] = np.asarray(v)
+    return out
+
+
+def save(name, d):
+    np.savez_compressed(os.path.join(HERE, name + ".npz"), **pack(d))
+    print("wrote", name, {k: tuple(np.asarray(v).shape) for k, v in pack(d).items()})
+
+
+def main():
+    sys.meta_path.insert(0, _Finder())
+    sgl = os.path.join(REF, "models/qwen35_35b_a3b/sgl")
+    sys.path[:0] = [os.path.join(sgl, "python"), os.path.join(sgl, "tests"),
+                    os.path.join(REF, "models/qwen35_2b/whole/src")]
+    cfg_dir = tempfile.mkdtemp()
+    json.dump({"text_config": {
+        "hidden_size": 2048, "num_experts": 256, "num_experts_per_tok": 8, "moe_intermediate_size": 512,
+        "shared_expert_intermediate_size": 512, "num_attention_heads": 16, "num_key_value_heads": 2, "head_dim": 256,
+        "rope_parameters": {"partial_rotary_factor": 0.25, "rope_theta": 1e7},
+        "layer_types": ["linear_attention"] * 3 + ["full_attention"], "num_hidden_layers": 4,
+        "linear_num_key_heads": 16, "linear_num_value_heads": 32, "linear_key_head_dim": 128,
+        "linear_value_head_dim": 128, "linear_conv_kernel_dim": 4, "rms_norm_eps": 1e-6, "vocab_size": 248320}},
+        open(os.path.join(cfg_dir, "config.json"), "w"))
+    os.environ["MODEL"] = cfg_dir
+    os.environ["WFMT"] = "mx8"
+    os.chdir(cfg_dir)
+    import q35_moe as mo  # models/qwen35_2b/whole/src/q35_moe.py
+    import q35_mx_build as mb  # models/qwen35_2b/whole/src/q35_mx_build.py
+    import test_gdn_attn as tg  # models/qwen35_35b_a3b/sgl/tests/test_gdn_attn.py
+
+    # 1. MXFP4 codec (q35_moe.py:46-63): random rows, a zero block, exact rounding ties, big/small magnitudes
+    g = torch.Generator().manual_seed(11)
+    w = torch.randn((12, 128), generator=g) * 0.02
+    w[1, :32] = 0
+    w[2, :8] = torch.tensor([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, -5.0])  # midpoints between E2M1 values
+    w[3] *= 1e4
+    w[4] *= 1e-6
+    pk, sc = mo.quant_mxfp4(w)
+    save("mxfp4_codec", dict(w=w, packed=pk, scale=sc, dequant=mo.dequant_mxfp4(pk, sc)))
+
+    # 2. MXFP8 (q35_mx_build.py:60-72) and NVFP4 (:168-186) codecs
+    w = torch.randn((6, 96), generator=g) * 0.05
+    w[0, :32] *= 1e3
+    q8, s8 = mb.quant_mxfp8(w)
+    save("mxfp8_codec", dict(w=w, q8=q8, scale=s8.view(torch.uint8), dequant=mb.dequant(q8, s8)))
+    w = torch.randn((6, 64), generator=g) * 0.02
+    p4, s4, t4 = mb.quant_nvfp4(w)
+    save("nvfp4_codec", dict(w=w, packed=p4.view(torch.uint8), scale=s4, scale2=t4,
+                             dequant=mb.dequant_nvfp4(p4, s4, t4)))
+
+    # 3. router (q35_moe.py:293-297), one token per call as the reference does
+    logits = torch.randn((24, 256), generator=g)
+    logits[3, 10] = logits[3, 200] = logits[3].max() + 1.0  # an exact tie at the top
+    logits[4, 7] = logits[4, 99] = torch.sort(logits[4], descending=True).values[7]  # a tie across the top-8 edge
+    ids, rws = [], []
+    for t in range(logits.shape[0]):
+        i, r = mo.route(logits[t])
+        ids.append(i)
+        rws.append(r.reshape(-1))
+    save("route", dict(logits=logits, ids=torch.tensor(ids, dtype=torch.int32), rw=torch.stack(rws)))
+
+    # 4. causal conv1d + SiLU (test_gdn_attn.py:241-257)
+    x = tg.bf16_randn((2, 9, 24), 0.5)
+    cw = tg.bf16_randn((24, 4), 0.2)
+    st = tg.bf16_randn((2, 3, 24), 0.3)
+    y, so = tg.causal_conv1d_silu_reference(x, cw, st)
+    save("conv1d", dict(x=x, weight=cw, state_in=st, y=y, state_out=so))
+
+    # 5. GDN core recurrence (gdn_reference, test_gdn_attn.py:260-296)
+    torch.manual_seed(5)
+    T, NK, NV, DK, DV = 10, 2, 4, 16, 16
+    q, k = tg.bf16_randn((1, T, NK, DK), 1.0), tg.bf16_randn((1, T, NK, DK), 1.0)
+    v = tg.bf16_randn((1, T, NV, DV), 1.0)
+    a, b = tg.bf16_randn((1, T, NV), 1.0), tg.bf16_randn((1, T, NV), 1.0)
+    a_log, dt_bias = torch.randn(NV) * 0.5, tg.bf16_randn((NV,), 0.5)
+    s0 = torch.randn((1, NV, DK, DV)) * 0.03
+    o, s1 = tg.gdn_reference(q, k, v, a, b, a_log, dt_bias, s0)
+    save("gdn_core", dict(q=q, k=k, v=v, a=a, b=b, a_log=a_log, dt_bias=dt_bias, state_in=s0, o=o, state_out=s1))
+
+    # 6. whole GDN sublayer (reference(), test_gdn_attn.py:427-474) on the fixture shape, seq 7
+    case = tg.random_case(7)
+    fused, st_out, cv_out = tg.reference(case, input_norm_eps=2e-6, o_norm_eps=3e-6)
+    hs, res, wts, ts, cs = case
+    d = dict(hidden=hs, residual=res, temporal_state=ts, conv_state=cs, fused=fused, state_out=st_out, conv_out=cv_out)
+    d.update({"w." + n: t for n, t in wts.items()})
+    save("gdn_sublayer", d)
+
+
+if __name__ == "__main__":
+    main()
