@@ -1,0 +1,181 @@
+// C ABI of the library: role registry, by-name binding, validation (see include/q35b200.h).
+#include "abi.h"
+#include <string>
+
+namespace q35 {
+
+static thread_local std::string g_err;
+
+int fail(int code, const char* fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof buf, fmt, ap);
+  va_end(ap);
+  g_err = buf;
+  return code;
+}
+
+int elem_bits(int dtype) {
+  switch (dtype) {
+    case Q35_U8: case Q35_E4M3: return 8;
+    case Q35_F32: case Q35_I32: return 32;
+    case Q35_BF16: case Q35_F16: return 16;
+    case Q35_FP4: return 4;
+    default: return 0;
+  }
+}
+
+int Call::get(const char* name, unsigned dtype_mask, Tensor* out, bool required) const {
+  *out = Tensor();
+  for (int i = 0; i < n; ++i) {
+    const q35_io& io = ios[i];
+    if (!io.name || strcmp(io.name, name) != 0) continue;
+    int bits = elem_bits(io.dtype);
+    Q35_REQUIRE(bits != 0, Q35_ERR_DTYPE, "%s: unknown dtype code %d", name, io.dtype);
+    Q35_REQUIRE((dtype_mask >> io.dtype) & 1u, Q35_ERR_DTYPE, "%s: dtype code %d not accepted here (mask 0x%x)", name,
+                io.dtype, dtype_mask);
+    Q35_REQUIRE(io.ndim >= 0 && io.ndim <= Q35_MAX_DIMS, Q35_ERR_SHAPE, "%s: ndim %d", name, io.ndim);
+    out->nd = io.ndim;
+    int64_t numel = 1;
+    for (int d = 0; d < io.ndim; ++d) {
+      Q35_REQUIRE(io.shape[d] >= 0, Q35_ERR_SHAPE, "%s: negative dim", name);
+      out->s[d] = io.shape[d];
+      numel *= io.shape[d];
+    }
+    Q35_REQUIRE((numel * bits) % 8 == 0 && size_t(numel * bits / 8) == io.bytes, Q35_ERR_BYTES,
+                "%s: %zu bytes bound, shape needs %lld", name, io.bytes, (long long)(numel * bits / 8));
+    out->dtype = io.dtype;
+    if (io.dtype == Q35_FP4) {  // logical FP4 [.., K] -> byte view [.., K/2]
+      Q35_REQUIRE(io.ndim >= 1 && io.shape[io.ndim - 1] % 2 == 0, Q35_ERR_SHAPE, "%s: odd FP4 inner dim", name);
+      out->s[io.ndim - 1] /= 2;
+      out->dtype = Q35_U8;
+    }
+    out->p = io.ptr;
+    out->bytes = io.bytes;
+    out->present = true;
+    Q35_REQUIRE(dry || io.ptr != nullptr || io.bytes == 0, Q35_ERR_MISSING, "%s: null pointer", name);
+    return 0;
+  }
+  Q35_REQUIRE(!required, Q35_ERR_MISSING, "tensor '%s' is not bound", name);
+  return 0;
+}
+
+int Call::workspace(int64_t need, Tensor* ws) {
+  ws_need = need;
+  *ws = Tensor();
+  if (dry) return 0;
+  Q35_TRY(get("workspace", M(Q35_U8), ws, need > 0));
+  Q35_REQUIRE(need == 0 || int64_t(ws->bytes) >= need, Q35_ERR_WORKSPACE, "workspace: %zu bytes bound, %lld needed",
+              ws->bytes, (long long)need);
+  Q35_REQUIRE(need == 0 || (reinterpret_cast<uintptr_t>(ws->p) & 255) == 0, Q35_ERR_ALIGN,
+              "workspace must be 256-byte aligned");
+  return 0;
+}
+
+__device__ int g_device_status;
+
+int* device_status_ptr() {
+  int* p = nullptr;
+  cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_device_status);
+  return p;
+}
+
+static const RoleDef kRoles[] = {
+    {"moe.route",
+     R"({"in":[["logits","f32","[T,NE]"]],"out":[["ids","i32","[T,K]"],["rw","f32","[T,K]"]]})", run_moe_route},
+    {"moe.pre",
+     R"({"in":[["x1","bf16","[T,H]"],["ln2","f32","[H]"],["w_gate","u8|e4m3","[FS,H/2]|[FS,H]"],["s_gate","u8","[FS,H/32]"],["w_up","u8|e4m3","[FS,H/2]|[FS,H]"],["s_up","u8","[FS,H/32]"],["w_down","u8|e4m3","[H,FS/2]|[H,FS]"],["s_down","u8","[H,FS/32]"],["w_router","bf16","[NE,H]"],["w_shg","bf16","[H]"],["workspace","u8","[*]"]],"out":[["out","bf16","[T,H]"],["h2_out","bf16","[T,H]"],["logits_out","f32","[T,NE]"]]})",
+     run_moe_pre},
+    {"moe.experts",
+     R"({"in":[["h2","bf16","[T,H]"],["base","bf16","[T,H]"],["ids","i32","[T,K]"],["rw","f32","[T,K]"],["e_gw","u8","[NE,2FE,H/2]"],["e_gs","u8","[NE,2FE,H/32]"],["e_dw","u8","[NE,H,FE/2]"],["e_ds","u8","[NE,H,FE/32]"],["workspace","u8","[*]"]],"out":[["out","bf16","[T,H]"]]})",
+     run_moe_experts},
+    {"moe.permute",
+     R"({"in":[["ids","i32","[T,K]"],["rw","f32","[T,K]"],["workspace","u8","[*]"]],"out":[["tok","i32","[S,1+G]"],["srw","f32","[S,G]"],["loc","i32","[K,T]"],["n_slots","i32","[1]"],["counts","i32","[NE]"]]})",
+     run_moe_permute},
+    {"moe.slots",
+     R"({"in":[["h2","bf16","[T,H]"],["tok","i32","[S,1+G]"],["rw","f32","[S,G]"],["e_gw","u8","[NE,2FE,H/2]"],["e_gs","u8","[NE,2FE,H/32]"],["e_dw","u8","[NE,H,FE/2]"],["e_ds","u8","[NE,H,FE/32]"],["n_slots","i32","[1] optional"],["workspace","u8","[*]"]],"out":[["out","bf16|f32","[S,G,H]"]]})",
+     run_moe_slots},
+    {"moe.combine",
+     R"({"in":[["base","bf16","[T,H]"],["loc","i32","[K,T]"],["sout","bf16|f32","[R,H]"]],"out":[["out","bf16","[T,H]"]]})",
+     run_moe_combine},
+    {"attn.paged_decode",
+     R"({"in":[["q","bf16","[B,HQ,D]"],["paged_kv_cache","bf16|e4m3","[pages,2,P,HKV,D]"],["indptr","i32","[B+1]"],["indices","i32","[N]"],["last_page_len","i32","[B]"],["sm_scale","f32","[1] optional"],["kv_scale","f32","[2,HKV] optional"],["k_new","bf16","[B,HKV,D] optional"],["v_new","bf16","[B,HKV,D] optional"],["workspace","u8","[*]"]],"out":[["out","bf16","[B,HQ,D]"]]})",
+     run_attn_paged_decode},
+    {"attn.kv_write",
+     R"({"in":[["k_new","bf16","[B,HKV,D]"],["v_new","bf16","[B,HKV,D]"],["cache_location","i32","[B,2]"],["kv_scale","f32","[2,HKV] optional"]],"out":[["paged_kv_cache","bf16|e4m3","[pages,2,P,HKV,D]"]]})",
+     run_attn_kv_write},
+    {"gdn.step",
+     R"({"in":[["q","bf16","[B,NK,DK]"],["k","bf16","[B,NK,DK]"],["v","bf16","[B,NV,DV]"],["g","f32","[B,NV]"],["beta","bf16","[B,NV]"],["state_in","f32","[B,NV,DK,DV]"]],"out":[["o","bf16","[B,NV,DV]"],["state_out","f32","[B,NV,DK,DV]"]]})",
+     run_gdn_step},
+    {"gdn.conv",
+     R"({"in":[["x","bf16","[B,T,C]"],["conv_w","bf16","[C,KW]"],["conv_in","bf16","[B,KW-1,C]"]],"out":[["y","bf16","[B,T,C]"],["conv_out","bf16","[B,KW-1,C]"]]})",
+     run_gdn_conv},
+    {"linear",
+     R"({"in":[["x","bf16","[T,K]"],["w","u8|e4m3|bf16","[N,K/2]|[N,K]"],["s","u8|f32","[N,K/32]|[N] optional"],["bias","f32","[N] optional"]],"out":[["out","bf16|f32","[T,N]"]]})",
+     run_linear},
+};
+static const int kNumRoles = int(sizeof(kRoles) / sizeof(kRoles[0]));
+
+static const RoleDef* find_role(const char* role) {
+  if (!role) return nullptr;
+  for (int i = 0; i < kNumRoles; ++i)
+    if (strcmp(kRoles[i].name, role) == 0) return &kRoles[i];
+  return nullptr;
+}
+
+}  // namespace q35
+
+using namespace q35;
+
+extern "C" {
+
+int q35_run(const char* role, const q35_io* ios, int n_io, void* stream) {
+  g_err.clear();
+  const RoleDef* r = find_role(role);
+  if (!r) return fail(Q35_ERR_ROLE, "unknown role '%s'", role ? role : "(null)");
+  if (n_io < 0 || (n_io > 0 && !ios)) return fail(Q35_ERR_MISSING, "bad io table");
+  Call c{ios, n_io, static_cast<cudaStream_t>(stream), false, 0};
+  return r->run(c);
+}
+
+int64_t q35_workspace_bytes(const char* role, const q35_io* ios, int n_io) {
+  g_err.clear();
+  const RoleDef* r = find_role(role);
+  if (!r) return -int64_t(fail(Q35_ERR_ROLE, "unknown role '%s'", role ? role : "(null)"));
+  Call c{ios, n_io, nullptr, true, 0};
+  int st = r->run(c);
+  if (st) return -int64_t(st);
+  return c.ws_need;
+}
+
+int q35_io_table(const char* role, char* buf, size_t cap) {
+  const RoleDef* r = find_role(role);
+  if (!r) return -fail(Q35_ERR_ROLE, "unknown role '%s'", role ? role : "(null)");
+  size_t len = strlen(r->io_json);
+  if (buf && cap) {
+    size_t ncopy = len < cap - 1 ? len : cap - 1;
+    memcpy(buf, r->io_json, ncopy);
+    buf[ncopy] = 0;
+  }
+  return int(len);
+}
+
+int q35_role_count(void) { return kNumRoles; }
+const char* q35_role_name(int i) { return (i >= 0 && i < kNumRoles) ? kRoles[i].name : nullptr; }
+const char* q35_last_error(void) { return g_err.c_str(); }
+
+int q35_device_status(void* stream) {
+  int* p = device_status_ptr();
+  int v = 0, zero = 0;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (!p) return -1;
+  if (cudaMemcpyAsync(&v, p, sizeof v, cudaMemcpyDeviceToHost, s) != cudaSuccess) return -1;
+  if (cudaMemcpyAsync(p, &zero, sizeof zero, cudaMemcpyHostToDevice, s) != cudaSuccess) return -1;
+  if (cudaStreamSynchronize(s) != cudaSuccess) return -1;
+  return v;
+}
+
+int q35_version(void) { return 1; }
+
+}  // extern "C"

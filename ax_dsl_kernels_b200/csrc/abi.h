@@ -1,0 +1,88 @@
+// Host-side plumbing shared by the kernel launchers: tensors bound by name, contract checks, error text.
+#pragma once
+#include <cuda_runtime.h>
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+#include "../../include/q35b200.h"
+
+namespace q35 {
+
+int fail(int code, const char* fmt, ...);
+
+struct Tensor {
+  void* p = nullptr;
+  size_t bytes = 0;
+  int dtype = 0;
+  int nd = 0;
+  int64_t s[Q35_MAX_DIMS] = {0, 0, 0, 0, 0, 0};
+  bool present = false;
+  int64_t numel() const {
+    int64_t n = 1;
+    for (int i = 0; i < nd; ++i) n *= s[i];
+    return n;
+  }
+  template <class T> T* as() const { return reinterpret_cast<T*>(p); }
+};
+
+constexpr unsigned M(int dtype) { return 1u << dtype; }
+constexpr unsigned M_BYTES = M(Q35_U8) | M(Q35_FP4);   // FP4 pairs / E8M0 scales
+constexpr unsigned M_FP8 = M(Q35_E4M3) | M(Q35_U8);
+
+// One q35_run / q35_workspace_bytes invocation.
+struct Call {
+  const q35_io* ios;
+  int n;
+  cudaStream_t stream;
+  bool dry;            // workspace query: validate shapes, launch nothing
+  int64_t ws_need;     // set by the launcher
+  // Finds `name`; checks dtype against the mask and bytes against the shape.  FP4 logical tensors are normalised
+  // to their byte view (last dim halved).  Returns 0 or a q35_status.
+  int get(const char* name, unsigned dtype_mask, Tensor* out, bool required = true) const;
+  // Workspace handling: records the need; when running, checks the bound `workspace` tensor is big enough.
+  int workspace(int64_t need, Tensor* ws);
+};
+
+struct RoleDef {
+  const char* name;
+  const char* io_json;  // symbolic IO table
+  int (*run)(Call&);
+};
+
+int elem_bits(int dtype);
+
+// device status word shared by all kernels (see q35_device_status)
+int* device_status_ptr();
+
+#define Q35_REQUIRE(cond, code, ...) \
+  do {                               \
+    if (!(cond)) return ::q35::fail(code, __VA_ARGS__); \
+  } while (0)
+#define Q35_TRY(expr)        \
+  do {                       \
+    int _st = (expr);        \
+    if (_st) return _st;     \
+  } while (0)
+#define Q35_CUDA_LAUNCH_CHECK(what)                                                        \
+  do {                                                                                     \
+    cudaError_t _e = cudaGetLastError();                                                   \
+    if (_e != cudaSuccess) return ::q35::fail(Q35_ERR_CUDA, "%s: %s", what, cudaGetErrorString(_e)); \
+  } while (0)
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+// launchers (one per role), defined next to their kernels
+int run_moe_route(Call&);
+int run_moe_pre(Call&);
+int run_moe_experts(Call&);
+int run_moe_slots(Call&);
+int run_moe_combine(Call&);
+int run_moe_permute(Call&);
+int run_attn_paged_decode(Call&);
+int run_attn_kv_write(Call&);
+int run_gdn_step(Call&);
+int run_gdn_conv(Call&);
+int run_linear(Call&);
+
+}  // namespace q35

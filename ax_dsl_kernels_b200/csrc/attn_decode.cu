@@ -1,0 +1,532 @@
+// Paged flash-attention decode (one query token per sequence) over a page-table KV cache.
+//
+// Interface of the reference's sgl line: paged_kv_cache [pages, 2, P, HKV, D], indptr [B+1], indices, last_page_len,
+// valid_kv_len = (n_pages - 1) * P + last_page_len
+// (models/qwen35_35b_a3b/sgl/python/sgl_kernel_axera/attention/flash_attn.py:1421-1596, 1991-2085, 2354-2358);
+// golden: models/qwen35_35b_a3b/sgl/tests/test_qwen35_runtime.py:57-93.  The reference splits the KV blocks of one
+// request over its 4 cores and merges [m, l, o] partials (models/qwen35_2b/whole/src/q35_layer_mc.py:308-379); here
+// the same split-KV scheme is applied to a whole batch.
+//
+// Bound: HBM (K and V are read once; 8 query heads share each KV head, so ~8 flop per byte).
+// Work = all 64-key tiles of all (sequence, KV head) segments laid end to end; it is cut into equal contiguous
+// ranges, one per CTA (one CTA per SM), so every SM streams the same number of bytes whatever the mix of sequence
+// lengths.  Inside a CTA each of the 4 warps owns 16 of a tile's 64 keys and runs its own 3-stage cp.async ring
+// (16-byte chunks, XOR-swizzled rows), with no block-wide barrier in the loop.  Scores are computed transposed
+// (S^T = K Q^T: 16 keys x 8 heads per mma) so the 8 query heads of a KV head fill the n = 8 side exactly and the
+// output accumulator O^T [D x 8 heads] costs 64 registers instead of 128.
+#include "abi.h"
+#include "common.cuh"
+
+namespace q35 {
+
+constexpr int AT_TILE = 64;      // keys per tile
+constexpr int AT_WKEYS = 16;     // keys per warp per tile
+constexpr int AT_GMAX = 8;       // query heads per KV head handled by one mma column block
+constexpr float LOG2E = 1.4426950408889634f;
+
+struct AttnPlan {     // header of the workspace, written by the plan kernel
+  int total_tiles;    // W
+  int tiles_per_cta;  // q
+  int pad[62];
+};
+
+struct AttnArgs {
+  const void* q;        // [B, HQ, D] bf16
+  const void* cache;    // [pages, 2, P, HKV, D]
+  const int* indptr;
+  const int* indices;
+  const int* last_page_len;
+  const float* sm_scale;   // optional [1]
+  const float* kv_scale;   // optional [2, HKV] (FP8 cache)
+  const __nv_bfloat16* k_new;  // optional [B, HKV, D]
+  const __nv_bfloat16* v_new;
+  __nv_bfloat16* out;   // [B, HQ, D]
+  int B, HQ, HKV, G, P, num_pages, n_indices, n_cta;
+  // workspace
+  AttnPlan* plan;
+  int* seg_start;   // [B * HKV + 1]
+  int* ctx;         // [B]
+  float* part_ml;   // [slots][2][8]
+  float* part_o;    // [slots][8][D]
+  int* status;
+};
+
+// one CTA: context lengths, tiles per segment, exclusive prefix in (b, kvh) order
+__global__ void __launch_bounds__(1024) attn_plan_kernel(AttnArgs a) {
+  __shared__ int s_part[1024];
+  const int tid = threadIdx.x;
+  const int per = (a.B + 1023) / 1024;
+  const int b0 = tid * per, b1 = min(a.B, b0 + per);
+  int local = 0;
+  for (int b = b0; b < b1; ++b) {
+    const int np = a.indptr[b + 1] - a.indptr[b];
+    int ctx = np > 0 ? (np - 1) * a.P + a.last_page_len[b] : 0;
+    if (np < 0 || ctx < 0 || a.indptr[b + 1] > a.n_indices || a.last_page_len[b] > a.P) {
+      atomicOr(a.status, DS_BAD_PAGE);
+      ctx = 0;
+    }
+    a.ctx[b] = ctx;
+    local += (ctx + AT_TILE - 1) / AT_TILE;
+  }
+  s_part[tid] = local;
+  __syncthreads();
+  // inclusive scan (Hillis-Steele) over 1024 partials
+  for (int o = 1; o < 1024; o <<= 1) {
+    const int v = tid >= o ? s_part[tid - o] : 0;
+    __syncthreads();
+    s_part[tid] += v;
+    __syncthreads();
+  }
+  int run = s_part[tid] - local;  // exclusive prefix of tiles (per KV head) before b0
+  for (int b = b0; b < b1; ++b) {
+    const int nt = (a.ctx[b] + AT_TILE - 1) / AT_TILE;
+    for (int h = 0; h < a.HKV; ++h) a.seg_start[b * a.HKV + h] = run * a.HKV + h * nt;
+    run += nt;
+  }
+  if (tid == 1023) {
+    const int W = s_part[1023] * a.HKV;
+    a.seg_start[a.B * a.HKV] = W;
+    a.plan->total_tiles = W;
+    a.plan->tiles_per_cta = max(1, (W + a.n_cta - 1) / a.n_cta);
+  }
+}
+
+template <int D, bool FP8>
+struct AttnCfg {
+  static constexpr int ELT = FP8 ? 1 : 2;
+  static constexpr int STAGES = FP8 ? 6 : 3;    // same bytes in flight for both cache types
+  static constexpr int ROWB = D * ELT;            // bytes of one key row of one head
+  static constexpr int CPR = ROWB / 16;           // 16-byte chunks per row
+  static constexpr int KV_BYTES = AT_WKEYS * ROWB;  // K (or V) bytes per warp per stage
+  static constexpr int STAGE_BYTES = 2 * KV_BYTES;
+  static constexpr int WARP_BYTES = STAGES * STAGE_BYTES;
+  static constexpr int SMEM = 4 * WARP_BYTES;
+  static constexpr int LD_PER_LANE = AT_WKEYS * CPR / 32;
+};
+
+__device__ __forceinline__ uint32_t cvt_e4m3x2_f16x2(uint32_t two_bytes) {
+  uint32_t d;
+  asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(d) : "h"((unsigned short)two_bytes));
+  return d;
+}
+
+template <int D, bool FP8>
+__global__ void __launch_bounds__(128, 1) attn_decode_kernel(const AttnArgs a) {
+  using C = AttnCfg<D, FP8>;
+  constexpr int AT_STAGES = C::STAGES;
+  extern __shared__ __align__(128) uint8_t smem[];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int r = lane >> 2, c = lane & 3;
+  const uint32_t sbase = smem_u32(smem) + warp * C::WARP_BYTES;
+
+  const int W = a.plan->total_tiles, q_per = a.plan->tiles_per_cta;
+  const int S = a.B * a.HKV;
+  int g = blockIdx.x * q_per;
+  const int g_end = min(W, g + q_per);
+  if (g >= g_end) return;
+  // segment containing tile g: last s with seg_start[s] <= g
+  int lo = 0, hi = S;
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (a.seg_start[mid] <= g) lo = mid; else hi = mid;
+  }
+  int s = lo;
+  const float scale_log2 = (a.sm_scale ? a.sm_scale[0] : rsqrtf(float(D))) * LOG2E;
+  const uint8_t* cache = static_cast<const uint8_t*>(a.cache);
+  const size_t row_stride = size_t(a.HKV) * C::ROWB;  // bytes between consecutive keys of a page plane
+
+  while (g < g_end) {
+    while (a.seg_start[s + 1] <= g) ++s;  // skip empty segments
+    const int b = s / a.HKV, kvh = s % a.HKV;
+    const int seg0 = a.seg_start[s];
+    const int t_begin = g - seg0;
+    const int t_end = min(g_end, a.seg_start[s + 1]) - seg0;
+    const int ctx = a.ctx[b];
+    const int page0 = a.indptr[b];
+
+    // query fragments: B operand of S^T = K Q^T, heads on the n side.  bf16 cache: natural k order.  FP8 cache:
+    // f16 fragments in the k order the byte-wise K fragments come out in (4 consecutive channels per lane).
+    uint32_t qf[D / 16][2];
+    float k_mul = 1.f, v_mul = 1.f;  // FP8 dequantisation factors of this KV head
+    {
+      const __nv_bfloat16* qp = static_cast<const __nv_bfloat16*>(a.q) + (size_t(b) * a.HQ + kvh * a.G + r) * D;
+      const bool hv = r < a.G;
+      if constexpr (!FP8) {
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+          qf[ks][0] = hv ? *reinterpret_cast<const uint32_t*>(qp + ks * 16 + 2 * c) : 0u;
+          qf[ks][1] = hv ? *reinterpret_cast<const uint32_t*>(qp + ks * 16 + 8 + 2 * c) : 0u;
+        }
+      } else {
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+          uint2 raw = make_uint2(0u, 0u);
+          if (hv) raw = *reinterpret_cast<const uint2*>(qp + ks * 16 + 4 * c);
+          qf[ks][0] = pack_f16(bf16lo(raw.x), bf16hi(raw.x));
+          qf[ks][1] = pack_f16(bf16lo(raw.y), bf16hi(raw.y));
+        }
+        k_mul = a.kv_scale ? a.kv_scale[kvh] : 0.125f;
+        v_mul = a.kv_scale ? a.kv_scale[a.HKV + kvh] : 0.125f;
+      }
+    }
+    const float seg_scale = scale_log2 * k_mul;
+    float oacc[D / 16][4];
+#pragma unroll
+    for (int mt = 0; mt < D / 16; ++mt) oacc[mt][0] = oacc[mt][1] = oacc[mt][2] = oacc[mt][3] = 0.f;
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+
+    auto issue = [&](int t) {  // t: tile index inside the sequence
+      const int kk = t * AT_TILE + warp * AT_WKEYS;
+      if (t < t_end && kk < ctx) {
+        const int pl = kk / a.P, ro = kk % a.P;
+        int page = a.indices[page0 + pl];
+        if (page < 0 || page >= a.num_pages) {
+          if (lane == 0) atomicOr(a.status, DS_BAD_PAGE);
+          page = 0;
+        }
+        const uint8_t* kb = cache + ((size_t(page) * 2 + 0) * a.P + ro) * row_stride + size_t(kvh) * C::ROWB;
+        const uint8_t* vb = cache + ((size_t(page) * 2 + 1) * a.P + ro) * row_stride + size_t(kvh) * C::ROWB;
+        const uint32_t st = sbase + ((t - t_begin) % AT_STAGES) * C::STAGE_BYTES;
+#pragma unroll
+        for (int j = 0; j < C::LD_PER_LANE; ++j) {
+          const int ci = lane + 32 * j;
+          const int key = ci / C::CPR, ch = ci % C::CPR;
+          const uint32_t off = key * C::ROWB + ((ch ^ (key & 7)) << 4);
+          cp_async_16(st + off, kb + size_t(key) * row_stride + ch * 16);
+          cp_async_16(st + C::KV_BYTES + off, vb + size_t(key) * row_stride + ch * 16);
+        }
+      }
+      cp_async_commit();
+    };
+
+#pragma unroll
+    for (int p = 0; p < AT_STAGES - 1; ++p) issue(t_begin + p);
+
+    for (int t = t_begin; t < t_end; ++t) {
+      issue(t + AT_STAGES - 1);
+      cp_async_wait<AT_STAGES - 1>();
+      __syncwarp();
+      const int kk = t * AT_TILE + warp * AT_WKEYS;
+      if (kk < ctx) {
+        const int valid = min(AT_WKEYS, ctx - kk);
+        const uint32_t st = sbase + ((t - t_begin) % AT_STAGES) * C::STAGE_BYTES;
+        if (valid < AT_WKEYS) {  // rows past the context may hold anything (NaN bits included): clear V
+          for (int idx = lane; idx < (AT_WKEYS - valid) * C::CPR; idx += 32) {
+            const uint32_t addr = st + C::KV_BYTES + (valid + idx / C::CPR) * C::ROWB + ((idx % C::CPR) << 4);
+            asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(addr), "r"(0u));
+          }
+          __syncwarp();
+        }
+        float sacc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+        {
+          const int key = (lane & 7) + (((lane >> 3) & 1) << 3);
+          const uint32_t rowa = st + key * C::ROWB;
+          if constexpr (!FP8) {
+#pragma unroll
+            for (int ks = 0; ks < D / 16; ++ks) {
+              const int ch = 2 * ks + (lane >> 4);
+              uint32_t a0, a1, a2, a3;
+              ldmatrix_x4(rowa + ((ch ^ (key & 7)) << 4), a0, a1, a2, a3);
+              mma_bf16_16816(sacc[ks & 1], a0, a1, a2, a3, qf[ks][0], qf[ks][1]);
+            }
+          } else {
+#pragma unroll
+            for (int kp = 0; kp < D / 32; ++kp) {  // 32 channels: two mma over bytes taken as b16 pairs
+              const int ch = 2 * kp + (lane >> 4);
+              uint32_t r0, r1, r2, r3;
+              ldmatrix_x4(rowa + ((ch ^ (key & 7)) << 4), r0, r1, r2, r3);
+              mma_f16_16816(sacc[0], cvt_e4m3x2_f16x2(r0), cvt_e4m3x2_f16x2(r1), cvt_e4m3x2_f16x2(r0 >> 16),
+                            cvt_e4m3x2_f16x2(r1 >> 16), qf[2 * kp][0], qf[2 * kp][1]);
+              mma_f16_16816(sacc[1], cvt_e4m3x2_f16x2(r2), cvt_e4m3x2_f16x2(r3), cvt_e4m3x2_f16x2(r2 >> 16),
+                            cvt_e4m3x2_f16x2(r3 >> 16), qf[2 * kp + 1][0], qf[2 * kp + 1][1]);
+            }
+          }
+        }
+        float sc[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int key = r + ((i >> 1) << 3);
+          sc[i] = key < valid ? (sacc[0][i] + sacc[1][i]) * seg_scale : -INFINITY;
+        }
+        float mt2[2] = {fmaxf(sc[0], sc[2]), fmaxf(sc[1], sc[3])};
+#pragma unroll
+        for (int o = 4; o < 32; o <<= 1) {
+          mt2[0] = fmaxf(mt2[0], __shfl_xor_sync(0xffffffffu, mt2[0], o));
+          mt2[1] = fmaxf(mt2[1], __shfl_xor_sync(0xffffffffu, mt2[1], o));
+        }
+        float alpha[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const float mn = fmaxf(m_run[h], mt2[h]);  // finite: key 0 of the tile is always valid
+          alpha[h] = exp2f(m_run[h] - mn);
+          m_run[h] = mn;
+        }
+        const float p0 = exp2f(sc[0] - m_run[0]), p1 = exp2f(sc[1] - m_run[1]);
+        const float p2 = exp2f(sc[2] - m_run[0]), p3 = exp2f(sc[3] - m_run[1]);
+        l_run[0] = l_run[0] * alpha[0] + p0 + p2;
+        l_run[1] = l_run[1] * alpha[1] + p1 + p3;
+        if (alpha[0] != 1.f || alpha[1] != 1.f) {
+#pragma unroll
+          for (int mt = 0; mt < D / 16; ++mt) {
+            oacc[mt][0] *= alpha[0]; oacc[mt][1] *= alpha[1];
+            oacc[mt][2] *= alpha[0]; oacc[mt][3] *= alpha[1];
+          }
+        }
+        if constexpr (!FP8) {
+          const uint32_t pb0 = movmatrix_trans(pack_bf16(p0, p1));
+          const uint32_t pb1 = movmatrix_trans(pack_bf16(p2, p3));
+          const int key = (lane & 7) + ((lane >> 4) << 3);
+          const uint32_t rowa = st + C::KV_BYTES + key * C::ROWB;
+#pragma unroll
+          for (int mt = 0; mt < D / 16; ++mt) {
+            const int ch = 2 * mt + ((lane >> 3) & 1);
+            uint32_t a0, a1, a2, a3;
+            ldmatrix_x4_trans(rowa + ((ch ^ (key & 7)) << 4), a0, a1, a2, a3);
+            mma_bf16_16816(oacc[mt], a0, a1, a2, a3, pb0, pb1);
+          }
+        } else {
+          // transposed b16 loads keep byte PAIRS (d, d+1) together: a lane gets {V[2c][2r], V[2c][2r+1], V[2c+1][2r],
+          // V[2c+1][2r+1]}; bytes (0,2) / (1,3) are the key pairs of channels 2r / 2r+1.  So mma row r holds channel
+          // 16 mt + 2r and mma row r + 8 holds channel 16 mt + 2r + 1 (undone when the partial is written).
+          const uint32_t pb0 = movmatrix_trans(pack_f16(p0, p1));
+          const uint32_t pb1 = movmatrix_trans(pack_f16(p2, p3));
+          const int key = lane & 15;
+          const uint32_t rowa = st + C::KV_BYTES + key * C::ROWB;
+#pragma unroll
+          for (int mp = 0; mp < D / 32; ++mp) {
+            const int ch = 2 * mp + (lane >> 4);
+            uint32_t r0, r1, r2, r3;  // (keys 0-7, chunk 2mp) (keys 8-15, 2mp) (keys 0-7, 2mp+1) (keys 8-15, 2mp+1)
+            ldmatrix_x4_trans(rowa + ((ch ^ (key & 7)) << 4), r0, r1, r2, r3);
+            mma_f16_16816(oacc[2 * mp], cvt_e4m3x2_f16x2(__byte_perm(r0, 0, 0x4420)),
+                          cvt_e4m3x2_f16x2(__byte_perm(r0, 0, 0x4431)), cvt_e4m3x2_f16x2(__byte_perm(r1, 0, 0x4420)),
+                          cvt_e4m3x2_f16x2(__byte_perm(r1, 0, 0x4431)), pb0, pb1);
+            mma_f16_16816(oacc[2 * mp + 1], cvt_e4m3x2_f16x2(__byte_perm(r2, 0, 0x4420)),
+                          cvt_e4m3x2_f16x2(__byte_perm(r2, 0, 0x4431)), cvt_e4m3x2_f16x2(__byte_perm(r3, 0, 0x4420)),
+                          cvt_e4m3x2_f16x2(__byte_perm(r3, 0, 0x4431)), pb0, pb1);
+          }
+        }
+      }
+      __syncwarp();
+    }
+    cp_async_wait<0>();
+
+    // partial of this (segment, CTA, warp): slot = (s + cta) * 4 + warp
+    {
+#pragma unroll
+      for (int o = 4; o < 32; o <<= 1) {
+        l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], o);
+        l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], o);
+      }
+      const size_t slot = size_t(s + blockIdx.x) * 4 + warp;
+      float* ml = a.part_ml + slot * 16;
+      if (r == 0) {
+        ml[2 * c] = m_run[0]; ml[2 * c + 1] = m_run[1];
+        ml[8 + 2 * c] = l_run[0]; ml[8 + 2 * c + 1] = l_run[1];
+      }
+      float* po = a.part_o + slot * (AT_GMAX * D);
+#pragma unroll
+      for (int mt = 0; mt < D / 16; ++mt) {
+        const int d0 = FP8 ? mt * 16 + 2 * r : mt * 16 + r;      // channel of mma row r
+        const int d1 = FP8 ? mt * 16 + 2 * r + 1 : mt * 16 + r + 8;  // channel of mma row r + 8
+        po[(2 * c) * D + d0] = oacc[mt][0] * v_mul;
+        po[(2 * c + 1) * D + d0] = oacc[mt][1] * v_mul;
+        po[(2 * c) * D + d1] = oacc[mt][2] * v_mul;
+        po[(2 * c + 1) * D + d1] = oacc[mt][3] * v_mul;
+      }
+    }
+    g = seg0 + t_end;
+  }
+}
+
+// out[b, h] = merge of the partials of segment (b, h / G) (+ the current token's own k / v) -> bf16
+template <int D>
+__global__ void __launch_bounds__(D / 2) attn_merge_kernel(const AttnArgs a) {
+  const int bh = blockIdx.x;
+  const int b = bh / a.HQ, h = bh % a.HQ;
+  const int kvh = h / a.G, gq = h % a.G;
+  const int s = b * a.HKV + kvh;
+  const int tid = threadIdx.x;  // two channels per thread
+  const int q_per = a.plan->tiles_per_cta;
+  const int seg0 = a.seg_start[s], seg1 = a.seg_start[s + 1];
+  float M = -INFINITY, L = 0.f, o0 = 0.f, o1 = 0.f;
+  if (seg1 > seg0) {
+    const int i0 = seg0 / q_per, i1 = (seg1 - 1) / q_per;
+    for (int i = i0; i <= i1; ++i) {
+      for (int w = 0; w < 4; ++w) {
+        const size_t slot = size_t(s + i) * 4 + w;
+        const float m = a.part_ml[slot * 16 + gq];
+        const float l = a.part_ml[slot * 16 + 8 + gq];
+        if (l <= 0.f || m == -INFINITY) continue;
+        const float mn = fmaxf(M, m);
+        const float fa = exp2f(M - mn), fb = exp2f(m - mn);
+        const float2 po = *reinterpret_cast<const float2*>(a.part_o + slot * (AT_GMAX * D) + gq * D + 2 * tid);
+        L = L * fa + l * fb;
+        o0 = o0 * fa + po.x * fb;
+        o1 = o1 * fa + po.y * fb;
+        M = mn;
+      }
+    }
+  }
+  if (a.k_new) {  // the current token, taken from its own k / v row instead of the cache
+    const float scale_log2 = (a.sm_scale ? a.sm_scale[0] : rsqrtf(float(D))) * LOG2E;
+    const __nv_bfloat16* qp = static_cast<const __nv_bfloat16*>(a.q) + (size_t(b) * a.HQ + h) * D;
+    const __nv_bfloat16* kp = a.k_new + (size_t(b) * a.HKV + kvh) * D;
+    const __nv_bfloat16* vp = a.v_new + (size_t(b) * a.HKV + kvh) * D;
+    float dot = __bfloat162float(qp[2 * tid]) * __bfloat162float(kp[2 * tid]) +
+                __bfloat162float(qp[2 * tid + 1]) * __bfloat162float(kp[2 * tid + 1]);
+    __shared__ float s_red[32];
+    dot = warp_sum(dot);
+    if ((tid & 31) == 0) s_red[tid >> 5] = dot;
+    __syncthreads();
+    float tot = 0.f;
+    for (int i = 0; i < (D / 2 + 31) / 32; ++i) tot += s_red[i];
+    const float m = tot * scale_log2;
+    const float mn = fmaxf(M, m);
+    const float fa = exp2f(M - mn), fb = exp2f(m - mn);
+    L = L * fa + fb;
+    o0 = o0 * fa + __bfloat162float(vp[2 * tid]) * fb;
+    o1 = o1 * fa + __bfloat162float(vp[2 * tid + 1]) * fb;
+  }
+  const float inv = L > 0.f ? 1.f / L : 0.f;
+  *reinterpret_cast<uint32_t*>(a.out + (size_t(b) * a.HQ + h) * D + 2 * tid) = pack_bf16(o0 * inv, o1 * inv);
+}
+
+// attn.kv_write: the current token's K / V rows into the cache at (page, offset)
+// (store_paged_kv, flash_attn.py:53-84; FP8: e4m3(8 x), models/qwen38_27b/decode/q35_group.py:244-249, or
+// e4m3(x / scale_h) with a per-head scale)
+__global__ void attn_kv_write_kernel(const __nv_bfloat16* __restrict__ k_new, const __nv_bfloat16* __restrict__ v_new,
+                                     const int* __restrict__ loc, const float* kv_scale, void* cache, int B, int HKV,
+                                     int D, int P, int num_pages, int fp8, int* status) {
+  const int b = blockIdx.x;
+  const int page = loc[2 * b], off = loc[2 * b + 1];
+  if (page < 0 || page >= num_pages || off < 0 || off >= P) {
+    if (threadIdx.x == 0) atomicOr(status, DS_BAD_PAGE);
+    return;
+  }
+  const int n = HKV * D;
+  for (int i = threadIdx.x; i < 2 * n; i += blockDim.x) {
+    const int kv = i / n, j = i % n;
+    const __nv_bfloat16 val = kv ? v_new[size_t(b) * n + j] : k_new[size_t(b) * n + j];
+    const size_t dst = ((size_t(page) * 2 + kv) * P + off) * n + j;
+    if (fp8) {
+      const float sc = kv_scale ? 1.f / kv_scale[kv * HKV + j / D] : 8.f;
+      static_cast<__nv_fp8_e4m3*>(cache)[dst] = __nv_fp8_e4m3(__bfloat162float(val) * sc);
+    } else {
+      static_cast<__nv_bfloat16*>(cache)[dst] = val;
+    }
+  }
+}
+
+int run_attn_kv_write(Call& c) {
+  Tensor k, v, loc, cache, sc;
+  Q35_TRY(c.get("k_new", M(Q35_BF16), &k));
+  Q35_TRY(c.get("v_new", M(Q35_BF16), &v));
+  Q35_TRY(c.get("cache_location", M(Q35_I32), &loc));
+  Q35_TRY(c.get("paged_kv_cache", M(Q35_BF16) | M_FP8, &cache));
+  Q35_TRY(c.get("kv_scale", M(Q35_F32), &sc, false));
+  Q35_REQUIRE(cache.nd == 5 && cache.s[1] == 2 && k.nd == 3, Q35_ERR_SHAPE,
+              "attn.kv_write: cache [pages, 2, P, HKV, D], k_new [B, HKV, D]");
+  const int64_t B = k.s[0], HKV = cache.s[3], D = cache.s[4], P = cache.s[2];
+  Q35_REQUIRE(k.s[1] == HKV && k.s[2] == D && v.numel() == k.numel() && loc.numel() == 2 * B, Q35_ERR_SHAPE,
+              "attn.kv_write: shapes");
+  Q35_REQUIRE(!sc.present || sc.numel() == 2 * HKV, Q35_ERR_SHAPE, "attn.kv_write: kv_scale [2, HKV]");
+  c.ws_need = 0;
+  if (c.dry || B == 0) return 0;
+  attn_kv_write_kernel<<<unsigned(B), 256, 0, c.stream>>>(
+      k.as<__nv_bfloat16>(), v.as<__nv_bfloat16>(), loc.as<int>(), sc.present ? sc.as<float>() : nullptr, cache.p,
+      int(B), int(HKV), int(D), int(P), int(cache.s[0]), cache.dtype != Q35_BF16, device_status_ptr());
+  Q35_CUDA_LAUNCH_CHECK("attn.kv_write");
+  return 0;
+}
+
+static int sm_count() {
+  static int n = 0;
+  if (!n) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (n <= 0) n = 148;
+  }
+  return n;
+}
+
+template <int D, bool FP8>
+static int launch_attn(const AttnArgs& a, cudaStream_t stream) {
+  using C = AttnCfg<D, FP8>;
+  static bool attr_done = false;
+  if (!attr_done) {
+    cudaFuncSetAttribute(attn_decode_kernel<D, FP8>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM);
+    attr_done = true;
+  }
+  attn_plan_kernel<<<1, 1024, 0, stream>>>(a);
+  Q35_CUDA_LAUNCH_CHECK("attn plan");
+  attn_decode_kernel<D, FP8><<<unsigned(a.n_cta), 128, C::SMEM, stream>>>(a);
+  Q35_CUDA_LAUNCH_CHECK("attn decode");
+  attn_merge_kernel<D><<<unsigned(a.B * a.HQ), D / 2, 0, stream>>>(a);
+  Q35_CUDA_LAUNCH_CHECK("attn merge");
+  return 0;
+}
+
+int run_attn_paged_decode(Call& c) {
+  Tensor q, cache, indptr, indices, lpl, scale, kvs, kn, vn, out, ws;
+  Q35_TRY(c.get("q", M(Q35_BF16), &q));
+  Q35_TRY(c.get("paged_kv_cache", M(Q35_BF16) | M_FP8, &cache));
+  Q35_TRY(c.get("indptr", M(Q35_I32), &indptr));
+  Q35_TRY(c.get("indices", M(Q35_I32), &indices));
+  Q35_TRY(c.get("last_page_len", M(Q35_I32), &lpl));
+  Q35_TRY(c.get("sm_scale", M(Q35_F32), &scale, false));
+  Q35_TRY(c.get("kv_scale", M(Q35_F32), &kvs, false));
+  Q35_TRY(c.get("k_new", M(Q35_BF16), &kn, false));
+  Q35_TRY(c.get("v_new", M(Q35_BF16), &vn, false));
+  Q35_TRY(c.get("out", M(Q35_BF16), &out));
+  Q35_REQUIRE(q.nd == 3 && cache.nd == 5 && cache.s[1] == 2, Q35_ERR_SHAPE,
+              "attn.paged_decode: q [B, HQ, D], paged_kv_cache [pages, 2, P, HKV, D]");
+  const int64_t B = q.s[0], HQ = q.s[1], D = q.s[2], P = cache.s[2], HKV = cache.s[3];
+  Q35_REQUIRE(cache.s[4] == D && HKV > 0 && HQ % HKV == 0, Q35_ERR_SHAPE, "attn.paged_decode: head shapes");
+  const int64_t G = HQ / HKV;
+  Q35_REQUIRE(G <= AT_GMAX, Q35_ERR_UNSUPPORTED, "attn.paged_decode: at most 8 query heads per KV head (got %lld)",
+              (long long)G);
+  Q35_REQUIRE(D == 64 || D == 128 || D == 256, Q35_ERR_UNSUPPORTED, "attn.paged_decode: head_dim must be 64/128/256");
+  Q35_REQUIRE(P % 16 == 0 && P >= 16, Q35_ERR_UNSUPPORTED, "attn.paged_decode: page size must be a multiple of 16");
+  Q35_REQUIRE(indptr.numel() == B + 1 && lpl.numel() >= B, Q35_ERR_SHAPE, "attn.paged_decode: indptr [B+1], last_page_len [B]");
+  Q35_REQUIRE(out.numel() == B * HQ * D, Q35_ERR_SHAPE, "attn.paged_decode: out [B, HQ, D]");
+  Q35_REQUIRE(kn.present == vn.present, Q35_ERR_MISSING, "attn.paged_decode: k_new and v_new go together");
+  Q35_REQUIRE(!kn.present || (kn.numel() == B * HKV * D && vn.numel() == B * HKV * D), Q35_ERR_SHAPE,
+              "attn.paged_decode: k_new / v_new [B, HKV, D]");
+  Q35_REQUIRE(!kvs.present || kvs.numel() == 2 * HKV, Q35_ERR_SHAPE, "attn.paged_decode: kv_scale [2, HKV]");
+  const bool fp8 = cache.dtype != Q35_BF16;
+  Q35_REQUIRE(!fp8 || D == 256 || D == 128, Q35_ERR_UNSUPPORTED, "attn.paged_decode: FP8 cache needs head_dim 128/256");
+  const int n_cta = sm_count();
+  const int64_t S = B * HKV, slots = (S + n_cta) * 4;
+  int64_t off = 0;
+  auto take = [&](int64_t bytes) { const int64_t o = off; off = (off + bytes + 255) / 256 * 256; return o; };
+  const int64_t o_plan = take(sizeof(AttnPlan)), o_seg = take((S + 1) * 4), o_ctx = take(B * 4),
+                o_ml = take(slots * 16 * 4), o_po = take(slots * AT_GMAX * D * 4);
+  Q35_TRY(c.workspace(off, &ws));
+  if (c.dry || B == 0) return 0;
+  Q35_REQUIRE(aligned16(q.p) && aligned16(cache.p) && aligned16(out.p), Q35_ERR_ALIGN,
+              "attn.paged_decode: pointers must be 16-byte aligned");
+  AttnArgs a{};
+  a.q = q.p; a.cache = cache.p; a.indptr = indptr.as<int>(); a.indices = indices.as<int>();
+  a.last_page_len = lpl.as<int>();
+  a.sm_scale = scale.present ? scale.as<float>() : nullptr;
+  a.kv_scale = kvs.present ? kvs.as<float>() : nullptr;
+  a.k_new = kn.present ? kn.as<__nv_bfloat16>() : nullptr;
+  a.v_new = vn.present ? vn.as<__nv_bfloat16>() : nullptr;
+  a.out = out.as<__nv_bfloat16>();
+  a.B = int(B); a.HQ = int(HQ); a.HKV = int(HKV); a.G = int(G); a.P = int(P);
+  a.num_pages = int(cache.s[0]); a.n_indices = int(indices.numel()); a.n_cta = n_cta;
+  uint8_t* w = ws.as<uint8_t>();
+  a.plan = reinterpret_cast<AttnPlan*>(w + o_plan);
+  a.seg_start = reinterpret_cast<int*>(w + o_seg);
+  a.ctx = reinterpret_cast<int*>(w + o_ctx);
+  a.part_ml = reinterpret_cast<float*>(w + o_ml);
+  a.part_o = reinterpret_cast<float*>(w + o_po);
+  a.status = device_status_ptr();
+  if (fp8) return D == 128 ? launch_attn<128, true>(a, c.stream) : launch_attn<256, true>(a, c.stream);
+  if (D == 64) return launch_attn<64, false>(a, c.stream);
+  if (D == 128) return launch_attn<128, false>(a, c.stream);
+  return launch_attn<256, false>(a, c.stream);
+}
+
+}  // namespace q35

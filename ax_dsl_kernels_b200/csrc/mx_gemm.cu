@@ -1,0 +1,400 @@
+// Launchers of the weight-streaming GEMM: routed experts (decode and slot form), the dense part of the MoE block
+// (RMSNorm, shared expert, router), and plain quantised projections.
+#include "abi.h"
+#include "common.cuh"
+#include "moe_group.cuh"
+#include "mx_gemm.cuh"
+
+namespace q35 {
+
+static inline int64_t align_up(int64_t x, int64_t a) { return (x + a - 1) / a * a; }
+
+struct WsCarver {
+  uint8_t* base;
+  int64_t off = 0;
+  template <class T> T* take(int64_t count) {
+    T* p = base ? reinterpret_cast<T*>(base + off) : nullptr;
+    off = align_up(off + count * int64_t(sizeof(T)), 256);
+    return p;
+  }
+};
+
+template <int FMT, int EPI>
+static int launch_skinny(const SkinnyArgs& a, int nt, int tiles, int groups, cudaStream_t stream) {
+  const dim3 grid{unsigned(tiles), unsigned(groups), 1u};
+#define Q35_SK(NTV)                                                                                         \
+  {                                                                                                         \
+    constexpr int smem = skinny_smem_bytes<FMT, NTV>();                                                     \
+    static bool attr_done = false;                                                                          \
+    if (!attr_done && smem > 48 * 1024) {                                                                   \
+      cudaFuncSetAttribute(skinny_gemm_kernel<FMT, EPI, NTV>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); \
+      attr_done = true;                                                                                     \
+    }                                                                                                       \
+    skinny_gemm_kernel<FMT, EPI, NTV><<<grid, 128, smem, stream>>>(a);                                      \
+  }
+  if (nt <= 1) Q35_SK(1)
+  else if (nt == 2) Q35_SK(2)
+  else Q35_SK(4)
+#undef Q35_SK
+  Q35_CUDA_LAUNCH_CHECK("skinny gemm");
+  return 0;
+}
+
+static int pick_nt(int64_t rows_per_group) { return rows_per_group <= 8 ? 1 : rows_per_group <= 16 ? 2 : 4; }
+
+// ---------------------------------------------------------------------------------------------------------------
+// moe.experts: decode form of the routed experts with planar expert tensors.
+// Reference: moe_experts_gu (models/qwen35_2b/whole/src/q35_moe.py:101-112) per token; golden :227-238; experts
+// picked from planes by id as moe_full does (models/qwen35_2b/whole/src/q35_layer_mc.py:863-885).
+__global__ void __launch_bounds__(256) experts_build_rows_kernel(const int* __restrict__ counts,
+                                                                 const int* __restrict__ list,
+                                                                 const float* __restrict__ rw, int T, int K, int NE,
+                                                                 int* g_expert, int* g_n, int* g_row0, int* src,
+                                                                 float* rw_row, int* loc) {
+  const int e = blockIdx.x, tid = threadIdx.x;
+  __shared__ int s_red[256];
+  int mine = 0;
+  for (int i = tid; i < e; i += 256) mine += counts[i];
+  s_red[tid] = mine;
+  __syncthreads();
+  for (int o = 128; o > 0; o >>= 1) {
+    if (tid < o) s_red[tid] += s_red[tid + o];
+    __syncthreads();
+  }
+  const int row0 = s_red[0];
+  const int n = counts[e];
+  if (tid == 0) { g_expert[e] = e; g_n[e] = n; g_row0[e] = row0; }
+  for (int j = tid; j < n; j += 256) {
+    const int p = list[size_t(e) * T + j];
+    const int t = p / K, k = p % K;
+    src[row0 + j] = t;
+    rw_row[row0 + j] = rw[p];
+    loc[size_t(k) * T + t] = row0 + j;
+  }
+}
+
+int run_moe_experts(Call& c) {
+  Tensor h2, base, ids, rw, gw, gs, dw, ds, out, ws;
+  Q35_TRY(c.get("h2", M(Q35_BF16), &h2));
+  Q35_TRY(c.get("base", M(Q35_BF16), &base));
+  Q35_TRY(c.get("ids", M(Q35_I32), &ids));
+  Q35_TRY(c.get("rw", M(Q35_F32), &rw));
+  Q35_TRY(c.get("e_gw", M_BYTES, &gw));
+  Q35_TRY(c.get("e_gs", M(Q35_U8), &gs));
+  Q35_TRY(c.get("e_dw", M_BYTES, &dw));
+  Q35_TRY(c.get("e_ds", M(Q35_U8), &ds));
+  Q35_TRY(c.get("out", M(Q35_BF16), &out));
+  Q35_REQUIRE(gw.nd == 3 && gs.nd == 3 && dw.nd == 3 && ds.nd == 3 && ids.nd == 2, Q35_ERR_SHAPE,
+              "moe.experts: expert planes must be rank 3, ids rank 2");
+  const int64_t NE = gw.s[0], FE2 = gw.s[1], H = gw.s[2] * 2, FE = FE2 / 2;
+  const int64_t T = ids.s[0], K = ids.s[1];
+  Q35_REQUIRE(h2.numel() == T * H && base.numel() == T * H && out.numel() == T * H, Q35_ERR_SHAPE,
+              "moe.experts: h2 / base / out must be [T=%lld, H=%lld]", (long long)T, (long long)H);
+  Q35_REQUIRE(rw.numel() == T * K, Q35_ERR_SHAPE, "moe.experts: rw must be [T, K]");
+  Q35_REQUIRE(gs.s[0] == NE && gs.s[1] == FE2 && gs.s[2] == H / 32, Q35_ERR_SHAPE, "moe.experts: e_gs [NE, 2FE, H/32]");
+  Q35_REQUIRE(dw.s[0] == NE && dw.s[1] == H && dw.s[2] == FE / 2, Q35_ERR_SHAPE, "moe.experts: e_dw [NE, H, FE/2]");
+  Q35_REQUIRE(ds.s[0] == NE && ds.s[1] == H && ds.s[2] == FE / 32, Q35_ERR_SHAPE, "moe.experts: e_ds [NE, H, FE/32]");
+  Q35_REQUIRE(H % 256 == 0 && FE % 256 == 0, Q35_ERR_UNSUPPORTED, "moe.experts: H and FE must be multiples of 256");
+  const int64_t P = T * K;
+  WsCarver w{nullptr};
+  auto carve = [&](WsCarver& cw, int*& counts, int*& list, int*& g_expert, int*& g_n, int*& g_row0, int*& src,
+                   float*& rw_row, int*& loc, __nv_bfloat16*& act, float*& sout) {
+    counts = cw.take<int>(NE); list = cw.take<int>(NE * T);
+    g_expert = cw.take<int>(NE); g_n = cw.take<int>(NE); g_row0 = cw.take<int>(NE);
+    src = cw.take<int>(P); rw_row = cw.take<float>(P); loc = cw.take<int>(P);
+    act = cw.take<__nv_bfloat16>(P * FE); sout = cw.take<float>(P * H);
+  };
+  int *counts, *list, *g_expert, *g_n, *g_row0, *src, *loc;
+  float *rw_row, *sout;
+  __nv_bfloat16* act;
+  carve(w, counts, list, g_expert, g_n, g_row0, src, rw_row, loc, act, sout);
+  Q35_TRY(c.workspace(w.off, &ws));
+  if (c.dry || T == 0) return 0;
+  Q35_REQUIRE(aligned16(h2.p) && aligned16(base.p) && aligned16(out.p) && aligned16(gw.p) && aligned16(dw.p) &&
+                  (uintptr_t(gs.p) & 1) == 0 && (uintptr_t(ds.p) & 1) == 0,
+              Q35_ERR_ALIGN, "moe.experts: pointers must be 16-byte aligned");
+  WsCarver wr{ws.as<uint8_t>()};
+  carve(wr, counts, list, g_expert, g_n, g_row0, src, rw_row, loc, act, sout);
+
+  Q35_TRY(launch_group_count(ids.as<int>(), int(T), int(K), int(NE), counts, list, c.stream));
+  experts_build_rows_kernel<<<unsigned(NE), 256, 0, c.stream>>>(counts, list, rw.as<float>(), int(T), int(K), int(NE),
+                                                                g_expert, g_n, g_row0, src, rw_row, loc);
+  Q35_CUDA_LAUNCH_CHECK("moe.experts rows");
+  const int nt = pick_nt((P + NE - 1) / NE);
+  SkinnyArgs a{};
+  a.status = device_status_ptr();
+  a.g_expert = g_expert; a.g_n = g_n; a.g_row0 = g_row0; a.n_planes = int(NE);
+  // gate-up + SiLU * up -> act
+  a.w[0] = a.w[1] = gw.as<uint8_t>(); a.s[0] = a.s[1] = gs.as<uint8_t>();
+  a.w_plane = FE2 * (H / 2); a.s_plane = FE2 * (H / 32);
+  a.K = int(H); a.roff[0] = 0; a.roff[1] = int(FE); a.lim[0] = int(FE); a.lim[1] = int(FE2);
+  a.act_rows = int(FE); a.tile_rows = 64; a.warp_rows = 16;
+  a.x = h2.as<__nv_bfloat16>(); a.x_stride = int(H); a.src = src; a.act_out = act;
+  Q35_TRY((launch_skinny<W_MXFP4, EPI_SILU_MUL>(a, nt, int(FE / 64), int(NE), c.stream)));
+  // down, scaled by the routing weight -> sout (fp32)
+  SkinnyArgs d{};
+  d.status = a.status;
+  d.g_expert = g_expert; d.g_n = g_n; d.g_row0 = g_row0; d.n_planes = int(NE);
+  d.w[0] = d.w[1] = dw.as<uint8_t>(); d.s[0] = d.s[1] = ds.as<uint8_t>();
+  d.w_plane = H * (FE / 2); d.s_plane = H * (FE / 32);
+  d.K = int(FE); d.roff[0] = 0; d.roff[1] = 16; d.lim[0] = d.lim[1] = int(H);
+  d.tile_rows = 128; d.warp_rows = 32;
+  d.x = act; d.x_stride = int(FE); d.src = nullptr;
+  d.f_out = sout; d.out_stride = int(H); d.rw_row = rw_row;
+  Q35_TRY((launch_skinny<W_MXFP4, EPI_ROW_SCALE>(d, nt, int((H + 127) / 128), int(NE), c.stream)));
+  return launch_combine(base.as<__nv_bfloat16>(), loc, sout, true, out.as<__nv_bfloat16>(), int(T), int(H), int(K),
+                        int(P), c.stream);
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// moe.slots: slot-grouped routed experts of a prefill group, reading rows out of h2 by token id
+// (moe_slots_px, models/qwen35_2b/whole/src/q35_moe_prefill.py:150-166; golden :239-246).
+__global__ void slots_build_groups_kernel(const int* __restrict__ tok, const int* n_slots, int S, int G, int T, int NE,
+                                          int* g_expert, int* g_n, int* g_row0, int* src, int* status) {
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= S * G) return;
+  const int s = idx / G, j = idx % G;
+  int t = tok[size_t(s) * (1 + G) + 1 + j];
+  if (t < 0 || t >= T) { atomicOr(status, DS_BAD_TOKEN); t = 0; }
+  src[idx] = t;
+  if (j == 0) {
+    const bool used = !n_slots || s < n_slots[0];
+    g_expert[s] = tok[size_t(s) * (1 + G)];
+    g_n[s] = used ? G : 0;
+    g_row0[s] = s * G;
+  }
+}
+
+int run_moe_slots(Call& c) {
+  Tensor h2, tok, rw, gw, gs, dw, ds, out, ns, ws;
+  Q35_TRY(c.get("h2", M(Q35_BF16), &h2));
+  Q35_TRY(c.get("tok", M(Q35_I32), &tok));
+  Q35_TRY(c.get("rw", M(Q35_F32), &rw));
+  Q35_TRY(c.get("e_gw", M_BYTES, &gw));
+  Q35_TRY(c.get("e_gs", M(Q35_U8), &gs));
+  Q35_TRY(c.get("e_dw", M_BYTES, &dw));
+  Q35_TRY(c.get("e_ds", M(Q35_U8), &ds));
+  Q35_TRY(c.get("out", M(Q35_BF16) | M(Q35_F32), &out));
+  Q35_TRY(c.get("n_slots", M(Q35_I32), &ns, false));
+  Q35_REQUIRE(gw.nd == 3 && gs.nd == 3 && dw.nd == 3 && ds.nd == 3 && tok.nd == 2 && h2.nd == 2, Q35_ERR_SHAPE,
+              "moe.slots: ranks");
+  const int64_t NE = gw.s[0], FE2 = gw.s[1], H = gw.s[2] * 2, FE = FE2 / 2;
+  const int64_t S = tok.s[0], G = tok.s[1] - 1, T = h2.s[0];
+  Q35_REQUIRE(G >= 1 && rw.numel() == S * G && out.numel() == S * G * H && h2.s[1] == H, Q35_ERR_SHAPE,
+              "moe.slots: tok [S, 1+G], rw [S, G], out [S, G, H], h2 [T, H]");
+  Q35_REQUIRE(gs.s[0] == NE && gs.s[1] == FE2 && gs.s[2] == H / 32 && dw.s[0] == NE && dw.s[1] == H &&
+                  dw.s[2] == FE / 2 && ds.s[0] == NE && ds.s[1] == H && ds.s[2] == FE / 32,
+              Q35_ERR_SHAPE, "moe.slots: expert plane shapes");
+  Q35_REQUIRE(H % 256 == 0 && FE % 256 == 0, Q35_ERR_UNSUPPORTED, "moe.slots: H and FE must be multiples of 256");
+  WsCarver w{nullptr};
+  auto carve = [&](WsCarver& cw, int*& g_expert, int*& g_n, int*& g_row0, int*& src, __nv_bfloat16*& act) {
+    g_expert = cw.take<int>(S); g_n = cw.take<int>(S); g_row0 = cw.take<int>(S);
+    src = cw.take<int>(S * G); act = cw.take<__nv_bfloat16>(S * G * FE);
+  };
+  int *g_expert, *g_n, *g_row0, *src;
+  __nv_bfloat16* act;
+  carve(w, g_expert, g_n, g_row0, src, act);
+  Q35_TRY(c.workspace(w.off, &ws));
+  if (c.dry || S == 0) return 0;
+  Q35_REQUIRE(aligned16(h2.p) && aligned16(out.p) && aligned16(gw.p) && aligned16(dw.p), Q35_ERR_ALIGN,
+              "moe.slots: pointers must be 16-byte aligned");
+  WsCarver wr{ws.as<uint8_t>()};
+  carve(wr, g_expert, g_n, g_row0, src, act);
+  if (ns.present) cudaMemsetAsync(out.p, 0, out.bytes, c.stream);  // rows of unused slots
+  slots_build_groups_kernel<<<unsigned((S * G + 255) / 256), 256, 0, c.stream>>>(
+      tok.as<int>(), ns.present ? ns.as<int>() : nullptr, int(S), int(G), int(T), int(NE), g_expert, g_n, g_row0, src,
+      device_status_ptr());
+  Q35_CUDA_LAUNCH_CHECK("moe.slots groups");
+  const int nt = pick_nt(G);
+  SkinnyArgs a{};
+  a.status = device_status_ptr();
+  a.g_expert = g_expert; a.g_n = g_n; a.g_row0 = g_row0; a.n_planes = int(NE);
+  a.w[0] = a.w[1] = gw.as<uint8_t>(); a.s[0] = a.s[1] = gs.as<uint8_t>();
+  a.w_plane = FE2 * (H / 2); a.s_plane = FE2 * (H / 32);
+  a.K = int(H); a.roff[0] = 0; a.roff[1] = int(FE); a.lim[0] = int(FE); a.lim[1] = int(FE2);
+  a.act_rows = int(FE); a.tile_rows = 64; a.warp_rows = 16;
+  a.x = h2.as<__nv_bfloat16>(); a.x_stride = int(H); a.src = src; a.act_out = act;
+  Q35_TRY((launch_skinny<W_MXFP4, EPI_SILU_MUL>(a, nt, int(FE / 64), int(S), c.stream)));
+  SkinnyArgs d{};
+  d.status = a.status;
+  d.g_expert = g_expert; d.g_n = g_n; d.g_row0 = g_row0; d.n_planes = int(NE);
+  d.w[0] = d.w[1] = dw.as<uint8_t>(); d.s[0] = d.s[1] = ds.as<uint8_t>();
+  d.w_plane = H * (FE / 2); d.s_plane = H * (FE / 32);
+  d.K = int(FE); d.roff[0] = 0; d.roff[1] = 16; d.lim[0] = d.lim[1] = int(H);
+  d.tile_rows = 128; d.warp_rows = 32;
+  d.x = act; d.x_stride = int(FE); d.src = nullptr;
+  if (out.dtype == Q35_F32) d.f_out = out.as<float>(); else d.b_out = out.as<__nv_bfloat16>();
+  d.out_stride = int(H); d.rw_row = rw.as<float>();
+  return launch_skinny<W_MXFP4, EPI_ROW_SCALE>(d, nt, int((H + 127) / 128), int(S), c.stream);
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// moe.pre: dense part of the MoE block (moe_pre, models/qwen35_2b/whole/src/q35_moe.py:123-137):
+// h2 = RMSNorm(x1) * ln2; base = bf16(x1 + sigmoid(h2 . w_shg) * shared_expert(h2)); logits = h2 @ w_router^T (fp32).
+__global__ void __launch_bounds__(256) rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ w,
+                                                      __nv_bfloat16* __restrict__ y, int H, float eps) {
+  const int t = blockIdx.x, tid = threadIdx.x;
+  const __nv_bfloat16* xr = x + size_t(t) * H;
+  float ss = 0.f;
+  for (int i = tid; i < H; i += 256) { const float v = __bfloat162float(xr[i]); ss += v * v; }
+  __shared__ float s_red[8];
+  ss = warp_sum(ss);
+  if ((tid & 31) == 0) s_red[tid >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) tot += s_red[i];
+  const float rs = rsqrtf(tot / float(H) + eps);
+  for (int i = tid; i < H; i += 256) y[size_t(t) * H + i] = __float2bfloat16_rn(__bfloat162float(xr[i]) * rs * w[i]);
+}
+
+// logits[t, e] = sum_k h2[t, k] * w_router[e, k] in fp32 (bf16 products are exact in fp32); row NE is the shared-
+// expert gate vector.  One warp per (t, e); lanes stride k so the order of the sum is fixed.
+__global__ void __launch_bounds__(256) router_kernel(const __nv_bfloat16* __restrict__ h2,
+                                                     const __nv_bfloat16* __restrict__ w_router,
+                                                     const __nv_bfloat16* __restrict__ w_shg,
+                                                     float* __restrict__ logits, float* __restrict__ gate, int H, int NE) {
+  const int t = blockIdx.y;
+  const int e = blockIdx.x * 8 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (e > NE) return;
+  const __nv_bfloat16* wr = e < NE ? w_router + size_t(e) * H : w_shg;
+  const __nv_bfloat16* xr = h2 + size_t(t) * H;
+  float acc = 0.f;
+  for (int k = lane * 8; k < H; k += 256) {
+    const uint4 xv = *reinterpret_cast<const uint4*>(xr + k);
+    const uint4 wv = *reinterpret_cast<const uint4*>(wr + k);
+    acc = fmaf(bf16lo(xv.x), bf16lo(wv.x), acc); acc = fmaf(bf16hi(xv.x), bf16hi(wv.x), acc);
+    acc = fmaf(bf16lo(xv.y), bf16lo(wv.y), acc); acc = fmaf(bf16hi(xv.y), bf16hi(wv.y), acc);
+    acc = fmaf(bf16lo(xv.z), bf16lo(wv.z), acc); acc = fmaf(bf16hi(xv.z), bf16hi(wv.z), acc);
+    acc = fmaf(bf16lo(xv.w), bf16lo(wv.w), acc); acc = fmaf(bf16hi(xv.w), bf16hi(wv.w), acc);
+  }
+  acc = warp_sum(acc);
+  if (lane == 0) {
+    if (e < NE) logits[size_t(t) * NE + e] = acc;
+    else gate[t] = acc;
+  }
+}
+
+static int weight_format(const Tensor& w, const Tensor& s, int64_t K, int* fmt) {
+  if (s.present && s.dtype == Q35_F32) { *fmt = W_FP8ROW; return 0; }
+  Q35_REQUIRE(s.present, Q35_ERR_MISSING, "quantised weight without scales");
+  const int64_t inner = w.s[w.nd - 1];
+  if (inner == K / 2 && w.dtype == Q35_U8) { *fmt = W_MXFP4; return 0; }
+  if (inner == K) { *fmt = W_MXFP8; return 0; }
+  return fail(Q35_ERR_SHAPE, "weight inner dim %lld matches neither K/2 (MXFP4) nor K (FP8) for K=%lld",
+              (long long)inner, (long long)K);
+}
+
+int run_moe_pre(Call& c) {
+  Tensor x1, ln2, wg, sg, wu, su, wd, sd, wr, wshg, out, h2o, lgo, eps_t, ws;
+  Q35_TRY(c.get("x1", M(Q35_BF16), &x1));
+  Q35_TRY(c.get("ln2", M(Q35_F32), &ln2));
+  Q35_TRY(c.get("w_gate", M_BYTES | M(Q35_E4M3), &wg));
+  Q35_TRY(c.get("s_gate", M(Q35_U8), &sg));
+  Q35_TRY(c.get("w_up", M_BYTES | M(Q35_E4M3), &wu));
+  Q35_TRY(c.get("s_up", M(Q35_U8), &su));
+  Q35_TRY(c.get("w_down", M_BYTES | M(Q35_E4M3), &wd));
+  Q35_TRY(c.get("s_down", M(Q35_U8), &sd));
+  Q35_TRY(c.get("w_router", M(Q35_BF16), &wr));
+  Q35_TRY(c.get("w_shg", M(Q35_BF16), &wshg));
+  Q35_TRY(c.get("out", M(Q35_BF16), &out));
+  Q35_TRY(c.get("h2_out", M(Q35_BF16), &h2o));
+  Q35_TRY(c.get("logits_out", M(Q35_F32), &lgo));
+  Q35_TRY(c.get("eps", M(Q35_F32), &eps_t, false));
+  Q35_REQUIRE(x1.nd >= 2 && wr.nd == 2 && wg.nd == 2 && wd.nd == 2, Q35_ERR_SHAPE, "moe.pre: ranks");
+  const int64_t H = x1.s[x1.nd - 1], T = x1.numel() / H, NE = wr.s[0], FS = wg.s[0];
+  Q35_REQUIRE(ln2.numel() == H && wr.s[1] == H && wshg.numel() == H, Q35_ERR_SHAPE, "moe.pre: ln2 / w_router / w_shg");
+  Q35_REQUIRE(out.numel() == T * H && h2o.numel() == T * H && lgo.numel() == T * NE, Q35_ERR_SHAPE, "moe.pre: outputs");
+  Q35_REQUIRE(wu.s[0] == FS && wd.s[0] == H, Q35_ERR_SHAPE, "moe.pre: shared expert shapes");
+  int f1, f2, f3;
+  Q35_TRY(weight_format(wg, sg, H, &f1));
+  Q35_TRY(weight_format(wu, su, H, &f2));
+  Q35_TRY(weight_format(wd, sd, FS, &f3));
+  Q35_REQUIRE(f1 == f2 && f1 == f3 && f1 != W_FP8ROW, Q35_ERR_UNSUPPORTED, "moe.pre: shared expert must be MXFP4 or MXFP8");
+  Q35_REQUIRE(sg.numel() == FS * (H / 32) && su.numel() == FS * (H / 32) && sd.numel() == H * (FS / 32), Q35_ERR_SHAPE,
+              "moe.pre: scale shapes");
+  Q35_REQUIRE(H % 256 == 0 && FS % 256 == 0, Q35_ERR_UNSUPPORTED, "moe.pre: H and FS must be multiples of 256");
+  WsCarver w{nullptr};
+  __nv_bfloat16* act = w.take<__nv_bfloat16>(T * FS);
+  float* gate = w.take<float>(T);
+  Q35_TRY(c.workspace(w.off, &ws));
+  if (c.dry || T == 0) return 0;
+  Q35_REQUIRE(aligned16(x1.p) && aligned16(out.p) && aligned16(h2o.p) && aligned16(wg.p) && aligned16(wu.p) &&
+                  aligned16(wd.p) && aligned16(wr.p) && aligned16(wshg.p),
+              Q35_ERR_ALIGN, "moe.pre: pointers must be 16-byte aligned");
+  WsCarver wc{ws.as<uint8_t>()};
+  act = wc.take<__nv_bfloat16>(T * FS);
+  gate = wc.take<float>(T);
+  // eps is a host-side constant of the model (1e-6 for every Qwen3.5 config); an `eps` tensor is not read on device
+  const float eps = 1e-6f;
+  rmsnorm_kernel<<<unsigned(T), 256, 0, c.stream>>>(x1.as<__nv_bfloat16>(), ln2.as<float>(), h2o.as<__nv_bfloat16>(),
+                                                    int(H), eps);
+  Q35_CUDA_LAUNCH_CHECK("moe.pre rmsnorm");
+  router_kernel<<<dim3(unsigned((NE + 1 + 7) / 8), unsigned(T)), 256, 0, c.stream>>>(
+      h2o.as<__nv_bfloat16>(), wr.as<__nv_bfloat16>(), wshg.as<__nv_bfloat16>(), lgo.as<float>(), gate, int(H), int(NE));
+  Q35_CUDA_LAUNCH_CHECK("moe.pre router");
+  const int nt = pick_nt(T);
+  SkinnyArgs a{};
+  a.status = device_status_ptr();
+  a.n_dense = int(T); a.n_planes = 1;
+  a.w[0] = wg.as<uint8_t>(); a.w[1] = wu.as<uint8_t>(); a.s[0] = sg.as<uint8_t>(); a.s[1] = su.as<uint8_t>();
+  a.K = int(H); a.roff[0] = a.roff[1] = 0; a.lim[0] = a.lim[1] = int(FS);
+  a.act_rows = int(FS); a.tile_rows = 64; a.warp_rows = 16;
+  a.x = h2o.as<__nv_bfloat16>(); a.x_stride = int(H); a.act_out = act;
+  SkinnyArgs d{};
+  d.status = a.status;
+  d.n_dense = int(T); d.n_planes = 1;
+  d.w[0] = d.w[1] = wd.as<uint8_t>(); d.s[0] = d.s[1] = sd.as<uint8_t>();
+  d.K = int(FS); d.roff[0] = 0; d.roff[1] = 16; d.lim[0] = d.lim[1] = int(H);
+  d.tile_rows = 128; d.warp_rows = 32;
+  d.x = act; d.x_stride = int(FS);
+  d.b_out = out.as<__nv_bfloat16>(); d.out_stride = int(H); d.resid = x1.as<__nv_bfloat16>(); d.gate = gate;
+  if (f1 == W_MXFP4) {
+    Q35_TRY((launch_skinny<W_MXFP4, EPI_SILU_MUL>(a, nt, int(FS / 64), 1, c.stream)));
+    return launch_skinny<W_MXFP4, EPI_SHARED_DOWN>(d, nt, int((H + 127) / 128), 1, c.stream);
+  }
+  Q35_TRY((launch_skinny<W_MXFP8, EPI_SILU_MUL>(a, nt, int(FS / 64), 1, c.stream)));
+  return launch_skinny<W_MXFP8, EPI_SHARED_DOWN>(d, nt, int((H + 127) / 128), 1, c.stream);
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// linear: out[t, n] = x[t, :] . dequant(w[n, :]) (+ bias): the quantised projections of the layer kernels.
+// MXFP4 / MXFP8: linear(x, w, s) of the reference's q35 line (models/qwen35_2b/whole/src/q35_mx_build.py:100-115);
+// FP8 with per-row fp32 scales: fp8_gemm with scale_a = 1
+// (models/qwen35_35b_a3b/sgl/python/sgl_kernel_axera/gemm.py:123-153, 457-466).
+int run_linear(Call& c) {
+  Tensor x, w, s, bias, out;
+  Q35_TRY(c.get("x", M(Q35_BF16), &x));
+  Q35_TRY(c.get("w", M_BYTES | M(Q35_E4M3), &w));
+  Q35_TRY(c.get("s", M(Q35_U8) | M(Q35_F32), &s));
+  Q35_TRY(c.get("bias", M(Q35_F32), &bias, false));
+  Q35_TRY(c.get("out", M(Q35_BF16) | M(Q35_F32), &out));
+  Q35_REQUIRE(x.nd >= 2 && w.nd == 2, Q35_ERR_SHAPE, "linear: x [T, K], w [N, K or K/2]");
+  const int64_t K = x.s[x.nd - 1], T = x.numel() / K, N = w.s[0];
+  int fmt;
+  Q35_TRY(weight_format(w, s, K, &fmt));
+  Q35_REQUIRE(out.numel() == T * N, Q35_ERR_SHAPE, "linear: out must be [T, N]");
+  Q35_REQUIRE(fmt == W_FP8ROW ? s.numel() == N : s.numel() == N * (K / 32), Q35_ERR_SHAPE, "linear: scale shape");
+  Q35_REQUIRE(!bias.present || bias.numel() == N, Q35_ERR_SHAPE, "linear: bias [N]");
+  Q35_REQUIRE(K % 256 == 0, Q35_ERR_UNSUPPORTED, "linear: K must be a multiple of 256");
+  c.ws_need = 0;
+  if (c.dry || T == 0 || N == 0) return 0;
+  Q35_REQUIRE(aligned16(x.p) && aligned16(w.p), Q35_ERR_ALIGN, "linear: pointers must be 16-byte aligned");
+  SkinnyArgs d{};
+  d.status = device_status_ptr();
+  d.n_dense = int(T); d.n_planes = 1;
+  d.w[0] = d.w[1] = w.as<uint8_t>(); d.s[0] = d.s[1] = s.as<uint8_t>();
+  d.K = int(K); d.roff[0] = 0; d.roff[1] = 16; d.lim[0] = d.lim[1] = int(N);
+  d.tile_rows = 128; d.warp_rows = 32;
+  d.x = x.as<__nv_bfloat16>(); d.x_stride = int(K);
+  if (out.dtype == Q35_F32) d.f_out = out.as<float>(); else d.b_out = out.as<__nv_bfloat16>();
+  d.out_stride = int(N);
+  d.bias = bias.present ? bias.as<float>() : nullptr;
+  const int nt = pick_nt(T), tiles = int((N + 127) / 128);
+  if (fmt == W_MXFP4) return launch_skinny<W_MXFP4, EPI_PLAIN>(d, nt, tiles, 1, c.stream);
+  if (fmt == W_MXFP8) return launch_skinny<W_MXFP8, EPI_PLAIN>(d, nt, tiles, 1, c.stream);
+  return launch_skinny<W_FP8ROW, EPI_PLAIN>(d, nt, tiles, 1, c.stream);
+}
+
+}  // namespace q35

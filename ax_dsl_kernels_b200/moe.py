@@ -1,0 +1,106 @@
+"""Host side of the MoE block, mirroring the reference's kernel entry points by name and argument meaning.
+
+Reference entry points (models/qwen35_2b/whole/src/): q35_moe.py `route` (:293-297), `moe_pre` (:123-137),
+`moe_experts` / `moe_experts_gu` (:73-112); q35_moe_prefill.py `moe_slots_px(h2, tok, rw, e_gw, e_gs, e_dw, e_ds, out)`
+(:150-166) and `moe_combine(base, loc, sout, out)` (:201-214).  Outputs are caller-allocated tensors, as there.
+"""
+import torch
+
+from . import _lib
+
+
+def _u8(t):
+    return t.view(torch.uint8) if t.dtype != torch.uint8 else t
+
+
+def route(logits, top_k, ids=None, rw=None):
+    """softmax over all experts -> top-k -> weights / their sum, per token.  logits [T, NE] fp32 on the GPU.
+    Returns (ids [T, K] int32, rw [T, K] fp32); exact ties go to the lower expert id."""
+    if logits.dtype != torch.float32:
+        raise TypeError("route: logits must be float32")
+    lg = logits.reshape(-1, logits.shape[-1])
+    T = lg.shape[0]
+    ids = torch.empty((T, top_k), dtype=torch.int32, device=lg.device) if ids is None else ids
+    rw = torch.empty((T, top_k), dtype=torch.float32, device=lg.device) if rw is None else rw
+    _lib.run("moe.route", logits=lg, ids=ids, rw=rw)
+    return ids, rw
+
+
+def moe_pre(x1, ln2, w_gate, s_gate, w_up, s_up, w_down, s_down, w_router, w_shg, out, h2_out, logits_out):
+    """dense part of the block: out = x1 + sigmoid(h2 . w_shg) * shared_expert(h2), h2 = RMSNorm(x1) * ln2,
+    logits = h2 @ w_router^T (fp32).  Shared-expert weights MXFP4 (uint8 pairs) or MXFP8 (e4m3), E8M0 scales."""
+    _lib.run("moe.pre", x1=x1, ln2=ln2, w_gate=w_gate, s_gate=_u8(s_gate), w_up=w_up, s_up=_u8(s_up), w_down=w_down,
+             s_down=_u8(s_down), w_router=w_router, w_shg=w_shg.reshape(-1), out=out, h2_out=h2_out,
+             logits_out=logits_out)
+    return out, h2_out, logits_out
+
+
+def moe_experts(h2, base, ids, rw, e_gw, e_gs, e_dw, e_ds, out):
+    """out[t] = base[t] + sum_i rw[t, i] * down_e(silu(gate_e h2[t]) * up_e h2[t]), e = ids[t, i].
+    Planar MXFP4 expert tensors (gate rows then up rows in e_gw), picked on the device by id; at batch 1 this is the
+    reference's moe_experts_gu with the K experts bound by address."""
+    _lib.run("moe.experts", h2=h2, base=base, ids=ids, rw=rw, e_gw=_u8(e_gw), e_gs=_u8(e_gs), e_dw=_u8(e_dw),
+             e_ds=_u8(e_ds), out=out)
+    return out
+
+
+def moe_slots_px(h2, tok, rw, e_gw, e_gs, e_dw, e_ds, out, n_slots=None):
+    """slot s = expert tok[s, 0] on the G token rows tok[s, 1:] of h2; out[s, g] = rw[s, g] * expert(h2[tok]).
+    n_slots (int32 [1], optional): slots at or beyond it are skipped and their rows zeroed."""
+    kw = dict(h2=h2, tok=tok, rw=rw, e_gw=_u8(e_gw), e_gs=_u8(e_gs), e_dw=_u8(e_dw), e_ds=_u8(e_ds), out=out)
+    if n_slots is not None:
+        kw["n_slots"] = n_slots
+    _lib.run("moe.slots", **kw)
+    return out
+
+
+def moe_combine(base, loc, sout, out):
+    """out[t] = base[t] + sum_k sout[loc[k, t]] (fp32 accumulate, bf16 out)."""
+    _lib.run("moe.combine", base=base, loc=loc, sout=sout.reshape(-1, sout.shape[-1]), out=out)
+    return out
+
+
+def moe_permute(ids, rw, n_experts, G, S=None):
+    """token -> slot tables for the slot kernels: experts in id order, each expert's tokens in index order,
+    ceil(n / G) slots per expert (unused rows: token 0 with weight 0).
+    Returns tok [S, 1+G] i32, srw [S, G] f32, loc [K, T] i32, n_slots i32 [1], counts [NE] i32."""
+    T, K = ids.shape
+    if S is None:
+        S = min(T * K, (T * K + G - 1) // G + n_experts)
+    dev = ids.device
+    tok = torch.empty((S, 1 + G), dtype=torch.int32, device=dev)
+    srw = torch.empty((S, G), dtype=torch.float32, device=dev)
+    loc = torch.empty((K, T), dtype=torch.int32, device=dev)
+    n_slots = torch.empty((1,), dtype=torch.int32, device=dev)
+    counts = torch.empty((n_experts,), dtype=torch.int32, device=dev)
+    _lib.run("moe.permute", ids=ids, rw=rw, tok=tok, srw=srw, loc=loc, n_slots=n_slots, counts=counts)
+    return tok, srw, loc, n_slots, counts
+
+
+def moe_block(x1, w, top_k, out=None):
+    """whole block on T tokens: dense part -> router -> routed experts.  w: dict with ln2, w_gate, s_gate, w_up,
+    s_up, w_down, s_down, w_router, w_shg, e_gw, e_gs, e_dw, e_ds.  Returns (out, ids, rw, logits)."""
+    T, H = x1.shape
+    dev = x1.device
+    base = torch.empty_like(x1)
+    h2 = torch.empty_like(x1)
+    logits = torch.empty((T, w["w_router"].shape[0]), dtype=torch.float32, device=dev)
+    moe_pre(x1, w["ln2"], w["w_gate"], w["s_gate"], w["w_up"], w["s_up"], w["w_down"], w["s_down"], w["w_router"],
+            w["w_shg"], base, h2, logits)
+    ids, rw = route(logits, top_k)
+    out = torch.empty_like(x1) if out is None else out
+    moe_experts(h2, base, ids, rw, w["e_gw"], w["e_gs"], w["e_dw"], w["e_ds"], out)
+    return out, ids, rw, logits
+
+
+def linear(x, w, s, out=None, bias=None, out_dtype=torch.bfloat16):
+    """x [T, K] bf16 times a quantised weight [N, K]: MXFP4 (uint8 [N, K/2] + E8M0 [N, K/32]), MXFP8 (e4m3 [N, K] +
+    E8M0) or FP8 per-row (e4m3 [N, K] + fp32 [N]; fp8_gemm with scale_a = 1,
+    models/qwen35_35b_a3b/sgl/python/sgl_kernel_axera/gemm.py:457-466)."""
+    T, N = x.shape[0], w.shape[0]
+    out = torch.empty((T, N), dtype=out_dtype, device=x.device) if out is None else out
+    kw = dict(x=x, w=w, s=s if s.dtype == torch.float32 else _u8(s), out=out)
+    if bias is not None:
+        kw["bias"] = bias
+    _lib.run("linear", **kw)
+    return out

@@ -1,0 +1,300 @@
+"""GPU parity: every kernel through the C ABI against the CPU oracle on identical seeded inputs.
+Tolerance of the hot path: bf16 outputs max-abs error <= 2e-2 of the output RMS; routing indices bit-exact."""
+import pytest
+import torch
+
+from conftest import rel_rms_err
+from oracle import attention as oattn, codecs, gdn as ogdn, moe as omoe
+from _cases import dequant_shared, gdn_step_case, moe_case, paged_case
+
+pytestmark = pytest.mark.gpu
+TOL = 2e-2
+
+
+@pytest.fixture(scope="module")
+def q35():
+    assert torch.cuda.is_available(), "GPU tests need a CUDA device"
+    import ax_dsl_kernels_b200 as m
+    yield m
+    assert m.device_status() == 0
+
+
+def cu(*ts):
+    return [t.cuda() if isinstance(t, torch.Tensor) else t for t in ts]
+
+
+# ------------------------------------------------------------------------------------------------ router
+def test_route_golden_fixture_bit_exact(q35, golden):
+    f = golden("route")
+    ids, rw = q35.route(f["logits"].cuda(), 8)
+    exp_ids, exp_rw = omoe.route(f["logits"], 8)
+    assert torch.equal(ids.cpu(), exp_ids)
+    torch.testing.assert_close(rw.cpu(), exp_rw, rtol=1e-5, atol=1e-7)
+    rest = [t for t in range(24) if t not in (3, 4)]  # rows without exact ties: the reference's own output
+    assert torch.equal(ids.cpu()[rest], f["ids"][rest])
+
+
+@pytest.mark.parametrize("T,NE,K", [(64, 256, 8), (1, 256, 8), (777, 128, 4), (5, 96, 3), (3, 512, 10)])
+def test_route_random_bit_exact(q35, T, NE, K):
+    g = torch.Generator().manual_seed(T + NE)
+    logits = torch.randn((T, NE), generator=g)
+    if T > 2:
+        logits[1, 5] = logits[1, 17] = logits[1].max() + 0.5
+        logits[2] = 0.25  # every expert tied
+    ids, rw = q35.route(logits.cuda(), K)
+    exp_ids, exp_rw = omoe.route(logits, K)
+    assert torch.equal(ids.cpu(), exp_ids)
+    torch.testing.assert_close(rw.cpu(), exp_rw, rtol=1e-5, atol=1e-7)
+
+
+# ------------------------------------------------------------------------------------------------ MoE
+@pytest.mark.parametrize("T", [1, 7, 64])
+def test_moe_experts_decode(q35, T):
+    x1, w = moe_case(T, NE=32, seed=3 + T)
+    g = torch.Generator().manual_seed(T)
+    h2 = torch.randn((T, 2048), generator=g).to(torch.bfloat16)
+    base = (torch.randn((T, 2048), generator=g) * 0.5).to(torch.bfloat16)
+    logits = torch.randn((T, 32), generator=g)
+    ids, rw = omoe.route(logits, 8)
+    ref = omoe.experts_decode(h2, base, ids, rw, w["e_gw"], w["e_gs"], w["e_dw"], w["e_ds"])
+    out = torch.full_like(h2, float("nan")).cuda()
+    q35.moe_experts(*cu(h2, base, ids, rw, w["e_gw"], w["e_gs"], w["e_dw"], w["e_ds"]), out)
+    assert rel_rms_err(out.cpu(), ref) <= TOL
+    out2 = torch.empty_like(out)
+    q35.moe_experts(*cu(h2, base, ids, rw, w["e_gw"], w["e_gs"], w["e_dw"], w["e_ds"]), out2)
+    assert torch.equal(out.view(torch.int16), out2.view(torch.int16))  # run-to-run bitwise determinism
+
+
+def test_moe_experts_one_expert_takes_every_token(q35):
+    T = 19
+    x1, w = moe_case(T, NE=8, seed=11)
+    g = torch.Generator().manual_seed(5)
+    h2 = torch.randn((T, 2048), generator=g).to(torch.bfloat16)
+    base = torch.zeros((T, 2048), dtype=torch.bfloat16)
+    ids = torch.tensor([[3, 1]] * T, dtype=torch.int32)
+    rw = torch.full((T, 2), 0.5)
+    ref = omoe.experts_decode(h2, base, ids, rw, w["e_gw"], w["e_gs"], w["e_dw"], w["e_ds"])
+    out = torch.empty_like(h2).cuda()
+    q35.moe_experts(*cu(h2, base, ids, rw, w["e_gw"], w["e_gs"], w["e_dw"], w["e_ds"]), out)
+    assert rel_rms_err(out.cpu(), ref) <= TOL
+
+
+@pytest.mark.parametrize("fmt", ["mxfp4", "mxfp8"])
+def test_moe_pre(q35, fmt):
+    T = 9
+    x1, w = moe_case(T, NE=64, seed=21, shared_fmt=fmt)
+    w["ln2"] = 1 + 0.05 * torch.randn(2048, generator=torch.Generator().manual_seed(1))
+    sg, su, sd = dequant_shared(w)
+    base, h2, logits = omoe.moe_pre(x1, w["ln2"], sg, su, sd, w["w_router"], w["w_shg"])
+    out, h2o = torch.empty_like(x1).cuda(), torch.empty_like(x1).cuda()
+    lg = torch.empty((T, 64), dtype=torch.float32).cuda()
+    q35.moe_pre(*cu(x1, w["ln2"], w["w_gate"], w["s_gate"], w["w_up"], w["s_up"], w["w_down"], w["s_down"],
+                    w["w_router"], w["w_shg"]), out, h2o, lg)
+    assert rel_rms_err(h2o.cpu(), h2) <= 1e-2
+    assert rel_rms_err(lg.cpu(), logits) <= TOL
+    assert rel_rms_err(out.cpu(), base) <= TOL
+
+
+def test_moe_block_end_to_end_ids_bit_exact(q35):
+    T = 16
+    x1, w = moe_case(T, NE=64, seed=33)
+    sg, su, sd = dequant_shared(w)
+    ref, ids, rw, logits = omoe.moe_block(x1, w["ln2"], sg, su, sd, w["w_router"], w["w_shg"], w["e_gw"], w["e_gs"],
+                                          w["e_dw"], w["e_ds"], 8)
+    wd = {k: v.cuda() for k, v in w.items()}
+    out, gids, grw, glog = q35.moe_block(x1.cuda(), wd, 8)
+    # routing computed on the device's own logits: bit-exact against the rule applied to those logits ...
+    assert torch.equal(gids.cpu(), omoe.route(glog.cpu(), 8)[0])
+    # ... and the same experts as the CPU golden picked from its logits
+    assert torch.equal(gids.cpu(), ids)
+    assert rel_rms_err(out.cpu(), ref) <= TOL
+
+
+def test_moe_permute_slots_combine(q35):
+    T, K, NE, G = 50, 4, 16, 8
+    x1, w = moe_case(T, NE=NE, K=K, seed=8)
+    g = torch.Generator().manual_seed(9)
+    h2 = torch.randn((T, 2048), generator=g).to(torch.bfloat16)
+    base = torch.randn((T, 2048), generator=g).to(torch.bfloat16)
+    ids, rw = omoe.route(torch.randn((T, NE), generator=g), K)
+    tok, srw, loc, n = omoe.permute(ids, rw, G)
+    S = n + 3
+    gtok, gsrw, gloc, gn, counts = q35.moe_permute(ids.cuda(), rw.cuda(), NE, G, S=S)
+    assert int(gn.item()) == n
+    assert torch.equal(gtok.cpu()[:n], tok) and torch.equal(gsrw.cpu()[:n], srw) and torch.equal(gloc.cpu(), loc)
+    assert (gsrw.cpu()[n:] == 0).all()
+    assert torch.equal(counts.cpu().long(), torch.bincount(ids.reshape(-1).long(), minlength=NE))
+    planes = cu(w["e_gw"], w["e_gs"], w["e_dw"], w["e_ds"])
+    for dt in (torch.float32, torch.bfloat16):
+        ref = omoe.slots(h2, tok, srw, w["e_gw"], w["e_gs"], w["e_dw"], w["e_ds"], out_dtype=dt)
+        sout = torch.full((S, G, 2048), float("nan"), dtype=dt).cuda()
+        q35.moe_slots_px(h2.cuda(), gtok, gsrw, *planes, sout, n_slots=gn)
+        assert rel_rms_err(sout.cpu()[:n], ref) <= TOL
+        assert (sout.cpu()[n:] == 0).all()
+        assert (sout.cpu()[:n].reshape(-1, 2048)[srw.reshape(-1) == 0] == 0).all()  # unused rows are zero
+        out = torch.empty_like(base).cuda()
+        q35.moe_combine(base.cuda(), gloc, sout, out)
+        assert torch.equal(out.cpu().view(torch.int16),
+                           omoe.combine(base, loc, sout.cpu().reshape(-1, 2048)).view(torch.int16))
+    full = omoe.experts_decode(h2, base, ids, rw, w["e_gw"], w["e_gs"], w["e_dw"], w["e_ds"])
+    assert rel_rms_err(out.cpu(), full) <= TOL
+
+
+@pytest.mark.parametrize("fmt", ["mxfp4", "mxfp8", "fp8row"])
+@pytest.mark.parametrize("T,N,K", [(1, 48, 512), (8, 256, 2048), (33, 130, 1024)])
+def test_linear_formats(q35, fmt, T, N, K):
+    g = torch.Generator().manual_seed(N + K)
+    x = torch.randn((T, K), generator=g).to(torch.bfloat16)
+    wf = torch.randn((N, K), generator=g) * 0.05
+    if fmt == "mxfp4":
+        w, s = codecs.quant_mxfp4(wf)
+        dq = codecs.dequant_mxfp4(w, s)
+    elif fmt == "mxfp8":
+        w, s = codecs.quant_mxfp8(wf)
+        dq = codecs.dequant_mxfp8(w, s)
+    else:
+        w, s = codecs.quant_fp8_rowwise(wf)
+        dq = codecs.dequant_fp8_rowwise(w, s)
+    ref = (x.float() @ dq.T)
+    out = q35.linear(x.cuda(), w.cuda(), s.cuda(), out_dtype=torch.float32)
+    assert rel_rms_err(out.cpu(), ref) <= 2e-3
+    outb = q35.linear(x.cuda(), w.cuda(), s.cuda())
+    assert rel_rms_err(outb.cpu(), ref.to(torch.bfloat16)) <= TOL
+    if fmt == "fp8row":  # the reference's fp8_gemm (operands scaled into bf16 first) stays within tolerance too
+        assert rel_rms_err(outb.cpu(), codecs.fp8_gemm(x, w, torch.ones(T), s)) <= TOL
+
+
+# ------------------------------------------------------------------------------------------------ attention
+def _attn_check(q35, ctxs, P=64, HKV=2, HQ=16, D=256, fp8=False, per_head=True, sm_scale=None, seed=1):
+    q, cache, indptr, indices, last, kvs = paged_case(ctxs, P=P, HKV=HKV, HQ=HQ, D=D, seed=seed, fp8=fp8,
+                                                      per_head_scale=per_head)
+    ref = oattn.paged_decode(q, cache, indptr, indices, last, sm_scale=sm_scale, kv_scale=kvs)
+    out = torch.full_like(q, float("nan")).cuda()
+    q35.paged_attention_decode(q.cuda(), cache.cuda(), indptr.cuda(), indices.cuda(), last.cuda(), out,
+                               sm_scale=sm_scale, kv_scale=None if kvs is None else kvs.cuda())
+    assert torch.isfinite(out).all()
+    for b, cx in enumerate(ctxs):
+        if cx == 0:
+            assert (out[b] == 0).all()
+    nz = [b for b, cx in enumerate(ctxs) if cx > 0]
+    if nz:
+        assert rel_rms_err(out.cpu()[nz], ref[nz]) <= TOL
+    return out
+
+
+def test_paged_decode_lengths_around_tile_and_page_edges(q35):
+    _attn_check(q35, [1, 15, 16, 17, 63, 64, 65, 127, 128, 129, 0, 300, 1000], sm_scale=1.0 / 16)
+
+
+def test_paged_decode_reference_history_cases_page256(q35):
+    # history 0 / 1 / 256 / 514 over noncontiguous 256-row pages (test_qwen35_runtime.py:57), 64-dim heads
+    _attn_check(q35, [0, 1, 256, 514], P=256, HKV=2, HQ=4, D=64, seed=359)
+
+
+def test_paged_decode_batch64_random_contexts(q35):
+    g = torch.Generator().manual_seed(1)
+    ctxs = torch.randint(64, 1500, (64,), generator=g).tolist()
+    _attn_check(q35, ctxs, sm_scale=1.0 / 16)
+
+
+def test_paged_decode_six_heads_per_kv_head_page16(q35):
+    _attn_check(q35, [5, 40, 333], P=16, HKV=4, HQ=24, D=256)
+    _attn_check(q35, [77, 130], P=32, HKV=1, HQ=8, D=128)
+
+
+@pytest.mark.parametrize("per_head", [True, False])
+def test_paged_decode_fp8_cache(q35, per_head):
+    _attn_check(q35, [1, 17, 64, 65, 500, 0, 1300], fp8=True, per_head=per_head, sm_scale=1.0 / 16)
+
+
+def test_paged_decode_poisoned_tail_rows_do_not_leak(q35):
+    ctxs = [10, 70]
+    q, cache, indptr, indices, last, _ = paged_case(ctxs)
+    ref = oattn.paged_decode(q, cache, indptr, indices, last)
+    poisoned = cache.clone()
+    for b, cx in enumerate(ctxs):  # everything past the context in the last page becomes NaN
+        page = int(indices[int(indptr[b + 1]) - 1])
+        poisoned[page, :, int(last[b]):] = float("nan")
+    out = q35.paged_attention_decode(q.cuda(), poisoned.cuda(), indptr.cuda(), indices.cuda(), last.cuda())
+    assert rel_rms_err(out.cpu(), ref) <= TOL
+
+
+def test_paged_decode_current_token_and_cache_write(q35):
+    hist = [0, 5, 64, 200]
+    P = 64
+    q, cache, _, _, _, _ = paged_case([h + 1 for h in hist], extra_pages=2)
+    n_pages = [h // P + 1 for h in hist]
+    g = torch.Generator().manual_seed(3)
+    indptr = torch.tensor([0, *torch.tensor(n_pages).cumsum(0).tolist()], dtype=torch.int32)
+    indices = torch.randperm(cache.shape[0], generator=g)[: sum(n_pages)].to(torch.int32)
+    last = torch.tensor([h % P for h in hist], dtype=torch.int32)
+    k_new = torch.randn((4, 2, 256), generator=g).to(torch.bfloat16)
+    v_new = torch.randn((4, 2, 256), generator=g).to(torch.bfloat16)
+    loc = torch.stack([indices[indptr[1:].long() - 1], last], 1).contiguous()
+    ref = oattn.paged_decode(q, cache, indptr, indices, last, k_new=k_new, v_new=v_new)
+    ref_cache = oattn.store_paged_kv(cache.clone(), loc, k_new, v_new)
+    gcache = cache.cuda()
+    out = q35.paged_attention_decode(q.cuda(), gcache, indptr.cuda(), indices.cuda(), last.cuda(), k_new=k_new.cuda(),
+                                     v_new=v_new.cuda(), cache_location=loc.cuda())
+    assert rel_rms_err(out.cpu(), ref) <= TOL
+    assert torch.equal(gcache.cpu().view(torch.int16), ref_cache.view(torch.int16))  # other rows untouched
+
+
+def test_bad_page_id_is_reported_not_faulted(q35):
+    q, cache, indptr, indices, last, _ = paged_case([100])
+    bad = indices.clone()
+    bad[0] = 10_000
+    q35.paged_attention_decode(q.cuda(), cache.cuda(), indptr.cuda(), bad.cuda(), last.cuda())
+    assert q35.device_status() & 1
+    assert q35.device_status() == 0
+
+
+# ------------------------------------------------------------------------------------------------ GDN
+def test_gdn_step_matches_golden(q35):
+    q, k, v, g, beta, s0 = gdn_step_case(B=5, NK=4, NV=8)
+    o_ref, s_ref = ogdn.recurrent(q, k, v, g, beta, s0)
+    o, s1 = q35.gdn_recurrent_step(q[:, 0].cuda(), k[:, 0].cuda(), v[:, 0].cuda(), g[:, 0].cuda(), beta[:, 0].cuda(),
+                                   s0.cuda(), state_out=torch.empty_like(s0).cuda())
+    assert rel_rms_err(o.cpu(), o_ref[:, 0]) <= TOL
+    torch.testing.assert_close(s1.cpu(), s_ref, rtol=0, atol=3e-3)  # the reference's temporal-state tolerance
+
+
+def test_gdn_step_in_place_and_chained_tokens(q35):
+    B, NK, NV, T = 3, 2, 6, 6  # three value heads per key head
+    g = torch.Generator().manual_seed(7)
+    q = (ogdn.l2norm(torch.randn((B, T, NK, 128), generator=g)).float() * 128 ** -0.5).to(torch.bfloat16)
+    k = ogdn.l2norm(torch.randn((B, T, NK, 128), generator=g))
+    v = torch.randn((B, T, NV, 128), generator=g).to(torch.bfloat16)
+    beta = torch.sigmoid(torch.randn((B, T, NV), generator=g)).to(torch.bfloat16)
+    gg = -torch.nn.functional.softplus(torch.randn((B, T, NV), generator=g))
+    s0 = torch.randn((B, NV, 128, 128), generator=g) * 0.03
+    o_ref, s_ref = ogdn.recurrent(q, k, v, gg, beta, s0)
+    st = s0.cuda()
+    outs = []
+    for t in range(T):
+        o, st = q35.gdn_recurrent_step(*cu(q[:, t].contiguous(), k[:, t].contiguous(), v[:, t].contiguous(),
+                                           gg[:, t].contiguous(), beta[:, t].contiguous()), st)  # in place
+        outs.append(o.cpu())
+    assert rel_rms_err(torch.stack(outs, 1), o_ref) <= 3e-2  # bf16 rounding flips compound over a chain of tokens
+    torch.testing.assert_close(st.cpu(), s_ref, rtol=0, atol=4e-3)
+
+
+def test_gdn_conv_matches_golden_bitwise(q35, golden):
+    f = golden("conv1d")
+    y, so = q35.gdn_conv1d_silu(f["x"].cuda(), f["weight"].cuda(), f["state_in"].cuda())
+    assert (y.cpu().float() - f["y"].float()).abs().max() <= 2 ** -8 * f["y"].float().abs().max()
+    assert torch.equal(so.cpu().view(torch.int16), f["state_out"].view(torch.int16))
+
+
+@pytest.mark.parametrize("T", [1, 2, 3, 200])
+def test_gdn_conv_long_and_in_place_state(q35, T):
+    g = torch.Generator().manual_seed(T)
+    B, C = 2, 8192
+    x = torch.randn((B, T, C), generator=g).to(torch.bfloat16)
+    w = (torch.randn((C, 4), generator=g) * 0.1).to(torch.bfloat16)
+    st = (torch.randn((B, 3, C), generator=g) * 0.1).to(torch.bfloat16)
+    y_ref, s_ref = ogdn.causal_conv1d_silu(x, w, st)
+    gst = st.cuda()
+    y, so = q35.gdn_conv1d_silu(x.cuda(), w.cuda(), gst, conv_out=gst)
+    assert rel_rms_err(y.cpu(), y_ref) <= 1e-2
+    assert torch.equal(so.cpu().view(torch.int16), s_ref.contiguous().view(torch.int16))
