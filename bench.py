@@ -124,12 +124,12 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    clocks = ClockSampler(local) if rank == 0 else None
+    if clocks:
+        clocks.start()  # sampled from the warm-up to the end of the end-to-end loop (nvidia-smi, every 100 ms)
     for _ in range(max(args.warmup, 3)):
         step()
     barrier()
-    clocks = ClockSampler(local) if rank == 0 else None
-    if clocks:
-        clocks.start()
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     t0.record()
@@ -323,8 +323,8 @@ def run_profile_case(name, reps):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--steps", type=int, default=300)
+    ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
     ap.add_argument("--profile-case", choices=["attn", "gdn", "moe"], help="run one kernel on a capture-sized case")

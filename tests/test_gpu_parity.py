@@ -134,8 +134,9 @@ def test_moe_permute_slots_combine(q35):
         assert (sout.cpu()[:n].reshape(-1, 2048)[srw.reshape(-1) == 0] == 0).all()  # unused rows are zero
         out = torch.empty_like(base).cuda()
         q35.moe_combine(base.cuda(), gloc, sout, out)
-        assert torch.equal(out.cpu().view(torch.int16),
-                           omoe.combine(base, loc, sout.cpu().reshape(-1, 2048)).view(torch.int16))
+        # same inputs on both sides; only the order of the K fp32 additions differs (the kernel adds row by row as
+        # the reference kernel does, the golden sums the rows first): at most one bf16 rounding step
+        assert_parity(out.cpu(), omoe.combine(base, loc, sout.cpu().reshape(-1, 2048)), tol=1e-3)
     full = omoe.experts_decode(h2, base, ids, rw, w["e_gw"], w["e_gs"], w["e_dw"], w["e_ds"])
     assert_parity(out.cpu(), full)
 
