@@ -125,7 +125,7 @@ def test_moe_permute_slots_combine(q35):
     assert (gsrw.cpu()[n:] == 0).all()
     assert torch.equal(counts.cpu().long(), torch.bincount(ids.reshape(-1).long(), minlength=NE))
     planes = cu(w["e_gw"], w["e_gs"], w["e_dw"], w["e_ds"])
-    for dt in (torch.float32, torch.bfloat16):
+    for dt in (torch.bfloat16, torch.float32):  # fp32 last: the end-to-end check below uses the fp32 slot rows
         ref = omoe.slots(h2, tok, srw, w["e_gw"], w["e_gs"], w["e_dw"], w["e_ds"], out_dtype=dt)
         sout = torch.full((S, G, 2048), float("nan"), dtype=dt).cuda()
         q35.moe_slots_px(h2.cuda(), gtok, gsrw, *planes, sout, n_slots=gn)
