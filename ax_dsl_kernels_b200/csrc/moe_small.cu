@@ -109,7 +109,7 @@ __global__ void __launch_bounds__(256) moe_group_count_kernel(const int* __restr
       for (int k = 0; k < K; ++k) {
         const int id = ids[size_t(t) * K + k];
         if (id == e && hit < 0) hit = k;
-        if (e == 0 && (id < 0 || id >= NE)) atomicOr(status, DS_BAD_EXPERT);
+        if (e == 0 && id >= NE) atomicOr(status, DS_BAD_EXPERT);  // negative ids mean "not on this rank"
       }
     }
     const unsigned m = __ballot_sync(0xffffffffu, hit >= 0);
@@ -222,6 +222,29 @@ int run_moe_permute(Call& c) {
 // ---------------------------------------------------------------------------------------------------------------
 // moe.combine: out[t] = bf16(base[t] + sum_k sout[loc[k, t]]), fp32, k ascending
 // (models/qwen35_2b/whole/src/q35_moe_prefill.py:201-214).  One thread per 8 channels.
+// expert-parallel form: partial[t] = sum over the pairs present on this rank (loc >= 0) of sout[loc[k, t]], fp32
+__global__ void __launch_bounds__(256) moe_partial_sum_kernel(const int* __restrict__ loc, const float* __restrict__ sout,
+                                                              float* __restrict__ partial, int T, int H, int K, int R) {
+  const int t = blockIdx.x;
+  for (int h = threadIdx.x * 4; h < H; h += blockDim.x * 4) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int k = 0; k < K; ++k) {
+      const int r = loc[size_t(k) * T + t];
+      if (r < 0 || r >= R) continue;
+      const float4 a = *reinterpret_cast<const float4*>(sout + size_t(r) * H + h);
+      acc.x += a.x; acc.y += a.y; acc.z += a.z; acc.w += a.w;
+    }
+    *reinterpret_cast<float4*>(partial + size_t(t) * H + h) = acc;
+  }
+}
+
+int launch_partial_sum(const int* loc, const float* sout, float* partial, int T, int H, int K, int R,
+                       cudaStream_t stream) {
+  moe_partial_sum_kernel<<<unsigned(T), 256, 0, stream>>>(loc, sout, partial, T, H, K, R);
+  Q35_CUDA_LAUNCH_CHECK("moe partial sum");
+  return 0;
+}
+
 template <typename ST>
 __global__ void __launch_bounds__(256) moe_combine_kernel(const __nv_bfloat16* __restrict__ base,
                                                           const int* __restrict__ loc, const ST* __restrict__ sout,

@@ -74,22 +74,27 @@ __global__ void __launch_bounds__(256) experts_build_rows_kernel(const int* __re
 }
 
 int run_moe_experts(Call& c) {
-  Tensor h2, base, ids, rw, gw, gs, dw, ds, out, ws;
+  Tensor h2, base, ids, rw, gw, gs, dw, ds, out, partial, ws;
   Q35_TRY(c.get("h2", M(Q35_BF16), &h2));
-  Q35_TRY(c.get("base", M(Q35_BF16), &base));
+  Q35_TRY(c.get("partial_out", M(Q35_F32), &partial, false));  // expert-parallel form: fp32 sums, no base
+  Q35_TRY(c.get("base", M(Q35_BF16), &base, !partial.present));
   Q35_TRY(c.get("ids", M(Q35_I32), &ids));
   Q35_TRY(c.get("rw", M(Q35_F32), &rw));
   Q35_TRY(c.get("e_gw", M_BYTES, &gw));
   Q35_TRY(c.get("e_gs", M(Q35_U8), &gs));
   Q35_TRY(c.get("e_dw", M_BYTES, &dw));
   Q35_TRY(c.get("e_ds", M(Q35_U8), &ds));
-  Q35_TRY(c.get("out", M(Q35_BF16), &out));
+  Q35_TRY(c.get("out", M(Q35_BF16), &out, !partial.present));
   Q35_REQUIRE(gw.nd == 3 && gs.nd == 3 && dw.nd == 3 && ds.nd == 3 && ids.nd == 2, Q35_ERR_SHAPE,
               "moe.experts: expert planes must be rank 3, ids rank 2");
   const int64_t NE = gw.s[0], FE2 = gw.s[1], H = gw.s[2] * 2, FE = FE2 / 2;
   const int64_t T = ids.s[0], K = ids.s[1];
-  Q35_REQUIRE(h2.numel() == T * H && base.numel() == T * H && out.numel() == T * H, Q35_ERR_SHAPE,
-              "moe.experts: h2 / base / out must be [T=%lld, H=%lld]", (long long)T, (long long)H);
+  Q35_REQUIRE(h2.numel() == T * H, Q35_ERR_SHAPE, "moe.experts: h2 must be [T=%lld, H=%lld]", (long long)T, (long long)H);
+  if (partial.present) {
+    Q35_REQUIRE(partial.numel() == T * H, Q35_ERR_SHAPE, "moe.experts: partial_out must be [T, H]");
+  } else {
+    Q35_REQUIRE(base.numel() == T * H && out.numel() == T * H, Q35_ERR_SHAPE, "moe.experts: base / out must be [T, H]");
+  }
   Q35_REQUIRE(rw.numel() == T * K, Q35_ERR_SHAPE, "moe.experts: rw must be [T, K]");
   Q35_REQUIRE(gs.s[0] == NE && gs.s[1] == FE2 && gs.s[2] == H / 32, Q35_ERR_SHAPE, "moe.experts: e_gs [NE, 2FE, H/32]");
   Q35_REQUIRE(dw.s[0] == NE && dw.s[1] == H && dw.s[2] == FE / 2, Q35_ERR_SHAPE, "moe.experts: e_dw [NE, H, FE/2]");
@@ -110,12 +115,14 @@ int run_moe_experts(Call& c) {
   carve(w, counts, list, g_expert, g_n, g_row0, src, rw_row, loc, act, sout);
   Q35_TRY(c.workspace(w.off, &ws));
   if (c.dry || T == 0) return 0;
-  Q35_REQUIRE(aligned16(h2.p) && aligned16(base.p) && aligned16(out.p) && aligned16(gw.p) && aligned16(dw.p) &&
+  Q35_REQUIRE(aligned16(h2.p) && (partial.present ? aligned16(partial.p) : aligned16(base.p) && aligned16(out.p)) &&
+                  aligned16(gw.p) && aligned16(dw.p) &&
                   (uintptr_t(gs.p) & 1) == 0 && (uintptr_t(ds.p) & 1) == 0,
               Q35_ERR_ALIGN, "moe.experts: pointers must be 16-byte aligned");
   WsCarver wr{ws.as<uint8_t>()};
   carve(wr, counts, list, g_expert, g_n, g_row0, src, rw_row, loc, act, sout);
 
+  if (partial.present) cudaMemsetAsync(loc, 0xff, size_t(P) * 4, c.stream);  // pairs of other ranks: loc = -1
   Q35_TRY(launch_group_count(ids.as<int>(), int(T), int(K), int(NE), counts, list, c.stream));
   experts_build_rows_kernel<<<unsigned(NE), 256, 0, c.stream>>>(counts, list, rw.as<float>(), int(T), int(K), int(NE),
                                                                 g_expert, g_n, g_row0, src, rw_row, loc);
@@ -142,6 +149,7 @@ int run_moe_experts(Call& c) {
   d.x = act; d.x_stride = int(FE); d.src = nullptr;
   d.f_out = sout; d.out_stride = int(H); d.rw_row = rw_row;
   Q35_TRY((launch_skinny<W_MXFP4, EPI_ROW_SCALE>(d, nt, int((H + 127) / 128), int(NE), c.stream)));
+  if (partial.present) return launch_partial_sum(loc, sout, partial.as<float>(), int(T), int(H), int(K), int(P), c.stream);
   return launch_combine(base.as<__nv_bfloat16>(), loc, sout, true, out.as<__nv_bfloat16>(), int(T), int(H), int(K),
                         int(P), c.stream);
 }

@@ -79,6 +79,34 @@ def test_moe_experts_one_expert_takes_every_token(q35):
     assert_parity(out.cpu(), ref)
 
 
+def test_moe_experts_partial_sums_for_expert_parallel(q35):
+    """ids < 0 mark pairs owned by another rank: they are skipped and the fp32 partial holds only the local sums"""
+    T, NE = 12, 16
+    x1, w = moe_case(T, NE=NE, seed=17)
+    g = torch.Generator().manual_seed(4)
+    h2 = torch.randn((T, 2048), generator=g).to(torch.bfloat16)
+    ids, rw = omoe.route(torch.randn((T, NE), generator=g), 8)
+    lo, hi = 4, 8
+    from ax_dsl_kernels_b200.parallel import local_ids
+    lids = local_ids(ids, lo, hi)
+    planes = [w[n][lo:hi].contiguous() for n in ("e_gw", "e_gs", "e_dw", "e_ds")]
+    ref = torch.zeros((T, 2048))
+    for t in range(T):
+        for i in range(8):
+            if lids[t, i] >= 0:
+                one = omoe.experts_decode(h2[t:t + 1], torch.zeros((1, 2048), dtype=torch.bfloat16), lids[t:t + 1, i:i + 1],
+                                          torch.ones((1, 1)), *planes).float()[0]
+                ref[t] += rw[t, i] * one
+    partial = torch.full((T, 2048), float("nan")).cuda()
+    q35.run("moe.experts", h2=h2.cuda(), ids=lids.cuda(), rw=rw.cuda(), e_gw=planes[0].cuda(), e_gs=planes[1].cuda(),
+            e_dw=planes[2].cuda(), e_ds=planes[3].cuda(), partial_out=partial)
+    assert_parity(partial.cpu(), ref)
+    none = torch.full_like(lids, -1).cuda()
+    q35.run("moe.experts", h2=h2.cuda(), ids=none, rw=rw.cuda(), e_gw=planes[0].cuda(), e_gs=planes[1].cuda(),
+            e_dw=planes[2].cuda(), e_ds=planes[3].cuda(), partial_out=partial)
+    assert (partial == 0).all()
+
+
 @pytest.mark.parametrize("fmt", ["mxfp4", "mxfp8"])
 def test_moe_pre(q35, fmt):
     T = 9
