@@ -189,8 +189,13 @@ def test_linear_formats(q35, fmt, T, N, K):
     assert rel_rms_err(out.cpu(), ref) <= 2e-3
     outb = q35.linear(x.cuda(), w.cuda(), s.cuda())
     assert rel_rms_err(outb.cpu(), ref.to(torch.bfloat16)) <= TOL
-    if fmt == "fp8row":  # the reference's fp8_gemm (operands scaled into bf16 first) stays within tolerance too
-        assert rel_rms_err(outb.cpu(), codecs.fp8_gemm(x, w, torch.ones(T), s)) <= TOL
+    if fmt == "fp8row":
+        # the reference's fp8_gemm golden rounds every dequantised weight to the OUTPUT dtype (bf16) before the
+        # product (gemm.py:143-151): that rounding alone puts the golden 2-3 % of RMS (worst element) away from
+        # exact arithmetic at K = 2048; the kernel keeps the weights exact and scales the fp32 accumulator
+        golden = codecs.fp8_gemm(x, w, torch.ones(T), s)
+        assert rel_rms_err(golden, ref) <= 5e-2
+        assert rel_rms_err(outb.cpu(), golden) <= 5e-2
 
 
 # ------------------------------------------------------------------------------------------------ attention
