@@ -182,7 +182,7 @@ def run_ours(args):
             "weights expanded to bf16, fp32 accumulate/state", "data": "synthetic (seeded, on-device)",
             "config": {"workload": workload_name(), "batch_per_gpu": B, "context": CTX,
                        "parallelism": "1 GPU" if world == 1 else f"sequences data-parallel x{world}, experts sharded "
-                       f"x{world} (NCCL all-to-all)", "l2": "inputs larger than L2 (2.1 GB KV + 0.43 GB experts + "
+                       f"x{world} (NCCL all-gather of tokens + reduce-scatter of expert sums)", "l2": "inputs larger than L2 (2.1 GB KV + 0.43 GB experts + "
                        "0.27 GB state per step)"},
             "e2e": {"value": world * B * args.steps / (e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h},
