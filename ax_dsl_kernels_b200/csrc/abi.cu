@@ -114,6 +114,9 @@ static const RoleDef kRoles[] = {
     {"linear",
      R"({"in":[["x","bf16","[T,K]"],["w","u8|e4m3|bf16","[N,K/2]|[N,K]"],["s","u8|f32","[N,K/32]|[N] optional"],["bias","f32","[N] optional"]],"out":[["out","bf16|f32","[T,N]"]]})",
      run_linear},
+    {"linear.tc",
+     R"({"in":[["x","bf16","[T,K]"],["w","u8","[N,K/2]"],["s","u8","[N,K/32]"],["bias","f32","[N] optional"],["workspace","u8","[*]"]],"out":[["out","bf16|f32","[T,N]"]]})",
+     run_linear_tc},
 };
 static const int kNumRoles = int(sizeof(kRoles) / sizeof(kRoles[0]));
 

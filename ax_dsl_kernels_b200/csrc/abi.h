@@ -84,5 +84,6 @@ int run_attn_kv_write(Call&);
 int run_gdn_step(Call&);
 int run_gdn_conv(Call&);
 int run_linear(Call&);
+int run_linear_tc(Call&);
 
 }  // namespace q35

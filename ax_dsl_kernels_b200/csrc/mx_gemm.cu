@@ -4,6 +4,8 @@
 #include "common.cuh"
 #include "moe_group.cuh"
 #include "mx_gemm.cuh"
+#include "tc_gemm.cuh"
+#include "tc_host.h"
 
 namespace q35 {
 
@@ -41,6 +43,46 @@ static int launch_skinny(const SkinnyArgs& a, int nt, int tiles, int groups, cud
 }
 
 static int pick_nt(int64_t rows_per_group) { return rows_per_group <= 8 ? 1 : rows_per_group <= 16 ? 2 : 4; }
+
+// ---------------------------------------------------------------------------------------------------------------
+// Routed experts on the tensor cores: quantise the gathered activation rows, gate-up GEMM with SiLU * up epilogue,
+// quantise the bf16 activations, down GEMM scaled by the routing weight.  Used when H and FE are multiples of 512
+// (every Qwen3.5 MoE shape); other shapes take the CUDA-core weight-streaming kernel.
+struct ExpertPlanes {
+  const uint8_t *gw, *gs, *dw, *ds;
+  int64_t NE, FE, H;
+};
+
+static bool tc_shapes_ok(int64_t H, int64_t FE) { return H % 512 == 0 && FE % 512 == 0; }
+
+static int64_t tc_routed_bytes(int64_t R, int64_t H, int64_t FE) { return tc_quant_bytes(R, H) + tc_quant_bytes(R, FE); }
+
+static int tc_routed(const ExpertPlanes& e, const __nv_bfloat16* x, const int* src, int R, int groups,
+                     const int* g_expert, const int* g_n, const int* g_row0, int nb, __nv_bfloat16* act,
+                     uint8_t* qws, float* f_out, __nv_bfloat16* b_out, const float* rw_row, cudaStream_t stream) {
+  const TcQuant q1 = tc_quant_carve(qws, R, e.H);
+  const TcQuant q2 = tc_quant_carve(qws + tc_quant_bytes(R, e.H), R, e.FE);
+  Q35_TRY(tc_quantize(x, int(e.H), src, R, int(e.H), q1, stream));
+  TcArgs a{};
+  a.g_expert = g_expert; a.g_n = g_n; a.g_row0 = g_row0; a.n_planes = int(e.NE);
+  a.K = int(e.H);
+  a.plane_rows[0] = a.plane_rows[1] = int(2 * e.FE);
+  a.roff[0] = 0; a.roff[1] = int(e.FE); a.lim[0] = int(e.FE); a.lim[1] = int(2 * e.FE); a.tile_rows = 64;
+  a.sw[0] = a.sw[1] = e.gs; a.s_plane = 2 * e.FE * (e.H / 32);
+  a.act_rows = int(e.FE); a.act_out = act;
+  const TcWeights wg{{e.gw, e.gw}, {uint64_t(e.NE * 2 * e.FE), uint64_t(e.NE * 2 * e.FE)}};
+  Q35_TRY(tc_launch<TC_EPI_SILU_MUL>(wg, q1, a, nb, int(e.FE / 64), groups, stream));
+  Q35_TRY(tc_quantize(act, int(e.FE), nullptr, R, int(e.FE), q2, stream));
+  TcArgs d{};
+  d.g_expert = g_expert; d.g_n = g_n; d.g_row0 = g_row0; d.n_planes = int(e.NE);
+  d.K = int(e.FE);
+  d.plane_rows[0] = d.plane_rows[1] = int(e.H);
+  d.roff[0] = 0; d.roff[1] = 64; d.lim[0] = d.lim[1] = int(e.H); d.tile_rows = 128;
+  d.sw[0] = d.sw[1] = e.ds; d.s_plane = e.H * (e.FE / 32);
+  d.f_out = f_out; d.b_out = b_out; d.out_stride = int(e.H); d.rw_row = rw_row;
+  const TcWeights wd{{e.dw, e.dw}, {uint64_t(e.NE * e.H), uint64_t(e.NE * e.H)}};
+  return tc_launch<TC_EPI_ROW_SCALE>(wd, q2, d, nb, int(e.H / 128), groups, stream);
+}
 
 // ---------------------------------------------------------------------------------------------------------------
 // moe.experts: decode form of the routed experts with planar expert tensors.
@@ -101,6 +143,8 @@ int run_moe_experts(Call& c) {
   Q35_REQUIRE(ds.s[0] == NE && ds.s[1] == H && ds.s[2] == FE / 32, Q35_ERR_SHAPE, "moe.experts: e_ds [NE, H, FE/32]");
   Q35_REQUIRE(H % 256 == 0 && FE % 256 == 0, Q35_ERR_UNSUPPORTED, "moe.experts: H and FE must be multiples of 256");
   const int64_t P = T * K;
+  const bool use_tc = tc_shapes_ok(H, FE);
+  uint8_t* qws = nullptr;
   WsCarver w{nullptr};
   auto carve = [&](WsCarver& cw, int*& counts, int*& list, int*& g_expert, int*& g_n, int*& g_row0, int*& src,
                    float*& rw_row, int*& loc, __nv_bfloat16*& act, float*& sout) {
@@ -108,6 +152,7 @@ int run_moe_experts(Call& c) {
     g_expert = cw.take<int>(NE); g_n = cw.take<int>(NE); g_row0 = cw.take<int>(NE);
     src = cw.take<int>(P); rw_row = cw.take<float>(P); loc = cw.take<int>(P);
     act = cw.take<__nv_bfloat16>(P * FE); sout = cw.take<float>(P * H);
+    qws = use_tc ? cw.take<uint8_t>(tc_routed_bytes(P, H, FE)) : nullptr;
   };
   int *counts, *list, *g_expert, *g_n, *g_row0, *src, *loc;
   float *rw_row, *sout;
@@ -127,6 +172,15 @@ int run_moe_experts(Call& c) {
   experts_build_rows_kernel<<<unsigned(NE), 256, 0, c.stream>>>(counts, list, rw.as<float>(), int(T), int(K), int(NE),
                                                                 g_expert, g_n, g_row0, src, rw_row, loc);
   Q35_CUDA_LAUNCH_CHECK("moe.experts rows");
+  if (use_tc) {
+    const ExpertPlanes ep{gw.as<uint8_t>(), gs.as<uint8_t>(), dw.as<uint8_t>(), ds.as<uint8_t>(), NE, FE, H};
+    Q35_TRY(tc_routed(ep, h2.as<__nv_bfloat16>(), src, int(P), int(NE), g_expert, g_n, g_row0,
+                      int((P + NE - 1) / NE), act, qws, sout, nullptr, rw_row, c.stream));
+    if (partial.present)
+      return launch_partial_sum(loc, sout, partial.as<float>(), int(T), int(H), int(K), int(P), c.stream);
+    return launch_combine(base.as<__nv_bfloat16>(), loc, sout, true, out.as<__nv_bfloat16>(), int(T), int(H), int(K),
+                          int(P), c.stream);
+  }
   const int nt = pick_nt((P + NE - 1) / NE);
   SkinnyArgs a{};
   a.status = device_status_ptr();

@@ -1,0 +1,171 @@
+// Host side of the block-scaled tensor-core GEMM: tensor maps, activation quantisation, launch.
+#include "abi.h"
+#include "common.cuh"
+#include "tc_gemm.cuh"
+#include "tc_host.h"
+
+namespace q35 {
+
+// ---------------------------------------------------------------------------------------------------------------
+// cuTensorMapEncodeTiled is taken from the driver at run time, so the library links against the runtime only.
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// 2D row-major tensor [rows, cols] with a [box_rows, 128-element] box and 128-byte swizzle
+static int make_map(CUtensorMap* m, bool fp4, const void* base, uint64_t rows, uint64_t cols, uint64_t pitch_bytes,
+                    uint32_t box_rows, const char* what) {
+  EncodeTiledFn fn = encode_fn();
+  Q35_REQUIRE(fn != nullptr, Q35_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {pitch_bytes};
+  const cuuint32_t box[2] = {128, box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = fn(m, fp4 ? CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2,
+                        const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  Q35_REQUIRE(r == CUDA_SUCCESS, Q35_ERR_CUDA, "tensor map for %s rejected by the driver (CUresult %d)", what, int(r));
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// x (bf16) -> two E4M3 terms with UE8M0 block-32 scales: x = hi * 2^eh + lo * 2^el.  One warp per 32-block,
+// rows gathered through `src` (destination row -> source row; nullptr = identity).
+__device__ __forceinline__ int e8m0_for(float amax) {  // smallest e with amax * 2^-e <= 448 (= 1.75 * 2^8)
+  if (amax == 0.f) return -127;
+  const uint32_t b = __float_as_uint(amax);
+  const int E = int(b >> 23) - 127;
+  const uint32_t mant = b & 0x7fffffu;
+  int e = E - 8 + (mant > 0x600000u ? 1 : 0);  // mantissa above 1.75 needs one more octave
+  return max(-127, min(127, e));
+}
+
+__global__ void __launch_bounds__(256) tc_quant_kernel(const __nv_bfloat16* __restrict__ x, int x_stride,
+                                                       const int* __restrict__ src, int R, int K,
+                                                       uint8_t* __restrict__ qh, uint8_t* __restrict__ ql,
+                                                       uint8_t* __restrict__ sh, uint8_t* __restrict__ sl) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  const int blocks_per_row = K / 32;
+  if (warp >= R * blocks_per_row) return;
+  const int row = warp / blocks_per_row, kb = warp % blocks_per_row;
+  const long long srow = src ? src[row] : row;
+  const float v = __bfloat162float(x[srow * x_stride + kb * 32 + lane]);
+  const int eh = e8m0_for(warp_max(fabsf(v)));
+  const __nv_fp8_e4m3 h(v * exp2f(float(-eh)));
+  const float rem = v - float(h) * exp2f(float(eh));
+  const int el = e8m0_for(warp_max(fabsf(rem)));
+  const __nv_fp8_e4m3 l(rem * exp2f(float(-el)));
+  const long long o = (long long)row * K + kb * 32 + lane;
+  qh[o] = *reinterpret_cast<const uint8_t*>(&h);
+  ql[o] = *reinterpret_cast<const uint8_t*>(&l);
+  if (lane == 0) {
+    sh[(long long)row * blocks_per_row + kb] = uint8_t(eh + 127);
+    sl[(long long)row * blocks_per_row + kb] = uint8_t(el + 127);
+  }
+}
+
+int tc_quantize(const __nv_bfloat16* x, int x_stride, const int* src, int R, int K, const TcQuant& q,
+                cudaStream_t stream) {
+  const long long warps = (long long)R * (K / 32);
+  if (warps == 0) return 0;
+  tc_quant_kernel<<<unsigned((warps + 7) / 8), 256, 0, stream>>>(x, x_stride, src, R, K, q.qh, q.ql, q.sh, q.sl);
+  Q35_CUDA_LAUNCH_CHECK("tc quantize");
+  return 0;
+}
+
+int64_t tc_quant_bytes(int64_t R, int64_t K) { return 2 * (R * K + 256) + 2 * (R * (K / 32) + 256) + 1024; }
+
+TcQuant tc_quant_carve(uint8_t* base, int64_t R, int64_t K) {
+  auto up = [](int64_t v) { return (v + 255) / 256 * 256; };
+  TcQuant q;
+  q.qh = base;
+  q.ql = q.qh + up(R * K);
+  q.sh = q.ql + up(R * K);
+  q.sl = q.sh + up(R * (K / 32));
+  q.R = int(R);
+  q.K = int(K);
+  return q;
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+template <int NB, int EPI>
+static int launch_nb(const CUtensorMap& w0, const CUtensorMap& w1, const CUtensorMap& xh, const CUtensorMap& xl,
+                     const TcArgs& a, int tiles, int groups, cudaStream_t stream) {
+  const int smem = TcCfg<NB>::smem_bytes(a.K);
+  static int attr_smem = 0;
+  if (smem > attr_smem) {
+    cudaFuncSetAttribute(tc_gemm_kernel<NB, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    attr_smem = smem;
+  }
+  const dim3 grid{unsigned(tiles), unsigned(groups), 1u};
+  tc_gemm_kernel<NB, EPI><<<grid, 192, smem, stream>>>(w0, w1, xh, xl, a);
+  Q35_CUDA_LAUNCH_CHECK("tc gemm");
+  return 0;
+}
+
+template <int EPI>
+int tc_launch(const TcWeights& w, const TcQuant& q, TcArgs a, int nb, int tiles, int groups, cudaStream_t stream) {
+  Q35_REQUIRE(a.K % 512 == 0 && a.K == q.K, Q35_ERR_UNSUPPORTED, "tc gemm: K must be a multiple of 512");
+  CUtensorMap w0, w1, xh, xl;
+  Q35_TRY(make_map(&w0, true, w.w[0], w.rows_total[0], a.K, a.K / 2, 64, "weights"));
+  Q35_TRY(make_map(&w1, true, w.w[1], w.rows_total[1], a.K, a.K / 2, 64, "weights"));
+  nb = nb <= 16 ? 16 : nb <= 32 ? 32 : 64;
+  Q35_TRY(make_map(&xh, false, q.qh, q.R, a.K, a.K, nb, "activations"));
+  Q35_TRY(make_map(&xl, false, q.ql, q.R, a.K, a.K, nb, "activations"));
+  a.sfh = q.sh; a.sfl = q.sl; a.total_rows = q.R;
+  a.status = device_status_ptr();
+  if (nb == 16) return launch_nb<16, EPI>(w0, w1, xh, xl, a, tiles, groups, stream);
+  if (nb == 32) return launch_nb<32, EPI>(w0, w1, xh, xl, a, tiles, groups, stream);
+  return launch_nb<64, EPI>(w0, w1, xh, xl, a, tiles, groups, stream);
+}
+
+template int tc_launch<TC_EPI_SILU_MUL>(const TcWeights&, const TcQuant&, TcArgs, int, int, int, cudaStream_t);
+template int tc_launch<TC_EPI_ROW_SCALE>(const TcWeights&, const TcQuant&, TcArgs, int, int, int, cudaStream_t);
+template int tc_launch<TC_EPI_SHARED_DOWN>(const TcWeights&, const TcQuant&, TcArgs, int, int, int, cudaStream_t);
+template int tc_launch<TC_EPI_PLAIN>(const TcWeights&, const TcQuant&, TcArgs, int, int, int, cudaStream_t);
+
+// ---------------------------------------------------------------------------------------------------------------
+// linear.tc: out[t, n] = x[t, :] . dequant_mxfp4(w[n, :]) on the tensor cores (same contract as `linear` with MXFP4
+// weights; reference: linear(x, w, s) of the MX projections, models/qwen35_2b/whole/src/q35_mx_build.py:100-115)
+int run_linear_tc(Call& c) {
+  Tensor x, w, s, bias, out, ws;
+  Q35_TRY(c.get("x", M(Q35_BF16), &x));
+  Q35_TRY(c.get("w", M_BYTES, &w));
+  Q35_TRY(c.get("s", M(Q35_U8), &s));
+  Q35_TRY(c.get("bias", M(Q35_F32), &bias, false));
+  Q35_TRY(c.get("out", M(Q35_BF16) | M(Q35_F32), &out));
+  Q35_REQUIRE(x.nd >= 2 && w.nd == 2, Q35_ERR_SHAPE, "linear.tc: x [T, K], w [N, K/2]");
+  const int64_t K = x.s[x.nd - 1], T = x.numel() / K, N = w.s[0];
+  Q35_REQUIRE(w.s[1] == K / 2 && s.numel() == N * (K / 32) && out.numel() == T * N, Q35_ERR_SHAPE, "linear.tc: shapes");
+  Q35_REQUIRE(K % 512 == 0, Q35_ERR_UNSUPPORTED, "linear.tc: K must be a multiple of 512");
+  Q35_TRY(c.workspace(tc_quant_bytes(T, K), &ws));
+  if (c.dry || T == 0 || N == 0) return 0;
+  Q35_REQUIRE((uintptr_t(w.p) & 31) == 0 && aligned16(x.p) && aligned16(s.p), Q35_ERR_ALIGN, "linear.tc: alignment");
+  const TcQuant q = tc_quant_carve(ws.as<uint8_t>(), T, K);
+  Q35_TRY(tc_quantize(x.as<__nv_bfloat16>(), int(K), nullptr, int(T), int(K), q, c.stream));
+  TcWeights tw{{w.as<uint8_t>(), w.as<uint8_t>()}, {uint64_t(N), uint64_t(N)}};
+  TcArgs a{};
+  a.n_dense = int(T); a.n_planes = 1; a.K = int(K);
+  a.plane_rows[0] = a.plane_rows[1] = int(N);
+  a.roff[0] = 0; a.roff[1] = 64; a.lim[0] = a.lim[1] = int(N); a.tile_rows = 128;
+  a.sw[0] = a.sw[1] = s.as<uint8_t>(); a.s_plane = 0;
+  if (out.dtype == Q35_F32) a.f_out = out.as<float>(); else a.b_out = out.as<__nv_bfloat16>();
+  a.out_stride = int(N);
+  a.bias = bias.present ? bias.as<float>() : nullptr;
+  return tc_launch<TC_EPI_PLAIN>(tw, q, a, int(T), int((N + 127) / 128), 1, c.stream);
+}
+
+}  // namespace q35

@@ -1,0 +1,30 @@
+// Host-side interface of the block-scaled tensor-core GEMM (tc_gemm.cu), shared with the MoE launchers.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <cstdint>
+
+namespace q35 {
+
+struct TcArgs;
+
+struct TcWeights {            // the two 64-row halves of a tile may come from different matrices (gate / up)
+  const uint8_t* w[2];        // packed FP4 [rows_total, K/2]
+  uint64_t rows_total[2];     // rows of each matrix over all expert planes
+};
+
+struct TcQuant {              // activations as two E4M3 terms + UE8M0 block-32 scales, rows in destination order
+  uint8_t *qh, *ql;           // [R, K]
+  uint8_t *sh, *sl;           // [R, K/32]
+  int R, K;
+};
+
+int64_t tc_quant_bytes(int64_t R, int64_t K);
+TcQuant tc_quant_carve(uint8_t* base, int64_t R, int64_t K);
+int tc_quantize(const __nv_bfloat16* x, int x_stride, const int* src, int R, int K, const TcQuant& q,
+                cudaStream_t stream);
+
+template <int EPI>
+int tc_launch(const TcWeights& w, const TcQuant& q, TcArgs a, int nb, int tiles, int groups, cudaStream_t stream);
+
+}  // namespace q35

@@ -332,3 +332,20 @@ def test_gdn_conv_long_and_in_place_state(q35, T):
     y, so = q35.gdn_conv1d_silu(x.cuda(), w.cuda(), gst, conv_out=gst)
     assert rel_rms_err(y.cpu(), y_ref) <= 1e-2
     assert torch.equal(so.cpu().view(torch.int16), s_ref.contiguous().view(torch.int16))
+
+
+# ------------------------------------------------------------------------------------------------ tensor-core GEMM
+@pytest.mark.parametrize("T,N,K", [(8, 128, 512), (16, 1024, 2048), (40, 130, 512), (100, 384, 2048), (1, 64, 1024)])
+def test_linear_tc_block_scaled_mma(q35, T, N, K):
+    """tcgen05 kind::mxf8f6f4 path: MXFP4 weights straight from TMA, activations as two E4M3 terms"""
+    g = torch.Generator().manual_seed(T * N + K)
+    w, s = codecs.random_mxfp4((N, K), g)
+    x = torch.randn((T, K), generator=g).to(torch.bfloat16)
+    ref = x.double() @ codecs.dequant_mxfp4(w, s).double().T
+    out = torch.full((T, N), float("nan"), device="cuda")
+    q35.run("linear.tc", x=x.cuda(), w=w.cuda(), s=s.cuda(), out=out)
+    assert rel_rms_err(out.cpu().double(), ref) <= 1e-4
+    outb = torch.empty((T, N), dtype=torch.bfloat16, device="cuda")
+    bias = torch.randn(N, generator=g)
+    q35.run("linear.tc", x=x.cuda(), w=w.cuda(), s=s.cuda(), bias=bias.cuda(), out=outb)
+    assert_parity(outb.cpu(), (ref + bias.double()).to(torch.bfloat16))
