@@ -55,15 +55,20 @@ struct ExpertPlanes {
 
 static bool tc_shapes_ok(int64_t H, int64_t FE) { return H % 512 == 0 && FE % 512 == 0; }
 
-static int64_t tc_routed_bytes(int64_t R, int64_t H, int64_t FE) { return tc_quant_bytes(R, H) + tc_quant_bytes(R, FE); }
+static int64_t tc_routed_bytes(int64_t R, int64_t H, int64_t FE, int64_t groups = 0) {
+  return tc_quant_bytes(R, H) + tc_quant_bytes(R, FE) + (groups + 1) * 4 + 256;
+}
 
 static int tc_routed(const ExpertPlanes& e, const __nv_bfloat16* x, const int* src, int R, int groups,
                      const int* g_expert, const int* g_n, const int* g_row0, int nb, __nv_bfloat16* act,
                      uint8_t* qws, float* f_out, __nv_bfloat16* b_out, const float* rw_row, cudaStream_t stream) {
   const TcQuant q1 = tc_quant_carve(qws, R, e.H);
   const TcQuant q2 = tc_quant_carve(qws + tc_quant_bytes(R, e.H), R, e.FE);
+  int* active = reinterpret_cast<int*>(qws + (tc_quant_bytes(R, e.H) + tc_quant_bytes(R, e.FE) + 255) / 256 * 256);
+  Q35_TRY(tc_build_active(g_n, groups, active, stream));
   Q35_TRY(tc_quantize(x, int(e.H), src, R, int(e.H), q1, stream));
   TcArgs a{};
+  a.n_active = active; a.active = active + 1;
   a.g_expert = g_expert; a.g_n = g_n; a.g_row0 = g_row0; a.n_planes = int(e.NE);
   a.K = int(e.H);
   a.plane_rows[0] = a.plane_rows[1] = int(2 * e.FE);
@@ -74,6 +79,7 @@ static int tc_routed(const ExpertPlanes& e, const __nv_bfloat16* x, const int* s
   Q35_TRY(tc_launch<TC_EPI_SILU_MUL>(wg, q1, a, nb, int(e.FE / 64), groups, stream));
   Q35_TRY(tc_quantize(act, int(e.FE), nullptr, R, int(e.FE), q2, stream));
   TcArgs d{};
+  d.n_active = active; d.active = active + 1;
   d.g_expert = g_expert; d.g_n = g_n; d.g_row0 = g_row0; d.n_planes = int(e.NE);
   d.K = int(e.FE);
   d.plane_rows[0] = d.plane_rows[1] = int(e.H);
@@ -152,7 +158,7 @@ int run_moe_experts(Call& c) {
     g_expert = cw.take<int>(NE); g_n = cw.take<int>(NE); g_row0 = cw.take<int>(NE);
     src = cw.take<int>(P); rw_row = cw.take<float>(P); loc = cw.take<int>(P);
     act = cw.take<__nv_bfloat16>(P * FE); sout = cw.take<float>(P * H);
-    qws = use_tc ? cw.take<uint8_t>(tc_routed_bytes(P, H, FE)) : nullptr;
+    qws = use_tc ? cw.take<uint8_t>(tc_routed_bytes(P, H, FE, NE)) : nullptr;
   };
   int *counts, *list, *g_expert, *g_n, *g_row0, *src, *loc;
   float *rw_row, *sout;
@@ -377,9 +383,11 @@ int run_moe_pre(Call& c) {
   Q35_REQUIRE(sg.numel() == FS * (H / 32) && su.numel() == FS * (H / 32) && sd.numel() == H * (FS / 32), Q35_ERR_SHAPE,
               "moe.pre: scale shapes");
   Q35_REQUIRE(H % 256 == 0 && FS % 256 == 0, Q35_ERR_UNSUPPORTED, "moe.pre: H and FS must be multiples of 256");
+  const bool use_tc = f1 == W_MXFP4 && tc_shapes_ok(H, FS);
   WsCarver w{nullptr};
   __nv_bfloat16* act = w.take<__nv_bfloat16>(T * FS);
   float* gate = w.take<float>(T);
+  uint8_t* qws = use_tc ? w.take<uint8_t>(tc_routed_bytes(T, H, FS)) : nullptr;
   Q35_TRY(c.workspace(w.off, &ws));
   if (c.dry || T == 0) return 0;
   Q35_REQUIRE(aligned16(x1.p) && aligned16(out.p) && aligned16(h2o.p) && aligned16(wg.p) && aligned16(wu.p) &&
@@ -388,6 +396,7 @@ int run_moe_pre(Call& c) {
   WsCarver wc{ws.as<uint8_t>()};
   act = wc.take<__nv_bfloat16>(T * FS);
   gate = wc.take<float>(T);
+  qws = use_tc ? wc.take<uint8_t>(tc_routed_bytes(T, H, FS)) : nullptr;
   // eps is a host-side constant of the model (1e-6 for every Qwen3.5 config); an `eps` tensor is not read on device
   const float eps = 1e-6f;
   rmsnorm_kernel<<<unsigned(T), 256, 0, c.stream>>>(x1.as<__nv_bfloat16>(), ln2.as<float>(), h2o.as<__nv_bfloat16>(),
@@ -396,6 +405,28 @@ int run_moe_pre(Call& c) {
   router_kernel<<<dim3(unsigned((NE + 1 + 7) / 8), unsigned(T)), 256, 0, c.stream>>>(
       h2o.as<__nv_bfloat16>(), wr.as<__nv_bfloat16>(), wshg.as<__nv_bfloat16>(), lgo.as<float>(), gate, int(H), int(NE));
   Q35_CUDA_LAUNCH_CHECK("moe.pre router");
+  if (use_tc) {  // shared expert on the tensor cores: one dense group of T rows
+    const TcQuant q1 = tc_quant_carve(qws, T, H);
+    const TcQuant q2 = tc_quant_carve(qws + tc_quant_bytes(T, H), T, FS);
+    Q35_TRY(tc_quantize(h2o.as<__nv_bfloat16>(), int(H), nullptr, int(T), int(H), q1, c.stream));
+    TcArgs ta{};
+    ta.n_dense = int(T); ta.n_planes = 1; ta.K = int(H);
+    ta.plane_rows[0] = ta.plane_rows[1] = int(FS);
+    ta.roff[0] = ta.roff[1] = 0; ta.lim[0] = ta.lim[1] = int(FS); ta.tile_rows = 64;
+    ta.sw[0] = sg.as<uint8_t>(); ta.sw[1] = su.as<uint8_t>(); ta.s_plane = 0;
+    ta.act_rows = int(FS); ta.act_out = act;
+    const TcWeights wgu{{wg.as<uint8_t>(), wu.as<uint8_t>()}, {uint64_t(FS), uint64_t(FS)}};
+    Q35_TRY(tc_launch<TC_EPI_SILU_MUL>(wgu, q1, ta, int(T), int(FS / 64), 1, c.stream));
+    Q35_TRY(tc_quantize(act, int(FS), nullptr, int(T), int(FS), q2, c.stream));
+    TcArgs td{};
+    td.n_dense = int(T); td.n_planes = 1; td.K = int(FS);
+    td.plane_rows[0] = td.plane_rows[1] = int(H);
+    td.roff[0] = 0; td.roff[1] = 64; td.lim[0] = td.lim[1] = int(H); td.tile_rows = 128;
+    td.sw[0] = td.sw[1] = sd.as<uint8_t>(); td.s_plane = 0;
+    td.b_out = out.as<__nv_bfloat16>(); td.out_stride = int(H); td.resid = x1.as<__nv_bfloat16>(); td.gate = gate;
+    const TcWeights wdn{{wd.as<uint8_t>(), wd.as<uint8_t>()}, {uint64_t(H), uint64_t(H)}};
+    return tc_launch<TC_EPI_SHARED_DOWN>(wdn, q2, td, int(T), int(H / 128), 1, c.stream);
+  }
   const int nt = pick_nt(T);
   SkinnyArgs a{};
   a.status = device_status_ptr();

@@ -101,6 +101,51 @@ TcQuant tc_quant_carve(uint8_t* base, int64_t R, int64_t K) {
 }
 
 // ---------------------------------------------------------------------------------------------------------------
+// compacted list of the groups that have rows, in group order (one CTA; groups <= a few thousand)
+__global__ void __launch_bounds__(1024) tc_active_kernel(const int* __restrict__ g_n, int G, int* __restrict__ active,
+                                                         int* __restrict__ n_active) {
+  __shared__ int s_warp[32];
+  __shared__ int s_base;
+  const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+  if (tid == 0) s_base = 0;
+  __syncthreads();
+  for (int g0 = 0; g0 < G; g0 += 1024) {
+    const int g = g0 + tid;
+    const bool on = g < G && g_n[g] > 0;
+    const unsigned m = __ballot_sync(0xffffffffu, on);
+    if (lane == 0) s_warp[wid] = __popc(m);
+    __syncthreads();
+    int before = s_base;
+    for (int w = 0; w < wid; ++w) before += s_warp[w];
+    if (on) active[before + __popc(m & ((1u << lane) - 1))] = g;
+    __syncthreads();
+    if (tid == 0) {
+      int tot = 0;
+      for (int w = 0; w < 32; ++w) tot += s_warp[w];
+      s_base += tot;
+    }
+    __syncthreads();
+  }
+  if (tid == 0) n_active[0] = s_base;
+}
+
+int tc_build_active(const int* g_n, int groups, int* active, cudaStream_t stream) {
+  tc_active_kernel<<<1, 1024, 0, stream>>>(g_n, groups, active + 1, active);
+  Q35_CUDA_LAUNCH_CHECK("tc active groups");
+  return 0;
+}
+
+static int tc_sm_count() {
+  static int n = 0;
+  if (!n) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (n <= 0) n = 148;
+  }
+  return n;
+}
+
 template <int NB, int EPI>
 static int launch_nb(const CUtensorMap& w0, const CUtensorMap& w1, const CUtensorMap& xh, const CUtensorMap& xl,
                      const TcArgs& a, int tiles, int groups, cudaStream_t stream) {
@@ -110,8 +155,9 @@ static int launch_nb(const CUtensorMap& w0, const CUtensorMap& w1, const CUtenso
     cudaFuncSetAttribute(tc_gemm_kernel<NB, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     attr_smem = smem;
   }
-  const dim3 grid{unsigned(tiles), unsigned(groups), 1u};
-  tc_gemm_kernel<NB, EPI><<<grid, 192, smem, stream>>>(w0, w1, xh, xl, a);
+  const long long items = (long long)tiles * groups;
+  const unsigned grid = unsigned(items < tc_sm_count() ? items : tc_sm_count());
+  tc_gemm_kernel<NB, EPI><<<grid, 256, smem, stream>>>(w0, w1, xh, xl, a);
   Q35_CUDA_LAUNCH_CHECK("tc gemm");
   return 0;
 }
@@ -126,6 +172,9 @@ int tc_launch(const TcWeights& w, const TcQuant& q, TcArgs a, int nb, int tiles,
   Q35_TRY(make_map(&xh, false, q.qh, q.R, a.K, a.K, nb, "activations"));
   Q35_TRY(make_map(&xl, false, q.ql, q.R, a.K, a.K, nb, "activations"));
   a.sfh = q.sh; a.sfl = q.sl; a.total_rows = q.R;
+  a.n_tiles = tiles;
+  Q35_REQUIRE(a.g_n == nullptr || (a.active != nullptr && a.n_active != nullptr), Q35_ERR_WORKSPACE,
+              "tc gemm: grouped launch without an active-group list");
   a.status = device_status_ptr();
   if (nb == 16) return launch_nb<16, EPI>(w0, w1, xh, xl, a, tiles, groups, stream);
   if (nb == 32) return launch_nb<32, EPI>(w0, w1, xh, xl, a, tiles, groups, stream);

@@ -7,9 +7,14 @@
 // Why two terms: the reference multiplies bf16 activations by the dequantised weights (golden
 // models/qwen35_2b/whole/src/q35_moe.py:235-238); a single E4M3 term misses the 2e-2 tolerance by a factor 6.
 //
-// Work item = (group, 128-row weight tile, NB-token tile).  One CTA of 192 threads per (group, row tile): warp 0
-// issues TMA, warp 1 owns tensor memory and issues the MMAs, warps 2-5 gather scale factors and run the epilogue.
-// 4-stage mbarrier ring, K = 128 per stage (4 MMAs of K = 32), accumulators [128 lanes x 2 NB columns] in TMEM.
+// Work item = (group, 128-row weight tile, NB-token tile).  Persistent kernel, one CTA of 256 threads per SM, items
+// dealt round-robin over the compacted list of non-empty groups.  Warp-specialised and fully decoupled:
+//   warp 0    TMA producer: weight and activation tiles into a ring of stages (K = 128 per stage), running ahead
+//             across item boundaries;
+//   warp 1    owns tensor memory, copies the stage's scale blocks into TMEM (tcgen05.cp) and issues 4 MMAs of K = 32;
+//   warps 2-5 epilogue: tcgen05.ld of a finished accumulator while the next item accumulates into the other buffer;
+//   warps 6-7 gather the E8M0 scales of the NEXT item from global memory into the 32 x 16-byte blocks tcgen05.cp wants.
+// Accumulators [128 lanes x 2 NB columns] and the scale blocks are double-buffered; every hand-over is an mbarrier.
 #pragma once
 #include "tc_ptx.cuh"
 
@@ -35,12 +40,13 @@ struct TcArgs {
   __nv_bfloat16* act_out;
   float* f_out; __nv_bfloat16* b_out; int out_stride;
   const float* rw_row; const __nv_bfloat16* resid; const float* gate; const float* bias;
+  const int* active; const int* n_active;  // compacted list of groups with rows (nullptr: dense)
+  int n_tiles;              // row tiles per group
   int* status;
 };
 
 template <int NB>
 struct TcCfg {
-  static constexpr int STAGES = 4;
   static constexpr int N = 2 * NB;                         // MMA N: hi columns then lo columns
   static constexpr int A_BYTES = 128 * 128;                // 128 rows x 128 unpacked FP4 bytes
   static constexpr int B_BYTES = N * 128;
@@ -48,55 +54,71 @@ struct TcCfg {
   // bytes the TMA unit reports per stage: the FP4 loads count their PACKED source bytes (128 rows x 64 B), measured on
   // B200: with the unpacked size the barrier never completes
   static constexpr int STAGE_TX = 128 * 64 + B_BYTES;
-  static constexpr int TMEM_COLS = (N + 8) <= 32 ? 32 : (N + 8) <= 64 ? 64 : (N + 8) <= 128 ? 128 : 256;
-  static constexpr int SFA_COL = N, SFB_COL = N + 4;
+  static constexpr int STAGES = NB <= 16 ? 7 : NB <= 32 ? 6 : 5;
+  static constexpr int TMEM_COLS = (2 * N + 8) <= 128 ? 128 : (2 * N + 8) <= 256 ? 256 : 512;
+  static constexpr int SFA_COL = 2 * N, SFB_COL = 2 * N + 4;
+  static constexpr int XCH_BYTES = 16 * 64 * 4;            // gate/up exchange of one 16-column chunk
   static constexpr int smem_bytes(int K) {                 // + 1024 for manual alignment
-    return 1024 + STAGES * STAGE_BYTES + (K / 128) * 1024 + 256;
+    return 1024 + STAGES * STAGE_BYTES + 2 * (K / 128) * 1024 + XCH_BYTES + 256;
   }
 };
 
+// sub-item iteration shared by all roles: (active group, row tile) pairs dealt round-robin to the CTAs, and inside
+// a pair the token tiles of NB rows
+struct TcItem {
+  int plane, row0, n, tile;
+};
+
+__device__ __forceinline__ bool tc_get_item(const TcArgs& a, int j, TcItem* it) {
+  if (a.g_n) {
+    const int grp = a.active[j / a.n_tiles];
+    it->n = a.g_n[grp]; it->plane = a.g_expert[grp]; it->row0 = a.g_row0[grp];
+    if (it->plane < 0 || it->plane >= a.n_planes) {
+      atomicOr(a.status, DS_BAD_EXPERT);
+      it->n = 0;
+    }
+  } else {
+    it->n = a.n_dense; it->plane = 0; it->row0 = 0;
+  }
+  it->tile = j % a.n_tiles;
+  return it->n > 0;
+}
+
 template <int NB, int EPI>
-__global__ void __launch_bounds__(192) tc_gemm_kernel(const __grid_constant__ CUtensorMap wmap0,
-                                                      const __grid_constant__ CUtensorMap wmap1,
-                                                      const __grid_constant__ CUtensorMap xmap_hi,
-                                                      const __grid_constant__ CUtensorMap xmap_lo, const TcArgs a) {
+__global__ void __launch_bounds__(256, 1) tc_gemm_kernel(const __grid_constant__ CUtensorMap wmap0,
+                                                         const __grid_constant__ CUtensorMap wmap1,
+                                                         const __grid_constant__ CUtensorMap xmap_hi,
+                                                         const __grid_constant__ CUtensorMap xmap_lo, const TcArgs a) {
   using C = TcCfg<NB>;
   using namespace tc;
   extern __shared__ uint8_t smem_raw[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int grp = blockIdx.y, tile = blockIdx.x;
-  int n, plane, row0;
-  if (a.g_n) {
-    n = a.g_n[grp]; plane = a.g_expert[grp]; row0 = a.g_row0[grp];
-    if (plane < 0 || plane >= a.n_planes) {
-      if (tid == 0 && n > 0) atomicOr(a.status, DS_BAD_EXPERT);
-      n = 0;
-    }
-  } else {
-    n = a.n_dense; plane = 0; row0 = 0;
-  }
-  if (n <= 0) return;
+  const int n_items = (a.g_n ? a.n_active[0] : 1) * a.n_tiles;
+  if (int(blockIdx.x) >= n_items) return;
 
   const int KS = a.K / 128;
   const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* sgen = smem_raw + (sbase - smem_u32(smem_raw));
   const uint32_t s_stage = sbase;
-  const uint32_t s_atomA = sbase + C::STAGES * C::STAGE_BYTES;
-  const uint32_t s_atomB = s_atomA + KS * 512;
-  const uint32_t s_bar = s_atomB + KS * 512;                  // full[4], empty[4], tmem_full
-  uint32_t* g_atomA = reinterpret_cast<uint32_t*>(sgen + C::STAGES * C::STAGE_BYTES);
-  uint32_t* g_atomB = g_atomA + KS * 128;
-  volatile uint32_t* g_slot = reinterpret_cast<volatile uint32_t*>(sgen + C::STAGES * C::STAGE_BYTES + KS * 1024 + 128);
-  const uint32_t s_slot = s_bar + 128;
-  auto full_bar = [&](int s) { return s_bar + 8 * s; };
-  auto empty_bar = [&](int s) { return s_bar + 32 + 8 * s; };
-  const uint32_t tfull_bar = s_bar + 64;
-
-  const int rowh[2] = {tile * a.tile_rows + a.roff[0], tile * a.tile_rows + a.roff[1]};
+  const uint32_t s_atoms = sbase + C::STAGES * C::STAGE_BYTES;     // [2 buffers][A: KS x 512 | B: KS x 512]
+  const uint32_t s_xch = s_atoms + 2 * KS * 1024;
+  const uint32_t s_bar = s_xch + C::XCH_BYTES;
+  uint8_t* g_atoms = sgen + C::STAGES * C::STAGE_BYTES;
+  float* g_xch = reinterpret_cast<float*>(g_atoms + 2 * KS * 1024);
+  volatile uint32_t* g_slot = reinterpret_cast<volatile uint32_t*>(g_atoms + 2 * KS * 1024 + C::XCH_BYTES + 192);
+  const uint32_t s_slot = s_bar + 192;
+  auto full_bar = [&](int s) { return s_bar + 8 * s; };            // [0, 64): up to 8 stages
+  auto empty_bar = [&](int s) { return s_bar + 64 + 8 * s; };      // [64, 128)
+  auto sf_full = [&](int b) { return s_bar + 128 + 8 * b; };
+  auto sf_empty = [&](int b) { return s_bar + 144 + 8 * b; };
+  auto acc_full = [&](int b) { return s_bar + 160 + 8 * b; };
+  auto acc_empty = [&](int b) { return s_bar + 176 + 8 * b; };
 
   if (tid == 0) {
     for (int s = 0; s < C::STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-    mbar_init(tfull_bar, 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(sf_full(b), 1); mbar_init(sf_empty(b), 1); mbar_init(acc_full(b), 1); mbar_init(acc_empty(b), 1);
+    }
     fence_barrier_init();
     tma_prefetch_desc(&wmap0); tma_prefetch_desc(&wmap1); tma_prefetch_desc(&xmap_hi); tma_prefetch_desc(&xmap_lo);
   }
@@ -106,145 +128,195 @@ __global__ void __launch_bounds__(192) tc_gemm_kernel(const __grid_constant__ CU
   tc_fence_after();
   const uint32_t tmem = *g_slot;
 
-  // weight scale atoms: word (row r = r0 + 32 r1, stage ks) -> atomA[ks][r0 * 4 + r1], the 32 x 16-byte block that
-  // tcgen05.cp replicates over the four lane quadrants
-  {
-    const int chunks = a.K / 32 / 16;  // 16-byte chunks per scale row (16 k-blocks = 4 stages each)
-    for (int idx = tid; idx < 128 * chunks; idx += 192) {
-      const int r = idx / chunks, ch = idx % chunks;
-      const int h = r >> 6;
-      const int row = rowh[h] + (r & 63);
-      uint4 v = make_uint4(0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu);
-      if (row < a.lim[h])
-        v = *reinterpret_cast<const uint4*>(a.sw[h] + (long long)plane * a.s_plane + (long long)row * (a.K / 32) + ch * 16);
-      const int w = (r & 31) * 4 + (r >> 5);
-      g_atomA[(ch * 4 + 0) * 128 + w] = v.x; g_atomA[(ch * 4 + 1) * 128 + w] = v.y;
-      g_atomA[(ch * 4 + 2) * 128 + w] = v.z; g_atomA[(ch * 4 + 3) * 128 + w] = v.w;
-    }
-  }
-
-  uint32_t it = 0;  // k-stages issued so far (ring position), identical in every role
-  int item = 0;
-  for (int t0 = 0; t0 < n; t0 += NB, ++item) {
-    // activation scale atoms of this token tile: columns [0, NB) = hi term, [NB, 2 NB) = lo term
-    {
-      const int chunks = a.K / 32 / 16;
-      for (int idx = tid; idx < C::N * chunks; idx += 192) {
-        const int col = idx / chunks, ch = idx % chunks;
-        const int t = t0 + (col < NB ? col : col - NB);
-        const int row = row0 + t;
-        uint4 v = make_uint4(0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu);
-        if (t < n && row < a.total_rows)
-          v = *reinterpret_cast<const uint4*>((col < NB ? a.sfh : a.sfl) + (long long)row * (a.K / 32) + ch * 16);
-        const int w = (col & 31) * 4 + (col >> 5);
-        g_atomB[(ch * 4 + 0) * 128 + w] = v.x; g_atomB[(ch * 4 + 1) * 128 + w] = v.y;
-        g_atomB[(ch * 4 + 2) * 128 + w] = v.z; g_atomB[(ch * 4 + 3) * 128 + w] = v.w;
-      }
-    }
-    fence_proxy_async();
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-
-    if (warp == 0) {
-      if (elect_one()) {
-        for (int ks = 0; ks < KS; ++ks) {
-          const uint32_t s = (it + ks) % C::STAGES, ph = ((it + ks) / C::STAGES) & 1;
-          if (!mbar_wait(empty_bar(s), ph ^ 1)) { atomicOr(a.status, DS_WAIT_TIMEOUT | 0x10); break; }
-          mbar_expect_tx(full_bar(s), C::STAGE_TX);
-          const uint32_t sa = s_stage + s * C::STAGE_BYTES, sb = sa + C::A_BYTES;
-          tma_load_2d(sa, &wmap0, full_bar(s), ks * 128, plane * a.plane_rows[0] + rowh[0]);
-          tma_load_2d(sa + 8192, &wmap1, full_bar(s), ks * 128, plane * a.plane_rows[1] + rowh[1]);
-          tma_load_2d(sb, &xmap_hi, full_bar(s), ks * 128, row0 + t0);
-          tma_load_2d(sb + NB * 128, &xmap_lo, full_bar(s), ks * 128, row0 + t0);
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer
+    if (elect_one()) {
+      uint32_t it = 0;
+      bool dead = false;
+      for (int j = blockIdx.x; j < n_items && !dead; j += gridDim.x) {
+        TcItem im;
+        if (!tc_get_item(a, j, &im)) continue;
+        const int r0 = im.tile * a.tile_rows + a.roff[0], r1 = im.tile * a.tile_rows + a.roff[1];
+        for (int t0 = 0; t0 < im.n && !dead; t0 += NB) {
+          for (int ks = 0; ks < KS; ++ks, ++it) {
+            const uint32_t s = it % C::STAGES, ph = (it / C::STAGES) & 1;
+            if (!mbar_wait(empty_bar(s), ph ^ 1)) { atomicOr(a.status, DS_WAIT_TIMEOUT | 0x10); dead = true; break; }
+            mbar_expect_tx(full_bar(s), C::STAGE_TX);
+            const uint32_t sa = s_stage + s * C::STAGE_BYTES, sb = sa + C::A_BYTES;
+            tma_load_2d(sa, &wmap0, full_bar(s), ks * 128, im.plane * a.plane_rows[0] + r0);
+            tma_load_2d(sa + 8192, &wmap1, full_bar(s), ks * 128, im.plane * a.plane_rows[1] + r1);
+            tma_load_2d(sb, &xmap_hi, full_bar(s), ks * 128, im.row0 + t0);
+            tma_load_2d(sb + NB * 128, &xmap_lo, full_bar(s), ks * 128, im.row0 + t0);
+          }
         }
       }
-      __syncwarp();
-    } else if (warp == 1) {
-      if (elect_one()) {
-        bool ok = true;
-        for (int ks = 0; ks < KS && ok; ++ks) {
-          const uint32_t s = (it + ks) % C::STAGES, ph = ((it + ks) / C::STAGES) & 1;
-          if (!mbar_wait(full_bar(s), ph)) { atomicOr(a.status, DS_WAIT_TIMEOUT | 0x20 | (ks << 8)); ok = false; break; }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer
+    if (elect_one()) {
+      uint32_t it = 0, q = 0;
+      bool dead = false;
+      for (int j = blockIdx.x; j < n_items && !dead; j += gridDim.x) {
+        TcItem im;
+        if (!tc_get_item(a, j, &im)) continue;
+        for (int t0 = 0; t0 < im.n && !dead; t0 += NB, ++q) {
+          const uint32_t b = q & 1, bph = (q >> 1) & 1;
+          if (!mbar_wait(sf_full(b), bph) || !mbar_wait(acc_empty(b), bph ^ 1)) {
+            atomicOr(a.status, DS_WAIT_TIMEOUT | 0x20);
+            dead = true;
+            break;
+          }
           tc_fence_after();
-          tc_cp_32x128b_warpx4(tmem + C::SFA_COL, smem_desc(s_atomA + ks * 512, 0, 128, 0));
-          tc_cp_32x128b_warpx4(tmem + C::SFB_COL, smem_desc(s_atomB + ks * 512, 0, 128, 0));
-          const uint32_t sa = s_stage + s * C::STAGE_BYTES, sb = sa + C::A_BYTES;
+          const uint32_t acc = tmem + b * C::N;
+          const uint32_t atomA = s_atoms + b * KS * 1024, atomB = atomA + KS * 512;
+          for (int ks = 0; ks < KS; ++ks, ++it) {
+            const uint32_t s = it % C::STAGES, ph = (it / C::STAGES) & 1;
+            if (!mbar_wait(full_bar(s), ph)) { atomicOr(a.status, DS_WAIT_TIMEOUT | 0x40); dead = true; break; }
+            tc_fence_after();
+            tc_cp_32x128b_warpx4(tmem + C::SFA_COL, smem_desc(atomA + ks * 512, 0, 128, 0));
+            tc_cp_32x128b_warpx4(tmem + C::SFB_COL, smem_desc(atomB + ks * 512, 0, 128, 0));
+            const uint32_t sa = s_stage + s * C::STAGE_BYTES, sb = sa + C::A_BYTES;
 #pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            tc_mma_mxf8f6f4(tmem, smem_desc(sa + k * 32, 16, 1024, 2), smem_desc(sb + k * 32, 16, 1024, 2),
-                            idesc_mxf8f6f4(FMT_E2M1, FMT_E4M3, 128, C::N, k, k), tmem + C::SFA_COL,
-                            tmem + C::SFB_COL, (ks | k) != 0);
+            for (int k = 0; k < 4; ++k) {
+              tc_mma_mxf8f6f4(acc, smem_desc(sa + k * 32, 16, 1024, 2), smem_desc(sb + k * 32, 16, 1024, 2),
+                              idesc_mxf8f6f4(FMT_E2M1, FMT_E4M3, 128, C::N, k, k), tmem + C::SFA_COL,
+                              tmem + C::SFB_COL, (ks | k) != 0);
+            }
+            tc_commit(empty_bar(s));
           }
-          tc_commit(empty_bar(s));
+          tc_commit(sf_empty(b));
+          tc_commit(acc_full(b));  // also after a failed wait: the epilogue must not be left waiting
         }
-        tc_commit(tfull_bar);  // also on failure: the epilogue's wait must not be left hanging
       }
-      __syncwarp();
-    } else {
-      // epilogue warps 2..5 own lane quadrants (warp % 4): rows 32 q .. 32 q + 31 of the tile
-      const int q = warp & 3;
-      const bool ok = mbar_wait(tfull_bar, item & 1);
-      if (!ok && lane == 0) atomicOr(a.status, DS_WAIT_TIMEOUT | 0x40);
-      tc_fence_after();
-      const int r = q * 32 + lane;        // row of the 128-row tile
-      const int h = r >> 6;
-      const int row = rowh[h] + (r & 63);
+    }
+    __syncwarp();
+  } else if (warp >= 6) {
+    // ---------------------------------------------------------------- scale gather (64 threads)
+    const int gt = tid - 192;
+    const int chunks = a.K / 32 / 16;  // 16-byte chunks per scale row: 16 k-blocks = 4 stages each
+    uint32_t q = 0;
+    bool dead = false;
+    for (int j = blockIdx.x; j < n_items; j += gridDim.x) {
+      TcItem im;
+      if (!tc_get_item(a, j, &im)) continue;
+      const int rowh[2] = {im.tile * a.tile_rows + a.roff[0], im.tile * a.tile_rows + a.roff[1]};
+      for (int t0 = 0; t0 < im.n; t0 += NB, ++q) {
+        const uint32_t b = q & 1, bph = (q >> 1) & 1;
+        if (!dead && !mbar_wait(sf_empty(b), bph ^ 1)) {
+          if (gt == 0) atomicOr(a.status, DS_WAIT_TIMEOUT | 0x80);
+          dead = true;
+        }
+        uint32_t* atomA = reinterpret_cast<uint32_t*>(g_atoms + b * KS * 1024);
+        uint32_t* atomB = atomA + KS * 128;
+        // word (row r = r0 + 32 r1, stage ks) -> atom[ks][r0 * 4 + r1]: the 32 x 16-byte block that tcgen05.cp
+        // replicates over the four lane quadrants
+        for (int idx = gt; idx < 128 * chunks; idx += 64) {
+          const int r = idx / chunks, ch = idx % chunks;
+          const int h = r >> 6;
+          const int row = rowh[h] + (r & 63);
+          uint4 v = make_uint4(0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu);
+          if (row < a.lim[h])
+            v = *reinterpret_cast<const uint4*>(a.sw[h] + (long long)im.plane * a.s_plane +
+                                                (long long)row * (a.K / 32) + ch * 16);
+          const int w = (r & 31) * 4 + (r >> 5);
+          atomA[(ch * 4 + 0) * 128 + w] = v.x; atomA[(ch * 4 + 1) * 128 + w] = v.y;
+          atomA[(ch * 4 + 2) * 128 + w] = v.z; atomA[(ch * 4 + 3) * 128 + w] = v.w;
+        }
+        // activation scales: columns [0, NB) = hi term, [NB, 2 NB) = lo term
+        for (int idx = gt; idx < C::N * chunks; idx += 64) {
+          const int col = idx / chunks, ch = idx % chunks;
+          const int t = t0 + (col < NB ? col : col - NB);
+          const int row = im.row0 + t;
+          uint4 v = make_uint4(0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu);
+          if (t < im.n && row < a.total_rows)
+            v = *reinterpret_cast<const uint4*>((col < NB ? a.sfh : a.sfl) + (long long)row * (a.K / 32) + ch * 16);
+          const int w = (col & 31) * 4 + (col >> 5);
+          atomB[(ch * 4 + 0) * 128 + w] = v.x; atomB[(ch * 4 + 1) * 128 + w] = v.y;
+          atomB[(ch * 4 + 2) * 128 + w] = v.z; atomB[(ch * 4 + 3) * 128 + w] = v.w;
+        }
+        fence_proxy_async();
+        asm volatile("bar.sync 2, 64;" ::: "memory");
+        if (gt == 0) mbar_arrive(sf_full(b));
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue: warps 2..5 own lane quadrant warp % 4
+    const int qd = warp & 3;
+    const int r = qd * 32 + lane;  // row of the 128-row tile
+    const int h = r >> 6;
+    uint32_t q = 0;
+    bool dead = false;
+    for (int j = blockIdx.x; j < n_items; j += gridDim.x) {
+      TcItem im;
+      if (!tc_get_item(a, j, &im)) continue;
+      const int row = im.tile * a.tile_rows + a.roff[h] + (r & 63);
       const bool rvalid = row < a.lim[h];
-      float* xch = reinterpret_cast<float*>(sgen);  // stage memory is free once the accumulator is complete
-      for (int c0 = 0; c0 < NB; c0 += 16) {  // runs even after a timed-out wait: the named barriers below must pair up
-        float hi[16], lo[16];
-        tmem_ld_x16(tmem + (uint32_t(q * 32) << 16) + c0, hi);
-        tmem_ld_x16(tmem + (uint32_t(q * 32) << 16) + NB + c0, lo);
+      for (int t0 = 0; t0 < im.n; t0 += NB, ++q) {
+        const uint32_t b = q & 1, bph = (q >> 1) & 1;
+        if (!dead && !mbar_wait(acc_full(b), bph)) {
+          if (lane == 0) atomicOr(a.status, DS_WAIT_TIMEOUT | 0x100);
+          dead = true;  // keep walking the loops so that the named barriers below still pair up
+        }
+        tc_fence_after();
+        const uint32_t acc = tmem + b * C::N + (uint32_t(qd * 32) << 16);
+        for (int c0 = 0; c0 < NB; c0 += 16) {
+          float hi[16], lo[16];
+          tmem_ld_x16(acc + c0, hi);
+          tmem_ld_x16(acc + NB + c0, lo);
 #pragma unroll
-        for (int j = 0; j < 16; ++j) hi[j] += lo[j];
-        if constexpr (EPI == TC_EPI_SILU_MUL) {
-          // rows 64..127 (up) hand their values to rows 0..63 (gate) through shared memory
-          if (h == 1) {
+          for (int jj = 0; jj < 16; ++jj) hi[jj] += lo[jj];
+          if constexpr (EPI == TC_EPI_SILU_MUL) {
+            // rows 64..127 (up) hand their values to rows 0..63 (gate) through shared memory
+            if (h == 1) {
 #pragma unroll
-            for (int j = 0; j < 16; ++j) xch[(c0 + j) * 64 + (r & 63)] = hi[j];
-          }
-          asm volatile("bar.sync 1, 128;" ::: "memory");
-          if (h == 0) {
+              for (int jj = 0; jj < 16; ++jj) g_xch[jj * 64 + (r & 63)] = hi[jj];
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (h == 0) {
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              const int t = t0 + c0 + j;
-              if (t < n && rvalid) {
-                const float g = round_bf16(hi[j]), u = round_bf16(xch[(c0 + j) * 64 + r]);
-                a.act_out[(long long)(row0 + t) * a.act_rows + row] = __float2bfloat16_rn(g / (1.0f + expf(-g)) * u);
+              for (int jj = 0; jj < 16; ++jj) {
+                const int t = t0 + c0 + jj;
+                if (t < im.n && rvalid) {
+                  const float g = round_bf16(hi[jj]), u = round_bf16(g_xch[jj * 64 + r]);
+                  a.act_out[(long long)(im.row0 + t) * a.act_rows + row] =
+                      __float2bfloat16_rn(g / (1.0f + expf(-g)) * u);
+                }
+              }
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+          } else {
+#pragma unroll
+            for (int jj = 0; jj < 16; ++jj) {
+              const int t = t0 + c0 + jj;
+              if (t >= im.n || !rvalid) continue;
+              const long long dst = im.row0 + t;
+              float v = hi[jj];
+              if constexpr (EPI == TC_EPI_ROW_SCALE) {
+                v *= a.rw_row[dst];
+                if (a.f_out) a.f_out[dst * a.out_stride + row] = v;
+                else a.b_out[dst * a.out_stride + row] = __float2bfloat16_rn(v);
+              } else if constexpr (EPI == TC_EPI_SHARED_DOWN) {
+                const float sig = 1.0f / (1.0f + expf(-a.gate[dst]));
+                const float res = __bfloat162float(a.resid[dst * a.out_stride + row]);
+                a.b_out[dst * a.out_stride + row] = __float2bfloat16_rn(res + v * sig);
+              } else {
+                if (a.bias) v += a.bias[row];
+                if (a.f_out) a.f_out[dst * a.out_stride + row] = v;
+                else a.b_out[dst * a.out_stride + row] = __float2bfloat16_rn(v);
               }
             }
           }
-          asm volatile("bar.sync 1, 128;" ::: "memory");
-        } else {
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const int t = t0 + c0 + j;
-            if (t >= n || !rvalid) continue;
-            const long long dst = row0 + t;
-            float v = hi[j];
-            if constexpr (EPI == TC_EPI_ROW_SCALE) {
-              v *= a.rw_row[dst];
-              if (a.f_out) a.f_out[dst * a.out_stride + row] = v;
-              else a.b_out[dst * a.out_stride + row] = __float2bfloat16_rn(v);
-            } else if constexpr (EPI == TC_EPI_SHARED_DOWN) {
-              const float sig = 1.0f / (1.0f + expf(-a.gate[dst]));
-              const float res = __bfloat162float(a.resid[dst * a.out_stride + row]);
-              a.b_out[dst * a.out_stride + row] = __float2bfloat16_rn(res + v * sig);
-            } else {
-              if (a.bias) v += a.bias[row];
-              if (a.f_out) a.f_out[dst * a.out_stride + row] = v;
-              else a.b_out[dst * a.out_stride + row] = __float2bfloat16_rn(v);
-            }
-          }
         }
+        tc_fence_before();
+        asm volatile("bar.sync 3, 128;" ::: "memory");
+        if (tid == 64) mbar_arrive(acc_empty(b));  // first epilogue thread: the accumulator buffer may be overwritten
       }
     }
-    it += KS;
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
   }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
   if (warp == 1) tmem_dealloc(tmem, C::TMEM_COLS);
 }
 

@@ -24,6 +24,9 @@ TcQuant tc_quant_carve(uint8_t* base, int64_t R, int64_t K);
 int tc_quantize(const __nv_bfloat16* x, int x_stride, const int* src, int R, int K, const TcQuant& q,
                 cudaStream_t stream);
 
+// active[0] = number of groups with rows, active[1 ..] = their indices; `active` holds groups + 1 ints
+int tc_build_active(const int* g_n, int groups, int* active, cudaStream_t stream);
+
 template <int EPI>
 int tc_launch(const TcWeights& w, const TcQuant& q, TcArgs a, int nb, int tiles, int groups, cudaStream_t stream);
 

@@ -211,8 +211,8 @@ def _attn_check(q35, ctxs, P=64, HKV=2, HQ=16, D=256, fp8=False, per_head=True, 
         if cx == 0:
             assert (out[b] == 0).all()
     nz = [b for b, cx in enumerate(ctxs) if cx > 0]
-    if nz:
-        assert rel_rms_err(out.cpu()[nz], ref[nz]) <= TOL
+    if nz:  # one bf16 rounding step allowed: the split of the keys over CTAs follows the SM count of the device
+        assert_parity(out.cpu()[nz], ref[nz])
     return out
 
 
@@ -250,7 +250,8 @@ def test_paged_decode_poisoned_tail_rows_do_not_leak(q35):
         page = int(indices[int(indptr[b + 1]) - 1])
         poisoned[page, :, int(last[b]):] = float("nan")
     out = q35.paged_attention_decode(q.cuda(), poisoned.cuda(), indptr.cuda(), indices.cuda(), last.cuda())
-    assert rel_rms_err(out.cpu(), ref) <= TOL
+    assert torch.isfinite(out).all()
+    assert_parity(out.cpu(), ref)
 
 
 def test_paged_decode_current_token_and_cache_write(q35):
