@@ -101,6 +101,7 @@ def workspace_bytes(role, **tensors):
 
 
 _ws_cache = {}
+_need_cache = {}
 
 
 def _workspace(device, nbytes):
@@ -122,7 +123,11 @@ def run(role, stream=None, **tensors):
             raise ValueError("all tensors must live on the GPU (the library has no CPU path)")
         dev = t.device
     if "workspace" not in tensors:
-        need = workspace_bytes(role, **tensors)
+        # the scratch size depends on shapes and dtypes only: ask the library once per signature
+        sig = (role, tuple((n, t.dtype, tuple(t.shape)) for n, t in tensors.items()))
+        need = _need_cache.get(sig)
+        if need is None:
+            need = _need_cache[sig] = workspace_bytes(role, **tensors)
         if need:
             tensors = dict(tensors, workspace=_workspace(dev, need))
     arr, _keep = _table(tensors)

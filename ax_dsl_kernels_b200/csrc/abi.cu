@@ -75,9 +75,9 @@ int Call::workspace(int64_t need, Tensor* ws) {
 
 __device__ int g_device_status;
 
-int* device_status_ptr() {
-  int* p = nullptr;
-  cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_device_status);
+int* device_status_ptr() {  // one process drives one GPU: looked up once
+  static int* p = nullptr;
+  if (!p) cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_device_status);
   return p;
 }
 

@@ -156,7 +156,8 @@ static int launch_nb(const CUtensorMap& w0, const CUtensorMap& w1, const CUtenso
     attr_smem = smem;
   }
   const long long items = (long long)tiles * groups;
-  const unsigned grid = unsigned(items < tc_sm_count() ? items : tc_sm_count());
+  const long long slots = (long long)tc_sm_count() * TcCfg<NB>::CTAS_PER_SM;
+  const unsigned grid = unsigned(items < slots ? items : slots);
   tc_gemm_kernel<NB, EPI><<<grid, 256, smem, stream>>>(w0, w1, xh, xl, a);
   Q35_CUDA_LAUNCH_CHECK("tc gemm");
   return 0;

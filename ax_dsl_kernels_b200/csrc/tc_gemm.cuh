@@ -54,7 +54,10 @@ struct TcCfg {
   // bytes the TMA unit reports per stage: the FP4 loads count their PACKED source bytes (128 rows x 64 B), measured on
   // B200: with the unpacked size the barrier never completes
   static constexpr int STAGE_TX = 128 * 64 + B_BYTES;
-  static constexpr int STAGES = NB <= 16 ? 7 : NB <= 32 ? 6 : 5;
+  // small token tiles: two CTAs per SM with short rings (the per-stage hand-over costs ~250 ns of a single issuing
+  // thread whatever the tile size, so two independent rings are needed to keep up with the SM's share of HBM)
+  static constexpr int CTAS_PER_SM = NB <= 32 ? 2 : 1;
+  static constexpr int STAGES = NB <= 32 ? 3 : 5;
   static constexpr int TMEM_COLS = (2 * N + 8) <= 128 ? 128 : (2 * N + 8) <= 256 ? 256 : 512;
   static constexpr int SFA_COL = 2 * N, SFB_COL = 2 * N + 4;
   static constexpr int XCH_BYTES = 16 * 64 * 4;            // gate/up exchange of one 16-column chunk
@@ -85,7 +88,7 @@ __device__ __forceinline__ bool tc_get_item(const TcArgs& a, int j, TcItem* it) 
 }
 
 template <int NB, int EPI>
-__global__ void __launch_bounds__(256, 1) tc_gemm_kernel(const __grid_constant__ CUtensorMap wmap0,
+__global__ void __launch_bounds__(256, TcCfg<NB>::CTAS_PER_SM) tc_gemm_kernel(const __grid_constant__ CUtensorMap wmap0,
                                                          const __grid_constant__ CUtensorMap wmap1,
                                                          const __grid_constant__ CUtensorMap xmap_hi,
                                                          const __grid_constant__ CUtensorMap xmap_lo, const TcArgs a) {
@@ -210,30 +213,53 @@ __global__ void __launch_bounds__(256, 1) tc_gemm_kernel(const __grid_constant__
         uint32_t* atomA = reinterpret_cast<uint32_t*>(g_atoms + b * KS * 1024);
         uint32_t* atomB = atomA + KS * 128;
         // word (row r = r0 + 32 r1, stage ks) -> atom[ks][r0 * 4 + r1]: the 32 x 16-byte block that tcgen05.cp
-        // replicates over the four lane quadrants
-        for (int idx = gt; idx < 128 * chunks; idx += 64) {
-          const int r = idx / chunks, ch = idx % chunks;
-          const int h = r >> 6;
-          const int row = rowh[h] + (r & 63);
-          uint4 v = make_uint4(0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu);
-          if (row < a.lim[h])
-            v = *reinterpret_cast<const uint4*>(a.sw[h] + (long long)im.plane * a.s_plane +
-                                                (long long)row * (a.K / 32) + ch * 16);
-          const int w = (r & 31) * 4 + (r >> 5);
-          atomA[(ch * 4 + 0) * 128 + w] = v.x; atomA[(ch * 4 + 1) * 128 + w] = v.y;
-          atomA[(ch * 4 + 2) * 128 + w] = v.z; atomA[(ch * 4 + 3) * 128 + w] = v.w;
+        // replicates over the four lane quadrants.  Loads are issued in batches of 8 per thread before any store, so
+        // one round trip to L2 / HBM covers the whole gather.
+        const uint4 ones = make_uint4(0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu);
+        for (int base = 0; base < 128 * chunks; base += 64 * 8) {
+          uint4 v[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            const int idx = base + u * 64 + gt;
+            const int r = idx / chunks, ch = idx % chunks;
+            const int hh = (r >> 6) & 1;
+            const int row = rowh[hh] + (r & 63);
+            v[u] = ones;
+            if (idx < 128 * chunks && row < a.lim[hh])
+              v[u] = ldg_nc_16(a.sw[hh] + (long long)im.plane * a.s_plane + (long long)row * (a.K / 32) + ch * 16);
+          }
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            const int idx = base + u * 64 + gt;
+            if (idx >= 128 * chunks) continue;
+            const int r = idx / chunks, ch = idx % chunks;
+            const int w = (r & 31) * 4 + (r >> 5);
+            atomA[(ch * 4 + 0) * 128 + w] = v[u].x; atomA[(ch * 4 + 1) * 128 + w] = v[u].y;
+            atomA[(ch * 4 + 2) * 128 + w] = v[u].z; atomA[(ch * 4 + 3) * 128 + w] = v[u].w;
+          }
         }
         // activation scales: columns [0, NB) = hi term, [NB, 2 NB) = lo term
-        for (int idx = gt; idx < C::N * chunks; idx += 64) {
-          const int col = idx / chunks, ch = idx % chunks;
-          const int t = t0 + (col < NB ? col : col - NB);
-          const int row = im.row0 + t;
-          uint4 v = make_uint4(0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu);
-          if (t < im.n && row < a.total_rows)
-            v = *reinterpret_cast<const uint4*>((col < NB ? a.sfh : a.sfl) + (long long)row * (a.K / 32) + ch * 16);
-          const int w = (col & 31) * 4 + (col >> 5);
-          atomB[(ch * 4 + 0) * 128 + w] = v.x; atomB[(ch * 4 + 1) * 128 + w] = v.y;
-          atomB[(ch * 4 + 2) * 128 + w] = v.z; atomB[(ch * 4 + 3) * 128 + w] = v.w;
+        for (int base = 0; base < C::N * chunks; base += 64 * 8) {
+          uint4 v[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            const int idx = base + u * 64 + gt;
+            const int col = idx / chunks, ch = idx % chunks;
+            const int t = t0 + (col < NB ? col : col - NB);
+            const int row = im.row0 + t;
+            v[u] = ones;
+            if (idx < C::N * chunks && t < im.n && row < a.total_rows)
+              v[u] = ldg_nc_16((col < NB ? a.sfh : a.sfl) + (long long)row * (a.K / 32) + ch * 16);
+          }
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            const int idx = base + u * 64 + gt;
+            if (idx >= C::N * chunks) continue;
+            const int col = idx / chunks, ch = idx % chunks;
+            const int w = (col & 31) * 4 + (col >> 5);
+            atomB[(ch * 4 + 0) * 128 + w] = v[u].x; atomB[(ch * 4 + 1) * 128 + w] = v[u].y;
+            atomB[(ch * 4 + 2) * 128 + w] = v[u].z; atomB[(ch * 4 + 3) * 128 + w] = v[u].w;
+          }
         }
         fence_proxy_async();
         asm volatile("bar.sync 2, 64;" ::: "memory");
@@ -310,7 +336,9 @@ __global__ void __launch_bounds__(256, 1) tc_gemm_kernel(const __grid_constant__
         }
         tc_fence_before();
         asm volatile("bar.sync 3, 128;" ::: "memory");
-        if (tid == 64) mbar_arrive(acc_empty(b));  // first epilogue thread: the accumulator buffer may be overwritten
+        if (tid == 64) {  // first epilogue thread: the accumulator buffer may be overwritten
+          mbar_arrive(acc_empty(b));
+        }
       }
     }
   }
