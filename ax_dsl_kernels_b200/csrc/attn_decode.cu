@@ -529,4 +529,97 @@ int run_attn_paged_decode(Call& c) {
   return launch_attn<256, false>(a, c.stream);
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// q35_attn_paged_decode_static: paged attention decode for callers that cannot provide a workspace.
+//
+// Some hosts of these kernels have no way to allocate device memory at call time: an inference runtime whose
+// buffers are all planned before the first token and then frozen (the llama.cpp-style backends the reference
+// targets work that way), or a caller sitting inside somebody else's memory pool.  q35_run("attn.paged_decode")
+// needs a `workspace` tensor for the split-KV partials; this entry point takes none.  The same kernels run, with
+// their scratch in the file-scope device array below.
+//
+// Limits and rules:
+//  * the scratch is Q35_ATTN_STATIC_SCRATCH_BYTES (16 MiB) per GPU, held from library load until process exit; a
+//    call whose shapes need more is rejected with Q35_ERR_WORKSPACE (need = what q35_workspace_bytes reports for
+//    "attn.paged_decode": about (B * HKV + SMs) * 4 * (64 + 32 * D) bytes, e.g. 9.1 MB for batch 64, 2 KV heads,
+//    head_dim 256 on 148 SMs);
+//  * the first call on a device looks up the array's device address (cudaGetSymbolAddress, with that device
+//    current).  That first call should be made outside any stream capture;
+//  * nothing here calls cudaMalloc / cudaFree or any allocating library routine;
+//  * every call on a GPU uses the same array and finds in it whatever the previous call left.  The kernels write
+//    every plan entry and every partial slot before reading it, so nothing has to be cleared, but two calls that
+//    overlap on the GPU (different streams, or threads) race on it: serialise them.
+constexpr size_t Q35_ATTN_STATIC_SCRATCH_BYTES = size_t(16) << 20;
+static __device__ __align__(256) unsigned char g_attn_static_scratch[Q35_ATTN_STATIC_SCRATCH_BYTES];
+
+// In host code `g_attn_static_scratch` is only a host-side handle for the symbol, not an address a kernel can use:
+// the device address comes from cudaGetSymbolAddress, once per device.
+static int attn_static_scratch(uint8_t** out) {
+  constexpr int kMaxDevices = 64;
+  static uint8_t* per_device[kMaxDevices] = {nullptr};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  Q35_REQUIRE(e == cudaSuccess && dev >= 0 && dev < kMaxDevices, Q35_ERR_CUDA, "cudaGetDevice: %s",
+              cudaGetErrorString(e));
+  if (!per_device[dev]) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_attn_static_scratch);
+    Q35_REQUIRE(e == cudaSuccess && p != nullptr, Q35_ERR_CUDA, "cudaGetSymbolAddress(static scratch): %s",
+                cudaGetErrorString(e));
+    per_device[dev] = static_cast<uint8_t*>(p);
+  }
+  *out = per_device[dev];
+  return 0;
+}
+
 }  // namespace q35
+
+extern "C" int q35_attn_paged_decode_static(const void* q, const void* paged_kv_cache, int cache_dtype,
+                                            const int* indptr, const int* indices, const int* last_page_len,
+                                            const float* sm_scale, const float* kv_scale, void* out, int B, int HQ,
+                                            int HKV, int D, int P, int num_pages, int n_indices, void* stream) {
+  using namespace q35;
+  Q35_REQUIRE(q && paged_kv_cache && indptr && indices && last_page_len && out, Q35_ERR_MISSING,
+              "q35_attn_paged_decode_static: null pointer");
+  Q35_REQUIRE(cache_dtype == Q35_BF16 || cache_dtype == Q35_E4M3, Q35_ERR_DTYPE,
+              "q35_attn_paged_decode_static: cache dtype must be bf16 (9) or e4m3 (11)");
+  Q35_REQUIRE(B >= 0 && HKV > 0 && HQ > 0 && HQ % HKV == 0 && HQ / HKV <= AT_GMAX, Q35_ERR_UNSUPPORTED,
+              "q35_attn_paged_decode_static: at most 8 query heads per KV head");
+  const bool fp8 = cache_dtype == Q35_E4M3;
+  Q35_REQUIRE(fp8 ? (D == 128 || D == 256) : (D == 64 || D == 128 || D == 256), Q35_ERR_UNSUPPORTED,
+              "q35_attn_paged_decode_static: head_dim %d", D);
+  Q35_REQUIRE(P >= 16 && P % 16 == 0 && num_pages > 0 && n_indices >= 0, Q35_ERR_SHAPE,
+              "q35_attn_paged_decode_static: page size must be a multiple of 16");
+  if (B == 0) return 0;
+  Q35_REQUIRE(aligned16(q) && aligned16(paged_kv_cache) && aligned16(out), Q35_ERR_ALIGN,
+              "q35_attn_paged_decode_static: pointers must be 16-byte aligned");
+  const int n_cta = sm_count();
+  const int64_t S = int64_t(B) * HKV, slots = (S + n_cta) * 4;
+  int64_t off = 0;
+  auto take = [&](int64_t bytes) { const int64_t o = off; off = (off + bytes + 255) / 256 * 256; return o; };
+  const int64_t o_plan = take(sizeof(AttnPlan)), o_seg = take((S + 1) * 4), o_ctx = take(int64_t(B) * 4),
+                o_ml = take(slots * 16 * 4), o_po = take(slots * AT_GMAX * D * 4);
+  Q35_REQUIRE(off <= int64_t(Q35_ATTN_STATIC_SCRATCH_BYTES), Q35_ERR_WORKSPACE,
+              "q35_attn_paged_decode_static: these shapes need %lld bytes of scratch, the built-in array holds %lld; "
+              "use q35_run(\"attn.paged_decode\") with a workspace",
+              (long long)off, (long long)Q35_ATTN_STATIC_SCRATCH_BYTES);
+  uint8_t* w = nullptr;
+  Q35_TRY(attn_static_scratch(&w));
+  AttnArgs a{};
+  a.q = q; a.cache = paged_kv_cache; a.indptr = indptr; a.indices = indices; a.last_page_len = last_page_len;
+  a.sm_scale = sm_scale; a.kv_scale = kv_scale; a.k_new = nullptr; a.v_new = nullptr;
+  a.out = static_cast<__nv_bfloat16*>(out);
+  a.B = B; a.HQ = HQ; a.HKV = HKV; a.G = HQ / HKV; a.P = P;
+  a.num_pages = num_pages; a.n_indices = n_indices; a.n_cta = n_cta;
+  a.plan = reinterpret_cast<AttnPlan*>(w + o_plan);
+  a.seg_start = reinterpret_cast<int*>(w + o_seg);
+  a.ctx = reinterpret_cast<int*>(w + o_ctx);
+  a.part_ml = reinterpret_cast<float*>(w + o_ml);
+  a.part_o = reinterpret_cast<float*>(w + o_po);
+  a.status = device_status_ptr();
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (fp8) return D == 128 ? launch_attn<128, true>(a, s) : launch_attn<256, true>(a, s);
+  if (D == 64) return launch_attn<64, false>(a, s);
+  if (D == 128) return launch_attn<128, false>(a, s);
+  return launch_attn<256, false>(a, s);
+}

@@ -88,6 +88,20 @@ int q35_device_status(void* stream);
 
 int q35_version(void);
 
+/* Paged attention decode without any caller-provided scratch.  No counterpart in the reference: it exists for hosts
+ * that cannot allocate device memory when they call in (runtimes whose buffers are planned up front and frozen, callers
+ * living inside another component's memory pool).  Same computation and argument meaning as the role
+ * "attn.paged_decode" (q [B, HQ, D] bf16; paged_kv_cache [num_pages, 2, P, HKV, D] of cache_dtype Q35_BF16 or Q35_E4M3;
+ * indptr [B + 1], indices [n_indices], last_page_len [B]; sm_scale / kv_scale device pointers or NULL; out [B, HQ, D]
+ * bf16), but the split-KV scratch is a 16 MiB array built into the library (held on every GPU that loads it).
+ * Shapes that need more return Q35_ERR_WORKSPACE.  Calls nothing that allocates.  The first call on a device resolves
+ * the array's device address and should happen outside stream capture.  All calls on a GPU share the array: calls that
+ * overlap on the GPU race, so keep them on one stream or otherwise ordered. */
+int q35_attn_paged_decode_static(const void* q, const void* paged_kv_cache, int cache_dtype, const int* indptr,
+                                 const int* indices, const int* last_page_len, const float* sm_scale,
+                                 const float* kv_scale, void* out, int B, int HQ, int HKV, int D, int P, int num_pages,
+                                 int n_indices, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
