@@ -254,10 +254,13 @@ int run_moe_slots(Call& c) {
                   dw.s[2] == FE / 2 && ds.s[0] == NE && ds.s[1] == H && ds.s[2] == FE / 32,
               Q35_ERR_SHAPE, "moe.slots: expert plane shapes");
   Q35_REQUIRE(H % 256 == 0 && FE % 256 == 0, Q35_ERR_UNSUPPORTED, "moe.slots: H and FE must be multiples of 256");
+  const bool use_tc = tc_shapes_ok(H, FE);
+  uint8_t* qws = nullptr;
   WsCarver w{nullptr};
   auto carve = [&](WsCarver& cw, int*& g_expert, int*& g_n, int*& g_row0, int*& src, __nv_bfloat16*& act) {
     g_expert = cw.take<int>(S); g_n = cw.take<int>(S); g_row0 = cw.take<int>(S);
     src = cw.take<int>(S * G); act = cw.take<__nv_bfloat16>(S * G * FE);
+    qws = use_tc ? cw.take<uint8_t>(tc_routed_bytes(S * G, H, FE, S)) : nullptr;
   };
   int *g_expert, *g_n, *g_row0, *src;
   __nv_bfloat16* act;
@@ -273,6 +276,12 @@ int run_moe_slots(Call& c) {
       tok.as<int>(), ns.present ? ns.as<int>() : nullptr, int(S), int(G), int(T), int(NE), g_expert, g_n, g_row0, src,
       device_status_ptr());
   Q35_CUDA_LAUNCH_CHECK("moe.slots groups");
+  if (use_tc) {
+    const ExpertPlanes ep{gw.as<uint8_t>(), gs.as<uint8_t>(), dw.as<uint8_t>(), ds.as<uint8_t>(), NE, FE, H};
+    return tc_routed(ep, h2.as<__nv_bfloat16>(), src, int(S * G), int(S), g_expert, g_n, g_row0, int(G), act, qws,
+                     out.dtype == Q35_F32 ? out.as<float>() : nullptr,
+                     out.dtype == Q35_F32 ? nullptr : out.as<__nv_bfloat16>(), rw.as<float>(), c.stream);
+  }
   const int nt = pick_nt(G);
   SkinnyArgs a{};
   a.status = device_status_ptr();

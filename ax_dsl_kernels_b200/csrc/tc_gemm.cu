@@ -155,7 +155,7 @@ static int launch_nb(const CUtensorMap& w0, const CUtensorMap& w1, const CUtenso
     cudaFuncSetAttribute(tc_gemm_kernel<NB, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     attr_smem = smem;
   }
-  const long long items = (long long)tiles * groups;
+  const long long items = (long long)tiles * (a.g_n ? groups : (a.n_dense + TC_DENSE_ROWS - 1) / TC_DENSE_ROWS);
   const long long slots = (long long)tc_sm_count() * TcCfg<NB>::CTAS_PER_SM;
   const unsigned grid = unsigned(items < slots ? items : slots);
   tc_gemm_kernel<NB, EPI><<<grid, 256, smem, stream>>>(w0, w1, xh, xl, a);

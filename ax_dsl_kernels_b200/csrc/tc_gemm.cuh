@@ -68,6 +68,8 @@ struct TcCfg {
 
 // sub-item iteration shared by all roles: (active group, row tile) pairs dealt round-robin to the CTAs, and inside
 // a pair the token tiles of NB rows
+constexpr int TC_DENSE_ROWS = 256;
+
 struct TcItem {
   int plane, row0, n, tile;
 };
@@ -80,8 +82,11 @@ __device__ __forceinline__ bool tc_get_item(const TcArgs& a, int j, TcItem* it) 
       atomicOr(a.status, DS_BAD_EXPERT);
       it->n = 0;
     }
-  } else {
-    it->n = a.n_dense; it->plane = 0; it->row0 = 0;
+  } else {  // one dense matrix: the rows are cut into virtual groups of TC_DENSE_ROWS so that prefill-sized inputs
+            // spread over all CTAs
+    it->row0 = (j / a.n_tiles) * TC_DENSE_ROWS;
+    it->n = min(TC_DENSE_ROWS, a.n_dense - it->row0);
+    it->plane = 0;
   }
   it->tile = j % a.n_tiles;
   return it->n > 0;
@@ -96,7 +101,7 @@ __global__ void __launch_bounds__(256, TcCfg<NB>::CTAS_PER_SM) tc_gemm_kernel(co
   using namespace tc;
   extern __shared__ uint8_t smem_raw[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int n_items = (a.g_n ? a.n_active[0] : 1) * a.n_tiles;
+  const int n_items = (a.g_n ? a.n_active[0] : (a.n_dense + TC_DENSE_ROWS - 1) / TC_DENSE_ROWS) * a.n_tiles;
   if (int(blockIdx.x) >= n_items) return;
 
   const int KS = a.K / 128;

@@ -350,3 +350,19 @@ def test_linear_tc_block_scaled_mma(q35, T, N, K):
     bias = torch.randn(N, generator=g)
     q35.run("linear.tc", x=x.cuda(), w=w.cuda(), s=s.cuda(), bias=bias.cuda(), out=outb)
     assert_parity(outb.cpu(), (ref + bias.double()).to(torch.bfloat16))
+
+
+def test_moe_block_prefill_sized_batch(q35):
+    """1024 tokens through the whole block (tensor-core grouped GEMM with many tokens per expert); the CPU golden is
+    evaluated on a sample of the tokens (it loops over tokens in Python)"""
+    T = 1024
+    x1, w = moe_case(T, NE=32, seed=77)
+    wd = {k: v.cuda() for k, v in w.items()}
+    out, gids, grw, glog = q35.moe_block(x1.cuda(), wd, 8)
+    sample = torch.arange(0, T, 43)
+    sg, su, sd = dequant_shared(w)
+    ref, ids, rw, logits = omoe.moe_block(x1[sample], w["ln2"], sg, su, sd, w["w_router"], w["w_shg"], w["e_gw"],
+                                          w["e_gs"], w["e_dw"], w["e_ds"], 8)
+    assert torch.equal(gids.cpu()[sample], ids)
+    assert_parity(out.cpu()[sample], ref)
+    assert torch.isfinite(out).all()
