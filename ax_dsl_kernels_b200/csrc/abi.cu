@@ -111,6 +111,9 @@ static const RoleDef kRoles[] = {
     {"gdn.conv",
      R"({"in":[["x","bf16","[B,T,C]"],["conv_w","bf16","[C,KW]"],["conv_in","bf16","[B,KW-1,C]"]],"out":[["y","bf16","[B,T,C]"],["conv_out","bf16","[B,KW-1,C]"]]})",
      run_gdn_conv},
+    {"gdn.chunk_prefill",
+     R"({"in":[["q","bf16","[B,T,NK,128]"],["k","bf16","[B,T,NK,128]"],["v","bf16","[B,T,NV,128]"],["g","f32","[B,T,NV]"],["beta","bf16","[B,T,NV]"],["state_in","f32","[B,NV,128,128]"],["workspace","u8","[*]"]],"out":[["o","bf16","[B,T,NV,128]"],["state_out","f32","[B,NV,128,128]"]]})",
+     run_gdn_chunk_prefill},
     {"linear",
      R"({"in":[["x","bf16","[T,K]"],["w","u8|e4m3|bf16","[N,K/2]|[N,K]"],["s","u8|f32","[N,K/32]|[N] optional"],["bias","f32","[N] optional"]],"out":[["out","bf16|f32","[T,N]"]]})",
      run_linear},

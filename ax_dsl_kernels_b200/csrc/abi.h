@@ -83,6 +83,7 @@ int run_attn_paged_decode(Call&);
 int run_attn_kv_write(Call&);
 int run_gdn_step(Call&);
 int run_gdn_conv(Call&);
+int run_gdn_chunk_prefill(Call&);
 int run_linear(Call&);
 int run_linear_tc(Call&);
 

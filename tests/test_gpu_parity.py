@@ -366,3 +366,47 @@ def test_moe_block_prefill_sized_batch(q35):
     assert torch.equal(gids.cpu()[sample], ids)
     assert_parity(out.cpu()[sample], ref)
     assert torch.isfinite(out).all()
+
+
+# ------------------------------------------------------------------------------------------------ GDN prefill
+def _gdn_seq(T, NK, NV, seed, B=1, zero_state=False):
+    g = torch.Generator().manual_seed(seed)
+    q = (ogdn.l2norm(torch.randn((B, T, NK, 128), generator=g)).float() * 128 ** -0.5).to(torch.bfloat16)
+    k = ogdn.l2norm(torch.randn((B, T, NK, 128), generator=g))
+    v = torch.randn((B, T, NV, 128), generator=g).to(torch.bfloat16)
+    beta = torch.sigmoid(torch.randn((B, T, NV), generator=g)).to(torch.bfloat16)
+    gg = -torch.nn.functional.softplus(torch.randn((B, T, NV), generator=g))
+    s0 = torch.zeros((B, NV, 128, 128)) if zero_state else torch.randn((B, NV, 128, 128), generator=g) * 0.03
+    return q, k, v, gg, beta, s0
+
+
+@pytest.mark.parametrize("T,NK,NV,B", [(64, 2, 4, 1), (200, 2, 4, 1), (1, 1, 1, 2), (777, 1, 3, 1), (130, 2, 2, 2)])
+def test_gdn_chunk_prefill_against_token_recurrence(q35, T, NK, NV, B):
+    """The chunked kernel and the token-by-token golden round at different points, so they agree only to the golden's
+    own rounding noise; both are measured against the unrounded float64 recurrence and the kernel must be at least as
+    close as the golden (with a 2e-2 floor), and within the sum of both distances of the golden itself."""
+    q, k, v, gg, beta, s0 = _gdn_seq(T, NK, NV, seed=T + NV, B=B)
+    o64, s64 = ogdn.recurrent_f64(q, k, v, gg, beta, s0)
+    og, sg = ogdn.recurrent(q, k, v, gg, beta, s0)
+    o, s1 = q35.gdn_chunk_prefill(*cu(q, k, v, gg, beta, s0))
+    rms = o64.square().mean().sqrt()
+    d_kernel = ((o.cpu().double() - o64).abs().max() / rms).item()
+    d_golden = ((og.double() - o64).abs().max() / rms).item()
+    assert d_kernel <= max(2e-2, 1.5 * d_golden), (d_kernel, d_golden)
+    assert ((o.cpu().double() - og.double()).abs().max() / rms).item() <= d_kernel + d_golden + 1e-3
+    assert (s1.cpu().double() - s64).abs().max().item() <= max(4e-3, 1.5 * (sg.double() - s64).abs().max().item())
+
+
+def test_gdn_chunk_prefill_then_decode_continues(q35):
+    """prefill T tokens, then one recurrent step from the prefill's state = the golden run over T + 1 tokens
+    (the reference's decode-continues-prefill check, test_gdn_attn.py:694-721)"""
+    T = 150
+    q, k, v, gg, beta, s0 = _gdn_seq(T + 1, 2, 4, seed=9)
+    o64, s64 = ogdn.recurrent_f64(q, k, v, gg, beta, s0)
+    cut = lambda t: t[:, :T].contiguous()  # noqa: E731
+    _, st = q35.gdn_chunk_prefill(*cu(cut(q), cut(k), cut(v), cut(gg), cut(beta), s0))
+    o, st = q35.gdn_recurrent_step(*cu(q[:, T].contiguous(), k[:, T].contiguous(), v[:, T].contiguous(),
+                                       gg[:, T].contiguous(), beta[:, T].contiguous()), st)
+    rms = o64.square().mean().sqrt()
+    assert ((o.cpu().double() - o64[:, T]).abs().max() / rms).item() <= 6e-2
+    assert (st.cpu().double() - s64).abs().max().item() <= 6e-3
