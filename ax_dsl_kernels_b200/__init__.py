@@ -6,11 +6,11 @@ CPU path and no fallback: without the built library every call raises.
 """
 from . import _lib
 from ._lib import Q35Error, device_status, io_table, roles, run, workspace_bytes  # noqa: F401
-from .attention import kv_write, paged_attention_decode  # noqa: F401
+from .attention import kv_write, paged_attention_decode, paged_attention_prefill  # noqa: F401
 from .gdn import gdn_chunk_prefill, gdn_conv1d_silu, gdn_recurrent_step  # noqa: F401
 from .moe import (linear, moe_block, moe_combine, moe_experts, moe_permute, moe_pre, moe_slots_px,  # noqa: F401
                   route)
 
 __all__ = ["run", "roles", "io_table", "workspace_bytes", "device_status", "Q35Error", "route", "moe_pre",
            "moe_experts", "moe_slots_px", "moe_combine", "moe_permute", "moe_block", "linear",
-           "paged_attention_decode", "kv_write", "gdn_recurrent_step", "gdn_conv1d_silu", "gdn_chunk_prefill"]
+           "paged_attention_decode", "paged_attention_prefill", "kv_write", "gdn_recurrent_step", "gdn_conv1d_silu", "gdn_chunk_prefill"]

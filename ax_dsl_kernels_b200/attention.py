@@ -40,3 +40,21 @@ def kv_write(paged_kv_cache, cache_location, k_new, v_new, kv_scale=None):
         kw["kv_scale"] = kv_scale
     _lib.run("attn.kv_write", **kw)
     return paged_kv_cache
+
+
+def paged_attention_prefill(q, paged_kv_cache, qo_indptr, indptr, indices, last_page_len, out=None, *, sm_scale=None,
+                            k_new=None, v_new=None):
+    """Causal attention of T new tokens per sequence over the paged cache.  q [Ttot, HQ, D] bf16 with the sequences
+    delimited by qo_indptr [B + 1]; the page table (indptr / indices / last_page_len) describes each sequence INCLUDING
+    its new tokens.  k_new / v_new [Ttot, HKV, D], when given, are first written into the cache at the new tokens'
+    positions (otherwise the cache must already hold them).  Page size must be a multiple of 64."""
+    out = torch.empty_like(q) if out is None else out
+    kw = dict(q=q, paged_kv_cache=paged_kv_cache, qo_indptr=qo_indptr, indptr=indptr, indices=indices,
+              last_page_len=last_page_len, out=out)
+    if sm_scale is not None:
+        kw["sm_scale"] = sm_scale if isinstance(sm_scale, torch.Tensor) else torch.tensor(
+            [float(sm_scale)], dtype=torch.float32, device=q.device)
+    if k_new is not None:
+        kw["k_new"], kw["v_new"] = k_new, v_new
+    _lib.run("attn.paged_prefill", **kw)
+    return out

@@ -1,0 +1,296 @@
+// Paged flash-attention prefill: T new tokens per sequence attend causally to the sequence's paged KV cache, which
+// already holds their own K / V rows (written with attn.kv_write / attn.kv_write_rows).
+//
+// Reference: paged_flash_attention (models/qwen35_35b_a3b/sgl/python/sgl_kernel_axera/attention/flash_attn.py:
+// 471-610: history pages plus the causal current tile) and attn_layer_prefill
+// (models/qwen35_2b/whole/src/q35_prefill.py:250-318: G * P query rows per KV head against the cache with a causal
+// mask).  Same arithmetic as the decode golden with a causal mask: softmax(q k^T * scale) v per query head.
+//
+// One CTA = 16 query tokens x the (up to 8) query heads of one KV head = 128 rows of the score tile, 8 warps of 16
+// rows, so a K / V tile fetched once serves all heads of the group.  Keys stream in tiles of 64 through a 2-stage
+// cp.async ring (XOR-swizzled rows); S = Q K^T and O += P V on mma.sync bf16 with fp32 accumulation and an online
+// softmax in the log2 domain.  Tensor-bound for long prompts (4 T^2 / 2 * HQ * D flop against T * 2 KB of KV).
+#include "abi.h"
+#include "common.cuh"
+
+namespace q35 {
+
+constexpr int PF_TOK = 16;    // query tokens per CTA
+constexpr int PF_KEYS = 64;   // keys per tile
+constexpr float PF_LOG2E = 1.4426950408889634f;
+
+struct PrefillArgs {
+  const __nv_bfloat16* q;      // [Ttot, HQ, D]
+  const __nv_bfloat16* cache;  // [pages, 2, P, HKV, D]
+  const int* qo_indptr;        // [B + 1] token ranges of the sequences inside q
+  const int* indptr; const int* indices; const int* last_page_len;  // page table incl. the new tokens
+  const float* sm_scale;
+  __nv_bfloat16* out;          // [Ttot, HQ, D]
+  int B, HQ, HKV, G, P, num_pages, n_indices;
+  int* status;
+};
+
+template <int D>
+__global__ void __launch_bounds__(256, 1) attn_prefill_kernel(const PrefillArgs a) {
+  constexpr int ROWB = D * 2, CPR = ROWB / 16, TILE_BYTES = PF_KEYS * ROWB;
+  extern __shared__ __align__(128) uint8_t smem[];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int r = lane >> 2, c = lane & 3;
+  const int b = blockIdx.z, kvh = blockIdx.y;
+  const int q0 = a.qo_indptr[b], q1 = a.qo_indptr[b + 1];
+  const int tq = q1 - q0;                       // new tokens of this sequence
+  const int tok0 = blockIdx.x * PF_TOK;
+  if (tok0 >= tq) return;
+  const int np = a.indptr[b + 1] - a.indptr[b];
+  int kv_len = np > 0 ? (np - 1) * a.P + a.last_page_len[b] : 0;
+  if (kv_len < tq || a.indptr[b + 1] > a.n_indices) {  // the cache must already contain the new tokens
+    if (tid == 0) atomicOr(a.status, DS_BAD_PAGE);
+    kv_len = max(kv_len, tq);
+    return;
+  }
+  const int hist = kv_len - tq;                 // tokens before this call
+  const int page0 = a.indptr[b];
+  const float scale_log2 = (a.sm_scale ? a.sm_scale[0] : rsqrtf(float(D))) * PF_LOG2E;
+
+  // this thread's two rows: row m = warp * 16 + r (+ 8); token = m / 8, head = m % 8
+  const int m0 = warp * 16 + r, m1 = m0 + 8;
+  const int tk0 = tok0 + (m0 >> 3), tk1 = tok0 + (m1 >> 3);
+  const int h0 = m0 & 7, h1 = m1 & 7;  // equal (r and r + 8 differ by one token), kept for clarity
+  const bool v0 = tk0 < tq && h0 < a.G, v1 = tk1 < tq && h1 < a.G;
+  const int pos0 = hist + tk0, pos1 = hist + tk1;  // last visible key of each row
+
+  // Q fragments (A operand): a0 = (row m0, d 2c..), a1 = (row m1, ..), a2 = (m0, d + 8), a3 = (m1, d + 8)
+  uint32_t qf[D / 16][4];
+  {
+    const __nv_bfloat16* p0 = a.q + (size_t(q0 + min(tk0, tq - 1)) * a.HQ + kvh * a.G + min(h0, a.G - 1)) * D;
+    const __nv_bfloat16* p1 = a.q + (size_t(q0 + min(tk1, tq - 1)) * a.HQ + kvh * a.G + min(h1, a.G - 1)) * D;
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+      qf[ks][0] = v0 ? *reinterpret_cast<const uint32_t*>(p0 + ks * 16 + 2 * c) : 0u;
+      qf[ks][1] = v1 ? *reinterpret_cast<const uint32_t*>(p1 + ks * 16 + 2 * c) : 0u;
+      qf[ks][2] = v0 ? *reinterpret_cast<const uint32_t*>(p0 + ks * 16 + 8 + 2 * c) : 0u;
+      qf[ks][3] = v1 ? *reinterpret_cast<const uint32_t*>(p1 + ks * 16 + 8 + 2 * c) : 0u;
+    }
+  }
+  float o[D / 8][4];
+#pragma unroll
+  for (int nt = 0; nt < D / 8; ++nt) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.f;
+  float mrow[2] = {-INFINITY, -INFINITY}, lrow[2] = {0.f, 0.f};
+
+  const int last_pos = hist + min(tok0 + PF_TOK, tq) - 1;  // last key any row of this CTA may see
+  const int n_tiles = last_pos / PF_KEYS + 1;
+  const size_t row_stride = size_t(a.HKV) * ROWB;
+  const uint8_t* cbase = reinterpret_cast<const uint8_t*>(a.cache);
+  const uint32_t sbase = smem_u32(smem);
+
+  auto issue = [&](int t) {
+    if (t < n_tiles) {
+      const int kk = t * PF_KEYS;
+      const int pl = kk / a.P, ro = kk % a.P;
+      int page = a.indices[page0 + min(pl, np - 1)];
+      if (page < 0 || page >= a.num_pages) {
+        if (tid == 0) atomicOr(a.status, DS_BAD_PAGE);
+        page = 0;
+      }
+      const uint8_t* kb = cbase + ((size_t(page) * 2 + 0) * a.P + ro) * row_stride + size_t(kvh) * ROWB;
+      const uint8_t* vb = cbase + ((size_t(page) * 2 + 1) * a.P + ro) * row_stride + size_t(kvh) * ROWB;
+      const uint32_t st = sbase + (t & 1) * 2 * TILE_BYTES;
+      for (int idx = tid; idx < PF_KEYS * CPR; idx += 256) {
+        const int key = idx / CPR, ch = idx % CPR;
+        const uint32_t off = key * ROWB + ((ch ^ (key & 7)) << 4);
+        cp_async_16(st + off, kb + size_t(key) * row_stride + ch * 16);
+        cp_async_16(st + TILE_BYTES + off, vb + size_t(key) * row_stride + ch * 16);
+      }
+    }
+    cp_async_commit();
+  };
+
+  issue(0);
+  for (int t = 0; t < n_tiles; ++t) {
+    issue(t + 1);
+    cp_async_wait<1>();
+    __syncthreads();
+    const uint32_t sK = sbase + (t & 1) * 2 * TILE_BYTES, sV = sK + TILE_BYTES;
+    const int kk = t * PF_KEYS;
+    if (kk + PF_KEYS > kv_len) {  // rows past the cached length may hold anything (NaN bits): clear V there
+      const int first = kv_len - kk;
+      for (int idx = tid; idx < (PF_KEYS - first) * CPR; idx += 256) {
+        const uint32_t addr = sV + (first + idx / CPR) * ROWB + ((idx % CPR) << 4);
+        asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(addr), "r"(0u));
+      }
+      __syncthreads();
+    }
+    // S = Q K^T: 16 rows x 64 keys per warp
+    float s[8][4];
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+#pragma unroll
+      for (int np2 = 0; np2 < 4; ++np2) {
+        const int brow = np2 * 16 + (lane & 7) + ((lane >> 4) << 3);
+        const int ch = 2 * ks + ((lane >> 3) & 1);
+        uint32_t b0, b1, b2, b3;
+        ldmatrix_x4(sK + brow * ROWB + ((ch ^ (brow & 7)) << 4), b0, b1, b2, b3);
+        mma_bf16_16816(s[2 * np2], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], b0, b1);
+        mma_bf16_16816(s[2 * np2 + 1], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], b2, b3);
+      }
+    }
+    // causal mask, online softmax (rows m0: regs 0,1; m1: regs 2,3)
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int key = kk + nt * 8 + 2 * c + (i & 1);
+        const int pos = (i >> 1) ? pos1 : pos0;
+        s[nt][i] = key <= pos ? s[nt][i] * scale_log2 : -INFINITY;
+        mx[i >> 1] = fmaxf(mx[i >> 1], s[nt][i]);
+      }
+    float alpha[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+      mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+      const float mn = fmaxf(mrow[h], mx[h]);
+      alpha[h] = mn == -INFINITY ? 1.f : exp2f(mrow[h] - mn);
+      mrow[h] = mn;
+    }
+    uint32_t pf[8][2];  // P as bf16 pairs in the accumulator layout
+    float ls[2] = {0.f, 0.f};
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) {
+      const float p0 = mrow[0] == -INFINITY ? 0.f : exp2f(s[nt][0] - mrow[0]);
+      const float p1 = mrow[0] == -INFINITY ? 0.f : exp2f(s[nt][1] - mrow[0]);
+      const float p2 = mrow[1] == -INFINITY ? 0.f : exp2f(s[nt][2] - mrow[1]);
+      const float p3 = mrow[1] == -INFINITY ? 0.f : exp2f(s[nt][3] - mrow[1]);
+      ls[0] += p0 + p1; ls[1] += p2 + p3;
+      pf[nt][0] = pack_bf16(p0, p1);
+      pf[nt][1] = pack_bf16(p2, p3);
+    }
+    lrow[0] = lrow[0] * alpha[0] + ls[0];
+    lrow[1] = lrow[1] * alpha[1] + ls[1];
+    if (alpha[0] != 1.f || alpha[1] != 1.f) {
+#pragma unroll
+      for (int nt = 0; nt < D / 8; ++nt) {
+        o[nt][0] *= alpha[0]; o[nt][1] *= alpha[0]; o[nt][2] *= alpha[1]; o[nt][3] *= alpha[1];
+      }
+    }
+    // O += P V: A = P (score accumulators reused as fragments), B = V tile [key][d] read transposed
+#pragma unroll
+    for (int ks = 0; ks < PF_KEYS / 16; ++ks) {
+      const uint32_t a0 = pf[2 * ks][0], a1 = pf[2 * ks][1], a2 = pf[2 * ks + 1][0], a3 = pf[2 * ks + 1][1];
+      const int brow = ks * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
+#pragma unroll
+      for (int np2 = 0; np2 < D / 16; ++np2) {
+        const int ch = 2 * np2 + (lane >> 4);
+        uint32_t b0, b1, b2, b3;
+        ldmatrix_x4_trans(sV + brow * ROWB + ((ch ^ (brow & 7)) << 4), b0, b1, b2, b3);
+        mma_bf16_16816(o[2 * np2], a0, a1, a2, a3, b0, b1);
+        mma_bf16_16816(o[2 * np2 + 1], a0, a1, a2, a3, b2, b3);
+      }
+    }
+    __syncthreads();
+  }
+  cp_async_wait<0>();
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    lrow[h] += __shfl_xor_sync(0xffffffffu, lrow[h], 1);
+    lrow[h] += __shfl_xor_sync(0xffffffffu, lrow[h], 2);
+  }
+  const float inv0 = lrow[0] > 0.f ? 1.f / lrow[0] : 0.f, inv1 = lrow[1] > 0.f ? 1.f / lrow[1] : 0.f;
+  __nv_bfloat16* d0 = a.out + (size_t(q0 + tk0) * a.HQ + kvh * a.G + h0) * D;
+  __nv_bfloat16* d1 = a.out + (size_t(q0 + tk1) * a.HQ + kvh * a.G + h1) * D;
+#pragma unroll
+  for (int nt = 0; nt < D / 8; ++nt) {
+    if (v0) *reinterpret_cast<uint32_t*>(d0 + nt * 8 + 2 * c) = pack_bf16(o[nt][0] * inv0, o[nt][1] * inv0);
+    if (v1) *reinterpret_cast<uint32_t*>(d1 + nt * 8 + 2 * c) = pack_bf16(o[nt][2] * inv1, o[nt][3] * inv1);
+  }
+}
+
+// attn.kv_write_rows: K / V rows of T new tokens per sequence into the paged cache at positions hist .. hist + T - 1
+// (store_paged_kv for a prefill tile, flash_attn.py:53-84)
+__global__ void attn_kv_write_rows_kernel(const __nv_bfloat16* __restrict__ k_new, const __nv_bfloat16* __restrict__ v_new,
+                                          const int* __restrict__ qo_indptr, const int* __restrict__ indptr,
+                                          const int* __restrict__ indices, const int* __restrict__ last_page_len,
+                                          __nv_bfloat16* cache, int B, int HKV, int D, int P, int num_pages, int* status) {
+  const int tok = blockIdx.x;  // global token index
+  int b = 0;
+  while (b + 1 < B && qo_indptr[b + 1] <= tok) ++b;
+  if (tok < qo_indptr[b] || tok >= qo_indptr[b + 1]) return;
+  const int tq = qo_indptr[b + 1] - qo_indptr[b];
+  const int np = indptr[b + 1] - indptr[b];
+  const int kv_len = np > 0 ? (np - 1) * P + last_page_len[b] : 0;
+  const int pos = kv_len - tq + (tok - qo_indptr[b]);
+  if (pos < 0 || pos / P >= np) { if (threadIdx.x == 0) atomicOr(status, DS_BAD_PAGE); return; }
+  const int page = indices[indptr[b] + pos / P];
+  if (page < 0 || page >= num_pages) { if (threadIdx.x == 0) atomicOr(status, DS_BAD_PAGE); return; }
+  const int n = HKV * D;
+  for (int i = threadIdx.x * 8; i < n; i += blockDim.x * 8) {
+    *reinterpret_cast<uint4*>(cache + ((size_t(page) * 2 + 0) * P + pos % P) * n + i) =
+        *reinterpret_cast<const uint4*>(k_new + size_t(tok) * n + i);
+    *reinterpret_cast<uint4*>(cache + ((size_t(page) * 2 + 1) * P + pos % P) * n + i) =
+        *reinterpret_cast<const uint4*>(v_new + size_t(tok) * n + i);
+  }
+}
+
+int run_attn_paged_prefill(Call& c) {
+  Tensor q, cache, qo, indptr, indices, lpl, scale, kn, vn, out;
+  Q35_TRY(c.get("q", M(Q35_BF16), &q));
+  Q35_TRY(c.get("paged_kv_cache", M(Q35_BF16), &cache));
+  Q35_TRY(c.get("qo_indptr", M(Q35_I32), &qo));
+  Q35_TRY(c.get("indptr", M(Q35_I32), &indptr));
+  Q35_TRY(c.get("indices", M(Q35_I32), &indices));
+  Q35_TRY(c.get("last_page_len", M(Q35_I32), &lpl));
+  Q35_TRY(c.get("sm_scale", M(Q35_F32), &scale, false));
+  Q35_TRY(c.get("k_new", M(Q35_BF16), &kn, false));
+  Q35_TRY(c.get("v_new", M(Q35_BF16), &vn, false));
+  Q35_TRY(c.get("out", M(Q35_BF16), &out));
+  Q35_REQUIRE(q.nd == 3 && cache.nd == 5 && cache.s[1] == 2, Q35_ERR_SHAPE,
+              "attn.paged_prefill: q [T, HQ, D], paged_kv_cache [pages, 2, P, HKV, D]");
+  const int64_t T = q.s[0], HQ = q.s[1], D = q.s[2], P = cache.s[2], HKV = cache.s[3], B = qo.numel() - 1;
+  Q35_REQUIRE(cache.s[4] == D && HKV > 0 && HQ % HKV == 0 && HQ / HKV <= 8, Q35_ERR_UNSUPPORTED,
+              "attn.paged_prefill: at most 8 query heads per KV head");
+  Q35_REQUIRE(D == 128 || D == 256, Q35_ERR_UNSUPPORTED, "attn.paged_prefill: head_dim must be 128 or 256");
+  Q35_REQUIRE(P % 64 == 0, Q35_ERR_UNSUPPORTED, "attn.paged_prefill: page size must be a multiple of 64");
+  Q35_REQUIRE(B >= 1 && indptr.numel() == B + 1 && lpl.numel() >= B && out.numel() == q.numel(), Q35_ERR_SHAPE,
+              "attn.paged_prefill: qo_indptr / indptr [B+1], last_page_len [B], out like q");
+  Q35_REQUIRE(kn.present == vn.present && (!kn.present || (kn.numel() == T * HKV * D && vn.numel() == T * HKV * D)),
+              Q35_ERR_SHAPE, "attn.paged_prefill: k_new / v_new [T, HKV, D]");
+  c.ws_need = 0;
+  if (c.dry || T == 0) return 0;
+  Q35_REQUIRE(aligned16(q.p) && aligned16(cache.p) && aligned16(out.p), Q35_ERR_ALIGN, "attn.paged_prefill: alignment");
+  if (kn.present) {
+    attn_kv_write_rows_kernel<<<unsigned(T), 128, 0, c.stream>>>(
+        kn.as<__nv_bfloat16>(), vn.as<__nv_bfloat16>(), qo.as<int>(), indptr.as<int>(), indices.as<int>(),
+        lpl.as<int>(), cache.as<__nv_bfloat16>(), int(B), int(HKV), int(D), int(P), int(cache.s[0]),
+        device_status_ptr());
+    Q35_CUDA_LAUNCH_CHECK("attn.kv_write_rows");
+  }
+  PrefillArgs a{};
+  a.q = q.as<__nv_bfloat16>(); a.cache = cache.as<__nv_bfloat16>(); a.qo_indptr = qo.as<int>();
+  a.indptr = indptr.as<int>(); a.indices = indices.as<int>(); a.last_page_len = lpl.as<int>();
+  a.sm_scale = scale.present ? scale.as<float>() : nullptr;
+  a.out = out.as<__nv_bfloat16>();
+  a.B = int(B); a.HQ = int(HQ); a.HKV = int(HKV); a.G = int(HQ / HKV); a.P = int(P);
+  a.num_pages = int(cache.s[0]); a.n_indices = int(indices.numel());
+  a.status = device_status_ptr();
+  // the longest sequence is not known on the host: the grid covers T tokens for every sequence, CTAs past a
+  // sequence's own length leave at once
+  const dim3 grid{unsigned((T + PF_TOK - 1) / PF_TOK), unsigned(HKV), unsigned(B)};
+  if (D == 256) {
+    constexpr int smem = 4 * PF_KEYS * 512;
+    static bool done = false;
+    if (!done) { cudaFuncSetAttribute(attn_prefill_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); done = true; }
+    attn_prefill_kernel<256><<<grid, 256, smem, c.stream>>>(a);
+  } else {
+    constexpr int smem = 4 * PF_KEYS * 256;
+    static bool done = false;
+    if (!done) { cudaFuncSetAttribute(attn_prefill_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); done = true; }
+    attn_prefill_kernel<128><<<grid, 256, smem, c.stream>>>(a);
+  }
+  Q35_CUDA_LAUNCH_CHECK("attn.paged_prefill");
+  return 0;
+}
+
+}  // namespace q35

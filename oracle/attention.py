@@ -62,6 +62,31 @@ def paged_decode(q, cache, indptr, indices, last_page_len, sm_scale=None, kv_sca
     return out.to(torch.bfloat16)
 
 
+def paged_prefill(q, cache, qo_indptr, indptr, indices, last_page_len, sm_scale=None):
+    """T new tokens per sequence against the paged cache that already holds their K / V rows, causal:
+    token i of a sequence with `hist` earlier tokens sees keys 0 .. hist + i (prefill form of the decode golden;
+    reference kernels: flash_attn.py:471-610, models/qwen35_2b/whole/src/q35_prefill.py:250-318).
+    q [Ttot, HQ, D] bf16, sequences delimited by qo_indptr [B + 1]."""
+    Ttot, HQ, D = q.shape
+    HKV = cache.shape[3]
+    G = HQ // HKV
+    scale = 1.0 / math.sqrt(D) if sm_scale is None else float(sm_scale)
+    out = torch.zeros((Ttot, HQ, D))
+    for b in range(qo_indptr.numel() - 1):
+        q0, q1 = int(qo_indptr[b]), int(qo_indptr[b + 1])
+        if q1 == q0:
+            continue
+        k, v = gather_kv(cache, indptr, indices, last_page_len, b)
+        hist = k.shape[0] - (q1 - q0)
+        qb = q[q0:q1].float().reshape(q1 - q0, HKV, G, D)
+        s = torch.einsum("thgd,lhd->thgl", qb, k) * scale
+        pos = hist + torch.arange(q1 - q0)
+        mask = torch.arange(k.shape[0])[None, :] > pos[:, None]
+        s = s.masked_fill(mask[:, None, None, :], float("-inf"))
+        out[q0:q1] = torch.einsum("thgl,lhd->thgd", torch.softmax(s, -1), v).reshape(q1 - q0, HQ, D)
+    return out.to(torch.bfloat16)
+
+
 def store_paged_kv(cache, cache_location, k_new, v_new, kv_scale=None):
     """write the current token's K / V rows at (page, offset) per sequence (flash_attn.py:53-84); FP8 caches store
     e4m3(x * 8) (models/qwen38_27b/decode/q35_group.py:244-249) or e4m3(x / scale_h) with kv_scale [2, HKV]."""

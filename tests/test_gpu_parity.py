@@ -410,3 +410,49 @@ def test_gdn_chunk_prefill_then_decode_continues(q35):
     rms = o64.square().mean().sqrt()
     assert ((o.cpu().double() - o64[:, T]).abs().max() / rms).item() <= 6e-2
     assert (st.cpu().double() - s64).abs().max().item() <= 6e-3
+
+
+# ------------------------------------------------------------------------------------------------ attention prefill
+@pytest.mark.parametrize("hist,T,P,HKV,HQ,D", [([0], [64], 64, 2, 16, 256), ([70, 0, 300], [33, 1, 130], 64, 2, 16, 256),
+                                               ([256], [257], 256, 2, 4, 128), ([10], [100], 128, 4, 24, 256)])
+def test_paged_prefill(q35, hist, T, P, HKV, HQ, D):
+    g = torch.Generator().manual_seed(sum(T) + P)
+    ctxs = [h + t for h, t in zip(hist, T)]
+    _, cache, indptr, indices, last, _ = paged_case(ctxs, P=P, HKV=HKV, HQ=HQ, D=D, seed=sum(T))
+    qo = torch.tensor([0, *torch.tensor(T).cumsum(0).tolist()], dtype=torch.int32)
+    q = torch.randn((sum(T), HQ, D), generator=g).to(torch.bfloat16)
+    ref = oattn.paged_prefill(q, cache, qo, indptr, indices, last, sm_scale=0.07)
+    out = torch.full_like(q, float("nan")).cuda()
+    q35.paged_attention_prefill(q.cuda(), cache.cuda(), qo.cuda(), indptr.cuda(), indices.cuda(), last.cuda(), out,
+                                sm_scale=0.07)
+    assert torch.isfinite(out).all()
+    assert_parity(out.cpu(), ref)
+
+
+def test_paged_prefill_writes_new_rows_then_decode_continues(q35):
+    """prefill with k_new / v_new: rows land at the new tokens' positions, other rows untouched, and a decode step
+    over the resulting cache matches the golden"""
+    hist, T, P = [40, 0], [50, 64], 64
+    g = torch.Generator().manual_seed(12)
+    ctxs = [h + t for h, t in zip(hist, T)]
+    _, cache, indptr, indices, last, _ = paged_case(ctxs, P=P, seed=5)
+    qo = torch.tensor([0, 50, 114], dtype=torch.int32)
+    q = torch.randn((114, 16, 256), generator=g).to(torch.bfloat16)
+    k_new = torch.randn((114, 2, 256), generator=g).to(torch.bfloat16)
+    v_new = torch.randn((114, 2, 256), generator=g).to(torch.bfloat16)
+    ref_cache = cache.clone()
+    for b in range(2):
+        for i in range(T[b]):
+            pos = hist[b] + i
+            page = int(indices[int(indptr[b]) + pos // P])
+            ref_cache[page, 0, pos % P] = k_new[int(qo[b]) + i]
+            ref_cache[page, 1, pos % P] = v_new[int(qo[b]) + i]
+    ref = oattn.paged_prefill(q, ref_cache, qo, indptr, indices, last)
+    gcache = cache.cuda()
+    out = q35.paged_attention_prefill(q.cuda(), gcache, qo.cuda(), indptr.cuda(), indices.cuda(), last.cuda(),
+                                      k_new=k_new.cuda(), v_new=v_new.cuda())
+    assert torch.equal(gcache.cpu().view(torch.int16), ref_cache.view(torch.int16))
+    assert_parity(out.cpu(), ref)
+    qd = torch.randn((2, 16, 256), generator=g).to(torch.bfloat16)
+    dec = q35.paged_attention_decode(qd.cuda(), gcache, indptr.cuda(), indices.cuda(), last.cuda())
+    assert_parity(dec.cpu(), oattn.paged_decode(qd, ref_cache, indptr, indices, last))

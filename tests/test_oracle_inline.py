@@ -146,3 +146,18 @@ def test_fp8_rowwise_gemm():
     out = codecs.fp8_gemm(x, q8, torch.ones(3), s)
     ref = x.double() @ codecs.dequant_fp8_rowwise(q8, s).double().T
     assert (out.double() - ref).abs().max() / ref.square().mean().sqrt() < 3e-2
+
+
+def test_paged_prefill_equals_decode_token_by_token():
+    """the prefill golden on T tokens = the decode golden applied to each token with the history it sees"""
+    g = torch.Generator().manual_seed(8)
+    P, hist, T = 8, 5, 7
+    q1, cache, indptr, indices, last = _paged_case(g, [hist + T], P=P)
+    q = torch.randn((T, 4, 16), generator=g).to(torch.bfloat16)
+    out = attention.paged_prefill(q, cache, torch.tensor([0, T], dtype=torch.int32), indptr, indices, last)
+    for i in range(T):
+        n = hist + i + 1
+        npg = (n + P - 1) // P
+        dec = attention.paged_decode(q[i:i + 1], cache, torch.tensor([0, npg], dtype=torch.int32), indices[:npg],
+                                     torch.tensor([n - (npg - 1) * P], dtype=torch.int32))
+        assert torch.equal(out[i].view(torch.int16), dec[0].view(torch.int16))
