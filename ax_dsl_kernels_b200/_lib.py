@@ -104,9 +104,10 @@ _ws_cache = {}
 _need_cache = {}
 
 
-def _workspace(device, nbytes):
-    """one growing scratch buffer per device, owned by the Python host (the library itself never allocates)"""
-    key = (device.type, device.index)
+def _workspace(device, nbytes, stream=0):
+    """one growing scratch buffer per (device, stream), owned by the Python host (the library itself never allocates);
+    roles running concurrently on different streams must not share scratch"""
+    key = (device.type, device.index, stream)
     buf = _ws_cache.get(key)
     if buf is None or buf.numel() < nbytes:
         buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
@@ -128,8 +129,10 @@ def run(role, stream=None, **tensors):
         need = _need_cache.get(sig)
         if need is None:
             need = _need_cache[sig] = workspace_bytes(role, **tensors)
+        if stream is None:
+            stream = torch.cuda.current_stream(dev).cuda_stream
         if need:
-            tensors = dict(tensors, workspace=_workspace(dev, need))
+            tensors = dict(tensors, workspace=_workspace(dev, need, stream))
     arr, _keep = _table(tensors)
     if stream is None:
         stream = torch.cuda.current_stream(dev).cuda_stream

@@ -87,6 +87,15 @@ static const RoleDef kRoles[] = {
     {"moe.pre",
      R"({"in":[["x1","bf16","[T,H]"],["ln2","f32","[H]"],["w_gate","u8|e4m3","[FS,H/2]|[FS,H]"],["s_gate","u8","[FS,H/32]"],["w_up","u8|e4m3","[FS,H/2]|[FS,H]"],["s_up","u8","[FS,H/32]"],["w_down","u8|e4m3","[H,FS/2]|[H,FS]"],["s_down","u8","[H,FS/32]"],["w_router","bf16","[NE,H]"],["w_shg","bf16","[H]"],["workspace","u8","[*]"]],"out":[["out","bf16","[T,H]"],["h2_out","bf16","[T,H]"],["logits_out","f32","[T,NE]"]]})",
      run_moe_pre},
+    {"moe.norm_router",
+     R"({"in":[["x1","bf16","[T,H]"],["ln2","f32","[H]"],["w_router","bf16","[NE,H]"],["w_shg","bf16","[H]"]],"out":[["h2_out","bf16","[T,H]"],["logits_out","f32","[T,NE]"],["gate_out","f32","[T]"]]})",
+     run_moe_norm_router},
+    {"moe.shared",
+     R"({"in":[["x1","bf16","[T,H]"],["h2","bf16","[T,H]"],["gate","f32","[T]"],["w_gate","u8|e4m3","[FS,H/2]|[FS,H]"],["s_gate","u8","[FS,H/32]"],["w_up","u8|e4m3","[FS,H/2]|[FS,H]"],["s_up","u8","[FS,H/32]"],["w_down","u8|e4m3","[H,FS/2]|[H,FS]"],["s_down","u8","[H,FS/32]"],["workspace","u8","[*]"]],"out":[["out","bf16","[T,H]"]]})",
+     run_moe_shared},
+    {"moe.finish",
+     R"({"in":[["base","bf16","[T,H]"],["partial","f32","[T,H]"]],"out":[["out","bf16","[T,H]"]]})",
+     run_moe_finish},
     {"moe.experts",
      R"({"in":[["h2","bf16","[T,H]"],["base","bf16","[T,H]"],["ids","i32","[T,K]"],["rw","f32","[T,K]"],["e_gw","u8","[NE,2FE,H/2]"],["e_gs","u8","[NE,2FE,H/32]"],["e_dw","u8","[NE,H,FE/2]"],["e_ds","u8","[NE,H,FE/32]"],["workspace","u8","[*]"]],"out":[["out","bf16","[T,H]"],["partial_out","f32","[T,H] instead of base/out: sums of the pairs with ids >= 0"]]})",
      run_moe_experts},

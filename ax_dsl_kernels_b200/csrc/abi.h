@@ -75,6 +75,9 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 // launchers (one per role), defined next to their kernels
 int run_moe_route(Call&);
 int run_moe_pre(Call&);
+int run_moe_norm_router(Call&);
+int run_moe_shared(Call&);
+int run_moe_finish(Call&);
 int run_moe_experts(Call&);
 int run_moe_slots(Call&);
 int run_moe_combine(Call&);

@@ -363,57 +363,84 @@ static int weight_format(const Tensor& w, const Tensor& s, int64_t K, int* fmt) 
               (long long)inner, (long long)K);
 }
 
-int run_moe_pre(Call& c) {
-  Tensor x1, ln2, wg, sg, wu, su, wd, sd, wr, wshg, out, h2o, lgo, eps_t, ws;
+// mode 0: the whole dense part (moe.pre); 1: RMSNorm + router logits + shared-expert gate dot only (moe.norm_router);
+// 2: the shared expert on given h2 / gate (moe.shared).  Modes 1 and 2 let a host overlap the shared expert with the
+// routed experts on a second stream.
+static int moe_pre_impl(Call& c, int mode) {
+  const bool do_norm = mode != 2, do_shared = mode != 1;
+  Tensor x1, ln2, wg, sg, wu, su, wd, sd, wr, wshg, out, h2o, lgo, gate_t, ws;
   Q35_TRY(c.get("x1", M(Q35_BF16), &x1));
-  Q35_TRY(c.get("ln2", M(Q35_F32), &ln2));
-  Q35_TRY(c.get("w_gate", M_BYTES | M(Q35_E4M3), &wg));
-  Q35_TRY(c.get("s_gate", M(Q35_U8), &sg));
-  Q35_TRY(c.get("w_up", M_BYTES | M(Q35_E4M3), &wu));
-  Q35_TRY(c.get("s_up", M(Q35_U8), &su));
-  Q35_TRY(c.get("w_down", M_BYTES | M(Q35_E4M3), &wd));
-  Q35_TRY(c.get("s_down", M(Q35_U8), &sd));
-  Q35_TRY(c.get("w_router", M(Q35_BF16), &wr));
-  Q35_TRY(c.get("w_shg", M(Q35_BF16), &wshg));
-  Q35_TRY(c.get("out", M(Q35_BF16), &out));
-  Q35_TRY(c.get("h2_out", M(Q35_BF16), &h2o));
-  Q35_TRY(c.get("logits_out", M(Q35_F32), &lgo));
-  Q35_TRY(c.get("eps", M(Q35_F32), &eps_t, false));
-  Q35_REQUIRE(x1.nd >= 2 && wr.nd == 2 && wg.nd == 2 && wd.nd == 2, Q35_ERR_SHAPE, "moe.pre: ranks");
-  const int64_t H = x1.s[x1.nd - 1], T = x1.numel() / H, NE = wr.s[0], FS = wg.s[0];
-  Q35_REQUIRE(ln2.numel() == H && wr.s[1] == H && wshg.numel() == H, Q35_ERR_SHAPE, "moe.pre: ln2 / w_router / w_shg");
-  Q35_REQUIRE(out.numel() == T * H && h2o.numel() == T * H && lgo.numel() == T * NE, Q35_ERR_SHAPE, "moe.pre: outputs");
-  Q35_REQUIRE(wu.s[0] == FS && wd.s[0] == H, Q35_ERR_SHAPE, "moe.pre: shared expert shapes");
-  int f1, f2, f3;
-  Q35_TRY(weight_format(wg, sg, H, &f1));
-  Q35_TRY(weight_format(wu, su, H, &f2));
-  Q35_TRY(weight_format(wd, sd, FS, &f3));
-  Q35_REQUIRE(f1 == f2 && f1 == f3 && f1 != W_FP8ROW, Q35_ERR_UNSUPPORTED, "moe.pre: shared expert must be MXFP4 or MXFP8");
-  Q35_REQUIRE(sg.numel() == FS * (H / 32) && su.numel() == FS * (H / 32) && sd.numel() == H * (FS / 32), Q35_ERR_SHAPE,
-              "moe.pre: scale shapes");
-  Q35_REQUIRE(H % 256 == 0 && FS % 256 == 0, Q35_ERR_UNSUPPORTED, "moe.pre: H and FS must be multiples of 256");
-  const bool use_tc = f1 == W_MXFP4 && tc_shapes_ok(H, FS);
+  Q35_REQUIRE(x1.nd >= 2, Q35_ERR_SHAPE, "moe.pre: x1 [T, H]");
+  const int64_t H = x1.s[x1.nd - 1], T = x1.numel() / H;
+  int64_t NE = 0, FS = 0;
+  int f1 = W_MXFP4;
+  if (do_norm) {
+    Q35_TRY(c.get("ln2", M(Q35_F32), &ln2));
+    Q35_TRY(c.get("w_router", M(Q35_BF16), &wr));
+    Q35_TRY(c.get("w_shg", M(Q35_BF16), &wshg));
+    Q35_TRY(c.get("h2_out", M(Q35_BF16), &h2o));
+    Q35_TRY(c.get("logits_out", M(Q35_F32), &lgo));
+    Q35_REQUIRE(wr.nd == 2, Q35_ERR_SHAPE, "moe.pre: w_router [NE, H]");
+    NE = wr.s[0];
+    Q35_REQUIRE(ln2.numel() == H && wr.s[1] == H && wshg.numel() == H, Q35_ERR_SHAPE, "moe.pre: ln2 / w_router / w_shg");
+    Q35_REQUIRE(h2o.numel() == T * H && lgo.numel() == T * NE, Q35_ERR_SHAPE, "moe.pre: h2_out / logits_out");
+  } else {
+    Q35_TRY(c.get("h2", M(Q35_BF16), &h2o));
+    Q35_REQUIRE(h2o.numel() == T * H, Q35_ERR_SHAPE, "moe.shared: h2 [T, H]");
+  }
+  if (mode != 0) {  // the gate dot products travel between the two halves as a tensor
+    Q35_TRY(c.get(mode == 1 ? "gate_out" : "gate", M(Q35_F32), &gate_t));
+    Q35_REQUIRE(gate_t.numel() == T, Q35_ERR_SHAPE, "moe.pre: gate [T]");
+  }
+  if (do_shared) {
+    Q35_TRY(c.get("w_gate", M_BYTES | M(Q35_E4M3), &wg));
+    Q35_TRY(c.get("s_gate", M(Q35_U8), &sg));
+    Q35_TRY(c.get("w_up", M_BYTES | M(Q35_E4M3), &wu));
+    Q35_TRY(c.get("s_up", M(Q35_U8), &su));
+    Q35_TRY(c.get("w_down", M_BYTES | M(Q35_E4M3), &wd));
+    Q35_TRY(c.get("s_down", M(Q35_U8), &sd));
+    Q35_TRY(c.get("out", M(Q35_BF16), &out));
+    Q35_REQUIRE(wg.nd == 2 && wd.nd == 2, Q35_ERR_SHAPE, "moe.pre: shared expert ranks");
+    FS = wg.s[0];
+    Q35_REQUIRE(out.numel() == T * H && wu.s[0] == FS && wd.s[0] == H, Q35_ERR_SHAPE, "moe.pre: shared expert shapes");
+    int f2, f3;
+    Q35_TRY(weight_format(wg, sg, H, &f1));
+    Q35_TRY(weight_format(wu, su, H, &f2));
+    Q35_TRY(weight_format(wd, sd, FS, &f3));
+    Q35_REQUIRE(f1 == f2 && f1 == f3 && f1 != W_FP8ROW, Q35_ERR_UNSUPPORTED,
+                "moe.pre: shared expert must be MXFP4 or MXFP8");
+    Q35_REQUIRE(sg.numel() == FS * (H / 32) && su.numel() == FS * (H / 32) && sd.numel() == H * (FS / 32),
+                Q35_ERR_SHAPE, "moe.pre: scale shapes");
+    Q35_REQUIRE(FS % 256 == 0, Q35_ERR_UNSUPPORTED, "moe.pre: FS must be a multiple of 256");
+  }
+  Q35_REQUIRE(H % 256 == 0, Q35_ERR_UNSUPPORTED, "moe.pre: H must be a multiple of 256");
+  const bool use_tc = do_shared && f1 == W_MXFP4 && tc_shapes_ok(H, FS);
   WsCarver w{nullptr};
   __nv_bfloat16* act = w.take<__nv_bfloat16>(T * FS);
   float* gate = w.take<float>(T);
   uint8_t* qws = use_tc ? w.take<uint8_t>(tc_routed_bytes(T, H, FS)) : nullptr;
   Q35_TRY(c.workspace(w.off, &ws));
   if (c.dry || T == 0) return 0;
-  Q35_REQUIRE(aligned16(x1.p) && aligned16(out.p) && aligned16(h2o.p) && aligned16(wg.p) && aligned16(wu.p) &&
-                  aligned16(wd.p) && aligned16(wr.p) && aligned16(wshg.p),
+  Q35_REQUIRE(aligned16(x1.p) && aligned16(h2o.p) && (!do_shared || (aligned16(out.p) && aligned16(wg.p) &&
+                  aligned16(wu.p) && aligned16(wd.p))) && (!do_norm || (aligned16(wr.p) && aligned16(wshg.p))),
               Q35_ERR_ALIGN, "moe.pre: pointers must be 16-byte aligned");
   WsCarver wc{ws.as<uint8_t>()};
   act = wc.take<__nv_bfloat16>(T * FS);
   gate = wc.take<float>(T);
   qws = use_tc ? wc.take<uint8_t>(tc_routed_bytes(T, H, FS)) : nullptr;
-  // eps is a host-side constant of the model (1e-6 for every Qwen3.5 config); an `eps` tensor is not read on device
-  const float eps = 1e-6f;
-  rmsnorm_kernel<<<unsigned(T), 256, 0, c.stream>>>(x1.as<__nv_bfloat16>(), ln2.as<float>(), h2o.as<__nv_bfloat16>(),
-                                                    int(H), eps);
-  Q35_CUDA_LAUNCH_CHECK("moe.pre rmsnorm");
-  router_kernel<<<dim3(unsigned((NE + 1 + 7) / 8), unsigned(T)), 256, 0, c.stream>>>(
-      h2o.as<__nv_bfloat16>(), wr.as<__nv_bfloat16>(), wshg.as<__nv_bfloat16>(), lgo.as<float>(), gate, int(H), int(NE));
-  Q35_CUDA_LAUNCH_CHECK("moe.pre router");
+  if (mode != 0) gate = gate_t.as<float>();
+  if (do_norm) {
+    // eps is a constant of the model family (1e-6 for every Qwen3.5 config)
+    const float eps = 1e-6f;
+    rmsnorm_kernel<<<unsigned(T), 256, 0, c.stream>>>(x1.as<__nv_bfloat16>(), ln2.as<float>(),
+                                                      h2o.as<__nv_bfloat16>(), int(H), eps);
+    Q35_CUDA_LAUNCH_CHECK("moe.pre rmsnorm");
+    router_kernel<<<dim3(unsigned((NE + 1 + 7) / 8), unsigned(T)), 256, 0, c.stream>>>(
+        h2o.as<__nv_bfloat16>(), wr.as<__nv_bfloat16>(), wshg.as<__nv_bfloat16>(), lgo.as<float>(), gate, int(H),
+        int(NE));
+    Q35_CUDA_LAUNCH_CHECK("moe.pre router");
+  }
+  if (!do_shared) return 0;
   if (use_tc) {  // shared expert on the tensor cores: one dense group of T rows
     const TcQuant q1 = tc_quant_carve(qws, T, H);
     const TcQuant q2 = tc_quant_carve(qws + tc_quant_bytes(T, H), T, FS);
@@ -458,6 +485,41 @@ int run_moe_pre(Call& c) {
   }
   Q35_TRY((launch_skinny<W_MXFP8, EPI_SILU_MUL>(a, nt, int(FS / 64), 1, c.stream)));
   return launch_skinny<W_MXFP8, EPI_SHARED_DOWN>(d, nt, int((H + 127) / 128), 1, c.stream);
+}
+
+int run_moe_pre(Call& c) { return moe_pre_impl(c, 0); }
+int run_moe_norm_router(Call& c) { return moe_pre_impl(c, 1); }
+int run_moe_shared(Call& c) { return moe_pre_impl(c, 2); }
+
+// moe.finish: out = bf16(base + partial): closes the block when the routed experts were summed separately
+// (the fp32 accumulation `acc = base; acc += rw_i * d_i` of moe_experts, models/qwen35_2b/whole/src/q35_moe.py:73-85,
+// with the routed terms added first)
+__global__ void moe_finish_kernel(const __nv_bfloat16* __restrict__ base, const float* __restrict__ partial,
+                                  __nv_bfloat16* __restrict__ out, long long n) {
+  const long long i = (long long)(blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  if (i >= n) return;
+  const uint2 b = *reinterpret_cast<const uint2*>(base + i);
+  const float4 p = *reinterpret_cast<const float4*>(partial + i);
+  uint2 o;
+  o.x = pack_bf16(bf16lo(b.x) + p.x, bf16hi(b.x) + p.y);
+  o.y = pack_bf16(bf16lo(b.y) + p.z, bf16hi(b.y) + p.w);
+  *reinterpret_cast<uint2*>(out + i) = o;
+}
+
+int run_moe_finish(Call& c) {
+  Tensor base, partial, out;
+  Q35_TRY(c.get("base", M(Q35_BF16), &base));
+  Q35_TRY(c.get("partial", M(Q35_F32), &partial));
+  Q35_TRY(c.get("out", M(Q35_BF16), &out));
+  const int64_t n = base.numel();
+  Q35_REQUIRE(partial.numel() == n && out.numel() == n && n % 4 == 0, Q35_ERR_SHAPE, "moe.finish: base, partial, out [T, H]");
+  c.ws_need = 0;
+  if (c.dry || n == 0) return 0;
+  Q35_REQUIRE(aligned16(base.p) && aligned16(partial.p) && aligned16(out.p), Q35_ERR_ALIGN, "moe.finish: alignment");
+  moe_finish_kernel<<<unsigned((n / 4 + 255) / 256), 256, 0, c.stream>>>(base.as<__nv_bfloat16>(), partial.as<float>(),
+                                                                        out.as<__nv_bfloat16>(), n);
+  Q35_CUDA_LAUNCH_CHECK("moe.finish");
+  return 0;
 }
 
 // ---------------------------------------------------------------------------------------------------------------

@@ -77,19 +77,55 @@ def moe_permute(ids, rw, n_experts, G, S=None):
     return tok, srw, loc, n_slots, counts
 
 
-def moe_block(x1, w, top_k, out=None):
+_side_streams = {}
+_block_bufs = {}
+
+
+def _side_stream(dev):
+    key = (dev.type, dev.index)
+    if key not in _side_streams:
+        _side_streams[key] = torch.cuda.Stream(device=dev)
+    return _side_streams[key]
+
+
+def moe_block(x1, w, top_k, out=None, overlap=True):
     """whole block on T tokens: dense part -> router -> routed experts.  w: dict with ln2, w_gate, s_gate, w_up,
-    s_up, w_down, s_down, w_router, w_shg, e_gw, e_gs, e_dw, e_ds.  Returns (out, ids, rw, logits)."""
+    s_up, w_down, s_down, w_router, w_shg, e_gw, e_gs, e_dw, e_ds.  Returns (out, ids, rw, logits).
+    overlap=True runs the shared expert on a second stream while the main stream routes and runs the routed experts
+    (the two only meet in the final sum); overlap=False is the plain moe_pre -> route -> moe_experts sequence."""
     T, H = x1.shape
     dev = x1.device
-    base = torch.empty_like(x1)
-    h2 = torch.empty_like(x1)
-    logits = torch.empty((T, w["w_router"].shape[0]), dtype=torch.float32, device=dev)
-    moe_pre(x1, w["ln2"], w["w_gate"], w["s_gate"], w["w_up"], w["s_up"], w["w_down"], w["s_down"], w["w_router"],
-            w["w_shg"], base, h2, logits)
-    ids, rw = route(logits, top_k)
+    NE = w["w_router"].shape[0]
+    key = (dev.index, T, H, NE, top_k)
+    bufs = _block_bufs.get(key)
+    if bufs is None:
+        bufs = _block_bufs[key] = dict(
+            base=torch.empty_like(x1), h2=torch.empty_like(x1),
+            logits=torch.empty((T, NE), dtype=torch.float32, device=dev),
+            gate=torch.empty((T,), dtype=torch.float32, device=dev),
+            partial=torch.empty((T, H), dtype=torch.float32, device=dev),
+            ids=torch.empty((T, top_k), dtype=torch.int32, device=dev),
+            rw=torch.empty((T, top_k), dtype=torch.float32, device=dev))
+    base, h2, logits = bufs["base"], bufs["h2"], bufs["logits"]
     out = torch.empty_like(x1) if out is None else out
-    moe_experts(h2, base, ids, rw, w["e_gw"], w["e_gs"], w["e_dw"], w["e_ds"], out)
+    if not overlap:
+        moe_pre(x1, w["ln2"], w["w_gate"], w["s_gate"], w["w_up"], w["s_up"], w["w_down"], w["s_down"], w["w_router"],
+                w["w_shg"], base, h2, logits)
+        ids, rw = route(logits, top_k, bufs["ids"], bufs["rw"])
+        moe_experts(h2, base, ids, rw, w["e_gw"], w["e_gs"], w["e_dw"], w["e_ds"], out)
+        return out, ids, rw, logits
+    _lib.run("moe.norm_router", x1=x1, ln2=w["ln2"], w_router=w["w_router"], w_shg=w["w_shg"].reshape(-1), h2_out=h2,
+             logits_out=logits, gate_out=bufs["gate"])
+    main, side = torch.cuda.current_stream(dev), _side_stream(dev)
+    side.wait_stream(main)
+    with torch.cuda.stream(side):
+        _lib.run("moe.shared", x1=x1, h2=h2, gate=bufs["gate"], w_gate=w["w_gate"], s_gate=_u8(w["s_gate"]),
+                 w_up=w["w_up"], s_up=_u8(w["s_up"]), w_down=w["w_down"], s_down=_u8(w["s_down"]), out=base)
+    ids, rw = route(logits, top_k, bufs["ids"], bufs["rw"])
+    _lib.run("moe.experts", h2=h2, ids=ids, rw=rw, e_gw=_u8(w["e_gw"]), e_gs=_u8(w["e_gs"]), e_dw=_u8(w["e_dw"]),
+             e_ds=_u8(w["e_ds"]), partial_out=bufs["partial"])
+    main.wait_stream(side)
+    _lib.run("moe.finish", base=base, partial=bufs["partial"], out=out)
     return out, ids, rw, logits
 
 

@@ -206,7 +206,7 @@ def run_ours(args):
                        "0.27 GB state per step)"},
             "e2e": {"value": world * B * args.steps / (e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h},
-            "gpu_launches": args.steps * (14 if world == 1 else 16),
+            "gpu_launches": args.steps * (21 if world == 1 else 19),  # kernels of this library per step (torch and NCCL kernels not counted)
             "roofline": {"bound": "hbm", "kernel": "attn_decode_kernel<256,bf16> (+ plan and merge launches)",
                          "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_source": peak_src, "traffic": None, "algorithmic_bytes": wl.attn_bytes(),
