@@ -127,8 +127,24 @@ static const RoleDef kRoles[] = {
      R"({"in":[["q","bf16","[B,T,NK,128]"],["k","bf16","[B,T,NK,128]"],["v","bf16","[B,T,NV,128]"],["g","f32","[B,T,NV]"],["beta","bf16","[B,T,NV]"],["state_in","f32","[B,NV,128,128]"],["workspace","u8","[*]"]],"out":[["o","bf16","[B,T,NV,128]"],["state_out","f32","[B,NV,128,128]"]]})",
      run_gdn_chunk_prefill},
     {"linear",
-     R"({"in":[["x","bf16","[T,K]"],["w","u8|e4m3|bf16","[N,K/2]|[N,K]"],["s","u8|f32","[N,K/32]|[N] optional"],["bias","f32","[N] optional"]],"out":[["out","bf16|f32","[T,N]"]]})",
+     R"({"in":[["x","bf16","[T,K]"],["w","u8|e4m3|bf16","[N,K/2]|[N,K]"],["s","u8|f32","[N,K/32]|[N] optional"],["bias","f32","[N] optional"],["row_div","f32","[T] optional"],["residual","bf16","[T,N] optional"]],"out":[["out","bf16|f32","[T,N]"]]})",
      run_linear},
+    {"norm.rms",
+     R"({"in":[["x","bf16","[T,H]"],["residual","bf16","[T,H] optional"],["w","f32|bf16","[H]"],["eps","f32","[1] optional"]],"out":[["y","bf16","[T,H]"],["base_out","bf16","[T,H] optional"],["xsqrt_out","f32","[T] optional: folded form"]]})",
+     run_norm_rms},
+    {"gdn.prep",
+     R"({"in":[["q","bf16","[R,NK,DK]"],["k","bf16","[R,NK,DK]"],["a","bf16","[R,NV]"],["b","bf16","[R,NV]"],["a_log","f32","[NV]"],["dt_bias","f32|bf16","[NV]"]],"out":[["q_out","bf16","[R,NK,DK]"],["k_out","bf16","[R,NK,DK]"],["g","f32","[R,NV]"],["beta","bf16","[R,NV]"]]})",
+     run_gdn_prep},
+    {"gdn.out_norm",
+     R"({"in":[["core","bf16","[R,NV,DV]"],["z","bf16","[R,NV,DV]"],["w","f32|bf16","[DV]"],["eps","f32","[1] optional"]],"out":[["y","bf16","[R,NV,DV]"]]})",
+     run_gdn_out_norm},
+    {"attn.qk_prep",
+     R"({"in":[["qg","bf16","[R,HQ,D|2D]"],["k","bf16","[R,HKV,D]"],["q_norm","f32","[D]"],["k_norm","f32","[D]"],["cos","f32","[R,rot/2]"],["sin","f32","[R,rot/2]"],["eps","f32","[1] optional"]],"out":[["q_out","bf16","[R,HQ,D]"],["k_out","bf16","[R,HKV,D]"],["gate_out","bf16","[R,HQ,D] optional"]]})",
+     run_attn_qk_prep},
+    {"act.silu_mul",
+     R"({"in":[["a","bf16","[*]"],["b","bf16","[*]"]],"out":[["y","bf16","[*]"]]})", run_act_silu_mul},
+    {"act.sigmoid_gate",
+     R"({"in":[["a","bf16","[*]"],["b","bf16","[*]"]],"out":[["y","bf16","[*]"]]})", run_act_sigmoid_gate},
     {"linear.tc",
      R"({"in":[["x","bf16","[T,K]"],["w","u8","[N,K/2]"],["s","u8","[N,K/32]"],["bias","f32","[N] optional"],["workspace","u8","[*]"]],"out":[["out","bf16|f32","[T,N]"]]})",
      run_linear_tc},

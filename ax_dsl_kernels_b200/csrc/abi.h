@@ -89,6 +89,12 @@ int run_gdn_step(Call&);
 int run_gdn_conv(Call&);
 int run_gdn_chunk_prefill(Call&);
 int run_linear(Call&);
+int run_norm_rms(Call&);
+int run_gdn_prep(Call&);
+int run_gdn_out_norm(Call&);
+int run_attn_qk_prep(Call&);
+int run_act_silu_mul(Call&);
+int run_act_sigmoid_gate(Call&);
 int run_linear_tc(Call&);
 
 }  // namespace q35

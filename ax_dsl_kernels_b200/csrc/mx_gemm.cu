@@ -528,7 +528,9 @@ int run_moe_finish(Call& c) {
 // FP8 with per-row fp32 scales: fp8_gemm with scale_a = 1
 // (models/qwen35_35b_a3b/sgl/python/sgl_kernel_axera/gemm.py:123-153, 457-466).
 int run_linear(Call& c) {
-  Tensor x, w, s, bias, out;
+  Tensor x, w, s, bias, out, rdiv, resid;
+  Q35_TRY(c.get("row_div", M(Q35_F32), &rdiv, false));
+  Q35_TRY(c.get("residual", M(Q35_BF16), &resid, false));
   Q35_TRY(c.get("x", M(Q35_BF16), &x));
   Q35_TRY(c.get("w", M_BYTES | M(Q35_E4M3), &w));
   Q35_TRY(c.get("s", M(Q35_U8) | M(Q35_F32), &s));
@@ -541,6 +543,8 @@ int run_linear(Call& c) {
   Q35_REQUIRE(out.numel() == T * N, Q35_ERR_SHAPE, "linear: out must be [T, N]");
   Q35_REQUIRE(fmt == W_FP8ROW ? s.numel() == N : s.numel() == N * (K / 32), Q35_ERR_SHAPE, "linear: scale shape");
   Q35_REQUIRE(!bias.present || bias.numel() == N, Q35_ERR_SHAPE, "linear: bias [N]");
+  Q35_REQUIRE((!rdiv.present || rdiv.numel() == T) && (!resid.present || resid.numel() == T * N), Q35_ERR_SHAPE,
+              "linear: row_div [T], residual [T, N]");
   Q35_REQUIRE(K % 256 == 0, Q35_ERR_UNSUPPORTED, "linear: K must be a multiple of 256");
   c.ws_need = 0;
   if (c.dry || T == 0 || N == 0) return 0;
@@ -555,6 +559,8 @@ int run_linear(Call& c) {
   if (out.dtype == Q35_F32) d.f_out = out.as<float>(); else d.b_out = out.as<__nv_bfloat16>();
   d.out_stride = int(N);
   d.bias = bias.present ? bias.as<float>() : nullptr;
+  d.row_div = rdiv.present ? rdiv.as<float>() : nullptr;
+  d.resid2 = resid.present ? resid.as<__nv_bfloat16>() : nullptr;
   const int nt = pick_nt(T), tiles = int((N + 127) / 128);
   if (fmt == W_MXFP4) return launch_skinny<W_MXFP4, EPI_PLAIN>(d, nt, tiles, 1, c.stream);
   if (fmt == W_MXFP8) return launch_skinny<W_MXFP8, EPI_PLAIN>(d, nt, tiles, 1, c.stream);

@@ -40,6 +40,8 @@ struct SkinnyArgs {
   const __nv_bfloat16* resid;  // EPI_SHARED_DOWN: residual [T, out_stride]
   const float* gate;       // EPI_SHARED_DOWN: pre-sigmoid gate per token
   const float* bias;       // EPI_PLAIN: optional per-row bias
+  const float* row_div;    // EPI_PLAIN: optional per-token divisor applied to the bf16-rounded product (folded RMSNorm)
+  const __nv_bfloat16* resid2;  // EPI_PLAIN: optional residual [T, out_stride] added to the bf16-rounded product
   int* status;
 };
 
@@ -283,6 +285,8 @@ __global__ void __launch_bounds__(128) skinny_gemm_kernel(const SkinnyArgs a) {
               a.b_out[(long long)dst * a.out_stride + row] = __float2bfloat16_rn(res + v * sig);
             } else {
               if (a.bias) v += a.bias[row];
+              if (a.row_div) v = round_bf16(v) / a.row_div[dst];
+              if (a.resid2) v = round_bf16(v) + __bfloat162float(a.resid2[(long long)dst * a.out_stride + row]);
               if (a.f_out) a.f_out[(long long)dst * a.out_stride + row] = v;
               else a.b_out[(long long)dst * a.out_stride + row] = __float2bfloat16_rn(v);
             }

@@ -129,7 +129,7 @@ def moe_block(x1, w, top_k, out=None, overlap=True):
     return out, ids, rw, logits
 
 
-def linear(x, w, s, out=None, bias=None, out_dtype=torch.bfloat16):
+def linear(x, w, s, out=None, bias=None, out_dtype=torch.bfloat16, row_div=None, residual=None):
     """x [T, K] bf16 times a quantised weight [N, K]: MXFP4 (uint8 [N, K/2] + E8M0 [N, K/32]), MXFP8 (e4m3 [N, K] +
     E8M0) or FP8 per-row (e4m3 [N, K] + fp32 [N]; fp8_gemm with scale_a = 1,
     models/qwen35_35b_a3b/sgl/python/sgl_kernel_axera/gemm.py:457-466)."""
@@ -138,5 +138,9 @@ def linear(x, w, s, out=None, bias=None, out_dtype=torch.bfloat16):
     kw = dict(x=x, w=w, s=s if s.dtype == torch.float32 else _u8(s), out=out)
     if bias is not None:
         kw["bias"] = bias
+    if row_div is not None:  # per-token divisor applied to the bf16-rounded product (folded RMSNorm of the GDN sublayer)
+        kw["row_div"] = row_div
+    if residual is not None:  # out = residual + bf16(product)
+        kw["residual"] = residual
     _lib.run("linear", **kw)
     return out

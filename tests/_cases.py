@@ -65,3 +65,45 @@ def gdn_step_case(B=64, NK=16, NV=32, D=128, seed=2):
     gg = -torch.nn.functional.softplus(torch.randn((B, 1, NV), generator=g))
     state = torch.randn((B, NV, D, D), generator=g) * 0.03
     return q, k, v, gg, beta, state
+
+
+def stack_case(kinds, H=512, F=1024, heads=4, kv_heads=1, head_dim=128, NK=2, NV=4, DV=128, seed=0, gated=True):
+    """weights of a hybrid stack in the configuration-1 style: projections N(0, 0.02) quantised to FP8 E4M3 with
+    per-row fp32 scales, norms 1 + N(0, 0.02), A_log = log U(1, 16), conv taps N(0, 0.1)
+    (value distributions of models/qwen35_2b/whole/src/q35_step.py:313-321).
+    Returns (kernel weights: quantised pairs, oracle weights: dequantised fp32) per layer."""
+    g = torch.Generator().manual_seed(seed)
+    rn = lambda *s: torch.randn(s, generator=g)  # noqa: E731
+    kernel, golden = [], []
+
+    def quant(kw, ow, name, shape):
+        q8, sc = codecs.quant_fp8_rowwise(rn(*shape) * 0.02)
+        kw["w_" + name], kw["s_" + name] = q8, sc
+        ow["w_" + name] = codecs.dequant_fp8_rowwise(q8, sc)
+
+    KD, VD = NK * DV, NV * DV
+    for kind in kinds:
+        kw, ow = {}, {}
+        if kind == "g":
+            for name, shape in (("q", (KD, H)), ("k", (KD, H)), ("v", (VD, H)), ("z", (VD, H)), ("a", (NV, H)),
+                                ("b", (NV, H)), ("o", (H, VD))):
+                quant(kw, ow, name, shape)
+            for n, width in (("q", KD), ("k", KD), ("v", VD)):
+                kw[f"w_{n}_conv"] = ow[f"w_{n}_conv"] = (rn(width, 4) * 0.1).to(torch.bfloat16)
+            kw["input_norm_w"] = ow["input_norm_w"] = (1 + 0.02 * rn(H)).to(torch.bfloat16)
+            kw["a_log"] = ow["a_log"] = (torch.rand(NV, generator=g) * 15 + 1).log()
+            kw["dt_bias"] = ow["dt_bias"] = (rn(NV) * 0.02).to(torch.bfloat16)
+            kw["o_norm_w"] = ow["o_norm_w"] = (1 + 0.02 * rn(DV)).to(torch.bfloat16)
+        else:
+            for name, shape in (("q", (heads * head_dim * (2 if gated else 1), H)), ("k", (kv_heads * head_dim, H)),
+                                ("v", (kv_heads * head_dim, H)), ("o", (H, heads * head_dim))):
+                quant(kw, ow, name, shape)
+            kw["ln1"] = ow["ln1"] = 1 + 0.02 * rn(H)
+            kw["q_norm"] = ow["q_norm"] = 1 + 0.02 * rn(head_dim)
+            kw["k_norm"] = ow["k_norm"] = 1 + 0.02 * rn(head_dim)
+        for name, shape in (("gate", (F, H)), ("up", (F, H)), ("down", (H, F))):
+            quant(kw, ow, name, shape)
+        kw["ln2"] = ow["ln2"] = 1 + 0.02 * rn(H)
+        kernel.append(kw)
+        golden.append(ow)
+    return kernel, golden

@@ -1,0 +1,121 @@
+"""Sublayers and the hybrid stack (GDN / gated attention / dense SwiGLU with FP8 per-row weights) through the host
+layer functions against the CPU oracle stack, configuration-1 style at a reduced width."""
+import pytest
+import torch
+
+from conftest import assert_parity, rel_rms_err
+from oracle import attention as oattn, gdn as ogdn, stack as ostack
+from _cases import stack_case
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def q35():
+    assert torch.cuda.is_available()
+    import ax_dsl_kernels_b200 as m
+    yield m
+    assert m.device_status() == 0
+
+
+def to_dev(ws):
+    return [{k: v.cuda() for k, v in w.items()} for w in ws]
+
+
+def cosine(a, b):
+    return torch.nn.functional.cosine_similarity(a.flatten().double(), b.flatten().double(), dim=0).item()
+
+
+@pytest.mark.parametrize("T", [1, 70])
+def test_gdn_sublayer(q35, T):
+    kw, ow = stack_case("g", seed=3)
+    g = torch.Generator().manual_seed(T)
+    x = (torch.randn((1, T, 512), generator=g) * 0.5).to(torch.bfloat16)
+    res = (torch.randn((1, T, 512), generator=g) * 0.5).to(torch.bfloat16)
+    s0 = torch.randn((1, 4, 128, 128), generator=g) * 0.03
+    cq, ck, cv = ((torch.randn((1, 3, wd), generator=g) * 0.03).to(torch.bfloat16) for wd in (256, 256, 512))
+    ref, s_ref, c_ref = ogdn.gdn_sublayer(x, res, ow[0], s0, torch.cat((cq, ck, cv), -1))
+    fused, s1, conv = q35.layers.gdn(x.cuda(), res.cuda(), to_dev(kw)[0], s0.cuda(), (cq.cuda(), ck.cuda(), cv.cuda()))
+    # the new conv-state rows are projection outputs: equal up to a bf16 rounding step
+    assert_parity(torch.cat([c.cpu() for c in conv], -1), c_ref)
+    assert rel_rms_err(fused.cpu(), ref) <= (2e-2 if T == 1 else 5e-2)
+    torch.testing.assert_close(s1.cpu(), s_ref, rtol=0, atol=4e-3)
+
+
+def test_dense_mlp(q35):
+    kw, ow = stack_case("a", seed=5)
+    g = torch.Generator().manual_seed(1)
+    x1 = torch.randn((9, 512), generator=g).to(torch.bfloat16)
+    ref = ostack.dense_mlp(x1, ow[0]["ln2"], ow[0]["w_gate"], ow[0]["w_up"], ow[0]["w_down"])
+    out = q35.layers.mlp_residual(x1.cuda(), to_dev(kw)[0])
+    assert_parity(out.cpu(), ref)
+
+
+def test_attention_sublayer_decode_and_prefill(q35):
+    kw, ow = stack_case("a", seed=7)
+    cfg = dict(heads=4, kv_heads=1, head_dim=128)
+    g = torch.Generator().manual_seed(2)
+    P, T = 64, 90
+    cache = torch.zeros((4, 2, P, 1, 128), dtype=torch.bfloat16)
+    gcache = cache.cuda()
+    indices = torch.tensor([2, 0, 3, 1], dtype=torch.int32)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32)  # noqa: E731
+    x = (torch.randn((T, 512), generator=g) * 0.5).to(torch.bfloat16)
+    cos, sin = oattn.rope_cos_sin(torch.arange(T), 32, 1e7)
+    ref = ostack.attn_sublayer(x, ow[0], cache, i32([0, 2]), indices, i32([T - P]), cos, sin, rot=32, qo_indptr=i32([0, T]),
+                               **cfg)
+    dw = to_dev(kw)[0]
+    out = q35.layers.attention(x.cuda(), dw, cos.cuda(), sin.cuda(), gcache, i32([0, 2]).cuda(), indices.cuda(),
+                               i32([T - P]).cuda(), qo_indptr=i32([0, T]).cuda(), **cfg)
+    assert_parity(out.cpu(), ref)
+    assert rel_rms_err(gcache.cpu(), cache) <= 2e-2
+    # one decode token on top of the prefilled cache
+    xd = (torch.randn((1, 512), generator=g) * 0.5).to(torch.bfloat16)
+    cosd, sind = oattn.rope_cos_sin(torch.tensor([T]), 32, 1e7)
+    loc = i32([[int(indices[T // P]), T % P]])
+    refd = ostack.attn_sublayer(xd, ow[0], cache, i32([0, T // P + 1]), indices, i32([T % P]), cosd, sind, rot=32,
+                                cache_location=loc, **cfg)
+    outd = q35.layers.attention(xd.cuda(), dw, cosd.cuda(), sind.cuda(), gcache, i32([0, T // P + 1]).cuda(),
+                                indices.cuda(), i32([T % P]).cuda(), cache_location=loc.cuda(), **cfg)
+    assert_parity(outd.cpu(), refd)
+
+
+def test_hybrid_stack_prefill_then_decode(q35):
+    """g g g a stack: prefill of 70 tokens, then 3 decode steps; per-step outputs against the CPU oracle stack
+    (the reference's gate for stacks is a cosine on the hidden states, models/qwen35_2b/whole/src/q35_step.py:533)"""
+    kinds = "ggga"
+    kw, ow = stack_case(kinds, seed=11)
+    cfg = dict(heads=4, kv_heads=1, head_dim=128, rot=32, theta=1e7, page_size=64, max_tokens=256)
+    ref_stack = ostack.HybridStack(ow, kinds, **cfg)
+    gpu_stack = q35.layers.HybridStack(to_dev(kw), kinds, **cfg)
+    g = torch.Generator().manual_seed(4)
+    x = (torch.randn((70, 512), generator=g) * 0.05).to(torch.bfloat16)
+    ref = ref_stack.forward(x)
+    out = gpu_stack.forward(x.cuda())
+    assert cosine(out.cpu().float(), ref.float()) >= 0.999
+    assert rel_rms_err(out.cpu(), ref) <= 0.1
+    for step in range(3):
+        xd = (torch.randn((1, 512), generator=g) * 0.05).to(torch.bfloat16)
+        ref, out = ref_stack.forward(xd), gpu_stack.forward(xd.cuda())
+        assert cosine(out.cpu().float(), ref.float()) >= 0.999, step
+    assert gpu_stack.pos == ref_stack.pos == 73
+
+
+def test_configuration1_stack_full_shape(q35):
+    """Configuration 1: hidden 2048, 8 layers (3 GDN : 1 gated attention), 16 q / 2 kv heads of 256, RoPE theta 1e7 on
+    64 channels, GDN 16 key / 16 value heads of 128, FFN 6144, FP8 E4M3 per-row weights N(0, 0.02), batch 1,
+    512-token prefill then 64 decode steps, seed 0."""
+    kinds = "gggaggga"
+    kw, ow = stack_case(kinds, H=2048, F=6144, heads=16, kv_heads=2, head_dim=256, NK=16, NV=16, DV=128, seed=0)
+    cfg = dict(heads=16, kv_heads=2, head_dim=256, rot=64, theta=1e7, page_size=64, max_tokens=640)
+    ref_stack = ostack.HybridStack(ow, kinds, **cfg)
+    gpu_stack = q35.layers.HybridStack(to_dev(kw), kinds, **cfg)
+    g = torch.Generator().manual_seed(0)
+    emb = (torch.randn((576, 2048), generator=g) * 0.05).to(torch.bfloat16)
+    ref, out = ref_stack.forward(emb[:512]), gpu_stack.forward(emb[:512].cuda())
+    assert cosine(out.cpu().float(), ref.float()) >= 0.999
+    worst = 1.0
+    for t in range(512, 576):
+        ref, out = ref_stack.forward(emb[t:t + 1]), gpu_stack.forward(emb[t:t + 1].cuda())
+        worst = min(worst, cosine(out.cpu().float(), ref.float()))
+    assert worst >= 0.999, worst
