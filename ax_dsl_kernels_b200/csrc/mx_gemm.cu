@@ -59,14 +59,14 @@ static int64_t tc_routed_bytes(int64_t R, int64_t H, int64_t FE, int64_t groups 
   return tc_quant_bytes(R, H) + tc_quant_bytes(R, FE) + (groups + 1) * 4 + 256;
 }
 
-static int tc_routed(const ExpertPlanes& e, const __nv_bfloat16* x, const int* src, int R, int groups,
+static int tc_routed(const ExpertPlanes& e, const __nv_bfloat16* x, int x_rows, const int* src, int R, int groups,
                      const int* g_expert, const int* g_n, const int* g_row0, int nb, __nv_bfloat16* act,
                      uint8_t* qws, float* f_out, __nv_bfloat16* b_out, const float* rw_row, cudaStream_t stream) {
   const TcQuant q1 = tc_quant_carve(qws, R, e.H);
   const TcQuant q2 = tc_quant_carve(qws + tc_quant_bytes(R, e.H), R, e.FE);
   int* active = reinterpret_cast<int*>(qws + (tc_quant_bytes(R, e.H) + tc_quant_bytes(R, e.FE) + 255) / 256 * 256);
   Q35_TRY(tc_build_active(g_n, groups, active, stream));
-  Q35_TRY(tc_quantize(x, int(e.H), src, R, int(e.H), q1, stream));
+  Q35_TRY(tc_quantize(x, int(e.H), src, x_rows, R, int(e.H), q1, stream));
   TcArgs a{};
   a.n_active = active; a.active = active + 1;
   a.g_expert = g_expert; a.g_n = g_n; a.g_row0 = g_row0; a.n_planes = int(e.NE);
@@ -77,7 +77,7 @@ static int tc_routed(const ExpertPlanes& e, const __nv_bfloat16* x, const int* s
   a.act_rows = int(e.FE); a.act_out = act;
   const TcWeights wg{{e.gw, e.gw}, {uint64_t(e.NE * 2 * e.FE), uint64_t(e.NE * 2 * e.FE)}};
   Q35_TRY(tc_launch<TC_EPI_SILU_MUL>(wg, q1, a, nb, int(e.FE / 64), groups, stream));
-  Q35_TRY(tc_quantize(act, int(e.FE), nullptr, R, int(e.FE), q2, stream));
+  Q35_TRY(tc_quantize(act, int(e.FE), nullptr, R, R, int(e.FE), q2, stream));
   TcArgs d{};
   d.n_active = active; d.active = active + 1;
   d.g_expert = g_expert; d.g_n = g_n; d.g_row0 = g_row0; d.n_planes = int(e.NE);
@@ -180,7 +180,7 @@ int run_moe_experts(Call& c) {
   Q35_CUDA_LAUNCH_CHECK("moe.experts rows");
   if (use_tc) {
     const ExpertPlanes ep{gw.as<uint8_t>(), gs.as<uint8_t>(), dw.as<uint8_t>(), ds.as<uint8_t>(), NE, FE, H};
-    Q35_TRY(tc_routed(ep, h2.as<__nv_bfloat16>(), src, int(P), int(NE), g_expert, g_n, g_row0,
+    Q35_TRY(tc_routed(ep, h2.as<__nv_bfloat16>(), int(T), src, int(P), int(NE), g_expert, g_n, g_row0,
                       int((P + NE - 1) / NE), act, qws, sout, nullptr, rw_row, c.stream));
     if (partial.present)
       return launch_partial_sum(loc, sout, partial.as<float>(), int(T), int(H), int(K), int(P), c.stream);
@@ -278,7 +278,7 @@ int run_moe_slots(Call& c) {
   Q35_CUDA_LAUNCH_CHECK("moe.slots groups");
   if (use_tc) {
     const ExpertPlanes ep{gw.as<uint8_t>(), gs.as<uint8_t>(), dw.as<uint8_t>(), ds.as<uint8_t>(), NE, FE, H};
-    return tc_routed(ep, h2.as<__nv_bfloat16>(), src, int(S * G), int(S), g_expert, g_n, g_row0, int(G), act, qws,
+    return tc_routed(ep, h2.as<__nv_bfloat16>(), int(T), src, int(S * G), int(S), g_expert, g_n, g_row0, int(G), act, qws,
                      out.dtype == Q35_F32 ? out.as<float>() : nullptr,
                      out.dtype == Q35_F32 ? nullptr : out.as<__nv_bfloat16>(), rw.as<float>(), c.stream);
   }
@@ -444,7 +444,7 @@ static int moe_pre_impl(Call& c, int mode) {
   if (use_tc) {  // shared expert on the tensor cores: one dense group of T rows
     const TcQuant q1 = tc_quant_carve(qws, T, H);
     const TcQuant q2 = tc_quant_carve(qws + tc_quant_bytes(T, H), T, FS);
-    Q35_TRY(tc_quantize(h2o.as<__nv_bfloat16>(), int(H), nullptr, int(T), int(H), q1, c.stream));
+    Q35_TRY(tc_quantize(h2o.as<__nv_bfloat16>(), int(H), nullptr, int(T), int(T), int(H), q1, c.stream));
     TcArgs ta{};
     ta.n_dense = int(T); ta.n_planes = 1; ta.K = int(H);
     ta.plane_rows[0] = ta.plane_rows[1] = int(FS);
@@ -453,7 +453,7 @@ static int moe_pre_impl(Call& c, int mode) {
     ta.act_rows = int(FS); ta.act_out = act;
     const TcWeights wgu{{wg.as<uint8_t>(), wu.as<uint8_t>()}, {uint64_t(FS), uint64_t(FS)}};
     Q35_TRY(tc_launch<TC_EPI_SILU_MUL>(wgu, q1, ta, int(T), int(FS / 64), 1, c.stream));
-    Q35_TRY(tc_quantize(act, int(FS), nullptr, int(T), int(FS), q2, c.stream));
+    Q35_TRY(tc_quantize(act, int(FS), nullptr, int(T), int(T), int(FS), q2, c.stream));
     TcArgs td{};
     td.n_dense = int(T); td.n_planes = 1; td.K = int(FS);
     td.plane_rows[0] = td.plane_rows[1] = int(H);

@@ -54,14 +54,18 @@ __device__ __forceinline__ int e8m0_for(float amax) {  // smallest e with amax *
 }
 
 __global__ void __launch_bounds__(256) tc_quant_kernel(const __nv_bfloat16* __restrict__ x, int x_stride,
-                                                       const int* __restrict__ src, int R, int K,
+                                                       const int* __restrict__ src, int x_rows, int R, int K,
                                                        uint8_t* __restrict__ qh, uint8_t* __restrict__ ql,
                                                        uint8_t* __restrict__ sh, uint8_t* __restrict__ sl) {
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   const int blocks_per_row = K / 32;
   if (warp >= R * blocks_per_row) return;
   const int row = warp / blocks_per_row, kb = warp % blocks_per_row;
-  const long long srow = src ? src[row] : row;
+  long long srow = row;
+  if (src) {  // rows past the filled part of a grouped list hold stale ids: read row 0 instead, nobody uses the result
+    srow = src[row];
+    if (srow < 0 || srow >= x_rows) srow = 0;
+  }
   const float v = __bfloat162float(x[srow * x_stride + kb * 32 + lane]);
   const int eh = e8m0_for(warp_max(fabsf(v)));
   const __nv_fp8_e4m3 h(v * exp2f(float(-eh)));
@@ -77,11 +81,11 @@ __global__ void __launch_bounds__(256) tc_quant_kernel(const __nv_bfloat16* __re
   }
 }
 
-int tc_quantize(const __nv_bfloat16* x, int x_stride, const int* src, int R, int K, const TcQuant& q,
+int tc_quantize(const __nv_bfloat16* x, int x_stride, const int* src, int x_rows, int R, int K, const TcQuant& q,
                 cudaStream_t stream) {
   const long long warps = (long long)R * (K / 32);
   if (warps == 0) return 0;
-  tc_quant_kernel<<<unsigned((warps + 7) / 8), 256, 0, stream>>>(x, x_stride, src, R, K, q.qh, q.ql, q.sh, q.sl);
+  tc_quant_kernel<<<unsigned((warps + 7) / 8), 256, 0, stream>>>(x, x_stride, src, x_rows, R, K, q.qh, q.ql, q.sh, q.sl);
   Q35_CUDA_LAUNCH_CHECK("tc quantize");
   return 0;
 }
@@ -158,7 +162,7 @@ static int launch_nb(const CUtensorMap& w0, const CUtensorMap& w1, const CUtenso
   const long long items = (long long)tiles * (a.g_n ? groups : (a.n_dense + TC_DENSE_ROWS - 1) / TC_DENSE_ROWS);
   const long long slots = (long long)tc_sm_count() * TcCfg<NB>::CTAS_PER_SM;
   const unsigned grid = unsigned(items < slots ? items : slots);
-  tc_gemm_kernel<NB, EPI><<<grid, 256, smem, stream>>>(w0, w1, xh, xl, a);
+  tc_gemm_kernel<NB, EPI><<<grid, TcCfg<NB>::THREADS, smem, stream>>>(w0, w1, xh, xl, a);
   Q35_CUDA_LAUNCH_CHECK("tc gemm");
   return 0;
 }
@@ -166,6 +170,8 @@ static int launch_nb(const CUtensorMap& w0, const CUtensorMap& w1, const CUtenso
 template <int EPI>
 int tc_launch(const TcWeights& w, const TcQuant& q, TcArgs a, int nb, int tiles, int groups, cudaStream_t stream) {
   Q35_REQUIRE(a.K % 512 == 0 && a.K == q.K, Q35_ERR_UNSUPPORTED, "tc gemm: K must be a multiple of 512");
+  Q35_REQUIRE((uintptr_t(a.sw[0]) & 15) == 0 && (uintptr_t(a.sw[1]) & 15) == 0 && (a.s_plane & 15) == 0, Q35_ERR_ALIGN,
+              "tc gemm: scale tensors must be 16-byte aligned");
   CUtensorMap w0, w1, xh, xl;
   Q35_TRY(make_map(&w0, true, w.w[0], w.rows_total[0], a.K, a.K / 2, 64, "weights"));
   Q35_TRY(make_map(&w1, true, w.w[1], w.rows_total[1], a.K, a.K / 2, 64, "weights"));
@@ -205,7 +211,7 @@ int run_linear_tc(Call& c) {
   if (c.dry || T == 0 || N == 0) return 0;
   Q35_REQUIRE((uintptr_t(w.p) & 31) == 0 && aligned16(x.p) && aligned16(s.p), Q35_ERR_ALIGN, "linear.tc: alignment");
   const TcQuant q = tc_quant_carve(ws.as<uint8_t>(), T, K);
-  Q35_TRY(tc_quantize(x.as<__nv_bfloat16>(), int(K), nullptr, int(T), int(K), q, c.stream));
+  Q35_TRY(tc_quantize(x.as<__nv_bfloat16>(), int(K), nullptr, int(T), int(T), int(K), q, c.stream));
   TcWeights tw{{w.as<uint8_t>(), w.as<uint8_t>()}, {uint64_t(N), uint64_t(N)}};
   TcArgs a{};
   a.n_dense = int(T); a.n_planes = 1; a.K = int(K);

@@ -7,14 +7,17 @@
 // Why two terms: the reference multiplies bf16 activations by the dequantised weights (golden
 // models/qwen35_2b/whole/src/q35_moe.py:235-238); a single E4M3 term misses the 2e-2 tolerance by a factor 6.
 //
-// Work item = (group, 128-row weight tile, NB-token tile).  Persistent kernel, one CTA of 256 threads per SM, items
-// dealt round-robin over the compacted list of non-empty groups.  Warp-specialised and fully decoupled:
+// Work item = (group, 128-row weight tile, NB-token tile).  Persistent kernel (320 threads, two CTAs per SM for small
+// token tiles), items dealt round-robin over the compacted list of non-empty groups.  Warp-specialised and decoupled:
 //   warp 0    TMA producer: weight and activation tiles into a ring of stages (K = 128 per stage), running ahead
 //             across item boundaries;
 //   warp 1    owns tensor memory, copies the stage's scale blocks into TMEM (tcgen05.cp) and issues 4 MMAs of K = 32;
 //   warps 2-5 epilogue: tcgen05.ld of a finished accumulator while the next item accumulates into the other buffer;
-//   warps 6-7 gather the E8M0 scales of the NEXT item from global memory into the 32 x 16-byte blocks tcgen05.cp wants.
-// Accumulators [128 lanes x 2 NB columns] and the scale blocks are double-buffered; every hand-over is an mbarrier.
+//   warps 6-9 gather the E8M0 scales from global memory into the stage's two 32 x 16-byte blocks (the layout tcgen05.cp
+//             wants) and arrive on the same "full" barrier as the TMA bytes.
+// Accumulators [128 lanes x 2 NB columns] are double-buffered; every hand-over is an mbarrier.  A stage carries only
+// 8 KB of HBM bytes (the unpacked FP4 tile takes 16 KB of shared memory), so the ring is made as deep as shared memory
+// allows: HBM latency under load needs > 64 KB in flight per SM.
 #pragma once
 #include "tc_ptx.cuh"
 
@@ -50,24 +53,22 @@ struct TcCfg {
   static constexpr int N = 2 * NB;                         // MMA N: hi columns then lo columns
   static constexpr int A_BYTES = 128 * 128;                // 128 rows x 128 unpacked FP4 bytes
   static constexpr int B_BYTES = N * 128;
-  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int SF_BYTES = 1024;                    // scale blocks of the stage: weights (512 B), activations
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SF_BYTES;
   // bytes the TMA unit reports per stage: the FP4 loads count their PACKED source bytes (128 rows x 64 B), measured on
   // B200: with the unpacked size the barrier never completes
   static constexpr int STAGE_TX = 128 * 64 + B_BYTES;
-  // small token tiles: two CTAs per SM with short rings (the per-stage hand-over costs ~250 ns of a single issuing
-  // thread whatever the tile size, so two independent rings are needed to keep up with the SM's share of HBM)
   static constexpr int CTAS_PER_SM = NB <= 32 ? 2 : 1;
-  static constexpr int STAGES = NB <= 32 ? 3 : 5;
+  static constexpr int STAGES = NB <= 16 ? 5 : NB <= 32 ? 4 : 6;
+  static constexpr int THREADS = 320;
   static constexpr int TMEM_COLS = (2 * N + 8) <= 128 ? 128 : (2 * N + 8) <= 256 ? 256 : 512;
   static constexpr int SFA_COL = 2 * N, SFB_COL = 2 * N + 4;
   static constexpr int XCH_BYTES = 16 * 64 * 4;            // gate/up exchange of one 16-column chunk
-  static constexpr int smem_bytes(int K) {                 // + 1024 for manual alignment
-    return 1024 + STAGES * STAGE_BYTES + 2 * (K / 128) * 1024 + XCH_BYTES + 256;
+  static constexpr int smem_bytes(int) {                   // + 1024 for manual alignment
+    return 1024 + STAGES * STAGE_BYTES + XCH_BYTES + 256;
   }
 };
 
-// sub-item iteration shared by all roles: (active group, row tile) pairs dealt round-robin to the CTAs, and inside
-// a pair the token tiles of NB rows
 constexpr int TC_DENSE_ROWS = 256;
 
 struct TcItem {
@@ -93,7 +94,7 @@ __device__ __forceinline__ bool tc_get_item(const TcArgs& a, int j, TcItem* it) 
 }
 
 template <int NB, int EPI>
-__global__ void __launch_bounds__(256, TcCfg<NB>::CTAS_PER_SM) tc_gemm_kernel(const __grid_constant__ CUtensorMap wmap0,
+__global__ void __launch_bounds__(TcCfg<NB>::THREADS, TcCfg<NB>::CTAS_PER_SM) tc_gemm_kernel(const __grid_constant__ CUtensorMap wmap0,
                                                          const __grid_constant__ CUtensorMap wmap1,
                                                          const __grid_constant__ CUtensorMap xmap_hi,
                                                          const __grid_constant__ CUtensorMap xmap_lo, const TcArgs a) {
@@ -108,25 +109,21 @@ __global__ void __launch_bounds__(256, TcCfg<NB>::CTAS_PER_SM) tc_gemm_kernel(co
   const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* sgen = smem_raw + (sbase - smem_u32(smem_raw));
   const uint32_t s_stage = sbase;
-  const uint32_t s_atoms = sbase + C::STAGES * C::STAGE_BYTES;     // [2 buffers][A: KS x 512 | B: KS x 512]
-  const uint32_t s_xch = s_atoms + 2 * KS * 1024;
+  const uint32_t s_xch = sbase + C::STAGES * C::STAGE_BYTES;
   const uint32_t s_bar = s_xch + C::XCH_BYTES;
-  uint8_t* g_atoms = sgen + C::STAGES * C::STAGE_BYTES;
-  float* g_xch = reinterpret_cast<float*>(g_atoms + 2 * KS * 1024);
-  volatile uint32_t* g_slot = reinterpret_cast<volatile uint32_t*>(g_atoms + 2 * KS * 1024 + C::XCH_BYTES + 192);
+  float* g_xch = reinterpret_cast<float*>(sgen + C::STAGES * C::STAGE_BYTES);
+  volatile uint32_t* g_slot =
+      reinterpret_cast<volatile uint32_t*>(sgen + C::STAGES * C::STAGE_BYTES + C::XCH_BYTES + 192);
   const uint32_t s_slot = s_bar + 192;
   auto full_bar = [&](int s) { return s_bar + 8 * s; };            // [0, 64): up to 8 stages
   auto empty_bar = [&](int s) { return s_bar + 64 + 8 * s; };      // [64, 128)
-  auto sf_full = [&](int b) { return s_bar + 128 + 8 * b; };
-  auto sf_empty = [&](int b) { return s_bar + 144 + 8 * b; };
   auto acc_full = [&](int b) { return s_bar + 160 + 8 * b; };
   auto acc_empty = [&](int b) { return s_bar + 176 + 8 * b; };
 
   if (tid == 0) {
-    for (int s = 0; s < C::STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-    for (int b = 0; b < 2; ++b) {
-      mbar_init(sf_full(b), 1); mbar_init(sf_empty(b), 1); mbar_init(acc_full(b), 1); mbar_init(acc_empty(b), 1);
-    }
+    // a stage is full when the TMA bytes have landed AND the scale gatherers have arrived
+    for (int s = 0; s < C::STAGES; ++s) { mbar_init(full_bar(s), 2); mbar_init(empty_bar(s), 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(acc_full(b), 1); mbar_init(acc_empty(b), 1); }
     fence_barrier_init();
     tma_prefetch_desc(&wmap0); tma_prefetch_desc(&wmap1); tma_prefetch_desc(&xmap_hi); tma_prefetch_desc(&xmap_lo);
   }
@@ -170,21 +167,20 @@ __global__ void __launch_bounds__(256, TcCfg<NB>::CTAS_PER_SM) tc_gemm_kernel(co
         if (!tc_get_item(a, j, &im)) continue;
         for (int t0 = 0; t0 < im.n && !dead; t0 += NB, ++q) {
           const uint32_t b = q & 1, bph = (q >> 1) & 1;
-          if (!mbar_wait(sf_full(b), bph) || !mbar_wait(acc_empty(b), bph ^ 1)) {
+          if (!mbar_wait(acc_empty(b), bph ^ 1)) {
             atomicOr(a.status, DS_WAIT_TIMEOUT | 0x20);
             dead = true;
             break;
           }
           tc_fence_after();
           const uint32_t acc = tmem + b * C::N;
-          const uint32_t atomA = s_atoms + b * KS * 1024, atomB = atomA + KS * 512;
           for (int ks = 0; ks < KS; ++ks, ++it) {
             const uint32_t s = it % C::STAGES, ph = (it / C::STAGES) & 1;
             if (!mbar_wait(full_bar(s), ph)) { atomicOr(a.status, DS_WAIT_TIMEOUT | 0x40); dead = true; break; }
             tc_fence_after();
-            tc_cp_32x128b_warpx4(tmem + C::SFA_COL, smem_desc(atomA + ks * 512, 0, 128, 0));
-            tc_cp_32x128b_warpx4(tmem + C::SFB_COL, smem_desc(atomB + ks * 512, 0, 128, 0));
-            const uint32_t sa = s_stage + s * C::STAGE_BYTES, sb = sa + C::A_BYTES;
+            const uint32_t sa = s_stage + s * C::STAGE_BYTES, sb = sa + C::A_BYTES, ssf = sb + C::B_BYTES;
+            tc_cp_32x128b_warpx4(tmem + C::SFA_COL, smem_desc(ssf, 0, 128, 0));
+            tc_cp_32x128b_warpx4(tmem + C::SFB_COL, smem_desc(ssf + 512, 0, 128, 0));
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
               tc_mma_mxf8f6f4(acc, smem_desc(sa + k * 32, 16, 1024, 2), smem_desc(sb + k * 32, 16, 1024, 2),
@@ -193,82 +189,60 @@ __global__ void __launch_bounds__(256, TcCfg<NB>::CTAS_PER_SM) tc_gemm_kernel(co
             }
             tc_commit(empty_bar(s));
           }
-          tc_commit(sf_empty(b));
           tc_commit(acc_full(b));  // also after a failed wait: the epilogue must not be left waiting
         }
       }
     }
     __syncwarp();
   } else if (warp >= 6) {
-    // ---------------------------------------------------------------- scale gather (64 threads)
-    const int gt = tid - 192;
-    const int chunks = a.K / 32 / 16;  // 16-byte chunks per scale row: 16 k-blocks = 4 stages each
-    uint32_t q = 0;
+    // ---------------------------------------------------------------- scale gather (128 threads: one tile row each)
+    const int gt = tid - 192;           // row of the weight tile and column of the activation tile
+    const int srow = a.K / 32;          // scale bytes per row
+    uint32_t it = 0;
     bool dead = false;
     for (int j = blockIdx.x; j < n_items; j += gridDim.x) {
       TcItem im;
       if (!tc_get_item(a, j, &im)) continue;
-      const int rowh[2] = {im.tile * a.tile_rows + a.roff[0], im.tile * a.tile_rows + a.roff[1]};
-      for (int t0 = 0; t0 < im.n; t0 += NB, ++q) {
-        const uint32_t b = q & 1, bph = (q >> 1) & 1;
-        if (!dead && !mbar_wait(sf_empty(b), bph ^ 1)) {
-          if (gt == 0) atomicOr(a.status, DS_WAIT_TIMEOUT | 0x80);
-          dead = true;
-        }
-        uint32_t* atomA = reinterpret_cast<uint32_t*>(g_atoms + b * KS * 1024);
-        uint32_t* atomB = atomA + KS * 128;
-        // word (row r = r0 + 32 r1, stage ks) -> atom[ks][r0 * 4 + r1]: the 32 x 16-byte block that tcgen05.cp
-        // replicates over the four lane quadrants.  Loads are issued in batches of 8 per thread before any store, so
-        // one round trip to L2 / HBM covers the whole gather.
-        const uint4 ones = make_uint4(0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu);
-        for (int base = 0; base < 128 * chunks; base += 64 * 8) {
-          uint4 v[8];
+      const int hh = gt >> 6;
+      const int wrow = im.tile * a.tile_rows + a.roff[hh] + (gt & 63);
+      const uint8_t* wsc = wrow < a.lim[hh] ? a.sw[hh] + (long long)im.plane * a.s_plane + (long long)wrow * srow : nullptr;
+      for (int t0 = 0; t0 < im.n; t0 += NB) {
+        const int tcol = t0 + (gt < NB ? gt : gt - NB);
+        const long long xrow = im.row0 + tcol;
+        const uint8_t* xsc = (gt < C::N && tcol < im.n && xrow < a.total_rows)
+                                 ? (gt < NB ? a.sfh : a.sfl) + xrow * srow : nullptr;
+        for (int seg = 0; seg < KS; seg += 16) {  // 16 stages = 64 scale bytes of a row per round trip
+          uint32_t wa[16], wb[16];
 #pragma unroll
-          for (int u = 0; u < 8; ++u) {
-            const int idx = base + u * 64 + gt;
-            const int r = idx / chunks, ch = idx % chunks;
-            const int hh = (r >> 6) & 1;
-            const int row = rowh[hh] + (r & 63);
-            v[u] = ones;
-            if (idx < 128 * chunks && row < a.lim[hh])
-              v[u] = ldg_nc_16(a.sw[hh] + (long long)im.plane * a.s_plane + (long long)row * (a.K / 32) + ch * 16);
+          for (int u = 0; u < 4; ++u) {
+            uint4 va = make_uint4(0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu), vb = va;
+            if (seg + 4 * u < KS) {
+              if (wsc) va = ldg_nc_16(wsc + (seg + 4 * u) * 4);
+              if (xsc) vb = ldg_nc_16(xsc + (seg + 4 * u) * 4);
+            }
+            wa[4 * u] = va.x; wa[4 * u + 1] = va.y; wa[4 * u + 2] = va.z; wa[4 * u + 3] = va.w;
+            wb[4 * u] = vb.x; wb[4 * u + 1] = vb.y; wb[4 * u + 2] = vb.z; wb[4 * u + 3] = vb.w;
           }
 #pragma unroll
-          for (int u = 0; u < 8; ++u) {
-            const int idx = base + u * 64 + gt;
-            if (idx >= 128 * chunks) continue;
-            const int r = idx / chunks, ch = idx % chunks;
-            const int w = (r & 31) * 4 + (r >> 5);
-            atomA[(ch * 4 + 0) * 128 + w] = v[u].x; atomA[(ch * 4 + 1) * 128 + w] = v[u].y;
-            atomA[(ch * 4 + 2) * 128 + w] = v[u].z; atomA[(ch * 4 + 3) * 128 + w] = v[u].w;
-          }
-        }
-        // activation scales: columns [0, NB) = hi term, [NB, 2 NB) = lo term
-        for (int base = 0; base < C::N * chunks; base += 64 * 8) {
-          uint4 v[8];
-#pragma unroll
-          for (int u = 0; u < 8; ++u) {
-            const int idx = base + u * 64 + gt;
-            const int col = idx / chunks, ch = idx % chunks;
-            const int t = t0 + (col < NB ? col : col - NB);
-            const int row = im.row0 + t;
-            v[u] = ones;
-            if (idx < C::N * chunks && t < im.n && row < a.total_rows)
-              v[u] = ldg_nc_16((col < NB ? a.sfh : a.sfl) + (long long)row * (a.K / 32) + ch * 16);
-          }
-#pragma unroll
-          for (int u = 0; u < 8; ++u) {
-            const int idx = base + u * 64 + gt;
-            if (idx >= C::N * chunks) continue;
-            const int col = idx / chunks, ch = idx % chunks;
-            const int w = (col & 31) * 4 + (col >> 5);
-            atomB[(ch * 4 + 0) * 128 + w] = v[u].x; atomB[(ch * 4 + 1) * 128 + w] = v[u].y;
-            atomB[(ch * 4 + 2) * 128 + w] = v[u].z; atomB[(ch * 4 + 3) * 128 + w] = v[u].w;
+          for (int st = 0; st < 16; ++st) {
+            if (seg + st < KS) {
+              const uint32_t s = it % C::STAGES, ph = (it / C::STAGES) & 1;
+              if (!dead && !mbar_wait(empty_bar(s), ph ^ 1)) {
+                if (gt == 0) atomicOr(a.status, DS_WAIT_TIMEOUT | 0x80);
+                dead = true;
+              }
+              // word of row r = r0 + 32 r1 goes to [r0 * 4 + r1]: the 32 x 16-byte block tcgen05.cp replicates over
+              // the four lane quadrants
+              uint32_t* blk = reinterpret_cast<uint32_t*>(sgen + s * C::STAGE_BYTES + C::A_BYTES + C::B_BYTES);
+              blk[(gt & 31) * 4 + (gt >> 5)] = wa[st];
+              blk[128 + (gt & 31) * 4 + (gt >> 5)] = wb[st];
+              fence_proxy_async();
+              asm volatile("bar.sync 2, 128;" ::: "memory");
+              if (gt == 0) mbar_arrive(full_bar(s));
+              ++it;
+            }
           }
         }
-        fence_proxy_async();
-        asm volatile("bar.sync 2, 64;" ::: "memory");
-        if (gt == 0) mbar_arrive(sf_full(b));
       }
     }
   } else {

@@ -21,7 +21,8 @@ struct TcQuant {              // activations as two E4M3 terms + UE8M0 block-32 
 
 int64_t tc_quant_bytes(int64_t R, int64_t K);
 TcQuant tc_quant_carve(uint8_t* base, int64_t R, int64_t K);
-int tc_quantize(const __nv_bfloat16* x, int x_stride, const int* src, int R, int K, const TcQuant& q,
+// src (optional): row r of the result quantises x[src[r]]; ids outside [0, x_rows) read row 0
+int tc_quantize(const __nv_bfloat16* x, int x_stride, const int* src, int x_rows, int R, int K, const TcQuant& q,
                 cudaStream_t stream);
 
 // active[0] = number of groups with rows, active[1 ..] = their indices; `active` holds groups + 1 ints
