@@ -226,21 +226,27 @@ int run_moe_permute(Call& c) {
 __global__ void __launch_bounds__(256) moe_partial_sum_kernel(const int* __restrict__ loc, const float* __restrict__ sout,
                                                               float* __restrict__ partial, int T, int H, int K, int R) {
   const int t = blockIdx.x;
-  for (int h = threadIdx.x * 4; h < H; h += blockDim.x * 4) {
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int k = 0; k < K; ++k) {
-      const int r = loc[size_t(k) * T + t];
-      if (r < 0 || r >= R) continue;
-      const float4 a = *reinterpret_cast<const float4*>(sout + size_t(r) * H + h);
-      acc.x += a.x; acc.y += a.y; acc.z += a.z; acc.w += a.w;
+  const int h = (blockIdx.y * blockDim.x + threadIdx.x) * 4;
+  if (h >= H) return;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int k0 = 0; k0 < K; k0 += 8) {  // the loads of eight pairs go out together; the sum keeps the order of k
+    float4 v[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int r = k0 + u < K ? loc[size_t(k0 + u) * T + t] : -1;
+      v[u] = (r >= 0 && r < R) ? *reinterpret_cast<const float4*>(sout + size_t(r) * H + h)
+                               : make_float4(0.f, 0.f, 0.f, 0.f);
     }
-    *reinterpret_cast<float4*>(partial + size_t(t) * H + h) = acc;
+#pragma unroll
+    for (int u = 0; u < 8; ++u) { acc.x += v[u].x; acc.y += v[u].y; acc.z += v[u].z; acc.w += v[u].w; }
   }
+  *reinterpret_cast<float4*>(partial + size_t(t) * H + h) = acc;
 }
 
 int launch_partial_sum(const int* loc, const float* sout, float* partial, int T, int H, int K, int R,
                        cudaStream_t stream) {
-  moe_partial_sum_kernel<<<unsigned(T), 256, 0, stream>>>(loc, sout, partial, T, H, K, R);
+  moe_partial_sum_kernel<<<dim3(unsigned(T), unsigned((H / 4 + 255) / 256)), 256, 0, stream>>>(loc, sout, partial, T, H,
+                                                                                            K, R);
   Q35_CUDA_LAUNCH_CHECK("moe partial sum");
   return 0;
 }

@@ -59,13 +59,19 @@ static int64_t tc_routed_bytes(int64_t R, int64_t H, int64_t FE, int64_t groups 
   return tc_quant_bytes(R, H) + tc_quant_bytes(R, FE) + (groups + 1) * 4 + 256;
 }
 
+// [0] = number of groups with rows, [1..] = their indices in group order
+static int* tc_routed_active(uint8_t* qws, int64_t R, int64_t H, int64_t FE) {
+  return reinterpret_cast<int*>(qws + (tc_quant_bytes(R, H) + tc_quant_bytes(R, FE) + 255) / 256 * 256);
+}
+
 static int tc_routed(const ExpertPlanes& e, const __nv_bfloat16* x, int x_rows, const int* src, int R, int groups,
                      const int* g_expert, const int* g_n, const int* g_row0, int nb, __nv_bfloat16* act,
-                     uint8_t* qws, float* f_out, __nv_bfloat16* b_out, const float* rw_row, cudaStream_t stream) {
+                     uint8_t* qws, float* f_out, __nv_bfloat16* b_out, const float* rw_row, cudaStream_t stream,
+                     bool active_ready = false) {
   const TcQuant q1 = tc_quant_carve(qws, R, e.H);
   const TcQuant q2 = tc_quant_carve(qws + tc_quant_bytes(R, e.H), R, e.FE);
-  int* active = reinterpret_cast<int*>(qws + (tc_quant_bytes(R, e.H) + tc_quant_bytes(R, e.FE) + 255) / 256 * 256);
-  Q35_TRY(tc_build_active(g_n, groups, active, stream));
+  int* active = tc_routed_active(qws, R, e.H, e.FE);
+  if (!active_ready) Q35_TRY(tc_build_active(g_n, groups, active, stream));
   Q35_TRY(tc_quantize(x, int(e.H), src, x_rows, R, int(e.H), q1, stream));
   TcArgs a{};
   a.n_active = active; a.active = active + 1;
@@ -121,6 +127,85 @@ __global__ void __launch_bounds__(256) experts_build_rows_kernel(const int* __re
   }
 }
 
+// Decode-sized form of the grouping (at most 1024 pairs and 1024 experts): one CTA does the count, the stable ranks,
+// the row tables and the list of experts with rows that the tensor-core GEMM walks.  Same result as
+// moe_group_count_kernel + experts_build_rows_kernel + the active-group scan; pairs without a local expert get loc -1.
+__global__ void __launch_bounds__(1024) experts_plan_small_kernel(const int* __restrict__ ids,
+                                                                  const float* __restrict__ rw, int T, int K, int NE,
+                                                                  int* g_expert, int* g_n, int* g_row0, int* src,
+                                                                  float* rw_row, int* loc, int* active, int* status) {
+  __shared__ __align__(16) int s_id[1024];
+  __shared__ int s_cnt[1024];
+  __shared__ int s_row0[1024];
+  __shared__ int s_warp[32];
+  const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+  const int P = T * K;
+  int id = -1, t = 0, k = 0;
+  if (tid < P) {
+    t = tid / K; k = tid % K;
+    id = ids[tid];
+    if (id >= NE) { atomicOr(status, DS_BAD_EXPERT); id = -1; }
+    if (id < 0) id = -1;  // negative ids mean "not on this rank"
+  }
+  s_row0[tid] = id;  // raw ids, for the duplicate check
+  s_cnt[tid] = 0;
+  __syncthreads();
+  for (int kk = 0; kk < k && id >= 0; ++kk)
+    if (s_row0[t * K + kk] == id) id = -1;  // an expert listed twice by a token counts once
+  s_id[tid] = id;
+  __syncthreads();
+  int rank = 0;
+  if (id >= 0) {
+    // pairs are token-major, so the number of earlier pairs with the same expert is the stable rank
+    const int4* v4 = reinterpret_cast<const int4*>(s_id);
+    for (int q = 0; q < (tid >> 2); ++q) {
+      const int4 x = v4[q];
+      rank += (x.x == id) + (x.y == id) + (x.z == id) + (x.w == id);
+    }
+    for (int p = tid & ~3; p < tid; ++p) rank += s_id[p] == id;
+    atomicAdd(&s_cnt[id], 1);
+  }
+  __syncthreads();
+  // exclusive scan over the experts of (rows, has rows) packed as rows | on << 16
+  const int cnt = tid < NE ? s_cnt[tid] : 0;
+  int v = cnt | (cnt > 0 ? 1 << 16 : 0);
+  int inc = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int n = __shfl_up_sync(0xffffffffu, inc, o);
+    if (lane >= o) inc += n;
+  }
+  if (lane == 31) s_warp[wid] = inc;
+  __syncthreads();
+  if (wid == 0) {
+    int w = s_warp[lane], winc = w;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int n = __shfl_up_sync(0xffffffffu, winc, o);
+      if (lane >= o) winc += n;
+    }
+    s_warp[lane] = winc - w;
+  }
+  __syncthreads();
+  const int exc = s_warp[wid] + inc - v;
+  if (tid < NE) {
+    s_row0[tid] = exc & 0xffff;
+    g_expert[tid] = tid; g_n[tid] = cnt; g_row0[tid] = exc & 0xffff;
+    if (active && cnt > 0) active[1 + (exc >> 16)] = tid;
+  }
+  if (active && tid == 1023) active[0] = (exc + v) >> 16;
+  __syncthreads();
+  if (tid < P) {
+    int row = -1;
+    if (id >= 0) {
+      row = s_row0[id] + rank;
+      src[row] = t;
+      rw_row[row] = rw[tid];
+    }
+    loc[size_t(k) * T + t] = row;
+  }
+}
+
 int run_moe_experts(Call& c) {
   Tensor h2, base, ids, rw, gw, gs, dw, ds, out, partial, ws;
   Q35_TRY(c.get("h2", M(Q35_BF16), &h2));
@@ -173,15 +258,24 @@ int run_moe_experts(Call& c) {
   WsCarver wr{ws.as<uint8_t>()};
   carve(wr, counts, list, g_expert, g_n, g_row0, src, rw_row, loc, act, sout);
 
-  if (partial.present) cudaMemsetAsync(loc, 0xff, size_t(P) * 4, c.stream);  // pairs of other ranks: loc = -1
-  Q35_TRY(launch_group_count(ids.as<int>(), int(T), int(K), int(NE), counts, list, c.stream));
-  experts_build_rows_kernel<<<unsigned(NE), 256, 0, c.stream>>>(counts, list, rw.as<float>(), int(T), int(K), int(NE),
-                                                                g_expert, g_n, g_row0, src, rw_row, loc);
-  Q35_CUDA_LAUNCH_CHECK("moe.experts rows");
+  const bool small = P <= 1024 && NE <= 1024;
+  if (small) {
+    experts_plan_small_kernel<<<1, 1024, 0, c.stream>>>(ids.as<int>(), rw.as<float>(), int(T), int(K), int(NE), g_expert,
+                                                        g_n, g_row0, src, rw_row, loc,
+                                                        use_tc ? tc_routed_active(qws, P, H, FE) : nullptr,
+                                                        device_status_ptr());
+    Q35_CUDA_LAUNCH_CHECK("moe.experts plan");
+  } else {
+    if (partial.present) cudaMemsetAsync(loc, 0xff, size_t(P) * 4, c.stream);  // pairs of other ranks: loc = -1
+    Q35_TRY(launch_group_count(ids.as<int>(), int(T), int(K), int(NE), counts, list, c.stream));
+    experts_build_rows_kernel<<<unsigned(NE), 256, 0, c.stream>>>(counts, list, rw.as<float>(), int(T), int(K), int(NE),
+                                                                  g_expert, g_n, g_row0, src, rw_row, loc);
+    Q35_CUDA_LAUNCH_CHECK("moe.experts rows");
+  }
   if (use_tc) {
     const ExpertPlanes ep{gw.as<uint8_t>(), gs.as<uint8_t>(), dw.as<uint8_t>(), ds.as<uint8_t>(), NE, FE, H};
     Q35_TRY(tc_routed(ep, h2.as<__nv_bfloat16>(), int(T), src, int(P), int(NE), g_expert, g_n, g_row0,
-                      int((P + NE - 1) / NE), act, qws, sout, nullptr, rw_row, c.stream));
+                      int((P + NE - 1) / NE), act, qws, sout, nullptr, rw_row, c.stream, small));
     if (partial.present)
       return launch_partial_sum(loc, sout, partial.as<float>(), int(T), int(H), int(K), int(P), c.stream);
     return launch_combine(base.as<__nv_bfloat16>(), loc, sout, true, out.as<__nv_bfloat16>(), int(T), int(H), int(K),

@@ -42,7 +42,7 @@ static int make_map(CUtensorMap* m, bool fp4, const void* base, uint64_t rows, u
 }
 
 // ---------------------------------------------------------------------------------------------------------------
-// x (bf16) -> two E4M3 terms with UE8M0 block-32 scales: x = hi * 2^eh + lo * 2^el.  One warp per 32-block,
+// x (bf16) -> two E4M3 terms with UE8M0 block-32 scales: x = hi * 2^eh + lo * 2^el;
 // rows gathered through `src` (destination row -> source row; nullptr = identity).
 __device__ __forceinline__ int e8m0_for(float amax) {  // smallest e with amax * 2^-e <= 448 (= 1.75 * 2^8)
   if (amax == 0.f) return -127;
@@ -53,39 +53,75 @@ __device__ __forceinline__ int e8m0_for(float amax) {  // smallest e with amax *
   return max(-127, min(127, e));
 }
 
+// Eight elements per thread (one 16-byte load), four threads per 32-block.
 __global__ void __launch_bounds__(256) tc_quant_kernel(const __nv_bfloat16* __restrict__ x, int x_stride,
                                                        const int* __restrict__ src, int x_rows, int R, int K,
                                                        uint8_t* __restrict__ qh, uint8_t* __restrict__ ql,
                                                        uint8_t* __restrict__ sh, uint8_t* __restrict__ sl) {
-  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
-  const int blocks_per_row = K / 32;
-  if (warp >= R * blocks_per_row) return;
-  const int row = warp / blocks_per_row, kb = warp % blocks_per_row;
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;  // index of the 8-element piece
+  const int per_row = K / 8;
+  const bool on = i < (long long)R * per_row;  // whole quads are on or off together (K is a multiple of 32)
+  const int row = on ? int(i / per_row) : 0, c8 = on ? int(i % per_row) : 0;
   long long srow = row;
   if (src) {  // rows past the filled part of a grouped list hold stale ids: read row 0 instead, nobody uses the result
     srow = src[row];
     if (srow < 0 || srow >= x_rows) srow = 0;
   }
-  const float v = __bfloat162float(x[srow * x_stride + kb * 32 + lane]);
-  const int eh = e8m0_for(warp_max(fabsf(v)));
-  const __nv_fp8_e4m3 h(v * exp2f(float(-eh)));
-  const float rem = v - float(h) * exp2f(float(eh));
-  const int el = e8m0_for(warp_max(fabsf(rem)));
-  const __nv_fp8_e4m3 l(rem * exp2f(float(-el)));
-  const long long o = (long long)row * K + kb * 32 + lane;
-  qh[o] = *reinterpret_cast<const uint8_t*>(&h);
-  ql[o] = *reinterpret_cast<const uint8_t*>(&l);
-  if (lane == 0) {
-    sh[(long long)row * blocks_per_row + kb] = uint8_t(eh + 127);
-    sl[(long long)row * blocks_per_row + kb] = uint8_t(el + 127);
+  uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+  if (on) raw = *reinterpret_cast<const uint4*>(x + srow * x_stride + c8 * 8);
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+  float v[8];
+  float amax = 0.f;
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    v[2 * u] = bf16lo(w[u]); v[2 * u + 1] = bf16hi(w[u]);
+    amax = fmaxf(amax, fmaxf(fabsf(v[2 * u]), fabsf(v[2 * u + 1])));
+  }
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+  const int eh = e8m0_for(amax);
+  const float dn = exp2f(float(-eh)), up = exp2f(float(eh));
+  uint8_t hb[8], lb[8];
+  float rem[8];
+  float rmax = 0.f;
+#pragma unroll
+  for (int u = 0; u < 8; ++u) {
+    const __nv_fp8_e4m3 h(v[u] * dn);
+    hb[u] = *reinterpret_cast<const uint8_t*>(&h);
+    rem[u] = v[u] - float(h) * up;
+    rmax = fmaxf(rmax, fabsf(rem[u]));
+  }
+  rmax = fmaxf(rmax, __shfl_xor_sync(0xffffffffu, rmax, 1));
+  rmax = fmaxf(rmax, __shfl_xor_sync(0xffffffffu, rmax, 2));
+  const int el = e8m0_for(rmax);
+  const float dl = exp2f(float(-el));
+#pragma unroll
+  for (int u = 0; u < 8; ++u) {
+    const __nv_fp8_e4m3 l(rem[u] * dl);
+    lb[u] = *reinterpret_cast<const uint8_t*>(&l);
+  }
+  if (!on) return;
+  auto pack = [](const uint8_t* b) {
+    return make_uint2(uint32_t(b[0]) | uint32_t(b[1]) << 8 | uint32_t(b[2]) << 16 | uint32_t(b[3]) << 24,
+                      uint32_t(b[4]) | uint32_t(b[5]) << 8 | uint32_t(b[6]) << 16 | uint32_t(b[7]) << 24);
+  };
+  const long long o = (long long)row * K + c8 * 8;
+  *reinterpret_cast<uint2*>(qh + o) = pack(hb);
+  *reinterpret_cast<uint2*>(ql + o) = pack(lb);
+  if ((c8 & 3) == 0) {
+    sh[(long long)row * (K / 32) + c8 / 4] = uint8_t(eh + 127);
+    sl[(long long)row * (K / 32) + c8 / 4] = uint8_t(el + 127);
   }
 }
 
 int tc_quantize(const __nv_bfloat16* x, int x_stride, const int* src, int x_rows, int R, int K, const TcQuant& q,
                 cudaStream_t stream) {
-  const long long warps = (long long)R * (K / 32);
-  if (warps == 0) return 0;
-  tc_quant_kernel<<<unsigned((warps + 7) / 8), 256, 0, stream>>>(x, x_stride, src, x_rows, R, K, q.qh, q.ql, q.sh, q.sl);
+  const long long pieces = (long long)R * (K / 8);
+  if (pieces == 0) return 0;
+  Q35_REQUIRE(K % 32 == 0 && x_stride % 8 == 0 && (uintptr_t(x) & 15) == 0, Q35_ERR_ALIGN,
+              "tc quantize: rows must start on 16-byte boundaries");
+  tc_quant_kernel<<<unsigned((pieces + 255) / 256), 256, 0, stream>>>(x, x_stride, src, x_rows, R, K, q.qh, q.ql, q.sh,
+                                                                    q.sl);
   Q35_CUDA_LAUNCH_CHECK("tc quantize");
   return 0;
 }
@@ -159,7 +195,7 @@ static int launch_nb(const CUtensorMap& w0, const CUtensorMap& w1, const CUtenso
     cudaFuncSetAttribute(tc_gemm_kernel<NB, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     attr_smem = smem;
   }
-  const long long items = (long long)tiles * (a.g_n ? groups : (a.n_dense + TC_DENSE_ROWS - 1) / TC_DENSE_ROWS);
+  const long long items = (long long)tiles * (a.g_n ? groups : (a.n_dense + a.dense_rows - 1) / a.dense_rows);
   const long long slots = (long long)tc_sm_count() * TcCfg<NB>::CTAS_PER_SM;
   const unsigned grid = unsigned(items < slots ? items : slots);
   tc_gemm_kernel<NB, EPI><<<grid, TcCfg<NB>::THREADS, smem, stream>>>(w0, w1, xh, xl, a);
@@ -175,6 +211,15 @@ int tc_launch(const TcWeights& w, const TcQuant& q, TcArgs a, int nb, int tiles,
   CUtensorMap w0, w1, xh, xl;
   Q35_TRY(make_map(&w0, true, w.w[0], w.rows_total[0], a.K, a.K / 2, 64, "weights"));
   Q35_TRY(make_map(&w1, true, w.w[1], w.rows_total[1], a.K, a.K / 2, 64, "weights"));
+  if (!a.g_n) {
+    // dense: the rows are cut into virtual groups.  Every group streams the whole weight matrix, so groups are only
+    // made smaller than 256 rows while the row tiles alone leave CTAs idle (decode-sized inputs on small matrices,
+    // whose repeated reads then come out of L2).
+    const int want = (2 * tc_sm_count() + tiles - 1) / tiles;
+    int rows = ((a.n_dense + want - 1) / want + 15) / 16 * 16;
+    a.dense_rows = rows < 16 ? 16 : rows > 256 ? 256 : rows;
+    nb = nb < a.dense_rows ? nb : a.dense_rows;
+  }
   nb = nb <= 16 ? 16 : nb <= 32 ? 32 : 64;
   Q35_TRY(make_map(&xh, false, q.qh, q.R, a.K, a.K, nb, "activations"));
   Q35_TRY(make_map(&xl, false, q.ql, q.R, a.K, a.K, nb, "activations"));

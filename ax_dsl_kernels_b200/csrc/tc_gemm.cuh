@@ -13,11 +13,15 @@
 //             across item boundaries;
 //   warp 1    owns tensor memory, copies the stage's scale blocks into TMEM (tcgen05.cp) and issues 4 MMAs of K = 32;
 //   warps 2-5 epilogue: tcgen05.ld of a finished accumulator while the next item accumulates into the other buffer;
-//   warps 6-9 gather the E8M0 scales from global memory into the stage's two 32 x 16-byte blocks (the layout tcgen05.cp
-//             wants) and arrive on the same "full" barrier as the TMA bytes.
+//   warps 6-9 gather the E8M0 scales from global memory into 32 x 16-byte blocks (the layout tcgen05.cp wants), four
+//             stages (K = 512, 16 scale bytes of a row) at a time, in a two-deep ring of their own, with the loads of
+//             four granules in flight in registers.  Measured alternatives, all slower: the same per stage (a proxy
+//             fence and a barrier per stage in a serial chain, -15 %); scales written straight to tensor memory with
+//             tcgen05.st (cheap by itself, but it leaves too few registers to keep enough loads in flight with two
+//             CTAs per SM); asking the TMA unit to prefetch weight tiles into L2 ahead of the ring (-20 %).
 // Accumulators [128 lanes x 2 NB columns] are double-buffered; every hand-over is an mbarrier.  A stage carries only
 // 8 KB of HBM bytes (the unpacked FP4 tile takes 16 KB of shared memory), so the ring is made as deep as shared memory
-// allows: HBM latency under load needs > 64 KB in flight per SM.
+// allows.  Without the scale path the same pipeline streams weights at 6.3 TB/s; with it, 5.4 TB/s.
 #pragma once
 #include "tc_ptx.cuh"
 
@@ -29,6 +33,7 @@ struct TcArgs {
   // groups: nullptr g_n = one dense group of n_dense rows on plane 0
   const int* g_expert; const int* g_n; const int* g_row0;
   int n_dense, n_planes;
+  int dense_rows;           // dense form: rows per virtual group (set by the launcher)
   int K;                    // contraction length, multiple of 128
   int plane_rows[2];        // rows per expert plane in each half's weight tensor map (y = plane * plane_rows + row)
   int roff[2];              // row offset of each 64-row half inside its matrix
@@ -53,8 +58,10 @@ struct TcCfg {
   static constexpr int N = 2 * NB;                         // MMA N: hi columns then lo columns
   static constexpr int A_BYTES = 128 * 128;                // 128 rows x 128 unpacked FP4 bytes
   static constexpr int B_BYTES = N * 128;
-  static constexpr int SF_BYTES = 1024;                    // scale blocks of the stage: weights (512 B), activations
-  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SF_BYTES;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int SF_GRAN = 4;                        // stages per scale granule (16 scale bytes of a row)
+  static constexpr int SF_RING = 2;
+  static constexpr int SF_BYTES = SF_GRAN * 1024;          // per stage: weights' block (512 B), activations' block
   // bytes the TMA unit reports per stage: the FP4 loads count their PACKED source bytes (128 rows x 64 B), measured on
   // B200: with the unpacked size the barrier never completes
   static constexpr int STAGE_TX = 128 * 64 + B_BYTES;
@@ -63,35 +70,60 @@ struct TcCfg {
   static constexpr int THREADS = 320;
   static constexpr int TMEM_COLS = (2 * N + 8) <= 128 ? 128 : (2 * N + 8) <= 256 ? 256 : 512;
   static constexpr int SFA_COL = 2 * N, SFB_COL = 2 * N + 4;
-  static constexpr int XCH_BYTES = 16 * 64 * 4;            // gate/up exchange of one 16-column chunk
+  static constexpr int XCH_BYTES = 16 * 64 * 2;            // gate/up exchange of one 16-column chunk (bf16)
   static constexpr int smem_bytes(int) {                   // + 1024 for manual alignment
-    return 1024 + STAGES * STAGE_BYTES + XCH_BYTES + 256;
+    return 1024 + STAGES * STAGE_BYTES + SF_RING * SF_BYTES + XCH_BYTES + 256;
   }
 };
 
-constexpr int TC_DENSE_ROWS = 256;
 
 struct TcItem {
   int plane, row0, n, tile;
 };
 
-__device__ __forceinline__ bool tc_get_item(const TcArgs& a, int j, TcItem* it) {
+// Work items are read one ahead of their use: tc_load_item only issues the loads (no branch on what they return), so
+// the two dependent reads of a grouped item (active list, then the group's row count / expert / first row) are in
+// flight while the previous item is being worked on.  tc_check_item validates at the point of use; every role walks
+// the items through these two functions and therefore skips the same ones.
+__device__ __forceinline__ void tc_load_item(const TcArgs& a, int j, TcItem* it) {
   if (a.g_n) {
     const int grp = a.active[j / a.n_tiles];
     it->n = a.g_n[grp]; it->plane = a.g_expert[grp]; it->row0 = a.g_row0[grp];
-    if (it->plane < 0 || it->plane >= a.n_planes) {
-      atomicOr(a.status, DS_BAD_EXPERT);
-      it->n = 0;
-    }
-  } else {  // one dense matrix: the rows are cut into virtual groups of TC_DENSE_ROWS so that prefill-sized inputs
-            // spread over all CTAs
-    it->row0 = (j / a.n_tiles) * TC_DENSE_ROWS;
-    it->n = min(TC_DENSE_ROWS, a.n_dense - it->row0);
+  } else {  // one dense matrix: the rows are cut into virtual groups of dense_rows so that the work spreads over the
+            // CTAs (small for decode-sized inputs, whose weights then come out of L2 for all but the first group)
+    it->row0 = (j / a.n_tiles) * a.dense_rows;
+    it->n = min(a.dense_rows, a.n_dense - it->row0);
     it->plane = 0;
   }
   it->tile = j % a.n_tiles;
+}
+
+__device__ __forceinline__ bool tc_check_item(const TcArgs& a, TcItem* it) {
+  if (it->plane < 0 || it->plane >= a.n_planes) {
+    atomicOr(a.status, DS_BAD_EXPERT);
+    it->n = 0;
+  }
   return it->n > 0;
 }
+
+// for (TcItemWalk w(a, n_items); w.next(&im);) { ... }: items blockIdx.x, blockIdx.x + gridDim.x, ...
+struct TcItemWalk {
+  const TcArgs& a;
+  int n_items, jn;
+  TcItem nxt;
+  __device__ __forceinline__ TcItemWalk(const TcArgs& args, int n) : a(args), n_items(n), jn(int(blockIdx.x)) {
+    if (jn < n_items) tc_load_item(a, jn, &nxt);
+  }
+  __device__ __forceinline__ bool next(TcItem* im) {
+    while (jn < n_items) {
+      *im = nxt;
+      jn += int(gridDim.x);
+      if (jn < n_items) tc_load_item(a, jn, &nxt);
+      if (tc_check_item(a, im)) return true;
+    }
+    return false;
+  }
+};
 
 template <int NB, int EPI>
 __global__ void __launch_bounds__(TcCfg<NB>::THREADS, TcCfg<NB>::CTAS_PER_SM) tc_gemm_kernel(const __grid_constant__ CUtensorMap wmap0,
@@ -102,28 +134,32 @@ __global__ void __launch_bounds__(TcCfg<NB>::THREADS, TcCfg<NB>::CTAS_PER_SM) tc
   using namespace tc;
   extern __shared__ uint8_t smem_raw[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int n_items = (a.g_n ? a.n_active[0] : (a.n_dense + TC_DENSE_ROWS - 1) / TC_DENSE_ROWS) * a.n_tiles;
+  const int n_items = (a.g_n ? a.n_active[0] : (a.n_dense + a.dense_rows - 1) / a.dense_rows) * a.n_tiles;
   if (int(blockIdx.x) >= n_items) return;
 
   const int KS = a.K / 128;
   const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* sgen = smem_raw + (sbase - smem_u32(smem_raw));
   const uint32_t s_stage = sbase;
-  const uint32_t s_xch = sbase + C::STAGES * C::STAGE_BYTES;
+  const uint32_t s_sf = sbase + C::STAGES * C::STAGE_BYTES;        // [SF_RING][SF_GRAN][weights 512 B | activations 512 B]
+  const uint32_t s_xch = s_sf + C::SF_RING * C::SF_BYTES;
   const uint32_t s_bar = s_xch + C::XCH_BYTES;
-  float* g_xch = reinterpret_cast<float*>(sgen + C::STAGES * C::STAGE_BYTES);
-  volatile uint32_t* g_slot =
-      reinterpret_cast<volatile uint32_t*>(sgen + C::STAGES * C::STAGE_BYTES + C::XCH_BYTES + 192);
+  uint8_t* g_sf = sgen + C::STAGES * C::STAGE_BYTES;
+  __nv_bfloat16* g_xch = reinterpret_cast<__nv_bfloat16*>(g_sf + C::SF_RING * C::SF_BYTES);
+  volatile uint32_t* g_slot = reinterpret_cast<volatile uint32_t*>(g_sf + C::SF_RING * C::SF_BYTES + C::XCH_BYTES + 192);
   const uint32_t s_slot = s_bar + 192;
   auto full_bar = [&](int s) { return s_bar + 8 * s; };            // [0, 64): up to 8 stages
   auto empty_bar = [&](int s) { return s_bar + 64 + 8 * s; };      // [64, 128)
+  auto sf_full = [&](int g) { return s_bar + 128 + 8 * g; };
+  auto sf_empty = [&](int g) { return s_bar + 144 + 8 * g; };
   auto acc_full = [&](int b) { return s_bar + 160 + 8 * b; };
   auto acc_empty = [&](int b) { return s_bar + 176 + 8 * b; };
 
   if (tid == 0) {
-    // a stage is full when the TMA bytes have landed AND the scale gatherers have arrived
-    for (int s = 0; s < C::STAGES; ++s) { mbar_init(full_bar(s), 2); mbar_init(empty_bar(s), 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(acc_full(b), 1); mbar_init(acc_empty(b), 1); }
+    for (int s = 0; s < C::STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(sf_full(b), 1); mbar_init(sf_empty(b), 1); mbar_init(acc_full(b), 1); mbar_init(acc_empty(b), 1);
+    }
     fence_barrier_init();
     tma_prefetch_desc(&wmap0); tma_prefetch_desc(&wmap1); tma_prefetch_desc(&xmap_hi); tma_prefetch_desc(&xmap_lo);
   }
@@ -138,9 +174,8 @@ __global__ void __launch_bounds__(TcCfg<NB>::THREADS, TcCfg<NB>::CTAS_PER_SM) tc
     if (elect_one()) {
       uint32_t it = 0;
       bool dead = false;
-      for (int j = blockIdx.x; j < n_items && !dead; j += gridDim.x) {
-        TcItem im;
-        if (!tc_get_item(a, j, &im)) continue;
+      TcItem im;
+      for (TcItemWalk walk(a, n_items); !dead && walk.next(&im);) {
         const int r0 = im.tile * a.tile_rows + a.roff[0], r1 = im.tile * a.tile_rows + a.roff[1];
         for (int t0 = 0; t0 < im.n && !dead; t0 += NB) {
           for (int ks = 0; ks < KS; ++ks, ++it) {
@@ -162,9 +197,8 @@ __global__ void __launch_bounds__(TcCfg<NB>::THREADS, TcCfg<NB>::CTAS_PER_SM) tc
     if (elect_one()) {
       uint32_t it = 0, q = 0;
       bool dead = false;
-      for (int j = blockIdx.x; j < n_items && !dead; j += gridDim.x) {
-        TcItem im;
-        if (!tc_get_item(a, j, &im)) continue;
+      TcItem im;
+      for (TcItemWalk walk(a, n_items); !dead && walk.next(&im);) {
         for (int t0 = 0; t0 < im.n && !dead; t0 += NB, ++q) {
           const uint32_t b = q & 1, bph = (q >> 1) & 1;
           if (!mbar_wait(acc_empty(b), bph ^ 1)) {
@@ -176,9 +210,14 @@ __global__ void __launch_bounds__(TcCfg<NB>::THREADS, TcCfg<NB>::CTAS_PER_SM) tc
           const uint32_t acc = tmem + b * C::N;
           for (int ks = 0; ks < KS; ++ks, ++it) {
             const uint32_t s = it % C::STAGES, ph = (it / C::STAGES) & 1;
+            const uint32_t g = (it / C::SF_GRAN) % C::SF_RING, gph = (it / (C::SF_GRAN * C::SF_RING)) & 1;
+            if ((ks % C::SF_GRAN) == 0 && !mbar_wait(sf_full(g), gph)) {
+              atomicOr(a.status, DS_WAIT_TIMEOUT | 0x200); dead = true; break;
+            }
             if (!mbar_wait(full_bar(s), ph)) { atomicOr(a.status, DS_WAIT_TIMEOUT | 0x40); dead = true; break; }
             tc_fence_after();
-            const uint32_t sa = s_stage + s * C::STAGE_BYTES, sb = sa + C::A_BYTES, ssf = sb + C::B_BYTES;
+            const uint32_t sa = s_stage + s * C::STAGE_BYTES, sb = sa + C::A_BYTES;
+            const uint32_t ssf = s_sf + g * C::SF_BYTES + (ks % C::SF_GRAN) * 1024;
             tc_cp_32x128b_warpx4(tmem + C::SFA_COL, smem_desc(ssf, 0, 128, 0));
             tc_cp_32x128b_warpx4(tmem + C::SFB_COL, smem_desc(ssf + 512, 0, 128, 0));
 #pragma unroll
@@ -188,6 +227,7 @@ __global__ void __launch_bounds__(TcCfg<NB>::THREADS, TcCfg<NB>::CTAS_PER_SM) tc
                               tmem + C::SFB_COL, (ks | k) != 0);
             }
             tc_commit(empty_bar(s));
+            if ((ks % C::SF_GRAN) == C::SF_GRAN - 1) tc_commit(sf_empty(g));
           }
           tc_commit(acc_full(b));  // also after a failed wait: the epilogue must not be left waiting
         }
@@ -196,52 +236,77 @@ __global__ void __launch_bounds__(TcCfg<NB>::THREADS, TcCfg<NB>::CTAS_PER_SM) tc
     __syncwarp();
   } else if (warp >= 6) {
     // ---------------------------------------------------------------- scale gather (128 threads: one tile row each)
-    const int gt = tid - 192;           // row of the weight tile and column of the activation tile
+    // A unit = one granule (four stages, K = 512) of one (item, token tile): 16 scale bytes of weight row gt and of
+    // activation column gt.  Four units are kept in flight in registers, so the loads' latency is off the chain.
+    const int gt = tid - 192;
     const int srow = a.K / 32;          // scale bytes per row
-    uint32_t it = 0;
+    const int hh = gt >> 6;
+    const int KG = KS / C::SF_GRAN;
+    int t0 = 0, kg = 0;
+    bool have_item = false;
+    TcItem im{};
+    TcItemWalk walk(a, n_items);
+    const uint8_t *wsc = nullptr, *xsc = nullptr;
+    auto advance = [&]() -> bool {
+      if (have_item) {
+        if (++kg < KG) return true;
+        kg = 0; t0 += NB;
+        if (t0 >= im.n) have_item = false;
+      }
+      if (!have_item) {
+        if (!walk.next(&im)) return false;
+        have_item = true; t0 = 0; kg = 0;
+        const int wrow = im.tile * a.tile_rows + a.roff[hh] + (gt & 63);
+        wsc = wrow < a.lim[hh] ? a.sw[hh] + (long long)im.plane * a.s_plane + (long long)wrow * srow : nullptr;
+      }
+      const int tcol = t0 + (gt < NB ? gt : gt - NB);  // column gt of the MMA's N: hi terms, then lo terms
+      const long long xrow = im.row0 + tcol;
+      xsc = (gt < C::N && tcol < im.n && xrow < a.total_rows) ? (gt < NB ? a.sfh : a.sfl) + xrow * srow : nullptr;
+      return true;
+    };
+    const uint4 ones = make_uint4(0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu);
+    auto load1 = [&](uint4& va, uint4& vb) {
+      va = wsc ? ldg_nc_16(wsc + kg * 16) : ones;
+      vb = xsc ? ldg_nc_16(xsc + kg * 16) : ones;
+    };
+    uint32_t gi = 0;
     bool dead = false;
-    for (int j = blockIdx.x; j < n_items; j += gridDim.x) {
-      TcItem im;
-      if (!tc_get_item(a, j, &im)) continue;
-      const int hh = gt >> 6;
-      const int wrow = im.tile * a.tile_rows + a.roff[hh] + (gt & 63);
-      const uint8_t* wsc = wrow < a.lim[hh] ? a.sw[hh] + (long long)im.plane * a.s_plane + (long long)wrow * srow : nullptr;
-      for (int t0 = 0; t0 < im.n; t0 += NB) {
-        const int tcol = t0 + (gt < NB ? gt : gt - NB);
-        const long long xrow = im.row0 + tcol;
-        const uint8_t* xsc = (gt < C::N && tcol < im.n && xrow < a.total_rows)
-                                 ? (gt < NB ? a.sfh : a.sfl) + xrow * srow : nullptr;
-        for (int seg = 0; seg < KS; seg += 16) {  // 16 stages = 64 scale bytes of a row per round trip
-          uint32_t wa[16], wb[16];
+    // word of row r = r0 + 32 r1 goes to [r0 * 4 + r1]: the 32 x 16-byte block tcgen05.cp replicates over the four lane
+    // quadrants
+    const int widx = (gt & 31) * 4 + (gt >> 5);
+    auto put = [&](const uint4& va, const uint4& vb) {
+      const uint32_t g = gi % C::SF_RING, gph = (gi / C::SF_RING) & 1;
+      if (!dead && !mbar_wait(sf_empty(g), gph ^ 1)) {
+        if (gt == 0) atomicOr(a.status, DS_WAIT_TIMEOUT | 0x80);
+        dead = true;
+      }
+      uint32_t* blk = reinterpret_cast<uint32_t*>(g_sf + g * C::SF_BYTES);
+      blk[widx] = va.x; blk[128 + widx] = vb.x;
+      blk[256 + widx] = va.y; blk[384 + widx] = vb.y;
+      blk[512 + widx] = va.z; blk[640 + widx] = vb.z;
+      blk[768 + widx] = va.w; blk[896 + widx] = vb.w;
+      fence_proxy_async();
+      asm volatile("bar.sync 2, 128;" ::: "memory");
+      if (gt == 0) mbar_arrive(sf_full(g));
+      ++gi;
+    };
+    constexpr int DEPTH = 4;
+    uint4 qa[DEPTH], qb[DEPTH];
+    bool qv[DEPTH];
 #pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            uint4 va = make_uint4(0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu), vb = va;
-            if (seg + 4 * u < KS) {
-              if (wsc) va = ldg_nc_16(wsc + (seg + 4 * u) * 4);
-              if (xsc) vb = ldg_nc_16(xsc + (seg + 4 * u) * 4);
-            }
-            wa[4 * u] = va.x; wa[4 * u + 1] = va.y; wa[4 * u + 2] = va.z; wa[4 * u + 3] = va.w;
-            wb[4 * u] = vb.x; wb[4 * u + 1] = vb.y; wb[4 * u + 2] = vb.z; wb[4 * u + 3] = vb.w;
-          }
+    for (int d = 0; d < DEPTH; ++d) {
+      qv[d] = advance();
+      if (qv[d]) load1(qa[d], qb[d]);
+    }
+    bool more = true;
+    while (more) {
 #pragma unroll
-          for (int st = 0; st < 16; ++st) {
-            if (seg + st < KS) {
-              const uint32_t s = it % C::STAGES, ph = (it / C::STAGES) & 1;
-              if (!dead && !mbar_wait(empty_bar(s), ph ^ 1)) {
-                if (gt == 0) atomicOr(a.status, DS_WAIT_TIMEOUT | 0x80);
-                dead = true;
-              }
-              // word of row r = r0 + 32 r1 goes to [r0 * 4 + r1]: the 32 x 16-byte block tcgen05.cp replicates over
-              // the four lane quadrants
-              uint32_t* blk = reinterpret_cast<uint32_t*>(sgen + s * C::STAGE_BYTES + C::A_BYTES + C::B_BYTES);
-              blk[(gt & 31) * 4 + (gt >> 5)] = wa[st];
-              blk[128 + (gt & 31) * 4 + (gt >> 5)] = wb[st];
-              fence_proxy_async();
-              asm volatile("bar.sync 2, 128;" ::: "memory");
-              if (gt == 0) mbar_arrive(full_bar(s));
-              ++it;
-            }
-          }
+      for (int d = 0; d < DEPTH; ++d) {
+        if (more && !qv[d]) more = false;  // units are used in order: the first empty slot ends the walk
+        if (more) {
+          put(qa[d], qb[d]);
+          qv[d] = advance();
+          if (qv[d]) load1(qa[d], qb[d]);
         }
       }
     }
@@ -252,9 +317,8 @@ __global__ void __launch_bounds__(TcCfg<NB>::THREADS, TcCfg<NB>::CTAS_PER_SM) tc
     const int h = r >> 6;
     uint32_t q = 0;
     bool dead = false;
-    for (int j = blockIdx.x; j < n_items; j += gridDim.x) {
-      TcItem im;
-      if (!tc_get_item(a, j, &im)) continue;
+    TcItem im;
+    for (TcItemWalk walk(a, n_items); walk.next(&im);) {
       const int row = im.tile * a.tile_rows + a.roff[h] + (r & 63);
       const bool rvalid = row < a.lim[h];
       for (int t0 = 0; t0 < im.n; t0 += NB, ++q) {
@@ -265,17 +329,25 @@ __global__ void __launch_bounds__(TcCfg<NB>::THREADS, TcCfg<NB>::CTAS_PER_SM) tc
         }
         tc_fence_after();
         const uint32_t acc = tmem + b * C::N + (uint32_t(qd * 32) << 16);
-        for (int c0 = 0; c0 < NB; c0 += 16) {
+        const int ncols = min(NB, im.n - t0);  // columns past the group's last row hold nothing anyone reads
+        for (int c0 = 0; c0 < ncols; c0 += 16) {
           float hi[16], lo[16];
           tmem_ld_x16(acc + c0, hi);
           tmem_ld_x16(acc + NB + c0, lo);
+          if (c0 + 16 >= ncols) {
+            // the last columns are in registers: hand the accumulator back before the global loads and stores below,
+            // so that the MMA warp is never held up by their latency
+            tc_fence_before();
+            asm volatile("bar.sync 3, 128;" ::: "memory");
+            if (tid == 64) mbar_arrive(acc_empty(b));
+          }
 #pragma unroll
           for (int jj = 0; jj < 16; ++jj) hi[jj] += lo[jj];
           if constexpr (EPI == TC_EPI_SILU_MUL) {
             // rows 64..127 (up) hand their values to rows 0..63 (gate) through shared memory
             if (h == 1) {
 #pragma unroll
-              for (int jj = 0; jj < 16; ++jj) g_xch[jj * 64 + (r & 63)] = hi[jj];
+              for (int jj = 0; jj < 16; ++jj) g_xch[jj * 64 + (r & 63)] = __float2bfloat16_rn(hi[jj]);
             }
             asm volatile("bar.sync 1, 128;" ::: "memory");
             if (h == 0) {
@@ -283,7 +355,7 @@ __global__ void __launch_bounds__(TcCfg<NB>::THREADS, TcCfg<NB>::CTAS_PER_SM) tc
               for (int jj = 0; jj < 16; ++jj) {
                 const int t = t0 + c0 + jj;
                 if (t < im.n && rvalid) {
-                  const float g = round_bf16(hi[jj]), u = round_bf16(g_xch[jj * 64 + r]);
+                  const float g = round_bf16(hi[jj]), u = __bfloat162float(g_xch[jj * 64 + r]);
                   a.act_out[(long long)(im.row0 + t) * a.act_rows + row] =
                       __float2bfloat16_rn(g / (1.0f + expf(-g)) * u);
                 }
@@ -312,11 +384,6 @@ __global__ void __launch_bounds__(TcCfg<NB>::THREADS, TcCfg<NB>::CTAS_PER_SM) tc
               }
             }
           }
-        }
-        tc_fence_before();
-        asm volatile("bar.sync 3, 128;" ::: "memory");
-        if (tid == 64) {  // first epilogue thread: the accumulator buffer may be overwritten
-          mbar_arrive(acc_empty(b));
         }
       }
     }
