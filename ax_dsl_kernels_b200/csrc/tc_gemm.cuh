@@ -363,6 +363,27 @@ __global__ void __launch_bounds__(TcCfg<NB>::THREADS, TcCfg<NB>::CTAS_PER_SM) tc
             }
             asm volatile("bar.sync 1, 128;" ::: "memory");
           } else {
+            // every global load of the chunk goes out before the first store: the output may alias the residual, so
+            // the compiler cannot move a load above a store, and one round trip per column would be paid otherwise
+            float aux[16];
+            uint32_t res2[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};  // residual, two bf16 per register
+            const float bias = (EPI == TC_EPI_PLAIN && a.bias && rvalid) ? a.bias[row] : 0.f;
+#pragma unroll
+            for (int jj = 0; jj < 16; ++jj) {
+              const int t = t0 + c0 + jj;
+              const bool ok = t < im.n && rvalid;
+              const long long dst = im.row0 + t;
+              aux[jj] = 0.f;
+              if constexpr (EPI == TC_EPI_ROW_SCALE) {
+                if (ok) aux[jj] = a.rw_row[dst];
+              } else if constexpr (EPI == TC_EPI_SHARED_DOWN) {
+                if (ok) {
+                  aux[jj] = a.gate[dst];
+                  const uint32_t rb = *reinterpret_cast<const unsigned short*>(a.resid + dst * a.out_stride + row);
+                  res2[jj >> 1] |= rb << (16 * (jj & 1));
+                }
+              }
+            }
 #pragma unroll
             for (int jj = 0; jj < 16; ++jj) {
               const int t = t0 + c0 + jj;
@@ -370,15 +391,15 @@ __global__ void __launch_bounds__(TcCfg<NB>::THREADS, TcCfg<NB>::CTAS_PER_SM) tc
               const long long dst = im.row0 + t;
               float v = hi[jj];
               if constexpr (EPI == TC_EPI_ROW_SCALE) {
-                v *= a.rw_row[dst];
+                v *= aux[jj];
                 if (a.f_out) a.f_out[dst * a.out_stride + row] = v;
                 else a.b_out[dst * a.out_stride + row] = __float2bfloat16_rn(v);
               } else if constexpr (EPI == TC_EPI_SHARED_DOWN) {
-                const float sig = 1.0f / (1.0f + expf(-a.gate[dst]));
-                const float res = __bfloat162float(a.resid[dst * a.out_stride + row]);
+                const float sig = 1.0f / (1.0f + expf(-aux[jj]));
+                const float res = (jj & 1) ? bf16hi(res2[jj >> 1]) : bf16lo(res2[jj >> 1]);
                 a.b_out[dst * a.out_stride + row] = __float2bfloat16_rn(res + v * sig);
               } else {
-                if (a.bias) v += a.bias[row];
+                v += bias;
                 if (a.f_out) a.f_out[dst * a.out_stride + row] = v;
                 else a.b_out[dst * a.out_stride + row] = __float2bfloat16_rn(v);
               }

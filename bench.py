@@ -47,12 +47,12 @@ def workload_name():
 class Workload:
     """all tensors of one rank, generated on the device from a seed"""
 
-    def __init__(self, dev, seed, n_experts_local=NE):
+    def __init__(self, dev, seed, n_experts_local=NE, attn=True):
         g = torch.Generator(device=dev).manual_seed(seed)
         bf = torch.bfloat16
         rn = lambda *s: torch.randn(s, generator=g, device=dev)  # noqa: E731
         # paged attention: every sequence at CTX, page table a random permutation of the physical pages
-        n_pages = CTX // PAGE
+        n_pages = CTX // PAGE if attn else 1  # attn=False: profile cases of the other kernels keep the device small
         total = B * n_pages
         self.cache = torch.empty((total, 2, PAGE, HKV, D), dtype=bf, device=dev)
         for i in range(0, total, 2048):  # chunked: keeps the fp32 temporary small
@@ -320,24 +320,69 @@ def run_reference(args):
 
 
 def run_profile_case(name, reps):
-    """one kernel on a case sized for a profiler capture (inputs larger than L2, well under a few GB); prints nothing
-    that is a benchmark value"""
+    """one kernel on a case sized for a profiler capture (inputs larger than L2 where the kernel is memory-bound, well
+    under a few GB); prints the device time per repetition, which is not a benchmark value of the decode workload"""
     import ax_dsl_kernels_b200 as q35
     global B, CTX
-    if name == "attn":
-        B, CTX = 16, 8192  # 268 MB of bf16 KV
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(0)
-    wl = Workload(dev, seed=1)
-    for _ in range(reps):
+    if name == "attn":
+        B, CTX = 16, 8192  # 268 MB of bf16 KV
+    g = torch.Generator(device=dev).manual_seed(1)
+    rn = lambda *s: torch.randn(s, generator=g, device=dev)  # noqa: E731
+    bf = torch.bfloat16
+    if name == "gdn_prefill":  # chunked GDN prefill of one 16k-token sequence, 32 value / 16 key heads
+        T = 16384
+        nrm = lambda t: t / torch.sqrt(t.square().sum(-1, keepdim=True) + 1e-6)  # noqa: E731
+        q = (nrm(rn(1, T, NK, GD)) * GD ** -0.5).to(bf)
+        k = nrm(rn(1, T, NK, GD)).to(bf)
+        v = rn(1, T, NV, GD).to(bf)
+        gg = -torch.nn.functional.softplus(rn(1, T, NV))
+        beta = torch.sigmoid(rn(1, T, NV)).to(bf)
+        s0 = torch.zeros((1, NV, GD, GD), device=dev)
+        o, s1 = torch.empty_like(v), torch.empty_like(s0)
+        fn = lambda: q35.gdn_chunk_prefill(q, k, v, gg, beta, s0, o, s1)  # noqa: E731
+        units = T
+    elif name == "attn_prefill":  # causal prefill of one 8k-token sequence into an empty paged cache
+        T = 8192
+        npg = T // PAGE
+        cache = rn(npg, 2, PAGE, HKV, D).to(bf)
+        indptr = torch.tensor([0, npg], device=dev, dtype=torch.int32)
+        indices = torch.randperm(npg, generator=g, device=dev).to(torch.int32)
+        last = torch.tensor([PAGE], device=dev, dtype=torch.int32)
+        qo = torch.tensor([0, T], device=dev, dtype=torch.int32)
+        q = rn(T, HQ, D).to(bf)
+        out = torch.empty_like(q)
+        fn = lambda: q35.paged_attention_prefill(q, cache, qo, indptr, indices, last, out)  # noqa: E731
+        units = T
+    elif name == "moe_prefill":  # MoE block on 8192 tokens (prefill-sized groups on the tensor-core GEMM)
+        wl = Workload(dev, seed=1, attn=False)
+        T = 8192
+        x1 = (rn(T, H) * 0.5).to(bf)
+        out = torch.empty_like(x1)
+        fn = lambda: q35.moe_block(x1, wl.w, TOPK, out)  # noqa: E731
+        units = T
+    else:
+        wl = Workload(dev, seed=1, attn=(name == "attn"))
+        units = B
         if name == "attn":
-            q35.paged_attention_decode(wl.q, wl.cache, wl.indptr, wl.indices, wl.last, wl.attn_out, sm_scale=wl.sm_scale)
+            fn = lambda: q35.paged_attention_decode(wl.q, wl.cache, wl.indptr, wl.indices, wl.last, wl.attn_out,  # noqa: E731
+                                                    sm_scale=wl.sm_scale)
         elif name == "gdn":
-            q35.gdn_recurrent_step(wl.gq, wl.gk, wl.gv, wl.gg, wl.gbeta, wl.state, wl.g_out, wl.state)
+            fn = lambda: q35.gdn_recurrent_step(wl.gq, wl.gk, wl.gv, wl.gg, wl.gbeta, wl.state, wl.g_out, wl.state)  # noqa: E731
         else:
-            q35.moe_block(wl.x1, wl.w, TOPK, wl.moe_out)
+            fn = lambda: q35.moe_block(wl.x1, wl.w, TOPK, wl.moe_out)  # noqa: E731
+    fn()
     torch.cuda.synchronize()
-    print(f"profile case {name}: {reps} repetitions done, device status {q35.device_status()}")
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / reps
+    print(f"profile case {name}: {reps} repetitions, {ms * 1e3:.1f} us each ({units / ms * 1e3:.0f} tokens/s), "
+          f"device status {q35.device_status()}")
 
 
 def main():
@@ -348,7 +393,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
     ap.add_argument("--no-graph", action="store_true", help="launch the timed steps eagerly instead of replaying a CUDA graph")
-    ap.add_argument("--profile-case", choices=["attn", "gdn", "moe"], help="run one kernel on a capture-sized case")
+    ap.add_argument("--profile-case", choices=["attn", "gdn", "moe", "gdn_prefill", "attn_prefill", "moe_prefill"], help="run one kernel on a capture-sized case")
     args = ap.parse_args()
     if args.profile_case:
         run_profile_case(args.profile_case, max(1, min(args.steps, 5)))
