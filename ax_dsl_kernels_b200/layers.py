@@ -43,11 +43,22 @@ def _proj(x, w, name, **kw):
     return linear(x, w["w_" + name], w["s_" + name], **kw)
 
 
-def gdn(hidden_states, residual, weights, temporal_state, conv_state, *, input_norm_eps=1e-6, o_norm_eps=1e-6):
+def finish_residual(base, partial, out=None):
+    """out = bf16(base + partial): closes a sublayer whose output projection was summed in fp32 (over tensor-parallel
+    ranks) before the residual is added."""
+    out = torch.empty_like(base) if out is None else out
+    _lib.run("moe.finish", base=base, partial=partial, out=out)
+    return out
+
+
+def gdn(hidden_states, residual, weights, temporal_state, conv_state, *, input_norm_eps=1e-6, o_norm_eps=1e-6,
+        reduce=None):
     """GDN sublayer on [B, T, H] (T = 1: recurrent step, T > 1: chunked prefill).  weights: input_norm_w, (w_x, s_x) for
     x in q k v z a b o, w_q_conv / w_k_conv / w_v_conv [C, 4], a_log, dt_bias, o_norm_w.  conv_state: tuple (q, k, v) of
     [B, 3, C] bf16.  Returns (fused [B, T, H], temporal_state_out, conv_state_out) -- the reference returns
-    (zeros, residual_out, state_out, conv_out); fused is its residual_out."""
+    (zeros, residual_out, state_out, conv_out); fused is its residual_out.
+    reduce (tensor parallel, weights = this rank's heads): called with the fp32 partial of the output projection
+    [B * T, H], returns the sum over ranks; the residual is added after it."""
     w = weights
     B, T, H = hidden_states.shape
     R = B * T
@@ -85,17 +96,21 @@ def gdn(hidden_states, residual, weights, temporal_state, conv_state, *, input_n
     if o_norm_eps is not None:
         kw["eps"] = torch.tensor([o_norm_eps], dtype=torch.float32, device=x2.device)
     _lib.run("gdn.out_norm", **kw)
-    fused = _proj(normed.reshape(R, VD), w, "o", residual=base)
+    if reduce is None:
+        fused = _proj(normed.reshape(R, VD), w, "o", residual=base)
+    else:
+        fused = finish_residual(base, reduce(_proj(normed.reshape(R, VD), w, "o", out_dtype=torch.float32)))
     return fused.reshape(B, T, H), state_out, tuple(conv_out)
 
 
 def attention(x, weights, cos, sin, cache, indptr, indices, last_page_len, *, heads, kv_heads, head_dim,
-              cache_location=None, qo_indptr=None, gated=True, sm_scale=None):
+              cache_location=None, qo_indptr=None, gated=True, sm_scale=None, reduce=None):
     """Attention sublayer.  x [R, H] bf16: R = B sequences x 1 token (decode: the page table describes the HISTORY and
     cache_location [B, 2] says where the new row goes) or the concatenated new tokens of B sequences (prefill:
     qo_indptr [B + 1] given, the page table INCLUDES the new tokens).  weights: ln1 [H] f32 (effective multiplier),
     (w_q, s_q) [HQ * D * (2 if gated), H] per head [q | gate], (w_k, s_k), (w_v, s_v), q_norm, k_norm [D] f32,
-    (w_o, s_o).  cos / sin [R, rot / 2] f32.  The cache is updated in place.  Returns x + o_proj(attention)."""
+    (w_o, s_o).  cos / sin [R, rot / 2] f32.  The cache is updated in place.  Returns x + o_proj(attention).
+    reduce: as in gdn() (heads / kv_heads are then this rank's counts)."""
     w = weights
     R, H = x.shape
     n, _, _ = rmsnorm(x, w["ln1"])
@@ -120,18 +135,24 @@ def attention(x, weights, cos, sin, cache, indptr, indices, last_page_len, *, he
         gated_attn = torch.empty_like(attn)
         _lib.run("act.sigmoid_gate", a=attn, b=gate, y=gated_attn)
         attn = gated_attn
-    return _proj(attn.reshape(R, heads * head_dim), w, "o", residual=x)
+    if reduce is None:
+        return _proj(attn.reshape(R, heads * head_dim), w, "o", residual=x)
+    return finish_residual(x, reduce(_proj(attn.reshape(R, heads * head_dim), w, "o", out_dtype=torch.float32)))
 
 
-def mlp_residual(x1, weights):
-    """dense SwiGLU block: x1 + down(bf16(silu(gate h) * up h)), h = RMSNorm(x1) * ln2 (q35_step.py:118-146)."""
+def mlp_residual(x1, weights, reduce=None):
+    """dense SwiGLU block: x1 + down(bf16(silu(gate h) * up h)), h = RMSNorm(x1) * ln2 (q35_step.py:118-146).
+    reduce: as in gdn() (gate / up rows and down columns are then this rank's slice of the intermediate size, the
+    split of the reference's multi-core form, models/qwen35_2b/whole/src/q35_layer_mc.py:129-136)."""
     w = weights
     h2, _, _ = rmsnorm(x1, w["ln2"])
     g = _proj(h2, w, "gate")
     u = _proj(h2, w, "up")
     act = torch.empty_like(g)
     _lib.run("act.silu_mul", a=g, b=u, y=act)
-    return _proj(act, w, "down", residual=x1)
+    if reduce is None:
+        return _proj(act, w, "down", residual=x1)
+    return finish_residual(x1, reduce(_proj(act, w, "down", out_dtype=torch.float32)))
 
 
 class HybridStack:
@@ -139,8 +160,9 @@ class HybridStack:
     states, conv states and paged KV caches (one cache per attention layer, shared page table)."""
 
     def __init__(self, layers, kinds, *, heads, kv_heads, head_dim, rot, theta, page_size=64, max_tokens=1024,
-                 gated=True):
+                 gated=True, reduce=None):
         self.layers, self.kinds = layers, kinds
+        self.reduce = reduce  # tensor parallel: layers hold this rank's shards, heads / kv_heads its counts
         self.cfg = dict(heads=heads, kv_heads=kv_heads, head_dim=head_dim)
         self.rot, self.theta, self.P, self.gated = rot, theta, page_size, gated
         dev = layers[0]["ln2"].device
@@ -175,17 +197,17 @@ class HybridStack:
             if kind == "g":
                 zero = torch.zeros_like(x)
                 fused, self.state[i], self.conv[i] = gdn(x.reshape(1, T, -1), zero.reshape(1, T, -1), w, self.state[i],
-                                                         self.conv[i])
+                                                         self.conv[i], reduce=self.reduce)
                 x1 = fused.reshape(T, -1)
             elif T == 1:
                 hist = self.pos
                 x1 = attention(x, w, cos, sin, self.cache[i], i32([0, hist // P + 1]), self.indices, i32([hist % P]),
-                               cache_location=i32([[hist // P, hist % P]]), gated=self.gated, **self.cfg)
+                               cache_location=i32([[hist // P, hist % P]]), gated=self.gated, reduce=self.reduce, **self.cfg)
             else:
                 total = self.pos + T
                 npg = (total + P - 1) // P
                 x1 = attention(x, w, cos, sin, self.cache[i], i32([0, npg]), self.indices, i32([total - (npg - 1) * P]),
-                               qo_indptr=i32([0, T]), gated=self.gated, **self.cfg)
-            x = mlp_residual(x1, w)
+                               qo_indptr=i32([0, T]), gated=self.gated, reduce=self.reduce, **self.cfg)
+            x = mlp_residual(x1, w, reduce=self.reduce)
         self.pos += T
         return x

@@ -1,5 +1,6 @@
 """Multi-GPU host logic: one process per GPU, torch.distributed for the plumbing (NCCL on GPUs; the same code runs
-over gloo on CPU in the tests, with the local compute injected).
+over gloo on CPU in the tests, with the local compute injected).  Two forms: expert parallelism of the MoE block
+(below) and tensor parallelism of the dense hybrid stack (second half of the file).
 
 Expert parallelism for decode-sized batches.  Experts are sharded contiguously (rank r owns experts
 [r * NE / N, (r + 1) * NE / N)), router and shared expert are replicated, sequences stay on their rank.
@@ -88,3 +89,116 @@ class ExpertParallelMoE:
         out = torch.empty_like(x1) if out is None else out
         out.copy_((base.float() + mine).to(out.dtype))
         return out
+
+
+# ----------------------------------------------------------------------------------------------------------------
+# Tensor parallelism of the dense hybrid stack (27B-class decode group: heads split across 2 / 4 / 8 GPUs).
+# The reference splits the same way across its 4 NPU cores: projection rows by head, FFN rows by column block,
+# partial sums of the output projections added (models/qwen35_2b/whole/src/q35_layer_mc.py:129-136, 242-423).
+# Every sublayer ends in ONE all-reduce of the fp32 partial [tokens, H] of its output projection; the residual is
+# added after the sum.  Nothing else crosses GPUs: GDN state, conv state and KV cache are sharded by head.
+
+def _rows(w, s, lo, hi):
+    """rows [lo, hi) of a quantised matrix: block scales [N, K/32] and per-row scales [N] follow the rows"""
+    return w[lo:hi].contiguous(), s[lo:hi].contiguous()
+
+
+def _cols(w, s, lo, hi):
+    """input columns [lo, hi) (multiples of 32) of a quantised matrix [N, K]: MXFP4 bytes hold two columns each, block
+    scales one per 32 columns, per-row fp32 scales are unchanged"""
+    if lo % 32 or hi % 32:
+        raise ValueError("column shards of quantised weights must be multiples of 32")
+    packed = w.dtype == torch.uint8 and s.dim() == 2 and w.shape[1] * 2 == s.shape[1] * 32
+    wc = w[:, lo // 2:hi // 2] if packed else w[:, lo:hi]
+    sc = s if s.dim() == 1 else s[:, lo // 32:hi // 32]
+    return wc.contiguous(), sc.contiguous()
+
+
+def shard_gdn_weights(w, rank, world, head_dim=128):
+    """this rank's value heads [rank * NV / N, ...) and the key heads they use (grouped map kh = vh // (NV / NK))"""
+    NV = w["a_log"].numel()
+    NK = w["w_q"].shape[0] // head_dim
+    if NV % world or NK % world:
+        raise ValueError(f"{NV} value / {NK} key heads do not divide over {world} ranks")
+    v0, v1 = rank * NV // world, (rank + 1) * NV // world
+    k0, k1 = rank * NK // world, (rank + 1) * NK // world
+    out = dict(input_norm_w=w["input_norm_w"], o_norm_w=w["o_norm_w"], a_log=w["a_log"][v0:v1].contiguous(),
+               dt_bias=w["dt_bias"][v0:v1].contiguous())
+    for n, (lo, hi) in (("q", (k0 * head_dim, k1 * head_dim)), ("k", (k0 * head_dim, k1 * head_dim)),
+                        ("v", (v0 * head_dim, v1 * head_dim)), ("z", (v0 * head_dim, v1 * head_dim)),
+                        ("a", (v0, v1)), ("b", (v0, v1))):
+        out["w_" + n], out["s_" + n] = _rows(w["w_" + n], w["s_" + n], lo, hi)
+    for n, (lo, hi) in (("q", (k0, k1)), ("k", (k0, k1)), ("v", (v0, v1))):
+        out[f"w_{n}_conv"] = w[f"w_{n}_conv"][lo * head_dim:hi * head_dim].contiguous()
+    out["w_o"], out["s_o"] = _cols(w["w_o"], w["s_o"], v0 * head_dim, v1 * head_dim)
+    return out
+
+
+def shard_attention_weights(w, rank, world, heads, kv_heads, head_dim, gated=True):
+    """this rank's query heads; its KV heads while world <= kv_heads, else the single KV head its query heads belong to
+    (ranks sharing a KV head each keep that head's cache: no exchange inside the attention).
+    Returns (weights, local heads, local kv heads)."""
+    if heads % world:
+        raise ValueError(f"{heads} query heads do not divide over {world} ranks")
+    hl = heads // world
+    h0 = rank * hl
+    per_q = head_dim * (2 if gated else 1)  # rows per head in w_q: [q | gate]
+    if kv_heads % world == 0:
+        kl = kv_heads // world
+        kv0 = rank * kl
+    else:
+        group = heads // kv_heads
+        if world % kv_heads or group % hl:
+            raise ValueError(f"{heads} / {kv_heads} heads cannot be split over {world} ranks by whole KV-head groups")
+        kl, kv0 = 1, h0 // group
+    out = dict(ln1=w["ln1"], q_norm=w["q_norm"], k_norm=w["k_norm"])
+    out["w_q"], out["s_q"] = _rows(w["w_q"], w["s_q"], h0 * per_q, (h0 + hl) * per_q)
+    for n in ("k", "v"):
+        out["w_" + n], out["s_" + n] = _rows(w["w_" + n], w["s_" + n], kv0 * head_dim, (kv0 + kl) * head_dim)
+    out["w_o"], out["s_o"] = _cols(w["w_o"], w["s_o"], h0 * head_dim, (h0 + hl) * head_dim)
+    return out, hl, kl
+
+
+def shard_mlp_weights(w, rank, world):
+    """rows [rank * F / N, ...) of gate and up, the same columns of down"""
+    F = w["w_gate"].shape[0]
+    if F % (32 * world):
+        raise ValueError(f"intermediate size {F} does not divide over {world} ranks in multiples of 32")
+    lo, hi = rank * F // world, (rank + 1) * F // world
+    out = dict(ln2=w["ln2"])
+    for n in ("gate", "up"):
+        out["w_" + n], out["s_" + n] = _rows(w["w_" + n], w["s_" + n], lo, hi)
+    out["w_down"], out["s_down"] = _cols(w["w_down"], w["s_down"], lo, hi)
+    return out
+
+
+def shard_stack_weights(layers, kinds, rank, world, *, heads, kv_heads, head_dim, gated=True, gdn_head_dim=128):
+    """per-layer shards of a hybrid stack; returns (layers, local heads, local kv heads)"""
+    out, hl, kl = [], heads // world, max(1, kv_heads // world)
+    for w, kind in zip(layers, kinds):
+        if kind == "g":
+            lw = shard_gdn_weights(w, rank, world, gdn_head_dim)
+        else:
+            lw, hl, kl = shard_attention_weights(w, rank, world, heads, kv_heads, head_dim, gated)
+        lw.update(shard_mlp_weights(w, rank, world))
+        out.append(lw)
+    return out, hl, kl
+
+
+def all_reduce_sum(group=None):
+    """the `reduce` hook of the sublayers: in-place sum of the fp32 partial over the group"""
+    def reduce(partial):
+        dist.all_reduce(partial, op=dist.ReduceOp.SUM, group=group)
+        return partial
+    return reduce
+
+
+def tensor_parallel_stack(layers, kinds, *, heads, kv_heads, head_dim, group=None, gated=True, **stack_kw):
+    """layers.HybridStack over this rank's shards with an all-reduce after each of the two sublayers of a layer"""
+    from .layers import HybridStack
+    g = group if group is not None else dist.group.WORLD
+    rank, world = dist.get_rank(g), dist.get_world_size(g)
+    shards, hl, kl = shard_stack_weights(layers, kinds, rank, world, heads=heads, kv_heads=kv_heads, head_dim=head_dim,
+                                         gated=gated)
+    return HybridStack(shards, kinds, heads=hl, kv_heads=kl, head_dim=head_dim, gated=gated, reduce=all_reduce_sum(g),
+                       **stack_kw)

@@ -119,3 +119,71 @@ def test_configuration1_stack_full_shape(q35):
         ref, out = ref_stack.forward(emb[t:t + 1]), gpu_stack.forward(emb[t:t + 1].cuda())
         worst = min(worst, cosine(out.cpu().float(), ref.float()))
     assert worst >= 0.999, worst
+
+
+def test_tensor_parallel_sublayers_two_ranks_emulated_on_one_gpu(q35):
+    """heads / FFN columns split over 2 ranks (ax_dsl_kernels_b200/parallel.py); both ranks run one after the other on
+    this GPU and the `reduce` hook of the second adds the first one's partial, which is what the all-reduce does"""
+    from ax_dsl_kernels_b200 import parallel
+    kw, ow = stack_case("ga", heads=4, kv_heads=2, NK=2, NV=4, seed=11)
+    dkw = to_dev(kw)
+    g = torch.Generator().manual_seed(4)
+    B = 3
+    x = (torch.randn((B, 1, 512), generator=g) * 0.5).to(torch.bfloat16)
+
+    def both(run):
+        held = {}
+
+        def first(p):
+            held["p"] = p.clone()
+            return p
+
+        def second(p):
+            return p.add_(held["p"])
+
+        run(0, first)
+        return run(1, second)
+
+    # GDN sublayer, decode
+    s0 = torch.randn((B, 4, 128, 128), generator=g) * 0.03
+    conv = [(torch.randn((B, 3, wd), generator=g) * 0.03).to(torch.bfloat16) for wd in (256, 256, 512)]
+    zero = torch.zeros_like(x)
+    ref, s_ref, _ = ogdn.gdn_sublayer(x, zero, ow[0], s0, torch.cat(conv, -1))
+    states = {}
+
+    def run_gdn(rank, reduce):
+        lw = parallel.shard_gdn_weights(dkw[0], rank, 2)
+        cl = [c[..., rank * c.shape[-1] // 2:(rank + 1) * c.shape[-1] // 2].contiguous().cuda() for c in conv]
+        fused, st, _ = q35.layers.gdn(x.cuda(), zero.cuda(), lw, s0[:, rank * 2:rank * 2 + 2].contiguous().cuda(),
+                                      tuple(cl), reduce=reduce)
+        states[rank] = st.cpu()
+        return fused
+
+    assert_parity(both(run_gdn).cpu(), ref)
+    torch.testing.assert_close(torch.cat((states[0], states[1]), 1), s_ref, rtol=0, atol=4e-3)
+
+    # attention sublayer, decode on 70 tokens of history; each rank keeps its own KV head's cache
+    P, hist = 64, 70
+    cache = torch.randn((2 * B, 2, P, 2, 128), generator=g).to(torch.bfloat16)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32)  # noqa: E731
+    indptr, indices = i32([0, 2, 4, 6]), i32([3, 0, 5, 1, 2, 4])
+    last, loc = i32([hist - P] * B), i32([[0, hist - P], [1, hist - P], [4, hist - P]])
+    cos, sin = oattn.rope_cos_sin(torch.tensor([hist] * B), 32, 1e7)
+    x2 = x.reshape(B, 512)
+    ref = ostack.attn_sublayer(x2, ow[1], cache.clone(), indptr, indices, last, cos, sin, heads=4, kv_heads=2,
+                               head_dim=128, rot=32, cache_location=loc)
+
+    def run_attn(rank, reduce):
+        aw, hl, kl = parallel.shard_attention_weights(dkw[1], rank, 2, 4, 2, 128)
+        assert (hl, kl) == (2, 1)
+        return q35.layers.attention(x2.cuda(), aw, cos.cuda(), sin.cuda(), cache[:, :, :, rank:rank + 1].contiguous().cuda(),
+                                    indptr.cuda(), indices.cuda(), last.cuda(), heads=hl, kv_heads=kl, head_dim=128,
+                                    cache_location=loc.cuda(), reduce=reduce)
+
+    assert_parity(both(run_attn).cpu(), ref)
+
+    # dense FFN
+    ref = ostack.dense_mlp(x2, ow[0]["ln2"], ow[0]["w_gate"], ow[0]["w_up"], ow[0]["w_down"])
+    out = both(lambda rank, reduce: q35.layers.mlp_residual(x2.cuda(), parallel.shard_mlp_weights(dkw[0], rank, 2),
+                                                            reduce=reduce))
+    assert_parity(out.cpu(), ref)

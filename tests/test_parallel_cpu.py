@@ -89,3 +89,101 @@ def test_shard_range_and_local_ids():
         parallel.shard_range(10, 0, 4)
     ids = torch.tensor([[0, 5, 9], [4, 7, 8]], dtype=torch.int32)
     assert parallel.local_ids(ids, 4, 8).tolist() == [[-1, 1, -1], [0, 3, -1]]
+
+
+# ----------------------------------------------------------------------------------------------------------------
+# tensor parallelism: the sharding of heads / FFN columns and the all-reduce, with the oracle as the local compute
+def _deq(w):
+    out = {}
+    for k, v in w.items():
+        if k.startswith("w_") and ("s_" + k[2:]) in w:
+            out[k] = codecs.dequant_fp8_rowwise(v, w["s_" + k[2:]])
+        elif not k.startswith("s_"):
+            out[k] = v
+    return out
+
+
+def _tp_worker(rank, world, port, ret):
+    import sys
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from _cases import stack_case
+    from oracle import attention as oattn, gdn as ogdn, stack as ostack
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        H, heads, kv_heads, D, NK, NV, DV = 256, 4, 1, 64, 2, 4, 32  # kv_heads < world: the KV head is replicated
+        kw, ow = stack_case("ga", H=H, F=128, heads=heads, kv_heads=kv_heads, head_dim=D, NK=NK, NV=NV, DV=DV, seed=3)
+        reduce = parallel.all_reduce_sum()
+        g = torch.Generator().manual_seed(9)
+        x = (torch.randn((2, 1, H), generator=g) * 0.5).to(torch.bfloat16)
+        errs = {}
+
+        def rel(a, b):
+            return float((a.float() - b.float()).abs().max() / b.float().square().mean().sqrt())
+
+        # GDN sublayer: value heads [rank * 2, rank * 2 + 2), key head rank
+        lw = _deq(parallel.shard_gdn_weights(kw[0], rank, world, head_dim=DV))
+        assert lw["w_v"].shape[0] == NV // world * DV and lw["w_o"].shape == (H, NV // world * DV)
+        st = torch.randn((2, NV, DV, DV), generator=g) * 0.03
+        cs = (torch.randn((2, 3, 2 * NK * DV + NV * DV), generator=g) * 0.1).to(torch.bfloat16)
+        zero = torch.zeros_like(x)
+        full, st_full, _ = ogdn.gdn_sublayer(x, zero, ow[0], st, cs)
+        k0, v0 = rank * NK // world * DV, rank * NV // world * DV
+        kd, vd = NK * DV, NV * DV
+        cs_l = torch.cat((cs[..., k0:k0 + kd // world], cs[..., kd + k0:kd + k0 + kd // world],
+                          cs[..., 2 * kd + v0:2 * kd + v0 + vd // world]), -1)
+        st_l = st[:, rank * NV // world:(rank + 1) * NV // world]
+        part, st_out, _ = ogdn.gdn_sublayer(x, zero, lw, st_l, cs_l)
+        partial = part.float() - x.float()  # the sublayer adds the residual; take it off again
+        out = (x.float() + reduce(partial)).to(torch.bfloat16)
+        errs["gdn"] = rel(out, full)
+        errs["gdn_state"] = rel(st_out, st_full[:, rank * NV // world:(rank + 1) * NV // world])
+
+        # attention sublayer (decode, 5 tokens of history)
+        aw, hl, kl = parallel.shard_attention_weights(kw[1], rank, world, heads, kv_heads, D)
+        assert (hl, kl) == (2, 1) and aw["w_q"].shape[0] == 2 * 2 * D and aw["w_o"].shape == (H, 2 * D)
+        cache = (torch.randn((2, 2, 8, kv_heads, D), generator=g)).to(torch.bfloat16)
+        indptr, indices = torch.tensor([0, 1, 2], dtype=torch.int32), torch.tensor([0, 1], dtype=torch.int32)
+        last = torch.tensor([5, 5], dtype=torch.int32)
+        loc = torch.tensor([[0, 5], [1, 5]], dtype=torch.int32)
+        cos, sin = oattn.rope_cos_sin(torch.tensor([5, 5]), 16, 1e7)
+        x2 = x.reshape(2, H)
+        kwa = dict(head_dim=D, rot=16, gated=True)
+        full = ostack.attn_sublayer(x2, ow[1], cache.clone(), indptr, indices, last, cos, sin, heads=heads,
+                                    kv_heads=kv_heads, cache_location=loc, **kwa)
+        part = ostack.attn_sublayer(x2, _deq(aw), cache.clone(), indptr, indices, last, cos, sin, heads=hl, kv_heads=kl,
+                                    cache_location=loc, **kwa)
+        out = (x2.float() + reduce(part.float() - x2.float())).to(torch.bfloat16)
+        errs["attn"] = rel(out, full)
+
+        # dense FFN
+        mw = _deq(parallel.shard_mlp_weights(kw[0], rank, world))
+        full = ostack.dense_mlp(x2, ow[0]["ln2"], ow[0]["w_gate"], ow[0]["w_up"], ow[0]["w_down"])
+        part = ostack.dense_mlp(x2, mw["ln2"], mw["w_gate"], mw["w_up"], mw["w_down"])
+        out = (x2.float() + reduce(part.float() - x2.float())).to(torch.bfloat16)
+        errs["mlp"] = rel(out, full)
+        ret[rank] = errs
+    finally:
+        dist.destroy_process_group()
+
+
+def test_tensor_parallel_shards_two_ranks_gloo():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    ret = mp.Manager().dict()
+    mp.spawn(_tp_worker, args=(2, port, ret), nprocs=2, join=True)
+    assert len(ret) == 2
+    for errs in ret.values():
+        # each rank's partial went through one extra bf16 rounding (the oracle sublayer rounds before the residual)
+        assert all(v <= 3e-2 for v in errs.values()), dict(ret)
+
+
+def test_column_shard_of_block_scaled_weights():
+    g = torch.Generator().manual_seed(1)
+    w, s = codecs.random_mxfp4((8, 128), g, -3, 0)
+    wc, sc = parallel._cols(w, s, 64, 128)
+    assert torch.equal(codecs.dequant_mxfp4(wc, sc), codecs.dequant_mxfp4(w, s)[:, 64:128])
+    with pytest.raises(ValueError):
+        parallel._cols(w, s, 16, 128)
