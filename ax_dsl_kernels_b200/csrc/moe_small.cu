@@ -93,11 +93,13 @@ int run_moe_route(Call& c) {
 // Grouping of (token, k) pairs by expert: a counting sort that is stable in token index.  One CTA per expert scans
 // the ids in token order and compacts the pairs that chose it, so the result does not depend on scheduling.
 // counts[e] = number of pairs, list[e * T + j] = pair index t * K + k of the j-th token (ascending t) of expert e.
-__global__ void __launch_bounds__(256) moe_group_count_kernel(const int* __restrict__ ids, int T, int K, int NE,
-                                                              int* __restrict__ counts, int* __restrict__ list,
-                                                              int* status) {
+// base (optional): first global expert id of this rank's planes; ids outside [base, base + NE) belong to other ranks.
+__global__ void __launch_bounds__(256) moe_group_count_kernel(const int* __restrict__ ids, const int* __restrict__ base,
+                                                              int T, int K, int NE, int* __restrict__ counts,
+                                                              int* __restrict__ list, int* status) {
   const int e = blockIdx.x;
   const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+  const int first = base ? base[0] : 0;
   __shared__ int s_warp[8];
   __shared__ int s_base;
   if (tid == 0) s_base = 0;
@@ -107,9 +109,9 @@ __global__ void __launch_bounds__(256) moe_group_count_kernel(const int* __restr
     int hit = -1;
     if (t < T) {
       for (int k = 0; k < K; ++k) {
-        const int id = ids[size_t(t) * K + k];
+        const int id = ids[size_t(t) * K + k] - first;
         if (id == e && hit < 0) hit = k;
-        if (e == 0 && id >= NE) atomicOr(status, DS_BAD_EXPERT);  // negative ids mean "not on this rank"
+        if (e == 0 && !base && id >= NE) atomicOr(status, DS_BAD_EXPERT);  // negative ids mean "not on this rank"
       }
     }
     const unsigned m = __ballot_sync(0xffffffffu, hit >= 0);
@@ -129,8 +131,9 @@ __global__ void __launch_bounds__(256) moe_group_count_kernel(const int* __restr
   if (tid == 0) counts[e] = s_base;
 }
 
-int launch_group_count(const int* ids, int T, int K, int NE, int* counts, int* list, cudaStream_t stream) {
-  moe_group_count_kernel<<<unsigned(NE), 256, 0, stream>>>(ids, T, K, NE, counts, list, device_status_ptr());
+int launch_group_count(const int* ids, const int* base, int T, int K, int NE, int* counts, int* list,
+                       cudaStream_t stream) {
+  moe_group_count_kernel<<<unsigned(NE), 256, 0, stream>>>(ids, base, T, K, NE, counts, list, device_status_ptr());
   Q35_CUDA_LAUNCH_CHECK("moe group count");
   return 0;
 }
@@ -211,7 +214,7 @@ int run_moe_permute(Call& c) {
               "moe.permute: rw [T, K], loc [K, T], n_slots [1], counts [NE]");
   Q35_TRY(c.workspace(NE * T * 4, &ws));
   if (c.dry || T == 0) return 0;
-  Q35_TRY(launch_group_count(ids.as<int>(), int(T), int(K), int(NE), counts.as<int>(), ws.as<int>(), c.stream));
+  Q35_TRY(launch_group_count(ids.as<int>(), nullptr, int(T), int(K), int(NE), counts.as<int>(), ws.as<int>(), c.stream));
   moe_permute_fill_kernel<<<unsigned(NE), 256, 0, c.stream>>>(counts.as<int>(), ws.as<int>(), rw.as<float>(), int(T),
                                                               int(K), int(NE), int(G), int(S), tok.as<int>(),
                                                               srw.as<float>(), loc.as<int>(), ns.as<int>());

@@ -131,6 +131,7 @@ __global__ void __launch_bounds__(256) experts_build_rows_kernel(const int* __re
 // the row tables and the list of experts with rows that the tensor-core GEMM walks.  Same result as
 // moe_group_count_kernel + experts_build_rows_kernel + the active-group scan; pairs without a local expert get loc -1.
 __global__ void __launch_bounds__(1024) experts_plan_small_kernel(const int* __restrict__ ids,
+                                                                  const int* __restrict__ base,
                                                                   const float* __restrict__ rw, int T, int K, int NE,
                                                                   int* g_expert, int* g_n, int* g_row0, int* src,
                                                                   float* rw_row, int* loc, int* active, int* status) {
@@ -143,8 +144,11 @@ __global__ void __launch_bounds__(1024) experts_plan_small_kernel(const int* __r
   int id = -1, t = 0, k = 0;
   if (tid < P) {
     t = tid / K; k = tid % K;
-    id = ids[tid];
-    if (id >= NE) { atomicOr(status, DS_BAD_EXPERT); id = -1; }
+    id = ids[tid] - (base ? base[0] : 0);  // base: first global id of this rank's planes
+    if (id >= NE) {
+      if (!base) atomicOr(status, DS_BAD_EXPERT);
+      id = -1;
+    }
     if (id < 0) id = -1;  // negative ids mean "not on this rank"
   }
   s_row0[tid] = id;  // raw ids, for the duplicate check
@@ -207,9 +211,10 @@ __global__ void __launch_bounds__(1024) experts_plan_small_kernel(const int* __r
 }
 
 int run_moe_experts(Call& c) {
-  Tensor h2, base, ids, rw, gw, gs, dw, ds, out, partial, ws;
+  Tensor h2, base, ids, rw, gw, gs, dw, ds, out, partial, ebase, ws;
   Q35_TRY(c.get("h2", M(Q35_BF16), &h2));
   Q35_TRY(c.get("partial_out", M(Q35_F32), &partial, false));  // expert-parallel form: fp32 sums, no base
+  Q35_TRY(c.get("expert_base", M(Q35_I32), &ebase, false));    // ids are global, the planes start at this id
   Q35_TRY(c.get("base", M(Q35_BF16), &base, !partial.present));
   Q35_TRY(c.get("ids", M(Q35_I32), &ids));
   Q35_TRY(c.get("rw", M(Q35_F32), &rw));
@@ -260,14 +265,16 @@ int run_moe_experts(Call& c) {
 
   const bool small = P <= 1024 && NE <= 1024;
   if (small) {
-    experts_plan_small_kernel<<<1, 1024, 0, c.stream>>>(ids.as<int>(), rw.as<float>(), int(T), int(K), int(NE), g_expert,
+    experts_plan_small_kernel<<<1, 1024, 0, c.stream>>>(ids.as<int>(), ebase.present ? ebase.as<int>() : nullptr,
+                                                        rw.as<float>(), int(T), int(K), int(NE), g_expert,
                                                         g_n, g_row0, src, rw_row, loc,
                                                         use_tc ? tc_routed_active(qws, P, H, FE) : nullptr,
                                                         device_status_ptr());
     Q35_CUDA_LAUNCH_CHECK("moe.experts plan");
   } else {
     if (partial.present) cudaMemsetAsync(loc, 0xff, size_t(P) * 4, c.stream);  // pairs of other ranks: loc = -1
-    Q35_TRY(launch_group_count(ids.as<int>(), int(T), int(K), int(NE), counts, list, c.stream));
+    Q35_TRY(launch_group_count(ids.as<int>(), ebase.present ? ebase.as<int>() : nullptr, int(T), int(K), int(NE), counts,
+                               list, c.stream));
     experts_build_rows_kernel<<<unsigned(NE), 256, 0, c.stream>>>(counts, list, rw.as<float>(), int(T), int(K), int(NE),
                                                                   g_expert, g_n, g_row0, src, rw_row, loc);
     Q35_CUDA_LAUNCH_CHECK("moe.experts rows");

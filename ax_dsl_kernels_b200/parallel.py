@@ -6,7 +6,8 @@ Expert parallelism for decode-sized batches.  Experts are sharded contiguously (
 [r * NE / N, (r + 1) * NE / N)), router and shared expert are replicated, sequences stay on their rank.
 Exchange per step, all fixed-size (no host round trip for counts):
   1. all-gather of every rank's post-norm hidden rows h2 [T, H] bf16, expert ids and routing weights;
-  2. every rank runs ITS experts over the gathered tokens and produces fp32 partial sums [N * T, H];
+  2. every rank runs ITS experts over the gathered tokens (ids stay global, `expert_base` tells the kernel where this
+     rank's planes start) and produces fp32 partial sums [N * T, H];
   3. reduce-scatter (sum) returns to each rank the sums of its own T tokens; out = bf16(base + sum).
 This moves the same bytes as an exact all-to-all dispatch/return of the routed rows (T * K rows out, T * K rows back)
 when T * K / N >= T, which holds for top-8 routing on up to 8 GPUs.
@@ -46,25 +47,47 @@ class ExpertParallelMoE:
             self.w[n] = t[self.lo:self.hi].contiguous() if t.shape[0] == self.n_experts else t
         self._buf = {}
 
-    # -- the three local compute pieces; the CPU tests override them with the oracle ------------------------------
+    # -- the local compute pieces; the CPU tests override them with the oracle ------------------------------------
     def _dense_part(self, x1):
-        from . import moe
+        """-> (base = bf16(x1 + shared expert), h2, ids, rw, event after which base is ready or None).  On the GPU the
+        shared expert runs on a second stream and is only waited for before the closing sum."""
+        from . import _lib, moe
         T, H = x1.shape
-        base, h2 = torch.empty_like(x1), torch.empty_like(x1)
-        logits = torch.empty((T, self.n_experts), dtype=torch.float32, device=x1.device)
+        dev = x1.device
         w = self.w
-        moe.moe_pre(x1, w["ln2"], w["w_gate"], w["s_gate"], w["w_up"], w["s_up"], w["w_down"], w["s_down"],
-                    w["w_router"], w["w_shg"], base, h2, logits)
-        ids, rw = moe.route(logits, self.top_k)
-        return base, h2, ids, rw
+        base, h2 = self._get("base", (T, H), x1.dtype, dev), self._get("h2", (T, H), x1.dtype, dev)
+        logits = self._get("logits", (T, self.n_experts), torch.float32, dev)
+        gate = self._get("gate", (T,), torch.float32, dev)
+        _lib.run("moe.norm_router", x1=x1, ln2=w["ln2"], w_router=w["w_router"], w_shg=w["w_shg"].reshape(-1), h2_out=h2,
+                 logits_out=logits, gate_out=gate)
+        main, side = torch.cuda.current_stream(dev), moe._side_stream(dev)
+        side.wait_stream(main)
+        with torch.cuda.stream(side):
+            _lib.run("moe.shared", x1=x1, h2=h2, gate=gate, w_gate=w["w_gate"], s_gate=moe._u8(w["s_gate"]),
+                     w_up=w["w_up"], s_up=moe._u8(w["s_up"]), w_down=w["w_down"], s_down=moe._u8(w["s_down"]), out=base)
+            ready = side.record_event()
+        ids, rw = moe.route(logits, self.top_k, self._get("ids", (T, self.top_k), torch.int32, dev),
+                            self._get("rw", (T, self.top_k), torch.float32, dev))
+        return base, h2, ids, rw, ready
 
-    def _local_experts(self, h2_all, ids_local, rw_all):
-        from . import _lib
+    def _local_experts(self, h2_all, ids_all, rw_all):
+        """fp32 sums over THIS rank's experts for every gathered token; ids are global"""
+        from . import _lib, moe
         w = self.w
         partial = self._get("partial", h2_all.shape, torch.float32, h2_all.device)
-        _lib.run("moe.experts", h2=h2_all, ids=ids_local, rw=rw_all, e_gw=w["e_gw"], e_gs=w["e_gs"], e_dw=w["e_dw"],
-                 e_ds=w["e_ds"], partial_out=partial)
+        if "expert_base" not in self._buf:
+            self._buf["expert_base"] = torch.tensor([self.lo], dtype=torch.int32, device=h2_all.device)
+        _lib.run("moe.experts", h2=h2_all, ids=ids_all, rw=rw_all, e_gw=moe._u8(w["e_gw"]), e_gs=moe._u8(w["e_gs"]),
+                 e_dw=moe._u8(w["e_dw"]), e_ds=moe._u8(w["e_ds"]), expert_base=self._buf["expert_base"],
+                 partial_out=partial)
         return partial
+
+    def _finish(self, base, mine, out, ready):
+        from . import _lib
+        if ready is not None:
+            torch.cuda.current_stream(base.device).wait_event(ready)
+        _lib.run("moe.finish", base=base, partial=mine, out=out)
+        return out
 
     # -------------------------------------------------------------------------------------------------------------
     def _get(self, name, shape, dtype, device):
@@ -76,20 +99,18 @@ class ExpertParallelMoE:
     def forward(self, x1, out=None):
         T, H = x1.shape
         N, K = self.world, self.top_k
-        base, h2, ids, rw = self._dense_part(x1)
+        base, h2, ids, rw, ready = self._dense_part(x1)
         h2_all = self._get("h2_all", (N * T, H), h2.dtype, h2.device)
         ids_all = self._get("ids_all", (N * T, K), ids.dtype, ids.device)
         rw_all = self._get("rw_all", (N * T, K), rw.dtype, rw.device)
         dist.all_gather_into_tensor(h2_all, h2.contiguous(), group=self.group)
         dist.all_gather_into_tensor(ids_all, ids.contiguous(), group=self.group)
         dist.all_gather_into_tensor(rw_all, rw.contiguous(), group=self.group)
-        partial = self._local_experts(h2_all, local_ids(ids_all, self.lo, self.hi), rw_all)
+        partial = self._local_experts(h2_all, ids_all, rw_all)
         mine = self._get("mine", (T, H), torch.float32, x1.device)
         dist.reduce_scatter_tensor(mine, partial, op=dist.ReduceOp.SUM, group=self.group)
         out = torch.empty_like(x1) if out is None else out
-        out.copy_((base.float() + mine).to(out.dtype))
-        return out
-
+        return self._finish(base, mine, out, ready)
 
 # ----------------------------------------------------------------------------------------------------------------
 # Tensor parallelism of the dense hybrid stack (27B-class decode group: heads split across 2 / 4 / 8 GPUs).

@@ -126,8 +126,9 @@ def run_ours(args):
     for _ in range(max(args.warmup, 3)):
         step()
     barrier()
-    # The device-resident loop replays a CUDA graph of the step (15 kernel launches that together take ~0.6 ms would
-    # otherwise be paced by the Python launch path); the NCCL variant runs eagerly.
+    # One GPU: the step is captured once into a CUDA graph through the public API and replayed (18 kernel launches
+    # that together take ~0.55 ms would otherwise be paced by the Python launch path); both the device-resident loop
+    # and the end-to-end loop replay it.  The NCCL variant runs eagerly.
     graph = None
     if world == 1 and not args.no_graph:
         graph = torch.cuda.CUDAGraph()
@@ -169,7 +170,7 @@ def run_ours(args):
     def step_e2e():
         for n, t in host_in.items():
             getattr(wl, n).copy_(t, non_blocking=True)
-        step()
+        run_step()  # the captured step reads and writes the same device buffers the copies fill and drain
         for n, t in host_out.items():
             t.copy_(getattr(wl, n), non_blocking=True)
         torch.cuda.current_stream().synchronize()  # the caller reads the results
@@ -206,7 +207,9 @@ def run_ours(args):
                        "0.27 GB state per step)"},
             "e2e": {"value": world * B * args.steps / (e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h},
-            "gpu_launches": args.steps * (21 if world == 1 else 19),  # kernels of this library per step (torch and NCCL kernels not counted)
+            # kernels of this library per step (torch and NCCL kernels not counted): GDN 1, attention 3, MoE 14 with
+            # the one-CTA routing plan (up to 1024 token-expert pairs per rank), 16 with the three-kernel plan
+            "gpu_launches": args.steps * (18 if world * B * TOPK <= 1024 else 20),
             "roofline": {"bound": "hbm", "kernel": "attn_decode_kernel<256,bf16> (+ plan and merge launches)",
                          "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_source": peak_src, "traffic": None, "algorithmic_bytes": wl.attn_bytes(),

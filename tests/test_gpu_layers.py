@@ -121,6 +121,24 @@ def test_configuration1_stack_full_shape(q35):
     assert worst >= 0.999, worst
 
 
+def test_configuration5_group_shape(q35):
+    """Configuration 5 shapes on one block of the 27B-class decode group (pattern g g g a): hidden 5120, 24 q / 4 kv
+    heads of 256, GDN 48 value / 16 key heads of 128, FFN 17408, FP8 E4M3 per-row weights; a 96-token prefill (not a
+    multiple of the GDN chunk or the page) and 4 decode steps against the CPU oracle stack."""
+    kinds = "ggga"
+    kw, ow = stack_case(kinds, H=5120, F=17408, heads=24, kv_heads=4, head_dim=256, NK=16, NV=48, DV=128, seed=4)
+    cfg = dict(heads=24, kv_heads=4, head_dim=256, rot=64, theta=1e7, page_size=64, max_tokens=128)
+    ref_stack = ostack.HybridStack(ow, kinds, **cfg)
+    gpu_stack = q35.layers.HybridStack(to_dev(kw), kinds, **cfg)
+    g = torch.Generator().manual_seed(4)
+    emb = (torch.randn((100, 5120), generator=g) * 0.05).to(torch.bfloat16)
+    ref, out = ref_stack.forward(emb[:96]), gpu_stack.forward(emb[:96].cuda())
+    assert cosine(out.cpu().float(), ref.float()) >= 0.999
+    for t in range(96, 100):
+        ref, out = ref_stack.forward(emb[t:t + 1]), gpu_stack.forward(emb[t:t + 1].cuda())
+        assert cosine(out.cpu().float(), ref.float()) >= 0.999, t
+
+
 def test_tensor_parallel_sublayers_two_ranks_emulated_on_one_gpu(q35):
     """heads / FFN columns split over 2 ranks (ax_dsl_kernels_b200/parallel.py); both ranks run one after the other on
     this GPU and the `reduce` hook of the second adds the first one's partial, which is what the all-reduce does"""

@@ -101,6 +101,12 @@ def test_moe_experts_partial_sums_for_expert_parallel(q35):
     q35.run("moe.experts", h2=h2.cuda(), ids=lids.cuda(), rw=rw.cuda(), e_gw=planes[0].cuda(), e_gs=planes[1].cuda(),
             e_dw=planes[2].cuda(), e_ds=planes[3].cuda(), partial_out=partial)
     assert_parity(partial.cpu(), ref)
+    # the same with GLOBAL ids and the first id of this rank's planes: bit-identical
+    partial2 = torch.full((T, 2048), float("nan")).cuda()
+    q35.run("moe.experts", h2=h2.cuda(), ids=ids.cuda(), rw=rw.cuda(), e_gw=planes[0].cuda(), e_gs=planes[1].cuda(),
+            e_dw=planes[2].cuda(), e_ds=planes[3].cuda(), expert_base=torch.tensor([lo], dtype=torch.int32).cuda(),
+            partial_out=partial2)
+    assert torch.equal(partial, partial2)
     none = torch.full_like(lids, -1).cuda()
     q35.run("moe.experts", h2=h2.cuda(), ids=none, rw=rw.cuda(), e_gw=planes[0].cuda(), e_gs=planes[1].cuda(),
             e_dw=planes[2].cuda(), e_ds=planes[3].cuda(), partial_out=partial)

@@ -29,9 +29,14 @@ class OracleEP(parallel.ExpertParallelMoE):
         deq = [codecs.dequant_mxfp4(w["w_" + n], w["s_" + n]) for n in ("gate", "up", "down")]
         base, h2, logits = omoe.moe_pre(x1, w["ln2"], *deq, w["w_router"], w["w_shg"])
         ids, rw = omoe.route(logits, self.top_k)
-        return base, h2, ids, rw
+        return base, h2, ids, rw, None
 
-    def _local_experts(self, h2_all, ids_local, rw_all):
+    def _finish(self, base, mine, out, ready):
+        out.copy_((base.float() + mine).to(out.dtype))
+        return out
+
+    def _local_experts(self, h2_all, ids_all, rw_all):
+        ids_local = parallel.local_ids(ids_all, self.lo, self.hi)
         w = self.w
         partial = torch.zeros(h2_all.shape)
         zero = torch.zeros_like(h2_all)
