@@ -1,5 +1,6 @@
 // Host-side plumbing shared by the kernel launchers: tensors bound by name, contract checks, error text.
 #pragma once
+#include <utility>
 #include <cuda_runtime.h>
 #include <cstdarg>
 #include <cstdint>
@@ -69,6 +70,22 @@ int* device_status_ptr();
     cudaError_t _e = cudaGetLastError();                                                   \
     if (_e != cudaSuccess) return ::q35::fail(Q35_ERR_CUDA, "%s: %s", what, cudaGetErrorString(_e)); \
   } while (0)
+
+// Launch with programmatic dependent launch allowed: the kernel's CTAs may become resident while the previous kernel
+// of the stream drains, and run up to their `pdl_wait()` (common.cuh) -- which EVERY kernel launched this way executes
+// before its first global memory access.  After anything that is not such a kernel the launch serialises as usual.
+// An error of the launch is left for Q35_CUDA_LAUNCH_CHECK.
+template <typename... KArgs, typename... Args>
+inline void launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                       Args&&... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr; cfg.numAttrs = 1;
+  cudaLaunchKernelEx(&cfg, kernel, KArgs(std::forward<Args>(args))...);
+}
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 

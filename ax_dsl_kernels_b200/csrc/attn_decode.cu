@@ -53,6 +53,8 @@ struct AttnArgs {
 
 // one CTA: context lengths, tiles per segment, exclusive prefix in (b, kvh) order
 __global__ void __launch_bounds__(1024) attn_plan_kernel(AttnArgs a) {
+  pdl_wait();
+  pdl_launch();
   __shared__ int s_part[1024];
   const int tid = threadIdx.x;
   const int per = (a.B + 1023) / 1024;
@@ -112,6 +114,8 @@ __device__ __forceinline__ uint32_t cvt_e4m3x2_f16x2(uint32_t two_bytes) {
 
 template <int D, bool FP8>
 __global__ void __launch_bounds__(128, 1) attn_decode_kernel(const AttnArgs a) {
+  pdl_wait();
+  pdl_launch();
   using C = AttnCfg<D, FP8>;
   constexpr int AT_STAGES = C::STAGES;
   extern __shared__ __align__(128) uint8_t smem[];
@@ -341,6 +345,8 @@ __global__ void __launch_bounds__(128, 1) attn_decode_kernel(const AttnArgs a) {
 // out[b, h] = merge of the partials of segment (b, h / G) (+ the current token's own k / v) -> bf16
 template <int D>
 __global__ void __launch_bounds__(D / 2) attn_merge_kernel(const AttnArgs a) {
+  pdl_wait();
+  pdl_launch();
   const int bh = blockIdx.x;
   const int b = bh / a.HQ, h = bh % a.HQ;
   const int kvh = h / a.G, gq = h % a.G;
@@ -458,11 +464,11 @@ static int launch_attn(const AttnArgs& a, cudaStream_t stream) {
     cudaFuncSetAttribute(attn_decode_kernel<D, FP8>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM);
     attr_done = true;
   }
-  attn_plan_kernel<<<1, 1024, 0, stream>>>(a);
+  launch_pdl(attn_plan_kernel, dim3(1), dim3(1024), 0, stream, a);
   Q35_CUDA_LAUNCH_CHECK("attn plan");
-  attn_decode_kernel<D, FP8><<<unsigned(a.n_cta), 128, C::SMEM, stream>>>(a);
+  launch_pdl(attn_decode_kernel<D, FP8>, dim3(unsigned(a.n_cta)), dim3(128), C::SMEM, stream, a);
   Q35_CUDA_LAUNCH_CHECK("attn decode");
-  attn_merge_kernel<D><<<unsigned(a.B * a.HQ), D / 2, 0, stream>>>(a);
+  launch_pdl(attn_merge_kernel<D>, dim3(unsigned(a.B * a.HQ)), dim3(D / 2), 0, stream, a);
   Q35_CUDA_LAUNCH_CHECK("attn merge");
   return 0;
 }

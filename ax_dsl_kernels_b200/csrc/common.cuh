@@ -24,6 +24,12 @@ __device__ __forceinline__ uint32_t pack_f16(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// Programmatic dependent launch (see launch_pdl in abi.h).  pdl_wait: returns once the previous kernel of the stream
+// has completed and its writes are visible; nothing in global memory may be touched before it.  pdl_launch: lets the
+// next kernel's CTAs become resident (they stop at their own pdl_wait until THIS grid has completed).
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ uint4 ldg_nc_16(const void* p) {
   uint4 v;
   asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"

@@ -20,6 +20,8 @@ __global__ void __launch_bounds__(128) gdn_step_kernel(const __nv_bfloat16* __re
                                                       const __nv_bfloat16* __restrict__ v, const float* __restrict__ g,
                                                       const __nv_bfloat16* __restrict__ beta, const float* state_in,
                                                       __nv_bfloat16* __restrict__ o, float* state_out, int NK, int NV) {
+  pdl_wait();
+  pdl_launch();
   const int bh = blockIdx.x;  // b * NV + vh
   const int b = bh / NV, vh = bh % NV;
   const int kh = vh / (NV / NK);
@@ -108,10 +110,9 @@ int run_gdn_step(Call& c) {
   c.ws_need = 0;
   if (c.dry || B * NV == 0) return 0;
   Q35_REQUIRE(aligned16(sin.p) && aligned16(sout.p) && aligned16(v.p), Q35_ERR_ALIGN, "gdn.step: 16-byte alignment");
-  gdn_step_kernel<<<unsigned(B * NV), 128, 0, c.stream>>>(q.as<__nv_bfloat16>(), k.as<__nv_bfloat16>(),
-                                                          v.as<__nv_bfloat16>(), g.as<float>(),
-                                                          beta.as<__nv_bfloat16>(), sin.as<float>(),
-                                                          o.as<__nv_bfloat16>(), sout.as<float>(), int(NK), int(NV));
+  launch_pdl(gdn_step_kernel, dim3(unsigned(B * NV)), dim3(128), 0, c.stream, q.as<__nv_bfloat16>(),
+             k.as<__nv_bfloat16>(), v.as<__nv_bfloat16>(), g.as<float>(), beta.as<__nv_bfloat16>(), sin.as<float>(),
+             o.as<__nv_bfloat16>(), sout.as<float>(), int(NK), int(NV));
   Q35_CUDA_LAUNCH_CHECK("gdn.step");
   return 0;
 }

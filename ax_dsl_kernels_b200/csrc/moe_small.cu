@@ -14,6 +14,8 @@ namespace q35 {
 template <int PER>
 __global__ void moe_route_kernel(const float* __restrict__ logits, int* __restrict__ ids, float* __restrict__ rw,
                                  int T, int NE, int K) {
+  pdl_wait();
+  pdl_launch();
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (warp >= T) return;
@@ -77,7 +79,8 @@ int run_moe_route(Call& c) {
   const int per = int((NE + 31) / 32);
   const unsigned blocks = unsigned((T + 3) / 4);
 #define Q35_ROUTE(P) \
-  moe_route_kernel<P><<<blocks, 128, 0, c.stream>>>(lg.as<float>(), ids.as<int>(), rw.as<float>(), int(T), int(NE), int(K))
+  launch_pdl(moe_route_kernel<P>, dim3(blocks), dim3(128), 0, c.stream, lg.as<float>(), ids.as<int>(), rw.as<float>(), \
+             int(T), int(NE), int(K))
   if (per <= 1) Q35_ROUTE(1);
   else if (per <= 2) Q35_ROUTE(2);
   else if (per <= 4) Q35_ROUTE(4);
@@ -228,6 +231,8 @@ int run_moe_permute(Call& c) {
 // expert-parallel form: partial[t] = sum over the pairs present on this rank (loc >= 0) of sout[loc[k, t]], fp32
 __global__ void __launch_bounds__(256) moe_partial_sum_kernel(const int* __restrict__ loc, const float* __restrict__ sout,
                                                               float* __restrict__ partial, int T, int H, int K, int R) {
+  pdl_wait();
+  pdl_launch();
   const int t = blockIdx.x;
   const int h = (blockIdx.y * blockDim.x + threadIdx.x) * 4;
   if (h >= H) return;
@@ -248,8 +253,8 @@ __global__ void __launch_bounds__(256) moe_partial_sum_kernel(const int* __restr
 
 int launch_partial_sum(const int* loc, const float* sout, float* partial, int T, int H, int K, int R,
                        cudaStream_t stream) {
-  moe_partial_sum_kernel<<<dim3(unsigned(T), unsigned((H / 4 + 255) / 256)), 256, 0, stream>>>(loc, sout, partial, T, H,
-                                                                                            K, R);
+  launch_pdl(moe_partial_sum_kernel, dim3(unsigned(T), unsigned((H / 4 + 255) / 256)), dim3(256), 0, stream, loc, sout,
+             partial, T, H, K, R);
   Q35_CUDA_LAUNCH_CHECK("moe partial sum");
   return 0;
 }

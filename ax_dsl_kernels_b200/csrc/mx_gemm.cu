@@ -135,6 +135,8 @@ __global__ void __launch_bounds__(1024) experts_plan_small_kernel(const int* __r
                                                                   const float* __restrict__ rw, int T, int K, int NE,
                                                                   int* g_expert, int* g_n, int* g_row0, int* src,
                                                                   float* rw_row, int* loc, int* active, int* status) {
+  pdl_wait();
+  pdl_launch();
   __shared__ __align__(16) int s_id[1024];
   __shared__ int s_cnt[1024];
   __shared__ int s_row0[1024];
@@ -265,11 +267,9 @@ int run_moe_experts(Call& c) {
 
   const bool small = P <= 1024 && NE <= 1024;
   if (small) {
-    experts_plan_small_kernel<<<1, 1024, 0, c.stream>>>(ids.as<int>(), ebase.present ? ebase.as<int>() : nullptr,
-                                                        rw.as<float>(), int(T), int(K), int(NE), g_expert,
-                                                        g_n, g_row0, src, rw_row, loc,
-                                                        use_tc ? tc_routed_active(qws, P, H, FE) : nullptr,
-                                                        device_status_ptr());
+    launch_pdl(experts_plan_small_kernel, dim3(1), dim3(1024), 0, c.stream, ids.as<int>(),
+               ebase.present ? ebase.as<int>() : nullptr, rw.as<float>(), int(T), int(K), int(NE), g_expert, g_n, g_row0,
+               src, rw_row, loc, use_tc ? tc_routed_active(qws, P, H, FE) : nullptr, device_status_ptr());
     Q35_CUDA_LAUNCH_CHECK("moe.experts plan");
   } else {
     if (partial.present) cudaMemsetAsync(loc, 0xff, size_t(P) * 4, c.stream);  // pairs of other ranks: loc = -1
@@ -411,6 +411,8 @@ int run_moe_slots(Call& c) {
 // h2 = RMSNorm(x1) * ln2; base = bf16(x1 + sigmoid(h2 . w_shg) * shared_expert(h2)); logits = h2 @ w_router^T (fp32).
 __global__ void __launch_bounds__(256) rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ w,
                                                       __nv_bfloat16* __restrict__ y, int H, float eps) {
+  pdl_wait();
+  pdl_launch();
   const int t = blockIdx.x, tid = threadIdx.x;
   const __nv_bfloat16* xr = x + size_t(t) * H;
   float ss = 0.f;
@@ -432,6 +434,8 @@ __global__ void __launch_bounds__(256) router_kernel(const __nv_bfloat16* __rest
                                                      const __nv_bfloat16* __restrict__ w_router,
                                                      const __nv_bfloat16* __restrict__ w_shg,
                                                      float* __restrict__ logits, float* __restrict__ gate, int H, int NE) {
+  pdl_wait();
+  pdl_launch();
   const int t = blockIdx.y;
   const int e = blockIdx.x * 8 + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
@@ -533,12 +537,12 @@ static int moe_pre_impl(Call& c, int mode) {
   if (do_norm) {
     // eps is a constant of the model family (1e-6 for every Qwen3.5 config)
     const float eps = 1e-6f;
-    rmsnorm_kernel<<<unsigned(T), 256, 0, c.stream>>>(x1.as<__nv_bfloat16>(), ln2.as<float>(),
-                                                      h2o.as<__nv_bfloat16>(), int(H), eps);
+    launch_pdl(rmsnorm_kernel, dim3(unsigned(T)), dim3(256), 0, c.stream, x1.as<__nv_bfloat16>(), ln2.as<float>(),
+               h2o.as<__nv_bfloat16>(), int(H), eps);
     Q35_CUDA_LAUNCH_CHECK("moe.pre rmsnorm");
-    router_kernel<<<dim3(unsigned((NE + 1 + 7) / 8), unsigned(T)), 256, 0, c.stream>>>(
-        h2o.as<__nv_bfloat16>(), wr.as<__nv_bfloat16>(), wshg.as<__nv_bfloat16>(), lgo.as<float>(), gate, int(H),
-        int(NE));
+    launch_pdl(router_kernel, dim3(unsigned((NE + 1 + 7) / 8), unsigned(T)), dim3(256), 0, c.stream,
+               h2o.as<__nv_bfloat16>(), wr.as<__nv_bfloat16>(), wshg.as<__nv_bfloat16>(), lgo.as<float>(), gate, int(H),
+               int(NE));
     Q35_CUDA_LAUNCH_CHECK("moe.pre router");
   }
   if (!do_shared) return 0;
@@ -597,6 +601,8 @@ int run_moe_shared(Call& c) { return moe_pre_impl(c, 2); }
 // with the routed terms added first)
 __global__ void moe_finish_kernel(const __nv_bfloat16* __restrict__ base, const float* __restrict__ partial,
                                   __nv_bfloat16* __restrict__ out, long long n) {
+  pdl_wait();
+  pdl_launch();
   const long long i = (long long)(blockIdx.x * blockDim.x + threadIdx.x) * 4;
   if (i >= n) return;
   const uint2 b = *reinterpret_cast<const uint2*>(base + i);
@@ -617,8 +623,8 @@ int run_moe_finish(Call& c) {
   c.ws_need = 0;
   if (c.dry || n == 0) return 0;
   Q35_REQUIRE(aligned16(base.p) && aligned16(partial.p) && aligned16(out.p), Q35_ERR_ALIGN, "moe.finish: alignment");
-  moe_finish_kernel<<<unsigned((n / 4 + 255) / 256), 256, 0, c.stream>>>(base.as<__nv_bfloat16>(), partial.as<float>(),
-                                                                        out.as<__nv_bfloat16>(), n);
+  launch_pdl(moe_finish_kernel, dim3(unsigned((n / 4 + 255) / 256)), dim3(256), 0, c.stream, base.as<__nv_bfloat16>(),
+             partial.as<float>(), out.as<__nv_bfloat16>(), n);
   Q35_CUDA_LAUNCH_CHECK("moe.finish");
   return 0;
 }

@@ -58,6 +58,8 @@ __global__ void __launch_bounds__(256) tc_quant_kernel(const __nv_bfloat16* __re
                                                        const int* __restrict__ src, int x_rows, int R, int K,
                                                        uint8_t* __restrict__ qh, uint8_t* __restrict__ ql,
                                                        uint8_t* __restrict__ sh, uint8_t* __restrict__ sl) {
+  pdl_wait();
+  pdl_launch();
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;  // index of the 8-element piece
   const int per_row = K / 8;
   const bool on = i < (long long)R * per_row;  // whole quads are on or off together (K is a multiple of 32)
@@ -120,8 +122,8 @@ int tc_quantize(const __nv_bfloat16* x, int x_stride, const int* src, int x_rows
   if (pieces == 0) return 0;
   Q35_REQUIRE(K % 32 == 0 && x_stride % 8 == 0 && (uintptr_t(x) & 15) == 0, Q35_ERR_ALIGN,
               "tc quantize: rows must start on 16-byte boundaries");
-  tc_quant_kernel<<<unsigned((pieces + 255) / 256), 256, 0, stream>>>(x, x_stride, src, x_rows, R, K, q.qh, q.ql, q.sh,
-                                                                    q.sl);
+  launch_pdl(tc_quant_kernel, dim3(unsigned((pieces + 255) / 256)), dim3(256), 0, stream, x, x_stride, src, x_rows, R, K,
+             q.qh, q.ql, q.sh, q.sl);
   Q35_CUDA_LAUNCH_CHECK("tc quantize");
   return 0;
 }
@@ -198,7 +200,7 @@ static int launch_nb(const CUtensorMap& w0, const CUtensorMap& w1, const CUtenso
   const long long items = (long long)tiles * (a.g_n ? groups : (a.n_dense + a.dense_rows - 1) / a.dense_rows);
   const long long slots = (long long)tc_sm_count() * TcCfg<NB>::CTAS_PER_SM;
   const unsigned grid = unsigned(items < slots ? items : slots);
-  tc_gemm_kernel<NB, EPI><<<grid, TcCfg<NB>::THREADS, smem, stream>>>(w0, w1, xh, xl, a);
+  launch_pdl(tc_gemm_kernel<NB, EPI>, dim3(grid), dim3(TcCfg<NB>::THREADS), size_t(smem), stream, w0, w1, xh, xl, a);
   Q35_CUDA_LAUNCH_CHECK("tc gemm");
   return 0;
 }

@@ -134,9 +134,6 @@ __global__ void __launch_bounds__(TcCfg<NB>::THREADS, TcCfg<NB>::CTAS_PER_SM) tc
   using namespace tc;
   extern __shared__ uint8_t smem_raw[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int n_items = (a.g_n ? a.n_active[0] : (a.n_dense + a.dense_rows - 1) / a.dense_rows) * a.n_tiles;
-  if (int(blockIdx.x) >= n_items) return;
-
   const int KS = a.K / 128;
   const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* sgen = smem_raw + (sbase - smem_u32(smem_raw));
@@ -168,6 +165,11 @@ __global__ void __launch_bounds__(TcCfg<NB>::THREADS, TcCfg<NB>::CTAS_PER_SM) tc
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *g_slot;
+  // everything above touches only this CTA's shared and tensor memory and may overlap the previous kernel's tail
+  pdl_wait();
+  pdl_launch();
+  // a CTA without work walks empty loops and falls through to the release of its tensor memory
+  const int n_items = (a.g_n ? a.n_active[0] : (a.n_dense + a.dense_rows - 1) / a.dense_rows) * a.n_tiles;
 
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
