@@ -212,7 +212,7 @@ def run_ours(args):
             "gpu_launches": args.steps * (18 if world * B * TOPK <= 1024 else 20),
             "roofline": {"bound": "hbm", "kernel": "attn_decode_kernel<256,bf16> (+ plan and merge launches)",
                          "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "peak_source": peak_src, "traffic": None, "algorithmic_bytes": wl.attn_bytes(),
+                         "peak_source": peak_src, "traffic": attn_traffic(wl), "algorithmic_bytes": wl.attn_bytes(),
                          "ms_per_launch": attn_ms},
             "clocks": clocks.summary() if clocks else None,
             "device_status": status,
@@ -222,6 +222,16 @@ def run_ours(args):
         print(json.dumps(line), flush=True)
     if dist is not None:
         dist.destroy_process_group()
+
+
+def attn_traffic(wl):
+    """DRAM bytes of one attention decode launch, scaled from the ncu capture of the capture-sized case
+    (profiles/attn_decode_bf16_b16_ctx8192.md: 268.70 MB read for 268.44 MB of K/V, i.e. every byte once; writes = the
+    split-KV partials, one [m, l, O] per (segment or CTA, warp, query head of the group)).  Reads grow in proportion to
+    the K/V bytes, the partials with the number of segments."""
+    reads = wl.attn_bytes() * (268.70 / 268.44)
+    partials = (B * HKV + 148) * 4 * (HQ // HKV) * (D + 2) * 4
+    return int(reads + partials)
 
 
 # ----------------------------------------------------------------------------------------------------------------
