@@ -113,5 +113,6 @@ int run_attn_qk_prep(Call&);
 int run_act_silu_mul(Call&);
 int run_act_sigmoid_gate(Call&);
 int run_linear_tc(Call&);
+int run_lm_head(Call&);
 
 }  // namespace q35

@@ -356,20 +356,29 @@ __global__ void __launch_bounds__(D / 2) attn_merge_kernel(const AttnArgs a) {
   const int seg0 = a.seg_start[s], seg1 = a.seg_start[s + 1];
   float M = -INFINITY, L = 0.f, o0 = 0.f, o1 = 0.f;
   if (seg1 > seg0) {
-    const int i0 = seg0 / q_per, i1 = (seg1 - 1) / q_per;
-    for (int i = i0; i <= i1; ++i) {
-      for (int w = 0; w < 4; ++w) {
-        const size_t slot = size_t(s + i) * 4 + w;
-        const float m = a.part_ml[slot * 16 + gq];
-        const float l = a.part_ml[slot * 16 + 8 + gq];
-        if (l <= 0.f || m == -INFINITY) continue;
-        const float mn = fmaxf(M, m);
-        const float fa = exp2f(M - mn), fb = exp2f(m - mn);
-        const float2 po = *reinterpret_cast<const float2*>(a.part_o + slot * (AT_GMAX * D) + gq * D + 2 * tid);
-        L = L * fa + l * fb;
-        o0 = o0 * fa + po.x * fb;
-        o1 = o1 * fa + po.y * fb;
-        M = mn;
+    // Two passes so that no load waits for arithmetic on the previous one: first the maximum over the segment's
+    // partials, then every partial scaled by exp2(m - M) and added (slots: 4 warps of each CTA that touched it).
+    const size_t slot0 = (size_t(s) + seg0 / q_per) * 4;
+    const int ns = ((seg1 - 1) / q_per - seg0 / q_per + 1) * 4;
+#pragma unroll 4
+    for (int j = 0; j < ns; ++j) {
+      const float m = a.part_ml[(slot0 + j) * 16 + gq];
+      const float l = a.part_ml[(slot0 + j) * 16 + 8 + gq];
+      if (l > 0.f) M = fmaxf(M, m);
+    }
+    if (M != -INFINITY) {
+#pragma unroll 4
+      for (int j = 0; j < ns; ++j) {
+        const float m = a.part_ml[(slot0 + j) * 16 + gq];
+        const float l = a.part_ml[(slot0 + j) * 16 + 8 + gq];
+        const bool on = l > 0.f && m != -INFINITY;
+        // an unused slot may hold anything: it is not read, not multiplied by zero
+        const float2 po = on ? *reinterpret_cast<const float2*>(a.part_o + (slot0 + j) * (AT_GMAX * D) + gq * D + 2 * tid)
+                             : make_float2(0.f, 0.f);
+        const float fb = on ? exp2f(m - M) : 0.f;
+        L += on ? l * fb : 0.f;
+        o0 += po.x * fb;
+        o1 += po.y * fb;
       }
     }
   }

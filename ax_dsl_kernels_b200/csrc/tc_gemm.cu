@@ -243,6 +243,23 @@ template int tc_launch<TC_EPI_PLAIN>(const TcWeights&, const TcQuant&, TcArgs, i
 // ---------------------------------------------------------------------------------------------------------------
 // linear.tc: out[t, n] = x[t, :] . dequant_mxfp4(w[n, :]) on the tensor cores (same contract as `linear` with MXFP4
 // weights; reference: linear(x, w, s) of the MX projections, models/qwen35_2b/whole/src/q35_mx_build.py:100-115)
+// shared by linear.tc and lm_head: quantise x into the workspace and run the plain-epilogue GEMM
+static int linear_tc_impl(const Tensor& x, const Tensor& w, const Tensor& s, const float* bias, float* f_out,
+                          __nv_bfloat16* b_out, uint8_t* qws, int64_t T, int64_t N, int64_t K, cudaStream_t stream) {
+  const TcQuant q = tc_quant_carve(qws, T, K);
+  Q35_TRY(tc_quantize(x.as<__nv_bfloat16>(), int(K), nullptr, int(T), int(T), int(K), q, stream));
+  TcWeights tw{{w.as<uint8_t>(), w.as<uint8_t>()}, {uint64_t(N), uint64_t(N)}};
+  TcArgs a{};
+  a.n_dense = int(T); a.n_planes = 1; a.K = int(K);
+  a.plane_rows[0] = a.plane_rows[1] = int(N);
+  a.roff[0] = 0; a.roff[1] = 64; a.lim[0] = a.lim[1] = int(N); a.tile_rows = 128;
+  a.sw[0] = a.sw[1] = s.as<uint8_t>(); a.s_plane = 0;
+  a.f_out = f_out; a.b_out = b_out;
+  a.out_stride = int(N);
+  a.bias = bias;
+  return tc_launch<TC_EPI_PLAIN>(tw, q, a, int(T), int((N + 127) / 128), 1, stream);
+}
+
 int run_linear_tc(Call& c) {
   Tensor x, w, s, bias, out, ws;
   Q35_TRY(c.get("x", M(Q35_BF16), &x));
@@ -257,18 +274,70 @@ int run_linear_tc(Call& c) {
   Q35_TRY(c.workspace(tc_quant_bytes(T, K), &ws));
   if (c.dry || T == 0 || N == 0) return 0;
   Q35_REQUIRE((uintptr_t(w.p) & 31) == 0 && aligned16(x.p) && aligned16(s.p), Q35_ERR_ALIGN, "linear.tc: alignment");
-  const TcQuant q = tc_quant_carve(ws.as<uint8_t>(), T, K);
-  Q35_TRY(tc_quantize(x.as<__nv_bfloat16>(), int(K), nullptr, int(T), int(T), int(K), q, c.stream));
-  TcWeights tw{{w.as<uint8_t>(), w.as<uint8_t>()}, {uint64_t(N), uint64_t(N)}};
-  TcArgs a{};
-  a.n_dense = int(T); a.n_planes = 1; a.K = int(K);
-  a.plane_rows[0] = a.plane_rows[1] = int(N);
-  a.roff[0] = 0; a.roff[1] = 64; a.lim[0] = a.lim[1] = int(N); a.tile_rows = 128;
-  a.sw[0] = a.sw[1] = s.as<uint8_t>(); a.s_plane = 0;
-  if (out.dtype == Q35_F32) a.f_out = out.as<float>(); else a.b_out = out.as<__nv_bfloat16>();
-  a.out_stride = int(N);
-  a.bias = bias.present ? bias.as<float>() : nullptr;
-  return tc_launch<TC_EPI_PLAIN>(tw, q, a, int(T), int((N + 127) / 128), 1, c.stream);
+  return linear_tc_impl(x, w, s, bias.present ? bias.as<float>() : nullptr,
+                        out.dtype == Q35_F32 ? out.as<float>() : nullptr,
+                        out.dtype == Q35_F32 ? nullptr : out.as<__nv_bfloat16>(), ws.as<uint8_t>(), T, N, K, c.stream);
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// lm_head: fp32 logits of the MXFP4 output projection and / or the greedy token per row.
+// Reference: mul_mat_mx4 (models/qwen35_2b/whole/src/q35_layer_mc.py:741-758: x [1, K] bf16 x w [N, K] fp4 + s -> f32
+// logits), golden torch_logits (models/qwen38_27b/head/mx4_common.py:62-69); the token is the first index of the
+// row's maximum, as torch.argmax gives the reference's host code.
+__global__ void __launch_bounds__(1024) argmax_rows_kernel(const float* __restrict__ logits, int N, int* __restrict__ token) {
+  pdl_wait();
+  pdl_launch();
+  const float* row = logits + size_t(blockIdx.x) * N;
+  float best = -INFINITY;
+  int at = 0x7fffffff;
+  for (int i = threadIdx.x; i < N; i += 1024) {  // ascending i per thread: strict > keeps the first maximum
+    const float v = row[i];
+    if (v > best || (v == best && i < at)) { best = v; at = i; }
+  }
+  __shared__ float s_v[32];
+  __shared__ int s_i[32];
+  auto merge = [](float& v, int& i, float ov, int oi) {
+    if (ov > v || (ov == v && oi < i)) { v = ov; i = oi; }
+  };
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1)
+    merge(best, at, __shfl_xor_sync(0xffffffffu, best, o), __shfl_xor_sync(0xffffffffu, at, o));
+  if ((threadIdx.x & 31) == 0) { s_v[threadIdx.x >> 5] = best; s_i[threadIdx.x >> 5] = at; }
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    best = s_v[threadIdx.x]; at = s_i[threadIdx.x];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+      merge(best, at, __shfl_xor_sync(0xffffffffu, best, o), __shfl_xor_sync(0xffffffffu, at, o));
+    if (threadIdx.x == 0) token[blockIdx.x] = at == 0x7fffffff ? 0 : at;  // a row of NaNs: token 0
+  }
+}
+
+int run_lm_head(Call& c) {
+  Tensor x, w, s, logits, token, ws;
+  Q35_TRY(c.get("x", M(Q35_BF16), &x));
+  Q35_TRY(c.get("w", M_BYTES, &w));
+  Q35_TRY(c.get("s", M(Q35_U8), &s));
+  Q35_TRY(c.get("logits", M(Q35_F32), &logits, false));
+  Q35_TRY(c.get("token", M(Q35_I32), &token, false));
+  Q35_REQUIRE(logits.present || token.present, Q35_ERR_MISSING, "lm_head: give logits, token or both");
+  Q35_REQUIRE(x.nd >= 2 && w.nd == 2, Q35_ERR_SHAPE, "lm_head: x [T, K], w [N, K/2]");
+  const int64_t K = x.s[x.nd - 1], T = x.numel() / K, N = w.s[0];
+  Q35_REQUIRE(w.s[1] == K / 2 && s.numel() == N * (K / 32), Q35_ERR_SHAPE, "lm_head: w [N, K/2], s [N, K/32]");
+  Q35_REQUIRE((!logits.present || logits.numel() == T * N) && (!token.present || token.numel() == T), Q35_ERR_SHAPE,
+              "lm_head: logits [T, N], token [T]");
+  Q35_REQUIRE(K % 512 == 0, Q35_ERR_UNSUPPORTED, "lm_head: K must be a multiple of 512");
+  const int64_t qb = (tc_quant_bytes(T, K) + 255) / 256 * 256;
+  Q35_TRY(c.workspace(qb + (logits.present ? 0 : T * N * 4), &ws));
+  if (c.dry || T == 0 || N == 0) return 0;
+  Q35_REQUIRE((uintptr_t(w.p) & 31) == 0 && aligned16(x.p) && aligned16(s.p), Q35_ERR_ALIGN, "lm_head: alignment");
+  float* lg = logits.present ? logits.as<float>() : reinterpret_cast<float*>(ws.as<uint8_t>() + qb);
+  Q35_TRY(linear_tc_impl(x, w, s, nullptr, lg, nullptr, ws.as<uint8_t>(), T, N, K, c.stream));
+  if (token.present) {
+    launch_pdl(argmax_rows_kernel, dim3(unsigned(T)), dim3(1024), 0, c.stream, lg, int(N), token.as<int>());
+    Q35_CUDA_LAUNCH_CHECK("lm_head argmax");
+  }
+  return 0;
 }
 
 }  // namespace q35

@@ -144,3 +144,19 @@ def linear(x, w, s, out=None, bias=None, out_dtype=torch.bfloat16, row_div=None,
         kw["residual"] = residual
     _lib.run("linear", **kw)
     return out
+
+
+def lm_head(x, w, s, logits=None, token=None, want_logits=True, want_token=True):
+    """MXFP4 output projection: fp32 logits [T, N] and / or the greedy token [T] (first index of the row maximum).
+    Reference: mul_mat_mx4 (models/qwen35_2b/whole/src/q35_layer_mc.py:741-758), golden torch_logits
+    (models/qwen38_27b/head/mx4_common.py:62-69).  K must be a multiple of 512."""
+    T, N = x.shape[0], w.shape[0]
+    kw = dict(x=x, w=w, s=_u8(s))
+    if want_logits or logits is not None:
+        logits = torch.empty((T, N), dtype=torch.float32, device=x.device) if logits is None else logits
+        kw["logits"] = logits
+    if want_token or token is not None:
+        token = torch.empty((T,), dtype=torch.int32, device=x.device) if token is None else token
+        kw["token"] = token
+    _lib.run("lm_head", **kw)
+    return logits, token

@@ -375,6 +375,16 @@ def run_profile_case(name, reps):
         out = torch.empty_like(x1)
         fn = lambda: q35.moe_block(x1, wl.w, TOPK, out)  # noqa: E731
         units = T
+    elif name == "lm_head":  # MXFP4 output projection 248320 x 2048 (254 MB codes + 16 MB scales) on one token row
+        from ax_dsl_kernels_b200.moe import lm_head
+        N = 248320
+        pk = torch.randint(0, 256, (N, H // 2), generator=g, device=dev, dtype=torch.uint8)
+        sc = torch.randint(119, 128, (N, H // 32), generator=g, device=dev, dtype=torch.uint8)
+        x = rn(1, H).to(bf)
+        logits = torch.empty((1, N), dtype=torch.float32, device=dev)
+        token = torch.empty((1,), dtype=torch.int32, device=dev)
+        fn = lambda: lm_head(x, pk, sc, logits, token)  # noqa: E731
+        units = 1
     else:
         wl = Workload(dev, seed=1, attn=(name == "attn"))
         units = B
@@ -406,7 +416,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
     ap.add_argument("--no-graph", action="store_true", help="launch the timed steps eagerly instead of replaying a CUDA graph")
-    ap.add_argument("--profile-case", choices=["attn", "gdn", "moe", "gdn_prefill", "attn_prefill", "moe_prefill"], help="run one kernel on a capture-sized case")
+    ap.add_argument("--profile-case", choices=["attn", "gdn", "moe", "gdn_prefill", "attn_prefill", "moe_prefill", "lm_head"], help="run one kernel on a capture-sized case")
     args = ap.parse_args()
     if args.profile_case:
         run_profile_case(args.profile_case, max(1, min(args.steps, 5)))

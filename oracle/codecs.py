@@ -124,3 +124,29 @@ def kv_dequant_fp8(c, scale=None):
     if scale is None:
         return c.float() / KV8_SCALE
     return c.float() * scale.float().reshape(*([1] * (c.dim() - 2)), -1, 1)
+
+
+def quant_mxfp4_head(w):
+    """MXFP4 as the output-projection tools pack it (models/qwen38_27b/head/mx4_common.py:11-36): the same rule as
+    quant_mxfp4 with the scale byte clamped to [0, 254] (0xFF is the E8M0 NaN)."""
+    w = w.float()
+    n, k = w.shape
+    g = w.reshape(n, k // 32, 32)
+    amax = g.abs().amax(-1)
+    e = torch.where(amax > 0, torch.floor(torch.log2(amax.clamp_min(1e-30))) - 2, torch.zeros_like(amax))
+    x = g / torch.exp2(e).unsqueeze(-1)
+    lut = torch.tensor([0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0])
+    best = (x.abs().unsqueeze(-1) - lut).abs().argmin(-1).to(torch.uint8)  # ties go to the lower code
+    code = best | ((x < 0).to(torch.uint8) << 3)
+    packed = (code[..., 0::2] | (code[..., 1::2] << 4)).reshape(n, k // 2)
+    return packed.contiguous(), (e + 127).clamp(0, 254).to(torch.uint8).contiguous()
+
+
+def lm_head_logits(x, packed, scale):
+    """fp32 logits x @ dequant(w)^T and the greedy token (first index of the maximum): torch_logits,
+    models/qwen38_27b/head/mx4_common.py:62-69; the kernel role is mul_mat_mx4
+    (models/qwen35_2b/whole/src/q35_layer_mc.py:741-758)."""
+    logits = torch.empty((x.shape[0], packed.shape[0]), dtype=torch.float32)
+    for r0 in range(0, packed.shape[0], 8192):  # row chunks, as the reference does, to keep the temporaries small
+        logits[:, r0:r0 + 8192] = x.float() @ dequant_mxfp4(packed[r0:r0 + 8192], scale[r0:r0 + 8192]).T
+    return logits, logits.argmax(-1).to(torch.int32)

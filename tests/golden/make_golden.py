@@ -69,7 +69,25 @@ def save(name, d):
     print("wrote", name, {k: tuple(np.asarray(v).shape) for k, v in pack(d).items()})
 
 
+def lm_head():
+    """7. MXFP4 output projection: head-variant codec and logits golden (models/qwen38_27b/head/mx4_common.py:11-69)"""
+    sys.path.insert(0, os.path.join(REF, "models/qwen38_27b/head"))
+    import mx4_common as hc
+    g = torch.Generator().manual_seed(21)
+    w = torch.randn((160, 512), generator=g) * 0.02
+    w[5, :32] = 0                      # a zero block: exponent 0 -> byte 127
+    w[6] *= 2.0 ** 100                 # large: clamps nowhere near 254 but exercises big exponents
+    w[7, 32:64] = 3e-39                # amax below the reference's floor of 1e-30: scale byte 25
+    pk, sc = hc.quantize_mxfp4(w)
+    x = torch.randn((3, 512), generator=g).to(torch.bfloat16)
+    logits = hc.torch_logits(x.float(), pk, sc)
+    save("lm_head", dict(w=w, packed=pk, scale=sc, dequant=hc.dequantize_mxfp4(pk, sc), x=x, logits=logits,
+                         token=logits.argmax(-1).to(torch.int32)))
+
+
 def main():
+    if "--only-lm-head" in sys.argv:
+        return lm_head()
     sys.meta_path.insert(0, _Finder())
     sgl = os.path.join(REF, "models/qwen35_35b_a3b/sgl")
     sys.path[:0] = [os.path.join(sgl, "python"), os.path.join(sgl, "tests"),
@@ -146,6 +164,7 @@ def main():
     d = dict(hidden=hs, residual=res, temporal_state=ts, conv_state=cs, fused=fused, state_out=st_out, conv_out=cv_out)
     d.update({"w." + n: t for n, t in wts.items()})
     save("gdn_sublayer", d)
+    lm_head()
 
 
 if __name__ == "__main__":

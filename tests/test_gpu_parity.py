@@ -462,3 +462,30 @@ def test_paged_prefill_writes_new_rows_then_decode_continues(q35):
     qd = torch.randn((2, 16, 256), generator=g).to(torch.bfloat16)
     dec = q35.paged_attention_decode(qd.cuda(), gcache, indptr.cuda(), indices.cuda(), last.cuda())
     assert_parity(dec.cpu(), oattn.paged_decode(qd, ref_cache, indptr, indices, last))
+
+
+def test_lm_head_golden_fixture_and_vocabulary_sized(q35, golden):
+    """MXFP4 output projection (mul_mat_mx4 / torch_logits): the reference fixture, then a vocabulary-sized matrix"""
+    from ax_dsl_kernels_b200.moe import lm_head
+    f = golden("lm_head")
+    logits, token = lm_head(f["x"].cuda(), f["packed"].cuda(), f["scale"].cuda())
+    assert rel_rms_err(logits.cpu(), f["logits"]) <= 2e-2
+    assert torch.equal(token.cpu(), f["token"])
+    # token without logits: same answer
+    _, tok2 = lm_head(f["x"].cuda(), f["packed"].cuda(), f["scale"].cuda(), want_logits=False)
+    assert torch.equal(tok2, token)
+    # 248320 x 2048 as the 35B head, 2 rows; the token must be the argmax of the kernel's own logits, and the golden's
+    # token wherever the golden's top-2 margin exceeds the kernel's error
+    g = torch.Generator().manual_seed(8)
+    N, K = 248320, 2048
+    pk, sc = codecs.random_mxfp4((N, K), g, -8, 0)
+    x = torch.randn((2, K), generator=g).to(torch.bfloat16)
+    ref, ref_tok = codecs.lm_head_logits(x, pk, sc)
+    logits, token = lm_head(x.cuda(), pk.cuda(), sc.cuda())
+    assert rel_rms_err(logits.cpu(), ref) <= 2e-2
+    assert torch.equal(token.cpu(), logits.argmax(-1).to(torch.int32).cpu())
+    top2 = ref.topk(2, -1).values
+    err = (logits.cpu() - ref).abs().max(-1).values
+    for r in range(2):
+        if float(top2[r, 0] - top2[r, 1]) > 2 * float(err[r]):
+            assert int(token[r]) == int(ref_tok[r])

@@ -81,3 +81,14 @@ def test_gdn_recurrence_close_to_float64():
     o64, s64 = gdn.recurrent_f64(q, k, v, gg, beta, s0)
     assert (o.double() - o64).abs().max() / o64.square().mean().sqrt() < 0.1
     assert (s.double() - s64).abs().max() < 2e-2
+
+
+def test_lm_head_codec_and_logits_match_reference(golden):
+    f = golden("lm_head")
+    pk, sc = codecs.quant_mxfp4_head(f["w"])
+    assert torch.equal(pk, f["packed"]) and torch.equal(sc, f["scale"])
+    assert int(sc.min()) == 25  # amax below 1e-30 counts as 1e-30 in the reference: floor(log2 1e-30) - 2 + 127
+    assert torch.equal(codecs.dequant_mxfp4(f["packed"], f["scale"]), f["dequant"])
+    logits, token = codecs.lm_head_logits(f["x"], f["packed"], f["scale"])
+    torch.testing.assert_close(logits, f["logits"], rtol=1e-5, atol=1e-5 * float(f["logits"].abs().max()))
+    assert torch.equal(token, f["token"])
