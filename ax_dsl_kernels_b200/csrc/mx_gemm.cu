@@ -81,13 +81,9 @@ static int tc_routed(const ExpertPlanes& e, const __nv_bfloat16* x, int x_rows, 
   a.roff[0] = 0; a.roff[1] = int(e.FE); a.lim[0] = int(e.FE); a.lim[1] = int(2 * e.FE); a.tile_rows = 64;
   a.sw[0] = a.sw[1] = e.gs; a.s_plane = 2 * e.FE * (e.H / 32);
   a.act_rows = int(e.FE); a.act_out = act;
-  // decode-sized: the gate-up epilogue writes the down projection's operand directly (one launch and one round trip
-  // of the activation less); at prefill size the epilogue is the bottleneck of that GEMM and the separate pass wins
-  const bool fuse_quant = R <= 1024;
-  if (fuse_quant) { a.q_hi = q2.qh; a.q_lo = q2.ql; a.q_sh = q2.sh; a.q_sl = q2.sl; }
   const TcWeights wg{{e.gw, e.gw}, {uint64_t(e.NE * 2 * e.FE), uint64_t(e.NE * 2 * e.FE)}};
   Q35_TRY(tc_launch<TC_EPI_SILU_MUL>(wg, q1, a, nb, int(e.FE / 64), groups, stream));
-  if (!fuse_quant) Q35_TRY(tc_quantize(act, int(e.FE), nullptr, R, R, int(e.FE), q2, stream));
+  Q35_TRY(tc_quantize(act, int(e.FE), nullptr, R, R, int(e.FE), q2, stream));
   TcArgs d{};
   d.n_active = active; d.active = active + 1;
   d.g_expert = g_expert; d.g_n = g_n; d.g_row0 = g_row0; d.n_planes = int(e.NE);
@@ -560,11 +556,9 @@ static int moe_pre_impl(Call& c, int mode) {
     ta.roff[0] = ta.roff[1] = 0; ta.lim[0] = ta.lim[1] = int(FS); ta.tile_rows = 64;
     ta.sw[0] = sg.as<uint8_t>(); ta.sw[1] = su.as<uint8_t>(); ta.s_plane = 0;
     ta.act_rows = int(FS); ta.act_out = act;
-    const bool fuse_quant = T <= 1024;  // as in tc_routed
-    if (fuse_quant) { ta.q_hi = q2.qh; ta.q_lo = q2.ql; ta.q_sh = q2.sh; ta.q_sl = q2.sl; }
     const TcWeights wgu{{wg.as<uint8_t>(), wu.as<uint8_t>()}, {uint64_t(FS), uint64_t(FS)}};
     Q35_TRY(tc_launch<TC_EPI_SILU_MUL>(wgu, q1, ta, int(T), int(FS / 64), 1, c.stream));
-    if (!fuse_quant) Q35_TRY(tc_quantize(act, int(FS), nullptr, int(T), int(T), int(FS), q2, c.stream));
+    Q35_TRY(tc_quantize(act, int(FS), nullptr, int(T), int(T), int(FS), q2, c.stream));
     TcArgs td{};
     td.n_dense = int(T); td.n_planes = 1; td.K = int(FS);
     td.plane_rows[0] = td.plane_rows[1] = int(H);

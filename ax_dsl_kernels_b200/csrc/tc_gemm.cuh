@@ -19,6 +19,8 @@
 //             fence and a barrier per stage in a serial chain, -15 %); scales written straight to tensor memory with
 //             tcgen05.st (cheap by itself, but it leaves too few registers to keep enough loads in flight with two
 //             CTAs per SM); asking the TMA unit to prefetch weight tiles into L2 ahead of the ring (-20 %).
+//             Also measured and dropped: quantising the SiLU x up activation for the down projection inside this
+//             kernel's epilogue instead of in a pass of its own made the decode step 18 us slower.
 // Accumulators [128 lanes x 2 NB columns] are double-buffered; every hand-over is an mbarrier.  A stage carries only
 // 8 KB of HBM bytes (the unpacked FP4 tile takes 16 KB of shared memory), so the ring is made as deep as shared memory
 // allows.  Without the scale path the same pipeline streams weights at 6.3 TB/s; with it, 5.4 TB/s.
@@ -28,16 +30,6 @@
 namespace q35 {
 
 enum : int { TC_EPI_SILU_MUL = 0, TC_EPI_ROW_SCALE = 1, TC_EPI_SHARED_DOWN = 2, TC_EPI_PLAIN = 3 };
-
-// UE8M0 exponent of a block of the two-term activation format: the smallest e with amax * 2^-e <= 448
-__device__ __forceinline__ int e8m0_for(float amax) {  // 448 = 1.75 * 2^8
-  if (amax == 0.f) return -127;
-  const uint32_t b = __float_as_uint(amax);
-  const int E = int(b >> 23) - 127;
-  const uint32_t mant = b & 0x7fffffu;
-  int e = E - 8 + (mant > 0x600000u ? 1 : 0);  // mantissa above 1.75 needs one more octave
-  return max(-127, min(127, e));
-}
 
 struct TcArgs {
   // groups: nullptr g_n = one dense group of n_dense rows on plane 0
@@ -56,9 +48,6 @@ struct TcArgs {
   // epilogue
   int act_rows;             // TC_EPI_SILU_MUL: row stride of act_out
   __nv_bfloat16* act_out;
-  // TC_EPI_SILU_MUL, optional: the activation leaves the epilogue already in the two-term E4M3 form the next GEMM
-  // reads ([R, act_rows] bytes per term, scales [R, act_rows / 32]); act_out is then not written
-  uint8_t* q_hi; uint8_t* q_lo; uint8_t* q_sh; uint8_t* q_sl;
   float* f_out; __nv_bfloat16* b_out; int out_stride;
   const float* rw_row; const __nv_bfloat16* resid; const float* gate; const float* bias;
   const int* active; const int* n_active;  // compacted list of groups with rows (nullptr: dense)
@@ -369,30 +358,10 @@ __global__ void __launch_bounds__(TcCfg<NB>::THREADS, TcCfg<NB>::CTAS_PER_SM) tc
 #pragma unroll
               for (int jj = 0; jj < 16; ++jj) {
                 const int t = t0 + c0 + jj;
-                if (t >= im.n) continue;  // uniform over the warp
-                const float g = round_bf16(hi[jj]), u = __bfloat162float(g_xch[jj * 64 + r]);
-                const __nv_bfloat16 act = __float2bfloat16_rn(g / (1.0f + expf(-g)) * u);
-                if (!a.q_hi) {
-                  if (rvalid) a.act_out[(long long)(im.row0 + t) * a.act_rows + row] = act;
-                  continue;
-                }
-                // the warp's 32 rows are one block of 32 along the next GEMM's contraction: quantise it here, with the
-                // arithmetic of tc_quant_kernel (bit-identical result)
-                const float v = rvalid ? __bfloat162float(act) : 0.f;
-                const int eh = e8m0_for(warp_max(fabsf(v)));
-                const __nv_fp8_e4m3 qh(v * exp2f(float(-eh)));
-                const float rem = v - float(qh) * exp2f(float(eh));
-                const int el = e8m0_for(warp_max(fabsf(rem)));
-                const __nv_fp8_e4m3 ql(rem * exp2f(float(-el)));
-                if (rvalid) {
-                  const long long o = (long long)(im.row0 + t) * a.act_rows + row;
-                  a.q_hi[o] = *reinterpret_cast<const uint8_t*>(&qh);
-                  a.q_lo[o] = *reinterpret_cast<const uint8_t*>(&ql);
-                  if (lane == 0) {
-                    const long long so = (long long)(im.row0 + t) * (a.act_rows / 32) + row / 32;
-                    a.q_sh[so] = uint8_t(eh + 127);
-                    a.q_sl[so] = uint8_t(el + 127);
-                  }
+                if (t < im.n && rvalid) {
+                  const float g = round_bf16(hi[jj]), u = __bfloat162float(g_xch[jj * 64 + r]);
+                  a.act_out[(long long)(im.row0 + t) * a.act_rows + row] =
+                      __float2bfloat16_rn(g / (1.0f + expf(-g)) * u);
                 }
               }
             }
