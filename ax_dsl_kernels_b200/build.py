@@ -1,4 +1,5 @@
-"""Builds csrc/*.cu into libq35b200.so (in-tree, sm_100a only) with nvcc.
+"""Builds csrc/*.cu into libq35b200.so (in-tree, sm_100a only) with nvcc, and the native by-name runner
+runner/q35run.cc (plain C++ against the library's C ABI and the CUDA runtime) into ./q35run.
 
     python -m ax_dsl_kernels_b200.build [--force]
 """
@@ -10,6 +11,8 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libq35b200.so")
+RUNNER = os.path.join(HERE, "q35run")
+RUNNER_SRC = os.path.join(HERE, "runner", "q35run.cc")
 OBJ = os.path.join(HERE, "build")
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17", "-Xcompiler", "-fPIC",
@@ -51,6 +54,12 @@ def build(force=False, verbose=False):
         r = subprocess.run([NVCC, "-shared", "-o", LIB, *objs, "-lcudart"], capture_output=True, text=True)
         if r.returncode:
             raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
+    if force or _stale(RUNNER, [RUNNER_SRC, LIB, headers[-1]]):
+        r = subprocess.run([NVCC, "-O2", "-std=c++17", "-I", os.path.join(os.path.dirname(HERE), "include"), RUNNER_SRC,
+                            "-o", RUNNER, "-L", HERE, "-lq35b200", "-lcudart", "-Xlinker", "-rpath", "-Xlinker",
+                            "$ORIGIN"], capture_output=True, text=True)
+        if r.returncode:
+            raise RuntimeError(f"runner build failed:\n{r.stdout}\n{r.stderr}")
     return LIB
 
 

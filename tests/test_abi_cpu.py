@@ -1,6 +1,7 @@
 """The C-ABI library without a GPU: it loads, exports what include/q35b200.h declares, describes its roles, and
 rejects contract violations before anything would be launched (no compute calls here)."""
 import ctypes
+import json
 import os
 import re
 
@@ -92,3 +93,17 @@ def test_host_wrappers_reject_cpu_tensors_loudly():
         q35.route(torch.zeros((2, 256)), 8)
     with pytest.raises(TypeError):
         q35.route(torch.zeros((2, 256), dtype=torch.bfloat16), 8)
+
+
+def test_native_runner_lists_roles_and_io_tables_without_a_gpu():
+    """ax_dsl_kernels_b200/q35run (C++ host of the C ABI): the two commands that need no device"""
+    import subprocess
+    from ax_dsl_kernels_b200 import build, _lib
+    build.build()
+    roles = subprocess.run([build.RUNNER, "--roles"], capture_output=True, text=True, check=True).stdout.split()
+    assert roles == _lib.roles() and "lm_head" in roles
+    for role in roles:
+        out = subprocess.run([build.RUNNER, "--io", role], capture_output=True, text=True, check=True).stdout.strip()
+        assert json.loads(out) == _lib.io_table(role)
+    r = subprocess.run([build.RUNNER, "--io", "no.such.role"], capture_output=True, text=True)
+    assert r.returncode == 1 and "role" in r.stderr

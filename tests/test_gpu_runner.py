@@ -1,0 +1,65 @@
+"""The native runner q35run (C++ against the C ABI) on case directories: results bit-identical to the Python host's."""
+import os
+import subprocess
+
+import pytest
+import torch
+
+from _cases import gdn_step_case
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def runner():
+    from ax_dsl_kernels_b200 import build
+    build.build()
+    return build.RUNNER
+
+
+def test_route_from_files(runner, golden, tmp_path):
+    import ax_dsl_kernels_b200 as q35
+    from ax_dsl_kernels_b200 import casefile
+    f = golden("route")
+    ids, rw = q35.route(f["logits"].cuda(), 8)
+    casefile.dump_case(tmp_path, dict(logits=f["logits"]), dict(ids=ids, rw=rw))
+    r = subprocess.run([runner, "moe.route", str(tmp_path), "5", "--check", "2"], capture_output=True, text=True)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "check: 2 runs, 0 differing outputs" in r.stdout and "device status 0" in r.stdout
+    assert torch.equal(casefile.read_output(tmp_path, "ids", ids), f["ids"])
+    assert torch.equal(casefile.read_output(tmp_path, "rw", rw), rw.cpu())
+
+
+def test_gdn_step_in_place_state_from_files(runner, tmp_path):
+    """state_out aliased onto state_in (Q35RUN_ALIAS), as the reference's runner aliases recurrent state"""
+    import ax_dsl_kernels_b200 as q35
+    from ax_dsl_kernels_b200 import casefile
+    q, k, v, g, beta, state = gdn_step_case(B=4, NK=2, NV=4, seed=12)
+    ins = dict(q=q[:, 0], k=k[:, 0], v=v[:, 0], g=g[:, 0], beta=beta[:, 0], state_in=state)
+    o, s1 = q35.gdn_recurrent_step(*(t.contiguous().cuda() for t in ins.values()))
+    casefile.dump_case(tmp_path, {n: t.contiguous() for n, t in ins.items()}, dict(o=o, state_out=s1))
+    env = dict(os.environ, Q35RUN_ALIAS="state_out:state_in")
+    r = subprocess.run([runner, "gdn.step", str(tmp_path), "0", "--check", "3"], capture_output=True, text=True, env=env)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "in place of input state_in" in r.stdout and "check: 3 runs, 0 differing outputs" in r.stdout
+    assert torch.equal(casefile.read_output(tmp_path, "o", o), o.cpu())
+    assert torch.equal(casefile.read_output(tmp_path, "state_out", s1), s1.cpu())
+
+
+def test_workspace_role_and_contract_error(runner, golden, tmp_path):
+    import ax_dsl_kernels_b200 as q35
+    from ax_dsl_kernels_b200 import casefile
+    from ax_dsl_kernels_b200.moe import lm_head
+    f = golden("lm_head")
+    logits, token = lm_head(f["x"].cuda(), f["packed"].cuda(), f["scale"].cuda())
+    casefile.dump_case(tmp_path, dict(x=f["x"], w=f["packed"], s=f["scale"]), dict(logits=logits, token=token))
+    r = subprocess.run([runner, "lm_head", str(tmp_path), "3"], capture_output=True, text=True)
+    assert r.returncode == 0 and "(scratch)" in r.stdout, r.stdout + r.stderr
+    assert torch.equal(casefile.read_output(tmp_path, "logits", logits), logits.cpu())
+    assert torch.equal(casefile.read_output(tmp_path, "token", token), f["token"])
+    # a wrong shape is a status with a message, not a crash
+    bad = tmp_path / "bad"
+    casefile.dump_case(bad, dict(x=f["x"], w=f["packed"][:, :100], s=f["scale"]), dict(logits=logits))
+    r = subprocess.run([runner, "lm_head", str(bad), "0"], capture_output=True, text=True)
+    assert r.returncode == 1 and "lm_head" in r.stderr
+    assert q35.device_status() == 0
