@@ -149,7 +149,7 @@ static const RoleDef kRoles[] = {
      R"({"in":[["x","bf16","[T,K]"],["w","u8","[N,K/2]"],["s","u8","[N,K/32]"],["bias","f32","[N] optional"],["workspace","u8","[*]"]],"out":[["out","bf16|f32","[T,N]"]]})",
      run_linear_tc},
     {"lm_head",
-     R"({"in":[["x","bf16","[T,K]"],["w","u8","[N,K/2]"],["s","u8","[N,K/32]"],["workspace","u8","[*]"]],"out":[["logits","f32","[T,N] optional"],["token","i32","[T] optional: first index of the row maximum"]]})",
+     R"({"in":[["x","bf16","[T,K]"],["w","u8","[N,K/2]"],["s","u8","[N,K/32]"],["workspace","u8","[*]"]],"out":[["logits","f32","[T,N] optional; also accepted under the name out"],["token","i32","[T] optional: first index of the row maximum"]]})",
      run_lm_head},
 };
 static const int kNumRoles = int(sizeof(kRoles) / sizeof(kRoles[0]));

@@ -319,6 +319,7 @@ int run_lm_head(Call& c) {
   Q35_TRY(c.get("w", M_BYTES, &w));
   Q35_TRY(c.get("s", M(Q35_U8), &s));
   Q35_TRY(c.get("logits", M(Q35_F32), &logits, false));
+  if (!logits.present) Q35_TRY(c.get("out", M(Q35_F32), &logits, false));  // the name in the reference's manifests
   Q35_TRY(c.get("token", M(Q35_I32), &token, false));
   Q35_REQUIRE(logits.present || token.present, Q35_ERR_MISSING, "lm_head: give logits, token or both");
   Q35_REQUIRE(x.nd >= 2 && w.nd == 2, Q35_ERR_SHAPE, "lm_head: x [T, K], w [N, K/2]");

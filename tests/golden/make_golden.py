@@ -85,9 +85,25 @@ def lm_head():
                          token=logits.argmax(-1).to(torch.int32)))
 
 
+def manifest_roles():
+    """8. the roles of the reference's 35B manifest that map onto single roles of the library (IO metadata only), plus
+    the first entries of decode.group as an example of a role that does not"""
+    m = json.load(open(os.path.join(REF, "models/qwen35_35b_a3b/qwen35_35b_a3b.manifest.json")))
+    keep = {k: v for k, v in m["kernels"].items() if k.startswith("moe.") or k in ("lm_head", "decode.group")}
+    g = keep["decode.group"]
+    keep["decode.group"] = {"file": g["file"], "in": g["in"][:6], "out": g["out"][:2]}
+    out = {k: m[k] for k in ("format", "model", "context", "cores")}
+    out["params"] = {"experts": m["params"]["experts"]}
+    out["kernels"] = keep
+    json.dump(out, open(os.path.join(HERE, "manifest_35b_roles.json"), "w"), indent=0)
+    print("wrote manifest_35b_roles.json", list(keep))
+
+
 def main():
     if "--only-lm-head" in sys.argv:
         return lm_head()
+    if "--only-manifest" in sys.argv:
+        return manifest_roles()
     sys.meta_path.insert(0, _Finder())
     sgl = os.path.join(REF, "models/qwen35_35b_a3b/sgl")
     sys.path[:0] = [os.path.join(sgl, "python"), os.path.join(sgl, "tests"),
@@ -165,6 +181,7 @@ def main():
     d.update({"w." + n: t for n, t in wts.items()})
     save("gdn_sublayer", d)
     lm_head()
+    manifest_roles()
 
 
 if __name__ == "__main__":

@@ -107,3 +107,24 @@ def test_native_runner_lists_roles_and_io_tables_without_a_gpu():
         assert json.loads(out) == _lib.io_table(role)
     r = subprocess.run([build.RUNNER, "--io", "no.such.role"], capture_output=True, text=True)
     assert r.returncode == 1 and "role" in r.stderr
+
+
+def test_reference_manifest_roles_bind_to_library_roles():
+    """the 35B manifest's MoE and LM-head roles (trimmed copy of the reference's manifest, tests/golden/) go through
+    the library's own contract checks with their names, dtype codes, byte counts and shapes; no GPU involved"""
+    from ax_dsl_kernels_b200 import manifest
+    _ensure_built()
+    m = manifest.load(os.path.join(os.path.dirname(__file__), "golden", "manifest_35b_roles.json"))
+    assert manifest.library_role("moe.slots32_g64") == "moe.slots"
+    assert manifest.library_role("moe.combine_t2048") == "moe.combine"
+    assert manifest.library_role("decode.group") is None
+    ws = manifest.check(m)
+    assert set(ws) == {r for r in m["kernels"] if r != "decode.group"} and len(ws) == 10
+    assert ws["moe.combine_t2048"] == 0 and ws["moe.slots32_g64"] > 0 and ws["lm_head"] > 0
+    # a manifest whose table disagrees with itself is refused with a status, as a real call would be
+    bad = json.loads(json.dumps(m))
+    bad["kernels"]["lm_head"]["in"][2]["shape"] = [248320, 32]
+    with pytest.raises(_lib.Q35Error):
+        manifest.check_role(bad, "lm_head")
+    with pytest.raises(KeyError):
+        manifest.check_role(m, "decode.group")

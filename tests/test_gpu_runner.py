@@ -63,3 +63,32 @@ def test_workspace_role_and_contract_error(runner, golden, tmp_path):
     r = subprocess.run([runner, "lm_head", str(bad), "0"], capture_output=True, text=True)
     assert r.returncode == 1 and "lm_head" in r.stderr
     assert q35.device_status() == 0
+
+
+def test_manifest_roles_run_with_the_reference_shapes(tmp_path):
+    """moe.combine_t512 and lm_head exactly as the reference's 35B manifest declares them (tensor names, dtype codes,
+    byte counts; lm_head's output under the manifest's name `out`), against the oracle"""
+    import ax_dsl_kernels_b200 as q35
+    from ax_dsl_kernels_b200 import manifest
+    from conftest import assert_parity, rel_rms_err
+    from oracle import codecs, moe as omoe
+    m = manifest.load(os.path.join(os.path.dirname(__file__), "golden", "manifest_35b_roles.json"))
+    g = torch.Generator().manual_seed(6)
+    T, K, R, H = 512, 8, 32768, 2048
+    base = torch.randn((T, H), generator=g).to(torch.bfloat16)
+    sout = torch.randn((R, H), generator=g).to(torch.bfloat16)
+    loc = torch.randperm(R, generator=g)[:K * T].reshape(K, T).to(torch.int32)
+    out = torch.empty((T, H), dtype=torch.bfloat16).cuda()
+    manifest.run_role(m, "moe.combine_t512", dict(base=base.cuda(), loc=loc.cuda(), sout=sout.cuda(), out=out))
+    assert_parity(out.cpu(), omoe.combine(base, loc, sout), tol=1e-3)
+    with pytest.raises(ValueError):
+        manifest.run_role(m, "moe.combine_t512", dict(base=base[:8].cuda(), loc=loc.cuda(), sout=sout.cuda(), out=out))
+
+    N = 248320
+    pk, sc = codecs.random_mxfp4((N, H), g, -8, 0)
+    x = torch.randn((1, H), generator=g).to(torch.bfloat16)
+    logits = torch.empty((1, N), dtype=torch.float32).cuda()
+    # the manifest declares w as logical FP4 [N, K] (code 15); the bytes are the packed pairs
+    manifest.run_role(m, "lm_head", dict(x=x.cuda(), w=pk.cuda(), s=sc.cuda(), out=logits))
+    assert rel_rms_err(logits.cpu(), codecs.lm_head_logits(x, pk, sc)[0]) <= 2e-2
+    assert q35.device_status() == 0
