@@ -8,6 +8,6 @@ int launch_group_count(const int* ids, const int* base, int T, int K, int NE, in
                        cudaStream_t stream);
 int launch_combine(const __nv_bfloat16* base, const int* loc, const void* sout, bool sout_f32, __nv_bfloat16* out,
                    int T, int H, int K, int R, cudaStream_t stream);
-int launch_partial_sum(const int* loc, const float* sout, float* partial, int T, int H, int K, int R,
+int launch_partial_sum(const int* loc, const void* sout, bool sout_f32, float* partial, int T, int H, int K, int R,
                        cudaStream_t stream);
 }  // namespace q35

@@ -229,7 +229,8 @@ int run_moe_permute(Call& c) {
 // moe.combine: out[t] = bf16(base[t] + sum_k sout[loc[k, t]]), fp32, k ascending
 // (models/qwen35_2b/whole/src/q35_moe_prefill.py:201-214).  One thread per 8 channels.
 // expert-parallel form: partial[t] = sum over the pairs present on this rank (loc >= 0) of sout[loc[k, t]], fp32
-__global__ void __launch_bounds__(256) moe_partial_sum_kernel(const int* __restrict__ loc, const float* __restrict__ sout,
+template <typename ST>
+__global__ void __launch_bounds__(256) moe_partial_sum_kernel(const int* __restrict__ loc, const ST* __restrict__ sout,
                                                               float* __restrict__ partial, int T, int H, int K, int R) {
   pdl_wait();
   pdl_launch();
@@ -242,8 +243,15 @@ __global__ void __launch_bounds__(256) moe_partial_sum_kernel(const int* __restr
 #pragma unroll
     for (int u = 0; u < 8; ++u) {
       const int r = k0 + u < K ? loc[size_t(k0 + u) * T + t] : -1;
-      v[u] = (r >= 0 && r < R) ? *reinterpret_cast<const float4*>(sout + size_t(r) * H + h)
-                               : make_float4(0.f, 0.f, 0.f, 0.f);
+      v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (r >= 0 && r < R) {
+        if constexpr (sizeof(ST) == 4) {
+          v[u] = *reinterpret_cast<const float4*>(sout + size_t(r) * H + h);
+        } else {
+          const uint2 b = *reinterpret_cast<const uint2*>(sout + size_t(r) * H + h);
+          v[u] = make_float4(bf16lo(b.x), bf16hi(b.x), bf16lo(b.y), bf16hi(b.y));
+        }
+      }
     }
 #pragma unroll
     for (int u = 0; u < 8; ++u) { acc.x += v[u].x; acc.y += v[u].y; acc.z += v[u].z; acc.w += v[u].w; }
@@ -251,10 +259,15 @@ __global__ void __launch_bounds__(256) moe_partial_sum_kernel(const int* __restr
   *reinterpret_cast<float4*>(partial + size_t(t) * H + h) = acc;
 }
 
-int launch_partial_sum(const int* loc, const float* sout, float* partial, int T, int H, int K, int R,
+int launch_partial_sum(const int* loc, const void* sout, bool sout_f32, float* partial, int T, int H, int K, int R,
                        cudaStream_t stream) {
-  launch_pdl(moe_partial_sum_kernel, dim3(unsigned(T), unsigned((H / 4 + 255) / 256)), dim3(256), 0, stream, loc, sout,
-             partial, T, H, K, R);
+  const dim3 grid(unsigned(T), unsigned((H / 4 + 255) / 256));
+  if (sout_f32)
+    launch_pdl(moe_partial_sum_kernel<float>, grid, dim3(256), 0, stream, loc, static_cast<const float*>(sout), partial, T,
+               H, K, R);
+  else
+    launch_pdl(moe_partial_sum_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, loc,
+               static_cast<const __nv_bfloat16*>(sout), partial, T, H, K, R);
   Q35_CUDA_LAUNCH_CHECK("moe partial sum");
   return 0;
 }

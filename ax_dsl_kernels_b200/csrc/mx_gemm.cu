@@ -281,11 +281,16 @@ int run_moe_experts(Call& c) {
   }
   if (use_tc) {
     const ExpertPlanes ep{gw.as<uint8_t>(), gs.as<uint8_t>(), dw.as<uint8_t>(), ds.as<uint8_t>(), NE, FE, H};
+    // Prefill-sized: the weighted expert rows are kept in bf16, as the reference's slot kernels emit them
+    // (moe_slots_px out [S, G, H] bf16, models/qwen35_2b/whole/src/q35_moe_prefill.py:150-166), which halves the
+    // largest write of the block; decode-sized calls keep the fp32 rows of the decode golden.
+    const bool rows_f32 = P <= 4096;
     Q35_TRY(tc_routed(ep, h2.as<__nv_bfloat16>(), int(T), src, int(P), int(NE), g_expert, g_n, g_row0,
-                      int((P + NE - 1) / NE), act, qws, sout, nullptr, rw_row, c.stream, small));
+                      int((P + NE - 1) / NE), act, qws, rows_f32 ? sout : nullptr,
+                      rows_f32 ? nullptr : reinterpret_cast<__nv_bfloat16*>(sout), rw_row, c.stream, small));
     if (partial.present)
-      return launch_partial_sum(loc, sout, partial.as<float>(), int(T), int(H), int(K), int(P), c.stream);
-    return launch_combine(base.as<__nv_bfloat16>(), loc, sout, true, out.as<__nv_bfloat16>(), int(T), int(H), int(K),
+      return launch_partial_sum(loc, sout, rows_f32, partial.as<float>(), int(T), int(H), int(K), int(P), c.stream);
+    return launch_combine(base.as<__nv_bfloat16>(), loc, sout, rows_f32, out.as<__nv_bfloat16>(), int(T), int(H), int(K),
                           int(P), c.stream);
   }
   const int nt = pick_nt((P + NE - 1) / NE);
@@ -310,7 +315,8 @@ int run_moe_experts(Call& c) {
   d.x = act; d.x_stride = int(FE); d.src = nullptr;
   d.f_out = sout; d.out_stride = int(H); d.rw_row = rw_row;
   Q35_TRY((launch_skinny<W_MXFP4, EPI_ROW_SCALE>(d, nt, int((H + 127) / 128), int(NE), c.stream)));
-  if (partial.present) return launch_partial_sum(loc, sout, partial.as<float>(), int(T), int(H), int(K), int(P), c.stream);
+  if (partial.present)
+    return launch_partial_sum(loc, sout, true, partial.as<float>(), int(T), int(H), int(K), int(P), c.stream);
   return launch_combine(base.as<__nv_bfloat16>(), loc, sout, true, out.as<__nv_bfloat16>(), int(T), int(H), int(K),
                         int(P), c.stream);
 }
@@ -458,6 +464,79 @@ __global__ void __launch_bounds__(256) router_kernel(const __nv_bfloat16* __rest
   }
 }
 
+// Prefill-sized router: the same logits [T, NE] (+ the shared-expert gate dot as column NE) as a bf16 tensor-core GEMM
+// with fp32 accumulation -- bf16 products are exact in fp32, so only the order of the sum differs from router_kernel.
+// CTA = 64 tokens x 64 router rows, 4 warps of 16 tokens each, K in chunks of 64 through a two-stage cp.async ring with
+// XOR-swizzled 128-byte rows.
+__global__ void __launch_bounds__(128) router_mma_kernel(const __nv_bfloat16* __restrict__ h2,
+                                                         const __nv_bfloat16* __restrict__ w_router,
+                                                         const __nv_bfloat16* __restrict__ w_shg,
+                                                         float* __restrict__ logits, float* __restrict__ gate, int T,
+                                                         int H, int NE) {
+  pdl_wait();
+  pdl_launch();
+  __shared__ __align__(128) __nv_bfloat16 sA[2][64 * 64];
+  __shared__ __align__(128) __nv_bfloat16 sB[2][64 * 64];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int t0 = blockIdx.x * 64, e0 = blockIdx.y * 64;
+  auto stage_load = [&](int st, int k0) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int c = tid + i * 128, row = c >> 3, ch = c & 7;
+      const int t = min(t0 + row, T - 1), e = e0 + row;  // rows past the end repeat a valid row and are not stored
+      const __nv_bfloat16* wrow = e < NE ? w_router + size_t(e) * H : w_shg;
+      const int dst = row * 64 + ((ch ^ (row & 7)) << 3);
+      cp_async_16(smem_u32(&sA[st][dst]), h2 + size_t(t) * H + k0 + ch * 8);
+      cp_async_16(smem_u32(&sB[st][dst]), wrow + k0 + ch * 8);
+    }
+    cp_async_commit();
+  };
+  float acc[8][4];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) { acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f; }
+  const int nk = H / 64;
+  stage_load(0, 0);
+  for (int kc = 0; kc < nk; ++kc) {
+    if (kc + 1 < nk) { stage_load((kc + 1) & 1, (kc + 1) * 64); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
+    __syncthreads();
+    const __nv_bfloat16* A = sA[kc & 1];
+    const __nv_bfloat16* B = sB[kc & 1];
+#pragma unroll
+    for (int kk = 0; kk < 4; ++kk) {
+      uint32_t a0, a1, a2, a3;
+      {
+        const int row = warp * 16 + (lane & 15), ch = kk * 2 + (lane >> 4);
+        ldmatrix_x4(smem_u32(A + row * 64 + ((ch ^ (row & 7)) << 3)), a0, a1, a2, a3);
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {  // 16 router rows per ldmatrix: two n-tiles
+        uint32_t b0, b1, b2, b3;
+        const int row = j * 16 + (lane & 7) + ((lane >> 4) << 3), ch = kk * 2 + ((lane >> 3) & 1);
+        ldmatrix_x4(smem_u32(B + row * 64 + ((ch ^ (row & 7)) << 3)), b0, b1, b2, b3);
+        mma_bf16_16816(acc[2 * j], a0, a1, a2, a3, b0, b1);
+        mma_bf16_16816(acc[2 * j + 1], a0, a1, a2, a3, b2, b3);
+      }
+    }
+    __syncthreads();
+  }
+  const int gid = lane >> 2, tig = lane & 3;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int t = t0 + warp * 16 + gid + 8 * h;
+      if (t >= T) continue;
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        const int e = e0 + 8 * j + 2 * tig + c;
+        const float v = acc[j][2 * h + c];
+        if (e < NE) logits[size_t(t) * NE + e] = v;
+        else if (e == NE) gate[t] = v;
+      }
+    }
+  }
+}
+
 static int weight_format(const Tensor& w, const Tensor& s, int64_t K, int* fmt) {
   if (s.present && s.dtype == Q35_F32) { *fmt = W_FP8ROW; return 0; }
   Q35_REQUIRE(s.present, Q35_ERR_MISSING, "quantised weight without scales");
@@ -540,9 +619,15 @@ static int moe_pre_impl(Call& c, int mode) {
     launch_pdl(rmsnorm_kernel, dim3(unsigned(T)), dim3(256), 0, c.stream, x1.as<__nv_bfloat16>(), ln2.as<float>(),
                h2o.as<__nv_bfloat16>(), int(H), eps);
     Q35_CUDA_LAUNCH_CHECK("moe.pre rmsnorm");
-    launch_pdl(router_kernel, dim3(unsigned((NE + 1 + 7) / 8), unsigned(T)), dim3(256), 0, c.stream,
-               h2o.as<__nv_bfloat16>(), wr.as<__nv_bfloat16>(), wshg.as<__nv_bfloat16>(), lgo.as<float>(), gate, int(H),
-               int(NE));
+    if (T >= 256 && H % 64 == 0) {  // prefill-sized: tensor cores
+      launch_pdl(router_mma_kernel, dim3(unsigned((T + 63) / 64), unsigned((NE + 1 + 63) / 64)), dim3(128), 0, c.stream,
+                 h2o.as<__nv_bfloat16>(), wr.as<__nv_bfloat16>(), wshg.as<__nv_bfloat16>(), lgo.as<float>(), gate, int(T),
+                 int(H), int(NE));
+    } else {
+      launch_pdl(router_kernel, dim3(unsigned((NE + 1 + 7) / 8), unsigned(T)), dim3(256), 0, c.stream,
+                 h2o.as<__nv_bfloat16>(), wr.as<__nv_bfloat16>(), wshg.as<__nv_bfloat16>(), lgo.as<float>(), gate, int(H),
+                 int(NE));
+    }
     Q35_CUDA_LAUNCH_CHECK("moe.pre router");
   }
   if (!do_shared) return 0;

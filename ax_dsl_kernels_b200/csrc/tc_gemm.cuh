@@ -348,21 +348,26 @@ __global__ void __launch_bounds__(TcCfg<NB>::THREADS, TcCfg<NB>::CTAS_PER_SM) tc
 #pragma unroll
           for (int jj = 0; jj < 16; ++jj) hi[jj] += lo[jj];
           if constexpr (EPI == TC_EPI_SILU_MUL) {
-            // rows 64..127 (up) hand their values to rows 0..63 (gate) through shared memory
-            if (h == 1) {
+            // Row p of the gate half and row p of the up half make one output element.  The gate rows' threads finish
+            // columns 0..7 of the chunk, the up rows' threads columns 8..15; each side hands the other the eight
+            // values it needs through shared memory (already rounded to bf16, as the golden rounds gate and up).
+            const int p = r & 63;
+            const int orow = im.tile * a.tile_rows + a.roff[0] + p;  // the pair's row in the activation
+            const bool ovalid = orow < a.lim[0];
 #pragma unroll
-              for (int jj = 0; jj < 16; ++jj) g_xch[jj * 64 + (r & 63)] = __float2bfloat16_rn(hi[jj]);
+            for (int jj = 0; jj < 8; ++jj) {
+              const int col = h ? jj : jj + 8;
+              g_xch[col * 64 + p] = __float2bfloat16_rn(h ? hi[jj] : hi[jj + 8]);  // static indices: hi stays in registers
             }
             asm volatile("bar.sync 1, 128;" ::: "memory");
-            if (h == 0) {
 #pragma unroll
-              for (int jj = 0; jj < 16; ++jj) {
-                const int t = t0 + c0 + jj;
-                if (t < im.n && rvalid) {
-                  const float g = round_bf16(hi[jj]), u = __bfloat162float(g_xch[jj * 64 + r]);
-                  a.act_out[(long long)(im.row0 + t) * a.act_rows + row] =
-                      __float2bfloat16_rn(g / (1.0f + expf(-g)) * u);
-                }
+            for (int jj = 0; jj < 8; ++jj) {
+              const int col = h ? jj + 8 : jj;
+              const int t = t0 + c0 + col;
+              if (t < im.n && ovalid) {
+                const float mine = round_bf16(h ? hi[jj + 8] : hi[jj]), other = __bfloat162float(g_xch[col * 64 + p]);
+                const float g = h ? other : mine, u = h ? mine : other;
+                a.act_out[(long long)(im.row0 + t) * a.act_rows + orow] = __float2bfloat16_rn(g / (1.0f + expf(-g)) * u);
               }
             }
             asm volatile("bar.sync 1, 128;" ::: "memory");

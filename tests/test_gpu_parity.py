@@ -370,8 +370,29 @@ def test_moe_block_prefill_sized_batch(q35):
     ref, ids, rw, logits = omoe.moe_block(x1[sample], w["ln2"], sg, su, sd, w["w_router"], w["w_shg"], w["e_gw"],
                                           w["e_gs"], w["e_dw"], w["e_ds"], 8)
     assert torch.equal(gids.cpu()[sample], ids)
+    assert rel_rms_err(glog.cpu()[sample], logits) <= 1e-3  # tensor-core router GEMM, fp32 accumulation
     assert_parity(out.cpu()[sample], ref)
     assert torch.isfinite(out).all()
+
+
+def test_router_gemm_ragged_sizes(q35):
+    """prefill-sized router on the tensor cores with a token count and an expert count that are not multiples of the
+    64 x 64 tile: logits and the shared-expert gate dot against fp32 matmul of the same bf16 inputs"""
+    T, NE, H = 300, 96, 2048
+    g = torch.Generator().manual_seed(5)
+    x1 = torch.randn((T, H), generator=g).to(torch.bfloat16)
+    ln2 = 1 + 0.05 * torch.randn(H, generator=g)
+    wr = (torch.randn((NE, H), generator=g) / 45).to(torch.bfloat16)
+    wshg = (torch.randn((H,), generator=g) / 45).to(torch.bfloat16)
+    h2 = torch.empty_like(x1).cuda()
+    logits = torch.full((T, NE), float("nan")).cuda()
+    gate = torch.full((T,), float("nan")).cuda()
+    q35.run("moe.norm_router", x1=x1.cuda(), ln2=ln2.cuda(), w_router=wr.cuda(), w_shg=wshg.cuda(), h2_out=h2,
+            logits_out=logits, gate_out=gate)
+    h2f = h2.cpu().float()
+    assert rel_rms_err(h2.cpu(), omoe.rmsnorm(x1, ln2)) <= 1e-2
+    torch.testing.assert_close(logits.cpu(), h2f @ wr.float().T, rtol=1e-4, atol=1e-4)
+    torch.testing.assert_close(gate.cpu(), h2f @ wshg.float(), rtol=1e-4, atol=1e-4)
 
 
 # ------------------------------------------------------------------------------------------------ GDN prefill

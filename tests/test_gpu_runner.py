@@ -26,7 +26,7 @@ def test_route_from_files(runner, golden, tmp_path):
     r = subprocess.run([runner, "moe.route", str(tmp_path), "5", "--check", "2"], capture_output=True, text=True)
     assert r.returncode == 0, r.stdout + r.stderr
     assert "check: 2 runs, 0 differing outputs" in r.stdout and "device status 0" in r.stdout
-    assert torch.equal(casefile.read_output(tmp_path, "ids", ids), f["ids"])
+    assert torch.equal(casefile.read_output(tmp_path, "ids", ids), ids.cpu())
     assert torch.equal(casefile.read_output(tmp_path, "rw", rw), rw.cpu())
 
 
