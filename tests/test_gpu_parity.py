@@ -510,3 +510,51 @@ def test_lm_head_golden_fixture_and_vocabulary_sized(q35, golden):
     for r in range(2):
         if float(top2[r, 0] - top2[r, 1]) > 2 * float(err[r]):
             assert int(token[r]) == int(ref_tok[r])
+
+
+# ------------------------------------------------------------------------------- full BASELINE sizes, by properties
+def test_gdn_chunk_prefill_full_size_split_invariance(q35):
+    """configuration 3 at full size (16384 tokens, 32 value / 16 key heads, chunk 64), where the token-by-token golden
+    would take hours: prefilling in one call must equal prefilling two halves with the state carried over, bit for bit
+    (chunk boundaries coincide), and the second half must depend on the carried state"""
+    T = 16384
+    q, k, v, g, beta, s0 = (t.cuda() for t in _gdn_seq(T, 16, 32, seed=31))
+    o_full, s_full = q35.gdn_chunk_prefill(q, k, v, g, beta, s0)
+    h = T // 2
+    o1, s1 = q35.gdn_chunk_prefill(q[:, :h].contiguous(), k[:, :h].contiguous(), v[:, :h].contiguous(),
+                                   g[:, :h].contiguous(), beta[:, :h].contiguous(), s0)
+    o2, s2 = q35.gdn_chunk_prefill(q[:, h:].contiguous(), k[:, h:].contiguous(), v[:, h:].contiguous(),
+                                   g[:, h:].contiguous(), beta[:, h:].contiguous(), s1)
+    assert torch.equal(o_full[:, :h], o1) and torch.equal(o_full[:, h:], o2) and torch.equal(s_full, s2)
+    o2z, _ = q35.gdn_chunk_prefill(q[:, h:].contiguous(), k[:, h:].contiguous(), v[:, h:].contiguous(),
+                                   g[:, h:].contiguous(), beta[:, h:].contiguous(), torch.zeros_like(s1))
+    assert not torch.equal(o2z, o2)
+    assert torch.isfinite(o_full).all() and torch.isfinite(s_full).all()
+    # and the last token agrees with one recurrent step from the state before it
+    o_last, s_last = q35.gdn_chunk_prefill(q[:, :T - 1].contiguous(), k[:, :T - 1].contiguous(),
+                                           v[:, :T - 1].contiguous(), g[:, :T - 1].contiguous(),
+                                           beta[:, :T - 1].contiguous(), s0)
+    o_step, _ = q35.gdn_recurrent_step(q[:, -1].contiguous(), k[:, -1].contiguous(), v[:, -1].contiguous(),
+                                       g[:, -1].contiguous(), beta[:, -1].contiguous(), s_last)
+    assert_parity(o_step.cpu(), o_full[:, -1].cpu(), tol=5e-2)
+
+
+def test_moe_block_prefill_8192_tokens_permutation_equivariance(q35):
+    """configuration 4 at prefill size (8192 tokens, 256 experts top-8): every token is computed independently of the
+    others, so permuting the tokens must permute ids, routing weights and outputs bit for bit; a sample of tokens is
+    checked against the CPU golden"""
+    T = 8192
+    x1, w = moe_case(T, NE=256, seed=41)
+    wd = {k: v.cuda() for k, v in w.items()}
+    out, ids, rw, _ = q35.moe_block(x1.cuda(), wd, 8)
+    out, ids, rw = out.clone(), ids.clone(), rw.clone()
+    perm = torch.randperm(T, generator=torch.Generator().manual_seed(2))
+    out_p, ids_p, rw_p, _ = q35.moe_block(x1[perm].cuda(), wd, 8)
+    assert torch.equal(ids_p.cpu(), ids.cpu()[perm]) and torch.equal(rw_p.cpu(), rw.cpu()[perm])
+    assert torch.equal(out_p.cpu(), out.cpu()[perm])
+    sample = torch.arange(0, T, 683)
+    sg, su, sd = dequant_shared(w)
+    ref, rids, _, _ = omoe.moe_block(x1[sample], w["ln2"], sg, su, sd, w["w_router"], w["w_shg"], w["e_gw"], w["e_gs"],
+                                     w["e_dw"], w["e_ds"], 8)
+    assert torch.equal(ids.cpu()[sample], rids)
+    assert_parity(out.cpu()[sample], ref)
