@@ -321,6 +321,9 @@ __global__ void __launch_bounds__(TcCfg<NB>::THREADS, TcCfg<NB>::CTAS_PER_SM) tc
     const int h = r >> 6;
     uint32_t q = 0;
     bool dead = false;
+    // bf16 output whose 128 tile rows are 128 consecutive output columns (every epilogue but SiLU x up)
+    const bool staged = EPI != TC_EPI_SILU_MUL && a.b_out != nullptr && a.f_out == nullptr && a.tile_rows == 128 &&
+                        a.roff[1] == a.roff[0] + 64 && (a.lim[0] & 7) == 0 && (a.out_stride & 7) == 0;
     TcItem im;
     for (TcItemWalk walk(a, n_items); walk.next(&im);) {
       const int row = im.tile * a.tile_rows + a.roff[h] + (r & 63);
@@ -393,24 +396,44 @@ __global__ void __launch_bounds__(TcCfg<NB>::THREADS, TcCfg<NB>::CTAS_PER_SM) tc
                 }
               }
             }
+            float o[16];
 #pragma unroll
             for (int jj = 0; jj < 16; ++jj) {
-              const int t = t0 + c0 + jj;
-              if (t >= im.n || !rvalid) continue;
-              const long long dst = im.row0 + t;
               float v = hi[jj];
               if constexpr (EPI == TC_EPI_ROW_SCALE) {
                 v *= aux[jj];
-                if (a.f_out) a.f_out[dst * a.out_stride + row] = v;
-                else a.b_out[dst * a.out_stride + row] = __float2bfloat16_rn(v);
               } else if constexpr (EPI == TC_EPI_SHARED_DOWN) {
                 const float sig = 1.0f / (1.0f + expf(-aux[jj]));
-                const float res = (jj & 1) ? bf16hi(res2[jj >> 1]) : bf16lo(res2[jj >> 1]);
-                a.b_out[dst * a.out_stride + row] = __float2bfloat16_rn(res + v * sig);
+                v = ((jj & 1) ? bf16hi(res2[jj >> 1]) : bf16lo(res2[jj >> 1])) + v * sig;
               } else {
                 v += bias;
-                if (a.f_out) a.f_out[dst * a.out_stride + row] = v;
-                else a.b_out[dst * a.out_stride + row] = __float2bfloat16_rn(v);
+              }
+              o[jj] = v;
+            }
+            if (staged) {
+              // bf16 output of a full-width tile: 2-byte stores of one row per lane reach about 1 TB/s; the values go
+              // through shared memory instead (8 columns at a time) and leave as 16-byte stores, 16 lanes per token row
+#pragma unroll
+              for (int half = 0; half < 2; ++half) {
+#pragma unroll
+                for (int jj = 0; jj < 8; ++jj) g_xch[jj * 128 + r] = __float2bfloat16_rn(o[half * 8 + jj]);
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                const int e = tid - 64, tt = e >> 4, part = e & 15;
+                const int t = t0 + c0 + half * 8 + tt;
+                const int rowg = im.tile * 128 + a.roff[0] + part * 8;
+                if (t < im.n && rowg < a.lim[0])
+                  *reinterpret_cast<uint4*>(a.b_out + (long long)(im.row0 + t) * a.out_stride + rowg) =
+                      *reinterpret_cast<const uint4*>(g_xch + tt * 128 + part * 8);
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+              }
+            } else {
+#pragma unroll
+              for (int jj = 0; jj < 16; ++jj) {
+                const int t = t0 + c0 + jj;
+                if (t >= im.n || !rvalid) continue;
+                const long long dst = im.row0 + t;
+                if (a.f_out) a.f_out[dst * a.out_stride + row] = o[jj];
+                else a.b_out[dst * a.out_stride + row] = __float2bfloat16_rn(o[jj]);
               }
             }
           }
