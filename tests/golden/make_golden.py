@@ -1,7 +1,7 @@
 """Generates the golden fixtures in this directory from the reference's OWN torch goldens.
 
-Run in a container that has the reference checkout (path in REF, default /root/reference):
-    python tests/golden/make_golden.py
+Run where the reference checkout is available, with its path in the environment variable REF:
+    REF=<reference checkout> python tests/golden/make_golden.py
 The reference's kernels need its NPU DSL package `axnn`, which is not installable; its pure-torch golden functions do
 not, so `axnn` (and `onnx`, imported by a board helper) are replaced by inert stub modules and the golden functions
 are imported and called unchanged.  Outputs: small .npz files (bf16 tensors stored as their int16 bit patterns with a
@@ -19,7 +19,7 @@ from unittest.mock import MagicMock
 import numpy as np
 import torch
 
-REF = os.environ.get("REF", "/root/reference")
+REF = os.environ.get("REF", "")
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
@@ -100,6 +100,8 @@ def manifest_roles():
 
 
 def main():
+    if not os.path.isdir(REF):
+        sys.exit("set REF to the reference checkout")
     if "--only-lm-head" in sys.argv:
         return lm_head()
     if "--only-manifest" in sys.argv:
