@@ -199,9 +199,11 @@ def run_ours(args):
         line = {
             "metric": METRIC, "value": world * B * args.steps / (ms * 1e-3), "unit": "tok/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16 activations (two-term E4M3 into the block-scaled MMA), MXFP4 "
-            "weights expanded to bf16, fp32 accumulate/state", "data": "synthetic (seeded, on-device)",
-            "config": {"workload": workload_name(), "batch_per_gpu": B, "context": CTX, "launch": "cuda graph replay" if graph is not None else "eager",
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic (seeded, on-device)",
+            "config": {"workload": workload_name(), "batch_per_gpu": B, "context": CTX,
+                       "arithmetic": "bf16 activations and KV, MXFP4 expert weights into the block-scaled MMA with the "
+                       "activations as two E4M3 terms, fp32 accumulation and GDN state", "launch": "cuda graph replay" if graph is not None else "eager",
                        "parallelism": "1 GPU" if world == 1 else f"sequences data-parallel x{world}, experts sharded "
                        f"x{world} (NCCL all-gather of tokens + reduce-scatter of expert sums)", "l2": "inputs larger than L2 (2.1 GB KV + 0.43 GB experts + "
                        "0.27 GB state per step)"},
