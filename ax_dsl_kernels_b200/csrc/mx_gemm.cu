@@ -127,9 +127,12 @@ __global__ void __launch_bounds__(256) experts_build_rows_kernel(const int* __re
   }
 }
 
-// Decode-sized form of the grouping (at most 1024 pairs and 1024 experts): one CTA does the count, the stable ranks,
-// the row tables and the list of experts with rows that the tensor-core GEMM walks.  Same result as
+// Small form of the grouping (at most 4096 pairs, 1024 experts, experts x ceil(T / 32) <= 4096): one CTA does the count,
+// the stable ranks, the row tables and the list of experts with rows that the tensor-core GEMM walks.  Same result as
 // moe_group_count_kernel + experts_build_rows_kernel + the active-group scan; pairs without a local expert get loc -1.
+// Every expert keeps a bitmap of the tokens that chose it; a pair's rank inside its expert is the number of set bits
+// below its token (tokens ascending = the stable order), its expert's row count the number of set bits.
+constexpr int PLAN_MAX_PAIRS = 4096, PLAN_MAX_WORDS = 4096;
 __global__ void __launch_bounds__(1024) experts_plan_small_kernel(const int* __restrict__ ids,
                                                                   const int* __restrict__ base,
                                                                   const float* __restrict__ rw, int T, int K, int NE,
@@ -137,43 +140,42 @@ __global__ void __launch_bounds__(1024) experts_plan_small_kernel(const int* __r
                                                                   float* rw_row, int* loc, int* active, int* status) {
   pdl_wait();
   pdl_launch();
-  __shared__ __align__(16) int s_id[1024];
-  __shared__ int s_cnt[1024];
+  __shared__ short s_raw[PLAN_MAX_PAIRS];
+  __shared__ uint32_t s_bits[PLAN_MAX_WORDS];
   __shared__ int s_row0[1024];
   __shared__ int s_warp[32];
   const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
-  const int P = T * K;
-  int id = -1, t = 0, k = 0;
-  if (tid < P) {
-    t = tid / K; k = tid % K;
-    id = ids[tid] - (base ? base[0] : 0);  // base: first global id of this rank's planes
+  const int P = T * K, W = (T + 31) / 32;
+  const int first = base ? base[0] : 0;  // first global id of this rank's planes
+  for (int p = tid; p < P; p += 1024) {
+    int id = ids[p] - first;
     if (id >= NE) {
       if (!base) atomicOr(status, DS_BAD_EXPERT);
       id = -1;
     }
-    if (id < 0) id = -1;  // negative ids mean "not on this rank"
+    s_raw[p] = short(id < 0 ? -1 : id);  // negative ids mean "not on this rank"
   }
-  s_row0[tid] = id;  // raw ids, for the duplicate check
-  s_cnt[tid] = 0;
+  for (int i = tid; i < NE * W; i += 1024) s_bits[i] = 0u;
   __syncthreads();
-  for (int kk = 0; kk < k && id >= 0; ++kk)
-    if (s_row0[t * K + kk] == id) id = -1;  // an expert listed twice by a token counts once
-  s_id[tid] = id;
-  __syncthreads();
-  int rank = 0;
-  if (id >= 0) {
-    // pairs are token-major, so the number of earlier pairs with the same expert is the stable rank
-    const int4* v4 = reinterpret_cast<const int4*>(s_id);
-    for (int q = 0; q < (tid >> 2); ++q) {
-      const int4 x = v4[q];
-      rank += (x.x == id) + (x.y == id) + (x.z == id) + (x.w == id);
+  int myid[PLAN_MAX_PAIRS / 1024];
+#pragma unroll
+  for (int i = 0; i < PLAN_MAX_PAIRS / 1024; ++i) {
+    const int p = tid + i * 1024;
+    int id = -1;
+    if (p < P) {
+      const int t = p / K, k = p % K;
+      id = s_raw[p];
+      for (int kk = 0; kk < k && id >= 0; ++kk)
+        if (s_raw[t * K + kk] == id) id = -1;  // an expert listed twice by a token counts once
+      if (id >= 0) atomicOr(&s_bits[id * W + (t >> 5)], 1u << (t & 31));
     }
-    for (int p = tid & ~3; p < tid; ++p) rank += s_id[p] == id;
-    atomicAdd(&s_cnt[id], 1);
+    myid[i] = id;
   }
   __syncthreads();
   // exclusive scan over the experts of (rows, has rows) packed as rows | on << 16
-  const int cnt = tid < NE ? s_cnt[tid] : 0;
+  int cnt = 0;
+  if (tid < NE)
+    for (int w = 0; w < W; ++w) cnt += __popc(s_bits[tid * W + w]);
   int v = cnt | (cnt > 0 ? 1 << 16 : 0);
   int inc = v;
 #pragma unroll
@@ -201,12 +203,18 @@ __global__ void __launch_bounds__(1024) experts_plan_small_kernel(const int* __r
   }
   if (active && tid == 1023) active[0] = (exc + v) >> 16;
   __syncthreads();
-  if (tid < P) {
+#pragma unroll
+  for (int i = 0; i < PLAN_MAX_PAIRS / 1024; ++i) {
+    const int p = tid + i * 1024;
+    if (p >= P) continue;
+    const int t = p / K, k = p % K, id = myid[i];
     int row = -1;
     if (id >= 0) {
+      int rank = __popc(s_bits[id * W + (t >> 5)] & ((1u << (t & 31)) - 1u));
+      for (int w = 0; w < (t >> 5); ++w) rank += __popc(s_bits[id * W + w]);
       row = s_row0[id] + rank;
       src[row] = t;
-      rw_row[row] = rw[tid];
+      rw_row[row] = rw[p];
     }
     loc[size_t(k) * T + t] = row;
   }
@@ -265,7 +273,7 @@ int run_moe_experts(Call& c) {
   WsCarver wr{ws.as<uint8_t>()};
   carve(wr, counts, list, g_expert, g_n, g_row0, src, rw_row, loc, act, sout);
 
-  const bool small = P <= 1024 && NE <= 1024;
+  const bool small = P <= PLAN_MAX_PAIRS && NE <= 1024 && NE * ((T + 31) / 32) <= PLAN_MAX_WORDS;
   if (small) {
     launch_pdl(experts_plan_small_kernel, dim3(1), dim3(1024), 0, c.stream, ids.as<int>(),
                ebase.present ? ebase.as<int>() : nullptr, rw.as<float>(), int(T), int(K), int(NE), g_expert, g_n, g_row0,

@@ -210,8 +210,8 @@ def run_ours(args):
             "e2e": {"value": world * B * args.steps / (e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h},
             # kernels of this library per step (torch and NCCL kernels not counted): GDN 1, attention 3, MoE 14 with
-            # the one-CTA routing plan (up to 1024 token-expert pairs per rank), 16 with the three-kernel plan
-            "gpu_launches": args.steps * (18 if world * B * TOPK <= 1024 else 20),
+            # the one-CTA routing plan (up to 4096 token-expert pairs per rank), 16 with the three-kernel plan
+            "gpu_launches": args.steps * (18 if world * B * TOPK <= 4096 else 20),
             "roofline": {"bound": "hbm", "kernel": "attn_decode_kernel<256,bf16> (+ plan and merge launches)",
                          "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_source": peak_src, "traffic": attn_traffic(wl), "algorithmic_bytes": wl.attn_bytes(),

@@ -358,10 +358,11 @@ def test_linear_tc_block_scaled_mma(q35, T, N, K):
     assert_parity(outb.cpu(), (ref + bias.double()).to(torch.bfloat16))
 
 
-def test_moe_block_prefill_sized_batch(q35):
-    """1024 tokens through the whole block (tensor-core grouped GEMM with many tokens per expert); the CPU golden is
-    evaluated on a sample of the tokens (it loops over tokens in Python)"""
-    T = 1024
+@pytest.mark.parametrize("T", [400, 1024])
+def test_moe_block_prefill_sized_batch(q35, T):
+    """400 tokens (3200 pairs: the one-CTA routing plan with several pairs per thread, ragged last token word) and 1024
+    tokens (three-kernel plan, bf16 expert rows) through the whole block; the CPU golden is evaluated on a sample of
+    the tokens (it loops over tokens in Python)"""
     x1, w = moe_case(T, NE=32, seed=77)
     wd = {k: v.cuda() for k, v in w.items()}
     out, gids, grw, glog = q35.moe_block(x1.cuda(), wd, 8)
