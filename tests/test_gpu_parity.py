@@ -559,3 +559,36 @@ def test_moe_block_prefill_8192_tokens_permutation_equivariance(q35):
                                      w["e_dw"], w["e_ds"], 8)
     assert torch.equal(ids.cpu()[sample], rids)
     assert_parity(out.cpu()[sample], ref)
+
+
+def test_moe_experts_expert_parallel_shape_of_eight_ranks(q35):
+    """what one of 8 ranks runs per decode step: 512 gathered tokens, global ids over 256 experts, 32 local planes
+    starting at expert_base (4096 pairs through the one-CTA routing plan); a sample of tokens against the golden"""
+    T, NE, lo, hi = 512, 256, 96, 128
+    g = torch.Generator().manual_seed(23)
+    h2 = torch.randn((T, 2048), generator=g).to(torch.bfloat16)
+    ids, rw = omoe.route(torch.randn((T, NE), generator=g), 8)
+    planes = [codecs.random_mxfp4((hi - lo, 1024, 2048), g, -8, 0), codecs.random_mxfp4((hi - lo, 2048, 512), g, -8, 0)]
+    e_gw, e_gs, e_dw, e_ds = planes[0][0], planes[0][1], planes[1][0], planes[1][1]
+    partial = torch.full((T, 2048), float("nan")).cuda()
+    q35.run("moe.experts", h2=h2.cuda(), ids=ids.cuda(), rw=rw.cuda(), e_gw=e_gw.cuda(), e_gs=e_gs.cuda(),
+            e_dw=e_dw.cuda(), e_ds=e_ds.cuda(), expert_base=torch.tensor([lo], dtype=torch.int32).cuda(),
+            partial_out=partial)
+    assert torch.isfinite(partial).all()
+    got = partial.cpu()
+    zero = torch.zeros((1, 2048), dtype=torch.bfloat16)
+    checked = 0
+    for t in range(0, T, 29):
+        ref = torch.zeros(2048)
+        for i in range(8):
+            e = int(ids[t, i]) - lo
+            if 0 <= e < hi - lo:
+                one = omoe.experts_decode(h2[t:t + 1], zero, torch.tensor([[e]], dtype=torch.int32), torch.ones((1, 1)),
+                                          e_gw, e_gs, e_dw, e_ds).float()[0]
+                ref += rw[t, i] * one
+                checked += 1
+        if ref.abs().max() > 0:
+            assert_parity(got[t], ref)
+        else:
+            assert (got[t] == 0).all()
+    assert checked > 0
