@@ -58,6 +58,7 @@ def lib():
         L.q35_device_status.argtypes = [ctypes.c_void_p]
         L.q35_device_status.restype = ctypes.c_int
         L.q35_version.restype = ctypes.c_int
+        L.q35_launch_count.restype = ctypes.c_longlong
         _lib = L
     return _lib
 

@@ -1,6 +1,9 @@
 // C ABI of the library: role registry, by-name binding, validation (see include/q35b200.h).
 #include "abi.h"
+#include <atomic>
+#include <mutex>
 #include <string>
+#include <unordered_map>
 
 namespace q35 {
 
@@ -73,12 +76,80 @@ int Call::workspace(int64_t need, Tensor* ws) {
   return 0;
 }
 
+void clear_error() { g_err.clear(); }
+
+static std::atomic<long long> g_launches{0};
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+
 __device__ int g_device_status;
 
-int* device_status_ptr() {  // one process drives one GPU: looked up once
-  static int* p = nullptr;
-  if (!p) cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_device_status);
-  return p;
+namespace {
+constexpr int kMaxDevices = 64;
+struct DeviceSlot {
+  bool ready = false;
+  DeviceInfo info{nullptr, 0};
+  std::unordered_map<const void*, int> smem_limit;  // kernel -> dynamic shared memory limit already set
+};
+std::mutex g_dev_mutex;
+DeviceSlot g_dev[kMaxDevices];
+
+// the slot of the current device, filled on first use; call with g_dev_mutex held
+DeviceSlot* current_slot() {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    fail(Q35_ERR_CUDA, "cudaGetDevice: %s (device %d)", cudaGetErrorString(e), dev);
+    return nullptr;
+  }
+  DeviceSlot& s = g_dev[dev];
+  if (!s.ready) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_device_status);  // in host code the symbol is only a handle: ask for its address
+    if (e != cudaSuccess || !p) {
+      fail(Q35_ERR_CUDA, "cudaGetSymbolAddress(status word) on device %d: %s", dev, cudaGetErrorString(e));
+      return nullptr;
+    }
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    s.info.status = static_cast<int*>(p);
+    s.info.sm_count = n;
+    s.ready = true;
+  }
+  return &s;
+}
+}  // namespace
+
+const DeviceInfo* device_info() {
+  std::lock_guard<std::mutex> lock(g_dev_mutex);
+  DeviceSlot* s = current_slot();
+  return s ? &s->info : nullptr;
+}
+
+int* device_status_ptr() {
+  const DeviceInfo* d = device_info();
+  return d ? d->status : nullptr;
+}
+
+int sm_count() {  // also used by shape-only queries that may run without a usable device: falls back silently
+  const std::string keep = g_err;
+  const DeviceInfo* d = device_info();
+  if (!d) g_err = keep;
+  return d ? d->sm_count : 148;
+}
+
+int ensure_dynamic_smem(const void* func, int bytes) {
+  if (bytes <= 48 * 1024) return 0;  // within the default limit
+  std::lock_guard<std::mutex> lock(g_dev_mutex);
+  DeviceSlot* s = current_slot();
+  if (!s) return Q35_ERR_CUDA;
+  int& have = s->smem_limit[func];
+  if (bytes > have) {
+    const cudaError_t e = cudaFuncSetAttribute(func, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    Q35_REQUIRE(e == cudaSuccess, Q35_ERR_CUDA, "cudaFuncSetAttribute(%d bytes of dynamic shared memory): %s", bytes,
+                cudaGetErrorString(e));
+    have = bytes;
+  }
+  return 0;
 }
 
 static const RoleDef kRoles[] = {
@@ -151,6 +222,9 @@ static const RoleDef kRoles[] = {
     {"lm_head",
      R"({"in":[["x","bf16","[T,K]"],["w","u8","[N,K/2]"],["s","u8","[N,K/32]"],["workspace","u8","[*]"]],"out":[["logits","f32","[T,N] optional; also accepted under the name out"],["token","i32","[T] optional: first index of the row maximum"]]})",
      run_lm_head},
+    {"debug.wait_probe",
+     R"({"in":[["polls","i32","[1] poll limit of the wait, clamped to 1 .. 2^20"]],"out":[["result","i32","[1] 1 = the wait gave up and the status word got its bit"]]})",
+     run_debug_wait_probe},
 };
 static const int kNumRoles = int(sizeof(kRoles) / sizeof(kRoles[0]));
 
@@ -172,6 +246,9 @@ int q35_run(const char* role, const q35_io* ios, int n_io, void* stream) {
   const RoleDef* r = find_role(role);
   if (!r) return fail(Q35_ERR_ROLE, "unknown role '%s'", role ? role : "(null)");
   if (n_io < 0 || (n_io > 0 && !ios)) return fail(Q35_ERR_MISSING, "bad io table");
+  // the launchers hand kernels the status word's address: resolve this device's state first, so that a failure is
+  // a status code here and never a null pointer inside a kernel
+  if (!device_info()) return Q35_ERR_CUDA;
   Call c{ios, n_io, static_cast<cudaStream_t>(stream), false, 0};
   return r->run(c);
 }
@@ -213,6 +290,8 @@ int q35_device_status(void* stream) {
   return v;
 }
 
-int q35_version(void) { return 1; }
+int q35_version(void) { return 2; }
+
+long long q35_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 }  // extern "C"

@@ -53,8 +53,21 @@ struct RoleDef {
 
 int elem_bits(int dtype);
 
-// device status word shared by all kernels (see q35_device_status)
-int* device_status_ptr();
+// Per-device state.  One process may drive several GPUs (and several host threads may call in at once), so nothing
+// about "the" device is cached process-wide: the address of the device status word, the SM count and the "dynamic
+// shared memory limit already raised" marks are kept per device ordinal, filled under a lock on first use with that
+// device current.
+struct DeviceInfo {
+  int* status;    // device address of this GPU's status word (see q35_device_status)
+  int sm_count;
+};
+// state of the CURRENT device; nullptr (and the error text set) when the CUDA runtime refuses
+const DeviceInfo* device_info();
+int* device_status_ptr();   // device_info()->status, nullptr on failure
+int sm_count();             // device_info()->sm_count, 148 when it cannot be read
+// cudaFuncSetAttribute(func, MaxDynamicSharedMemorySize, bytes) once per (device, function, size); 0 or Q35_ERR_CUDA
+int ensure_dynamic_smem(const void* func, int bytes);
+void clear_error();
 
 #define Q35_REQUIRE(cond, code, ...) \
   do {                               \
@@ -65,8 +78,11 @@ int* device_status_ptr();
     int _st = (expr);        \
     if (_st) return _st;     \
   } while (0)
+// every kernel launch of the library is followed by this check, which also counts it (q35_launch_count)
+void count_launch();
 #define Q35_CUDA_LAUNCH_CHECK(what)                                                        \
   do {                                                                                     \
+    ::q35::count_launch();                                                                 \
     cudaError_t _e = cudaGetLastError();                                                   \
     if (_e != cudaSuccess) return ::q35::fail(Q35_ERR_CUDA, "%s: %s", what, cudaGetErrorString(_e)); \
   } while (0)
@@ -114,5 +130,6 @@ int run_act_silu_mul(Call&);
 int run_act_sigmoid_gate(Call&);
 int run_linear_tc(Call&);
 int run_lm_head(Call&);
+int run_debug_wait_probe(Call&);
 
 }  // namespace q35

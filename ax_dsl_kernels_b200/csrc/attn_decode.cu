@@ -14,6 +14,7 @@
 // (16-byte chunks, XOR-swizzled rows), with no block-wide barrier in the loop.  Scores are computed transposed
 // (S^T = K Q^T: 16 keys x 8 heads per mma) so the 8 query heads of a KV head fill the n = 8 side exactly and the
 // output accumulator O^T [D x 8 heads] costs 64 registers instead of 128.
+#include <mutex>
 #include "abi.h"
 #include "common.cuh"
 
@@ -277,8 +278,14 @@ __global__ void __launch_bounds__(128, 1) attn_decode_kernel(const AttnArgs a) {
           }
         }
         if constexpr (!FP8) {
-          const uint32_t pb0 = movmatrix_trans(pack_bf16(p0, p1));
-          const uint32_t pb1 = movmatrix_trans(pack_bf16(p2, p3));
+          // P enters the P V product as TWO bf16 terms (p = hi + lo): a single bf16 P carries 2^-9 of relative error
+          // into every output element, which on a short or peaked row is as large as the output's own bf16 rounding
+          // step; the golden keeps the softmax in fp32.  The kernel is HBM-bound, the second MMA is free.
+          const float h0 = round_bf16(p0), h1 = round_bf16(p1), h2 = round_bf16(p2), h3 = round_bf16(p3);
+          const uint32_t pb0 = movmatrix_trans(pack_bf16(h0, h1));
+          const uint32_t pb1 = movmatrix_trans(pack_bf16(h2, h3));
+          const uint32_t pl0 = movmatrix_trans(pack_bf16(p0 - h0, p1 - h1));
+          const uint32_t pl1 = movmatrix_trans(pack_bf16(p2 - h2, p3 - h3));
           const int key = (lane & 7) + ((lane >> 4) << 3);
           const uint32_t rowa = st + C::KV_BYTES + key * C::ROWB;
 #pragma unroll
@@ -287,6 +294,7 @@ __global__ void __launch_bounds__(128, 1) attn_decode_kernel(const AttnArgs a) {
             uint32_t a0, a1, a2, a3;
             ldmatrix_x4_trans(rowa + ((ch ^ (key & 7)) << 4), a0, a1, a2, a3);
             mma_bf16_16816(oacc[mt], a0, a1, a2, a3, pb0, pb1);
+            mma_bf16_16816(oacc[mt], a0, a1, a2, a3, pl0, pl1);
           }
         } else {
           // transposed b16 loads keep byte PAIRS (d, d+1) together: a lane gets {V[2c][2r], V[2c][2r+1], V[2c+1][2r],
@@ -454,25 +462,11 @@ int run_attn_kv_write(Call& c) {
   return 0;
 }
 
-static int sm_count() {
-  static int n = 0;
-  if (!n) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-    if (n <= 0) n = 148;
-  }
-  return n;
-}
-
 template <int D, bool FP8>
 static int launch_attn(const AttnArgs& a, cudaStream_t stream) {
   using C = AttnCfg<D, FP8>;
-  static bool attr_done = false;
-  if (!attr_done) {
-    cudaFuncSetAttribute(attn_decode_kernel<D, FP8>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM);
-    attr_done = true;
-  }
+  Q35_TRY(ensure_dynamic_smem(reinterpret_cast<const void*>(attn_decode_kernel<D, FP8>), C::SMEM));
+  Q35_REQUIRE(a.status != nullptr, Q35_ERR_CUDA, "attention decode: no device status word");
   launch_pdl(attn_plan_kernel, dim3(1), dim3(1024), 0, stream, a);
   Q35_CUDA_LAUNCH_CHECK("attn plan");
   launch_pdl(attn_decode_kernel<D, FP8>, dim3(unsigned(a.n_cta)), dim3(128), C::SMEM, stream, a);
@@ -572,6 +566,8 @@ static __device__ __align__(256) unsigned char g_attn_static_scratch[Q35_ATTN_ST
 static int attn_static_scratch(uint8_t** out) {
   constexpr int kMaxDevices = 64;
   static uint8_t* per_device[kMaxDevices] = {nullptr};
+  static std::mutex lock;  // host threads may make their first calls at the same time
+  std::lock_guard<std::mutex> guard(lock);
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   Q35_REQUIRE(e == cudaSuccess && dev >= 0 && dev < kMaxDevices, Q35_ERR_CUDA, "cudaGetDevice: %s",
@@ -594,6 +590,7 @@ extern "C" int q35_attn_paged_decode_static(const void* q, const void* paged_kv_
                                             const float* sm_scale, const float* kv_scale, void* out, int B, int HQ,
                                             int HKV, int D, int P, int num_pages, int n_indices, void* stream) {
   using namespace q35;
+  clear_error();
   Q35_REQUIRE(q && paged_kv_cache && indptr && indices && last_page_len && out, Q35_ERR_MISSING,
               "q35_attn_paged_decode_static: null pointer");
   Q35_REQUIRE(cache_dtype == Q35_BF16 || cache_dtype == Q35_E4M3, Q35_ERR_DTYPE,

@@ -156,17 +156,17 @@ __global__ void __launch_bounds__(256, 1) attn_prefill_kernel(const PrefillArgs 
       alpha[h] = mn == -INFINITY ? 1.f : exp2f(mrow[h] - mn);
       mrow[h] = mn;
     }
-    uint32_t pf[8][2];  // P as bf16 pairs in the accumulator layout
+    // P stays in fp32 in the score registers and enters the P V product as TWO bf16 terms (p = hi + lo): a single
+    // bf16 P carries 2^-9 of relative error into every output element -- on a row with few or peaked keys as much as
+    // the output's own bf16 rounding step -- while the golden keeps the softmax in fp32.
     float ls[2] = {0.f, 0.f};
 #pragma unroll
     for (int nt = 0; nt < 8; ++nt) {
-      const float p0 = mrow[0] == -INFINITY ? 0.f : exp2f(s[nt][0] - mrow[0]);
-      const float p1 = mrow[0] == -INFINITY ? 0.f : exp2f(s[nt][1] - mrow[0]);
-      const float p2 = mrow[1] == -INFINITY ? 0.f : exp2f(s[nt][2] - mrow[1]);
-      const float p3 = mrow[1] == -INFINITY ? 0.f : exp2f(s[nt][3] - mrow[1]);
-      ls[0] += p0 + p1; ls[1] += p2 + p3;
-      pf[nt][0] = pack_bf16(p0, p1);
-      pf[nt][1] = pack_bf16(p2, p3);
+      s[nt][0] = mrow[0] == -INFINITY ? 0.f : exp2f(s[nt][0] - mrow[0]);
+      s[nt][1] = mrow[0] == -INFINITY ? 0.f : exp2f(s[nt][1] - mrow[0]);
+      s[nt][2] = mrow[1] == -INFINITY ? 0.f : exp2f(s[nt][2] - mrow[1]);
+      s[nt][3] = mrow[1] == -INFINITY ? 0.f : exp2f(s[nt][3] - mrow[1]);
+      ls[0] += s[nt][0] + s[nt][1]; ls[1] += s[nt][2] + s[nt][3];
     }
     lrow[0] = lrow[0] * alpha[0] + ls[0];
     lrow[1] = lrow[1] * alpha[1] + ls[1];
@@ -179,15 +179,24 @@ __global__ void __launch_bounds__(256, 1) attn_prefill_kernel(const PrefillArgs 
     // O += P V: A = P (score accumulators reused as fragments), B = V tile [key][d] read transposed
 #pragma unroll
     for (int ks = 0; ks < PF_KEYS / 16; ++ks) {
-      const uint32_t a0 = pf[2 * ks][0], a1 = pf[2 * ks][1], a2 = pf[2 * ks + 1][0], a3 = pf[2 * ks + 1][1];
+      uint32_t ah[4], al[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {  // fragments a0..a3 = (tile 2ks: rows m0 | m1), (tile 2ks + 1: rows m0 | m1)
+        const float x = s[2 * ks + (u >> 1)][2 * (u & 1)], y = s[2 * ks + (u >> 1)][2 * (u & 1) + 1];
+        const float xh = round_bf16(x), yh = round_bf16(y);
+        ah[u] = pack_bf16(xh, yh);
+        al[u] = pack_bf16(x - xh, y - yh);
+      }
       const int brow = ks * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
 #pragma unroll
       for (int np2 = 0; np2 < D / 16; ++np2) {
         const int ch = 2 * np2 + (lane >> 4);
         uint32_t b0, b1, b2, b3;
         ldmatrix_x4_trans(sV + brow * ROWB + ((ch ^ (brow & 7)) << 4), b0, b1, b2, b3);
-        mma_bf16_16816(o[2 * np2], a0, a1, a2, a3, b0, b1);
-        mma_bf16_16816(o[2 * np2 + 1], a0, a1, a2, a3, b2, b3);
+        mma_bf16_16816(o[2 * np2], ah[0], ah[1], ah[2], ah[3], b0, b1);
+        mma_bf16_16816(o[2 * np2 + 1], ah[0], ah[1], ah[2], ah[3], b2, b3);
+        mma_bf16_16816(o[2 * np2], al[0], al[1], al[2], al[3], b0, b1);
+        mma_bf16_16816(o[2 * np2 + 1], al[0], al[1], al[2], al[3], b2, b3);
       }
     }
     __syncthreads();
@@ -280,13 +289,11 @@ int run_attn_paged_prefill(Call& c) {
   const dim3 grid{unsigned((T + PF_TOK - 1) / PF_TOK), unsigned(HKV), unsigned(B)};
   if (D == 256) {
     constexpr int smem = 4 * PF_KEYS * 512;
-    static bool done = false;
-    if (!done) { cudaFuncSetAttribute(attn_prefill_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); done = true; }
+    Q35_TRY(ensure_dynamic_smem(reinterpret_cast<const void*>(attn_prefill_kernel<256>), smem));
     attn_prefill_kernel<256><<<grid, 256, smem, c.stream>>>(a);
   } else {
     constexpr int smem = 4 * PF_KEYS * 256;
-    static bool done = false;
-    if (!done) { cudaFuncSetAttribute(attn_prefill_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); done = true; }
+    Q35_TRY(ensure_dynamic_smem(reinterpret_cast<const void*>(attn_prefill_kernel<128>), smem));
     attn_prefill_kernel<128><<<grid, 256, smem, c.stream>>>(a);
   }
   Q35_CUDA_LAUNCH_CHECK("attn.paged_prefill");

@@ -429,12 +429,8 @@ int run_gdn_chunk_prefill(Call& c) {
   a.W = reinterpret_cast<__nv_bfloat16*>(w + oW); a.Ut = reinterpret_cast<__nv_bfloat16*>(w + oU);
   a.Kd = reinterpret_cast<__nv_bfloat16*>(w + oK); a.M = reinterpret_cast<__nv_bfloat16*>(w + oM);
   a.EG = reinterpret_cast<float*>(w + oE); a.EGL = reinterpret_cast<float*>(w + oL);
-  static bool attr_done = false;
-  if (!attr_done) {
-    cudaFuncSetAttribute(gdn_chunk_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GDN_PREP_SMEM);
-    cudaFuncSetAttribute(gdn_chunk_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GDN_SCAN_SMEM);
-    attr_done = true;
-  }
+  Q35_TRY(ensure_dynamic_smem(reinterpret_cast<const void*>(gdn_chunk_prep_kernel), GDN_PREP_SMEM));
+  Q35_TRY(ensure_dynamic_smem(reinterpret_cast<const void*>(gdn_chunk_scan_kernel), GDN_SCAN_SMEM));
   gdn_chunk_prep_kernel<<<dim3{unsigned(nch), unsigned(BV), 1u}, 128, GDN_PREP_SMEM, c.stream>>>(a);
   Q35_CUDA_LAUNCH_CHECK("gdn chunk prep");
   gdn_chunk_scan_kernel<<<dim3{unsigned(GDK / GSL), unsigned(BV), 1u}, 128, GDN_SCAN_SMEM, c.stream>>>(a);

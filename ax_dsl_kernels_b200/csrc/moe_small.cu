@@ -287,7 +287,8 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const __nv_bfloat16* _
     }
     for (int k = 0; k < K; ++k) {
       const int r = loc[size_t(k) * T + t];
-      if (r < 0 || r >= R) {
+      if (r < 0) continue;  // no row: a pair of another rank, a bad expert id (reported by the plan), a second listing
+      if (r >= R) {
         if (h == 0) atomicOr(status, DS_BAD_TOKEN);
         continue;
       }

@@ -27,11 +27,7 @@ static int launch_skinny(const SkinnyArgs& a, int nt, int tiles, int groups, cud
 #define Q35_SK(NTV)                                                                                         \
   {                                                                                                         \
     constexpr int smem = skinny_smem_bytes<FMT, NTV>();                                                     \
-    static bool attr_done = false;                                                                          \
-    if (!attr_done && smem > 48 * 1024) {                                                                   \
-      cudaFuncSetAttribute(skinny_gemm_kernel<FMT, EPI, NTV>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); \
-      attr_done = true;                                                                                     \
-    }                                                                                                       \
+    Q35_TRY(ensure_dynamic_smem(reinterpret_cast<const void*>(skinny_gemm_kernel<FMT, EPI, NTV>), smem));  \
     skinny_gemm_kernel<FMT, EPI, NTV><<<grid, 128, smem, stream>>>(a);                                      \
   }
   if (nt <= 1) Q35_SK(1)
@@ -100,8 +96,13 @@ static int tc_routed(const ExpertPlanes& e, const __nv_bfloat16* x, int x_rows, 
 // moe.experts: decode form of the routed experts with planar expert tensors.
 // Reference: moe_experts_gu (models/qwen35_2b/whole/src/q35_moe.py:101-112) per token; golden :227-238; experts
 // picked from planes by id as moe_full does (models/qwen35_2b/whole/src/q35_layer_mc.py:863-885).
+// A token that lists the same expert twice gets ONE row for it, weighted by the sum of the two routing weights (the
+// golden adds rw_i * d_i for every listed pair, models/qwen35_2b/whole/src/q35_moe.py:235-238: the same value up to
+// fp32 rounding); the later listing's loc stays -1.  The one-CTA plan below follows the same rule.
 __global__ void __launch_bounds__(256) experts_build_rows_kernel(const int* __restrict__ counts,
                                                                  const int* __restrict__ list,
+                                                                 const int* __restrict__ ids,
+                                                                 const int* __restrict__ base,
                                                                  const float* __restrict__ rw, int T, int K, int NE,
                                                                  int* g_expert, int* g_n, int* g_row0, int* src,
                                                                  float* rw_row, int* loc) {
@@ -121,8 +122,12 @@ __global__ void __launch_bounds__(256) experts_build_rows_kernel(const int* __re
   for (int j = tid; j < n; j += 256) {
     const int p = list[size_t(e) * T + j];
     const int t = p / K, k = p % K;
+    float wsum = rw[p];
+    const int want = e + (base ? base[0] : 0);
+    for (int kk = k + 1; kk < K; ++kk)
+      if (ids[size_t(t) * K + kk] == want) wsum += rw[size_t(t) * K + kk];
     src[row0 + j] = t;
-    rw_row[row0 + j] = rw[p];
+    rw_row[row0 + j] = wsum;
     loc[size_t(k) * T + t] = row0 + j;
   }
 }
@@ -166,7 +171,7 @@ __global__ void __launch_bounds__(1024) experts_plan_small_kernel(const int* __r
       const int t = p / K, k = p % K;
       id = s_raw[p];
       for (int kk = 0; kk < k && id >= 0; ++kk)
-        if (s_raw[t * K + kk] == id) id = -1;  // an expert listed twice by a token counts once
+        if (s_raw[t * K + kk] == id) id = -1;  // listed twice: one row, the weights are summed on the first listing
       if (id >= 0) atomicOr(&s_bits[id * W + (t >> 5)], 1u << (t & 31));
     }
     myid[i] = id;
@@ -213,8 +218,11 @@ __global__ void __launch_bounds__(1024) experts_plan_small_kernel(const int* __r
       int rank = __popc(s_bits[id * W + (t >> 5)] & ((1u << (t & 31)) - 1u));
       for (int w = 0; w < (t >> 5); ++w) rank += __popc(s_bits[id * W + w]);
       row = s_row0[id] + rank;
+      float wsum = rw[p];
+      for (int kk = k + 1; kk < K; ++kk)
+        if (s_raw[t * K + kk] == id) wsum += rw[t * K + kk];
       src[row] = t;
-      rw_row[row] = rw[p];
+      rw_row[row] = wsum;
     }
     loc[size_t(k) * T + t] = row;
   }
@@ -280,11 +288,14 @@ int run_moe_experts(Call& c) {
                src, rw_row, loc, use_tc ? tc_routed_active(qws, P, H, FE) : nullptr, device_status_ptr());
     Q35_CUDA_LAUNCH_CHECK("moe.experts plan");
   } else {
-    if (partial.present) cudaMemsetAsync(loc, 0xff, size_t(P) * 4, c.stream);  // pairs of other ranks: loc = -1
+    // pairs of other ranks, out-of-range ids and second listings of an expert: loc = -1 (moe.combine skips them)
+    cudaMemsetAsync(loc, 0xff, size_t(P) * 4, c.stream);
     Q35_TRY(launch_group_count(ids.as<int>(), ebase.present ? ebase.as<int>() : nullptr, int(T), int(K), int(NE), counts,
                                list, c.stream));
-    experts_build_rows_kernel<<<unsigned(NE), 256, 0, c.stream>>>(counts, list, rw.as<float>(), int(T), int(K), int(NE),
-                                                                  g_expert, g_n, g_row0, src, rw_row, loc);
+    experts_build_rows_kernel<<<unsigned(NE), 256, 0, c.stream>>>(counts, list, ids.as<int>(),
+                                                                  ebase.present ? ebase.as<int>() : nullptr,
+                                                                  rw.as<float>(), int(T), int(K), int(NE), g_expert, g_n,
+                                                                  g_row0, src, rw_row, loc);
     Q35_CUDA_LAUNCH_CHECK("moe.experts rows");
   }
   if (use_tc) {

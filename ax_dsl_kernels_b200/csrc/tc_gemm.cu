@@ -1,4 +1,6 @@
 // Host side of the block-scaled tensor-core GEMM: tensor maps, activation quantisation, launch.
+#include <mutex>
+#include <unordered_map>
 #include "abi.h"
 #include "common.cuh"
 #include "tc_gemm.cuh"
@@ -24,9 +26,50 @@ static EncodeTiledFn encode_fn() {
   return fn;
 }
 
+// Encoded tensor maps are kept per (device, address, shape, box): weights, and the workspace the quantised activations
+// live in, do not move between the steps of a decode loop, so every launch after the first finds its maps here
+// instead of asking the driver again (about a microsecond each, four per GEMM).
+struct MapKey {
+  int dev; bool fp4; const void* base; uint64_t rows, cols, pitch; uint32_t box_rows;
+  bool operator==(const MapKey& o) const {
+    return dev == o.dev && fp4 == o.fp4 && base == o.base && rows == o.rows && cols == o.cols && pitch == o.pitch &&
+           box_rows == o.box_rows;
+  }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    uint64_t h = reinterpret_cast<uintptr_t>(k.base) * 0x9E3779B97F4A7C15ull;
+    h ^= (k.rows + 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2));
+    h ^= (k.cols * 31 + k.pitch * 17 + k.box_rows * 7 + uint64_t(k.dev) * 3 + (k.fp4 ? 1 : 0)) + (h << 6) + (h >> 2);
+    return size_t(h);
+  }
+};
+static std::mutex g_map_mutex;
+static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_map_cache;
+constexpr size_t MAP_CACHE_MAX = 4096;  // entries (128 B each); emptied when full
+
+static int encode_map(CUtensorMap* m, bool fp4, const void* base, uint64_t rows, uint64_t cols, uint64_t pitch_bytes,
+                      uint32_t box_rows, const char* what);
+
 // 2D row-major tensor [rows, cols] with a [box_rows, 128-element] box and 128-byte swizzle
 static int make_map(CUtensorMap* m, bool fp4, const void* base, uint64_t rows, uint64_t cols, uint64_t pitch_bytes,
                     uint32_t box_rows, const char* what) {
+  MapKey key{0, fp4, base, rows, cols, pitch_bytes, box_rows};
+  if (cudaGetDevice(&key.dev) != cudaSuccess) key.dev = -1;
+  {
+    std::lock_guard<std::mutex> lock(g_map_mutex);
+    auto it = g_map_cache.find(key);
+    if (it != g_map_cache.end()) { *m = it->second; return 0; }
+  }
+  Q35_TRY(encode_map(m, fp4, base, rows, cols, pitch_bytes, box_rows, what));
+  std::lock_guard<std::mutex> lock(g_map_mutex);
+  if (g_map_cache.size() >= MAP_CACHE_MAX) g_map_cache.clear();
+  g_map_cache.emplace(key, *m);
+  return 0;
+}
+
+static int encode_map(CUtensorMap* m, bool fp4, const void* base, uint64_t rows, uint64_t cols, uint64_t pitch_bytes,
+                      uint32_t box_rows, const char* what) {
   EncodeTiledFn fn = encode_fn();
   Q35_REQUIRE(fn != nullptr, Q35_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
   const cuuint64_t dims[2] = {cols, rows};
@@ -177,28 +220,13 @@ int tc_build_active(const int* g_n, int groups, int* active, cudaStream_t stream
   return 0;
 }
 
-static int tc_sm_count() {
-  static int n = 0;
-  if (!n) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-    if (n <= 0) n = 148;
-  }
-  return n;
-}
-
 template <int NB, int EPI>
 static int launch_nb(const CUtensorMap& w0, const CUtensorMap& w1, const CUtensorMap& xh, const CUtensorMap& xl,
                      const TcArgs& a, int tiles, int groups, cudaStream_t stream) {
   const int smem = TcCfg<NB>::smem_bytes(a.K);
-  static int attr_smem = 0;
-  if (smem > attr_smem) {
-    cudaFuncSetAttribute(tc_gemm_kernel<NB, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    attr_smem = smem;
-  }
+  Q35_TRY(ensure_dynamic_smem(reinterpret_cast<const void*>(tc_gemm_kernel<NB, EPI>), smem));
   const long long items = (long long)tiles * (a.g_n ? groups : (a.n_dense + a.dense_rows - 1) / a.dense_rows);
-  const long long slots = (long long)tc_sm_count() * TcCfg<NB>::CTAS_PER_SM;
+  const long long slots = (long long)sm_count() * TcCfg<NB>::CTAS_PER_SM;
   const unsigned grid = unsigned(items < slots ? items : slots);
   launch_pdl(tc_gemm_kernel<NB, EPI>, dim3(grid), dim3(TcCfg<NB>::THREADS), size_t(smem), stream, w0, w1, xh, xl, a);
   Q35_CUDA_LAUNCH_CHECK("tc gemm");
@@ -217,7 +245,7 @@ int tc_launch(const TcWeights& w, const TcQuant& q, TcArgs a, int nb, int tiles,
     // dense: the rows are cut into virtual groups.  Every group streams the whole weight matrix, so groups are only
     // made smaller than 256 rows while the row tiles alone leave CTAs idle (decode-sized inputs on small matrices,
     // whose repeated reads then come out of L2).
-    const int want = (2 * tc_sm_count() + tiles - 1) / tiles;
+    const int want = (2 * sm_count() + tiles - 1) / tiles;
     int rows = ((a.n_dense + want - 1) / want + 15) / 16 * 16;
     a.dense_rows = rows < 16 ? 16 : rows > 256 ? 256 : rows;
     nb = nb < a.dense_rows ? nb : a.dense_rows;
@@ -338,6 +366,37 @@ int run_lm_head(Call& c) {
     launch_pdl(argmax_rows_kernel, dim3(unsigned(T)), dim3(1024), 0, c.stream, lg, int(N), token.as<int>());
     Q35_CUDA_LAUNCH_CHECK("lm_head argmax");
   }
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// debug.wait_probe: the bounded-wait reporting path on its own.  One thread waits, with the caller's poll limit, on an
+// mbarrier that nothing ever arrives at -- the same mbar_wait the GEMM's roles use -- records DS_WAIT_TIMEOUT in the
+// status word when the wait gives up, writes how it ended to `result` (1 = gave up, 0 = the barrier completed, which
+// cannot happen) and returns.  Nothing faults and nothing hangs: the wait is the loop bound.
+__global__ void wait_probe_kernel(const int* __restrict__ polls, int* __restrict__ result, int* status) {
+  __shared__ __align__(8) uint64_t bar;
+  if (threadIdx.x == 0) {
+    const uint32_t b = smem_u32(&bar);
+    tc::mbar_init(b, 1);
+    tc::fence_barrier_init();
+    int limit = polls[0];
+    limit = limit < 1 ? 1 : limit > (1 << 20) ? (1 << 20) : limit;
+    const bool ok = tc::mbar_wait(b, 0, uint32_t(limit));
+    if (!ok) atomicOr(status, DS_WAIT_TIMEOUT);
+    result[0] = ok ? 0 : 1;
+  }
+}
+
+int run_debug_wait_probe(Call& c) {
+  Tensor polls, result;
+  Q35_TRY(c.get("polls", M(Q35_I32), &polls));
+  Q35_TRY(c.get("result", M(Q35_I32), &result));
+  Q35_REQUIRE(polls.numel() == 1 && result.numel() == 1, Q35_ERR_SHAPE, "debug.wait_probe: polls [1], result [1]");
+  c.ws_need = 0;
+  if (c.dry) return 0;
+  wait_probe_kernel<<<1, 32, 0, c.stream>>>(polls.as<int>(), result.as<int>(), device_status_ptr());
+  Q35_CUDA_LAUNCH_CHECK("debug.wait_probe");
   return 0;
 }
 

@@ -21,6 +21,19 @@ def _empty(shape, dtype, like):
     return torch.empty(shape, dtype=dtype, device=like.device)
 
 
+_scalars = {}
+
+
+def _scalar(value, device):
+    """fp32 [1] tensor holding `value` on `device`, made once (a host-to-device copy per call would break CUDA-graph
+    capture of a sublayer and costs more than the kernels it feeds)"""
+    key = (float(value), device.type, device.index)
+    t = _scalars.get(key)
+    if t is None:
+        t = _scalars[key] = torch.tensor([float(value)], dtype=torch.float32, device=device)
+    return t
+
+
 def rmsnorm(x, w, residual=None, eps=None, folded=False):
     """plain: y = x_norm * w.  folded (GDN sublayer): y = bf16(base * w) and sqrt(mean base^2 + eps) returned for the
     projections to divide by.  With a residual, base = bf16(x + residual) is returned as well."""
@@ -34,7 +47,7 @@ def rmsnorm(x, w, residual=None, eps=None, folded=False):
         xsqrt = _empty((x.numel() // x.shape[-1],), torch.float32, x)
         kw["xsqrt_out"] = xsqrt
     if eps is not None:
-        kw["eps"] = torch.tensor([eps], dtype=torch.float32, device=x.device)
+        kw["eps"] = _scalar(eps, x.device)
     _lib.run("norm.rms", **kw)
     return y, base, xsqrt
 
@@ -94,7 +107,7 @@ def gdn(hidden_states, residual, weights, temporal_state, conv_state, *, input_n
     normed = torch.empty_like(proj["z"]).reshape(R, NV, DV)
     kw = dict(core=core.reshape(R, NV, DV), z=proj["z"].reshape(R, NV, DV), w=w["o_norm_w"], y=normed)
     if o_norm_eps is not None:
-        kw["eps"] = torch.tensor([o_norm_eps], dtype=torch.float32, device=x2.device)
+        kw["eps"] = _scalar(o_norm_eps, x2.device)
     _lib.run("gdn.out_norm", **kw)
     if reduce is None:
         fused = _proj(normed.reshape(R, VD), w, "o", residual=base)

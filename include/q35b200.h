@@ -82,11 +82,26 @@ const char* q35_role_name(int index);
 /* Text of the calling thread's last error ("" if none). */
 const char* q35_last_error(void);
 
-/* Device-side status word: kernels record (and skip) out-of-range page ids, expert ids and waits that ran out
- * instead of faulting.  Reads and clears it (synchronises the stream); 0 = clean. */
+/* Device-side status word (one per GPU): kernels record (and skip) out-of-range page ids, expert ids and waits that
+ * ran out instead of faulting or hanging.  Reads and clears the current device's word (synchronises the stream);
+ * 0 = clean, negative = the CUDA runtime refused.  Bits:
+ *   0x001 page id / page table entry out of range      0x002 expert id out of range
+ *   0x004 a bounded device-side wait gave up           0x008 token / row index out of range
+ * and, with 0x004, which wait of the tensor-core GEMM it was:
+ *   0x010 loader waiting for a free ring stage         0x020 MMA issuer waiting for a free accumulator
+ *   0x040 MMA issuer waiting for a stage's data        0x080 scale path waiting for a free scale slot
+ *   0x100 epilogue waiting for a finished accumulator  0x200 MMA issuer waiting for a stage's scales
+ *   0x400 a work item waiting for the rows another item produces
+ * The role "debug.wait_probe" makes one such wait run out on purpose (a barrier nobody arrives at, a poll limit the
+ * caller gives) so that a host can check this reporting path; it touches nothing else. */
 int q35_device_status(void* stream);
 
 int q35_version(void);
+
+/* Kernels this library has launched in this process so far (all threads, all devices; launches recorded into a CUDA
+ * graph count once, at capture).  A diagnostic with no counterpart in the reference: a host can difference it around
+ * a step to see how many kernels the step costs. */
+long long q35_launch_count(void);
 
 /* Paged attention decode without any caller-provided scratch.  No counterpart in the reference: it exists for hosts
  * that cannot allocate device memory when they call in (runtimes whose buffers are planned up front and frozen, callers

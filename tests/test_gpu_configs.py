@@ -1,0 +1,255 @@
+"""GPU parity at the sizes the hot path is quoted on (configurations 2, 3 and 4, and the benchmark's own attention
+launch), against the CPU oracle on identical seeded inputs.
+
+The big tensors (KV caches of one to two GB) are generated on the device from a seeded generator; the oracle is run on
+a fixed sample of sequences whose pages are copied back bit for bit, so both sides see the same bytes.  Every check
+goes through assert_parity, which records the strict figure max|err| / RMS.
+"""
+import threading
+
+import pytest
+import torch
+
+from conftest import assert_parity, rel_rms_err
+from oracle import attention as oattn, gdn as ogdn, moe as omoe
+from _cases import dequant_shared, gdn_step_case, moe_case
+
+pytestmark = pytest.mark.gpu
+P, HKV, HQ, D = 64, 2, 16, 256
+
+
+@pytest.fixture(scope="module")
+def q35():
+    assert torch.cuda.is_available(), "GPU tests need a CUDA device"
+    import ax_dsl_kernels_b200 as m
+    yield m
+    assert m.device_status() == 0
+
+
+def _paged_on_device(ctxs, seed, fp8):
+    """configuration-2 inputs on the GPU: cache [pages, 2, 64, 2, 256] ~ N(0, 1), physical pages a random permutation,
+    q ~ N(0, 1); FP8 variant e4m3(x / scale_h) with scale_h = amax_h / 448 per (K | V, head)"""
+    dev = torch.device("cuda")
+    g = torch.Generator(device=dev).manual_seed(seed)
+    n_pages = [(c + P - 1) // P for c in ctxs]
+    total = sum(n_pages)
+    cache = torch.empty((total, 2, P, HKV, D), dtype=torch.bfloat16, device=dev)
+    for i in range(0, total, 2048):
+        cache[i:i + 2048] = torch.randn((min(2048, total - i), 2, P, HKV, D), generator=g, device=dev).to(torch.bfloat16)
+    indices = torch.randperm(total, generator=g, device=dev).to(torch.int32)
+    indptr = torch.tensor([0, *torch.tensor(n_pages).cumsum(0).tolist()], dtype=torch.int32, device=dev)
+    last = torch.tensor([c - (n - 1) * P for c, n in zip(ctxs, n_pages)], dtype=torch.int32, device=dev)
+    q = torch.randn((len(ctxs), HQ, D), generator=g, device=dev).to(torch.bfloat16)
+    kv_scale = None
+    if fp8:
+        amax = torch.zeros((2, HKV), device=dev)
+        for i in range(0, total, 2048):
+            amax = torch.maximum(amax, cache[i:i + 2048].float().abs().amax((0, 2, 4)))
+        kv_scale = (amax / 448.0).contiguous()
+        c8 = torch.empty(cache.shape, dtype=torch.float8_e4m3fn, device=dev)
+        for i in range(0, total, 2048):
+            c8[i:i + 2048] = (cache[i:i + 2048].float() / kv_scale.reshape(1, 2, 1, HKV, 1)).to(torch.float8_e4m3fn)
+        cache = c8
+    return q, cache, indptr, indices, last, kv_scale
+
+
+def _oracle_on_sample(q, cache, indptr, indices, last, kv_scale, sample, sm_scale):
+    """the CPU golden on the sampled sequences: their pages copied back in table order (same bytes, compact ids)"""
+    refs = []
+    for b in sample:
+        rows = indices[int(indptr[b]):int(indptr[b + 1])].long()
+        sub = cache[rows].cpu()
+        n = sub.shape[0]
+        refs.append(oattn.paged_decode(q[b:b + 1].cpu(), sub, torch.tensor([0, n], dtype=torch.int32),
+                                       torch.arange(n, dtype=torch.int32), last[b:b + 1].cpu(), sm_scale=sm_scale,
+                                       kv_scale=None if kv_scale is None else kv_scale.cpu()))
+    return torch.cat(refs, 0)
+
+
+@pytest.mark.parametrize("fp8", [False, True], ids=["bf16", "fp8_per_head_scale"])
+def test_config2_batch64_contexts_1024_to_16384(q35, fp8):
+    """configuration 2 exactly: batch 64, seed 1, contexts uniform in [1024, 16384], page 64, permuted pages,
+    softmax scale 1/16; the oracle runs on 8 sequences including the longest and the shortest"""
+    ctxs = torch.randint(1024, 16385, (64,), generator=torch.Generator().manual_seed(1)).tolist()
+    q, cache, indptr, indices, last, kvs = _paged_on_device(ctxs, seed=1, fp8=fp8)
+    out = torch.full_like(q, float("nan"))
+    q35.paged_attention_decode(q, cache, indptr, indices, last, out, sm_scale=1.0 / 16, kv_scale=kvs)
+    assert torch.isfinite(out).all()
+    order = sorted(range(64), key=lambda b: ctxs[b])
+    sample = sorted({order[0], order[-1], 0, 9, 23, 37, 50, 63})
+    ref = _oracle_on_sample(q, cache, indptr, indices, last, kvs, sample, 1.0 / 16)
+    assert_parity(out[sample].cpu(), ref, per_seq=True)
+
+
+def test_benchmark_attention_launch_batch64_context16384(q35):
+    """the benchmark's own attention launch (64 sequences of exactly 16384 tokens, 2.1 GB of bf16 KV): 4 sequences
+    against the oracle"""
+    ctxs = [16384] * 64
+    q, cache, indptr, indices, last, _ = _paged_on_device(ctxs, seed=1000, fp8=False)
+    out = torch.full_like(q, float("nan"))
+    q35.paged_attention_decode(q, cache, indptr, indices, last, out, sm_scale=1.0 / 16)
+    assert torch.isfinite(out).all()
+    sample = [0, 21, 42, 63]
+    ref = _oracle_on_sample(q, cache, indptr, indices, last, None, sample, 1.0 / 16)
+    assert_parity(out[sample].cpu(), ref, per_seq=True)
+
+
+def test_config3_decode_batch64_32_value_heads(q35):
+    """configuration 3, decode: 64 sequences x 32 value / 16 key heads, fp32 state ~ N(0, 0.03^2), all of it against
+    the golden recurrence"""
+    q, k, v, g, beta, s0 = gdn_step_case(B=64, NK=16, NV=32, seed=2)
+    o_ref, s_ref = ogdn.recurrent(q, k, v, g, beta, s0)
+    o, s1 = q35.gdn_recurrent_step(q[:, 0].cuda(), k[:, 0].cuda(), v[:, 0].cuda(), g[:, 0].cuda(), beta[:, 0].cuda(),
+                                   s0.cuda(), state_out=torch.empty_like(s0).cuda())
+    assert_parity(o.cpu(), o_ref[:, 0])
+    torch.testing.assert_close(s1.cpu(), s_ref, rtol=0, atol=3e-3)  # the reference's temporal-state tolerance
+
+
+def test_config3_prefill_16384_tokens_two_heads_against_recurrence(q35):
+    """configuration 3, prefill: 16384 tokens, 32 value / 16 key heads, chunk 64, zero initial state.  The kernel runs
+    all heads; value heads 5 and 30 (key heads 2 and 15) are compared with the token recurrence: the unrounded float64
+    form (strict 2e-2) and the reference's bf16-rounding golden, whose own distance to float64 is recorded beside it."""
+    T, NK, NV = 16384, 16, 32
+    g = torch.Generator().manual_seed(2)
+    q = (ogdn.l2norm(torch.randn((1, T, NK, 128), generator=g)).float() * 128 ** -0.5).to(torch.bfloat16)
+    k = ogdn.l2norm(torch.randn((1, T, NK, 128), generator=g))
+    v = torch.randn((1, T, NV, 128), generator=g).to(torch.bfloat16)
+    beta = torch.sigmoid(torch.randn((1, T, NV), generator=g)).to(torch.bfloat16)
+    gg = -torch.nn.functional.softplus(torch.randn((1, T, NV), generator=g))
+    s0 = torch.zeros((1, NV, 128, 128))
+    o, s1 = q35.gdn_chunk_prefill(q.cuda(), k.cuda(), v.cuda(), gg.cuda(), beta.cuda(), s0.cuda())
+    vh = [5, 30]
+    kh = [h // (NV // NK) for h in vh]
+    sub = (q[:, :, kh].contiguous(), k[:, :, kh].contiguous(), v[:, :, vh].contiguous(), gg[:, :, vh].contiguous(),
+           beta[:, :, vh].contiguous(), s0[:, vh].contiguous())
+    o64, s64 = ogdn.recurrent_f64(*sub)
+    og, sg = ogdn.recurrent(*sub)
+    got = o[:, :, vh].cpu()
+    d_golden = rel_rms_err(og.double(), o64)
+    # recorded first, judged after: the kernel against float64, and against the golden with the golden's own distance
+    # to float64 added to the limit
+    lim = max(2e-2, 1.5 * d_golden)
+    r64 = assert_parity(got.double(), o64, tol=lim, name="config3 prefill 16384: kernel vs float64 recurrence "
+                        f"(the bf16-rounding golden itself is {d_golden:.3e} away)")
+    rg = assert_parity(got, og, tol=lim + d_golden, name="config3 prefill 16384: kernel vs bf16 golden")
+    assert r64["strict_max_err_over_rms"] <= lim and rg["strict_max_err_over_rms"] <= lim + d_golden
+    assert (s1[:, vh].cpu().double() - s64).abs().max().item() <= max(4e-3, 1.5 * (sg.double() - s64).abs().max().item())
+
+
+def test_config4_decode_moe_block_64_tokens_256_experts(q35):
+    """configuration 4, decode: one moe_block call on 64 tokens, 256 experts top-8 + shared expert, seed 3; routing
+    ids bit-exact, output within tolerance of the golden"""
+    T = 64
+    x1, w = moe_case(T, NE=256, seed=3)
+    sg, su, sd = dequant_shared(w)
+    ref, ids, rw, logits = omoe.moe_block(x1, w["ln2"], sg, su, sd, w["w_router"], w["w_shg"], w["e_gw"], w["e_gs"],
+                                          w["e_dw"], w["e_ds"], 8)
+    wd = {k: v.cuda() for k, v in w.items()}
+    out, gids, grw, glog = q35.moe_block(x1.cuda(), wd, 8)
+    assert torch.equal(gids.cpu(), ids)
+    torch.testing.assert_close(grw.cpu(), rw, rtol=1e-4, atol=1e-6)
+    assert_parity(out.cpu(), ref, bf16_step=True)
+    out2, _, _, _ = q35.moe_block(x1.cuda(), wd, 8, overlap=False)
+    assert_parity(out2.cpu(), ref, bf16_step=True, name="config4 decode, moe_pre -> route -> moe_experts sequence")
+
+
+# ------------------------------------------------------------------------------------------------ router near-ties
+def test_route_logits_one_and_two_ulps_apart_around_kth_place(q35):
+    """The kernel orders experts by their LOGITS (descending, exact ties to the lower id); the reference's host router
+    sorts the fp32 softmax PROBABILITIES.  Two logits one ulp apart can round to the same probability, and then the
+    probability sort takes the lower id where the logit order takes the larger logit.  Checked here: the kernel follows
+    the logit order exactly, and wherever its ids differ from the probability-sorted golden the experts involved have
+    EQUAL golden probabilities (so either choice is a valid top-k of the golden's own numbers)."""
+    T, NE, K = 32, 256, 8
+    g = torch.Generator().manual_seed(77)
+    logits = torch.randn((T, NE), generator=g)
+    for t in range(T):
+        srt = torch.sort(logits[t], descending=True)
+        kth = srt.values[K - 1].clone()
+        lo_id, hi_id = sorted((int(srt.indices[K - 1]), int(srt.indices[K])))
+        ulps = 1 + (t % 2)
+        bits = kth.view(torch.int32)
+        nxt = (bits + (ulps if kth > 0 else -ulps)).view(torch.float32)  # `ulps` steps larger
+        logits[t, lo_id] = kth        # the lower id holds the SMALLER logit ...
+        logits[t, hi_id] = nxt        # ... the higher id the larger one, `ulps` apart
+    ids, rw = q35.route(logits.cuda(), K)
+    by_logit = torch.sort(logits, dim=-1, descending=True, stable=True).indices[:, :K].to(torch.int32)
+    assert torch.equal(ids.cpu(), by_logit)
+    gold_ids, gold_rw = omoe.route(logits, K)
+    pr = torch.softmax(logits, -1)
+    differing = 0
+    for t in range(T):
+        a, b = set(ids[t].tolist()), set(gold_ids[t].tolist())
+        if a != b:
+            differing += 1
+            pa = sorted(float(pr[t, e]) for e in a - b)
+            pb = sorted(float(pr[t, e]) for e in b - a)
+            assert pa == pb, "ids differ from the golden on experts whose golden probabilities are not equal"
+    torch.testing.assert_close(rw.cpu().sort(-1).values, gold_rw.sort(-1).values, rtol=1e-5, atol=1e-7)
+    print(f"rows whose ids differ from the probability-sorted golden: {differing} of {T}")
+
+
+# ------------------------------------------------------------------------------------------------ duplicate ids
+@pytest.mark.parametrize("T,K,NE", [(6, 4, 16), (640, 8, 16)], ids=["one_cta_plan", "three_kernel_plan"])
+def test_moe_experts_token_listing_an_expert_twice(q35, T, K, NE):
+    """ids is a caller tensor: a token may list an expert twice.  The golden adds rw * d for every listed pair; the
+    kernels give the expert one row weighted by the sum (both routing-plan forms)."""
+    from _cases import moe_case as mk
+    _, w = mk(1, NE=NE, seed=5)
+    g = torch.Generator().manual_seed(T)
+    h2 = torch.randn((T, 2048), generator=g).to(torch.bfloat16)
+    base = (torch.randn((T, 2048), generator=g) * 0.5).to(torch.bfloat16)
+    ids, rw = omoe.route(torch.randn((T, NE), generator=g), K)
+    ids[2, K - 1] = ids[2, 0]
+    ids[T - 1, 1] = ids[T - 1, 2]
+    sample = sorted({0, 2, T // 2, T - 1})
+    ref = omoe.experts_decode(h2[sample], base[sample], ids[sample], rw[sample], w["e_gw"], w["e_gs"], w["e_dw"], w["e_ds"])
+    out = torch.full_like(h2, float("nan")).cuda()
+    q35.moe_experts(h2.cuda(), base.cuda(), ids.cuda(), rw.cuda(), w["e_gw"].cuda(), w["e_gs"].cuda(), w["e_dw"].cuda(),
+                    w["e_ds"].cuda(), out)
+    assert torch.isfinite(out).all()
+    assert_parity(out.cpu()[sample], ref, bf16_step=True)
+
+
+# ------------------------------------------------------------------------------------------------ robustness
+def test_bounded_wait_reports_instead_of_hanging(q35):
+    """a device-side wait that can never complete (a barrier nothing arrives at, 4096 polls) gives up, sets the
+    wait-timeout bit of the status word and returns; the library works normally afterwards"""
+    polls = torch.tensor([4096], dtype=torch.int32, device="cuda")
+    result = torch.full((1,), -1, dtype=torch.int32, device="cuda")
+    q35.run("debug.wait_probe", polls=polls, result=result)
+    torch.cuda.synchronize()
+    assert int(result.item()) == 1
+    st = q35.device_status()
+    assert st & 4, st
+    assert q35.device_status() == 0
+    ids, _ = q35.route(torch.randn((4, 64), device="cuda"), 4)
+    assert ids.shape == (4, 4) and q35.device_status() == 0
+
+
+def test_two_host_threads_own_streams_bitwise_equal(q35):
+    """two host threads call in at the same time, each on its own stream with its own scratch: both must produce the
+    bytes a single-threaded call produces (the library keeps no state that one call could disturb for another)"""
+    from _cases import paged_case
+    q, cache, indptr, indices, last, _ = [t.cuda() if t is not None else None for t in paged_case([300, 17, 1500, 64])]
+    ref = q35.paged_attention_decode(q, cache, indptr, indices, last, sm_scale=1.0 / 16)
+    torch.cuda.synchronize()
+    outs, errs = [None, None], []
+
+    def work(i):
+        try:
+            s = torch.cuda.Stream()
+            with torch.cuda.stream(s):
+                for _ in range(20):
+                    o = q35.paged_attention_decode(q, cache, indptr, indices, last, sm_scale=1.0 / 16)
+                s.synchronize()
+            outs[i] = o
+        except Exception as e:  # noqa: BLE001
+            errs.append(e)
+
+    th = [threading.Thread(target=work, args=(i,)) for i in range(2)]
+    [t.start() for t in th]
+    [t.join() for t in th]
+    assert not errs, errs
+    for o in outs:
+        assert torch.equal(o.view(torch.int16), ref.view(torch.int16))

@@ -59,7 +59,7 @@ def test_moe_experts_decode(q35, T):
     ref = omoe.experts_decode(h2, base, ids, rw, w["e_gw"], w["e_gs"], w["e_dw"], w["e_ds"])
     out = torch.full_like(h2, float("nan")).cuda()
     q35.moe_experts(*cu(h2, base, ids, rw, w["e_gw"], w["e_gs"], w["e_dw"], w["e_ds"]), out)
-    assert_parity(out.cpu(), ref)
+    assert_parity(out.cpu(), ref, bf16_step=True)
     out2 = torch.empty_like(out)
     q35.moe_experts(*cu(h2, base, ids, rw, w["e_gw"], w["e_gs"], w["e_dw"], w["e_ds"]), out2)
     assert torch.equal(out.view(torch.int16), out2.view(torch.int16))  # run-to-run bitwise determinism
@@ -76,7 +76,7 @@ def test_moe_experts_one_expert_takes_every_token(q35):
     ref = omoe.experts_decode(h2, base, ids, rw, w["e_gw"], w["e_gs"], w["e_dw"], w["e_ds"])
     out = torch.empty_like(h2).cuda()
     q35.moe_experts(*cu(h2, base, ids, rw, w["e_gw"], w["e_gs"], w["e_dw"], w["e_ds"]), out)
-    assert_parity(out.cpu(), ref)
+    assert_parity(out.cpu(), ref, bf16_step=True)
 
 
 def test_moe_experts_partial_sums_for_expert_parallel(q35):
@@ -100,7 +100,7 @@ def test_moe_experts_partial_sums_for_expert_parallel(q35):
     partial = torch.full((T, 2048), float("nan")).cuda()
     q35.run("moe.experts", h2=h2.cuda(), ids=lids.cuda(), rw=rw.cuda(), e_gw=planes[0].cuda(), e_gs=planes[1].cuda(),
             e_dw=planes[2].cuda(), e_ds=planes[3].cuda(), partial_out=partial)
-    assert_parity(partial.cpu(), ref)
+    assert_parity(partial.cpu(), ref, bf16_step=True)
     # the same with GLOBAL ids and the first id of this rank's planes: bit-identical
     partial2 = torch.full((T, 2048), float("nan")).cuda()
     q35.run("moe.experts", h2=h2.cuda(), ids=ids.cuda(), rw=rw.cuda(), e_gw=planes[0].cuda(), e_gs=planes[1].cuda(),
@@ -141,7 +141,7 @@ def test_moe_block_end_to_end_ids_bit_exact(q35):
     assert torch.equal(gids.cpu(), omoe.route(glog.cpu(), 8)[0])
     # ... and the same experts as the CPU golden picked from its logits
     assert torch.equal(gids.cpu(), ids)
-    assert_parity(out.cpu(), ref)
+    assert_parity(out.cpu(), ref, bf16_step=True)
 
 
 def test_moe_permute_slots_combine(q35):
@@ -163,16 +163,16 @@ def test_moe_permute_slots_combine(q35):
         ref = omoe.slots(h2, tok, srw, w["e_gw"], w["e_gs"], w["e_dw"], w["e_ds"], out_dtype=dt)
         sout = torch.full((S, G, 2048), float("nan"), dtype=dt).cuda()
         q35.moe_slots_px(h2.cuda(), gtok, gsrw, *planes, sout, n_slots=gn)
-        assert_parity(sout.cpu()[:n], ref)
+        assert_parity(sout.cpu()[:n], ref, bf16_step=True)
         assert (sout.cpu()[n:] == 0).all()
         assert (sout.cpu()[:n].reshape(-1, 2048)[srw.reshape(-1) == 0] == 0).all()  # unused rows are zero
         out = torch.empty_like(base).cuda()
         q35.moe_combine(base.cuda(), gloc, sout, out)
         # same inputs on both sides; only the order of the K fp32 additions differs (the kernel adds row by row as
         # the reference kernel does, the golden sums the rows first): at most one bf16 rounding step
-        assert_parity(out.cpu(), omoe.combine(base, loc, sout.cpu().reshape(-1, 2048)), tol=1e-3)
+        assert_parity(out.cpu(), omoe.combine(base, loc, sout.cpu().reshape(-1, 2048)), tol=1e-3, bf16_step=True)
     full = omoe.experts_decode(h2, base, ids, rw, w["e_gw"], w["e_gs"], w["e_dw"], w["e_ds"])
-    assert_parity(out.cpu(), full)
+    assert_parity(out.cpu(), full, bf16_step=True)
 
 
 @pytest.mark.parametrize("fmt", ["mxfp4", "mxfp8", "fp8row"])
@@ -218,7 +218,7 @@ def _attn_check(q35, ctxs, P=64, HKV=2, HQ=16, D=256, fp8=False, per_head=True, 
             assert (out[b] == 0).all()
     nz = [b for b, cx in enumerate(ctxs) if cx > 0]
     if nz:  # one bf16 rounding step allowed: the split of the keys over CTAs follows the SM count of the device
-        assert_parity(out.cpu()[nz], ref[nz])
+        assert_parity(out.cpu()[nz], ref[nz], per_seq=True)
     return out
 
 
@@ -257,7 +257,7 @@ def test_paged_decode_poisoned_tail_rows_do_not_leak(q35):
         poisoned[page, :, int(last[b]):] = float("nan")
     out = q35.paged_attention_decode(q.cuda(), poisoned.cuda(), indptr.cuda(), indices.cuda(), last.cuda())
     assert torch.isfinite(out).all()
-    assert_parity(out.cpu(), ref)
+    assert_parity(out.cpu(), ref, per_seq=True)
 
 
 def test_paged_decode_current_token_and_cache_write(q35):
@@ -355,7 +355,7 @@ def test_linear_tc_block_scaled_mma(q35, T, N, K):
     outb = torch.empty((T, N), dtype=torch.bfloat16, device="cuda")
     bias = torch.randn(N, generator=g)
     q35.run("linear.tc", x=x.cuda(), w=w.cuda(), s=s.cuda(), bias=bias.cuda(), out=outb)
-    assert_parity(outb.cpu(), (ref + bias.double()).to(torch.bfloat16))
+    assert_parity(outb.cpu(), (ref + bias.double()).to(torch.bfloat16), bf16_step=True)
 
 
 @pytest.mark.parametrize("T", [400, 1024])
@@ -372,7 +372,7 @@ def test_moe_block_prefill_sized_batch(q35, T):
                                           w["e_gs"], w["e_dw"], w["e_ds"], 8)
     assert torch.equal(gids.cpu()[sample], ids)
     assert rel_rms_err(glog.cpu()[sample], logits) <= 1e-3  # tensor-core router GEMM, fp32 accumulation
-    assert_parity(out.cpu()[sample], ref)
+    assert_parity(out.cpu()[sample], ref, bf16_step=True)
     assert torch.isfinite(out).all()
 
 
@@ -454,7 +454,9 @@ def test_paged_prefill(q35, hist, T, P, HKV, HQ, D):
     q35.paged_attention_prefill(q.cuda(), cache.cuda(), qo.cuda(), indptr.cuda(), indices.cuda(), last.cuda(), out,
                                 sm_scale=0.07)
     assert torch.isfinite(out).all()
-    assert_parity(out.cpu(), ref)
+    # per token: every query token is a softmax of its own (one key for the first token of an empty history, hundreds
+    # for the last), so each token's output is measured against its own RMS
+    assert_parity(out.cpu(), ref, per_seq=True)
 
 
 def test_paged_prefill_writes_new_rows_then_decode_continues(q35):
@@ -480,10 +482,10 @@ def test_paged_prefill_writes_new_rows_then_decode_continues(q35):
     out = q35.paged_attention_prefill(q.cuda(), gcache, qo.cuda(), indptr.cuda(), indices.cuda(), last.cuda(),
                                       k_new=k_new.cuda(), v_new=v_new.cuda())
     assert torch.equal(gcache.cpu().view(torch.int16), ref_cache.view(torch.int16))
-    assert_parity(out.cpu(), ref)
+    assert_parity(out.cpu(), ref, per_seq=True)
     qd = torch.randn((2, 16, 256), generator=g).to(torch.bfloat16)
     dec = q35.paged_attention_decode(qd.cuda(), gcache, indptr.cuda(), indices.cuda(), last.cuda())
-    assert_parity(dec.cpu(), oattn.paged_decode(qd, ref_cache, indptr, indices, last))
+    assert_parity(dec.cpu(), oattn.paged_decode(qd, ref_cache, indptr, indices, last), per_seq=True)
 
 
 def test_lm_head_golden_fixture_and_vocabulary_sized(q35, golden):
@@ -558,7 +560,7 @@ def test_moe_block_prefill_8192_tokens_permutation_equivariance(q35):
     ref, rids, _, _ = omoe.moe_block(x1[sample], w["ln2"], sg, su, sd, w["w_router"], w["w_shg"], w["e_gw"], w["e_gs"],
                                      w["e_dw"], w["e_ds"], 8)
     assert torch.equal(ids.cpu()[sample], rids)
-    assert_parity(out.cpu()[sample], ref)
+    assert_parity(out.cpu()[sample], ref, bf16_step=True)
 
 
 def test_moe_experts_expert_parallel_shape_of_eight_ranks(q35):
@@ -588,7 +590,7 @@ def test_moe_experts_expert_parallel_shape_of_eight_ranks(q35):
                 ref += rw[t, i] * one
                 checked += 1
         if ref.abs().max() > 0:
-            assert_parity(got[t], ref)
+            assert_parity(got[t], ref, bf16_step=True)
         else:
             assert (got[t] == 0).all()
     assert checked > 0
