@@ -9,8 +9,8 @@ from ._lib import Q35Error, device_status, io_table, roles, run, workspace_bytes
 from .attention import kv_write, paged_attention_decode, paged_attention_prefill  # noqa: F401
 from .gdn import gdn_chunk_prefill, gdn_conv1d_silu, gdn_recurrent_step  # noqa: F401
 from .moe import (linear, moe_block, moe_combine, moe_experts, moe_permute, moe_pre, moe_slots_px,  # noqa: F401
-                  route)
+                  prepare_moe_weights, route, tile_scales)
 
 __all__ = ["run", "roles", "io_table", "workspace_bytes", "device_status", "Q35Error", "route", "moe_pre",
-           "moe_experts", "moe_slots_px", "moe_combine", "moe_permute", "moe_block", "linear",
+           "moe_experts", "moe_slots_px", "moe_combine", "moe_permute", "moe_block", "prepare_moe_weights", "tile_scales", "linear",
            "paged_attention_decode", "paged_attention_prefill", "kv_write", "gdn_recurrent_step", "gdn_conv1d_silu", "gdn_chunk_prefill"]

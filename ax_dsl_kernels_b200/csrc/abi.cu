@@ -222,6 +222,15 @@ static const RoleDef kRoles[] = {
     {"lm_head",
      R"({"in":[["x","bf16","[T,K]"],["w","u8","[N,K/2]"],["s","u8","[N,K/32]"],["workspace","u8","[*]"]],"out":[["logits","f32","[T,N] optional; also accepted under the name out"],["token","i32","[T] optional: first index of the row maximum"]]})",
      run_lm_head},
+    {"moe.block",
+     R"({"in":[["x1","bf16","[T,H]"],["ln2","f32","[H]"],["w_router","bf16","[NE,H]"],["w_shg","bf16","[H] with the shared expert"],["w_gate","u8","[FE,H/2] optional: shared expert, MXFP4"],["w_up","u8","[FE,H/2]"],["w_down","u8","[H,FE/2]"],["s_gate_up_tiled","u8","mx.tile_scales.paired of s_gate rows followed by s_up rows"],["s_down_tiled","u8","mx.tile_scales.plain of s_down"],["e_gw","u8","[NE,2FE,H/2]"],["e_dw","u8","[NE,H,FE/2]"],["e_gs_tiled","u8","mx.tile_scales.paired of e_gs"],["e_ds_tiled","u8","mx.tile_scales.plain of e_ds"],["workspace","u8","[*]"]],"out":[["out","bf16","[T,H]"],["ids","i32","[T,K]"],["rw","f32","[T,K]"],["logits_out","f32","[T,NE] optional"],["h2_out","bf16","[T,H] optional"]]})",
+     run_moe_block},
+    {"mx.tile_scales.paired",
+     R"({"in":[["s","u8","[planes,rows,K/32] E8M0, rows = gate rows then up rows"]],"out":[["out","u8","[planes,rows/128,K/128,512]"]]})",
+     run_tile_scales_paired},
+    {"mx.tile_scales.plain",
+     R"({"in":[["s","u8","[planes,rows,K/32] E8M0"]],"out":[["out","u8","[planes,rows/128,K/128,512]"]]})",
+     run_tile_scales_plain},
     {"debug.wait_probe",
      R"({"in":[["polls","i32","[1] poll limit of the wait, clamped to 1 .. 2^20"]],"out":[["result","i32","[1] 1 = the wait gave up and the status word got its bit"]]})",
      run_debug_wait_probe},

@@ -131,5 +131,8 @@ int run_act_sigmoid_gate(Call&);
 int run_linear_tc(Call&);
 int run_lm_head(Call&);
 int run_debug_wait_probe(Call&);
+int run_moe_block(Call&);
+int run_tile_scales_paired(Call&);
+int run_tile_scales_plain(Call&);
 
 }  // namespace q35

@@ -110,4 +110,59 @@ __device__ __forceinline__ float e8m0_to_f32(uint32_t s) {
   return s == 0 ? __uint_as_float(0x00400000u) : __uint_as_float(s << 23);
 }
 
+// RMSNorm of a row by a block of 256 threads, H a multiple of 8 and at most 8192: thread `tid` holds the 16-byte pieces
+// tid, tid + 256, ... of the row (at most four), all loaded before the first use.  The sum of squares is taken per
+// thread over its elements in order, then over the warp (warp_sum), then over the eight warp sums in order: every
+// kernel that normalises through these helpers produces the same bits.
+constexpr int RMS_MAX_PIECES = 4;
+struct RmsPieces { uint4 v[RMS_MAX_PIECES]; };
+__device__ __forceinline__ void rms_load(const __nv_bfloat16* xr, int H, int tid, RmsPieces& p) {
+#pragma unroll
+  for (int c = 0; c < RMS_MAX_PIECES; ++c) {
+    const int i = (tid + 256 * c) * 8;
+    p.v[c] = i < H ? *reinterpret_cast<const uint4*>(xr + i) : make_uint4(0u, 0u, 0u, 0u);
+  }
+}
+__device__ __forceinline__ float rms_sumsq(const RmsPieces& p) {
+  float ss = 0.f;
+#pragma unroll
+  for (int c = 0; c < RMS_MAX_PIECES; ++c) {
+    const uint32_t w[4] = {p.v[c].x, p.v[c].y, p.v[c].z, p.v[c].w};
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const float a = bf16lo(w[u]), b = bf16hi(w[u]);
+      ss += a * a;
+      ss += b * b;
+    }
+  }
+  return ss;
+}
+// y = bf16(x * rs * w) for this thread's pieces; dst0 / dst1 (either may be null) receive the row
+__device__ __forceinline__ void rms_apply(const RmsPieces& p, int H, int tid, float rs, const float* __restrict__ w,
+                                          __nv_bfloat16* dst0, __nv_bfloat16* dst1) {
+#pragma unroll
+  for (int c = 0; c < RMS_MAX_PIECES; ++c) {
+    const int i = (tid + 256 * c) * 8;
+    if (i >= H) break;
+    const float4 w0 = *reinterpret_cast<const float4*>(w + i), w1 = *reinterpret_cast<const float4*>(w + i + 4);
+    uint4 o;
+    o.x = pack_bf16(bf16lo(p.v[c].x) * rs * w0.x, bf16hi(p.v[c].x) * rs * w0.y);
+    o.y = pack_bf16(bf16lo(p.v[c].y) * rs * w0.z, bf16hi(p.v[c].y) * rs * w0.w);
+    o.z = pack_bf16(bf16lo(p.v[c].z) * rs * w1.x, bf16hi(p.v[c].z) * rs * w1.y);
+    o.w = pack_bf16(bf16lo(p.v[c].w) * rs * w1.z, bf16hi(p.v[c].w) * rs * w1.w);
+    if (dst0) *reinterpret_cast<uint4*>(dst0 + i) = o;
+    if (dst1) *reinterpret_cast<uint4*>(dst1 + i) = o;
+  }
+}
+
+// exponent of the UE8M0 block scale of an E4M3 block: the smallest e with amax * 2^-e <= 448 (= 1.75 * 2^8)
+__device__ __forceinline__ int e8m0_for(float amax) {
+  if (amax == 0.f) return -127;
+  const uint32_t b = __float_as_uint(amax);
+  const int E = int(b >> 23) - 127;
+  const uint32_t mant = b & 0x7fffffu;
+  int e = E - 8 + (mant > 0x600000u ? 1 : 0);  // mantissa above 1.75 needs one more octave
+  return max(-127, min(127, e));
+}
+
 }  // namespace q35

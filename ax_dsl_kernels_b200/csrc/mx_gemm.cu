@@ -440,9 +440,16 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const __nv_bfloat16* __res
   pdl_launch();
   const int t = blockIdx.x, tid = threadIdx.x;
   const __nv_bfloat16* xr = x + size_t(t) * H;
-  float ss = 0.f;
-  for (int i = tid; i < H; i += 256) { const float v = __bfloat162float(xr[i]); ss += v * v; }
   __shared__ float s_red[8];
+  const bool pieces = H <= 256 * 8 * RMS_MAX_PIECES && H % 8 == 0;  // the row fits the threads' registers
+  RmsPieces p;
+  float ss = 0.f;
+  if (pieces) {
+    rms_load(xr, H, tid, p);
+    ss = rms_sumsq(p);
+  } else {
+    for (int i = tid; i < H; i += 256) { const float v = __bfloat162float(xr[i]); ss += v * v; }
+  }
   ss = warp_sum(ss);
   if ((tid & 31) == 0) s_red[tid >> 5] = ss;
   __syncthreads();
@@ -450,7 +457,11 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const __nv_bfloat16* __res
 #pragma unroll
   for (int i = 0; i < 8; ++i) tot += s_red[i];
   const float rs = rsqrtf(tot / float(H) + eps);
-  for (int i = tid; i < H; i += 256) y[size_t(t) * H + i] = __float2bfloat16_rn(__bfloat162float(xr[i]) * rs * w[i]);
+  if (pieces) {
+    rms_apply(p, H, tid, rs, w, y + size_t(t) * H, nullptr);
+  } else {
+    for (int i = tid; i < H; i += 256) y[size_t(t) * H + i] = __float2bfloat16_rn(__bfloat162float(xr[i]) * rs * w[i]);
+  }
 }
 
 // logits[t, e] = sum_k h2[t, k] * w_router[e, k] in fp32 (bf16 products are exact in fp32); row NE is the shared-
@@ -625,7 +636,7 @@ static int moe_pre_impl(Call& c, int mode) {
   Q35_TRY(c.workspace(w.off, &ws));
   if (c.dry || T == 0) return 0;
   Q35_REQUIRE(aligned16(x1.p) && aligned16(h2o.p) && (!do_shared || (aligned16(out.p) && aligned16(wg.p) &&
-                  aligned16(wu.p) && aligned16(wd.p))) && (!do_norm || (aligned16(wr.p) && aligned16(wshg.p))),
+                  aligned16(wu.p) && aligned16(wd.p))) && (!do_norm || (aligned16(wr.p) && aligned16(wshg.p) && aligned16(ln2.p))),
               Q35_ERR_ALIGN, "moe.pre: pointers must be 16-byte aligned");
   WsCarver wc{ws.as<uint8_t>()};
   act = wc.take<__nv_bfloat16>(T * FS);

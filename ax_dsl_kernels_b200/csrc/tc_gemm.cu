@@ -87,15 +87,6 @@ static int encode_map(CUtensorMap* m, bool fp4, const void* base, uint64_t rows,
 // ---------------------------------------------------------------------------------------------------------------
 // x (bf16) -> two E4M3 terms with UE8M0 block-32 scales: x = hi * 2^eh + lo * 2^el;
 // rows gathered through `src` (destination row -> source row; nullptr = identity).
-__device__ __forceinline__ int e8m0_for(float amax) {  // smallest e with amax * 2^-e <= 448 (= 1.75 * 2^8)
-  if (amax == 0.f) return -127;
-  const uint32_t b = __float_as_uint(amax);
-  const int E = int(b >> 23) - 127;
-  const uint32_t mant = b & 0x7fffffu;
-  int e = E - 8 + (mant > 0x600000u ? 1 : 0);  // mantissa above 1.75 needs one more octave
-  return max(-127, min(127, e));
-}
-
 // Eight elements per thread (one 16-byte load), four threads per 32-block.
 __global__ void __launch_bounds__(256) tc_quant_kernel(const __nv_bfloat16* __restrict__ x, int x_stride,
                                                        const int* __restrict__ src, int x_rows, int R, int K,
@@ -218,6 +209,11 @@ int tc_build_active(const int* g_n, int groups, int* active, cudaStream_t stream
   tc_active_kernel<<<1, 1024, 0, stream>>>(g_n, groups, active + 1, active);
   Q35_CUDA_LAUNCH_CHECK("tc active groups");
   return 0;
+}
+
+int tc_make_map(CUtensorMap* m, bool fp4, const void* base, uint64_t rows, uint64_t cols, uint64_t pitch_bytes,
+                uint32_t box_rows, const char* what) {
+  return make_map(m, fp4, base, rows, cols, pitch_bytes, box_rows, what);
 }
 
 template <int NB, int EPI>

@@ -1,10 +1,16 @@
 // Host-side interface of the block-scaled tensor-core GEMM (tc_gemm.cu), shared with the MoE launchers.
 #pragma once
+#include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <cstdint>
 
 namespace q35 {
+
+// 2D row-major tensor [rows, cols] of bytes (fp4 = false) or packed FP4 codes (fp4 = true: cols counts codes, the
+// pitch is in bytes) with a [box_rows, 128-element] box and 128-byte swizzle; cached per (device, address, shape)
+int tc_make_map(CUtensorMap* m, bool fp4, const void* base, uint64_t rows, uint64_t cols, uint64_t pitch_bytes,
+                uint32_t box_rows, const char* what);
 
 struct TcArgs;
 

@@ -88,11 +88,48 @@ def _side_stream(dev):
     return _side_streams[key]
 
 
+def tile_scales(s, paired):
+    """E8M0 scales [planes, rows, K/32] (or [rows, K/32]) re-laid into the 512-byte blocks the decode kernel copies to
+    tensor memory (roles mx.tile_scales.paired / .plain): a load-time conversion, same bytes in another order.
+    paired: rows = gate rows followed by up rows, a tile takes 64 of each."""
+    s = _u8(s).contiguous()
+    out = torch.empty_like(s)
+    _lib.run("mx.tile_scales.paired" if paired else "mx.tile_scales.plain", s=s, out=out)
+    return out
+
+
+def prepare_moe_weights(w):
+    """adds the tiled scale tensors the one-call decode block (`moe.block`) reads -- e_gs_tiled, e_ds_tiled and, for an
+    MXFP4 shared expert, s_gate_up_tiled, s_down_tiled -- to a weight dict, once, at load time.  Returns the dict."""
+    if "e_gs_tiled" not in w:
+        w["e_gs_tiled"] = tile_scales(w["e_gs"], True)
+        w["e_ds_tiled"] = tile_scales(w["e_ds"], False)
+        if "w_gate" in w and w["w_gate"].dtype == torch.uint8:
+            w["s_gate_up_tiled"] = tile_scales(torch.cat([_u8(w["s_gate"]), _u8(w["s_up"])], 0), True)
+            w["s_down_tiled"] = tile_scales(w["s_down"], False)
+    return w
+
+
+def _one_call_ok(x1, w, top_k):
+    """shapes the one-call decode block takes: tiled scales present, decode-sized batch, MXFP4 shared expert of the
+    routed experts' shape, sizes that are multiples of 512"""
+    if "e_gs_tiled" not in w or "s_gate_up_tiled" not in w:
+        return False
+    T, H = x1.shape
+    NE, FE2 = w["e_gw"].shape[0], w["e_gw"].shape[1]
+    return (T * top_k <= 4096 and NE * ((T + 31) // 32) <= 4096 and NE < 1024 and H % 512 == 0 and H <= 8192
+            and (FE2 // 2) % 512 == 0 and w["w_gate"].shape[0] == FE2 // 2 and w["w_router"].shape[0] == NE)
+
+
 def moe_block(x1, w, top_k, out=None, overlap=True):
     """whole block on T tokens: dense part -> router -> routed experts.  w: dict with ln2, w_gate, s_gate, w_up,
-    s_up, w_down, s_down, w_router, w_shg, e_gw, e_gs, e_dw, e_ds.  Returns (out, ids, rw, logits).
-    overlap=True runs the shared expert on a second stream while the main stream routes and runs the routed experts
-    (the two only meet in the final sum); overlap=False is the plain moe_pre -> route -> moe_experts sequence."""
+    s_up, w_down, s_down, w_router, w_shg, e_gw, e_gs, e_dw, e_ds.  Returns (out, ids, rw, logits); ids, rw and logits
+    are scratch tensors of this module, valid until the next call with the same shapes (clone them to keep them).
+
+    A weight dict that went through prepare_moe_weights() takes the one-call decode form (role `moe.block`: five
+    launches on one stream) for decode-sized batches.  Otherwise: overlap=True runs the shared expert on a second
+    stream while the main stream routes and runs the routed experts (the two only meet in the final sum);
+    overlap=False is the plain moe_pre -> route -> moe_experts sequence."""
     T, H = x1.shape
     dev = x1.device
     NE = w["w_router"].shape[0]
@@ -108,6 +145,12 @@ def moe_block(x1, w, top_k, out=None, overlap=True):
             rw=torch.empty((T, top_k), dtype=torch.float32, device=dev))
     base, h2, logits = bufs["base"], bufs["h2"], bufs["logits"]
     out = torch.empty_like(x1) if out is None else out
+    if overlap and _one_call_ok(x1, w, top_k):
+        _lib.run("moe.block", x1=x1, ln2=w["ln2"], w_router=w["w_router"], w_shg=w["w_shg"].reshape(-1),
+                 w_gate=w["w_gate"], w_up=w["w_up"], w_down=w["w_down"], s_gate_up_tiled=w["s_gate_up_tiled"],
+                 s_down_tiled=w["s_down_tiled"], e_gw=_u8(w["e_gw"]), e_dw=_u8(w["e_dw"]), e_gs_tiled=w["e_gs_tiled"],
+                 e_ds_tiled=w["e_ds_tiled"], out=out, ids=bufs["ids"], rw=bufs["rw"], logits_out=logits, h2_out=h2)
+        return out, bufs["ids"], bufs["rw"], logits
     if not overlap:
         moe_pre(x1, w["ln2"], w["w_gate"], w["s_gate"], w["w_up"], w["s_up"], w["w_down"], w["s_down"], w["w_router"],
                 w["w_shg"], base, h2, logits)

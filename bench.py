@@ -257,6 +257,7 @@ def run_ours(args):
         ep = parallel.ExpertParallelMoE(wl.w, TOPK, dist.group.WORLD)
         moe_step = lambda x: ep.forward(x, wl.moe_out)  # noqa: E731
     else:
+        q35.prepare_moe_weights(wl.w)  # load-time re-layout of the E8M0 scales for the one-call decode block
         moe_step = lambda x: q35.moe_block(x, wl.w, TOPK, wl.moe_out)  # noqa: E731
 
     def gdn_only():
@@ -595,6 +596,7 @@ def run_profile_case(name, reps):
         elif name == "gdn":
             fn = lambda: q35.gdn_recurrent_step(wl.gq, wl.gk, wl.gv, wl.gg, wl.gbeta, wl.state, wl.g_out, wl.state)  # noqa: E731
         else:
+            q35.prepare_moe_weights(wl.w)
             fn = lambda: q35.moe_block(wl.x1, wl.w, TOPK, wl.moe_out)  # noqa: E731
     fn()
     torch.cuda.synchronize()

@@ -151,6 +151,59 @@ def test_config4_decode_moe_block_64_tokens_256_experts(q35):
     assert_parity(out.cpu(), ref, bf16_step=True)
     out2, _, _, _ = q35.moe_block(x1.cuda(), wd, 8, overlap=False)
     assert_parity(out2.cpu(), ref, bf16_step=True, name="config4 decode, moe_pre -> route -> moe_experts sequence")
+    q35.prepare_moe_weights(wd)  # one-call decode form
+    out3, gids3, _, _ = q35.moe_block(x1.cuda(), wd, 8)
+    assert torch.equal(gids3.cpu(), ids)
+    assert_parity(out3.cpu(), ref, bf16_step=True, name="config4 decode, one-call moe.block")
+
+
+# ------------------------------------------------------------------------------------------------ one-call decode block
+def _tile_ref(s, paired):
+    """the tiled scale layout stated in words: block (plane, tile, K / 128) of 512 bytes, byte [l * 16 + c * 4 + b] =
+    scale of tile row l + 32 c for inputs 128 s + 32 b ..; a paired tile = 64 gate rows then 64 up rows"""
+    planes, rows, KB = s.shape
+    tiles, KS = rows // 128, KB // 4
+    m = torch.arange(128)
+    t = torch.arange(tiles).reshape(-1, 1)
+    row = torch.where(m < 64, t * 64 + m, rows // 2 + t * 64 + (m - 64)) if paired else t * 128 + m
+    src = s[:, row]                                                  # [planes, tiles, 128 (m = l + 32 c), KB]
+    src = src.reshape(planes, tiles, 4, 32, KS, 4)                   # c, l, stage, b
+    return src.permute(0, 1, 4, 3, 2, 5).reshape(planes, tiles, KS, 512).contiguous()
+
+
+@pytest.mark.parametrize("paired", [True, False])
+def test_tile_scales_layout_bit_exact(q35, paired):
+    g = torch.Generator().manual_seed(3)
+    s = torch.randint(0, 256, (3, 256, 16), generator=g, dtype=torch.int32).to(torch.uint8)
+    got = q35.tile_scales(s.cuda(), paired).cpu()
+    assert torch.equal(got.reshape(-1), _tile_ref(s, paired).reshape(-1))
+
+
+@pytest.mark.parametrize("T,NE", [(1, 32), (7, 32), (33, 64), (64, 256)])
+def test_moe_block_one_call_decode_form(q35, T, NE):
+    """role moe.block (norm + router, route + plan, quantise, ONE persistent gate-up + down kernel with the shared
+    expert as a group, combine) against the golden and against the role-by-role path on the same weights"""
+    x1, w = moe_case(T, NE=NE, seed=100 + T)
+    w["ln2"] = 1 + 0.05 * torch.randn(2048, generator=torch.Generator().manual_seed(T))
+    sg, su, sd = dequant_shared(w)
+    ref, ids, rw, logits = omoe.moe_block(x1, w["ln2"], sg, su, sd, w["w_router"], w["w_shg"], w["e_gw"], w["e_gs"],
+                                          w["e_dw"], w["e_ds"], 8)
+    wd = {k: v.cuda() for k, v in w.items()}
+    old, oids, _, ologits = q35.moe_block(x1.cuda(), wd, 8)
+    old, oids, ologits = old.clone(), oids.clone(), ologits.clone()
+    q35.prepare_moe_weights(wd)
+    out = torch.full_like(x1, float("nan")).cuda()
+    out, gids, grw, glog = q35.moe_block(x1.cuda(), wd, 8, out)
+    assert q35.device_status() == 0
+    assert torch.equal(glog, ologits)          # same order of operations as the role-by-role router: same bits
+    assert torch.equal(gids, oids) and torch.equal(gids.cpu(), ids)
+    torch.testing.assert_close(grw.cpu(), rw, rtol=1e-4, atol=1e-6)
+    assert torch.isfinite(out).all()
+    assert_parity(out.cpu(), ref, bf16_step=True)
+    assert_parity(out.cpu(), old.cpu(), bf16_step=True, name=f"moe.block vs role-by-role path, T={T}")
+    out2 = torch.empty_like(out)
+    q35.moe_block(x1.cuda(), wd, 8, out2)
+    assert torch.equal(out.view(torch.int16), out2.view(torch.int16))  # run-to-run bitwise determinism
 
 
 # ------------------------------------------------------------------------------------------------ router near-ties
