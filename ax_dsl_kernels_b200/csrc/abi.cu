@@ -198,7 +198,7 @@ static const RoleDef kRoles[] = {
      R"({"in":[["q","bf16","[B,T,NK,128]"],["k","bf16","[B,T,NK,128]"],["v","bf16","[B,T,NV,128]"],["g","f32","[B,T,NV]"],["beta","bf16","[B,T,NV]"],["state_in","f32","[B,NV,128,128]"],["workspace","u8","[*]"]],"out":[["o","bf16","[B,T,NV,128]"],["state_out","f32","[B,NV,128,128]"]]})",
      run_gdn_chunk_prefill},
     {"linear",
-     R"({"in":[["x","bf16","[T,K]"],["w","u8|e4m3|bf16","[N,K/2]|[N,K]"],["s","u8|f32","[N,K/32]|[N] optional"],["bias","f32","[N] optional"],["row_div","f32","[T] optional"],["residual","bf16","[T,N] optional"]],"out":[["out","bf16|f32","[T,N]"]]})",
+     R"({"in":[["x","bf16","[T,K]"],["w","u8|e4m3|bf16","[N,K/2]|[N,K]"],["s","u8|f32","[N,K/32]|[N] optional"],["bias","f32","[N] optional"],["row_div","f32","[T] optional"],["residual","bf16","[T,N] optional"],["workspace","u8","[*] optional: with it (and K a multiple of 512) the tensor-core path runs"]],"out":[["out","bf16|f32","[T,N]"]]})",
      run_linear},
     {"norm.rms",
      R"({"in":[["x","bf16","[T,H]"],["residual","bf16","[T,H] optional"],["w","f32|bf16","[H]"],["eps","f32","[1] optional"]],"out":[["y","bf16","[T,H]"],["base_out","bf16","[T,H] optional"],["xsqrt_out","f32","[T] optional: folded form"]]})",

@@ -137,6 +137,19 @@ __device__ __forceinline__ float rms_sumsq(const RmsPieces& p) {
   }
   return ss;
 }
+// the running sum of squares continued over one more piece (same element order as rms_sumsq)
+__device__ __forceinline__ float rms_chain(float ss, const uint4& v) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    const float a = bf16lo(w[u]), b = bf16hi(w[u]);
+    ss += a * a;
+    ss += b * b;
+  }
+  return ss;
+}
+__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
+
 // y = bf16(x * rs * w) for this thread's pieces; dst0 / dst1 (either may be null) receive the row
 __device__ __forceinline__ void rms_apply(const RmsPieces& p, int H, int tid, float rs, const float* __restrict__ w,
                                           __nv_bfloat16* dst0, __nv_bfloat16* dst1) {

@@ -111,22 +111,9 @@ moe_decode_kernel(const __grid_constant__ CUtensorMap m_wg, const __grid_constan
   auto acc_full = [&](int b) { return s_bar + 128 + 8 * b; };
   auto acc_empty = [&](int b) { return s_bar + 144 + 8 * b; };
 
-  if (tid == 0) {
-    for (int s = 0; s < MD_STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(acc_full(b), 1); mbar_init(acc_empty(b), 1); }
-    fence_barrier_init();
-    tma_prefetch_desc(&m_wg); tma_prefetch_desc(&m_wd); tma_prefetch_desc(&m_x1h); tma_prefetch_desc(&m_x1l);
-    tma_prefetch_desc(&m_x2h); tma_prefetch_desc(&m_x2l);
-  }
-  if (warp == 1) { tmem_alloc(s_slot, MD_TMEM_COLS); tmem_relinquish(); }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = *g_slot;
-  // everything above touches only this CTA's shared and tensor memory and may overlap the previous kernel's tail
-  pdl_wait();
-  pdl_launch();
-
+  // The plan (groups, rows, list of groups with rows) was written by the kernel before the one ahead of this one, which
+  // had completed when this kernel was allowed to start: the item table is built before the wait, under the tail of
+  // the kernel ahead.
   const int n_act = a.active[0];
   const int T1 = a.FE / 64, T2 = a.H / 128;
   const int items1 = n_act * T1, total = items1 + n_act * T2;
@@ -166,7 +153,22 @@ moe_decode_kernel(const __grid_constant__ CUtensorMap m_wg, const __grid_constan
     s_item[tid] = im;
     s_grp[tid] = grp;
   }
+  if (tid == 0) {
+    for (int s = 0; s < MD_STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(acc_full(b), 1); mbar_init(acc_empty(b), 1); }
+    fence_barrier_init();
+    tma_prefetch_desc(&m_wg); tma_prefetch_desc(&m_wd); tma_prefetch_desc(&m_x1h); tma_prefetch_desc(&m_x1l);
+    tma_prefetch_desc(&m_x2h); tma_prefetch_desc(&m_x2l);
+  }
+  if (warp == 1) { tmem_alloc(s_slot, MD_TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before();
   __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *g_slot;
+  // everything above may overlap the previous kernel's tail
+  pdl_wait();
+  pdl_launch();
+
   const int KS1 = a.H / 128, KS2 = a.FE / 128;
 
   if (warp == 0) {
@@ -368,7 +370,7 @@ __device__ __forceinline__ uint32_t orderable(float f) {  // monotone map of flo
 }
 
 template <int PER>
-__global__ void __launch_bounds__(256) moe_front_kernel(const __nv_bfloat16* __restrict__ x1,
+__global__ void __launch_bounds__(256, 4) moe_front_kernel(const __nv_bfloat16* __restrict__ x1,
                                                         const float* __restrict__ ln2,
                                                         const __nv_bfloat16* __restrict__ w_router,
                                                         const __nv_bfloat16* __restrict__ w_shg,
@@ -386,34 +388,66 @@ __global__ void __launch_bounds__(256) moe_front_kernel(const __nv_bfloat16* __r
   __shared__ int s_flag, s_flag_all, s_tot;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int t0 = int(blockIdx.x) * tok_per, nt = min(tok_per, T - t0);
+  const int rows = NE + 1, per = (rows + int(gridDim.y) - 1) / int(gridDim.y);
+  const int e0 = int(blockIdx.y) * per, e1 = min(rows, e0 + per);
+  // Everything the CTA will need is requested at once: the tokens' rows as loads, ln2 and this warp's router rows as
+  // prefetches into L2 (they cost no registers; the loads that follow find the lines there or on their way).
+  for (int e = e0 + warp; e < e1; e += 8) {
+    const __nv_bfloat16* wr = e < NE ? w_router + size_t(e) * H : w_shg;
+    for (int b = lane * 128; b < H * 2; b += 32 * 128) prefetch_l2(reinterpret_cast<const char*>(wr) + b);
+  }
+  for (int b = tid * 128; b < H * 4; b += 256 * 128) prefetch_l2(reinterpret_cast<const char*>(ln2) + b);
   {
-    // every token's row goes out in one round of 16-byte loads (tok_per * H <= 8192 elements = four pieces a thread)
-    const int ppt = (H / 8 + 255) / 256;  // pieces per thread and token
-    RmsPieces p[NR_TOK];
+    // tok_per * ceil(H / 2048) <= 4 pieces of 16 bytes a thread: piece q = token q / ppt, chunk q % ppt
+    const int ppt = (H + 2047) / 2048;
+    uint4 xp[4];
 #pragma unroll
-    for (int j = 0; j < NR_TOK; ++j)
-      if (j < nt) rms_load(x1 + size_t(t0 + j) * H, H, tid, p[j]);
-    (void)ppt;
+    for (int q = 0; q < 4; ++q) {
+      const int j = q / ppt, i = (tid + 256 * (q % ppt)) * 8;
+      xp[q] = (j < nt && i < H) ? *reinterpret_cast<const uint4*>(x1 + size_t(t0 + j) * H + i) : make_uint4(0u, 0u, 0u, 0u);
+    }
+    float ssq[4];  // per piece, elements in order (the order rms_sumsq takes them in)
 #pragma unroll
-    for (int j = 0; j < NR_TOK; ++j) {
-      if (j >= nt) break;
-      const float ss = warp_sum(rms_sumsq(p[j]));
+    for (int q = 0; q < 4; ++q) {
+      const uint32_t w[4] = {xp[q].x, xp[q].y, xp[q].z, xp[q].w};
+      float ss = 0.f;
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const float a = bf16lo(w[u]), b = bf16hi(w[u]);
+        ss += a * a;
+        ss += b * b;
+      }
+      ssq[q] = ss;
+    }
+    for (int j = 0; j < nt; ++j) {
+      // a token's pieces in chunk order: continue one running sum, as rms_sumsq does over a thread's pieces
+      float ss = 0.f;
+#pragma unroll
+      for (int q = 0; q < 4; ++q)
+        if (q / ppt == j) ss = (q % ppt == 0) ? ssq[q] : rms_chain(ss, xp[q]);
+      ss = warp_sum(ss);
       if (lane == 0) s_red[j * 8 + warp] = ss;
     }
     __syncthreads();
 #pragma unroll
-    for (int j = 0; j < NR_TOK; ++j) {
-      if (j >= nt) break;
+    for (int q = 0; q < 4; ++q) {
+      const int j = q / ppt, i = (tid + 256 * (q % ppt)) * 8;
+      if (j >= nt || i >= H) continue;
       float tot = 0.f;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) tot += s_red[j * 8 + i];
+      for (int u = 0; u < 8; ++u) tot += s_red[j * 8 + u];
       const float rs = rsqrtf(tot / float(H) + eps);
-      rms_apply(p[j], H, tid, rs, ln2, s_h2 + j * H, blockIdx.y == 0 ? h2 + size_t(t0 + j) * H : nullptr);
+      const float4 w0 = *reinterpret_cast<const float4*>(ln2 + i), w1 = *reinterpret_cast<const float4*>(ln2 + i + 4);
+      uint4 o;
+      o.x = pack_bf16(bf16lo(xp[q].x) * rs * w0.x, bf16hi(xp[q].x) * rs * w0.y);
+      o.y = pack_bf16(bf16lo(xp[q].y) * rs * w0.z, bf16hi(xp[q].y) * rs * w0.w);
+      o.z = pack_bf16(bf16lo(xp[q].z) * rs * w1.x, bf16hi(xp[q].z) * rs * w1.y);
+      o.w = pack_bf16(bf16lo(xp[q].w) * rs * w1.z, bf16hi(xp[q].w) * rs * w1.w);
+      *reinterpret_cast<uint4*>(s_h2 + j * H + i) = o;
+      if (blockIdx.y == 0) *reinterpret_cast<uint4*>(h2 + size_t(t0 + j) * H + i) = o;
     }
   }
   __syncthreads();
-  const int rows = NE + 1, per = (rows + int(gridDim.y) - 1) / int(gridDim.y);
-  const int e0 = int(blockIdx.y) * per, e1 = min(rows, e0 + per);
   for (int e = e0 + warp; e < e1; e += 8) {
     const __nv_bfloat16* wr = e < NE ? w_router + size_t(e) * H : w_shg;
     float acc[NR_TOK] = {0.f, 0.f, 0.f, 0.f};
@@ -654,33 +688,43 @@ __global__ void __launch_bounds__(256) moe_block_combine_kernel(const __nv_bfloa
                                                                 const float* __restrict__ sout,
                                                                 __nv_bfloat16* __restrict__ out, int T, int H, int K,
                                                                 int has_shared) {
-  pdl_wait();
-  pdl_launch();
+  // x1, gate, rw and loc were written by kernels that completed before the kernel ahead of this one passed its own
+  // wait (every kernel of the chain waits before it lets its successor start), so they may be read before this
+  // kernel's wait: their latency then hides behind the tail of the GEMM.  Only the rows need the wait.
   const int t = blockIdx.x;
   const int h = (blockIdx.y * blockDim.x + threadIdx.x) * 4;
-  if (h >= H) return;
-  const uint2 xb = *reinterpret_cast<const uint2*>(x1 + size_t(t) * H + h);
-  float acc[4] = {bf16lo(xb.x), bf16hi(xb.x), bf16lo(xb.y), bf16hi(xb.y)};
-  float4 rows[8];
-  float wts[8];
-  // all row loads go out before the first use; K <= 8 here, the general loop below takes the rest
+  const bool on = h < H;
+  uint2 xb = make_uint2(0u, 0u);
+  int rix[8], rsh = -1;
+  float wts[8], sg = 0.f;
   const int kmax = K < 8 ? K : 8;
+  if (on) {
+    xb = *reinterpret_cast<const uint2*>(x1 + size_t(t) * H + h);
 #pragma unroll
-  for (int k = 0; k < 8; ++k) {
-    wts[k] = 0.f;
-    rows[k] = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (k < kmax) {
-      const int r = loc[size_t(k) * T + t];
-      if (r >= 0) {
-        rows[k] = *reinterpret_cast<const float4*>(sout + size_t(r) * H + h);
-        wts[k] = rw[size_t(t) * K + k];
-      }
+    for (int k = 0; k < 8; ++k) {
+      rix[k] = k < kmax ? loc[size_t(k) * T + t] : -1;
+      wts[k] = k < kmax ? rw[size_t(t) * K + k] : 0.f;
+    }
+    if (has_shared) {
+      rsh = loc[size_t(K) * T + t];
+      sg = 1.0f / (1.0f + expf(-gate[t]));
     }
   }
+  pdl_wait();
+  pdl_launch();
+  if (!on) return;
+  float acc[4] = {bf16lo(xb.x), bf16hi(xb.x), bf16lo(xb.y), bf16hi(xb.y)};
+  float4 rows[8];
+  float4 sh = make_float4(0.f, 0.f, 0.f, 0.f);
+  // all row loads go out before the first use; K <= 8 here, the general loop below takes the rest
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    rows[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (rix[k] >= 0) rows[k] = *reinterpret_cast<const float4*>(sout + size_t(rix[k]) * H + h);
+    else wts[k] = 0.f;
+  }
+  if (rsh >= 0) sh = *reinterpret_cast<const float4*>(sout + size_t(rsh) * H + h);
   if (has_shared) {
-    const int r = loc[size_t(K) * T + t];
-    const float4 sh = *reinterpret_cast<const float4*>(sout + size_t(r) * H + h);
-    const float sg = 1.0f / (1.0f + expf(-gate[t]));
     acc[0] = round_bf16(acc[0] + sh.x * sg); acc[1] = round_bf16(acc[1] + sh.y * sg);
     acc[2] = round_bf16(acc[2] + sh.z * sg); acc[3] = round_bf16(acc[3] + sh.w * sg);
   }
@@ -878,8 +922,7 @@ int run_moe_block(Call& c) {
   cudaStream_t st = c.stream;
 
   // 1. norm + router + route + plan
-  int tok_per = int(NR_MAX_H / H);
-  tok_per = tok_per > NR_TOK ? NR_TOK : tok_per < 1 ? 1 : tok_per;
+  const int tok_per = NR_TOK / int((H + 2047) / 2048);  // four 16-byte pieces a thread hold the CTA's token rows
   const int tgroups = int((T + tok_per - 1) / tok_per);
   cudaMemsetAsync(counters, 0, size_t(tgroups + 1) * sizeof(int), st);  // the "who finishes last" counters start at zero
   const int max_slices = int((NE + 1 + 7) / 8);  // at least eight rows (one per warp) per CTA

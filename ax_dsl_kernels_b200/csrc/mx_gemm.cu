@@ -768,9 +768,27 @@ int run_linear(Call& c) {
   Q35_REQUIRE((!rdiv.present || rdiv.numel() == T) && (!resid.present || resid.numel() == T * N), Q35_ERR_SHAPE,
               "linear: row_div [T], residual [T, N]");
   Q35_REQUIRE(K % 256 == 0, Q35_ERR_UNSUPPORTED, "linear: K must be a multiple of 256");
-  c.ws_need = 0;
+  // With K a multiple of 512 and a workspace bound, the projection runs on the tensor cores (tcgen05 block-scaled MMA:
+  // E2M1 or E4M3 weights straight from TMA, activations as two E4M3 terms); without a workspace, or for other K, on the
+  // CUDA-core weight-streaming kernel.  Same results within the tolerance of the role.
+  const bool tc_shape = K % 512 == 0;
+  const int64_t need = tc_shape ? tc_quant_bytes(T, K) : 0;
+  Tensor ws;
+  c.ws_need = need;
+  if (!c.dry) Q35_TRY(c.get("workspace", M(Q35_U8), &ws, false));
   if (c.dry || T == 0 || N == 0) return 0;
   Q35_REQUIRE(aligned16(x.p) && aligned16(w.p), Q35_ERR_ALIGN, "linear: pointers must be 16-byte aligned");
+  if (tc_shape && ws.present && int64_t(ws.bytes) >= need && (reinterpret_cast<uintptr_t>(ws.p) & 255) == 0 &&
+      (reinterpret_cast<uintptr_t>(w.p) & 31) == 0 && aligned16(s.p)) {
+    TcLinear p{};
+    p.w = w.p; p.s = s.p; p.fmt = fmt == W_MXFP4 ? 0 : fmt == W_MXFP8 ? 1 : 2;
+    p.bias = bias.present ? bias.as<float>() : nullptr;
+    p.row_div = rdiv.present ? rdiv.as<float>() : nullptr;
+    p.resid2 = resid.present ? resid.as<__nv_bfloat16>() : nullptr;
+    p.f_out = out.dtype == Q35_F32 ? out.as<float>() : nullptr;
+    p.b_out = out.dtype == Q35_F32 ? nullptr : out.as<__nv_bfloat16>();
+    return tc_linear(x.as<__nv_bfloat16>(), T, N, K, p, ws.as<uint8_t>(), c.stream);
+  }
   SkinnyArgs d{};
   d.status = device_status_ptr();
   d.n_dense = int(T); d.n_planes = 1;

@@ -234,9 +234,12 @@ int tc_launch(const TcWeights& w, const TcQuant& q, TcArgs a, int nb, int tiles,
   Q35_REQUIRE(a.K % 512 == 0 && a.K == q.K, Q35_ERR_UNSUPPORTED, "tc gemm: K must be a multiple of 512");
   Q35_REQUIRE((uintptr_t(a.sw[0]) & 15) == 0 && (uintptr_t(a.sw[1]) & 15) == 0 && (a.s_plane & 15) == 0, Q35_ERR_ALIGN,
               "tc gemm: scale tensors must be 16-byte aligned");
+  Q35_REQUIRE((a.sw[0] == nullptr) == (a.sw[1] == nullptr), Q35_ERR_MISSING, "tc gemm: scales of one half only");
   CUtensorMap w0, w1, xh, xl;
-  Q35_TRY(make_map(&w0, true, w.w[0], w.rows_total[0], a.K, a.K / 2, 64, "weights"));
-  Q35_TRY(make_map(&w1, true, w.w[1], w.rows_total[1], a.K, a.K / 2, 64, "weights"));
+  const bool fp4 = a.w_fp8 == 0;
+  a.a_fmt = fp4 ? int(tc::FMT_E2M1) : int(tc::FMT_E4M3);
+  Q35_TRY(make_map(&w0, fp4, w.w[0], w.rows_total[0], a.K, fp4 ? a.K / 2 : a.K, 64, "weights"));
+  Q35_TRY(make_map(&w1, fp4, w.w[1], w.rows_total[1], a.K, fp4 ? a.K / 2 : a.K, 64, "weights"));
   if (!a.g_n) {
     // dense: the rows are cut into virtual groups.  Every group streams the whole weight matrix, so groups are only
     // made smaller than 256 rows while the row tiles alone leave CTAs idle (decode-sized inputs on small matrices,
@@ -254,6 +257,7 @@ int tc_launch(const TcWeights& w, const TcQuant& q, TcArgs a, int nb, int tiles,
   Q35_REQUIRE(a.g_n == nullptr || (a.active != nullptr && a.n_active != nullptr), Q35_ERR_WORKSPACE,
               "tc gemm: grouped launch without an active-group list");
   a.status = device_status_ptr();
+  a.stage_tx = (fp4 ? 128 * 64 : 128 * 128) + 2 * nb * 128;
   if (nb == 16) return launch_nb<16, EPI>(w0, w1, xh, xl, a, tiles, groups, stream);
   if (nb == 32) return launch_nb<32, EPI>(w0, w1, xh, xl, a, tiles, groups, stream);
   return launch_nb<64, EPI>(w0, w1, xh, xl, a, tiles, groups, stream);
@@ -268,20 +272,33 @@ template int tc_launch<TC_EPI_PLAIN>(const TcWeights&, const TcQuant&, TcArgs, i
 // linear.tc: out[t, n] = x[t, :] . dequant_mxfp4(w[n, :]) on the tensor cores (same contract as `linear` with MXFP4
 // weights; reference: linear(x, w, s) of the MX projections, models/qwen35_2b/whole/src/q35_mx_build.py:100-115)
 // shared by linear.tc and lm_head: quantise x into the workspace and run the plain-epilogue GEMM
-static int linear_tc_impl(const Tensor& x, const Tensor& w, const Tensor& s, const float* bias, float* f_out,
-                          __nv_bfloat16* b_out, uint8_t* qws, int64_t T, int64_t N, int64_t K, cudaStream_t stream) {
+int tc_linear(const __nv_bfloat16* x, int64_t T, int64_t N, int64_t K, const TcLinear& p, uint8_t* qws,
+              cudaStream_t stream) {
   const TcQuant q = tc_quant_carve(qws, T, K);
-  Q35_TRY(tc_quantize(x.as<__nv_bfloat16>(), int(K), nullptr, int(T), int(T), int(K), q, stream));
-  TcWeights tw{{w.as<uint8_t>(), w.as<uint8_t>()}, {uint64_t(N), uint64_t(N)}};
+  Q35_TRY(tc_quantize(x, int(K), nullptr, int(T), int(T), int(K), q, stream));
+  const uint8_t* w = static_cast<const uint8_t*>(p.w);
+  TcWeights tw{{w, w}, {uint64_t(N), uint64_t(N)}};
   TcArgs a{};
   a.n_dense = int(T); a.n_planes = 1; a.K = int(K);
   a.plane_rows[0] = a.plane_rows[1] = int(N);
   a.roff[0] = 0; a.roff[1] = 64; a.lim[0] = a.lim[1] = int(N); a.tile_rows = 128;
-  a.sw[0] = a.sw[1] = s.as<uint8_t>(); a.s_plane = 0;
-  a.f_out = f_out; a.b_out = b_out;
+  a.w_fp8 = p.fmt == 0 ? 0 : 1;
+  // block scales: E8M0 [N, K/32] for the MX formats; FP8 per-row has none (block scale 1) and a fp32 scale per row
+  a.sw[0] = a.sw[1] = p.fmt == 2 ? nullptr : static_cast<const uint8_t*>(p.s);
+  a.row_scale = p.fmt == 2 ? static_cast<const float*>(p.s) : nullptr;
+  a.s_plane = 0;
+  a.f_out = p.f_out; a.b_out = p.b_out;
   a.out_stride = int(N);
-  a.bias = bias;
+  a.bias = p.bias; a.row_div = p.row_div; a.resid2 = p.resid2;
   return tc_launch<TC_EPI_PLAIN>(tw, q, a, int(T), int((N + 127) / 128), 1, stream);
+}
+
+// shared by linear.tc and lm_head: quantise x into the workspace and run the plain-epilogue GEMM
+static int linear_tc_impl(const Tensor& x, const Tensor& w, const Tensor& s, const float* bias, float* f_out,
+                          __nv_bfloat16* b_out, uint8_t* qws, int64_t T, int64_t N, int64_t K, cudaStream_t stream) {
+  TcLinear p{};
+  p.w = w.p; p.s = s.p; p.fmt = 0; p.bias = bias; p.f_out = f_out; p.b_out = b_out;
+  return tc_linear(x.as<__nv_bfloat16>(), T, N, K, p, qws, stream);
 }
 
 int run_linear_tc(Call& c) {

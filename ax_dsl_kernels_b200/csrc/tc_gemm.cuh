@@ -50,6 +50,12 @@ struct TcArgs {
   __nv_bfloat16* act_out;
   float* f_out; __nv_bfloat16* b_out; int out_stride;
   const float* rw_row; const __nv_bfloat16* resid; const float* gate; const float* bias;
+  // TC_EPI_PLAIN extras (the `linear` role): v = acc * row_scale[row] + bias[row]; then, when bound,
+  // v = bf16(v) / row_div[token] and v = bf16(v) + resid2[token, row]
+  const float* row_scale; const float* row_div; const __nv_bfloat16* resid2;
+  int w_fp8;                // 0: weights are MXFP4 pairs; 1: E4M3 bytes (MXFP8 with E8M0 scales, or FP8 per-row: sw null)
+  int a_fmt;                // set by the launcher from w_fp8: FMT_E2M1 or FMT_E4M3
+  int stage_tx;             // bytes the TMA unit reports per stage (FP4 tiles count their packed bytes)
   const int* active; const int* n_active;  // compacted list of groups with rows (nullptr: dense)
   int n_tiles;              // row tiles per group
   int* status;
@@ -185,7 +191,7 @@ __global__ void __launch_bounds__(TcCfg<NB>::THREADS, TcCfg<NB>::CTAS_PER_SM) tc
           for (int ks = 0; ks < KS; ++ks, ++it) {
             const uint32_t s = it % C::STAGES, ph = (it / C::STAGES) & 1;
             if (!mbar_wait(empty_bar(s), ph ^ 1)) { atomicOr(a.status, DS_WAIT_TIMEOUT | 0x10); dead = true; break; }
-            mbar_expect_tx(full_bar(s), C::STAGE_TX);
+            mbar_expect_tx(full_bar(s), uint32_t(a.stage_tx));
             const uint32_t sa = s_stage + s * C::STAGE_BYTES, sb = sa + C::A_BYTES;
             tma_load_2d(sa, &wmap0, full_bar(s), ks * 128, im.plane * a.plane_rows[0] + r0);
             tma_load_2d(sa + 8192, &wmap1, full_bar(s), ks * 128, im.plane * a.plane_rows[1] + r1);
@@ -227,7 +233,7 @@ __global__ void __launch_bounds__(TcCfg<NB>::THREADS, TcCfg<NB>::CTAS_PER_SM) tc
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
               tc_mma_mxf8f6f4(acc, smem_desc(sa + k * 32, 16, 1024, 2), smem_desc(sb + k * 32, 16, 1024, 2),
-                              idesc_mxf8f6f4(FMT_E2M1, FMT_E4M3, 128, C::N, k, k), tmem + C::SFA_COL,
+                              idesc_mxf8f6f4(uint32_t(a.a_fmt), FMT_E4M3, 128, C::N, k, k), tmem + C::SFA_COL,
                               tmem + C::SFB_COL, (ks | k) != 0);
             }
             tc_commit(empty_bar(s));
@@ -261,7 +267,7 @@ __global__ void __launch_bounds__(TcCfg<NB>::THREADS, TcCfg<NB>::CTAS_PER_SM) tc
         if (!walk.next(&im)) return false;
         have_item = true; t0 = 0; kg = 0;
         const int wrow = im.tile * a.tile_rows + a.roff[hh] + (gt & 63);
-        wsc = wrow < a.lim[hh] ? a.sw[hh] + (long long)im.plane * a.s_plane + (long long)wrow * srow : nullptr;
+        wsc = (a.sw[hh] && wrow < a.lim[hh]) ? a.sw[hh] + (long long)im.plane * a.s_plane + (long long)wrow * srow : nullptr;
       }
       const int tcol = t0 + (gt < NB ? gt : gt - NB);  // column gt of the MMA's N: hi terms, then lo terms
       const long long xrow = im.row0 + tcol;
@@ -380,6 +386,7 @@ __global__ void __launch_bounds__(TcCfg<NB>::THREADS, TcCfg<NB>::CTAS_PER_SM) tc
             float aux[16];
             uint32_t res2[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};  // residual, two bf16 per register
             const float bias = (EPI == TC_EPI_PLAIN && a.bias && rvalid) ? a.bias[row] : 0.f;
+            const float rscale = (EPI == TC_EPI_PLAIN && a.row_scale && rvalid) ? a.row_scale[row] : 1.f;
 #pragma unroll
             for (int jj = 0; jj < 16; ++jj) {
               const int t = t0 + c0 + jj;
@@ -394,6 +401,12 @@ __global__ void __launch_bounds__(TcCfg<NB>::THREADS, TcCfg<NB>::CTAS_PER_SM) tc
                   const uint32_t rb = *reinterpret_cast<const unsigned short*>(a.resid + dst * a.out_stride + row);
                   res2[jj >> 1] |= rb << (16 * (jj & 1));
                 }
+              } else if constexpr (EPI == TC_EPI_PLAIN) {
+                if (ok && a.row_div) aux[jj] = a.row_div[dst];
+                if (ok && a.resid2) {
+                  const uint32_t rb = *reinterpret_cast<const unsigned short*>(a.resid2 + dst * a.out_stride + row);
+                  res2[jj >> 1] |= rb << (16 * (jj & 1));
+                }
               }
             }
             float o[16];
@@ -406,7 +419,9 @@ __global__ void __launch_bounds__(TcCfg<NB>::THREADS, TcCfg<NB>::CTAS_PER_SM) tc
                 const float sig = 1.0f / (1.0f + expf(-aux[jj]));
                 v = ((jj & 1) ? bf16hi(res2[jj >> 1]) : bf16lo(res2[jj >> 1])) + v * sig;
               } else {
-                v += bias;
+                v = v * rscale + bias;
+                if (a.row_div) v = round_bf16(v) / aux[jj];
+                if (a.resid2) v = round_bf16(v) + ((jj & 1) ? bf16hi(res2[jj >> 1]) : bf16lo(res2[jj >> 1]));
               }
               o[jj] = v;
             }

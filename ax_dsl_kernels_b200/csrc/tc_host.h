@@ -34,6 +34,19 @@ int tc_quantize(const __nv_bfloat16* x, int x_stride, const int* src, int x_rows
 // active[0] = number of groups with rows, active[1 ..] = their indices; `active` holds groups + 1 ints
 int tc_build_active(const int* g_n, int groups, int* active, cudaStream_t stream);
 
+// out[t, n] = x[t, :] . dequant(w[n, :]) on the tensor cores, the epilogue of the `linear` role:
+// v = acc (* s[n] for FP8 per-row) + bias[n]; with row_div: v = bf16(v) / row_div[t]; with resid2: v = bf16(v) + resid2[t, n]
+struct TcLinear {
+  const void* w;      // [N, K/2] MXFP4 pairs (fmt 0) or [N, K] E4M3 (fmt 1, 2)
+  const void* s;      // E8M0 [N, K/32] (fmt 0, 1) or fp32 [N] (fmt 2)
+  int fmt;            // 0 MXFP4, 1 MXFP8, 2 FP8 with per-row scales
+  const float* bias; const float* row_div; const __nv_bfloat16* resid2;
+  float* f_out; __nv_bfloat16* b_out;   // one of the two
+};
+// K a multiple of 512; qws = tc_quant_bytes(T, K) bytes of scratch
+int tc_linear(const __nv_bfloat16* x, int64_t T, int64_t N, int64_t K, const TcLinear& p, uint8_t* qws,
+              cudaStream_t stream);
+
 template <int EPI>
 int tc_launch(const TcWeights& w, const TcQuant& q, TcArgs a, int nb, int tiles, int groups, cudaStream_t stream);
 

@@ -191,8 +191,23 @@ def test_linear_formats(q35, fmt, T, N, K):
         w, s = codecs.quant_fp8_rowwise(wf)
         dq = codecs.dequant_fp8_rowwise(w, s)
     ref = (x.float() @ dq.T)
-    out = q35.linear(x.cuda(), w.cuda(), s.cuda(), out_dtype=torch.float32)
+    out = q35.linear(x.cuda(), w.cuda(), s.cuda(), out_dtype=torch.float32)  # tensor-core path (K multiple of 512)
     assert rel_rms_err(out.cpu(), ref) <= 2e-3
+    # without scratch the role runs the CUDA-core weight-streaming kernel: same contract
+    out_cc = torch.full((T, N), float("nan"), device="cuda")
+    q35.run("linear", x=x.cuda(), w=w.cuda(), s=s.cuda() if s.dtype == torch.float32 else s.cuda().view(torch.uint8),
+            out=out_cc, workspace=torch.empty(0, dtype=torch.uint8, device="cuda"))
+    assert rel_rms_err(out_cc.cpu(), ref) <= 2e-3
+    # epilogue extras on both paths: bias, per-token divisor of the bf16-rounded product, residual
+    g2 = torch.Generator().manual_seed(T)
+    bias, rdiv = torch.randn(N, generator=g2), torch.rand(T, generator=g2) + 0.5
+    resid = torch.randn((T, N), generator=g2).to(torch.bfloat16)
+    exp = (((ref + bias).to(torch.bfloat16).float() / rdiv[:, None]).to(torch.bfloat16).float() + resid.float()).to(torch.bfloat16)
+    for extra in ({}, {"workspace": torch.empty(0, dtype=torch.uint8, device="cuda")}):
+        got = torch.empty((T, N), dtype=torch.bfloat16, device="cuda")
+        q35.run("linear", x=x.cuda(), w=w.cuda(), s=s.cuda() if s.dtype == torch.float32 else s.cuda().view(torch.uint8),
+                bias=bias.cuda(), row_div=rdiv.cuda(), residual=resid.cuda(), out=got, **extra)
+        assert rel_rms_err(got.cpu(), exp) <= TOL
     outb = q35.linear(x.cuda(), w.cuda(), s.cuda())
     assert rel_rms_err(outb.cpu(), ref.to(torch.bfloat16)) <= TOL
     if fmt == "fp8row":
