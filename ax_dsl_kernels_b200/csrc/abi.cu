@@ -168,7 +168,7 @@ static const RoleDef kRoles[] = {
      R"({"in":[["base","bf16","[T,H]"],["partial","f32","[T,H]"]],"out":[["out","bf16","[T,H]"]]})",
      run_moe_finish},
     {"moe.experts",
-     R"({"in":[["h2","bf16","[T,H]"],["base","bf16","[T,H]"],["ids","i32","[T,K]"],["rw","f32","[T,K]"],["e_gw","u8","[NE,2FE,H/2]"],["e_gs","u8","[NE,2FE,H/32]"],["e_dw","u8","[NE,H,FE/2]"],["e_ds","u8","[NE,H,FE/32]"],["expert_base","i32","[1] optional: ids are global and the planes start at this id"],["workspace","u8","[*]"]],"out":[["out","bf16","[T,H]"],["partial_out","f32","[T,H] instead of base/out: sums of the pairs with ids >= 0"]]})",
+     R"({"in":[["h2","bf16","[T,H]"],["base","bf16","[T,H]"],["ids","i32","[T,K]"],["rw","f32","[T,K]"],["e_gw","u8","[NE,2FE,H/2]"],["e_gs","u8","[NE,2FE,H/32]"],["e_dw","u8","[NE,H,FE/2]"],["e_ds","u8","[NE,H,FE/32]"],["expert_base","i32","[1] optional: ids are global and the planes start at this id"],["e_gs_tiled","u8","optional with e_ds_tiled: mx.tile_scales.paired / .plain of the scales; decode-sized batches then run as one persistent kernel"],["e_ds_tiled","u8","optional"],["workspace","u8","[*]"]],"out":[["out","bf16","[T,H]"],["partial_out","f32","[T,H] instead of base/out: sums of the pairs with ids >= 0"]]})",
      run_moe_experts},
     {"moe.permute",
      R"({"in":[["ids","i32","[T,K]"],["rw","f32","[T,K]"],["workspace","u8","[*]"]],"out":[["tok","i32","[S,1+G]"],["srw","f32","[S,G]"],["loc","i32","[K,T]"],["n_slots","i32","[1]"],["counts","i32","[NE]"]]})",

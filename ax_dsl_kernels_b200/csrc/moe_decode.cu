@@ -835,6 +835,215 @@ struct WsCut {
   }
 };
 
+// ---------------------------------------------------------------------------------------------------------------
+// Routed experts alone on given ids (role moe.experts with tiled scales bound): the expert-parallel form, where the
+// tokens of all ranks were gathered and every rank runs ITS experts.  Plan from the caller's ids (one CTA; ids
+// outside [base, base + NE) belong to other ranks and get loc = -1; an expert a token lists twice gets one row that
+// both listings point at, so its two weights are both applied), then the same quantise / GEMM launches as moe.block,
+// then the weighted sum of each token's rows: out = bf16(base + sum) or, without a base, the fp32 partial sum.
+__global__ void __launch_bounds__(1024) moe_plan_kernel(const int* __restrict__ ids, const int* __restrict__ base, int T,
+                                                        int K, int NE, int* g_plane, int* g_n, int* g_row0, int* active,
+                                                        int* ready, int* loc, int* status) {
+  pdl_wait();
+  pdl_launch();
+  __shared__ short s_raw[MD_MAX_PAIRS];
+  __shared__ uint32_t s_bits[MD_MAX_WORDS];
+  __shared__ int s_row0[1024];
+  __shared__ int s_warp[32];
+  const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+  const int P = T * K, W = (T + 31) / 32;
+  const int first = base ? base[0] : 0;
+  for (int p = tid; p < P; p += 1024) {
+    int id = ids[p] - first;
+    if (id >= NE) {
+      if (!base) atomicOr(status, DS_BAD_EXPERT);
+      id = -1;
+    }
+    s_raw[p] = short(id < 0 ? -1 : id);  // negative: not on this rank
+  }
+  for (int i = tid; i < NE * W; i += 1024) s_bits[i] = 0u;
+  __syncthreads();
+  for (int p = tid; p < P; p += 1024) {
+    const int t = p / K, id = s_raw[p];
+    if (id >= 0) atomicOr(&s_bits[id * W + (t >> 5)], 1u << (t & 31));
+  }
+  __syncthreads();
+  int cnt = 0;
+  if (tid < NE)
+    for (int w = 0; w < W; ++w) cnt += __popc(s_bits[tid * W + w]);
+  const int v = ((cnt + MD_NB - 1) / MD_NB) | (cnt > 0 ? 1 << 16 : 0);
+  int inc = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int n = __shfl_up_sync(0xffffffffu, inc, o);
+    if (lane >= o) inc += n;
+  }
+  if (lane == 31) s_warp[wid] = inc;
+  __syncthreads();
+  if (wid == 0) {
+    int w = s_warp[lane], winc = w;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int n = __shfl_up_sync(0xffffffffu, winc, o);
+      if (lane >= o) winc += n;
+    }
+    s_warp[lane] = winc - w;
+  }
+  __syncthreads();
+  const int exc = s_warp[wid] + inc - v;
+  if (tid < NE) {
+    s_row0[tid] = (exc & 0xffff) * MD_NB;
+    g_plane[tid] = tid; g_n[tid] = cnt; g_row0[tid] = (exc & 0xffff) * MD_NB;
+    ready[tid] = 0;
+    if (cnt > 0) active[1 + (exc >> 16)] = tid;
+  }
+  if (tid == 1023) active[0] = (exc + v) >> 16;
+  __syncthreads();
+  for (int p = tid; p < P; p += 1024) {
+    const int t = p / K, k = p % K, id = s_raw[p];
+    int row = -1;
+    if (id >= 0) {
+      int rank = __popc(s_bits[id * W + (t >> 5)] & ((1u << (t & 31)) - 1u));
+      for (int w = 0; w < (t >> 5); ++w) rank += __popc(s_bits[id * W + w]);
+      row = s_row0[id] + rank;
+    }
+    loc[size_t(k) * T + t] = row;
+  }
+}
+
+// out[t] = bf16(base[t] + sum_k rw[t, k] * row(loc[k, t])) in fp32, k ascending, product rounded before the add (the
+// golden's acc += rw * d, models/qwen35_2b/whole/src/q35_moe.py:235-238); without base / out: partial[t] = the sum
+__global__ void __launch_bounds__(256) moe_rows_combine_kernel(const __nv_bfloat16* __restrict__ base,
+                                                               const float* __restrict__ rw,
+                                                               const int* __restrict__ loc,
+                                                               const float* __restrict__ sout,
+                                                               __nv_bfloat16* __restrict__ out,
+                                                               float* __restrict__ partial, int T, int H, int K) {
+  const int t = blockIdx.x;
+  const int h = (blockIdx.y * blockDim.x + threadIdx.x) * 4;
+  const bool on = h < H;
+  int rix[8];
+  float wts[8];
+  const int kmax = K < 8 ? K : 8;
+  if (on) {  // the plan and the routing weights were complete before the kernel ahead of this one could start
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      rix[k] = k < kmax ? loc[size_t(k) * T + t] : -1;
+      wts[k] = k < kmax ? rw[size_t(t) * K + k] : 0.f;
+    }
+  }
+  pdl_wait();
+  pdl_launch();
+  if (!on) return;
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  if (base) {
+    const uint2 xb = *reinterpret_cast<const uint2*>(base + size_t(t) * H + h);
+    acc[0] = bf16lo(xb.x); acc[1] = bf16hi(xb.x); acc[2] = bf16lo(xb.y); acc[3] = bf16hi(xb.y);
+  }
+  float4 rows[8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    rows[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (rix[k] >= 0) rows[k] = *reinterpret_cast<const float4*>(sout + size_t(rix[k]) * H + h);
+    else wts[k] = 0.f;
+  }
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    acc[0] = __fadd_rn(acc[0], __fmul_rn(wts[k], rows[k].x)); acc[1] = __fadd_rn(acc[1], __fmul_rn(wts[k], rows[k].y));
+    acc[2] = __fadd_rn(acc[2], __fmul_rn(wts[k], rows[k].z)); acc[3] = __fadd_rn(acc[3], __fmul_rn(wts[k], rows[k].w));
+  }
+  for (int k = 8; k < K; ++k) {
+    const int r = loc[size_t(k) * T + t];
+    if (r < 0) continue;
+    const float4 d = *reinterpret_cast<const float4*>(sout + size_t(r) * H + h);
+    const float wk = rw[size_t(t) * K + k];
+    acc[0] = __fadd_rn(acc[0], __fmul_rn(wk, d.x)); acc[1] = __fadd_rn(acc[1], __fmul_rn(wk, d.y));
+    acc[2] = __fadd_rn(acc[2], __fmul_rn(wk, d.z)); acc[3] = __fadd_rn(acc[3], __fmul_rn(wk, d.w));
+  }
+  if (partial) {
+    *reinterpret_cast<float4*>(partial + size_t(t) * H + h) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+  } else {
+    uint2 o;
+    o.x = pack_bf16(acc[0], acc[1]);
+    o.y = pack_bf16(acc[2], acc[3]);
+    *reinterpret_cast<uint2*>(out + size_t(t) * H + h) = o;
+  }
+}
+
+bool moe_experts_tiled_ok(int64_t T, int64_t K, int64_t NE, int64_t H, int64_t FE) {
+  return T >= 1 && T * K <= MD_MAX_PAIRS && NE <= 1024 && NE * ((T + 31) / 32) <= MD_MAX_WORDS && H % 512 == 0 &&
+         FE % 512 == 0;
+}
+
+int moe_experts_tiled(Call& c, const Tensor& h2, const Tensor& base, const Tensor& ids, const Tensor& rw,
+                      const Tensor& egw, const Tensor& edw, const Tensor& egs, const Tensor& eds, const Tensor& ebase,
+                      const Tensor& out, const Tensor& partial) {
+  const int64_t NE = egw.s[0], FE = egw.s[1] / 2, H = egw.s[2] * 2, T = ids.s[0], K = ids.s[1], P = T * K;
+  Q35_REQUIRE(egs.numel() == NE * 2 * FE * (H / 32) && eds.numel() == NE * H * (FE / 32), Q35_ERR_SHAPE,
+              "moe.experts: tiled scale tensors must hold as many bytes as the scales they were made from");
+  const int64_t max_blocks = (NE < P ? NE : P) + P / MD_NB + 1, R = max_blocks * MD_NB;
+  auto carve = [&](WsCut& w, int*& g_plane, int*& g_n, int*& g_row0, int*& active, int*& ready, int*& loc,
+                   uint8_t*& q1h, uint8_t*& q1l, uint8_t*& sfb1, uint8_t*& q2h, uint8_t*& q2l, uint8_t*& sfb2, float*& sout) {
+    g_plane = w.take<int>(NE); g_n = w.take<int>(NE); g_row0 = w.take<int>(NE);
+    active = w.take<int>(NE + 1); ready = w.take<int>(NE); loc = w.take<int>(K * T);
+    q1h = w.take<uint8_t>(R * H); q1l = w.take<uint8_t>(R * H);
+    sfb1 = w.take<uint8_t>(max_blocks * (H / 128) * MD_SF_BYTES);
+    q2h = w.take<uint8_t>(R * FE); q2l = w.take<uint8_t>(R * FE);
+    sfb2 = w.take<uint8_t>(max_blocks * (FE / 128) * MD_SF_BYTES);
+    sout = w.take<float>(R * H);
+  };
+  int *g_plane, *g_n, *g_row0, *active, *ready, *loc;
+  uint8_t *q1h, *q1l, *sfb1, *q2h, *q2l, *sfb2;
+  float* sout;
+  WsCut cut{nullptr};
+  carve(cut, g_plane, g_n, g_row0, active, ready, loc, q1h, q1l, sfb1, q2h, q2l, sfb2, sout);
+  Tensor ws;
+  Q35_TRY(c.workspace(cut.off, &ws));
+  if (c.dry || T == 0) return 0;
+  Q35_REQUIRE(aligned16(h2.p) && (uintptr_t(egw.p) & 31) == 0 && (uintptr_t(edw.p) & 31) == 0 && aligned16(egs.p) &&
+                  aligned16(eds.p) && (partial.present ? aligned16(partial.p) : aligned16(base.p) && aligned16(out.p)),
+              Q35_ERR_ALIGN, "moe.experts: pointers must be 16-byte aligned (FP4 planes 32)");
+  WsCut wc{ws.as<uint8_t>()};
+  carve(wc, g_plane, g_n, g_row0, active, ready, loc, q1h, q1l, sfb1, q2h, q2l, sfb2, sout);
+  cudaStream_t st = c.stream;
+  launch_pdl(moe_plan_kernel, dim3(1), dim3(1024), 0, st, (const int*)ids.as<int>(),
+             (const int*)(ebase.present ? ebase.as<int>() : nullptr), int(T), int(K), int(NE), g_plane, g_n, g_row0, active,
+             ready, loc, device_status_ptr());
+  Q35_CUDA_LAUNCH_CHECK("moe.experts plan");
+  const long long pieces = (long long)P * (H / 8);
+  launch_pdl(moe_decode_quant_kernel, dim3(unsigned((pieces + 255) / 256)), dim3(256), 0, st,
+             (const __nv_bfloat16*)h2.as<__nv_bfloat16>(), (const int*)loc, int(P), int(T), int(H), q1h, q1l, sfb1);
+  Q35_CUDA_LAUNCH_CHECK("moe.experts quantise");
+  CUtensorMap m_wg, m_wd, m_x1h, m_x1l, m_x2h, m_x2l;
+  Q35_TRY(tc_make_map(&m_wg, true, egw.p, uint64_t(NE * 2 * FE), uint64_t(H), uint64_t(H / 2), 64, "e_gw"));
+  Q35_TRY(tc_make_map(&m_wd, true, edw.p, uint64_t(NE * H), uint64_t(FE), uint64_t(FE / 2), 64, "e_dw"));
+  Q35_TRY(tc_make_map(&m_x1h, false, q1h, uint64_t(R), uint64_t(H), uint64_t(H), MD_NB, "activations"));
+  Q35_TRY(tc_make_map(&m_x1l, false, q1l, uint64_t(R), uint64_t(H), uint64_t(H), MD_NB, "activations"));
+  Q35_TRY(tc_make_map(&m_x2h, false, q2h, uint64_t(R), uint64_t(FE), uint64_t(FE), MD_NB, "activations"));
+  Q35_TRY(tc_make_map(&m_x2l, false, q2l, uint64_t(R), uint64_t(FE), uint64_t(FE), MD_NB, "activations"));
+  MdArgs a{};
+  a.g_plane = g_plane; a.g_n = g_n; a.g_row0 = g_row0; a.active = active; a.ready = ready;
+  a.n_planes = int(NE); a.H = int(H); a.FE = int(FE);
+  a.ratio = int(H / FE) < 1 ? 1 : int(H / FE);
+  a.gs_t = egs.as<uint8_t>(); a.ds_t = eds.as<uint8_t>();
+  a.sfb1 = sfb1; a.q2h = q2h; a.q2l = q2l; a.sfb2 = sfb2; a.sout = sout; a.status = device_status_ptr();
+  int grid = 0;
+  Q35_TRY(md_grid(&grid));
+  // a group may hold more than one token tile here, but every CTA's item count is what matters for the table
+  const int64_t max_items = NE * (FE / 64 + H / 128);
+  Q35_REQUIRE((max_items + grid - 1) / grid + a.ratio + 2 <= MD_MAX_ITEMS, Q35_ERR_UNSUPPORTED,
+              "moe.experts: %lld work items over %d CTAs exceed the per-CTA item table", (long long)max_items, grid);
+  launch_pdl(moe_decode_kernel, dim3(unsigned(grid)), dim3(MD_THREADS), size_t(MD_SMEM), st, m_wg, m_wd, m_wg, m_wg, m_wd,
+             m_x1h, m_x1l, m_x2h, m_x2l, a);
+  Q35_CUDA_LAUNCH_CHECK("moe.experts gate-up + down");
+  launch_pdl(moe_rows_combine_kernel, dim3(unsigned(T), unsigned((H / 4 + 255) / 256)), dim3(256), 0, st,
+             (const __nv_bfloat16*)(partial.present ? nullptr : base.as<__nv_bfloat16>()), (const float*)rw.as<float>(),
+             (const int*)loc, (const float*)sout, partial.present ? nullptr : out.as<__nv_bfloat16>(),
+             partial.present ? partial.as<float>() : nullptr, int(T), int(H), int(K));
+  Q35_CUDA_LAUNCH_CHECK("moe.experts combine");
+  return 0;
+}
+
 // moe.block: the whole block on a decode-sized batch.  Needs the tiled scale tensors (mx.tile_scales.*) of the routed
 // and, when bound, the shared expert; MXFP4 everywhere; H and FE multiples of 512; shared intermediate size == FE.
 int run_moe_block(Call& c) {

@@ -236,13 +236,25 @@ int run_moe_experts(Call& c) {
   Q35_TRY(c.get("base", M(Q35_BF16), &base, !partial.present));
   Q35_TRY(c.get("ids", M(Q35_I32), &ids));
   Q35_TRY(c.get("rw", M(Q35_F32), &rw));
+  Tensor gs_t, ds_t;
+  Q35_TRY(c.get("e_gs_tiled", M(Q35_U8), &gs_t, false));  // mx.tile_scales.* of the scales: the one-kernel decode form
+  Q35_TRY(c.get("e_ds_tiled", M(Q35_U8), &ds_t, false));
+  const bool tiled = gs_t.present && ds_t.present;
   Q35_TRY(c.get("e_gw", M_BYTES, &gw));
-  Q35_TRY(c.get("e_gs", M(Q35_U8), &gs));
+  Q35_TRY(c.get("e_gs", M(Q35_U8), &gs, !tiled));
   Q35_TRY(c.get("e_dw", M_BYTES, &dw));
-  Q35_TRY(c.get("e_ds", M(Q35_U8), &ds));
+  Q35_TRY(c.get("e_ds", M(Q35_U8), &ds, !tiled));
   Q35_TRY(c.get("out", M(Q35_BF16), &out, !partial.present));
-  Q35_REQUIRE(gw.nd == 3 && gs.nd == 3 && dw.nd == 3 && ds.nd == 3 && ids.nd == 2, Q35_ERR_SHAPE,
-              "moe.experts: expert planes must be rank 3, ids rank 2");
+  Q35_REQUIRE(gw.nd == 3 && dw.nd == 3 && ids.nd == 2, Q35_ERR_SHAPE, "moe.experts: expert planes must be rank 3, ids rank 2");
+  if (tiled && moe_experts_tiled_ok(ids.s[0], ids.s[1], gw.s[0], gw.s[2] * 2, gw.s[1] / 2)) {
+    const int64_t NE_ = gw.s[0], FE_ = gw.s[1] / 2, H_ = gw.s[2] * 2, T_ = ids.s[0], K_ = ids.s[1];
+    Q35_REQUIRE(h2.numel() == T_ * H_ && rw.numel() == T_ * K_ && dw.s[0] == NE_ && dw.s[1] == H_ && dw.s[2] == FE_ / 2 &&
+                    (partial.present ? partial.numel() == T_ * H_ : base.numel() == T_ * H_ && out.numel() == T_ * H_),
+                Q35_ERR_SHAPE, "moe.experts: shapes");
+    return moe_experts_tiled(c, h2, base, ids, rw, gw, dw, gs_t, ds_t, ebase, out, partial);
+  }
+  Q35_REQUIRE(gs.present && ds.present, Q35_ERR_MISSING, "moe.experts: e_gs / e_ds are needed for this shape");
+  Q35_REQUIRE(gs.nd == 3 && ds.nd == 3, Q35_ERR_SHAPE, "moe.experts: scale planes must be rank 3");
   const int64_t NE = gw.s[0], FE2 = gw.s[1], H = gw.s[2] * 2, FE = FE2 / 2;
   const int64_t T = ids.s[0], K = ids.s[1];
   Q35_REQUIRE(h2.numel() == T * H, Q35_ERR_SHAPE, "moe.experts: h2 must be [T=%lld, H=%lld]", (long long)T, (long long)H);

@@ -35,12 +35,15 @@ def moe_pre(x1, ln2, w_gate, s_gate, w_up, s_up, w_down, s_down, w_router, w_shg
     return out, h2_out, logits_out
 
 
-def moe_experts(h2, base, ids, rw, e_gw, e_gs, e_dw, e_ds, out):
+def moe_experts(h2, base, ids, rw, e_gw, e_gs, e_dw, e_ds, out, e_gs_tiled=None, e_ds_tiled=None):
     """out[t] = base[t] + sum_i rw[t, i] * down_e(silu(gate_e h2[t]) * up_e h2[t]), e = ids[t, i].
     Planar MXFP4 expert tensors (gate rows then up rows in e_gw), picked on the device by id; at batch 1 this is the
-    reference's moe_experts_gu with the K experts bound by address."""
-    _lib.run("moe.experts", h2=h2, base=base, ids=ids, rw=rw, e_gw=_u8(e_gw), e_gs=_u8(e_gs), e_dw=_u8(e_dw),
-             e_ds=_u8(e_ds), out=out)
+    reference's moe_experts_gu with the K experts bound by address.  With the tiled scale tensors of
+    prepare_moe_weights() a decode-sized batch runs as one persistent gate-up + down kernel."""
+    kw = dict(h2=h2, base=base, ids=ids, rw=rw, e_gw=_u8(e_gw), e_gs=_u8(e_gs), e_dw=_u8(e_dw), e_ds=_u8(e_ds), out=out)
+    if e_gs_tiled is not None:
+        kw.update(e_gs_tiled=e_gs_tiled, e_ds_tiled=e_ds_tiled)
+    _lib.run("moe.experts", **kw)
     return out
 
 

@@ -78,9 +78,12 @@ class ExpertParallelMoE:
         partial = self._get("partial", h2_all.shape, torch.float32, h2_all.device)
         if "expert_base" not in self._buf:
             self._buf["expert_base"] = torch.tensor([self.lo], dtype=torch.int32, device=h2_all.device)
+        if "e_gs_tiled" not in w and w["e_gs"].is_cuda:  # load-time re-layout of this rank's scales, once
+            w["e_gs_tiled"], w["e_ds_tiled"] = moe.tile_scales(w["e_gs"], True), moe.tile_scales(w["e_ds"], False)
+        kw = dict(e_gs_tiled=w["e_gs_tiled"], e_ds_tiled=w["e_ds_tiled"]) if "e_gs_tiled" in w else {}
         _lib.run("moe.experts", h2=h2_all, ids=ids_all, rw=rw_all, e_gw=moe._u8(w["e_gw"]), e_gs=moe._u8(w["e_gs"]),
                  e_dw=moe._u8(w["e_dw"]), e_ds=moe._u8(w["e_ds"]), expert_base=self._buf["expert_base"],
-                 partial_out=partial)
+                 partial_out=partial, **kw)
         return partial
 
     def _finish(self, base, mine, out, ready):

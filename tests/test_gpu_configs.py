@@ -206,6 +206,51 @@ def test_moe_block_one_call_decode_form(q35, T, NE):
     assert torch.equal(out.view(torch.int16), out2.view(torch.int16))  # run-to-run bitwise determinism
 
 
+@pytest.mark.parametrize("T,NE,lo,hi", [(7, 16, 0, 16), (64, 32, 8, 24), (512, 256, 96, 128)])
+def test_moe_experts_tiled_scales_decode_form(q35, T, NE, lo, hi):
+    """moe.experts with tiled scales (the per-rank step of expert parallelism: gathered tokens, global ids, this rank's
+    planes): the one-kernel form must agree with the role's general form on base / out and on partial sums, and a
+    sample of tokens with the golden"""
+    g = torch.Generator().manual_seed(T + NE)
+    h2 = torch.randn((T, 2048), generator=g).to(torch.bfloat16)
+    base = (torch.randn((T, 2048), generator=g) * 0.5).to(torch.bfloat16)
+    ids, rw = omoe.route(torch.randn((T, NE), generator=g), 8)
+    if T == 7:
+        ids[3, 5] = ids[3, 1]  # an expert listed twice
+    from oracle import codecs
+    e_gw, e_gs = codecs.random_mxfp4((hi - lo, 1024, 2048), g, -8, 0)
+    e_dw, e_ds = codecs.random_mxfp4((hi - lo, 2048, 512), g, -8, 0)
+    dev = [t.cuda() for t in (h2, base, ids, rw, e_gw, e_gs, e_dw, e_ds)]
+    gs_t, ds_t = q35.tile_scales(dev[5], True), q35.tile_scales(dev[7], False)
+    eb = torch.tensor([lo], dtype=torch.int32).cuda()
+    p_old = torch.full((T, 2048), float("nan")).cuda()
+    p_new = torch.full((T, 2048), float("nan")).cuda()
+    common = dict(h2=dev[0], ids=dev[2], rw=dev[3], e_gw=dev[4], e_gs=dev[5], e_dw=dev[6], e_ds=dev[7], expert_base=eb)
+    q35.run("moe.experts", partial_out=p_old, **common)
+    q35.run("moe.experts", partial_out=p_new, e_gs_tiled=gs_t, e_ds_tiled=ds_t, **common)
+    assert q35.device_status() == 0
+    assert torch.isfinite(p_new).all()
+    assert_parity(p_new.cpu(), p_old.cpu(), bf16_step=True, name=f"moe.experts tiled vs general, partial sums, T={T}")
+    if lo == 0 and hi == NE:
+        ref = omoe.experts_decode(h2, base, ids, rw, e_gw, e_gs, e_dw, e_ds)
+        out = torch.full_like(h2, float("nan")).cuda()
+        q35.moe_experts(*dev, out, e_gs_tiled=gs_t, e_ds_tiled=ds_t)
+        assert_parity(out.cpu(), ref, bf16_step=True)
+    else:
+        zero = torch.zeros((1, 2048), dtype=torch.bfloat16)
+        for t in range(0, T, max(1, T // 6)):
+            ref = torch.zeros(2048)
+            for i in range(8):
+                e = int(ids[t, i]) - lo
+                if 0 <= e < hi - lo:
+                    ref += rw[t, i] * omoe.experts_decode(h2[t:t + 1], zero, torch.tensor([[e]], dtype=torch.int32),
+                                                          torch.ones((1, 1)), e_gw, e_gs, e_dw, e_ds).float()[0]
+            if ref.abs().max() > 0:
+                assert_parity(p_new[t].cpu(), ref, bf16_step=True)
+            else:
+                assert (p_new[t] == 0).all()
+
+
 # ------------------------------------------------------------------------------------------------ router near-ties
 def test_route_logits_one_and_two_ulps_apart_around_kth_place(q35):
     """The kernel orders experts by their LOGITS (descending, exact ties to the lower id); the reference's host router
