@@ -231,6 +231,8 @@ static const RoleDef kRoles[] = {
     {"mx.tile_scales.plain",
      R"({"in":[["s","u8","[planes,rows,K/32] E8M0"]],"out":[["out","u8","[planes,rows/128,K/128,512]"]]})",
      run_tile_scales_plain},
+    {"debug.tc_peak",
+     R"({"in":[["iters","i32","[1] MMA groups of K = 128 per CTA"]],"out":[["done","i32","[1]"]]})", run_debug_tc_peak},
     {"debug.wait_probe",
      R"({"in":[["polls","i32","[1] poll limit of the wait, clamped to 1 .. 2^20"]],"out":[["result","i32","[1] 1 = the wait gave up and the status word got its bit"]]})",
      run_debug_wait_probe},

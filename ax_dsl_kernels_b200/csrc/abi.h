@@ -131,6 +131,7 @@ int run_act_sigmoid_gate(Call&);
 int run_linear_tc(Call&);
 int run_lm_head(Call&);
 int run_debug_wait_probe(Call&);
+int run_debug_tc_peak(Call&);
 int run_moe_block(Call&);
 bool moe_experts_tiled_ok(int64_t T, int64_t K, int64_t NE, int64_t H, int64_t FE);
 int moe_experts_tiled(Call& c, const Tensor& h2, const Tensor& base, const Tensor& ids, const Tensor& rw, const Tensor& egw,

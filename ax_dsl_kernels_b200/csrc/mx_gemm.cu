@@ -780,10 +780,10 @@ int run_linear(Call& c) {
   Q35_REQUIRE((!rdiv.present || rdiv.numel() == T) && (!resid.present || resid.numel() == T * N), Q35_ERR_SHAPE,
               "linear: row_div [T], residual [T, N]");
   Q35_REQUIRE(K % 256 == 0, Q35_ERR_UNSUPPORTED, "linear: K must be a multiple of 256");
-  // With K a multiple of 512 and a workspace bound, the projection runs on the tensor cores (tcgen05 block-scaled MMA:
+  // With a workspace bound, the projection runs on the tensor cores (tcgen05 block-scaled MMA:
   // E2M1 or E4M3 weights straight from TMA, activations as two E4M3 terms); without a workspace, or for other K, on the
   // CUDA-core weight-streaming kernel.  Same results within the tolerance of the role.
-  const bool tc_shape = K % 512 == 0;
+  const bool tc_shape = K % 256 == 0;
   const int64_t need = tc_shape ? tc_quant_bytes(T, K) : 0;
   Tensor ws;
   c.ws_need = need;

@@ -231,9 +231,10 @@ static int launch_nb(const CUtensorMap& w0, const CUtensorMap& w1, const CUtenso
 
 template <int EPI>
 int tc_launch(const TcWeights& w, const TcQuant& q, TcArgs a, int nb, int tiles, int groups, cudaStream_t stream) {
-  Q35_REQUIRE(a.K % 512 == 0 && a.K == q.K, Q35_ERR_UNSUPPORTED, "tc gemm: K must be a multiple of 512");
-  Q35_REQUIRE((uintptr_t(a.sw[0]) & 15) == 0 && (uintptr_t(a.sw[1]) & 15) == 0 && (a.s_plane & 15) == 0, Q35_ERR_ALIGN,
-              "tc gemm: scale tensors must be 16-byte aligned");
+  Q35_REQUIRE(a.K % 128 == 0 && a.K == q.K, Q35_ERR_UNSUPPORTED, "tc gemm: K must be a multiple of 128");
+  Q35_REQUIRE((uintptr_t(a.sw[0]) & 15) == 0 && (uintptr_t(a.sw[1]) & 15) == 0 &&
+                  (a.s_plane & (a.K % 512 == 0 ? 15 : 3)) == 0,
+              Q35_ERR_ALIGN, "tc gemm: scale tensors must be 16-byte aligned");
   Q35_REQUIRE((a.sw[0] == nullptr) == (a.sw[1] == nullptr), Q35_ERR_MISSING, "tc gemm: scales of one half only");
   CUtensorMap w0, w1, xh, xl;
   const bool fp4 = a.w_fp8 == 0;
@@ -311,7 +312,7 @@ int run_linear_tc(Call& c) {
   Q35_REQUIRE(x.nd >= 2 && w.nd == 2, Q35_ERR_SHAPE, "linear.tc: x [T, K], w [N, K/2]");
   const int64_t K = x.s[x.nd - 1], T = x.numel() / K, N = w.s[0];
   Q35_REQUIRE(w.s[1] == K / 2 && s.numel() == N * (K / 32) && out.numel() == T * N, Q35_ERR_SHAPE, "linear.tc: shapes");
-  Q35_REQUIRE(K % 512 == 0, Q35_ERR_UNSUPPORTED, "linear.tc: K must be a multiple of 512");
+  Q35_REQUIRE(K % 128 == 0, Q35_ERR_UNSUPPORTED, "linear.tc: K must be a multiple of 128");
   Q35_TRY(c.workspace(tc_quant_bytes(T, K), &ws));
   if (c.dry || T == 0 || N == 0) return 0;
   Q35_REQUIRE((uintptr_t(w.p) & 31) == 0 && aligned16(x.p) && aligned16(s.p), Q35_ERR_ALIGN, "linear.tc: alignment");
@@ -399,6 +400,62 @@ __global__ void wait_probe_kernel(const int* __restrict__ polls, int* __restrict
     if (!ok) atomicOr(status, DS_WAIT_TIMEOUT);
     result[0] = ok ? 0 : 1;
   }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// debug.tc_peak: what the block-scaled tensor-core path can do with operands that are already in shared memory: every
+// CTA (one per SM) issues `iters` x 4 tcgen05.mma kind::mxf8f6f4.block_scale of 128 x 256 x 32 (E2M1 x E4M3, the
+// formats of the MoE GEMMs) on a fixed pseudo-random tile, nothing is loaded or stored.  The host times the launch:
+// FLOP = CTAs x iters x 4 x 2 x 128 x 256 x 32.  This is the denominator "FP4 / FP8 tensor peak" of the prefill numbers.
+__global__ void __launch_bounds__(128, 1) tc_peak_kernel(const int* __restrict__ iters_p, int* __restrict__ done,
+                                                         int* status) {
+  using namespace tc;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bar;
+  __shared__ uint32_t slot;
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* sgen = smem_raw + (sbase - smem_u32(smem_raw));
+  for (int i = tid; i < (16384 + 32768) / 4; i += 128)  // operand tiles: A 128 x 128 bytes, B 256 x 128 bytes
+    reinterpret_cast<uint32_t*>(sgen)[i] = (uint32_t(i) * 2654435761u) & 0x37373737u;  // small finite E4M3 / E2M1 codes
+  if (tid == 0) { mbar_init(smem_u32(&bar), 1); fence_barrier_init(); }
+  if (warp == 0) { tmem_alloc(smem_u32(&slot), 512); tmem_relinquish(); }
+  fence_proxy_async();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(&slot);
+  const int iters = iters_p[0];
+  if (tid == 0) {
+    const uint32_t sa = sbase, sb = sbase + 16384;
+    for (int i = 0; i < iters; ++i) {
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        tc_mma_mxf8f6f4(tmem, smem_desc(sa + k * 32, 16, 1024, 2), smem_desc(sb + k * 32, 16, 1024, 2),
+                        idesc_mxf8f6f4(FMT_E2M1, FMT_E4M3, 128, 256, k, k), tmem + 256, tmem + 264, (i | k) != 0);
+    }
+    tc_commit(smem_u32(&bar));
+    if (!mbar_wait(smem_u32(&bar), 0, 1u << 28)) atomicOr(status, DS_WAIT_TIMEOUT);
+    if (blockIdx.x == 0) done[0] = iters;
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (warp == 0) tmem_dealloc(tmem, 512);
+}
+
+int run_debug_tc_peak(Call& c) {
+  Tensor iters, done;
+  Q35_TRY(c.get("iters", M(Q35_I32), &iters));
+  Q35_TRY(c.get("done", M(Q35_I32), &done));
+  Q35_REQUIRE(iters.numel() == 1 && done.numel() == 1, Q35_ERR_SHAPE, "debug.tc_peak: iters [1], done [1]");
+  c.ws_need = 0;
+  if (c.dry) return 0;
+  const int smem = 1024 + 16384 + 32768;
+  Q35_TRY(ensure_dynamic_smem(reinterpret_cast<const void*>(tc_peak_kernel), smem));
+  tc_peak_kernel<<<unsigned(sm_count()), 128, smem, c.stream>>>(iters.as<int>(), done.as<int>(), device_status_ptr());
+  Q35_CUDA_LAUNCH_CHECK("debug.tc_peak");
+  return 0;
 }
 
 int run_debug_wait_probe(Call& c) {

@@ -142,7 +142,9 @@ __global__ void __launch_bounds__(TcCfg<NB>::THREADS, TcCfg<NB>::CTAS_PER_SM) tc
   using namespace tc;
   extern __shared__ uint8_t smem_raw[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int KS = a.K / 128;
+  // stages of K = 128, rounded up to whole scale granules of four: the stages past the real K load out-of-range boxes,
+  // which the TMA unit fills with zeros (weights and activations), so they add nothing
+  const int KS = (a.K / 128 + C::SF_GRAN - 1) / C::SF_GRAN * C::SF_GRAN;
   const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* sgen = smem_raw + (sbase - smem_u32(smem_raw));
   const uint32_t s_stage = sbase;
@@ -275,9 +277,21 @@ __global__ void __launch_bounds__(TcCfg<NB>::THREADS, TcCfg<NB>::CTAS_PER_SM) tc
       return true;
     };
     const uint4 ones = make_uint4(0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu);
+    // 16 scale bytes of a row = one granule; the last granule of a K that is not a multiple of 512 holds fewer
+    // (4 per real stage): the rest reads as scale 1 (it multiplies zeros)
+    auto load_g = [&](const uint8_t* p) -> uint4 {
+      if ((srow & 15) == 0) return ldg_nc_16(p + kg * 16);  // K a multiple of 512: whole, aligned granules
+      const int rem = srow - kg * 16;                       // rows are only 4-byte aligned: word loads
+      uint4 v = ones;
+      if (rem > 0) v.x = ldg_nc_4(p + kg * 16);
+      if (rem > 4) v.y = ldg_nc_4(p + kg * 16 + 4);
+      if (rem > 8) v.z = ldg_nc_4(p + kg * 16 + 8);
+      if (rem > 12) v.w = ldg_nc_4(p + kg * 16 + 12);
+      return v;
+    };
     auto load1 = [&](uint4& va, uint4& vb) {
-      va = wsc ? ldg_nc_16(wsc + kg * 16) : ones;
-      vb = xsc ? ldg_nc_16(xsc + kg * 16) : ones;
+      va = wsc ? load_g(wsc) : ones;
+      vb = xsc ? load_g(xsc) : ones;
     };
     uint32_t gi = 0;
     bool dead = false;

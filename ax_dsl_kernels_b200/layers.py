@@ -65,13 +65,15 @@ def finish_residual(base, partial, out=None):
 
 
 def gdn(hidden_states, residual, weights, temporal_state, conv_state, *, input_norm_eps=1e-6, o_norm_eps=1e-6,
-        reduce=None):
+        reduce=None, in_place=False):
     """GDN sublayer on [B, T, H] (T = 1: recurrent step, T > 1: chunked prefill).  weights: input_norm_w, (w_x, s_x) for
     x in q k v z a b o, w_q_conv / w_k_conv / w_v_conv [C, 4], a_log, dt_bias, o_norm_w.  conv_state: tuple (q, k, v) of
     [B, 3, C] bf16.  Returns (fused [B, T, H], temporal_state_out, conv_state_out) -- the reference returns
     (zeros, residual_out, state_out, conv_out); fused is its residual_out.
     reduce (tensor parallel, weights = this rank's heads): called with the fp32 partial of the output projection
-    [B * T, H], returns the sum over ranks; the residual is added after it."""
+    [B * T, H], returns the sum over ranks; the residual is added after it.
+    in_place: the new temporal and conv states overwrite the given tensors (state_out == state_in, as the reference's
+    resident state buffers) instead of being returned in fresh ones."""
     w = weights
     B, T, H = hidden_states.shape
     R = B * T
@@ -85,7 +87,7 @@ def gdn(hidden_states, residual, weights, temporal_state, conv_state, *, input_n
     conv_out = []
     mixed = {}
     for n, st in zip(("q", "k", "v"), conv_state):
-        y, so = gdn_conv1d_silu(proj[n].reshape(B, T, -1), w[f"w_{n}_conv"], st)
+        y, so = gdn_conv1d_silu(proj[n].reshape(B, T, -1), w[f"w_{n}_conv"], st, conv_out=st if in_place else None)
         mixed[n] = y
         conv_out.append(so)
     qn = torch.empty_like(mixed["q"]).reshape(R, NK, DV)
@@ -95,7 +97,7 @@ def gdn(hidden_states, residual, weights, temporal_state, conv_state, *, input_n
     _lib.run("gdn.prep", q=mixed["q"].reshape(R, NK, DV), k=mixed["k"].reshape(R, NK, DV), a=proj["a"], b=proj["b"],
              a_log=w["a_log"], dt_bias=w["dt_bias"], q_out=qn, k_out=kn, g=g, beta=beta)
     v = mixed["v"].reshape(B, T, NV, DV)
-    state_out = torch.empty_like(temporal_state)
+    state_out = temporal_state if in_place else torch.empty_like(temporal_state)
     if T == 1:
         core, state_out = gdn_recurrent_step(qn.reshape(B, NK, DV), kn.reshape(B, NK, DV), v.reshape(B, NV, DV),
                                              g.reshape(B, NV), beta.reshape(B, NV), temporal_state,
@@ -223,4 +225,76 @@ class HybridStack:
                                qo_indptr=i32([0, T]), gated=self.gated, reduce=self.reduce, **self.cfg)
             x = mlp_residual(x1, w, reduce=self.reduce)
         self.pos += T
+        return x
+
+
+class DecodeGroup:
+    """One decode step of a stack of layers for B sequences at once: the batched form of the reference's decode group
+    (group_body, models/qwen38_27b/decode/q35_group.py:413-437; decode_qwen35_blocks, models/qwen35_35b_a3b/sgl/python/
+    sgl_kernel_axera/models/qwen36_35b_a3b/decode.py:23-110).  Every attention layer owns a paged KV cache
+    [B * pages_per_seq, 2, P, HKV, D] over ONE page table shared by the layers (sequence b owns pages
+    b * pages_per_seq ...); GDN layers own temporal states [B, NV, DV, DV] and conv states, updated in place.
+    The page table, write locations and RoPE rows live on the device and change only in advance(), so step() issues no
+    host-to-device copy and can be captured into a CUDA graph.
+    reduce: tensor parallel (layers = this rank's shards, heads / kv_heads its counts), as in gdn()."""
+
+    def __init__(self, layers, kinds, *, batch, heads, kv_heads, head_dim, rot, theta, max_tokens, page_size=64,
+                 gated=True, reduce=None, kv_dtype=torch.bfloat16):
+        self.layers, self.kinds, self.B = layers, kinds, batch
+        self.reduce, self.gated = reduce, gated
+        self.cfg = dict(heads=heads, kv_heads=kv_heads, head_dim=head_dim)
+        self.rot, self.theta, self.P = rot, theta, page_size
+        self.npp = (max_tokens + page_size - 1) // page_size
+        dev = layers[0]["ln2"].device
+        self.dev = dev
+        self.state, self.conv, self.cache = {}, {}, {}
+        for i, (w, kind) in enumerate(zip(layers, kinds)):
+            if kind == "g":
+                NV, DV = w["a_log"].numel(), w["o_norm_w"].numel()
+                self.state[i] = torch.zeros((batch, NV, DV, DV), dtype=torch.float32, device=dev)
+                self.conv[i] = tuple(torch.zeros((batch, 3, w[f"w_{n}_conv"].shape[0]), dtype=torch.bfloat16, device=dev)
+                                     for n in ("q", "k", "v"))
+            else:
+                self.cache[i] = torch.zeros((batch * self.npp, 2, page_size, kv_heads, head_dim), dtype=kv_dtype,
+                                            device=dev)
+        self.sm_scale = _scalar(head_dim ** -0.5, dev)
+        self.set_context([0] * batch)
+
+    def set_context(self, ctx):
+        """history length of every sequence (tokens already in the caches and states)"""
+        ctx = [int(c) for c in ctx]
+        if len(ctx) != self.B or max(ctx) >= self.npp * self.P:
+            raise ValueError("DecodeGroup.set_context: one length per sequence, below the cache size")
+        self.ctx = ctx
+        P, npp = self.P, self.npp
+        n_hist = [(c + P - 1) // P for c in ctx]
+        i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=self.dev)  # noqa: E731
+        self.indptr = i32([0, *torch.tensor(n_hist).cumsum(0).tolist()])
+        self.indices = i32([b * npp + i for b, n in enumerate(n_hist) for i in range(n)] or [0])
+        self.last_page_len = i32([c - (n - 1) * P if n else 0 for c, n in zip(ctx, n_hist)])
+        self.cache_location = i32([[b * npp + c // P, c % P] for b, c in enumerate(ctx)])
+        inv = 1.0 / (self.theta ** (torch.arange(0, self.rot, 2, dtype=torch.int64).float() / self.rot))
+        f = torch.tensor(ctx, dtype=torch.float32).reshape(-1, 1) * inv.reshape(1, -1)
+        self.cos, self.sin = f.cos().to(self.dev).contiguous(), f.sin().to(self.dev).contiguous()
+
+    def advance(self):
+        """every sequence has taken one more token"""
+        self.set_context([c + 1 for c in self.ctx])
+
+    def step(self, x, advance=True):
+        """x [B, H] bf16, one token per sequence -> [B, H]"""
+        B = self.B
+        zero = torch.zeros_like(x)
+        for i, (w, kind) in enumerate(zip(self.layers, self.kinds)):
+            if kind == "g":
+                fused, _, _ = gdn(x.reshape(B, 1, -1), zero.reshape(B, 1, -1), w, self.state[i], self.conv[i],
+                                  reduce=self.reduce, in_place=True)
+                x1 = fused.reshape(B, -1)
+            else:
+                x1 = attention(x, w, self.cos, self.sin, self.cache[i], self.indptr, self.indices, self.last_page_len,
+                               cache_location=self.cache_location, gated=self.gated, sm_scale=self.sm_scale,
+                               reduce=self.reduce, **self.cfg)
+            x = mlp_residual(x1, w, reduce=self.reduce)
+        if advance:
+            self.advance()
         return x

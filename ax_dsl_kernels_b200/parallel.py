@@ -241,3 +241,16 @@ def tensor_parallel_stack(layers, kinds, *, heads, kv_heads, head_dim, group=Non
                                          gated=gated)
     return HybridStack(shards, kinds, heads=hl, kv_heads=kl, head_dim=head_dim, gated=gated, reduce=all_reduce_sum(g),
                        **stack_kw)
+
+
+def tensor_parallel_decode_group(layers, kinds, *, batch, heads, kv_heads, head_dim, group=None, gated=True, **group_kw):
+    """layers.DecodeGroup (B sequences, one token each per step) over this rank's shards: heads, GDN value heads and FFN
+    columns split over the group, one all-reduce of the fp32 partial [B, H] after each sublayer's output projection --
+    the split of the 27B-class decode group over 2 / 4 / 8 devices (models/qwen38_27b/decode/q35_group.py:128-137)."""
+    from .layers import DecodeGroup
+    g = group if group is not None else dist.group.WORLD
+    rank, world = dist.get_rank(g), dist.get_world_size(g)
+    shards, hl, kl = shard_stack_weights(layers, kinds, rank, world, heads=heads, kv_heads=kv_heads, head_dim=head_dim,
+                                         gated=gated)
+    return DecodeGroup(shards, kinds, batch=batch, heads=hl, kv_heads=kl, head_dim=head_dim, gated=gated,
+                       reduce=all_reduce_sum(g), **group_kw)

@@ -194,11 +194,13 @@ class FullLayer:
 
 
 # ----------------------------------------------------------------------------------------------------------------
-def timed_rounds(run_step, steps, barrier, min_seconds=0.5, max_rounds=200):
-    """rounds of exactly `steps` steps, each bracketed by CUDA events on the launching stream; rounds repeat until
-    min_seconds of device time have been measured (at least 3 rounds).  Returns the per-round milliseconds."""
-    rounds, total = [], 0.0
-    while len(rounds) < 3 or (total < min_seconds * 1e3 and len(rounds) < max_rounds):
+def timed_rounds(run_step, steps, barrier, min_seconds=0.5, max_rounds=200, agree=None):
+    """rounds of exactly `steps` steps, each bracketed by CUDA events on the launching stream.  The number of rounds is
+    fixed after the first one so that about min_seconds of device time are measured (at least 3 rounds); with several
+    ranks `agree` (a max-reduction over the ranks) makes every rank run the same number of rounds -- the rounds hold
+    collectives.  Returns the per-round milliseconds."""
+    rounds, n_rounds = [], 3
+    while len(rounds) < n_rounds:
         t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         barrier()
         t0.record()
@@ -206,9 +208,10 @@ def timed_rounds(run_step, steps, barrier, min_seconds=0.5, max_rounds=200):
             run_step()
         t1.record()
         barrier()
-        ms = t0.elapsed_time(t1)
-        rounds.append(ms)
-        total += ms
+        rounds.append(t0.elapsed_time(t1))
+        if len(rounds) == 1:
+            first = agree(rounds[0]) if agree else rounds[0]
+            n_rounds = max(3, min(max_rounds, int(math.ceil(min_seconds * 1e3 / max(first, 1e-3)))))
     return rounds
 
 
@@ -249,7 +252,8 @@ def run_ours(args):
     dist = None
     if world > 1:
         import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=dev)
+        import datetime
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=120))
     wl = Workload(dev, seed=1000 + rank)
     L = q35._lib.lib()
     if world > 1:
@@ -276,6 +280,13 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    def agree(ms):  # the slowest rank's figure, the same on every rank
+        if dist is None:
+            return ms
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
     clocks = ClockSampler(local) if rank == 0 else None
     if clocks:
         clocks.start()  # sampled from the warm-up to the end of the end-to-end loop (nvidia-smi, every 100 ms)
@@ -293,7 +304,7 @@ def run_ours(args):
         graph = capture(step)
     run_step = graph.replay if graph is not None else step
     barrier()
-    rounds = timed_rounds(run_step, args.steps, barrier)
+    rounds = timed_rounds(run_step, args.steps, barrier, agree=agree)
     ms = median(rounds)
 
     # every part on its own, same process, right after the timed region (events cannot be placed inside a replayed
@@ -307,7 +318,7 @@ def run_ours(args):
     else:
         gph = capture(attn_only) if not args.no_graph else None
         parts["attn.paged_decode (plan + decode + merge)"] = median(
-            timed_rounds(gph.replay if gph else attn_only, args.steps, barrier, min_seconds=0.2)) / args.steps
+            timed_rounds(gph.replay if gph else attn_only, args.steps, barrier, min_seconds=0.2, agree=agree)) / args.steps
     attn_ms = parts["attn.paged_decode (plan + decode + merge)"]
 
     # end to end: the per-step activations start in ONE pinned host block and the results come back into one
@@ -323,7 +334,7 @@ def run_ours(args):
 
     for _ in range(3):
         step_e2e()
-    e2e_ms = median(timed_rounds(step_e2e, args.steps, barrier))
+    e2e_ms = median(timed_rounds(step_e2e, args.steps, barrier, agree=agree))
 
     # the same step with the sublayer glue (projections, conv, norms, RoPE, KV write, o-proj), one GPU only
     full = None
@@ -618,6 +629,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="headline")
+    ap.add_argument("--layers", type=int, default=16, help="layers of the --config c5 decode group")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
     ap.add_argument("--no-full-layer", action="store_true", help="skip the full-layer variant of the step")
     ap.add_argument("--no-graph", action="store_true", help="launch the timed steps eagerly instead of replaying a CUDA graph")

@@ -205,3 +205,46 @@ def test_tensor_parallel_sublayers_two_ranks_emulated_on_one_gpu(q35):
     out = both(lambda rank, reduce: q35.layers.mlp_residual(x2.cuda(), parallel.shard_mlp_weights(dkw[0], rank, 2),
                                                             reduce=reduce))
     assert_parity(out.cpu(), ref)
+
+
+def test_decode_group_batched_sequences_match_per_sequence_oracle(q35):
+    """DecodeGroup: B sequences with different histories through a g g a stack in one batched step per token.  Every
+    sequence's history is built on the CPU by the oracle stack (prefill), its caches and states are copied into the
+    group's batched buffers, and two batched decode steps are compared with each oracle's own decode steps."""
+    kinds = "gga"
+    kw, ow = stack_case(kinds, seed=21)
+    cfg = dict(heads=4, kv_heads=1, head_dim=128, rot=64, theta=1e7)
+    hist = [0, 5, 70]
+    B, H, P, max_tokens = len(hist), 512, 64, 192
+    g = torch.Generator().manual_seed(4)
+    oracles = []
+    for h in hist:
+        o = ostack.HybridStack(ow, kinds, page_size=P, max_tokens=max_tokens, **cfg)
+        if h:
+            o.forward((torch.randn((h, H), generator=g) * 0.5).to(torch.bfloat16))
+        oracles.append(o)
+    grp = q35.layers.DecodeGroup(to_dev(kw), kinds, batch=B, max_tokens=max_tokens, page_size=P, **cfg)
+    npp = grp.npp
+    for b, o in enumerate(oracles):
+        for i, kind in enumerate(kinds):
+            if kind == "g":
+                grp.state[i][b].copy_(o.state[i][0])
+                widths = [c.shape[-1] for c in grp.conv[i]]
+                for c, part in zip(grp.conv[i], torch.split(o.conv[i][0], widths, dim=-1)):
+                    c[b].copy_(part)
+            else:
+                grp.cache[i][b * npp:(b + 1) * npp].copy_(o.cache[i])
+    grp.set_context(hist)
+    for step in range(2):
+        x = (torch.randn((B, H), generator=g) * 0.5).to(torch.bfloat16)
+        got = grp.step(x.cuda()).cpu()
+        ref = torch.cat([o.forward(x[b:b + 1]) for b, o in enumerate(oracles)], 0)
+        for b in range(B):
+            assert cosine(got[b], ref[b]) >= 0.999, (step, b)
+        assert rel_rms_err(got, ref) <= 5e-2
+    assert grp.ctx == [h + 2 for h in hist]
+    # the written KV rows are where the oracle wrote them
+    a = kinds.index("a")
+    for b, o in enumerate(oracles):
+        got_c, ref_c = grp.cache[a][b * npp:(b + 1) * npp].cpu().float(), o.cache[a].float()
+        assert (got_c - ref_c).abs().max() <= 0.05 * ref_c.abs().max()

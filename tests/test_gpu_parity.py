@@ -176,7 +176,7 @@ def test_moe_permute_slots_combine(q35):
 
 
 @pytest.mark.parametrize("fmt", ["mxfp4", "mxfp8", "fp8row"])
-@pytest.mark.parametrize("T,N,K", [(1, 48, 512), (8, 256, 2048), (33, 130, 1024)])
+@pytest.mark.parametrize("T,N,K", [(1, 48, 512), (8, 256, 2048), (33, 130, 1024), (8, 72, 768)])
 def test_linear_formats(q35, fmt, T, N, K):
     g = torch.Generator().manual_seed(N + K)
     x = torch.randn((T, K), generator=g).to(torch.bfloat16)
@@ -357,7 +357,8 @@ def test_gdn_conv_long_and_in_place_state(q35, T):
 
 
 # ------------------------------------------------------------------------------------------------ tensor-core GEMM
-@pytest.mark.parametrize("T,N,K", [(8, 128, 512), (16, 1024, 2048), (40, 130, 512), (100, 384, 2048), (1, 64, 1024)])
+@pytest.mark.parametrize("T,N,K", [(8, 128, 512), (16, 1024, 2048), (40, 130, 512), (100, 384, 2048), (1, 64, 1024),
+                                   (9, 200, 768), (33, 96, 2176), (5, 128, 128)])
 def test_linear_tc_block_scaled_mma(q35, T, N, K):
     """tcgen05 kind::mxf8f6f4 path: MXFP4 weights straight from TMA, activations as two E4M3 terms"""
     g = torch.Generator().manual_seed(T * N + K)
