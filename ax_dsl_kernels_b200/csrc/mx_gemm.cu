@@ -784,7 +784,7 @@ int run_linear(Call& c) {
   // E2M1 or E4M3 weights straight from TMA, activations as two E4M3 terms); without a workspace, or for other K, on the
   // CUDA-core weight-streaming kernel.  Same results within the tolerance of the role.
   const bool tc_shape = K % 256 == 0;
-  const int64_t need = tc_shape ? tc_quant_bytes(T, K) : 0;
+  const int64_t need = tc_shape ? tc_linear_bytes(T, N, K) : 0;
   Tensor ws;
   c.ws_need = need;
   if (!c.dry) Q35_TRY(c.get("workspace", M(Q35_U8), &ws, false));

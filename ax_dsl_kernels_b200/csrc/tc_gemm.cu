@@ -221,7 +221,7 @@ static int launch_nb(const CUtensorMap& w0, const CUtensorMap& w1, const CUtenso
                      const TcArgs& a, int tiles, int groups, cudaStream_t stream) {
   const int smem = TcCfg<NB>::smem_bytes(a.K);
   Q35_TRY(ensure_dynamic_smem(reinterpret_cast<const void*>(tc_gemm_kernel<NB, EPI>), smem));
-  const long long items = (long long)tiles * (a.g_n ? groups : (a.n_dense + a.dense_rows - 1) / a.dense_rows);
+  const long long items = (long long)tiles * (a.g_n ? groups : (a.n_dense + a.dense_rows - 1) / a.dense_rows * a.k_slices);
   const long long slots = (long long)sm_count() * TcCfg<NB>::CTAS_PER_SM;
   const unsigned grid = unsigned(items < slots ? items : slots);
   launch_pdl(tc_gemm_kernel<NB, EPI>, dim3(grid), dim3(TcCfg<NB>::THREADS), size_t(smem), stream, w0, w1, xh, xl, a);
@@ -251,6 +251,12 @@ int tc_launch(const TcWeights& w, const TcQuant& q, TcArgs a, int nb, int tiles,
     nb = nb < a.dense_rows ? nb : a.dense_rows;
   }
   nb = nb <= 16 ? 16 : nb <= 32 ? 32 : 64;
+  if (a.k_slices < 1 || a.g_n || a.part == nullptr) a.k_slices = 1;
+  {
+    const int ks_total = (a.K / 128 + 3) / 4 * 4;
+    a.slice_stages = ((ks_total / 4 + a.k_slices - 1) / a.k_slices) * 4;
+    a.k_slices = (ks_total + a.slice_stages - 1) / a.slice_stages;  // no empty slice
+  }
   Q35_TRY(make_map(&xh, false, q.qh, q.R, a.K, a.K, nb, "activations"));
   Q35_TRY(make_map(&xl, false, q.ql, q.R, a.K, a.K, nb, "activations"));
   a.sfh = q.sh; a.sfl = q.sl; a.total_rows = q.R;
@@ -273,9 +279,50 @@ template int tc_launch<TC_EPI_PLAIN>(const TcWeights&, const TcQuant&, TcArgs, i
 // linear.tc: out[t, n] = x[t, :] . dequant_mxfp4(w[n, :]) on the tensor cores (same contract as `linear` with MXFP4
 // weights; reference: linear(x, w, s) of the MX projections, models/qwen35_2b/whole/src/q35_mx_build.py:100-115)
 // shared by linear.tc and lm_head: quantise x into the workspace and run the plain-epilogue GEMM
+// split-K slices of a dense launch: only for decode-sized inputs (one group of token rows) whose row tiles leave more
+// than half of the CTAs without work; as many slices as bring the items up to the CTA count, in whole scale granules
+int tc_linear_slices(int64_t T, int64_t N, int64_t K) {
+  if (T > 16) return 1;
+  const int64_t tiles = (N + 127) / 128, slots = 2 * int64_t(sm_count()), granules = (K / 128 + 3) / 4;
+  if (tiles * 2 > slots) return 1;
+  int64_t s = slots / tiles;
+  s = s > granules ? granules : s;
+  s = s > 16 ? 16 : s < 1 ? 1 : s;
+  const int64_t per = (granules + s - 1) / s;  // granules a slice; no slice is left empty
+  return int((granules + per - 1) / per);
+}
+
+int64_t tc_linear_bytes(int64_t T, int64_t N, int64_t K) {
+  const int s = tc_linear_slices(T, N, K);
+  return (tc_quant_bytes(T, K) + 255) / 256 * 256 + (s > 1 ? int64_t(s) * T * N * 4 : 0);
+}
+
+// sums the slices' fp32 planes and applies the epilogue of the `linear` role
+__global__ void __launch_bounds__(256) tc_linear_reduce_kernel(const float* __restrict__ part, long long plane, int slices,
+                                                               int T, int N, const float* __restrict__ row_scale,
+                                                               const float* __restrict__ bias,
+                                                               const float* __restrict__ row_div,
+                                                               const __nv_bfloat16* __restrict__ resid2, float* f_out,
+                                                               __nv_bfloat16* b_out) {
+  pdl_wait();
+  pdl_launch();
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (long long)T * N) return;
+  const int t = int(i / N), n = int(i % N);
+  float v = 0.f;
+  for (int s = 0; s < slices; ++s) v += part[s * plane + i];
+  v = v * (row_scale ? row_scale[n] : 1.f) + (bias ? bias[n] : 0.f);
+  if (row_div) v = round_bf16(v) / row_div[t];
+  if (resid2) v = round_bf16(v) + __bfloat162float(resid2[i]);
+  if (f_out) f_out[i] = v;
+  else b_out[i] = __float2bfloat16_rn(v);
+}
+
 int tc_linear(const __nv_bfloat16* x, int64_t T, int64_t N, int64_t K, const TcLinear& p, uint8_t* qws,
               cudaStream_t stream) {
   const TcQuant q = tc_quant_carve(qws, T, K);
+  const int slices = tc_linear_slices(T, N, K);
+  float* part = slices > 1 ? reinterpret_cast<float*>(qws + (tc_quant_bytes(T, K) + 255) / 256 * 256) : nullptr;
   Q35_TRY(tc_quantize(x, int(K), nullptr, int(T), int(T), int(K), q, stream));
   const uint8_t* w = static_cast<const uint8_t*>(p.w);
   TcWeights tw{{w, w}, {uint64_t(N), uint64_t(N)}};
@@ -291,7 +338,14 @@ int tc_linear(const __nv_bfloat16* x, int64_t T, int64_t N, int64_t K, const TcL
   a.f_out = p.f_out; a.b_out = p.b_out;
   a.out_stride = int(N);
   a.bias = p.bias; a.row_div = p.row_div; a.resid2 = p.resid2;
-  return tc_launch<TC_EPI_PLAIN>(tw, q, a, int(T), int((N + 127) / 128), 1, stream);
+  a.k_slices = slices; a.part = part; a.part_plane = (long long)T * N;
+  Q35_TRY(tc_launch<TC_EPI_PLAIN>(tw, q, a, int(T), int((N + 127) / 128), 1, stream));
+  if (slices > 1) {
+    launch_pdl(tc_linear_reduce_kernel, dim3(unsigned((T * N + 255) / 256)), dim3(256), 0, stream, (const float*)part,
+               (long long)T * N, slices, int(T), int(N), a.row_scale, p.bias, p.row_div, p.resid2, p.f_out, p.b_out);
+    Q35_CUDA_LAUNCH_CHECK("tc linear reduce");
+  }
+  return 0;
 }
 
 // shared by linear.tc and lm_head: quantise x into the workspace and run the plain-epilogue GEMM
@@ -313,7 +367,7 @@ int run_linear_tc(Call& c) {
   const int64_t K = x.s[x.nd - 1], T = x.numel() / K, N = w.s[0];
   Q35_REQUIRE(w.s[1] == K / 2 && s.numel() == N * (K / 32) && out.numel() == T * N, Q35_ERR_SHAPE, "linear.tc: shapes");
   Q35_REQUIRE(K % 128 == 0, Q35_ERR_UNSUPPORTED, "linear.tc: K must be a multiple of 128");
-  Q35_TRY(c.workspace(tc_quant_bytes(T, K), &ws));
+  Q35_TRY(c.workspace(tc_linear_bytes(T, N, K), &ws));
   if (c.dry || T == 0 || N == 0) return 0;
   Q35_REQUIRE((uintptr_t(w.p) & 31) == 0 && aligned16(x.p) && aligned16(s.p), Q35_ERR_ALIGN, "linear.tc: alignment");
   return linear_tc_impl(x, w, s, bias.present ? bias.as<float>() : nullptr,
@@ -370,7 +424,7 @@ int run_lm_head(Call& c) {
   Q35_REQUIRE((!logits.present || logits.numel() == T * N) && (!token.present || token.numel() == T), Q35_ERR_SHAPE,
               "lm_head: logits [T, N], token [T]");
   Q35_REQUIRE(K % 512 == 0, Q35_ERR_UNSUPPORTED, "lm_head: K must be a multiple of 512");
-  const int64_t qb = (tc_quant_bytes(T, K) + 255) / 256 * 256;
+  const int64_t qb = (tc_linear_bytes(T, N, K) + 255) / 256 * 256;
   Q35_TRY(c.workspace(qb + (logits.present ? 0 : T * N * 4), &ws));
   if (c.dry || T == 0 || N == 0) return 0;
   Q35_REQUIRE((uintptr_t(w.p) & 31) == 0 && aligned16(x.p) && aligned16(s.p), Q35_ERR_ALIGN, "lm_head: alignment");

@@ -58,6 +58,11 @@ struct TcArgs {
   int stage_tx;             // bytes the TMA unit reports per stage (FP4 tiles count their packed bytes)
   const int* active; const int* n_active;  // compacted list of groups with rows (nullptr: dense)
   int n_tiles;              // row tiles per group
+  // split K (dense launches whose row tiles alone leave most CTAs idle): the stages are cut into k_slices ranges of
+  // slice_stages each, an item is (group, tile, slice), and every slice's fp32 sums go to its own plane of `part`
+  // ([k_slices][rows of x][out_stride]) for a reduction kernel that also applies the epilogue
+  int k_slices, slice_stages;
+  float* part; long long part_plane;
   int* status;
 };
 
@@ -86,7 +91,7 @@ struct TcCfg {
 
 
 struct TcItem {
-  int plane, row0, n, tile;
+  int plane, row0, n, tile, slice;
 };
 
 // Work items are read one ahead of their use: tc_load_item only issues the loads (no branch on what they return), so
@@ -99,11 +104,16 @@ __device__ __forceinline__ void tc_load_item(const TcArgs& a, int j, TcItem* it)
     it->n = a.g_n[grp]; it->plane = a.g_expert[grp]; it->row0 = a.g_row0[grp];
   } else {  // one dense matrix: the rows are cut into virtual groups of dense_rows so that the work spreads over the
             // CTAs (small for decode-sized inputs, whose weights then come out of L2 for all but the first group)
-    it->row0 = (j / a.n_tiles) * a.dense_rows;
+    const int per = a.n_tiles * a.k_slices, jj = j % per;
+    it->row0 = (j / per) * a.dense_rows;
     it->n = min(a.dense_rows, a.n_dense - it->row0);
     it->plane = 0;
+    it->tile = jj % a.n_tiles;
+    it->slice = jj / a.n_tiles;
+    return;
   }
   it->tile = j % a.n_tiles;
+  it->slice = 0;
 }
 
 __device__ __forceinline__ bool tc_check_item(const TcArgs& a, TcItem* it) {
@@ -179,7 +189,11 @@ __global__ void __launch_bounds__(TcCfg<NB>::THREADS, TcCfg<NB>::CTAS_PER_SM) tc
   pdl_wait();
   pdl_launch();
   // a CTA without work walks empty loops and falls through to the release of its tensor memory
-  const int n_items = (a.g_n ? a.n_active[0] : (a.n_dense + a.dense_rows - 1) / a.dense_rows) * a.n_tiles;
+  const int n_items = a.g_n ? a.n_active[0] * a.n_tiles
+                            : (a.n_dense + a.dense_rows - 1) / a.dense_rows * a.n_tiles * a.k_slices;
+  // stage range of an item: all of K, or its slice (slices start on scale-granule boundaries)
+  auto ks_begin = [&](const TcItem& im) { return im.slice * a.slice_stages; };
+  auto ks_end = [&](const TcItem& im) { return min(KS, (im.slice + 1) * a.slice_stages); };
 
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
@@ -189,8 +203,9 @@ __global__ void __launch_bounds__(TcCfg<NB>::THREADS, TcCfg<NB>::CTAS_PER_SM) tc
       TcItem im;
       for (TcItemWalk walk(a, n_items); !dead && walk.next(&im);) {
         const int r0 = im.tile * a.tile_rows + a.roff[0], r1 = im.tile * a.tile_rows + a.roff[1];
+        const int ks0 = ks_begin(im), ks1 = ks_end(im);
         for (int t0 = 0; t0 < im.n && !dead; t0 += NB) {
-          for (int ks = 0; ks < KS; ++ks, ++it) {
+          for (int ks = ks0; ks < ks1; ++ks, ++it) {
             const uint32_t s = it % C::STAGES, ph = (it / C::STAGES) & 1;
             if (!mbar_wait(empty_bar(s), ph ^ 1)) { atomicOr(a.status, DS_WAIT_TIMEOUT | 0x10); dead = true; break; }
             mbar_expect_tx(full_bar(s), uint32_t(a.stage_tx));
@@ -220,7 +235,8 @@ __global__ void __launch_bounds__(TcCfg<NB>::THREADS, TcCfg<NB>::CTAS_PER_SM) tc
           }
           tc_fence_after();
           const uint32_t acc = tmem + b * C::N;
-          for (int ks = 0; ks < KS; ++ks, ++it) {
+          const int ks0 = ks_begin(im), ks1 = ks_end(im);
+          for (int ks = ks0; ks < ks1; ++ks, ++it) {
             const uint32_t s = it % C::STAGES, ph = (it / C::STAGES) & 1;
             const uint32_t g = (it / C::SF_GRAN) % C::SF_RING, gph = (it / (C::SF_GRAN * C::SF_RING)) & 1;
             if ((ks % C::SF_GRAN) == 0 && !mbar_wait(sf_full(g), gph)) {
@@ -236,7 +252,7 @@ __global__ void __launch_bounds__(TcCfg<NB>::THREADS, TcCfg<NB>::CTAS_PER_SM) tc
             for (int k = 0; k < 4; ++k) {
               tc_mma_mxf8f6f4(acc, smem_desc(sa + k * 32, 16, 1024, 2), smem_desc(sb + k * 32, 16, 1024, 2),
                               idesc_mxf8f6f4(uint32_t(a.a_fmt), FMT_E4M3, 128, C::N, k, k), tmem + C::SFA_COL,
-                              tmem + C::SFB_COL, (ks | k) != 0);
+                              tmem + C::SFB_COL, ((ks - ks0) | k) != 0);
             }
             tc_commit(empty_bar(s));
             if ((ks % C::SF_GRAN) == C::SF_GRAN - 1) tc_commit(sf_empty(g));
@@ -253,21 +269,21 @@ __global__ void __launch_bounds__(TcCfg<NB>::THREADS, TcCfg<NB>::CTAS_PER_SM) tc
     const int gt = tid - 192;
     const int srow = a.K / 32;          // scale bytes per row
     const int hh = gt >> 6;
-    const int KG = KS / C::SF_GRAN;
-    int t0 = 0, kg = 0;
+    int t0 = 0, kg = 0, kg0 = 0, kg1 = 0;  // granules [kg0, kg1) of the item's stage range
     bool have_item = false;
     TcItem im{};
     TcItemWalk walk(a, n_items);
     const uint8_t *wsc = nullptr, *xsc = nullptr;
     auto advance = [&]() -> bool {
       if (have_item) {
-        if (++kg < KG) return true;
-        kg = 0; t0 += NB;
+        if (++kg < kg1) return true;
+        kg = kg0; t0 += NB;
         if (t0 >= im.n) have_item = false;
       }
       if (!have_item) {
         if (!walk.next(&im)) return false;
-        have_item = true; t0 = 0; kg = 0;
+        kg0 = ks_begin(im) / C::SF_GRAN; kg1 = ks_end(im) / C::SF_GRAN;
+        have_item = true; t0 = 0; kg = kg0;
         const int wrow = im.tile * a.tile_rows + a.roff[hh] + (gt & 63);
         wsc = (a.sw[hh] && wrow < a.lim[hh]) ? a.sw[hh] + (long long)im.plane * a.s_plane + (long long)wrow * srow : nullptr;
       }
@@ -370,6 +386,15 @@ __global__ void __launch_bounds__(TcCfg<NB>::THREADS, TcCfg<NB>::CTAS_PER_SM) tc
           }
 #pragma unroll
           for (int jj = 0; jj < 16; ++jj) hi[jj] += lo[jj];
+          if (EPI == TC_EPI_PLAIN && a.k_slices > 1) {  // split K: raw sums of this slice, the epilogue runs after the reduction
+            float* pp = a.part + (long long)im.slice * a.part_plane;
+#pragma unroll
+            for (int jj = 0; jj < 16; ++jj) {
+              const int t = t0 + c0 + jj;
+              if (t < im.n && rvalid) pp[(long long)(im.row0 + t) * a.out_stride + row] = hi[jj];
+            }
+            continue;
+          }
           if constexpr (EPI == TC_EPI_SILU_MUL) {
             // Row p of the gate half and row p of the up half make one output element.  The gate rows' threads finish
             // columns 0..7 of the chunk, the up rows' threads columns 8..15; each side hands the other the eight

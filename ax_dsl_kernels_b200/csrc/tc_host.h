@@ -43,7 +43,8 @@ struct TcLinear {
   const float* bias; const float* row_div; const __nv_bfloat16* resid2;
   float* f_out; __nv_bfloat16* b_out;   // one of the two
 };
-// K a multiple of 512; qws = tc_quant_bytes(T, K) bytes of scratch
+// K a multiple of 128; qws = tc_linear_bytes(T, N, K) bytes of scratch (quantised activations + split-K planes)
+int64_t tc_linear_bytes(int64_t T, int64_t N, int64_t K);
 int tc_linear(const __nv_bfloat16* x, int64_t T, int64_t N, int64_t K, const TcLinear& p, uint8_t* qws,
               cudaStream_t stream);
 
