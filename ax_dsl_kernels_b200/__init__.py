@@ -6,7 +6,8 @@ CPU path and no fallback: without the built library every call raises.
 """
 from . import _lib, layers  # noqa: F401
 from ._lib import Q35Error, device_status, io_table, roles, run, workspace_bytes  # noqa: F401
-from .attention import kv_write, paged_attention_decode, paged_attention_prefill  # noqa: F401
+from .attention import (kv_write, mrope_cos_sin, paged_attention_decode, paged_attention_prefill,  # noqa: F401
+                        rope_cos_sin)
 from .gdn import gdn_chunk_prefill, gdn_conv1d_silu, gdn_recurrent_step  # noqa: F401
 from .moe import (linear, moe_block, moe_combine, moe_experts, moe_permute, moe_pre, moe_slots_px,  # noqa: F401
                   prepare_moe_weights, route, tile_scales)

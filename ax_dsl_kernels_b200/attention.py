@@ -58,3 +58,39 @@ def paged_attention_prefill(q, paged_kv_cache, qo_indptr, indptr, indices, last_
         kw["k_new"], kw["v_new"] = k_new, v_new
     _lib.run("attn.paged_prefill", **kw)
     return out
+
+
+def rope_cos_sin(positions, rot, theta, device=None):
+    """cos / sin rows [T, rot / 2] fp32 of plain RoPE for integer positions [T] (the tables attn.qk_prep takes;
+    models/qwen35_2b/whole/src/q35_step.py:408-411)."""
+    pos = torch.as_tensor(positions)
+    device = device if device is not None else pos.device
+    inv = 1.0 / (theta ** (torch.arange(0, rot, 2, dtype=torch.int64).float() / rot))
+    f = pos.to(torch.float32).reshape(-1, 1).cpu() * inv.reshape(1, -1)
+    return f.cos().to(device).contiguous(), f.sin().to(device).contiguous()
+
+
+def mrope_cos_sin(position_ids, rot, theta, mrope_section=(11, 11, 10), interleaved=True, device=None):
+    """cos / sin rows [T, rot / 2] fp32 of multimodal RoPE from position_ids [3, T] (temporal, height, width): rotary
+    pair c turns by position_ids[axis(c), t] * inv_freq[c], where axis(c) follows mrope_section = (t, h, w) pairs --
+    chunked (T pairs first, then H, then W) or interleaved (pairs 1, 4, 7, ... below 3 h follow H, pairs 2, 5, 8, ...
+    below 3 w follow W, the rest T).  Reference: gather_mrope_cos_sin / mrope_channel_masks
+    (models/qwen35_35b_a3b/sgl/python/sgl_kernel_axera/attention/attn_utils/common.py:316-398).  The rows feed
+    attn.qk_prep exactly like plain RoPE rows; text-only input (three equal rows) gives plain RoPE."""
+    pos = torch.as_tensor(position_ids)
+    if pos.dim() != 2 or pos.shape[0] != 3:
+        raise ValueError("mrope_cos_sin: position_ids must be [3, T]")
+    t, h, w = (int(v) for v in mrope_section)
+    if min(t, h, w) < 0 or 2 * (t + h + w) != rot:
+        raise ValueError(f"mrope_cos_sin: mrope_section {tuple(mrope_section)} must sum to rot / 2 = {rot // 2}")
+    device = device if device is not None else pos.device
+    axis = torch.zeros(rot // 2, dtype=torch.long)
+    if interleaved:
+        axis[1:h * 3:3] = 1
+        axis[2:w * 3:3] = 2
+    else:
+        axis[t:t + h] = 1
+        axis[t + h:] = 2
+    inv = 1.0 / (theta ** (torch.arange(0, rot, 2, dtype=torch.int64).float() / rot))
+    f = pos.to(torch.float32).cpu()[axis].T * inv.reshape(1, -1)
+    return f.cos().to(device).contiguous(), f.sin().to(device).contiguous()

@@ -56,8 +56,7 @@ def _finish(args, name, metric, unit_items, step, ins, outs, roofline, config, d
     n0 = L.q35_launch_count()
     step()
     launches = L.q35_launch_count() - n0
-    use_graph = not args.no_graph and (world == 1 or args.graph_nccl)
-    graph = hb.capture(step) if use_graph else None
+    graph = hb.capture(step) if not args.no_graph else None  # several ranks: the NCCL all-reduces are captured too
     run = graph.replay if graph is not None else step
     barrier()
     rounds = hb.timed_rounds(run, args.steps, barrier, agree=agree)
@@ -101,7 +100,7 @@ def _finish(args, name, metric, unit_items, step, ins, outs, roofline, config, d
             line.update(extra(per_step))
         print(json.dumps(line), flush=True)
     if dist is not None:
-        if args.graph_nccl:  # captured collectives keep the communicator busy at teardown: leave without it
+        if graph is not None:  # captured collectives keep the communicator busy at teardown: leave without it
             barrier()
             os._exit(0)
         dist.destroy_process_group()
@@ -109,6 +108,7 @@ def _finish(args, name, metric, unit_items, step, ins, outs, roofline, config, d
 
 def _hbm(nbytes, kernel):
     peak, _, src = hb.measured_peaks()
+    peak *= int(os.environ.get("WORLD_SIZE", 1))  # whole-job bytes against the GPUs' aggregate bandwidth
 
     def f(ms):
         gbs = nbytes / (ms * 1e-3) / 1e9

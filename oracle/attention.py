@@ -122,6 +122,33 @@ def rope_cos_sin(pos, rot, theta):
     return f.cos(), f.sin()
 
 
+def mrope_channel_axis(section, interleaved):
+    """which of the three position rows (0 = temporal, 1 = height, 2 = width) rotary pair c follows
+    (mrope_channel_masks, models/qwen35_35b_a3b/sgl/python/sgl_kernel_axera/attention/attn_utils/common.py:316-335):
+    chunked: the first t pairs follow T, the next h follow H, the rest W; interleaved: pairs 1, 4, 7, ... below 3 h follow
+    H, pairs 2, 5, 8, ... below 3 w follow W, every other pair T."""
+    t, h, w = (int(v) for v in section)
+    half = t + h + w
+    axis = torch.zeros(half, dtype=torch.long)
+    if interleaved:
+        axis[1:h * 3:3] = 1
+        axis[2:w * 3:3] = 2
+    else:
+        axis[t:t + h] = 1
+        axis[t + h:] = 2
+    return axis
+
+
+def mrope_cos_sin(position_ids, rot, theta, section=(11, 11, 10), interleaved=True):
+    """M-RoPE rows for T tokens from position_ids [3, T]: pair c rotates by position_ids[axis(c), t] * inv_freq[c]
+    (gather_mrope_cos_sin / mix_mrope_tables, attn_utils/common.py:338-398).  Returns cos, sin [T, rot / 2] fp32."""
+    inv = 1.0 / (theta ** (torch.arange(0, rot, 2, dtype=torch.int64).float() / rot))
+    axis = mrope_channel_axis(section, interleaved)
+    pos = position_ids.float()[axis].T  # [T, rot / 2]
+    f = pos * inv
+    return f.cos(), f.sin()
+
+
 def attn_layer_decode(x, w, cache, indptr, indices, last_page_len, cache_location, cos, sin, *, heads, kv_heads,
                       head_dim, rot, gated=True, eps=1e-6, sm_scale=None, kv_scale=None):
     """Decode attention sublayer on B sequences (one token each), golden of

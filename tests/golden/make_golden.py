@@ -99,6 +99,27 @@ def manifest_roles():
     print("wrote manifest_35b_roles.json", list(keep))
 
 
+def mrope():
+    """9. M-RoPE table mixing (attn_utils/common.py:304-345): T / H / W rows of the cos / sin tables mixed by channel masks,
+    sections (11, 11, 10) of the 32 rotary pairs, chunked and interleaved"""
+    sys.meta_path.insert(0, _Finder())
+    sys.path.insert(0, os.path.join(REF, "models/qwen35_35b_a3b/sgl/python"))
+    from sgl_kernel_axera.attention.attn_utils import common as cm
+    g = torch.Generator().manual_seed(31)
+    rot, theta, T = 64, 1e7, 9
+    pos = torch.randint(0, 5000, (3, T), generator=g)
+    inv = 1.0 / (theta ** (torch.arange(0, rot, 2, dtype=torch.int64).float() / rot))
+    table = torch.arange(5000).float().reshape(-1, 1) * inv.reshape(1, -1)
+    cos_t, sin_t = table.cos(), table.sin()
+    d = dict(position_ids=pos.to(torch.int32), inv_freq=inv)
+    for name, inter in (("chunked", False), ("interleaved", True)):
+        m = cm.mrope_channel_masks((11, 11, 10), interleaved=inter)
+        d[f"mask_{name}"] = torch.tensor(np.stack(m))
+        d[f"cos_{name}"] = cm.mix_mrope_tables(cos_t[pos[0]], cos_t[pos[1]], cos_t[pos[2]], (11, 11, 10), interleaved=inter)
+        d[f"sin_{name}"] = cm.mix_mrope_tables(sin_t[pos[0]], sin_t[pos[1]], sin_t[pos[2]], (11, 11, 10), interleaved=inter)
+    save("mrope", d)
+
+
 def main():
     if not os.path.isdir(REF):
         sys.exit("set REF to the reference checkout")
@@ -106,6 +127,8 @@ def main():
         return lm_head()
     if "--only-manifest" in sys.argv:
         return manifest_roles()
+    if "--only-mrope" in sys.argv:
+        return mrope()
     sys.meta_path.insert(0, _Finder())
     sgl = os.path.join(REF, "models/qwen35_35b_a3b/sgl")
     sys.path[:0] = [os.path.join(sgl, "python"), os.path.join(sgl, "tests"),
@@ -184,6 +207,7 @@ def main():
     save("gdn_sublayer", d)
     lm_head()
     manifest_roles()
+    mrope()
 
 
 if __name__ == "__main__":

@@ -309,6 +309,30 @@ def test_moe_experts_token_listing_an_expert_twice(q35, T, K, NE):
     assert_parity(out.cpu()[sample], ref, bf16_step=True)
 
 
+def test_qk_prep_with_mrope_rows(q35, golden):
+    """multimodal RoPE: rows built from position_ids [3, T] (sections 11, 11, 10, interleaved) through attn.qk_prep
+    against the golden's q / k norm + NeoX rotation with the reference-mixed tables"""
+    from oracle.moe import rmsnorm
+    f = golden("mrope")
+    T, HQn, HKVn, Dn = 9, 4, 1, 256
+    g = torch.Generator().manual_seed(6)
+    qg = torch.randn((T, HQn, 2 * Dn), generator=g).to(torch.bfloat16)
+    k = torch.randn((T, HKVn, Dn), generator=g).to(torch.bfloat16)
+    qn, kn = 1 + 0.1 * torch.randn(Dn, generator=g), 1 + 0.1 * torch.randn(Dn, generator=g)
+    cos, sin = q35.mrope_cos_sin(f["position_ids"], 64, 1e7, (11, 11, 10), True, device="cuda")
+    q_out = torch.empty((T, HQn, Dn), dtype=torch.bfloat16, device="cuda")
+    k_out = torch.empty((T, HKVn, Dn), dtype=torch.bfloat16, device="cuda")
+    gate = torch.empty_like(q_out)
+    q35.run("attn.qk_prep", qg=qg.cuda(), k=k.cuda(), q_norm=qn.cuda(), k_norm=kn.cuda(), cos=cos, sin=sin, q_out=q_out,
+            k_out=k_out, gate_out=gate)
+    rc, rs = f["cos_interleaved"], f["sin_interleaved"]
+    q_ref = oattn.rope_neox(rmsnorm(qg[..., :Dn], qn), rc[:, None, :], rs[:, None, :], 64)
+    k_ref = oattn.rope_neox(rmsnorm(k, kn), rc[:, None, :], rs[:, None, :], 64)
+    assert_parity(q_out.cpu(), q_ref)
+    assert_parity(k_out.cpu(), k_ref)
+    assert torch.equal(gate.cpu(), qg[..., Dn:])
+
+
 # ------------------------------------------------------------------------------------------------ robustness
 def test_bounded_wait_reports_instead_of_hanging(q35):
     """a device-side wait that can never complete (a barrier nothing arrives at, 4096 polls) gives up, sets the

@@ -92,3 +92,26 @@ def test_lm_head_codec_and_logits_match_reference(golden):
     logits, token = codecs.lm_head_logits(f["x"], f["packed"], f["scale"])
     torch.testing.assert_close(logits, f["logits"], rtol=1e-5, atol=1e-5 * float(f["logits"].abs().max()))
     assert torch.equal(token, f["token"])
+
+
+def test_mrope_tables_match_reference_mixing(golden):
+    """M-RoPE rows: the oracle and the package's host helper against the reference's mix_mrope_tables /
+    mrope_channel_masks (sections 11, 11, 10; chunked and interleaved), and text-only positions give plain RoPE"""
+    from ax_dsl_kernels_b200.attention import mrope_cos_sin, rope_cos_sin
+    from oracle import attention as oattn
+    f = golden("mrope")
+    pos = f["position_ids"]
+    for name, inter in (("chunked", False), ("interleaved", True)):
+        axis = oattn.mrope_channel_axis((11, 11, 10), inter)
+        assert torch.equal(torch.nn.functional.one_hot(axis, 3).T.float(), f[f"mask_{name}"].float())
+        for fn in (oattn.mrope_cos_sin, mrope_cos_sin):
+            cos, sin = fn(pos, 64, 1e7, (11, 11, 10), inter)
+            torch.testing.assert_close(cos, f[f"cos_{name}"], rtol=0, atol=2e-6)
+            torch.testing.assert_close(sin, f[f"sin_{name}"], rtol=0, atol=2e-6)
+    same = torch.stack([pos[0]] * 3)
+    c1, s1 = mrope_cos_sin(same, 64, 1e7)
+    c0, s0 = rope_cos_sin(pos[0], 64, 1e7)
+    assert torch.equal(c1, c0) and torch.equal(s1, s0)
+    import pytest
+    with pytest.raises(ValueError):
+        mrope_cos_sin(pos, 64, 1e7, (11, 11, 11))
