@@ -4,7 +4,7 @@ and gated delta net, behind the reference's runtime-weight, tensors-by-name kern
 Host code is a thin Python layer over the C ABI in include/q35b200.h (libq35b200.so, hand-written CUDA).  There is no
 CPU path and no fallback: without the built library every call raises.
 """
-from . import _lib, layers  # noqa: F401
+from . import _lib, layers, packs, speculative  # noqa: F401
 from ._lib import Q35Error, device_status, io_table, roles, run, workspace_bytes  # noqa: F401
 from .attention import (kv_write, mrope_cos_sin, paged_attention_decode, paged_attention_prefill,  # noqa: F401
                         rope_cos_sin)

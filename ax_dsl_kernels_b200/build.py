@@ -56,7 +56,7 @@ def build(force=False, verbose=False):
             raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
     if force or _stale(RUNNER, [RUNNER_SRC, LIB, headers[-1]]):
         r = subprocess.run([NVCC, "-O2", "-std=c++17", "-I", os.path.join(os.path.dirname(HERE), "include"), RUNNER_SRC,
-                            "-o", RUNNER, "-L", HERE, "-lq35b200", "-lcudart", "-Xlinker", "-rpath", "-Xlinker",
+                            "-o", RUNNER, "-L", HERE, "-lq35b200", "-lcudart", "-lpthread", "-Xlinker", "-rpath", "-Xlinker",
                             "$ORIGIN"], capture_output=True, text=True)
         if r.returncode:
             raise RuntimeError(f"runner build failed:\n{r.stdout}\n{r.stderr}")

@@ -180,8 +180,11 @@ static const RoleDef kRoles[] = {
      R"({"in":[["base","bf16","[T,H]"],["loc","i32","[K,T]"],["sout","bf16|f32","[R,H]"]],"out":[["out","bf16","[T,H]"]]})",
      run_moe_combine},
     {"attn.paged_decode",
-     R"({"in":[["q","bf16","[B,HQ,D]"],["paged_kv_cache","bf16|e4m3","[pages,2,P,HKV,D]"],["indptr","i32","[B+1]"],["indices","i32","[N]"],["last_page_len","i32","[B]"],["sm_scale","f32","[1] optional"],["kv_scale","f32","[2,HKV] optional"],["k_new","bf16","[B,HKV,D] optional"],["v_new","bf16","[B,HKV,D] optional"],["workspace","u8","[*]"]],"out":[["out","bf16","[B,HQ,D]"]]})",
+     R"({"in":[["q","bf16","[B,HQ,D]"],["paged_kv_cache","bf16|e4m3","[pages,2,P,HKV,D]"],["indptr","i32","[B+1]"],["indices","i32","[N]"],["last_page_len","i32","[B]"],["sm_scale","f32","[1] optional"],["kv_scale","f32","[2,HKV] optional"],["k_new","bf16","[B,HKV,D] optional"],["v_new","bf16","[B,HKV,D] optional"],["workspace","u8","[*]"]],"out":[["out","bf16","[B,HQ,D]"],["part_m","f32","[B,HQ] optional with part_l, part_o instead of out: the unnormalised result for attn.lse_merge"],["part_l","f32","[B,HQ]"],["part_o","f32","[B,HQ,D]"]]})",
      run_attn_paged_decode},
+    {"attn.lse_merge",
+     R"({"in":[["part_m","f32","[G,B,HQ]"],["part_l","f32","[G,B,HQ]"],["part_o","f32","[G,B,HQ,D]"]],"out":[["out","bf16","[B,HQ,D]"]]})",
+     run_attn_lse_merge},
     {"attn.kv_write",
      R"({"in":[["k_new","bf16","[B,HKV,D]"],["v_new","bf16","[B,HKV,D]"],["cache_location","i32","[B,2]"],["kv_scale","f32","[2,HKV] optional"]],"out":[["paged_kv_cache","bf16|e4m3","[pages,2,P,HKV,D]"]]})",
      run_attn_kv_write},

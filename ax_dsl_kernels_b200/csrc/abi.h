@@ -117,6 +117,7 @@ int run_moe_combine(Call&);
 int run_moe_permute(Call&);
 int run_attn_paged_decode(Call&);
 int run_attn_kv_write(Call&);
+int run_attn_lse_merge(Call&);
 int run_attn_paged_prefill(Call&);
 int run_gdn_step(Call&);
 int run_gdn_conv(Call&);

@@ -42,6 +42,9 @@ struct AttnArgs {
   const __nv_bfloat16* k_new;  // optional [B, HKV, D]
   const __nv_bfloat16* v_new;
   __nv_bfloat16* out;   // [B, HQ, D]
+  // optional: the merged but UNNORMALISED result per (sequence, query head) instead of `out`, for a merge across
+  // devices that each hold a part of the keys: maximum (log2 domain), sum of weights, weighted values
+  float* lse_m; float* lse_l; float* lse_o;   // [B, HQ], [B, HQ], [B, HQ, D]
   int B, HQ, HKV, G, P, num_pages, n_indices, n_cta;
   // workspace
   AttnPlan* plan;
@@ -410,8 +413,54 @@ __global__ void __launch_bounds__(D / 2) attn_merge_kernel(const AttnArgs a) {
     o0 = o0 * fa + __bfloat162float(vp[2 * tid]) * fb;
     o1 = o1 * fa + __bfloat162float(vp[2 * tid + 1]) * fb;
   }
+  if (a.lse_o) {
+    if (tid == 0) { a.lse_m[size_t(b) * a.HQ + h] = M; a.lse_l[size_t(b) * a.HQ + h] = L; }
+    *reinterpret_cast<float2*>(a.lse_o + (size_t(b) * a.HQ + h) * D + 2 * tid) = make_float2(o0, o1);
+    return;
+  }
   const float inv = L > 0.f ? 1.f / L : 0.f;
   *reinterpret_cast<uint32_t*>(a.out + (size_t(b) * a.HQ + h) * D + 2 * tid) = pack_bf16(o0 * inv, o1 * inv);
+}
+
+// attn.lse_merge: out[b, h] = sum_g o_g 2^(m_g - M) / sum_g l_g 2^(m_g - M), M = max_g m_g: the partial results of G
+// devices that each attended to a part of the keys (split by pages inside a KV head), all-gathered and merged -- the
+// pair scheme of the reference's multi-core attention (models/qwen35_35b_a3b/sgl/python/sgl_kernel_axera/attention/
+// flash_attn.py:2393-2474; models/qwen35_2b/whole/src/q35_layer_mc.py:361-379).  Parts with l = 0 hold nothing.
+__global__ void attn_lse_merge_kernel(const float* __restrict__ pm, const float* __restrict__ pl,
+                                      const float* __restrict__ po, __nv_bfloat16* __restrict__ out, int G, int BH, int D) {
+  const int bh = blockIdx.x;
+  float M = -INFINITY;
+  for (int g = 0; g < G; ++g)
+    if (pl[size_t(g) * BH + bh] > 0.f) M = fmaxf(M, pm[size_t(g) * BH + bh]);
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float L = 0.f, o = 0.f;
+    for (int g = 0; g < G; ++g) {
+      const float l = pl[size_t(g) * BH + bh];
+      if (!(l > 0.f)) continue;
+      const float f = exp2f(pm[size_t(g) * BH + bh] - M);
+      L += l * f;
+      o += po[(size_t(g) * BH + bh) * D + d] * f;
+    }
+    out[size_t(bh) * D + d] = __float2bfloat16_rn(L > 0.f ? o / L : 0.f);
+  }
+}
+
+int run_attn_lse_merge(Call& c) {
+  Tensor pm, pl, po, out;
+  Q35_TRY(c.get("part_m", M(Q35_F32), &pm));
+  Q35_TRY(c.get("part_l", M(Q35_F32), &pl));
+  Q35_TRY(c.get("part_o", M(Q35_F32), &po));
+  Q35_TRY(c.get("out", M(Q35_BF16), &out));
+  Q35_REQUIRE(po.nd == 4 && out.nd == 3, Q35_ERR_SHAPE, "attn.lse_merge: part_o [G, B, HQ, D], out [B, HQ, D]");
+  const int64_t G = po.s[0], B = po.s[1], HQ = po.s[2], D = po.s[3];
+  Q35_REQUIRE(pm.numel() == G * B * HQ && pl.numel() == G * B * HQ && out.numel() == B * HQ * D, Q35_ERR_SHAPE,
+              "attn.lse_merge: part_m / part_l [G, B, HQ]");
+  c.ws_need = 0;
+  if (c.dry || B * HQ == 0) return 0;
+  attn_lse_merge_kernel<<<unsigned(B * HQ), 128, 0, c.stream>>>(pm.as<float>(), pl.as<float>(), po.as<float>(),
+                                                               out.as<__nv_bfloat16>(), int(G), int(B * HQ), int(D));
+  Q35_CUDA_LAUNCH_CHECK("attn.lse_merge");
+  return 0;
 }
 
 // attn.kv_write: the current token's K / V rows into the cache at (page, offset)
@@ -487,7 +536,13 @@ int run_attn_paged_decode(Call& c) {
   Q35_TRY(c.get("kv_scale", M(Q35_F32), &kvs, false));
   Q35_TRY(c.get("k_new", M(Q35_BF16), &kn, false));
   Q35_TRY(c.get("v_new", M(Q35_BF16), &vn, false));
-  Q35_TRY(c.get("out", M(Q35_BF16), &out));
+  Tensor lm, ll, lo;
+  Q35_TRY(c.get("part_m", M(Q35_F32), &lm, false));
+  Q35_TRY(c.get("part_l", M(Q35_F32), &ll, false));
+  Q35_TRY(c.get("part_o", M(Q35_F32), &lo, false));
+  Q35_REQUIRE(lm.present == lo.present && ll.present == lo.present, Q35_ERR_MISSING,
+              "attn.paged_decode: part_m, part_l and part_o go together");
+  Q35_TRY(c.get("out", M(Q35_BF16), &out, !lo.present));
   Q35_REQUIRE(q.nd == 3 && cache.nd == 5 && cache.s[1] == 2, Q35_ERR_SHAPE,
               "attn.paged_decode: q [B, HQ, D], paged_kv_cache [pages, 2, P, HKV, D]");
   const int64_t B = q.s[0], HQ = q.s[1], D = q.s[2], P = cache.s[2], HKV = cache.s[3];
@@ -498,7 +553,9 @@ int run_attn_paged_decode(Call& c) {
   Q35_REQUIRE(D == 64 || D == 128 || D == 256, Q35_ERR_UNSUPPORTED, "attn.paged_decode: head_dim must be 64/128/256");
   Q35_REQUIRE(P % 16 == 0 && P >= 16, Q35_ERR_UNSUPPORTED, "attn.paged_decode: page size must be a multiple of 16");
   Q35_REQUIRE(indptr.numel() == B + 1 && lpl.numel() >= B, Q35_ERR_SHAPE, "attn.paged_decode: indptr [B+1], last_page_len [B]");
-  Q35_REQUIRE(out.numel() == B * HQ * D, Q35_ERR_SHAPE, "attn.paged_decode: out [B, HQ, D]");
+  Q35_REQUIRE(lo.present || out.numel() == B * HQ * D, Q35_ERR_SHAPE, "attn.paged_decode: out [B, HQ, D]");
+  Q35_REQUIRE(!lo.present || (lo.numel() == B * HQ * D && lm.numel() == B * HQ && ll.numel() == B * HQ), Q35_ERR_SHAPE,
+              "attn.paged_decode: part_m / part_l [B, HQ], part_o [B, HQ, D]");
   Q35_REQUIRE(kn.present == vn.present, Q35_ERR_MISSING, "attn.paged_decode: k_new and v_new go together");
   Q35_REQUIRE(!kn.present || (kn.numel() == B * HKV * D && vn.numel() == B * HKV * D), Q35_ERR_SHAPE,
               "attn.paged_decode: k_new / v_new [B, HKV, D]");
@@ -513,7 +570,7 @@ int run_attn_paged_decode(Call& c) {
                 o_ml = take(slots * 16 * 4), o_po = take(slots * AT_GMAX * D * 4);
   Q35_TRY(c.workspace(off, &ws));
   if (c.dry || B == 0) return 0;
-  Q35_REQUIRE(aligned16(q.p) && aligned16(cache.p) && aligned16(out.p), Q35_ERR_ALIGN,
+  Q35_REQUIRE(aligned16(q.p) && aligned16(cache.p) && (lo.present ? aligned16(lo.p) : aligned16(out.p)), Q35_ERR_ALIGN,
               "attn.paged_decode: pointers must be 16-byte aligned");
   AttnArgs a{};
   a.q = q.p; a.cache = cache.p; a.indptr = indptr.as<int>(); a.indices = indices.as<int>();
@@ -522,7 +579,10 @@ int run_attn_paged_decode(Call& c) {
   a.kv_scale = kvs.present ? kvs.as<float>() : nullptr;
   a.k_new = kn.present ? kn.as<__nv_bfloat16>() : nullptr;
   a.v_new = vn.present ? vn.as<__nv_bfloat16>() : nullptr;
-  a.out = out.as<__nv_bfloat16>();
+  a.out = lo.present ? nullptr : out.as<__nv_bfloat16>();
+  a.lse_m = lo.present ? lm.as<float>() : nullptr;
+  a.lse_l = lo.present ? ll.as<float>() : nullptr;
+  a.lse_o = lo.present ? lo.as<float>() : nullptr;
   a.B = int(B); a.HQ = int(HQ); a.HKV = int(HKV); a.G = int(G); a.P = int(P);
   a.num_pages = int(cache.s[0]); a.n_indices = int(indices.numel()); a.n_cta = n_cta;
   uint8_t* w = ws.as<uint8_t>();

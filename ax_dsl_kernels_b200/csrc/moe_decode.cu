@@ -819,7 +819,6 @@ static int md_grid(int* grid) {  // CTAs that are resident at once: the kernel's
     int occ = int(std::min<long long>(smem_sm / per_cta, regs_sm / (regs_cta > 0 ? regs_cta : 1)));
     Q35_REQUIRE(occ >= 1, Q35_ERR_CUDA, "the decode MoE kernel does not fit an SM (%lld bytes of shared memory)", per_cta);
     per_device[dev] = sm_count() * (occ > 2 ? 2 : occ);
-    if (getenv("Q35_MD_GRID")) per_device[dev] = atoi(getenv("Q35_MD_GRID"));
   }
   *grid = per_device[dev];
   return 0;

@@ -779,12 +779,12 @@ int run_linear(Call& c) {
   Q35_REQUIRE(!bias.present || bias.numel() == N, Q35_ERR_SHAPE, "linear: bias [N]");
   Q35_REQUIRE((!rdiv.present || rdiv.numel() == T) && (!resid.present || resid.numel() == T * N), Q35_ERR_SHAPE,
               "linear: row_div [T], residual [T, N]");
-  Q35_REQUIRE(K % 256 == 0, Q35_ERR_UNSUPPORTED, "linear: K must be a multiple of 256");
+  Q35_REQUIRE(K % 128 == 0, Q35_ERR_UNSUPPORTED, "linear: K must be a multiple of 128");
   // With a workspace bound, the projection runs on the tensor cores (tcgen05 block-scaled MMA:
-  // E2M1 or E4M3 weights straight from TMA, activations as two E4M3 terms); without a workspace, or for other K, on the
-  // CUDA-core weight-streaming kernel.  Same results within the tolerance of the role.
-  const bool tc_shape = K % 256 == 0;
-  const int64_t need = tc_shape ? tc_linear_bytes(T, N, K) : 0;
+  // E2M1 or E4M3 weights straight from TMA, activations as two E4M3 terms); without a workspace on the CUDA-core
+  // weight-streaming kernel, which takes K in multiples of 256 only.  Same results within the tolerance of the role.
+  const bool tc_shape = true;
+  const int64_t need = tc_linear_bytes(T, N, K);
   Tensor ws;
   c.ws_need = need;
   if (!c.dry) Q35_TRY(c.get("workspace", M(Q35_U8), &ws, false));
@@ -801,6 +801,9 @@ int run_linear(Call& c) {
     p.b_out = out.dtype == Q35_F32 ? nullptr : out.as<__nv_bfloat16>();
     return tc_linear(x.as<__nv_bfloat16>(), T, N, K, p, ws.as<uint8_t>(), c.stream);
   }
+  Q35_REQUIRE(K % 256 == 0, Q35_ERR_UNSUPPORTED,
+              "linear: K that is not a multiple of 256 needs the tensor-core path (an aligned workspace of "
+              "q35_workspace_bytes)");
   SkinnyArgs d{};
   d.status = device_status_ptr();
   d.n_dense = int(T); d.n_planes = 1;

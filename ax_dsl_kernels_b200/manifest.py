@@ -4,8 +4,9 @@ bytes, dtype, shape}], "out": [...]}}}) and binding their roles to this library'
 
 A manifest role whose IO table is a plain list of named tensors maps onto one role here with the same tensor names:
 `moe.slots<S>_g<G>` -> `moe.slots`, `moe.combine_t<T>` -> `moe.combine`, `lm_head` -> `lm_head`.  The fused NPU roles
-(`decode.group`, `prefill<N>.gdn`, `prefill<N>.attn`) take weight PACKS and phase banks, which are not read here; the
-host functions in layers.py cover their computation with one tensor per weight.
+(`decode.group`, `prefill<N>.gdn`, `prefill<N>.attn`) take weight PACKS and phase banks: packs.py reads those
+(`packs.group_layers(manifest, role, tensors)` -> per-layer weights) and the host functions in layers.py
+(`DecodeGroup`, `gdn`, `attention`, `mlp_residual`) run their computation.
 """
 import json
 import re

@@ -116,19 +116,34 @@ class ExpertParallelMoE:
         for dst, src in pairs:
             dist.all_gather_into_tensor(dst, src.contiguous(), group=self.group)
 
-    def forward(self, x1, out=None):
+    def forward(self, x1, out=None, marks=None):
+        """marks: a list; when given, a (phase name, CUDA event) pair is appended after every phase of the step, so a
+        caller can time the phases on the device (the first entry marks the start)."""
+        def mark(name):
+            if marks is not None and x1.is_cuda:
+                ev = torch.cuda.Event(enable_timing=True)
+                ev.record()
+                marks.append((name, ev))
+
         T, H = x1.shape
         N, K = self.world, self.top_k
+        mark("start")
         base, h2, ids, rw, ready = self._dense_part(x1)
+        mark("norm + router + route (shared expert on a second stream)")
         h2_all = self._get("h2_all", (N * T, H), h2.dtype, h2.device)
         ids_all = self._get("ids_all", (N * T, K), ids.dtype, ids.device)
         rw_all = self._get("rw_all", (N * T, K), rw.dtype, rw.device)
         self._gather(((h2_all, h2), (ids_all, ids), (rw_all, rw)))
+        mark("all-gather of rows, ids, weights")
         partial = self._local_experts(h2_all, ids_all, rw_all)
+        mark("moe.experts on the gathered tokens, local experts")
         mine = self._get("mine", (T, H), torch.float32, x1.device)
         dist.reduce_scatter_tensor(mine, partial, op=dist.ReduceOp.SUM, group=self.group)
+        mark("reduce-scatter of the fp32 partial sums")
         out = torch.empty_like(x1) if out is None else out
-        return self._finish(base, mine, out, ready)
+        out = self._finish(base, mine, out, ready)
+        mark("closing sum (waits for the shared expert)")
+        return out
 
 # ----------------------------------------------------------------------------------------------------------------
 # Tensor parallelism of the dense hybrid stack (27B-class decode group: heads split across 2 / 4 / 8 GPUs).
@@ -254,3 +269,107 @@ def tensor_parallel_decode_group(layers, kinds, *, batch, heads, kv_heads, head_
                                          gated=gated)
     return DecodeGroup(shards, kinds, batch=batch, heads=hl, kv_heads=kl, head_dim=head_dim, gated=gated,
                        reduce=all_reduce_sum(g), **group_kw)
+
+
+# ----------------------------------------------------------------------------------------------------------------
+# Paged attention decode split over GPUs (the standalone attention configuration: batch 64, 16 q / 2 kv heads).
+# Query heads go with their KV head.  While there are at least as many KV heads as ranks, a rank owns whole KV heads
+# and nothing is exchanged inside the attention.  With more ranks than KV heads, the S = world / HKV ranks that share
+# a KV head split every sequence's PAGES among themselves (contiguous shares), each computes the unnormalised
+# partial (m, l, o) over its pages (role attn.paged_decode with part_* outputs), the partials are all-gathered and
+# merged by log-sum-exp (role attn.lse_merge) -- the pair scheme of the reference's multi-core attention
+# (models/qwen35_35b_a3b/sgl/python/sgl_kernel_axera/attention/flash_attn.py:2393-2474;
+#  models/qwen35_2b/whole/src/q35_layer_mc.py:308-379).
+
+def attention_split(heads, kv_heads, world, rank):
+    """-> dict(kv0, kv1: this rank's KV heads [kv0, kv1); q0, q1: its query heads; share, shares: its part of the pages)"""
+    group = heads // kv_heads
+    if world <= kv_heads:
+        if kv_heads % world:
+            raise ValueError(f"{kv_heads} KV heads do not divide over {world} ranks")
+        per = kv_heads // world
+        kv0 = rank * per
+        return dict(kv0=kv0, kv1=kv0 + per, q0=kv0 * group, q1=(kv0 + per) * group, share=0, shares=1)
+    if world % kv_heads:
+        raise ValueError(f"{world} ranks do not divide over {kv_heads} KV heads")
+    shares = world // kv_heads
+    kv0 = rank // shares
+    return dict(kv0=kv0, kv1=kv0 + 1, q0=kv0 * group, q1=(kv0 + 1) * group, share=rank % shares, shares=shares)
+
+
+def split_page_table(indptr, indices, last_page_len, page, share, shares):
+    """the contiguous share `share` of `shares` of every sequence's pages (host tensors in, host tensors out): pages
+    [share * n / shares, (share + 1) * n / shares) of a sequence with n pages; only the rank that holds a sequence's final
+    page sees its partial fill, the others see full pages.  Returns (indptr, indices, last_page_len)."""
+    ip, out_idx, out_last = [0], [], []
+    for b in range(indptr.numel() - 1):
+        a0, a1 = int(indptr[b]), int(indptr[b + 1])
+        n = a1 - a0
+        lo, hi = share * n // shares, (share + 1) * n // shares
+        out_idx.extend(indices[a0 + lo:a0 + hi].tolist())
+        ip.append(ip[-1] + (hi - lo))
+        out_last.append(int(last_page_len[b]) if hi == n else page)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32)  # noqa: E731
+    return i32(ip), i32(out_idx or [0]), i32(out_last)
+
+
+class HeadSplitAttention:
+    """paged attention decode over the ranks of a group: q [B, HQ, D] (replicated) -> out [B, HQ, D] (replicated).
+    The rank's cache holds ITS KV heads only ([pages, 2, P, kv_local, D]) and its page table ITS share of the pages.
+    local / merge: the compute pieces (default: the library's roles; the CPU tests inject the oracle)."""
+
+    def __init__(self, heads, kv_heads, group=None, local=None, merge=None):
+        self.group = group if group is not None else dist.group.WORLD
+        self.rank, self.world = dist.get_rank(self.group), dist.get_world_size(self.group)
+        self.heads, self.kv_heads = heads, kv_heads
+        self.plan = attention_split(heads, kv_heads, self.world, self.rank)
+        self._local = local or self._gpu_partial
+        self._merge = merge or self._gpu_merge
+        self._buf = {}
+
+    def _get(self, name, shape, dtype, device):
+        key = (name, tuple(shape), dtype)
+        if key not in self._buf:
+            self._buf[key] = torch.empty(tuple(shape), dtype=dtype, device=device)
+        return self._buf[key]
+
+    def _gpu_partial(self, q, cache, indptr, indices, last_page_len, sm_scale, kv_scale, packed):
+        from . import _lib
+        B, Hq, D = q.shape
+        m, ln, o = packed[..., D], packed[..., D + 1], packed[..., :D]
+        pm = self._get("pm", (B, Hq), torch.float32, q.device)
+        pl = self._get("pl", (B, Hq), torch.float32, q.device)
+        po = self._get("po", (B, Hq, D), torch.float32, q.device)
+        kw = dict(q=q, paged_kv_cache=cache, indptr=indptr, indices=indices, last_page_len=last_page_len, part_m=pm,
+                  part_l=pl, part_o=po)
+        if sm_scale is not None:
+            kw["sm_scale"] = sm_scale
+        if kv_scale is not None:
+            kw["kv_scale"] = kv_scale
+        _lib.run("attn.paged_decode", **kw)
+        o.copy_(po)
+        m.copy_(pm)
+        ln.copy_(pl)
+
+    def _gpu_merge(self, pm, pl, po, out):
+        from . import _lib
+        _lib.run("attn.lse_merge", part_m=pm, part_l=pl, part_o=po, out=out)
+
+    def forward(self, q, cache, indptr, indices, last_page_len, out=None, sm_scale=None, kv_scale=None):
+        """q [B, HQ, D]: every rank passes the full query; cache / page table: this rank's (see class docstring)"""
+        B, HQ, D = q.shape
+        p = self.plan
+        ql = q[:, p["q0"]:p["q1"]].contiguous()
+        Hq = ql.shape[1]
+        packed = self._get("packed", (B, Hq, D + 2), torch.float32, q.device)  # o | m | l, one message per rank
+        self._local(ql, cache, indptr, indices, last_page_len, sm_scale, kv_scale, packed)
+        gathered = self._get("gathered", (self.world * B, Hq, D + 2), torch.float32, q.device)  # ranks along dim 0
+        dist.all_gather_into_tensor(gathered, packed, group=self.group)
+        S = p["shares"]
+        n_kv_groups = self.world // S  # rank = kv group * S + share
+        g = gathered.reshape(n_kv_groups, S, B, Hq, D + 2).permute(1, 2, 0, 3, 4).reshape(S, B, n_kv_groups * Hq, D + 2)
+        po = g[..., :D].contiguous()
+        pm, pl = g[..., D].contiguous(), g[..., D + 1].contiguous()
+        out = torch.empty((B, HQ, D), dtype=q.dtype, device=q.device) if out is None else out
+        self._merge(pm, pl, po, out)
+        return out

@@ -325,6 +325,18 @@ def run_ours(args):
         parts["attn.paged_decode (plan + decode + merge)"] = median(
             timed_rounds(gph.replay if gph else attn_only, args.steps, barrier, min_seconds=0.2, agree=agree)) / args.steps
     attn_ms = parts["attn.paged_decode (plan + decode + merge)"]
+    ep_phases = None
+    if world > 1:  # the expert-parallel MoE step phase by phase: eager launches bracketed by events, median over steps
+        per = {}
+        for it in range(40):
+            marks = []
+            ep.forward(wl.x1, wl.moe_out, marks=marks)
+            torch.cuda.synchronize()
+            if it >= 8:
+                for (_, a), (name, b) in zip(marks[:-1], marks[1:]):
+                    per.setdefault(name, []).append(a.elapsed_time(b))
+                per.setdefault("whole MoE step (eager)", []).append(marks[0][1].elapsed_time(marks[-1][1]))
+        ep_phases = {name: round(median(v) * 1e3, 1) for name, v in per.items()}
 
     # end to end: the per-step activations start in ONE pinned host block and the results come back into one
     host_in = torch.empty(wl.inputs.nbytes, dtype=torch.uint8).pin_memory()
@@ -389,6 +401,8 @@ def run_ours(args):
             "clocks": clocks_summary(clocks),
             "device_status": status,
         }
+        if ep_phases is not None:
+            line["ep_phases_us_rank0"] = ep_phases
         if world == 1:
             ids = q35.moe_block(wl.x1, wl.w, TOPK, wl.moe_out)[1]
             distinct = int(torch.unique(ids).numel())

@@ -120,38 +120,61 @@ def _hbm(nbytes, kernel):
 
 def run_c2(args, fp8):
     import ax_dsl_kernels_b200 as q35
-    dev = torch.device("cuda", 0)
-    torch.cuda.set_device(0)
+    rank = int(os.environ.get("RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import datetime
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=180))
     B = 64
     ctxs = torch.randint(1024, 16385, (B,), generator=torch.Generator().manual_seed(1)).tolist()
-    g = torch.Generator(device=dev).manual_seed(1)
     n_pages = [(c + PAGE - 1) // PAGE for c in ctxs]
-    total = sum(n_pages)
-    cache = torch.empty((total, 2, PAGE, HKV, D), dtype=torch.bfloat16, device=dev)
+    indptr = torch.tensor([0, *torch.tensor(n_pages).cumsum(0).tolist()], dtype=torch.int32)
+    last = torch.tensor([c - (n - 1) * PAGE for c, n in zip(ctxs, n_pages)], dtype=torch.int32)
+    kv_local = HKV
+    if world > 1:  # this rank's KV heads and its share of every sequence's pages (see parallel.HeadSplitAttention)
+        from ax_dsl_kernels_b200 import parallel
+        plan = parallel.attention_split(HQ, HKV, world, rank)
+        kv_local = plan["kv1"] - plan["kv0"]
+        indptr, _, last = parallel.split_page_table(indptr, torch.arange(sum(n_pages), dtype=torch.int32), last, PAGE,
+                                                    plan["share"], plan["shares"])
+    total = int(indptr[-1])
+    g = torch.Generator(device=dev).manual_seed(1 + rank)
+    cache = torch.empty((total, 2, PAGE, kv_local, D), dtype=torch.bfloat16, device=dev)
     for i in range(0, total, 2048):
-        cache[i:i + 2048] = torch.randn((min(2048, total - i), 2, PAGE, HKV, D), generator=g, device=dev).to(torch.bfloat16)
-    indices = torch.randperm(total, generator=g, device=dev).to(torch.int32)
-    indptr = torch.tensor([0, *torch.tensor(n_pages).cumsum(0).tolist()], dtype=torch.int32, device=dev)
-    last = torch.tensor([c - (n - 1) * PAGE for c, n in zip(ctxs, n_pages)], dtype=torch.int32, device=dev)
-    q = torch.randn((B, HQ, D), generator=g, device=dev).to(torch.bfloat16)
+        cache[i:i + 2048] = torch.randn((min(2048, total - i), 2, PAGE, kv_local, D), generator=g, device=dev).to(torch.bfloat16)
+    indices = torch.randperm(total, generator=g, device=dev).to(torch.int32)  # physical pages: a random permutation
+    indptr, last = indptr.to(dev), last.to(dev)
+    q = torch.randn((B, HQ, D), generator=torch.Generator(device=dev).manual_seed(11), device=dev).to(torch.bfloat16)
     kvs = None
     if fp8:
-        amax = cache.float().abs().amax((0, 2, 4)) if total < 4096 else torch.stack(
-            [cache[i:i + 2048].float().abs().amax((0, 2, 4)) for i in range(0, total, 2048)]).amax(0)
+        amax = torch.stack([cache[i:i + 2048].float().abs().amax((0, 2, 4)) for i in range(0, total, 2048)]).amax(0)
         kvs = (amax / 448.0).contiguous()
         c8 = torch.empty(cache.shape, dtype=torch.float8_e4m3fn, device=dev)
         for i in range(0, total, 2048):
-            c8[i:i + 2048] = (cache[i:i + 2048].float() / kvs.reshape(1, 2, 1, HKV, 1)).to(torch.float8_e4m3fn)
+            c8[i:i + 2048] = (cache[i:i + 2048].float() / kvs.reshape(1, 2, 1, kv_local, 1)).to(torch.float8_e4m3fn)
         cache = c8
     out = torch.empty_like(q)
     scale = torch.tensor([1.0 / 16], device=dev)
-    step = lambda: q35.paged_attention_decode(q, cache, indptr, indices, last, out, sm_scale=scale, kv_scale=kvs)  # noqa: E731
+    if world > 1:
+        att = parallel.HeadSplitAttention(HQ, HKV)
+        step = lambda: att.forward(q, cache, indptr, indices, last, out, sm_scale=scale, kv_scale=kvs)  # noqa: E731
+    else:
+        step = lambda: q35.paged_attention_decode(q, cache, indptr, indices, last, out, sm_scale=scale, kv_scale=kvs)  # noqa: E731
     nbytes = sum(ctxs) * 2 * HKV * D * (1 if fp8 else 2)
     _finish(args, "c2_fp8" if fp8 else "c2", "paged attention decode tok/s (batch 64, contexts 1024..16384)", B, step,
             [q], [out], _hbm(nbytes, f"attn_decode_kernel<256,{'e4m3' if fp8 else 'bf16'}> (+ plan and merge)"),
             {"workload": f"attn.paged_decode alone, batch {B}, contexts uniform in [1024, 16384] (seed 1, {sum(ctxs)} "
              f"tokens), {HQ} q / {HKV} kv heads, head_dim {D}, page {PAGE}, permuted pages, "
-             f"{'FP8 E4M3 KV with per-head scales' if fp8 else 'bf16 KV'}", "l2": "KV larger than L2"}, dev=dev)
+             f"{'FP8 E4M3 KV with per-head scales' if fp8 else 'bf16 KV'}", "l2": "KV larger than L2",
+             "parallelism": "1 GPU" if world == 1 else f"query heads with their KV head over {min(world, HKV)} groups of "
+             f"ranks; {max(1, world // HKV)} ranks share a KV head and split every sequence's pages, one all-gather of "
+             "the unnormalised partials [64, 8, 258] fp32 per rank and a log-sum-exp merge"},
+            dist=dist, dev=dev, scaling="strong")
 
 
 def run_c3_decode(args):

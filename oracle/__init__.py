@@ -12,4 +12,4 @@ tests/golden/.  Goldens that the reference only has inline inside a check functi
 experts, slots, combine, paged decode) are restated from those lines and cross-checked against
 independent float64 formulations.
 """
-from . import codecs, moe, attention, gdn, stack  # noqa: F401
+from . import codecs, moe, attention, gdn, stack, speculative  # noqa: F401

@@ -62,6 +62,39 @@ def paged_decode(q, cache, indptr, indices, last_page_len, sm_scale=None, kv_sca
     return out.to(torch.bfloat16)
 
 
+def paged_decode_partial(q, cache, indptr, indices, last_page_len, sm_scale=None, kv_scale=None):
+    """the unnormalised partial of paged_decode over the given pages: m (maximum score in the log2 domain), l (sum of
+    2^(s - m)), o (sum of 2^(s - m) v) per (sequence, query head) -- what one of several devices that split a KV head's
+    pages contributes (flash_attn.py:2393-2474).  A sequence without keys gives l = 0."""
+    B, HQ, D = q.shape
+    HKV = cache.shape[3]
+    G = HQ // HKV
+    scale = (1.0 / math.sqrt(D) if sm_scale is None else float(sm_scale)) * math.log2(math.e)
+    m = torch.full((B, HQ), float("-inf"))
+    ln = torch.zeros((B, HQ))
+    o = torch.zeros((B, HQ, D))
+    for b in range(B):
+        k, v = gather_kv(cache, indptr, indices, last_page_len, b, kv_scale)
+        if k.shape[0] == 0:
+            continue
+        s = torch.einsum("hgd,lhd->hgl", q[b].float().reshape(HKV, G, D), k) * scale
+        mb = s.amax(-1)
+        p = torch.exp2(s - mb[..., None])
+        m[b], ln[b] = mb.reshape(HQ), p.sum(-1).reshape(HQ)
+        o[b] = torch.einsum("hgl,lhd->hgd", p, v).reshape(HQ, D)
+    return m, ln, o
+
+
+def lse_merge(pm, pl, po):
+    """merge of partials [S, B, HQ(, D)] by log-sum-exp (q35_layer_mc.py:361-379) -> bf16 [B, HQ, D]"""
+    live = pl > 0
+    M = torch.where(live, pm, torch.full_like(pm, float("-inf"))).amax(0)
+    f = torch.where(live, torch.exp2(pm - M), torch.zeros_like(pm))
+    L = (pl * f).sum(0)
+    o = (po * f[..., None]).sum(0)
+    return torch.where(L[..., None] > 0, o / L[..., None].clamp_min(1e-38), torch.zeros_like(o)).to(torch.bfloat16)
+
+
 def paged_prefill(q, cache, qo_indptr, indptr, indices, last_page_len, sm_scale=None):
     """T new tokens per sequence against the paged cache that already holds their K / V rows, causal:
     token i of a sequence with `hist` earlier tokens sees keys 0 .. hist + i (prefill form of the decode golden;

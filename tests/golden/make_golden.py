@@ -120,6 +120,33 @@ def mrope():
     save("mrope", d)
 
 
+def mtp():
+    """10. the MTP block of the speculative-decode group (mtp_step, models/qwen38_27b/mtp/mtp_ref.py:202-239) at a reduced
+    width (the module's size constants are set before its functions run): MXFP4 projections made and dequantised by
+    the module's own codec, three chained rows (the hidden fed back) appending to the block's own paged KV"""
+    sys.path.insert(0, os.path.join(REF, "models/qwen38_27b/mtp"))
+    import mtp_ref as mr
+    mr.H, mr.F, mr.HQ, mr.HKV, mr.D = 256, 512, 2, 1, 128
+    W = mr.MtpWeights("", random=True)
+    packed, deq = mr.mtp_args(W, quantized=True)
+    g = torch.Generator().manual_seed(41)
+    rows = 3
+    e = (torch.randn((rows, mr.H), generator=g) * 0.5).to(torch.bfloat16)
+    h0 = (torch.randn((mr.H,), generator=g) * 0.5).to(torch.bfloat16)
+    kv = torch.zeros((1, 2, 256, mr.HKV * mr.D), dtype=torch.bfloat16)
+    h, hn_all, y_all = h0.float(), [], []
+    for pos in range(rows):
+        hn, y = mr.mtp_step(e[pos].float(), h, pos, kv, deq)
+        hn_all.append(hn.reshape(-1))
+        y_all.append(y.reshape(-1))
+        h = hn.reshape(-1).to(torch.bfloat16).float()  # the next row takes the hidden as the kernels pass it: bf16
+    d = dict(e=e, h0=h0, h_next=torch.stack(hn_all), y=torch.stack(y_all), kv=kv,
+             dims=torch.tensor([mr.H, mr.F, mr.HQ, mr.HKV, mr.D, mr.ROT]))
+    for n, t in packed.items():
+        d["w." + n] = t.view(torch.uint8) if t.dtype in (torch.float4_e2m1fn_x2, torch.float8_e8m0fnu) else t
+    save("mtp", d)
+
+
 def main():
     if not os.path.isdir(REF):
         sys.exit("set REF to the reference checkout")
@@ -129,6 +156,8 @@ def main():
         return manifest_roles()
     if "--only-mrope" in sys.argv:
         return mrope()
+    if "--only-mtp" in sys.argv:
+        return mtp()
     sys.meta_path.insert(0, _Finder())
     sgl = os.path.join(REF, "models/qwen35_35b_a3b/sgl")
     sys.path[:0] = [os.path.join(sgl, "python"), os.path.join(sgl, "tests"),
@@ -208,6 +237,7 @@ def main():
     lm_head()
     manifest_roles()
     mrope()
+    mtp()
 
 
 if __name__ == "__main__":

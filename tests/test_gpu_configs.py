@@ -333,6 +333,40 @@ def test_qk_prep_with_mrope_rows(q35, golden):
     assert torch.equal(gate.cpu(), qg[..., Dn:])
 
 
+def test_attention_split_over_eight_ranks_emulated_on_one_gpu(q35):
+    """configuration-2 heads (16 q / 2 kv) over 8 ranks: four ranks share a KV head and split every sequence's pages;
+    each rank's unnormalised partial (attn.paged_decode with part_* outputs) and attn.lse_merge, run here one rank
+    after the other on this GPU, against the unsplit role and the oracle"""
+    from ax_dsl_kernels_b200 import parallel
+    from _cases import paged_case
+    world = 8
+    q, cache, indptr, indices, last, _ = paged_case([1000, 3, 64, 0, 2500, 129], seed=5)
+    B, HQn, Dn = q.shape
+    full = q35.paged_attention_decode(q.cuda(), cache.cuda(), indptr.cuda(), indices.cuda(), last.cuda())
+    parts = {}
+    for rank in range(world):
+        pl = parallel.attention_split(HQn, 2, world, rank)
+        ip, ix, lp = parallel.split_page_table(indptr, indices, last, 64, pl["share"], pl["shares"])
+        ql = q[:, pl["q0"]:pl["q1"]].contiguous().cuda()
+        pm = torch.full((B, 8), float("nan"), device="cuda")
+        pln = torch.full((B, 8), float("nan"), device="cuda")
+        po = torch.full((B, 8, Dn), float("nan"), device="cuda")
+        q35.run("attn.paged_decode", q=ql, paged_kv_cache=cache[:, :, :, pl["kv0"]:pl["kv1"]].contiguous().cuda(),
+                indptr=ip.cuda(), indices=ix.cuda(), last_page_len=lp.cuda(), part_m=pm, part_l=pln, part_o=po)
+        parts[(pl["kv0"], pl["share"])] = (pm, pln, po)
+    S = world // 2
+    pm = torch.stack([torch.cat([parts[(kv, s)][0] for kv in range(2)], 1) for s in range(S)])
+    pln = torch.stack([torch.cat([parts[(kv, s)][1] for kv in range(2)], 1) for s in range(S)])
+    po = torch.stack([torch.cat([parts[(kv, s)][2] for kv in range(2)], 1) for s in range(S)])
+    out = torch.full_like(full, float("nan"))
+    q35.run("attn.lse_merge", part_m=pm.contiguous(), part_l=pln.contiguous(), part_o=po.contiguous(), out=out)
+    ref = oattn.paged_decode(q, cache, indptr, indices, last)
+    nz = [0, 1, 2, 4, 5]
+    assert (out[3] == 0).all()
+    assert_parity(out.cpu()[nz], ref[nz], per_seq=True)
+    assert_parity(out.cpu()[nz], full.cpu()[nz], per_seq=True, name="attention split over 8 ranks vs the unsplit role")
+
+
 # ------------------------------------------------------------------------------------------------ robustness
 def test_bounded_wait_reports_instead_of_hanging(q35):
     """a device-side wait that can never complete (a barrier nothing arrives at, 4096 polls) gives up, sets the

@@ -248,3 +248,105 @@ def test_decode_group_batched_sequences_match_per_sequence_oracle(q35):
     for b, o in enumerate(oracles):
         got_c, ref_c = grp.cache[a][b * npp:(b + 1) * npp].cpu().float(), o.cache[a].float()
         assert (got_c - ref_c).abs().max() <= 0.05 * ref_c.abs().max()
+
+
+def test_mtp_block_against_reference_golden(q35, golden):
+    """speculative.mtp_step (norms, fc of the concatenated rows, gated attention on the block's own paged KV, dense
+    SwiGLU, head norm -- MXFP4 projections) on the reference's mtp_step fixture: three chained rows"""
+    from oracle import codecs
+    f = golden("mtp")
+    H, Fi, HQ, HKV, D, ROT = (int(v) for v in f["dims"])
+    w = {}
+    for k, t in f.items():
+        if k.startswith("w."):
+            w[k[2:]] = t.cuda()
+    P = 256
+    cache = torch.zeros((1, 2, P, HKV, D), dtype=torch.bfloat16, device="cuda")
+    h = f["h0"].reshape(1, H).cuda()
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda")  # noqa: E731
+    for pos in range(f["e"].shape[0]):
+        cos, sin = q35.rope_cos_sin(torch.tensor([pos]), ROT, 1e7, device="cuda")
+        hn, y = q35.speculative.mtp_step(f["e"][pos].reshape(1, H).cuda(), h, w, cos, sin, cache, i32([0, 1 if pos else 0]),
+                                         i32([0]), i32([pos]), i32([[0, pos]]), heads=HQ, kv_heads=HKV, head_dim=D)
+        assert cosine(y.cpu().float(), f["y"][pos]) >= 0.999, pos
+        assert rel_rms_err(hn.cpu().float().reshape(-1), f["h_next"][pos]) <= 5e-2, pos
+        h = hn
+    got = cache.cpu().reshape(1, 2, P, HKV * D).float()
+    assert (got - f["kv"].float()).abs().max() <= 0.03 * f["kv"].float().abs().max()
+
+
+def test_verify_rows_equal_decode_steps_and_accept_rolls_back(q35):
+    """speculative.verify: 4 candidate rows per sequence in one pass = 4 oracle decode steps, row by row; accept()
+    commits a prefix (different per sequence) and the next decode step continues from exactly there"""
+    kinds = "ga"
+    kw, ow = stack_case(kinds, seed=33)
+    cfg = dict(heads=4, kv_heads=1, head_dim=128, rot=64, theta=1e7)
+    hist, R, H, P, max_tokens = [3, 61], 4, 512, 64, 192
+    B = len(hist)
+    g = torch.Generator().manual_seed(8)
+
+    def fresh_oracles():
+        gg = torch.Generator().manual_seed(99)
+        os_ = []
+        for hlen in hist:
+            o = ostack.HybridStack(ow, kinds, page_size=P, max_tokens=max_tokens, **cfg)
+            o.forward((torch.randn((hlen, H), generator=gg) * 0.5).to(torch.bfloat16))
+            os_.append(o)
+        return os_
+
+    oracles = fresh_oracles()
+    grp = q35.layers.DecodeGroup(to_dev(kw), kinds, batch=B, max_tokens=max_tokens, page_size=P, **cfg)
+    npp = grp.npp
+    for b, o in enumerate(oracles):
+        grp.state[0][b].copy_(o.state[0][0])
+        widths = [c.shape[-1] for c in grp.conv[0]]
+        for c, part in zip(grp.conv[0], torch.split(o.conv[0][0], widths, dim=-1)):
+            c[b].copy_(part)
+        grp.cache[1][b * npp:(b + 1) * npp].copy_(o.cache[1])
+    grp.set_context(hist)
+    x = (torch.randn((B, R, H), generator=g) * 0.5).to(torch.bfloat16)
+    res = q35.speculative.verify(grp, x.cuda())
+    ref_rows = torch.stack([torch.cat([o.forward(x[b, r:r + 1]) for r in range(R)], 0) for b, o in enumerate(oracles)], 0)
+    for b in range(B):
+        for r in range(R):
+            assert cosine(res.out[b, r].cpu().float(), ref_rows[b, r].float()) >= 0.999, (b, r)
+    assert grp.ctx == hist  # nothing committed yet
+    # accept 1 row of sequence 0 and 3 of sequence 1, then one plain decode step
+    n_acc = [1, 3]
+    q35.speculative.accept(grp, res, n_acc)
+    assert grp.ctx == [h + n for h, n in zip(hist, n_acc)]
+    oracles = fresh_oracles()
+    for b, o in enumerate(oracles):
+        for r in range(n_acc[b]):
+            o.forward(x[b, r:r + 1])
+    nxt = (torch.randn((B, H), generator=g) * 0.5).to(torch.bfloat16)
+    got = grp.step(nxt.cuda()).cpu()
+    ref = torch.cat([o.forward(nxt[b:b + 1]) for b, o in enumerate(oracles)], 0)
+    for b in range(B):
+        assert cosine(got[b].float(), ref[b].float()) >= 0.999, b
+
+
+def test_decode_group_bound_through_packs_and_banks(q35):
+    """A `decode.group` role in the reference's binding form (small parameters in packs, projections in phase banks
+    k_b<phase>_<bank>, value heads in the GGUF's tiled order, conv taps reversed) is turned into per-layer weights by
+    packs.group_layers on the GPU and stepped: the output must equal the step of the group built from the plain weights
+    bit for bit (same kernels, same bytes)."""
+    from ax_dsl_kernels_b200 import packs
+    from test_packs_cpu import reference_form_group
+    kinds = "gggaggga"
+    NK, NV = 2, 4
+    kw, _ = stack_case(kinds, seed=9, NK=NK, NV=NV)
+    manifest, tensors = reference_form_group(kw, kinds, NK, NV)
+    bound = {n: t.cuda() for n, t in tensors.items()}
+    layers, got_kinds = packs.group_layers(manifest, "decode.group", bound)
+    cfg = dict(heads=4, kv_heads=1, head_dim=128, rot=64, theta=1e7)
+    B, H = 3, 512
+    outs = []
+    for ws in (to_dev(kw), layers):
+        grp = q35.layers.DecodeGroup(ws, "".join(got_kinds), batch=B, max_tokens=128, **cfg)
+        grp.set_context([0, 3, 64])
+        gx = torch.Generator().manual_seed(2)
+        y = [grp.step((torch.randn((B, H), generator=gx) * 0.5).to(torch.bfloat16).cuda()).cpu() for _ in range(2)]
+        outs.append(torch.stack(y))
+    assert torch.isfinite(outs[0].float()).all()
+    assert torch.equal(outs[0], outs[1])

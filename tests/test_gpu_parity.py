@@ -531,7 +531,7 @@ def test_lm_head_golden_fixture_and_vocabulary_sized(q35, golden):
             assert int(token[r]) == int(ref_tok[r])
 
 
-# ------------------------------------------------------------------------------- full BASELINE sizes, by properties
+# ------------------------------------------------------------------------------- full benchmark sizes, by properties
 def test_gdn_chunk_prefill_full_size_split_invariance(q35):
     """configuration 3 at full size (16384 tokens, 32 value / 16 key heads, chunk 64), where the token-by-token golden
     would take hours: prefilling in one call must equal prefilling two halves with the state carried over, bit for bit

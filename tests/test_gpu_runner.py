@@ -92,3 +92,43 @@ def test_manifest_roles_run_with_the_reference_shapes(tmp_path):
     manifest.run_role(m, "lm_head", dict(x=x.cuda(), w=pk.cuda(), s=sc.cuda(), out=logits))
     assert rel_rms_err(logits.cpu(), codecs.lm_head_logits(x, pk, sc)[0]) <= 2e-2
     assert q35.device_status() == 0
+
+
+def test_four_host_threads_run_replicas_bitwise_equal(runner, tmp_path):
+    """q35run --par: four host threads, a stream and a buffer set each, barrier per round; every replica's outputs
+    equal replica 0's (what the reference's par_test.cc checks across its four cores)"""
+    import ax_dsl_kernels_b200 as q35
+    from ax_dsl_kernels_b200 import casefile
+    from _cases import paged_case
+    q, cache, indptr, indices, last, _ = paged_case([300, 17, 1500, 64])
+    out = q35.paged_attention_decode(q.cuda(), cache.cuda(), indptr.cuda(), indices.cuda(), last.cuda())
+    casefile.dump_case(tmp_path, dict(q=q, paged_kv_cache=cache, indptr=indptr, indices=indices, last_page_len=last),
+                       dict(out=out))
+    r = subprocess.run([runner, "--par", "4", "attn.paged_decode", str(tmp_path), "--rounds", "8"], capture_output=True,
+                       text=True)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "RESULT par=4 rounds=8" in r.stdout and "differing=0 run_failures=0 device_status=0" in r.stdout
+
+
+def test_roles_alternated_with_poisoned_outputs(runner, golden, tmp_path):
+    """q35run --alt: three roles called in turn for several rounds, outputs filled with 0xFF before every call from
+    round 1 on and compared with round 0 (mc_alt.cc with SENTINEL=1): no role leaves output bytes unwritten"""
+    import ax_dsl_kernels_b200 as q35
+    from ax_dsl_kernels_b200 import casefile
+    from _cases import paged_case
+    f = golden("route")
+    ids, rw = q35.route(f["logits"].cuda(), 8)
+    d1, d2, d3 = tmp_path / "route", tmp_path / "attn", tmp_path / "gdn"
+    casefile.dump_case(d1, dict(logits=f["logits"]), dict(ids=ids, rw=rw))
+    q, cache, indptr, indices, last, _ = paged_case([70, 1, 200])
+    out = q35.paged_attention_decode(q.cuda(), cache.cuda(), indptr.cuda(), indices.cuda(), last.cuda())
+    casefile.dump_case(d2, dict(q=q, paged_kv_cache=cache, indptr=indptr, indices=indices, last_page_len=last),
+                       dict(out=out))
+    gq, gk, gv, gg, gb, st = gdn_step_case(B=2, NK=2, NV=4, seed=3)
+    ins = dict(q=gq[:, 0], k=gk[:, 0], v=gv[:, 0], g=gg[:, 0], beta=gb[:, 0], state_in=st)
+    o, s1 = q35.gdn_recurrent_step(*(t.contiguous().cuda() for t in ins.values()), state_out=torch.empty_like(st).cuda())
+    casefile.dump_case(d3, {n: t.contiguous() for n, t in ins.items()}, dict(o=o, state_out=s1))
+    r = subprocess.run([runner, "--alt", "moe.route", str(d1), "attn.paged_decode", str(d2), "gdn.step", str(d3),
+                        "--rounds", "4"], capture_output=True, text=True)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert r.stdout.count("fails=0 mismatches=0") == 3 and "device_status=0" in r.stdout

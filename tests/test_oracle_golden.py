@@ -115,3 +115,34 @@ def test_mrope_tables_match_reference_mixing(golden):
     import pytest
     with pytest.raises(ValueError):
         mrope_cos_sin(pos, 64, 1e7, (11, 11, 11))
+
+
+def _mtp_fixture(golden):
+    from oracle import codecs
+    f = golden("mtp")
+    H, Fi, HQ, HKV, D, ROT = (int(v) for v in f["dims"])
+    deq, raw = {}, {}
+    for k, t in f.items():
+        if not k.startswith("w."):
+            continue
+        n = k[2:]
+        raw[n] = t
+        if n.startswith("w_"):
+            deq[n] = codecs.dequant_mxfp4(t, f["w.s_" + n[2:]])
+        elif not n.startswith("s_"):
+            deq[n] = t
+    return f, deq, raw, dict(heads=HQ, kv_heads=HKV, head_dim=D, rot=ROT)
+
+
+def test_mtp_block_matches_reference_golden(golden):
+    """oracle/speculative.py against mtp_step of the reference (three chained rows on the block's own KV)"""
+    from oracle import speculative as ospec
+    f, deq, _, cfg = _mtp_fixture(golden)
+    kv = torch.zeros_like(f["kv"])
+    h = f["h0"].float()
+    for pos in range(f["e"].shape[0]):
+        hn, y = ospec.mtp_step(f["e"][pos].float(), h, pos, kv, deq, **cfg)
+        torch.testing.assert_close(hn, f["h_next"][pos], rtol=1e-4, atol=1e-4)
+        torch.testing.assert_close(y, f["y"][pos], rtol=1e-4, atol=1e-4)
+        h = hn.to(torch.bfloat16).float()
+    assert torch.equal(kv.view(torch.int16), f["kv"].view(torch.int16))

@@ -192,3 +192,61 @@ def test_column_shard_of_block_scaled_weights():
     assert torch.equal(codecs.dequant_mxfp4(wc, sc), codecs.dequant_mxfp4(w, s)[:, 64:128])
     with pytest.raises(ValueError):
         parallel._cols(w, s, 16, 128)
+
+
+# ----------------------------------------------------------------------------------------------------------------
+# attention split over ranks: KV heads per rank, pages split inside a KV head, LSE merge of the all-gathered partials
+def _attn_worker(rank, world, port, ret):
+    import sys
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from _cases import paged_case
+    from oracle import attention as oattn
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        HQ, HKV, D, P = 8, 2, 64, 16
+        q, cache, indptr, indices, last, _ = paged_case([5, 40, 333, 0, 16], P=P, HKV=HKV, HQ=HQ, D=D, seed=7)
+        ref = oattn.paged_decode(q, cache, indptr, indices, last)
+
+        def local(ql, c, ip, ix, lp, sm, kvs, packed):
+            m, ln, o = oattn.paged_decode_partial(ql, c, ip, ix, lp)
+            packed[..., :D], packed[..., D], packed[..., D + 1] = o, m, ln
+
+        def merge(pm, pl, po, out):
+            out.copy_(oattn.lse_merge(pm, pl, po))
+
+        att = parallel.HeadSplitAttention(HQ, HKV, local=local, merge=merge)
+        pl_ = att.plan
+        assert (pl_["shares"], pl_["kv0"], pl_["share"]) == (world // HKV, rank // (world // HKV), rank % (world // HKV))
+        my_cache = cache[:, :, :, pl_["kv0"]:pl_["kv1"]].contiguous()
+        ip, ix, lp = parallel.split_page_table(indptr, indices, last, P, pl_["share"], pl_["shares"])
+        out = att.forward(q, my_cache, ip, ix, lp)
+        ret[rank] = float((out.float() - ref.float()).abs().max() / ref.float().square().mean().sqrt())
+    finally:
+        dist.destroy_process_group()
+
+
+def test_attention_pages_split_inside_kv_heads_four_ranks_gloo():
+    """4 ranks, 2 KV heads: two ranks share each KV head and split every sequence's pages; the all-gathered partials
+    merged by log-sum-exp equal the unsplit golden on every rank"""
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    ret = mp.Manager().dict()
+    mp.spawn(_attn_worker, args=(4, port, ret), nprocs=4, join=True)
+    assert len(ret) == 4 and all(v <= 1e-2 for v in ret.values()), dict(ret)
+
+
+def test_attention_split_plan_and_page_shares():
+    assert parallel.attention_split(16, 2, 2, 1) == dict(kv0=1, kv1=2, q0=8, q1=16, share=0, shares=1)
+    assert parallel.attention_split(16, 2, 8, 5) == dict(kv0=1, kv1=2, q0=8, q1=16, share=1, shares=4)
+    assert parallel.attention_split(24, 4, 2, 0) == dict(kv0=0, kv1=2, q0=0, q1=12, share=0, shares=1)
+    with pytest.raises(ValueError):
+        parallel.attention_split(16, 2, 3, 0)
+    indptr = torch.tensor([0, 5, 5, 6], dtype=torch.int32)
+    indices = torch.tensor([9, 8, 7, 6, 5, 4], dtype=torch.int32)
+    last = torch.tensor([3, 0, 11], dtype=torch.int32)
+    got = [parallel.split_page_table(indptr, indices, last, 16, s, 2) for s in range(2)]
+    assert got[0][0].tolist() == [0, 2, 2, 2] and got[0][1].tolist() == [9, 8] and got[0][2].tolist() == [16, 0, 16]
+    assert got[1][0].tolist() == [0, 3, 3, 4] and got[1][1].tolist() == [7, 6, 5, 4] and got[1][2].tolist() == [3, 0, 11]
