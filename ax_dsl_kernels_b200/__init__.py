@@ -10,8 +10,8 @@ from .attention import (kv_write, mrope_cos_sin, paged_attention_decode, paged_a
                         rope_cos_sin)
 from .gdn import gdn_chunk_prefill, gdn_conv1d_silu, gdn_recurrent_step  # noqa: F401
 from .moe import (linear, moe_block, moe_combine, moe_experts, moe_permute, moe_pre, moe_slots_px,  # noqa: F401
-                  prepare_moe_weights, route, tile_scales)
+                  prepare_moe_weights, qwen3_moe, route, tile_scales)
 
 __all__ = ["run", "roles", "io_table", "workspace_bytes", "device_status", "Q35Error", "route", "moe_pre",
-           "moe_experts", "moe_slots_px", "moe_combine", "moe_permute", "moe_block", "prepare_moe_weights", "tile_scales", "linear",
+           "moe_experts", "moe_slots_px", "moe_combine", "moe_permute", "moe_block", "qwen3_moe", "prepare_moe_weights", "tile_scales", "linear",
            "paged_attention_decode", "paged_attention_prefill", "kv_write", "gdn_recurrent_step", "gdn_conv1d_silu", "gdn_chunk_prefill"]

@@ -17,7 +17,7 @@ MAX_DIMS = 6
 U8, F32, I32, BF16, F16, E4M3, FP4 = 1, 3, 6, 9, 10, 11, 15
 _DTYPE_CODE = {
     torch.uint8: U8, torch.float32: F32, torch.int32: I32, torch.bfloat16: BF16, torch.float16: F16,
-    torch.float8_e4m3fn: E4M3,
+    torch.float8_e4m3fn: E4M3, torch.int8: U8,  # int8 KV rows travel as bytes (the AX table has no int8 code)
 }
 for _n, _c in (("float8_e8m0fnu", U8), ("float4_e2m1fn_x2", U8)):  # scale / packed-FP4 views are raw bytes
     if hasattr(torch, _n):

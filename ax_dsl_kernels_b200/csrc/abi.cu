@@ -180,16 +180,16 @@ static const RoleDef kRoles[] = {
      R"({"in":[["base","bf16","[T,H]"],["loc","i32","[K,T]"],["sout","bf16|f32","[R,H]"]],"out":[["out","bf16","[T,H]"]]})",
      run_moe_combine},
     {"attn.paged_decode",
-     R"({"in":[["q","bf16","[B,HQ,D]"],["paged_kv_cache","bf16|e4m3","[pages,2,P,HKV,D]"],["indptr","i32","[B+1]"],["indices","i32","[N]"],["last_page_len","i32","[B]"],["sm_scale","f32","[1] optional"],["kv_scale","f32","[2,HKV] optional"],["k_new","bf16","[B,HKV,D] optional"],["v_new","bf16","[B,HKV,D] optional"],["workspace","u8","[*]"]],"out":[["out","bf16","[B,HQ,D]"],["part_m","f32","[B,HQ] optional with part_l, part_o instead of out: the unnormalised result for attn.lse_merge"],["part_l","f32","[B,HQ]"],["part_o","f32","[B,HQ,D]"]]})",
+     R"({"in":[["q","bf16","[B,HQ,D]"],["paged_kv_cache","bf16|e4m3","[pages,2,P,HKV,D]"],["indptr","i32","[B+1]"],["indices","i32","[N]"],["last_page_len","i32","[B]"],["sm_scale","f32","[1] optional"],["kv_scale","f32","[2,HKV] optional"],["paged_kv_scale","bf16","[pages,2,P,HKV] optional: int8 cache bound as bytes, one scale per row and head"],["k_new","bf16","[B,HKV,D] optional"],["v_new","bf16","[B,HKV,D] optional"],["workspace","u8","[*]"]],"out":[["out","bf16","[B,HQ,D]"],["part_m","f32","[B,HQ] optional with part_l, part_o instead of out: the unnormalised result for attn.lse_merge"],["part_l","f32","[B,HQ]"],["part_o","f32","[B,HQ,D]"],["part_packed","f32","[B,HQ,D+2] optional instead of the three: o, m, l of a row side by side, one message per rank"]]})",
      run_attn_paged_decode},
     {"attn.lse_merge",
-     R"({"in":[["part_m","f32","[G,B,HQ]"],["part_l","f32","[G,B,HQ]"],["part_o","f32","[G,B,HQ,D]"]],"out":[["out","bf16","[B,HQ,D]"]]})",
+     R"({"in":[["part_m","f32","[G,B,HQ] optional"],["part_l","f32","[G,B,HQ] optional"],["part_o","f32","[G,B,HQ,D] optional"],["packed","f32","[R,B,Hq,D+2] optional instead of the three: the all-gathered part_packed blocks of R ranks, KV group major"]],"out":[["out","bf16","[B,HQ,D]"]]})",
      run_attn_lse_merge},
     {"attn.kv_write",
-     R"({"in":[["k_new","bf16","[B,HKV,D]"],["v_new","bf16","[B,HKV,D]"],["cache_location","i32","[B,2]"],["kv_scale","f32","[2,HKV] optional"]],"out":[["paged_kv_cache","bf16|e4m3","[pages,2,P,HKV,D]"]]})",
+     R"({"in":[["k_new","bf16","[B,HKV,D]"],["v_new","bf16","[B,HKV,D]"],["cache_location","i32","[B,2]"],["kv_scale","f32","[2,HKV] optional"]],"out":[["paged_kv_cache","bf16|e4m3","[pages,2,P,HKV,D]"],["paged_kv_scale","bf16","[pages,2,P,HKV] optional: int8 cache bound as bytes, the rows' scales land here"]]})",
      run_attn_kv_write},
     {"attn.paged_prefill",
-     R"({"in":[["q","bf16","[T,HQ,D]"],["paged_kv_cache","bf16","[pages,2,P,HKV,D]"],["qo_indptr","i32","[B+1]"],["indptr","i32","[B+1]"],["indices","i32","[N]"],["last_page_len","i32","[B]"],["sm_scale","f32","[1] optional"],["k_new","bf16","[T,HKV,D] optional: written into the cache first"],["v_new","bf16","[T,HKV,D] optional"]],"out":[["out","bf16","[T,HQ,D]"]]})",
+     R"({"in":[["q","bf16","[T,HQ,D]"],["paged_kv_cache","bf16|e4m3","[pages,2,P,HKV,D]"],["qo_indptr","i32","[B+1]"],["indptr","i32","[B+1]"],["indices","i32","[N]"],["last_page_len","i32","[B]"],["sm_scale","f32","[1] optional"],["kv_scale","f32","[2,HKV] optional: FP8 cache with per-head scales; absent: the stored x 8 form"],["k_new","bf16","[T,HKV,D] optional: written into the cache first"],["v_new","bf16","[T,HKV,D] optional"]],"out":[["out","bf16","[T,HQ,D]"]]})",
      run_attn_paged_prefill},
     {"gdn.step",
      R"({"in":[["q","bf16","[B,NK,DK]"],["k","bf16","[B,NK,DK]"],["v","bf16","[B,NV,DV]"],["g","f32","[B,NV]"],["beta","bf16","[B,NV]"],["state_in","f32","[B,NV,DK,DV]"]],"out":[["o","bf16","[B,NV,DV]"],["state_out","f32","[B,NV,DK,DV]"]]})",

@@ -39,12 +39,14 @@ struct AttnArgs {
   const int* last_page_len;
   const float* sm_scale;   // optional [1]
   const float* kv_scale;   // optional [2, HKV] (FP8 cache)
+  const __nv_bfloat16* row_scale;  // int8 cache: [pages, 2, P, HKV] one scale per cached row and head
   const __nv_bfloat16* k_new;  // optional [B, HKV, D]
   const __nv_bfloat16* v_new;
   __nv_bfloat16* out;   // [B, HQ, D]
   // optional: the merged but UNNORMALISED result per (sequence, query head) instead of `out`, for a merge across
   // devices that each hold a part of the keys: maximum (log2 domain), sum of weights, weighted values
-  float* lse_m; float* lse_l; float* lse_o;   // [B, HQ], [B, HQ], [B, HQ, D]
+  float* lse_m; float* lse_l; float* lse_o;   // [B, HQ], [B, HQ], [B, HQ, D] -- or one packed [B, HQ, D + 2] block
+  int lse_os, lse_ms;                         // floats between rows of lse_o, between entries of lse_m / lse_l
   int B, HQ, HKV, G, P, num_pages, n_indices, n_cta;
   // workspace
   AttnPlan* plan;
@@ -97,8 +99,12 @@ __global__ void __launch_bounds__(1024) attn_plan_kernel(AttnArgs a) {
   }
 }
 
-template <int D, bool FP8>
+// KVF: cache element format.  0 = bf16, 1 = FP8 E4M3 (one scale per head or the constant 1 / 8), 2 = int8 with a bf16
+// scale per cached row and head (kv_quant_row, models/qwen38_27b/decode/q35_group.py:198-205).  The two one-byte
+// formats share the byte-wise fragment paths; they differ in the conversion to f16 and in where the scale enters.
+template <int D, int KVF>
 struct AttnCfg {
+  static constexpr bool FP8 = KVF != 0;
   static constexpr int ELT = FP8 ? 1 : 2;
   static constexpr int STAGES = FP8 ? 6 : 3;    // same bytes in flight for both cache types
   static constexpr int ROWB = D * ELT;            // bytes of one key row of one head
@@ -116,11 +122,29 @@ __device__ __forceinline__ uint32_t cvt_e4m3x2_f16x2(uint32_t two_bytes) {
   return d;
 }
 
-template <int D, bool FP8>
+// two one-byte FP8 cache elements (bytes I0, I1 of x) as f16x2
+template <int I0, int I1>
+__device__ __forceinline__ uint32_t cvt_kv(uint32_t x) {
+  return cvt_e4m3x2_f16x2(__byte_perm(x, 0, 0x4400 | I0 | (I1 << 4)));
+}
+
+// int8 bytes I0, I1 of xs (= x ^ 0x80808080) times their rows' scales, rounded to bf16 -- bf16(int8 * scale), the
+// reference's page dequantisation (kv_page, models/qwen38_27b/decode/q35_group.py:208-222), exactly: 0x4B000000 | b is
+// the float 2^23 + b, the fused multiply-add against -(2^23 + 128) * s leaves (b - 128) * s, a 15-bit product that
+// fp32 holds exactly, and one cvt.rn rounds the pair.
+template <int I0, int I1>
+__device__ __forceinline__ uint32_t cvt_s8x2_bf16x2(uint32_t xs, float s0, float s1) {
+  const float f0 = __uint_as_float(__byte_perm(xs, 0x4B000000u, 0x7540 | I0));
+  const float f1 = __uint_as_float(__byte_perm(xs, 0x4B000000u, 0x7540 | I1));
+  return pack_bf16(fmaf(f0, s0, -8388736.f * s0), fmaf(f1, s1, -8388736.f * s1));
+}
+
+template <int D, int KVF>
 __global__ void __launch_bounds__(128, 1) attn_decode_kernel(const AttnArgs a) {
   pdl_wait();
   pdl_launch();
-  using C = AttnCfg<D, FP8>;
+  using C = AttnCfg<D, KVF>;
+  constexpr bool FP8 = C::FP8;
   constexpr int AT_STAGES = C::STAGES;
   extern __shared__ __align__(128) uint8_t smem[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -170,14 +194,44 @@ __global__ void __launch_bounds__(128, 1) attn_decode_kernel(const AttnArgs a) {
         for (int ks = 0; ks < D / 16; ++ks) {
           uint2 raw = make_uint2(0u, 0u);
           if (hv) raw = *reinterpret_cast<const uint2*>(qp + ks * 16 + 4 * c);
-          qf[ks][0] = pack_f16(bf16lo(raw.x), bf16hi(raw.x));
-          qf[ks][1] = pack_f16(bf16lo(raw.y), bf16hi(raw.y));
+          if constexpr (KVF == 2) {  // bf16 MMAs: the query stays bf16
+            qf[ks][0] = raw.x;
+            qf[ks][1] = raw.y;
+          } else {
+            qf[ks][0] = pack_f16(bf16lo(raw.x), bf16hi(raw.x));
+            qf[ks][1] = pack_f16(bf16lo(raw.y), bf16hi(raw.y));
+          }
         }
         k_mul = a.kv_scale ? a.kv_scale[kvh] : 0.125f;
         v_mul = a.kv_scale ? a.kv_scale[a.HKV + kvh] : 0.125f;
       }
     }
+    if constexpr (KVF == 2) k_mul = v_mul = 1.f;  // the rows are dequantised with their own scales below
     const float seg_scale = scale_log2 * k_mul;
+    // int8 cache: the bf16 row scales this lane's fragments need -- K rows r and r + 8 of the warp's 16 keys, V rows
+    // 2c, 2c + 1, 2c + 8, 2c + 9 -- fetched two tiles ahead into registers (a plain load at the point of use would
+    // stall a warp that has no other work to hide it).  Rows past the context read as scale 0 (their bytes may be
+    // anything, and 0 * scale must not become NaN).
+    auto load_scales = [&](int t) -> uint3 {
+      uint3 v = make_uint3(0u, 0u, 0u);
+      if constexpr (KVF == 2) {
+        const int kk = t * AT_TILE + warp * AT_WKEYS;
+        if (t < t_end && kk < ctx) {
+          const int pl = kk / a.P, ro = kk % a.P, valid = ctx - kk;
+          int page = a.indices[page0 + pl];
+          if (page < 0 || page >= a.num_pages) page = 0;
+          const unsigned short* sp = reinterpret_cast<const unsigned short*>(a.row_scale);
+          const size_t k0 = ((size_t(page) * 2 + 0) * a.P + ro) * a.HKV + kvh;
+          const size_t v0 = ((size_t(page) * 2 + 1) * a.P + ro) * a.HKV + kvh;
+          auto at = [&](size_t base, int row) -> uint32_t { return row < valid ? sp[base + size_t(row) * a.HKV] : 0u; };
+          v.x = at(k0, r) | (at(k0, r + 8) << 16);
+          v.y = at(v0, 2 * c) | (at(v0, 2 * c + 1) << 16);
+          v.z = at(v0, 2 * c + 8) | (at(v0, 2 * c + 9) << 16);
+        }
+      }
+      return v;
+    };
+
     float oacc[D / 16][4];
 #pragma unroll
     for (int mt = 0; mt < D / 16; ++mt) oacc[mt][0] = oacc[mt][1] = oacc[mt][2] = oacc[mt][3] = 0.f;
@@ -209,9 +263,11 @@ __global__ void __launch_bounds__(128, 1) attn_decode_kernel(const AttnArgs a) {
 
 #pragma unroll
     for (int p = 0; p < AT_STAGES - 1; ++p) issue(t_begin + p);
+    uint3 rs_cur = load_scales(t_begin), rs_n1 = load_scales(t_begin + 1), rs_n2 = make_uint3(0u, 0u, 0u);
 
     for (int t = t_begin; t < t_end; ++t) {
       issue(t + AT_STAGES - 1);
+      rs_n2 = load_scales(t + 2);
       cp_async_wait<AT_STAGES - 1>();
       __syncwarp();
       const int kk = t * AT_TILE + warp * AT_WKEYS;
@@ -243,10 +299,21 @@ __global__ void __launch_bounds__(128, 1) attn_decode_kernel(const AttnArgs a) {
               const int ch = 2 * kp + (lane >> 4);
               uint32_t r0, r1, r2, r3;
               ldmatrix_x4(rowa + ((ch ^ (key & 7)) << 4), r0, r1, r2, r3);
-              mma_f16_16816(sacc[0], cvt_e4m3x2_f16x2(r0), cvt_e4m3x2_f16x2(r1), cvt_e4m3x2_f16x2(r0 >> 16),
-                            cvt_e4m3x2_f16x2(r1 >> 16), qf[2 * kp][0], qf[2 * kp][1]);
-              mma_f16_16816(sacc[1], cvt_e4m3x2_f16x2(r2), cvt_e4m3x2_f16x2(r3), cvt_e4m3x2_f16x2(r2 >> 16),
-                            cvt_e4m3x2_f16x2(r3 >> 16), qf[2 * kp + 1][0], qf[2 * kp + 1][1]);
+              if constexpr (KVF == 2) {  // rows r (r0, r2) and r + 8 (r1, r3) of the tile, each with its own scale
+                const float s0 = bf16lo(rs_cur.x), s1 = bf16hi(rs_cur.x);
+                r0 ^= 0x80808080u; r1 ^= 0x80808080u; r2 ^= 0x80808080u; r3 ^= 0x80808080u;
+                mma_bf16_16816(sacc[0], cvt_s8x2_bf16x2<0, 1>(r0, s0, s0), cvt_s8x2_bf16x2<0, 1>(r1, s1, s1),
+                               cvt_s8x2_bf16x2<2, 3>(r0, s0, s0), cvt_s8x2_bf16x2<2, 3>(r1, s1, s1), qf[2 * kp][0],
+                               qf[2 * kp][1]);
+                mma_bf16_16816(sacc[1], cvt_s8x2_bf16x2<0, 1>(r2, s0, s0), cvt_s8x2_bf16x2<0, 1>(r3, s1, s1),
+                               cvt_s8x2_bf16x2<2, 3>(r2, s0, s0), cvt_s8x2_bf16x2<2, 3>(r3, s1, s1), qf[2 * kp + 1][0],
+                               qf[2 * kp + 1][1]);
+              } else {
+                mma_f16_16816(sacc[0], cvt_kv<0, 1>(r0), cvt_kv<0, 1>(r1), cvt_kv<2, 3>(r0), cvt_kv<2, 3>(r1),
+                              qf[2 * kp][0], qf[2 * kp][1]);
+                mma_f16_16816(sacc[1], cvt_kv<0, 1>(r2), cvt_kv<0, 1>(r3), cvt_kv<2, 3>(r2), cvt_kv<2, 3>(r3),
+                              qf[2 * kp + 1][0], qf[2 * kp + 1][1]);
+              }
             }
           }
         }
@@ -303,8 +370,19 @@ __global__ void __launch_bounds__(128, 1) attn_decode_kernel(const AttnArgs a) {
           // transposed b16 loads keep byte PAIRS (d, d+1) together: a lane gets {V[2c][2r], V[2c][2r+1], V[2c+1][2r],
           // V[2c+1][2r+1]}; bytes (0,2) / (1,3) are the key pairs of channels 2r / 2r+1.  So mma row r holds channel
           // 16 mt + 2r and mma row r + 8 holds channel 16 mt + 2r + 1 (undone when the partial is written).
-          const uint32_t pb0 = movmatrix_trans(pack_f16(p0, p1));
-          const uint32_t pb1 = movmatrix_trans(pack_f16(p2, p3));
+          // P: f16 for the FP8 cache; for the int8 cache (bf16 MMAs on the rounded rows) two bf16 terms as in the
+          // bf16 path
+          uint32_t pb0, pb1, pl0 = 0u, pl1 = 0u;
+          if constexpr (KVF == 2) {
+            const float h0 = round_bf16(p0), h1 = round_bf16(p1), h2 = round_bf16(p2), h3 = round_bf16(p3);
+            pb0 = movmatrix_trans(pack_bf16(h0, h1));
+            pb1 = movmatrix_trans(pack_bf16(h2, h3));
+            pl0 = movmatrix_trans(pack_bf16(p0 - h0, p1 - h1));
+            pl1 = movmatrix_trans(pack_bf16(p2 - h2, p3 - h3));
+          } else {
+            pb0 = movmatrix_trans(pack_f16(p0, p1));
+            pb1 = movmatrix_trans(pack_f16(p2, p3));
+          }
           const int key = lane & 15;
           const uint32_t rowa = st + C::KV_BYTES + key * C::ROWB;
 #pragma unroll
@@ -312,16 +390,28 @@ __global__ void __launch_bounds__(128, 1) attn_decode_kernel(const AttnArgs a) {
             const int ch = 2 * mp + (lane >> 4);
             uint32_t r0, r1, r2, r3;  // (keys 0-7, chunk 2mp) (keys 8-15, 2mp) (keys 0-7, 2mp+1) (keys 8-15, 2mp+1)
             ldmatrix_x4_trans(rowa + ((ch ^ (key & 7)) << 4), r0, r1, r2, r3);
-            mma_f16_16816(oacc[2 * mp], cvt_e4m3x2_f16x2(__byte_perm(r0, 0, 0x4420)),
-                          cvt_e4m3x2_f16x2(__byte_perm(r0, 0, 0x4431)), cvt_e4m3x2_f16x2(__byte_perm(r1, 0, 0x4420)),
-                          cvt_e4m3x2_f16x2(__byte_perm(r1, 0, 0x4431)), pb0, pb1);
-            mma_f16_16816(oacc[2 * mp + 1], cvt_e4m3x2_f16x2(__byte_perm(r2, 0, 0x4420)),
-                          cvt_e4m3x2_f16x2(__byte_perm(r2, 0, 0x4431)), cvt_e4m3x2_f16x2(__byte_perm(r3, 0, 0x4420)),
-                          cvt_e4m3x2_f16x2(__byte_perm(r3, 0, 0x4431)), pb0, pb1);
+            if constexpr (KVF == 2) {  // bytes (0, 2) / (1, 3): keys 2c, 2c + 1 (r0, r2) and 2c + 8, 2c + 9 (r1, r3)
+              const float va = bf16lo(rs_cur.y), vb = bf16hi(rs_cur.y), vc = bf16lo(rs_cur.z), vd = bf16hi(rs_cur.z);
+              r0 ^= 0x80808080u; r1 ^= 0x80808080u; r2 ^= 0x80808080u; r3 ^= 0x80808080u;
+              const uint32_t a0 = cvt_s8x2_bf16x2<0, 2>(r0, va, vb), a1 = cvt_s8x2_bf16x2<1, 3>(r0, va, vb);
+              const uint32_t a2 = cvt_s8x2_bf16x2<0, 2>(r1, vc, vd), a3 = cvt_s8x2_bf16x2<1, 3>(r1, vc, vd);
+              mma_bf16_16816(oacc[2 * mp], a0, a1, a2, a3, pb0, pb1);
+              mma_bf16_16816(oacc[2 * mp], a0, a1, a2, a3, pl0, pl1);
+              const uint32_t b0 = cvt_s8x2_bf16x2<0, 2>(r2, va, vb), b1 = cvt_s8x2_bf16x2<1, 3>(r2, va, vb);
+              const uint32_t b2 = cvt_s8x2_bf16x2<0, 2>(r3, vc, vd), b3 = cvt_s8x2_bf16x2<1, 3>(r3, vc, vd);
+              mma_bf16_16816(oacc[2 * mp + 1], b0, b1, b2, b3, pb0, pb1);
+              mma_bf16_16816(oacc[2 * mp + 1], b0, b1, b2, b3, pl0, pl1);
+            } else {
+              mma_f16_16816(oacc[2 * mp], cvt_kv<0, 2>(r0), cvt_kv<1, 3>(r0), cvt_kv<0, 2>(r1), cvt_kv<1, 3>(r1), pb0, pb1);
+              mma_f16_16816(oacc[2 * mp + 1], cvt_kv<0, 2>(r2), cvt_kv<1, 3>(r2), cvt_kv<0, 2>(r3), cvt_kv<1, 3>(r3), pb0,
+                            pb1);
+            }
           }
         }
       }
       __syncwarp();
+      rs_cur = rs_n1;
+      rs_n1 = rs_n2;
     }
     cp_async_wait<0>();
 
@@ -414,8 +504,9 @@ __global__ void __launch_bounds__(D / 2) attn_merge_kernel(const AttnArgs a) {
     o1 = o1 * fa + __bfloat162float(vp[2 * tid + 1]) * fb;
   }
   if (a.lse_o) {
-    if (tid == 0) { a.lse_m[size_t(b) * a.HQ + h] = M; a.lse_l[size_t(b) * a.HQ + h] = L; }
-    *reinterpret_cast<float2*>(a.lse_o + (size_t(b) * a.HQ + h) * D + 2 * tid) = make_float2(o0, o1);
+    const size_t row = size_t(b) * a.HQ + h;
+    if (tid == 0) { a.lse_m[row * a.lse_ms] = M; a.lse_l[row * a.lse_ms] = L; }
+    *reinterpret_cast<float2*>(a.lse_o + row * a.lse_os + 2 * tid) = make_float2(o0, o1);
     return;
   }
   const float inv = L > 0.f ? 1.f / L : 0.f;
@@ -445,8 +536,46 @@ __global__ void attn_lse_merge_kernel(const float* __restrict__ pm, const float*
   }
 }
 
+// The same merge straight from the all-gathered messages: packed [R, B, Hq, D + 2] holds rank r's unnormalised result
+// (o | m | l per row) for ITS Hq query heads; ranks are ordered KV group major (r = group * S + share), so output head
+// h = group * Hq + hl merges the S rows (group * S + g, b, hl).
+__global__ void attn_lse_merge_packed_kernel(const float* __restrict__ packed, __nv_bfloat16* __restrict__ out, int S,
+                                             int B, int Hq, int HQ, int D) {
+  const int b = blockIdx.x / HQ, h = blockIdx.x % HQ, grp = h / Hq, hl = h % Hq;
+  const size_t W = size_t(D) + 2, rank_stride = size_t(B) * Hq * W;
+  const float* base = packed + size_t(grp) * S * rank_stride + (size_t(b) * Hq + hl) * W;
+  float M = -INFINITY;
+  for (int g = 0; g < S; ++g)
+    if (base[g * rank_stride + D + 1] > 0.f) M = fmaxf(M, base[g * rank_stride + D]);
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float L = 0.f, o = 0.f;
+    for (int g = 0; g < S; ++g) {
+      const float l = base[g * rank_stride + D + 1];
+      if (!(l > 0.f)) continue;
+      const float f = exp2f(base[g * rank_stride + D] - M);
+      L += l * f;
+      o += base[g * rank_stride + d] * f;
+    }
+    out[(size_t(b) * HQ + h) * D + d] = __float2bfloat16_rn(L > 0.f ? o / L : 0.f);
+  }
+}
+
 int run_attn_lse_merge(Call& c) {
-  Tensor pm, pl, po, out;
+  Tensor pm, pl, po, out, pk;
+  Q35_TRY(c.get("packed", M(Q35_F32), &pk, false));
+  if (pk.present) {
+    Q35_TRY(c.get("out", M(Q35_BF16), &out));
+    Q35_REQUIRE(pk.nd == 4 && out.nd == 3, Q35_ERR_SHAPE, "attn.lse_merge: packed [R, B, Hq, D + 2], out [B, HQ, D]");
+    const int64_t R = pk.s[0], B = pk.s[1], Hq = pk.s[2], D = pk.s[3] - 2, HQ = out.s[1];
+    Q35_REQUIRE(D > 0 && Hq > 0 && out.s[0] == B && out.s[2] == D && HQ % Hq == 0 && R % (HQ / Hq) == 0, Q35_ERR_SHAPE,
+                "attn.lse_merge: R ranks must be (HQ / Hq) KV groups times an equal number of page shares");
+    c.ws_need = 0;
+    if (c.dry || B * HQ == 0) return 0;
+    attn_lse_merge_packed_kernel<<<unsigned(B * HQ), 128, 0, c.stream>>>(pk.as<float>(), out.as<__nv_bfloat16>(),
+                                                                        int(R / (HQ / Hq)), int(B), int(Hq), int(HQ), int(D));
+    Q35_CUDA_LAUNCH_CHECK("attn.lse_merge");
+    return 0;
+  }
   Q35_TRY(c.get("part_m", M(Q35_F32), &pm));
   Q35_TRY(c.get("part_l", M(Q35_F32), &pl));
   Q35_TRY(c.get("part_o", M(Q35_F32), &po));
@@ -481,12 +610,41 @@ __global__ void attn_kv_write_kernel(const __nv_bfloat16* __restrict__ k_new, co
     const __nv_bfloat16 val = kv ? v_new[size_t(b) * n + j] : k_new[size_t(b) * n + j];
     const size_t dst = ((size_t(page) * 2 + kv) * P + off) * n + j;
     if (fp8) {
-      const float sc = kv_scale ? 1.f / kv_scale[kv * HKV + j / D] : 8.f;
-      static_cast<__nv_fp8_e4m3*>(cache)[dst] = __nv_fp8_e4m3(__bfloat162float(val) * sc);
+      const float x = __bfloat162float(val);  // per-head form: a true division, as the golden's
+      static_cast<__nv_fp8_e4m3*>(cache)[dst] = __nv_fp8_e4m3(kv_scale ? x / kv_scale[kv * HKV + j / D] : x * 8.f);
     } else {
       static_cast<__nv_bfloat16*>(cache)[dst] = val;
     }
   }
+}
+
+// int8 rows with one bf16 scale per row and head (kv_quant_row, models/qwen38_27b/decode/q35_group.py:198-205):
+// amax over the head's D values (at least 1e-5), s = bf16(amax * bf16(1 / 127)), q = round(bf16(x * bf16(1 / s))).
+// One warp per (sequence, K or V, head).
+__global__ void attn_kv_write_int8_kernel(const __nv_bfloat16* __restrict__ k_new, const __nv_bfloat16* __restrict__ v_new,
+                                          const int* __restrict__ loc, int8_t* cache, __nv_bfloat16* scales, int B,
+                                          int HKV, int D, int P, int num_pages, int* status) {
+  const int w = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (w >= B * 2 * HKV) return;
+  const int b = w / (2 * HKV), kv = (w / HKV) & 1, h = w % HKV;
+  const int page = loc[2 * b], off = loc[2 * b + 1];
+  if (page < 0 || page >= num_pages || off < 0 || off >= P) {
+    if (lane == 0) atomicOr(status, DS_BAD_PAGE);
+    return;
+  }
+  const __nv_bfloat16* src = (kv ? v_new : k_new) + (size_t(b) * HKV + h) * D;
+  float amax = 0.f;
+  for (int i = lane; i < D; i += 32) amax = fmaxf(amax, fabsf(__bfloat162float(src[i])));
+  for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  amax = fmaxf(amax, round_bf16(1e-5f));
+  const float sc = round_bf16(amax * round_bf16(1.f / 127.f));
+  const float inv = round_bf16(1.f / sc);
+  const size_t row = (size_t(page) * 2 + kv) * P + off;
+  for (int i = lane; i < D; i += 32) {
+    const float qv = rintf(round_bf16(__bfloat162float(src[i]) * inv));
+    cache[(row * HKV + h) * D + i] = int8_t(fminf(fmaxf(qv, -127.f), 127.f));
+  }
+  if (lane == 0) scales[row * HKV + h] = __float2bfloat16_rn(sc);
 }
 
 int run_attn_kv_write(Call& c) {
@@ -502,8 +660,20 @@ int run_attn_kv_write(Call& c) {
   Q35_REQUIRE(k.s[1] == HKV && k.s[2] == D && v.numel() == k.numel() && loc.numel() == 2 * B, Q35_ERR_SHAPE,
               "attn.kv_write: shapes");
   Q35_REQUIRE(!sc.present || sc.numel() == 2 * HKV, Q35_ERR_SHAPE, "attn.kv_write: kv_scale [2, HKV]");
+  Tensor rsc;
+  Q35_TRY(c.get("paged_kv_scale", M(Q35_BF16), &rsc, false));
+  Q35_REQUIRE(!rsc.present || (cache.dtype != Q35_BF16 && !sc.present && rsc.numel() == cache.s[0] * 2 * P * HKV),
+              Q35_ERR_SHAPE, "attn.kv_write: paged_kv_scale [pages, 2, P, HKV] bf16 goes with an int8 cache");
   c.ws_need = 0;
   if (c.dry || B == 0) return 0;
+  if (rsc.present) {
+    const int64_t warps = B * 2 * HKV;
+    attn_kv_write_int8_kernel<<<unsigned((warps + 3) / 4), 128, 0, c.stream>>>(
+        k.as<__nv_bfloat16>(), v.as<__nv_bfloat16>(), loc.as<int>(), static_cast<int8_t*>(cache.p),
+        rsc.as<__nv_bfloat16>(), int(B), int(HKV), int(D), int(P), int(cache.s[0]), device_status_ptr());
+    Q35_CUDA_LAUNCH_CHECK("attn.kv_write int8");
+    return 0;
+  }
   attn_kv_write_kernel<<<unsigned(B), 256, 0, c.stream>>>(
       k.as<__nv_bfloat16>(), v.as<__nv_bfloat16>(), loc.as<int>(), sc.present ? sc.as<float>() : nullptr, cache.p,
       int(B), int(HKV), int(D), int(P), int(cache.s[0]), cache.dtype != Q35_BF16, device_status_ptr());
@@ -511,14 +681,14 @@ int run_attn_kv_write(Call& c) {
   return 0;
 }
 
-template <int D, bool FP8>
+template <int D, int KVF>
 static int launch_attn(const AttnArgs& a, cudaStream_t stream) {
-  using C = AttnCfg<D, FP8>;
-  Q35_TRY(ensure_dynamic_smem(reinterpret_cast<const void*>(attn_decode_kernel<D, FP8>), C::SMEM));
+  using C = AttnCfg<D, KVF>;
+  Q35_TRY(ensure_dynamic_smem(reinterpret_cast<const void*>(attn_decode_kernel<D, KVF>), C::SMEM));
   Q35_REQUIRE(a.status != nullptr, Q35_ERR_CUDA, "attention decode: no device status word");
   launch_pdl(attn_plan_kernel, dim3(1), dim3(1024), 0, stream, a);
   Q35_CUDA_LAUNCH_CHECK("attn plan");
-  launch_pdl(attn_decode_kernel<D, FP8>, dim3(unsigned(a.n_cta)), dim3(128), C::SMEM, stream, a);
+  launch_pdl(attn_decode_kernel<D, KVF>, dim3(unsigned(a.n_cta)), dim3(128), C::SMEM, stream, a);
   Q35_CUDA_LAUNCH_CHECK("attn decode");
   launch_pdl(attn_merge_kernel<D>, dim3(unsigned(a.B * a.HQ)), dim3(D / 2), 0, stream, a);
   Q35_CUDA_LAUNCH_CHECK("attn merge");
@@ -542,7 +712,11 @@ int run_attn_paged_decode(Call& c) {
   Q35_TRY(c.get("part_o", M(Q35_F32), &lo, false));
   Q35_REQUIRE(lm.present == lo.present && ll.present == lo.present, Q35_ERR_MISSING,
               "attn.paged_decode: part_m, part_l and part_o go together");
-  Q35_TRY(c.get("out", M(Q35_BF16), &out, !lo.present));
+  Tensor lpk;
+  Q35_TRY(c.get("part_packed", M(Q35_F32), &lpk, false));
+  Q35_REQUIRE(!(lpk.present && lo.present), Q35_ERR_SHAPE, "attn.paged_decode: part_packed or part_m / part_l / part_o");
+  const bool partial = lo.present || lpk.present;
+  Q35_TRY(c.get("out", M(Q35_BF16), &out, !partial));
   Q35_REQUIRE(q.nd == 3 && cache.nd == 5 && cache.s[1] == 2, Q35_ERR_SHAPE,
               "attn.paged_decode: q [B, HQ, D], paged_kv_cache [pages, 2, P, HKV, D]");
   const int64_t B = q.s[0], HQ = q.s[1], D = q.s[2], P = cache.s[2], HKV = cache.s[3];
@@ -553,14 +727,20 @@ int run_attn_paged_decode(Call& c) {
   Q35_REQUIRE(D == 64 || D == 128 || D == 256, Q35_ERR_UNSUPPORTED, "attn.paged_decode: head_dim must be 64/128/256");
   Q35_REQUIRE(P % 16 == 0 && P >= 16, Q35_ERR_UNSUPPORTED, "attn.paged_decode: page size must be a multiple of 16");
   Q35_REQUIRE(indptr.numel() == B + 1 && lpl.numel() >= B, Q35_ERR_SHAPE, "attn.paged_decode: indptr [B+1], last_page_len [B]");
-  Q35_REQUIRE(lo.present || out.numel() == B * HQ * D, Q35_ERR_SHAPE, "attn.paged_decode: out [B, HQ, D]");
+  Q35_REQUIRE(partial || out.numel() == B * HQ * D, Q35_ERR_SHAPE, "attn.paged_decode: out [B, HQ, D]");
+  Q35_REQUIRE(!lpk.present || lpk.numel() == B * HQ * (D + 2), Q35_ERR_SHAPE,
+              "attn.paged_decode: part_packed [B, HQ, D + 2]");
   Q35_REQUIRE(!lo.present || (lo.numel() == B * HQ * D && lm.numel() == B * HQ && ll.numel() == B * HQ), Q35_ERR_SHAPE,
               "attn.paged_decode: part_m / part_l [B, HQ], part_o [B, HQ, D]");
   Q35_REQUIRE(kn.present == vn.present, Q35_ERR_MISSING, "attn.paged_decode: k_new and v_new go together");
   Q35_REQUIRE(!kn.present || (kn.numel() == B * HKV * D && vn.numel() == B * HKV * D), Q35_ERR_SHAPE,
               "attn.paged_decode: k_new / v_new [B, HKV, D]");
   Q35_REQUIRE(!kvs.present || kvs.numel() == 2 * HKV, Q35_ERR_SHAPE, "attn.paged_decode: kv_scale [2, HKV]");
+  Tensor rsc;
+  Q35_TRY(c.get("paged_kv_scale", M(Q35_BF16), &rsc, false));
   const bool fp8 = cache.dtype != Q35_BF16;
+  Q35_REQUIRE(!rsc.present || (fp8 && !kvs.present && rsc.numel() == cache.s[0] * 2 * P * HKV), Q35_ERR_SHAPE,
+              "attn.paged_decode: paged_kv_scale [pages, 2, P, HKV] bf16 goes with an int8 cache (bound as bytes)");
   Q35_REQUIRE(!fp8 || D == 256 || D == 128, Q35_ERR_UNSUPPORTED, "attn.paged_decode: FP8 cache needs head_dim 128/256");
   const int n_cta = sm_count();
   const int64_t S = B * HKV, slots = (S + n_cta) * 4;
@@ -570,7 +750,7 @@ int run_attn_paged_decode(Call& c) {
                 o_ml = take(slots * 16 * 4), o_po = take(slots * AT_GMAX * D * 4);
   Q35_TRY(c.workspace(off, &ws));
   if (c.dry || B == 0) return 0;
-  Q35_REQUIRE(aligned16(q.p) && aligned16(cache.p) && (lo.present ? aligned16(lo.p) : aligned16(out.p)), Q35_ERR_ALIGN,
+  Q35_REQUIRE(aligned16(q.p) && aligned16(cache.p) && (lpk.present ? aligned16(lpk.p) : lo.present ? aligned16(lo.p) : aligned16(out.p)), Q35_ERR_ALIGN,
               "attn.paged_decode: pointers must be 16-byte aligned");
   AttnArgs a{};
   a.q = q.p; a.cache = cache.p; a.indptr = indptr.as<int>(); a.indices = indices.as<int>();
@@ -579,10 +759,15 @@ int run_attn_paged_decode(Call& c) {
   a.kv_scale = kvs.present ? kvs.as<float>() : nullptr;
   a.k_new = kn.present ? kn.as<__nv_bfloat16>() : nullptr;
   a.v_new = vn.present ? vn.as<__nv_bfloat16>() : nullptr;
-  a.out = lo.present ? nullptr : out.as<__nv_bfloat16>();
+  a.out = partial ? nullptr : out.as<__nv_bfloat16>();
   a.lse_m = lo.present ? lm.as<float>() : nullptr;
   a.lse_l = lo.present ? ll.as<float>() : nullptr;
   a.lse_o = lo.present ? lo.as<float>() : nullptr;
+  a.lse_os = int(D); a.lse_ms = 1;
+  if (lpk.present) {  // one message per rank: o | m | l in every row
+    a.lse_o = lpk.as<float>(); a.lse_m = a.lse_o + D; a.lse_l = a.lse_o + D + 1;
+    a.lse_os = a.lse_ms = int(D) + 2;
+  }
   a.B = int(B); a.HQ = int(HQ); a.HKV = int(HKV); a.G = int(G); a.P = int(P);
   a.num_pages = int(cache.s[0]); a.n_indices = int(indices.numel()); a.n_cta = n_cta;
   uint8_t* w = ws.as<uint8_t>();
@@ -592,10 +777,14 @@ int run_attn_paged_decode(Call& c) {
   a.part_ml = reinterpret_cast<float*>(w + o_ml);
   a.part_o = reinterpret_cast<float*>(w + o_po);
   a.status = device_status_ptr();
-  if (fp8) return D == 128 ? launch_attn<128, true>(a, c.stream) : launch_attn<256, true>(a, c.stream);
-  if (D == 64) return launch_attn<64, false>(a, c.stream);
-  if (D == 128) return launch_attn<128, false>(a, c.stream);
-  return launch_attn<256, false>(a, c.stream);
+  if (rsc.present) {
+    a.row_scale = rsc.as<__nv_bfloat16>();
+    return D == 128 ? launch_attn<128, 2>(a, c.stream) : launch_attn<256, 2>(a, c.stream);
+  }
+  if (fp8) return D == 128 ? launch_attn<128, 1>(a, c.stream) : launch_attn<256, 1>(a, c.stream);
+  if (D == 64) return launch_attn<64, 0>(a, c.stream);
+  if (D == 128) return launch_attn<128, 0>(a, c.stream);
+  return launch_attn<256, 0>(a, c.stream);
 }
 
 // ---------------------------------------------------------------------------------------------------------------
@@ -690,8 +879,8 @@ extern "C" int q35_attn_paged_decode_static(const void* q, const void* paged_kv_
   a.part_o = reinterpret_cast<float*>(w + o_po);
   a.status = device_status_ptr();
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (fp8) return D == 128 ? launch_attn<128, true>(a, s) : launch_attn<256, true>(a, s);
-  if (D == 64) return launch_attn<64, false>(a, s);
-  if (D == 128) return launch_attn<128, false>(a, s);
-  return launch_attn<256, false>(a, s);
+  if (fp8) return D == 128 ? launch_attn<128, 1>(a, s) : launch_attn<256, 1>(a, s);
+  if (D == 64) return launch_attn<64, 0>(a, s);
+  if (D == 128) return launch_attn<128, 0>(a, s);
+  return launch_attn<256, 0>(a, s);
 }

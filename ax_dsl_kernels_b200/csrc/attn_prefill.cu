@@ -10,6 +10,13 @@
 // rows, so a K / V tile fetched once serves all heads of the group.  Keys stream in tiles of 64 through a 2-stage
 // cp.async ring (XOR-swizzled rows); S = Q K^T and O += P V on mma.sync bf16 with fp32 accumulation and an online
 // softmax in the log2 domain.  Tensor-bound for long prompts (4 T^2 / 2 * HQ * D flop against T * 2 KB of KV).
+//
+// FP8 cache (E4M3 rows holding x * 8, or x / scale_h with a per-head scale; models/qwen38_27b/prefill/
+// sgl_kv8_kvf8.patch, models/qwen38_27b/decode/q35_group.py:244-249): a tile's bytes land in a staging ring, are
+// expanded to bf16 (exact: E4M3 has 3 mantissa bits) into the tile the MMAs read, the K scale is folded into the
+// softmax scale and the V scale into the final normalisation -- the reference's "constant MX scale on K, block
+// weighted values x 1 / 8".  The rows of this call are quantised as they are written, so the call's own tokens are
+// attended to in their stored precision, as the reference's cache reads do.
 #include "abi.h"
 #include "common.cuh"
 
@@ -21,7 +28,8 @@ constexpr float PF_LOG2E = 1.4426950408889634f;
 
 struct PrefillArgs {
   const __nv_bfloat16* q;      // [Ttot, HQ, D]
-  const __nv_bfloat16* cache;  // [pages, 2, P, HKV, D]
+  const void* cache;           // [pages, 2, P, HKV, D] bf16 or e4m3
+  const float* kv_scale;       // FP8 cache: [2, HKV] per-head scales, or null = the constant form (stored x * 8)
   const int* qo_indptr;        // [B + 1] token ranges of the sequences inside q
   const int* indptr; const int* indices; const int* last_page_len;  // page table incl. the new tokens
   const float* sm_scale;
@@ -30,9 +38,11 @@ struct PrefillArgs {
   int* status;
 };
 
-template <int D>
+template <int D, bool FP8>
 __global__ void __launch_bounds__(256, 1) attn_prefill_kernel(const PrefillArgs a) {
   constexpr int ROWB = D * 2, CPR = ROWB / 16, TILE_BYTES = PF_KEYS * ROWB;
+  // FP8: [K tile | V tile] bf16 work tiles, then two staging stages of raw bytes (K rows then V rows, D bytes each)
+  constexpr int RAWB = D, RCPR = RAWB / 16, RAW_TILE = PF_KEYS * RAWB;
   extern __shared__ __align__(128) uint8_t smem[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int r = lane >> 2, c = lane & 3;
@@ -50,7 +60,9 @@ __global__ void __launch_bounds__(256, 1) attn_prefill_kernel(const PrefillArgs 
   }
   const int hist = kv_len - tq;                 // tokens before this call
   const int page0 = a.indptr[b];
-  const float scale_log2 = (a.sm_scale ? a.sm_scale[0] : rsqrtf(float(D))) * PF_LOG2E;
+  const float k_deq = !FP8 ? 1.f : a.kv_scale ? a.kv_scale[kvh] : 0.125f;
+  const float v_deq = !FP8 ? 1.f : a.kv_scale ? a.kv_scale[a.HKV + kvh] : 0.125f;
+  const float scale_log2 = (a.sm_scale ? a.sm_scale[0] : rsqrtf(float(D))) * PF_LOG2E * k_deq;
 
   // this thread's two rows: row m = warp * 16 + r (+ 8); token = m / 8, head = m % 8
   const int m0 = warp * 16 + r, m1 = m0 + 8;
@@ -79,7 +91,7 @@ __global__ void __launch_bounds__(256, 1) attn_prefill_kernel(const PrefillArgs 
 
   const int last_pos = hist + min(tok0 + PF_TOK, tq) - 1;  // last key any row of this CTA may see
   const int n_tiles = last_pos / PF_KEYS + 1;
-  const size_t row_stride = size_t(a.HKV) * ROWB;
+  const size_t row_stride = size_t(a.HKV) * (FP8 ? RAWB : ROWB);
   const uint8_t* cbase = reinterpret_cast<const uint8_t*>(a.cache);
   const uint32_t sbase = smem_u32(smem);
 
@@ -92,14 +104,23 @@ __global__ void __launch_bounds__(256, 1) attn_prefill_kernel(const PrefillArgs 
         if (tid == 0) atomicOr(a.status, DS_BAD_PAGE);
         page = 0;
       }
-      const uint8_t* kb = cbase + ((size_t(page) * 2 + 0) * a.P + ro) * row_stride + size_t(kvh) * ROWB;
-      const uint8_t* vb = cbase + ((size_t(page) * 2 + 1) * a.P + ro) * row_stride + size_t(kvh) * ROWB;
-      const uint32_t st = sbase + (t & 1) * 2 * TILE_BYTES;
-      for (int idx = tid; idx < PF_KEYS * CPR; idx += 256) {
-        const int key = idx / CPR, ch = idx % CPR;
-        const uint32_t off = key * ROWB + ((ch ^ (key & 7)) << 4);
-        cp_async_16(st + off, kb + size_t(key) * row_stride + ch * 16);
-        cp_async_16(st + TILE_BYTES + off, vb + size_t(key) * row_stride + ch * 16);
+      const uint8_t* kb = cbase + ((size_t(page) * 2 + 0) * a.P + ro) * row_stride + size_t(kvh) * (FP8 ? RAWB : ROWB);
+      const uint8_t* vb = cbase + ((size_t(page) * 2 + 1) * a.P + ro) * row_stride + size_t(kvh) * (FP8 ? RAWB : ROWB);
+      if constexpr (FP8) {
+        const uint32_t st = sbase + 2 * TILE_BYTES + (t & 1) * 2 * RAW_TILE;
+        for (int idx = tid; idx < PF_KEYS * RCPR; idx += 256) {
+          const int key = idx / RCPR, ch = idx % RCPR;
+          cp_async_16(st + key * RAWB + ch * 16, kb + size_t(key) * row_stride + ch * 16);
+          cp_async_16(st + RAW_TILE + key * RAWB + ch * 16, vb + size_t(key) * row_stride + ch * 16);
+        }
+      } else {
+        const uint32_t st = sbase + (t & 1) * 2 * TILE_BYTES;
+        for (int idx = tid; idx < PF_KEYS * CPR; idx += 256) {
+          const int key = idx / CPR, ch = idx % CPR;
+          const uint32_t off = key * ROWB + ((ch ^ (key & 7)) << 4);
+          cp_async_16(st + off, kb + size_t(key) * row_stride + ch * 16);
+          cp_async_16(st + TILE_BYTES + off, vb + size_t(key) * row_stride + ch * 16);
+        }
       }
     }
     cp_async_commit();
@@ -110,8 +131,32 @@ __global__ void __launch_bounds__(256, 1) attn_prefill_kernel(const PrefillArgs 
     issue(t + 1);
     cp_async_wait<1>();
     __syncthreads();
-    const uint32_t sK = sbase + (t & 1) * 2 * TILE_BYTES, sV = sK + TILE_BYTES;
+    const uint32_t sK = FP8 ? sbase : sbase + (t & 1) * 2 * TILE_BYTES, sV = sK + TILE_BYTES;
     const int kk = t * PF_KEYS;
+    if constexpr (FP8) {  // raw bytes -> the swizzled bf16 tiles (16 bytes in, two 16-byte chunks out)
+      const uint8_t* raw = smem + 2 * TILE_BYTES + (t & 1) * 2 * RAW_TILE;
+      for (int idx = tid; idx < 2 * PF_KEYS * RCPR; idx += 256) {
+        const int kv = idx / (PF_KEYS * RCPR), rem = idx % (PF_KEYS * RCPR), key = rem / RCPR, ch = rem % RCPR;
+        const uint4 in = *reinterpret_cast<const uint4*>(raw + kv * RAW_TILE + key * RAWB + ch * 16);
+        const uint32_t w[4] = {in.x, in.y, in.z, in.w};
+        uint32_t o8[8];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const __half2_raw lo = __nv_cvt_fp8x2_to_halfraw2(__nv_fp8x2_storage_t(w[j] & 0xffffu), __NV_E4M3);
+          const __half2_raw hi = __nv_cvt_fp8x2_to_halfraw2(__nv_fp8x2_storage_t(w[j] >> 16), __NV_E4M3);
+          const float2 fl = __half22float2(*reinterpret_cast<const __half2*>(&lo));
+          const float2 fh = __half22float2(*reinterpret_cast<const __half2*>(&hi));
+          o8[2 * j] = pack_bf16(fl.x, fl.y);
+          o8[2 * j + 1] = pack_bf16(fh.x, fh.y);
+        }
+        const uint32_t dst = sK + kv * TILE_BYTES + key * ROWB;
+        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst + (((2 * ch) ^ (key & 7)) << 4)), "r"(o8[0]),
+                     "r"(o8[1]), "r"(o8[2]), "r"(o8[3]));
+        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst + (((2 * ch + 1) ^ (key & 7)) << 4)), "r"(o8[4]),
+                     "r"(o8[5]), "r"(o8[6]), "r"(o8[7]));
+      }
+      __syncthreads();
+    }
     if (kk + PF_KEYS > kv_len) {  // rows past the cached length may hold anything (NaN bits): clear V there
       const int first = kv_len - kk;
       for (int idx = tid; idx < (PF_KEYS - first) * CPR; idx += 256) {
@@ -207,7 +252,7 @@ __global__ void __launch_bounds__(256, 1) attn_prefill_kernel(const PrefillArgs 
     lrow[h] += __shfl_xor_sync(0xffffffffu, lrow[h], 1);
     lrow[h] += __shfl_xor_sync(0xffffffffu, lrow[h], 2);
   }
-  const float inv0 = lrow[0] > 0.f ? 1.f / lrow[0] : 0.f, inv1 = lrow[1] > 0.f ? 1.f / lrow[1] : 0.f;
+  const float inv0 = lrow[0] > 0.f ? v_deq / lrow[0] : 0.f, inv1 = lrow[1] > 0.f ? v_deq / lrow[1] : 0.f;
   __nv_bfloat16* d0 = a.out + (size_t(q0 + tk0) * a.HQ + kvh * a.G + h0) * D;
   __nv_bfloat16* d1 = a.out + (size_t(q0 + tk1) * a.HQ + kvh * a.G + h1) * D;
 #pragma unroll
@@ -222,7 +267,8 @@ __global__ void __launch_bounds__(256, 1) attn_prefill_kernel(const PrefillArgs 
 __global__ void attn_kv_write_rows_kernel(const __nv_bfloat16* __restrict__ k_new, const __nv_bfloat16* __restrict__ v_new,
                                           const int* __restrict__ qo_indptr, const int* __restrict__ indptr,
                                           const int* __restrict__ indices, const int* __restrict__ last_page_len,
-                                          __nv_bfloat16* cache, int B, int HKV, int D, int P, int num_pages, int* status) {
+                                          void* cache, const float* kv_scale, int fp8, int B, int HKV, int D, int P,
+                                          int num_pages, int* status) {
   const int tok = blockIdx.x;  // global token index
   int b = 0;
   while (b + 1 < B && qo_indptr[b + 1] <= tok) ++b;
@@ -235,29 +281,49 @@ __global__ void attn_kv_write_rows_kernel(const __nv_bfloat16* __restrict__ k_ne
   const int page = indices[indptr[b] + pos / P];
   if (page < 0 || page >= num_pages) { if (threadIdx.x == 0) atomicOr(status, DS_BAD_PAGE); return; }
   const int n = HKV * D;
+  const size_t krow = ((size_t(page) * 2 + 0) * P + pos % P) * n, vrow = ((size_t(page) * 2 + 1) * P + pos % P) * n;
+  if (fp8) {  // e4m3(x * 8), or e4m3(x / scale_h) with per-head scales: the arithmetic of attn.kv_write
+    __nv_fp8_e4m3* c8 = static_cast<__nv_fp8_e4m3*>(cache);
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+      const float k = __bfloat162float(k_new[size_t(tok) * n + i]), v = __bfloat162float(v_new[size_t(tok) * n + i]);
+      c8[krow + i] = __nv_fp8_e4m3(kv_scale ? k / kv_scale[i / D] : k * 8.f);  // a true division, as the golden's
+      c8[vrow + i] = __nv_fp8_e4m3(kv_scale ? v / kv_scale[HKV + i / D] : v * 8.f);
+    }
+    return;
+  }
+  __nv_bfloat16* cb = static_cast<__nv_bfloat16*>(cache);
   for (int i = threadIdx.x * 8; i < n; i += blockDim.x * 8) {
-    *reinterpret_cast<uint4*>(cache + ((size_t(page) * 2 + 0) * P + pos % P) * n + i) =
-        *reinterpret_cast<const uint4*>(k_new + size_t(tok) * n + i);
-    *reinterpret_cast<uint4*>(cache + ((size_t(page) * 2 + 1) * P + pos % P) * n + i) =
-        *reinterpret_cast<const uint4*>(v_new + size_t(tok) * n + i);
+    *reinterpret_cast<uint4*>(cb + krow + i) = *reinterpret_cast<const uint4*>(k_new + size_t(tok) * n + i);
+    *reinterpret_cast<uint4*>(cb + vrow + i) = *reinterpret_cast<const uint4*>(v_new + size_t(tok) * n + i);
   }
 }
 
+template <int D, bool FP8>
+static int launch_prefill(const PrefillArgs& a, dim3 grid, cudaStream_t stream) {
+  constexpr int smem = FP8 ? 2 * PF_KEYS * D * 2 + 4 * PF_KEYS * D : 4 * PF_KEYS * D * 2;
+  Q35_TRY(ensure_dynamic_smem(reinterpret_cast<const void*>(attn_prefill_kernel<D, FP8>), smem));
+  attn_prefill_kernel<D, FP8><<<grid, 256, smem, stream>>>(a);
+  Q35_CUDA_LAUNCH_CHECK("attn.paged_prefill");
+  return 0;
+}
+
 int run_attn_paged_prefill(Call& c) {
-  Tensor q, cache, qo, indptr, indices, lpl, scale, kn, vn, out;
+  Tensor q, cache, qo, indptr, indices, lpl, scale, kvs, kn, vn, out;
   Q35_TRY(c.get("q", M(Q35_BF16), &q));
-  Q35_TRY(c.get("paged_kv_cache", M(Q35_BF16), &cache));
+  Q35_TRY(c.get("paged_kv_cache", M(Q35_BF16) | M_FP8, &cache));
   Q35_TRY(c.get("qo_indptr", M(Q35_I32), &qo));
   Q35_TRY(c.get("indptr", M(Q35_I32), &indptr));
   Q35_TRY(c.get("indices", M(Q35_I32), &indices));
   Q35_TRY(c.get("last_page_len", M(Q35_I32), &lpl));
   Q35_TRY(c.get("sm_scale", M(Q35_F32), &scale, false));
+  Q35_TRY(c.get("kv_scale", M(Q35_F32), &kvs, false));
   Q35_TRY(c.get("k_new", M(Q35_BF16), &kn, false));
   Q35_TRY(c.get("v_new", M(Q35_BF16), &vn, false));
   Q35_TRY(c.get("out", M(Q35_BF16), &out));
   Q35_REQUIRE(q.nd == 3 && cache.nd == 5 && cache.s[1] == 2, Q35_ERR_SHAPE,
               "attn.paged_prefill: q [T, HQ, D], paged_kv_cache [pages, 2, P, HKV, D]");
   const int64_t T = q.s[0], HQ = q.s[1], D = q.s[2], P = cache.s[2], HKV = cache.s[3], B = qo.numel() - 1;
+  const bool fp8 = cache.dtype != Q35_BF16;
   Q35_REQUIRE(cache.s[4] == D && HKV > 0 && HQ % HKV == 0 && HQ / HKV <= 8, Q35_ERR_UNSUPPORTED,
               "attn.paged_prefill: at most 8 query heads per KV head");
   Q35_REQUIRE(D == 128 || D == 256, Q35_ERR_UNSUPPORTED, "attn.paged_prefill: head_dim must be 128 or 256");
@@ -266,18 +332,21 @@ int run_attn_paged_prefill(Call& c) {
               "attn.paged_prefill: qo_indptr / indptr [B+1], last_page_len [B], out like q");
   Q35_REQUIRE(kn.present == vn.present && (!kn.present || (kn.numel() == T * HKV * D && vn.numel() == T * HKV * D)),
               Q35_ERR_SHAPE, "attn.paged_prefill: k_new / v_new [T, HKV, D]");
+  Q35_REQUIRE(!kvs.present || (fp8 && kvs.numel() == 2 * HKV), Q35_ERR_SHAPE,
+              "attn.paged_prefill: kv_scale [2, HKV] goes with an FP8 cache");
   c.ws_need = 0;
   if (c.dry || T == 0) return 0;
   Q35_REQUIRE(aligned16(q.p) && aligned16(cache.p) && aligned16(out.p), Q35_ERR_ALIGN, "attn.paged_prefill: alignment");
   if (kn.present) {
     attn_kv_write_rows_kernel<<<unsigned(T), 128, 0, c.stream>>>(
         kn.as<__nv_bfloat16>(), vn.as<__nv_bfloat16>(), qo.as<int>(), indptr.as<int>(), indices.as<int>(),
-        lpl.as<int>(), cache.as<__nv_bfloat16>(), int(B), int(HKV), int(D), int(P), int(cache.s[0]),
-        device_status_ptr());
+        lpl.as<int>(), cache.p, kvs.present ? kvs.as<float>() : nullptr, fp8, int(B), int(HKV), int(D), int(P),
+        int(cache.s[0]), device_status_ptr());
     Q35_CUDA_LAUNCH_CHECK("attn.kv_write_rows");
   }
   PrefillArgs a{};
-  a.q = q.as<__nv_bfloat16>(); a.cache = cache.as<__nv_bfloat16>(); a.qo_indptr = qo.as<int>();
+  a.q = q.as<__nv_bfloat16>(); a.cache = cache.p; a.qo_indptr = qo.as<int>();
+  a.kv_scale = kvs.present ? kvs.as<float>() : nullptr;
   a.indptr = indptr.as<int>(); a.indices = indices.as<int>(); a.last_page_len = lpl.as<int>();
   a.sm_scale = scale.present ? scale.as<float>() : nullptr;
   a.out = out.as<__nv_bfloat16>();
@@ -287,17 +356,8 @@ int run_attn_paged_prefill(Call& c) {
   // the longest sequence is not known on the host: the grid covers T tokens for every sequence, CTAs past a
   // sequence's own length leave at once
   const dim3 grid{unsigned((T + PF_TOK - 1) / PF_TOK), unsigned(HKV), unsigned(B)};
-  if (D == 256) {
-    constexpr int smem = 4 * PF_KEYS * 512;
-    Q35_TRY(ensure_dynamic_smem(reinterpret_cast<const void*>(attn_prefill_kernel<256>), smem));
-    attn_prefill_kernel<256><<<grid, 256, smem, c.stream>>>(a);
-  } else {
-    constexpr int smem = 4 * PF_KEYS * 256;
-    Q35_TRY(ensure_dynamic_smem(reinterpret_cast<const void*>(attn_prefill_kernel<128>), smem));
-    attn_prefill_kernel<128><<<grid, 256, smem, c.stream>>>(a);
-  }
-  Q35_CUDA_LAUNCH_CHECK("attn.paged_prefill");
-  return 0;
+  if (D == 256) return fp8 ? launch_prefill<256, true>(a, grid, c.stream) : launch_prefill<256, false>(a, grid, c.stream);
+  return fp8 ? launch_prefill<128, true>(a, grid, c.stream) : launch_prefill<128, false>(a, grid, c.stream);
 }
 
 }  // namespace q35

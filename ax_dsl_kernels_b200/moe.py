@@ -206,3 +206,102 @@ def lm_head(x, w, s, logits=None, token=None, want_logits=True, want_token=True)
         kw["token"] = token
     _lib.run("lm_head", **kw)
     return logits, token
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# The sgl line's one-call entry point, by the names of its `inputs` object
+# (models/qwen35_35b_a3b/sgl/python/sgl_kernel_axera/moe/m_qwen3.py:3607-3795).
+_MOE_MODES = ("expert_parallel", "token_parallel")
+_prepared = {}
+
+
+def _inp(inputs, name, default=None):
+    if isinstance(inputs, dict):
+        return inputs.get(name, default)
+    return getattr(inputs, name, default)
+
+
+def _mx4_pair(inputs, name, what):
+    w, s = _inp(inputs, "w_" + name), _inp(inputs, "w_scale_" + name)
+    if w is None or s is None:
+        raise ValueError(f"qwen3_moe inputs must provide w_{name} and w_scale_{name}")
+    if _inp(inputs, "w_zeropoint_" + name) is not None:
+        raise ValueError("qwen3_moe: AWQ INT4 experts (zero points) are not supported on this device path")
+    if s.element_size() != 1 or s.dtype == torch.float8_e4m3fn or w.shape[-1] * 2 != s.shape[-1] * 32:
+        raise ValueError(f"qwen3_moe: {what} must be MXFP4 (E2M1 pairs [.., K / 2] bytes with one E8M0 scale per 32 "
+                         "inputs); NVFP4 (E4M3 scales per 16 + scale2) and MXFP8 experts are not supported on this "
+                         "device path")
+    return _u8(w), _u8(s)
+
+
+def qwen3_moe(inputs, output=None, *, mode="auto", core_num=1, chunk_size=None, resident_weights=False):
+    """The MoE block by the reference's one-call contract: `output = x + moe(post_attention_layernorm(x))` with
+    `inputs.w_norm` in the Qwen3.5 zero-centred form (the multiplier is 1 + w_norm).  inputs (mapping or object): x (or
+    hidden_states) [..., H] bf16, w_norm [H], norm_eps, w_route [E, H] bf16, w_gate / w_up [E, I, H / 2] and w_down
+    [E, H, I / 2] MXFP4 bytes with w_scale_* E8M0 (w_gate may already hold gate and up rows, [E, 2 I, H / 2], with w_up
+    absent or the same tensor), shared_expert_gate [H], w_shared_expert_mlp_{gate, up, down} with their
+    w_scale_shared_expert_mlp_*, top_k, norm_topk_prob.  mode: "auto", "expert_parallel", "token_parallel" are accepted
+    and run the same kernels (they name how the reference spreads work over NPU cores); core_num and chunk_size are
+    accepted for the same reason and unused.  Weights are bound, not copied, except that separate gate and up planes are
+    joined once per weight set (the kernels read one gate-up plane per expert) and the E8M0 scales are re-tiled once.
+
+    Arithmetic is that of the q35 block (fp32 router logits, routing weights applied after the down projection); the
+    reference's sgl kernel computes router logits in bf16 and, for long prefills, scales the activation before the down
+    projection -- same results within the block's tolerance, not bit for bit."""
+    x = _inp(inputs, "x")
+    if x is None:
+        x = _inp(inputs, "hidden_states")
+    if x is None:
+        raise ValueError("qwen3_moe inputs must provide x")
+    if x.dim() < 2:
+        raise ValueError("qwen3_moe hidden states must have rank >= 2")
+    if output is None:
+        output = torch.empty_like(x)
+    elif tuple(output.shape) != tuple(x.shape) or output.dtype != x.dtype:
+        raise ValueError(f"output {tuple(output.shape)} {output.dtype} must match hidden_states {tuple(x.shape)} {x.dtype}")
+    if mode != "auto" and mode not in _MOE_MODES:
+        raise ValueError(f"unsupported qwen3_moe mode {mode!r}; expected one of: {', '.join(_MOE_MODES)}, auto")
+    if not x.is_cuda:
+        raise TypeError("qwen3_moe: tensors must be on the GPU (there is no CPU path)")
+    if not bool(_inp(inputs, "norm_topk_prob", True)):
+        raise ValueError("qwen3_moe: norm_topk_prob=False is not supported (the routing kernel normalises the top-k "
+                         "weights, as Qwen3.5 does)")
+    w_norm = _inp(inputs, "w_norm")
+    if w_norm is None:
+        raise ValueError("qwen3_moe: inputs.w_norm is required (the fused x + moe(norm(x)) contract)")
+    if _inp(inputs, "shared_expert_gate") is None:
+        raise ValueError("qwen3_moe: the block without a shared expert is not supported on this device path")
+    eps = _inp(inputs, "norm_eps")
+    if eps is not None and abs(float(eps) - 1e-6) > 1e-12:
+        raise ValueError("qwen3_moe: norm_eps other than 1e-6 is not supported")
+    H = x.shape[-1]
+    key = tuple(int(t.data_ptr()) for t in (w_norm, _inp(inputs, "w_gate"), _inp(inputs, "w_down"),
+                                            _inp(inputs, "w_route")) if t is not None)
+    w = _prepared.get(key)
+    if w is None:
+        if resident_weights and (_inp(inputs, "w_gate").dtype == torch.bfloat16):
+            raise ValueError("qwen3_moe: resident bf16 / per-row FP8 expert weights are not supported; bind MXFP4 planes")
+        gw, gs = _mx4_pair(inputs, "gate", "expert weights")
+        dw, ds = _mx4_pair(inputs, "down", "expert weights")
+        up = _inp(inputs, "w_up")
+        if up is not None and up.data_ptr() != _inp(inputs, "w_gate").data_ptr():
+            uw, us = _mx4_pair(inputs, "up", "expert weights")
+            gw, gs = torch.cat([gw, uw], 1).contiguous(), torch.cat([gs, us], 1).contiguous()
+        route_w = _inp(inputs, "w_route")
+        if route_w is None or route_w.dtype != torch.bfloat16:
+            raise ValueError("qwen3_moe: w_route must be a bf16 [E, H] matrix")
+        w = dict(ln2=(w_norm.float().reshape(-1) + 1.0).contiguous(), w_router=route_w,
+                 w_shg=_inp(inputs, "shared_expert_gate").to(torch.bfloat16).reshape(1, H).contiguous(),
+                 e_gw=gw, e_gs=gs, e_dw=dw, e_ds=ds)
+        for ours, theirs in (("gate", "shared_expert_mlp_gate"), ("up", "shared_expert_mlp_up"),
+                             ("down", "shared_expert_mlp_down")):
+            w["w_" + ours], w["s_" + ours] = _mx4_pair(inputs, theirs, "shared expert weights")
+        if w["ln2"].numel() != H:
+            raise ValueError(f"qwen3_moe w_norm shape {tuple(w_norm.shape)} must match hidden size {H}")
+        prepare_moe_weights(w)
+        _prepared[key] = w
+    top_k = _inp(inputs, "top_k")
+    if top_k is None:
+        raise ValueError("qwen3_moe inputs must provide top_k")
+    moe_block(x.reshape(-1, H), w, int(top_k), output.reshape(-1, H))
+    return output

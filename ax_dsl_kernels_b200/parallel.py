@@ -335,25 +335,27 @@ class HeadSplitAttention:
 
     def _gpu_partial(self, q, cache, indptr, indices, last_page_len, sm_scale, kv_scale, packed):
         from . import _lib
-        B, Hq, D = q.shape
-        m, ln, o = packed[..., D], packed[..., D + 1], packed[..., :D]
-        pm = self._get("pm", (B, Hq), torch.float32, q.device)
-        pl = self._get("pl", (B, Hq), torch.float32, q.device)
-        po = self._get("po", (B, Hq, D), torch.float32, q.device)
-        kw = dict(q=q, paged_kv_cache=cache, indptr=indptr, indices=indices, last_page_len=last_page_len, part_m=pm,
-                  part_l=pl, part_o=po)
+        kw = dict(q=q, paged_kv_cache=cache, indptr=indptr, indices=indices, last_page_len=last_page_len,
+                  part_packed=packed)  # the kernel writes o | m | l of every row straight into the message
         if sm_scale is not None:
             kw["sm_scale"] = sm_scale
         if kv_scale is not None:
             kw["kv_scale"] = kv_scale
         _lib.run("attn.paged_decode", **kw)
-        o.copy_(po)
-        m.copy_(pm)
-        ln.copy_(pl)
 
-    def _gpu_merge(self, pm, pl, po, out):
+    def _gpu_merge(self, gathered, out):
         from . import _lib
-        _lib.run("attn.lse_merge", part_m=pm, part_l=pl, part_o=po, out=out)
+        B = out.shape[0]
+        _lib.run("attn.lse_merge", packed=gathered.reshape(self.world, B, -1, gathered.shape[-1]), out=out)
+
+    @staticmethod
+    def unpack(gathered, world, shares):
+        """gathered [world * B, Hq, D + 2] (ranks along dim 0, KV group major) -> (m, l, o) as [shares, B, HQ] and
+        [shares, B, HQ, D]: the separate-tensor form of the merge (what a CPU merge takes)"""
+        B, Hq, W = gathered.shape[0] // world, gathered.shape[1], gathered.shape[2]
+        n_kv = world // shares
+        g = gathered.reshape(n_kv, shares, B, Hq, W).permute(1, 2, 0, 3, 4).reshape(shares, B, n_kv * Hq, W)
+        return g[..., W - 2].contiguous(), g[..., W - 1].contiguous(), g[..., :W - 2].contiguous()
 
     def forward(self, q, cache, indptr, indices, last_page_len, out=None, sm_scale=None, kv_scale=None):
         """q [B, HQ, D]: every rank passes the full query; cache / page table: this rank's (see class docstring)"""
@@ -365,11 +367,6 @@ class HeadSplitAttention:
         self._local(ql, cache, indptr, indices, last_page_len, sm_scale, kv_scale, packed)
         gathered = self._get("gathered", (self.world * B, Hq, D + 2), torch.float32, q.device)  # ranks along dim 0
         dist.all_gather_into_tensor(gathered, packed, group=self.group)
-        S = p["shares"]
-        n_kv_groups = self.world // S  # rank = kv group * S + share
-        g = gathered.reshape(n_kv_groups, S, B, Hq, D + 2).permute(1, 2, 0, 3, 4).reshape(S, B, n_kv_groups * Hq, D + 2)
-        po = g[..., :D].contiguous()
-        pm, pl = g[..., D].contiguous(), g[..., D + 1].contiguous()
         out = torch.empty((B, HQ, D), dtype=q.dtype, device=q.device) if out is None else out
-        self._merge(pm, pl, po, out)
+        self._merge(gathered, out)
         return out

@@ -9,7 +9,7 @@ import math
 import torch
 import torch.nn.functional as F
 
-from .codecs import kv_dequant_fp8, kv_quant_fp8
+from .codecs import kv_dequant_fp8, kv_dequant_int8_rows, kv_quant_fp8, kv_quant_int8_rows
 from .moe import bf, rmsnorm
 
 
@@ -19,7 +19,7 @@ def valid_kv_len(indptr, last_page_len, page):
     return torch.where(n > 0, (n - 1) * page + last_page_len.long(), torch.zeros_like(n))
 
 
-def gather_kv(cache, indptr, indices, last_page_len, b, kv_scale=None):
+def gather_kv(cache, indptr, indices, last_page_len, b, kv_scale=None, row_scale=None):
     """history K, V of sequence b as fp32 [ctx, HKV, D] (golden gather,
     models/qwen35_35b_a3b/sgl/tests/test_qwen35_runtime.py:76-79)."""
     P = cache.shape[2]
@@ -27,6 +27,10 @@ def gather_kv(cache, indptr, indices, last_page_len, b, kv_scale=None):
     ctx = int(valid_kv_len(indptr, last_page_len, P)[b])
     k = cache[rows, 0].reshape(-1, *cache.shape[3:])[:ctx]
     v = cache[rows, 1].reshape(-1, *cache.shape[3:])[:ctx]
+    if row_scale is not None:  # int8 rows with a bf16 scale per row and head: row_scale [pages, 2, P, HKV]
+        sk = row_scale[rows, 0].reshape(-1, row_scale.shape[-1])[:ctx]
+        sv = row_scale[rows, 1].reshape(-1, row_scale.shape[-1])[:ctx]
+        return kv_dequant_int8_rows(k, sk), kv_dequant_int8_rows(v, sv)
     if cache.dtype == torch.float8_e4m3fn:
         ks = vs = None
         if kv_scale is not None:
@@ -35,7 +39,8 @@ def gather_kv(cache, indptr, indices, last_page_len, b, kv_scale=None):
     return k.float(), v.float()
 
 
-def paged_decode(q, cache, indptr, indices, last_page_len, sm_scale=None, kv_scale=None, k_new=None, v_new=None):
+def paged_decode(q, cache, indptr, indices, last_page_len, sm_scale=None, kv_scale=None, k_new=None, v_new=None,
+                 row_scale=None):
     """One query token per sequence over its paged history (+ optionally the current token's own k / v row, which the
     kernel takes from registers instead of the cache, flash_attn.py:2088-2124).
 
@@ -49,7 +54,7 @@ def paged_decode(q, cache, indptr, indices, last_page_len, sm_scale=None, kv_sca
     scale = 1.0 / math.sqrt(D) if sm_scale is None else float(sm_scale)
     out = torch.zeros((B, HQ, D))
     for b in range(B):
-        k, v = gather_kv(cache, indptr, indices, last_page_len, b, kv_scale)
+        k, v = gather_kv(cache, indptr, indices, last_page_len, b, kv_scale, row_scale)
         if k_new is not None:
             k = torch.cat([k, k_new[b].float()[None]], 0)
             v = torch.cat([v, v_new[b].float()[None]], 0)
@@ -62,7 +67,7 @@ def paged_decode(q, cache, indptr, indices, last_page_len, sm_scale=None, kv_sca
     return out.to(torch.bfloat16)
 
 
-def paged_decode_partial(q, cache, indptr, indices, last_page_len, sm_scale=None, kv_scale=None):
+def paged_decode_partial(q, cache, indptr, indices, last_page_len, sm_scale=None, kv_scale=None, row_scale=None):
     """the unnormalised partial of paged_decode over the given pages: m (maximum score in the log2 domain), l (sum of
     2^(s - m)), o (sum of 2^(s - m) v) per (sequence, query head) -- what one of several devices that split a KV head's
     pages contributes (flash_attn.py:2393-2474).  A sequence without keys gives l = 0."""
@@ -74,7 +79,7 @@ def paged_decode_partial(q, cache, indptr, indices, last_page_len, sm_scale=None
     ln = torch.zeros((B, HQ))
     o = torch.zeros((B, HQ, D))
     for b in range(B):
-        k, v = gather_kv(cache, indptr, indices, last_page_len, b, kv_scale)
+        k, v = gather_kv(cache, indptr, indices, last_page_len, b, kv_scale, row_scale)
         if k.shape[0] == 0:
             continue
         s = torch.einsum("hgd,lhd->hgl", q[b].float().reshape(HKV, G, D), k) * scale
@@ -95,11 +100,13 @@ def lse_merge(pm, pl, po):
     return torch.where(L[..., None] > 0, o / L[..., None].clamp_min(1e-38), torch.zeros_like(o)).to(torch.bfloat16)
 
 
-def paged_prefill(q, cache, qo_indptr, indptr, indices, last_page_len, sm_scale=None):
+def paged_prefill(q, cache, qo_indptr, indptr, indices, last_page_len, sm_scale=None, kv_scale=None):
     """T new tokens per sequence against the paged cache that already holds their K / V rows, causal:
     token i of a sequence with `hist` earlier tokens sees keys 0 .. hist + i (prefill form of the decode golden;
     reference kernels: flash_attn.py:471-610, models/qwen35_2b/whole/src/q35_prefill.py:250-318).
-    q [Ttot, HQ, D] bf16, sequences delimited by qo_indptr [B + 1]."""
+    q [Ttot, HQ, D] bf16, sequences delimited by qo_indptr [B + 1].  An FP8 cache is read back through its dequantised
+    rows, the new tokens' own rows included (models/qwen38_27b/prefill/sgl_kv8_kvf8.patch: every K / V tile comes from
+    the cache); kv_scale [2, HKV] as in paged_decode."""
     Ttot, HQ, D = q.shape
     HKV = cache.shape[3]
     G = HQ // HKV
@@ -109,7 +116,7 @@ def paged_prefill(q, cache, qo_indptr, indptr, indices, last_page_len, sm_scale=
         q0, q1 = int(qo_indptr[b]), int(qo_indptr[b + 1])
         if q1 == q0:
             continue
-        k, v = gather_kv(cache, indptr, indices, last_page_len, b)
+        k, v = gather_kv(cache, indptr, indices, last_page_len, b, kv_scale)
         hist = k.shape[0] - (q1 - q0)
         qb = q[q0:q1].float().reshape(q1 - q0, HKV, G, D)
         s = torch.einsum("thgd,lhd->thgl", qb, k) * scale
@@ -120,12 +127,17 @@ def paged_prefill(q, cache, qo_indptr, indptr, indices, last_page_len, sm_scale=
     return out.to(torch.bfloat16)
 
 
-def store_paged_kv(cache, cache_location, k_new, v_new, kv_scale=None):
+def store_paged_kv(cache, cache_location, k_new, v_new, kv_scale=None, row_scale=None):
     """write the current token's K / V rows at (page, offset) per sequence (flash_attn.py:53-84); FP8 caches store
     e4m3(x * 8) (models/qwen38_27b/decode/q35_group.py:244-249) or e4m3(x / scale_h) with kv_scale [2, HKV]."""
     for b in range(k_new.shape[0]):
         page, off = int(cache_location[b, 0]), int(cache_location[b, 1])
-        if cache.dtype == torch.float8_e4m3fn:
+        if row_scale is not None:  # int8 rows, their scales stored alongside (kv_write_paged, q35_group.py:253-260)
+            for kv, row in ((0, k_new[b]), (1, v_new[b])):
+                q8, sc = kv_quant_int8_rows(row)
+                cache[page, kv, off] = q8.to(cache.dtype) if cache.dtype == torch.int8 else q8.view(torch.uint8)
+                row_scale[page, kv, off] = sc
+        elif cache.dtype == torch.float8_e4m3fn:
             ks = vs = None
             if kv_scale is not None:
                 ks, vs = kv_scale[0], kv_scale[1]

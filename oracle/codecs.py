@@ -120,6 +120,23 @@ def kv_quant_fp8(x, scale=None):
     return (x.float() / scale.float().reshape(*([1] * (x.dim() - 2)), -1, 1)).to(torch.float8_e4m3fn)
 
 
+def kv_quant_int8_rows(x):
+    """[..., HKV, D] bf16 -> (int8 [..., HKV, D], bf16 scale [..., HKV]): amax per head (at least 1e-5), s = bf16(amax *
+    bf16(1 / 127)), q = round(bf16(x * bf16(1 / s))) -- kv_quant_row (models/qwen38_27b/decode/q35_group.py:198-205),
+    every product rounded to bf16 as the reference's bf16 ops do."""
+    bf = lambda t: t.to(torch.bfloat16).float()  # noqa: E731
+    xb = x.to(torch.bfloat16).float()
+    amax = torch.maximum(xb.abs().amax(-1, keepdim=True), bf(torch.tensor(1e-5)))
+    sc = bf(amax * bf(torch.tensor(1.0 / 127)))
+    q = torch.round(bf(xb * bf(1.0 / sc))).clamp(-127, 127).to(torch.int8)
+    return q, sc.squeeze(-1).to(torch.bfloat16)
+
+
+def kv_dequant_int8_rows(q, sc):
+    """bf16(int8 * scale) as the reference's page dequantisation (kv_page, q35_group.py:208-222), returned as fp32"""
+    return (q.float() * sc.float().unsqueeze(-1)).to(torch.bfloat16).float()
+
+
 def kv_dequant_fp8(c, scale=None):
     if scale is None:
         return c.float() / KV8_SCALE

@@ -344,6 +344,7 @@ def test_attention_split_over_eight_ranks_emulated_on_one_gpu(q35):
     B, HQn, Dn = q.shape
     full = q35.paged_attention_decode(q.cuda(), cache.cuda(), indptr.cuda(), indices.cuda(), last.cuda())
     parts = {}
+    gathered = torch.full((world, B, 8, Dn + 2), float("nan"), device="cuda")  # what the all-gather would deliver
     for rank in range(world):
         pl = parallel.attention_split(HQn, 2, world, rank)
         ip, ix, lp = parallel.split_page_table(indptr, indices, last, 64, pl["share"], pl["shares"])
@@ -354,17 +355,63 @@ def test_attention_split_over_eight_ranks_emulated_on_one_gpu(q35):
         q35.run("attn.paged_decode", q=ql, paged_kv_cache=cache[:, :, :, pl["kv0"]:pl["kv1"]].contiguous().cuda(),
                 indptr=ip.cuda(), indices=ix.cuda(), last_page_len=lp.cuda(), part_m=pm, part_l=pln, part_o=po)
         parts[(pl["kv0"], pl["share"])] = (pm, pln, po)
+        # the one-message form of the same launch: o | m | l written straight into the rank's slot
+        q35.run("attn.paged_decode", q=ql, paged_kv_cache=cache[:, :, :, pl["kv0"]:pl["kv1"]].contiguous().cuda(),
+                indptr=ip.cuda(), indices=ix.cuda(), last_page_len=lp.cuda(), part_packed=gathered[rank])
+        assert torch.equal(gathered[rank][..., :Dn], po) and torch.equal(gathered[rank][..., Dn], pm)
+        assert torch.equal(gathered[rank][..., Dn + 1], pln)
     S = world // 2
     pm = torch.stack([torch.cat([parts[(kv, s)][0] for kv in range(2)], 1) for s in range(S)])
     pln = torch.stack([torch.cat([parts[(kv, s)][1] for kv in range(2)], 1) for s in range(S)])
     po = torch.stack([torch.cat([parts[(kv, s)][2] for kv in range(2)], 1) for s in range(S)])
     out = torch.full_like(full, float("nan"))
     q35.run("attn.lse_merge", part_m=pm.contiguous(), part_l=pln.contiguous(), part_o=po.contiguous(), out=out)
+    out2 = torch.full_like(full, float("nan"))
+    q35.run("attn.lse_merge", packed=gathered, out=out2)
+    assert torch.equal(out, out2)
     ref = oattn.paged_decode(q, cache, indptr, indices, last)
     nz = [0, 1, 2, 4, 5]
     assert (out[3] == 0).all()
     assert_parity(out.cpu()[nz], ref[nz], per_seq=True)
     assert_parity(out.cpu()[nz], full.cpu()[nz], per_seq=True, name="attention split over 8 ranks vs the unsplit role")
+
+
+def test_qwen3_moe_one_call_contract_by_the_reference_names(q35):
+    """qwen3_moe(inputs, output): the sgl line's entry point bound by its own names (w_norm in the zero-centred form,
+    separate gate / up planes, shared_expert_mlp_*); same kernels as moe_block, so the same bits, and parity with the
+    oracle block.  Contract violations raise ValueError as the reference's wrapper does."""
+    T = 64
+    x1, w = moe_case(T, seed=3)
+    dw = {k: v.cuda() for k, v in w.items()}
+    ref_out = q35.moe_block(x1.cuda(), q35.prepare_moe_weights(dict(dw)), 8)[0].clone()
+    FE = w["e_gw"].shape[1] // 2
+    inputs = dict(x=x1.cuda().reshape(4, 16, -1), w_norm=(w["ln2"] - 1).cuda(), w_route=dw["w_router"],
+                  w_gate=dw["e_gw"][:, :FE].contiguous(), w_scale_gate=dw["e_gs"][:, :FE].contiguous(),
+                  w_up=dw["e_gw"][:, FE:].contiguous(), w_scale_up=dw["e_gs"][:, FE:].contiguous(),
+                  w_down=dw["e_dw"], w_scale_down=dw["e_ds"], shared_expert_gate=dw["w_shg"].float(),
+                  w_shared_expert_mlp_gate=dw["w_gate"], w_scale_shared_expert_mlp_gate=dw["s_gate"],
+                  w_shared_expert_mlp_up=dw["w_up"], w_scale_shared_expert_mlp_up=dw["s_up"],
+                  w_shared_expert_mlp_down=dw["w_down"], w_scale_shared_expert_mlp_down=dw["s_down"],
+                  top_k=8, norm_topk_prob=True)
+    out = q35.qwen3_moe(inputs, mode="expert_parallel", core_num=4)
+    assert out.shape == (4, 16, x1.shape[1])
+    assert torch.equal(out.reshape(T, -1), ref_out)
+    fused = dict(inputs, w_gate=dw["e_gw"], w_scale_gate=dw["e_gs"], w_up=None, w_scale_up=None)
+    out2 = torch.full_like(out, float("nan"))
+    assert q35.qwen3_moe(fused, out2) is out2 and torch.equal(out2, out)
+    sg, su, sd = dequant_shared(w)
+    oref = omoe.moe_block(x1, w["ln2"], sg, su, sd, w["w_router"], w["w_shg"], w["e_gw"], w["e_gs"], w["e_dw"],
+                          w["e_ds"], 8)[0]
+    assert_parity(out.reshape(T, -1).cpu(), oref, bf16_step=True)
+    with pytest.raises(ValueError):
+        q35.qwen3_moe(inputs, mode="data_parallel")
+    with pytest.raises(ValueError):
+        q35.qwen3_moe(dict(inputs, norm_topk_prob=False))
+    with pytest.raises(ValueError):
+        q35.qwen3_moe(inputs, torch.empty((T, 7), dtype=torch.bfloat16, device="cuda"))
+    with pytest.raises(ValueError):  # NVFP4 scales (E4M3 per 16) are refused, not misread
+        q35.qwen3_moe(dict(fused, w_scale_gate=torch.zeros((256, 2 * FE, 128), dtype=torch.float8_e4m3fn, device="cuda"),
+                           w_norm=(w["ln2"] - 1).cuda().clone()))
 
 
 # ------------------------------------------------------------------------------------------------ robustness

@@ -212,7 +212,8 @@ def _attn_worker(rank, world, port, ret):
             m, ln, o = oattn.paged_decode_partial(ql, c, ip, ix, lp)
             packed[..., :D], packed[..., D], packed[..., D + 1] = o, m, ln
 
-        def merge(pm, pl, po, out):
+        def merge(gathered, out):
+            pm, pl, po = parallel.HeadSplitAttention.unpack(gathered, world, world // HKV)
             out.copy_(oattn.lse_merge(pm, pl, po))
 
         att = parallel.HeadSplitAttention(HQ, HKV, local=local, merge=merge)
