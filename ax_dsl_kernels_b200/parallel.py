@@ -13,6 +13,9 @@ This moves the same bytes as an exact all-to-all dispatch/return of the routed r
 when T * K / N >= T, which holds for top-8 routing on up to 8 GPUs.
 In the reference the same exchange happens between the 4 NPU cores through shared on-chip memory
 (models/qwen35_2b/whole/src/q35_layer_mc.py:830-886: logits gathered, expert partial sums added).
+
+Prefill-sized batches (thousands of tokens per rank) use `forward_all_to_all` instead: every routed row goes only to
+the rank that owns its expert and comes back weighted, T * K rows each way.
 """
 import torch
 import torch.distributed as dist
@@ -144,6 +147,70 @@ class ExpertParallelMoE:
         out = self._finish(base, mine, out, ready)
         mark("closing sum (waits for the shared expert)")
         return out
+
+    # -- prefill-sized batches: a true all-to-all ---------------------------------------------------------------------
+    def _combine(self, base, loc, rows, out):
+        from . import _lib
+        _lib.run("moe.combine", base=base, loc=loc, sout=rows, out=out)
+        return out
+
+    def forward_all_to_all(self, x1, out=None, marks=None):
+        """The block on THIS rank's T tokens (every rank holds different tokens) with every token's row sent only to
+        the ranks that own one of its experts, once per rank: dispatch all-to-all of (row, its K expert ids, its K
+        weights) sorted by destination; the owner runs its experts on the rows it received (landed in its own memory
+        first; ids of other ranks' experts are skipped, as in the decode form) and returns ONE weighted partial sum per
+        received row; the token's rank adds the returned rows onto the dense part in fp32 (moe_combine arithmetic,
+        models/qwen35_2b/whole/src/q35_moe_prefill.py:201-214, with the rank as the slot).  Moves at most
+        min(K, N) rows per token each way instead of the N * T rows per rank the all-gather form replicates, which is
+        what a prefill of thousands of tokens per rank needs; the per-destination row counts cross the host once per
+        call (one small device-to-host copy)."""
+        def mark(name):
+            if marks is not None and x1.is_cuda:
+                ev = torch.cuda.Event(enable_timing=True)
+                ev.record()
+                marks.append((name, ev))
+
+        T, H = x1.shape
+        N, K = self.world, self.top_k
+        per = self.n_experts // N
+        mark("start")
+        base, h2, ids, rw, ready = self._dense_part(x1)
+        mark("norm + router + route (shared expert on a second stream)")
+        dest = torch.div(ids.long(), per, rounding_mode="floor")                      # [T, K] owning rank of each pick
+        member = torch.zeros((N, T), dtype=torch.bool, device=x1.device)
+        member[dest.t().reshape(-1), torch.arange(T, device=x1.device).repeat(K)] = True  # rank r owns a pick of token t
+        rk, tok = member.nonzero(as_tuple=True)                                        # sorted by rank, then token
+        send_counts = member.sum(1)
+        counts = torch.empty_like(send_counts)
+        dist.all_to_all_single(counts, send_counts, group=self.group)
+        both = torch.stack([send_counts, counts]).cpu()          # the one host round trip: split sizes of the exchange
+        s_split, r_split = both[0].tolist(), both[1].tolist()
+        S, R = int(sum(s_split)), int(sum(r_split))
+        send_rows = h2[tok]
+        meta = torch.cat([ids[tok].float(), rw[tok].float()], 1).contiguous()          # [S, 2 K]
+        rows = torch.empty((R, H), dtype=h2.dtype, device=h2.device)
+        rmeta = torch.empty((R, 2 * K), dtype=torch.float32, device=h2.device)
+        dist.all_to_all_single(rows, send_rows, r_split, s_split, group=self.group)
+        dist.all_to_all_single(rmeta, meta, r_split, s_split, group=self.group)
+        mark("dispatch all-to-all (rows, ids, weights)")
+        if R:
+            partial = self._local_experts(rows, rmeta[:, :K].to(torch.int32).contiguous(), rmeta[:, K:].contiguous())
+            res = partial.to(h2.dtype)                           # weighted sums travel back in bf16
+        else:
+            res = rows
+        mark("expert GEMMs on the received rows")
+        back = torch.empty((S, H), dtype=h2.dtype, device=h2.device)
+        dist.all_to_all_single(back, res, s_split, r_split, group=self.group)
+        mark("return all-to-all")
+        loc = torch.full((N, T), -1, dtype=torch.int32, device=x1.device)              # slot of (rank, token) or -1
+        loc[rk, tok] = torch.arange(S, dtype=torch.int32, device=x1.device)
+        out = torch.empty_like(x1) if out is None else out
+        if ready is not None:
+            torch.cuda.current_stream(base.device).wait_event(ready)
+        self._combine(base, loc, back, out)
+        mark("combine (waits for the shared expert)")
+        return out
+
 
 # ----------------------------------------------------------------------------------------------------------------
 # Tensor parallelism of the dense hybrid stack (27B-class decode group: heads split across 2 / 4 / 8 GPUs).

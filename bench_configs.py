@@ -27,7 +27,7 @@ PAGE, HQ, HKV, D = 64, 16, 2, 256
 
 
 def _finish(args, name, metric, unit_items, step, ins, outs, roofline, config, dist=None, dev=None, extra=None,
-            scaling="weak"):
+            scaling="weak", graph_ok=True):
     """times `step` (graph replay on one GPU), the end-to-end variant, samples clocks, prints the line on rank 0"""
     import ax_dsl_kernels_b200 as q35
     rank = int(os.environ.get("RANK", 0))
@@ -56,7 +56,8 @@ def _finish(args, name, metric, unit_items, step, ins, outs, roofline, config, d
     n0 = L.q35_launch_count()
     step()
     launches = L.q35_launch_count() - n0
-    graph = hb.capture(step) if not args.no_graph else None  # several ranks: the NCCL all-reduces are captured too
+    # several ranks: the NCCL collectives are captured too; a step with a host round trip cannot be captured
+    graph = hb.capture(step) if graph_ok and not args.no_graph else None
     run = graph.replay if graph is not None else step
     barrier()
     rounds = hb.timed_rounds(run, args.steps, barrier, agree=agree)
@@ -220,8 +221,56 @@ def run_c3_prefill(args):
                    "bf16 inputs, fp32 state"}, dev=dev)
 
 
+def run_c4_prefill_ep(args):
+    """MoE prefill over several GPUs: experts sharded, the 8192 tokens split evenly, routed rows exchanged all-to-all"""
+    import datetime
+    import torch.distributed as dist
+    import ax_dsl_kernels_b200 as q35
+    from ax_dsl_kernels_b200 import parallel
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=180))
+    wl = hb.Workload(dev, seed=3, attn=False)  # the same weights on every rank; each keeps its experts
+    ep = parallel.ExpertParallelMoE(wl.w, hb.TOPK, dist.group.WORLD)
+    T = 8192 // world
+    g = torch.Generator(device=dev).manual_seed(3 + rank)
+    x1 = torch.randn((T, hb.H), generator=g, device=dev).to(torch.bfloat16)
+    out = torch.empty_like(x1)
+    step = lambda: ep.forward_all_to_all(x1, out)  # noqa: E731
+    flop = 8192 * hb.TOPK * 6 * hb.H * hb.FE + 8192 * 6 * hb.H * hb.FS + 8192 * 2 * hb.H * hb.NE
+    _, tf, src = hb.measured_peaks()
+
+    def roof(ms):
+        t = flop / (ms * 1e-3) / 1e12
+        return {"bound": "tensor", "kernel": "tc_gemm_kernel (routed gate-up, down on the received rows; shared expert)",
+                "achieved": t, "peak": tf * world, "unit": "TFLOP/s", "frac": t / (tf * world),
+                "peak_source": src + " (bf16 GEMM) x GPUs", "traffic": None, "algorithmic_flop": flop,
+                "exchange_rows_per_token_upper_bound": min(hb.TOPK, world) - 1}
+
+    per = {}  # phase times, every rank takes part (the step holds collectives); rank 0's medians are reported
+    for it in range(12):
+        marks = []
+        ep.forward_all_to_all(x1, out, marks=marks)
+        torch.cuda.synchronize()
+        if it >= 4:
+            for (_, a), (nm, b) in zip(marks[:-1], marks[1:]):
+                per.setdefault(nm, []).append(a.elapsed_time(b))
+    phases = {nm: round(hb.median(v) * 1e3, 1) for nm, v in per.items()}
+    extra = lambda _ms: {"ep_phases_us_rank0": phases}  # noqa: E731
+    _finish(args, "c4_prefill", "MoE block prefill tok/s (8192 tokens, 256 experts top-8); % of FP4/FP8 TC peak", 8192, step,
+            [x1], [out], roof,
+            {"workload": f"MoE block, 8192 tokens ({T} per GPU), {hb.NE} experts top-{hb.TOPK} MXFP4 + shared expert, "
+             f"hidden {hb.H}", "parallelism": f"experts sharded x{world}, tokens split x{world}, every token's row sent once to each rank "
+             "that owns one of its experts and one weighted partial sum returned per row (NCCL all-to-all both ways), "
+             "row counts through the host once per step"},
+            dist=dist, dev=dev, scaling="strong", graph_ok=False, extra=extra)
+
+
 def run_c4(args, prefill):
     import ax_dsl_kernels_b200 as q35
+    if prefill and int(os.environ.get("WORLD_SIZE", 1)) > 1:
+        return run_c4_prefill_ep(args)
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(0)
     wl = hb.Workload(dev, seed=3, attn=False)

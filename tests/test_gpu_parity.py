@@ -672,10 +672,13 @@ def test_moe_block_prefill_8192_tokens_permutation_equivariance(q35):
     assert_parity(out.cpu()[sample], ref, bf16_step=True)
 
 
-def test_moe_experts_expert_parallel_shape_of_eight_ranks(q35):
+@pytest.mark.parametrize("T,lo,hi,stride", [(512, 96, 128, 29), (4100, 128, 256, 211)])
+def test_moe_experts_expert_parallel_shape_of_eight_ranks(q35, T, lo, hi, stride):
     """what one of 8 ranks runs per decode step: 512 gathered tokens, global ids over 256 experts, 32 local planes
-    starting at expert_base (4096 pairs through the one-CTA routing plan); a sample of tokens against the golden"""
-    T, NE, lo, hi = 512, 256, 96, 128
+    starting at expert_base (4096 pairs through the one-CTA routing plan); and what one of 2 ranks runs on the rows an
+    all-to-all dispatch of a prefill delivers: thousands of rows, half of the experts local, the other picks skipped
+    (the prefill-sized plan).  A sample of tokens against the golden."""
+    NE = 256
     g = torch.Generator().manual_seed(23)
     h2 = torch.randn((T, 2048), generator=g).to(torch.bfloat16)
     ids, rw = omoe.route(torch.randn((T, NE), generator=g), 8)
@@ -689,7 +692,7 @@ def test_moe_experts_expert_parallel_shape_of_eight_ranks(q35):
     got = partial.cpu()
     zero = torch.zeros((1, 2048), dtype=torch.bfloat16)
     checked = 0
-    for t in range(0, T, 29):
+    for t in range(0, T, stride):
         ref = torch.zeros(2048)
         for i in range(8):
             e = int(ids[t, i]) - lo
