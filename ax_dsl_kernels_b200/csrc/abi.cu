@@ -203,6 +203,9 @@ static const RoleDef kRoles[] = {
     {"linear",
      R"({"in":[["x","bf16","[T,K]"],["w","u8|e4m3|bf16","[N,K/2]|[N,K]"],["s","u8|f32","[N,K/32]|[N] optional"],["bias","f32","[N] optional"],["row_div","f32","[T] optional"],["residual","bf16","[T,N] optional"],["workspace","u8","[*] optional: with it (and K a multiple of 512) the tensor-core path runs"]],"out":[["out","bf16|f32","[T,N]"]]})",
      run_linear},
+    {"linear.multi",
+     R"({"in":[["x","bf16","[T,K]"],["w","u8|e4m3","[N,K/2]|[N,K]: the projections' weights, rows concatenated"],["s","u8|f32","[N,K/32]|[N]"],["bias","f32","[N] optional"],["row_div","f32","[T] optional"],["workspace","u8","[*]"]],"out":[["out0","bf16|f32","[T,N_0]"],["out1","bf16|f32","[T,N_1] optional, and so on up to out7; the N_i add up to N"],["out2","bf16|f32","optional"],["out3","bf16|f32","optional"],["out4","bf16|f32","optional"],["out5","bf16|f32","optional"],["out6","bf16|f32","optional"],["out7","bf16|f32","optional"]]})",
+     run_linear_multi},
     {"norm.rms",
      R"({"in":[["x","bf16","[T,H]"],["residual","bf16","[T,H] optional"],["w","f32|bf16","[H]"],["eps","f32","[1] optional"]],"out":[["y","bf16","[T,H]"],["base_out","bf16","[T,H] optional"],["xsqrt_out","f32","[T] optional: folded form"]]})",
      run_norm_rms},

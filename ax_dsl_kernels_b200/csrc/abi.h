@@ -130,6 +130,7 @@ int run_attn_qk_prep(Call&);
 int run_act_silu_mul(Call&);
 int run_act_sigmoid_gate(Call&);
 int run_linear_tc(Call&);
+int run_linear_multi(Call&);
 int run_lm_head(Call&);
 int run_debug_wait_probe(Call&);
 int run_debug_tc_peak(Call&);

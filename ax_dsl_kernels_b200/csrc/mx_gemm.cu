@@ -822,4 +822,51 @@ int run_linear(Call& c) {
   return launch_skinny<W_FP8ROW, EPI_PLAIN>(d, nt, tiles, 1, c.stream);
 }
 
+// linear.multi: several projections of one input in one pass -- w is the row-wise concatenation of their weights
+// (the reference's fused w_qkv rows, models/qwen35_35b_a3b/qwen35_35b_a3b.manifest.json `prefill64.gdn`), out0 ..
+// out7 the projections' own tensors [T, N_i] in that order.  One activation quantisation, one pass over the weights,
+// one reduction that applies bias / per-row scale / per-token divisor and scatters the segments.
+int run_linear_multi(Call& c) {
+  Tensor x, w, s, bias, rdiv, ws;
+  Q35_TRY(c.get("x", M(Q35_BF16), &x));
+  Q35_TRY(c.get("row_div", M(Q35_F32), &rdiv, false));
+  Q35_TRY(c.get("w", M_BYTES | M(Q35_E4M3), &w));
+  Q35_TRY(c.get("s", M(Q35_U8) | M(Q35_F32), &s));
+  Q35_TRY(c.get("bias", M(Q35_F32), &bias, false));
+  Q35_REQUIRE(x.nd >= 2 && w.nd == 2, Q35_ERR_SHAPE, "linear.multi: x [T, K], w [N, K or K/2]");
+  const int64_t K = x.s[x.nd - 1], T = x.numel() / K, N = w.s[0];
+  int fmt;
+  Q35_TRY(weight_format(w, s, K, &fmt));
+  Q35_REQUIRE(fmt == W_FP8ROW ? s.numel() == N : s.numel() == N * (K / 32), Q35_ERR_SHAPE, "linear.multi: scale shape");
+  Q35_REQUIRE((!bias.present || bias.numel() == N) && (!rdiv.present || rdiv.numel() == T), Q35_ERR_SHAPE,
+              "linear.multi: bias [N], row_div [T]");
+  Q35_REQUIRE(K % 128 == 0, Q35_ERR_UNSUPPORTED, "linear.multi: K must be a multiple of 128");
+  TcSegments segs{};
+  int64_t rows = 0;
+  static const char* const names[8] = {"out0", "out1", "out2", "out3", "out4", "out5", "out6", "out7"};
+  for (int i = 0; i < 8; ++i) {
+    Tensor o;
+    Q35_TRY(c.get(names[i], M(Q35_BF16) | M(Q35_F32), &o, i == 0));
+    if (!o.present) break;
+    Q35_REQUIRE(T > 0 && o.numel() % T == 0 && o.numel() > 0, Q35_ERR_SHAPE, "linear.multi: %s must be [T, N_i]", names[i]);
+    segs.n0[i] = int(rows);
+    segs.out[i] = o.p;
+    segs.f32[i] = o.dtype == Q35_F32;
+    rows += o.numel() / T;
+    segs.n = i + 1;
+  }
+  segs.n0[segs.n] = int(rows);
+  Q35_REQUIRE(rows == N, Q35_ERR_SHAPE, "linear.multi: the outputs hold %lld rows, the weight %lld", (long long)rows,
+              (long long)N);
+  Q35_TRY(c.workspace(tc_linear_multi_bytes(T, N, K), &ws));
+  if (c.dry || T == 0) return 0;
+  Q35_REQUIRE(aligned16(x.p) && (reinterpret_cast<uintptr_t>(w.p) & 31) == 0 && aligned16(s.p), Q35_ERR_ALIGN,
+              "linear.multi: x, s 16-byte and w 32-byte aligned");
+  TcLinear p{};
+  p.w = w.p; p.s = s.p; p.fmt = fmt == W_MXFP4 ? 0 : fmt == W_MXFP8 ? 1 : 2;
+  p.bias = bias.present ? bias.as<float>() : nullptr;
+  p.row_div = rdiv.present ? rdiv.as<float>() : nullptr;
+  return tc_linear_multi(x.as<__nv_bfloat16>(), T, N, K, p, segs, ws.as<uint8_t>(), c.stream);
+}
+
 }  // namespace q35

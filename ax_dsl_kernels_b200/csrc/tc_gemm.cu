@@ -318,11 +318,38 @@ __global__ void __launch_bounds__(256) tc_linear_reduce_kernel(const float* __re
   else b_out[i] = __float2bfloat16_rn(v);
 }
 
-int tc_linear(const __nv_bfloat16* x, int64_t T, int64_t N, int64_t K, const TcLinear& p, uint8_t* qws,
-              cudaStream_t stream) {
+// the reduction with the rows cut into segments, each with an output tensor of its own
+__global__ void __launch_bounds__(256) tc_linear_reduce_multi_kernel(const float* __restrict__ part, long long plane,
+                                                                     int slices, int T, int N,
+                                                                     const float* __restrict__ row_scale,
+                                                                     const float* __restrict__ bias,
+                                                                     const float* __restrict__ row_div, TcSegments segs) {
+  pdl_wait();
+  pdl_launch();
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (long long)T * N) return;
+  const int t = int(i / N), n = int(i % N);
+  float v = 0.f;
+  for (int s = 0; s < slices; ++s) v += part[s * plane + i];
+  v = v * (row_scale ? row_scale[n] : 1.f) + (bias ? bias[n] : 0.f);
+  if (row_div) v = round_bf16(v) / row_div[t];
+  int g = 0;
+  while (g + 1 < segs.n && n >= segs.n0[g + 1]) ++g;
+  const long long o = (long long)t * (segs.n0[g + 1] - segs.n0[g]) + (n - segs.n0[g]);
+  if (segs.f32[g]) static_cast<float*>(segs.out[g])[o] = v;
+  else static_cast<__nv_bfloat16*>(segs.out[g])[o] = __float2bfloat16_rn(v);
+}
+
+int64_t tc_linear_multi_bytes(int64_t T, int64_t N, int64_t K) {
+  const int s = tc_linear_slices(T, N, K);
+  return (tc_quant_bytes(T, K) + 255) / 256 * 256 + int64_t(s) * T * N * 4;
+}
+
+static int tc_linear_impl(const __nv_bfloat16* x, int64_t T, int64_t N, int64_t K, const TcLinear& p,
+                          const TcSegments* segs, uint8_t* qws, cudaStream_t stream) {
   const TcQuant q = tc_quant_carve(qws, T, K);
   const int slices = tc_linear_slices(T, N, K);
-  float* part = slices > 1 ? reinterpret_cast<float*>(qws + (tc_quant_bytes(T, K) + 255) / 256 * 256) : nullptr;
+  float* part = (slices > 1 || segs) ? reinterpret_cast<float*>(qws + (tc_quant_bytes(T, K) + 255) / 256 * 256) : nullptr;
   Q35_TRY(tc_quantize(x, int(K), nullptr, int(T), int(T), int(K), q, stream));
   const uint8_t* w = static_cast<const uint8_t*>(p.w);
   TcWeights tw{{w, w}, {uint64_t(N), uint64_t(N)}};
@@ -339,13 +366,30 @@ int tc_linear(const __nv_bfloat16* x, int64_t T, int64_t N, int64_t K, const TcL
   a.out_stride = int(N);
   a.bias = p.bias; a.row_div = p.row_div; a.resid2 = p.resid2;
   a.k_slices = slices; a.part = part; a.part_plane = (long long)T * N;
+  a.raw = segs ? 1 : 0;
   Q35_TRY(tc_launch<TC_EPI_PLAIN>(tw, q, a, int(T), int((N + 127) / 128), 1, stream));
+  if (segs) {
+    launch_pdl(tc_linear_reduce_multi_kernel, dim3(unsigned((T * N + 255) / 256)), dim3(256), 0, stream,
+               (const float*)part, (long long)T * N, slices, int(T), int(N), a.row_scale, p.bias, p.row_div, *segs);
+    Q35_CUDA_LAUNCH_CHECK("tc linear reduce (segments)");
+    return 0;
+  }
   if (slices > 1) {
     launch_pdl(tc_linear_reduce_kernel, dim3(unsigned((T * N + 255) / 256)), dim3(256), 0, stream, (const float*)part,
                (long long)T * N, slices, int(T), int(N), a.row_scale, p.bias, p.row_div, p.resid2, p.f_out, p.b_out);
     Q35_CUDA_LAUNCH_CHECK("tc linear reduce");
   }
   return 0;
+}
+
+int tc_linear(const __nv_bfloat16* x, int64_t T, int64_t N, int64_t K, const TcLinear& p, uint8_t* qws,
+              cudaStream_t stream) {
+  return tc_linear_impl(x, T, N, K, p, nullptr, qws, stream);
+}
+
+int tc_linear_multi(const __nv_bfloat16* x, int64_t T, int64_t N, int64_t K, const TcLinear& p, const TcSegments& segs,
+                    uint8_t* qws, cudaStream_t stream) {
+  return tc_linear_impl(x, T, N, K, p, &segs, qws, stream);
 }
 
 // shared by linear.tc and lm_head: quantise x into the workspace and run the plain-epilogue GEMM

@@ -62,6 +62,7 @@ struct TcArgs {
   // slice_stages each, an item is (group, tile, slice), and every slice's fp32 sums go to its own plane of `part`
   // ([k_slices][rows of x][out_stride]) for a reduction kernel that also applies the epilogue
   int k_slices, slice_stages;
+  int raw;                  // 1: raw sums to `part` even with one slice (the reduction kernel owns the epilogue)
   float* part; long long part_plane;
   int* status;
 };
@@ -386,7 +387,7 @@ __global__ void __launch_bounds__(TcCfg<NB>::THREADS, TcCfg<NB>::CTAS_PER_SM) tc
           }
 #pragma unroll
           for (int jj = 0; jj < 16; ++jj) hi[jj] += lo[jj];
-          if (EPI == TC_EPI_PLAIN && a.k_slices > 1) {  // split K: raw sums of this slice, the epilogue runs after the reduction
+          if (EPI == TC_EPI_PLAIN && (a.k_slices > 1 || a.raw)) {  // split K: raw sums of this slice, the epilogue runs after the reduction
             float* pp = a.part + (long long)im.slice * a.part_plane;
 #pragma unroll
             for (int jj = 0; jj < 16; ++jj) {

@@ -48,6 +48,19 @@ int64_t tc_linear_bytes(int64_t T, int64_t N, int64_t K);
 int tc_linear(const __nv_bfloat16* x, int64_t T, int64_t N, int64_t K, const TcLinear& p, uint8_t* qws,
               cudaStream_t stream);
 
+// the same product with the weight's rows cut into up to 8 consecutive segments, each written to a tensor of its own
+// ([T, rows of the segment], bf16 or fp32): several projections of one input as ONE quantisation and ONE pass over a
+// row-concatenated weight.  Decode-sized T only (the sums always go through the fp32 planes of the split-K form).
+struct TcSegments {
+  int n;
+  int n0[9];       // segment i = weight rows [n0[i], n0[i + 1])
+  void* out[8];
+  int f32[8];      // 1: out[i] is fp32, 0: bf16
+};
+int64_t tc_linear_multi_bytes(int64_t T, int64_t N, int64_t K);
+int tc_linear_multi(const __nv_bfloat16* x, int64_t T, int64_t N, int64_t K, const TcLinear& p, const TcSegments& segs,
+                    uint8_t* qws, cudaStream_t stream);
+
 template <int EPI>
 int tc_launch(const TcWeights& w, const TcQuant& q, TcArgs a, int nb, int tiles, int groups, cudaStream_t stream);
 

@@ -14,7 +14,7 @@ import torch
 from . import _lib
 from .attention import paged_attention_decode, paged_attention_prefill
 from .gdn import gdn_chunk_prefill, gdn_conv1d_silu, gdn_recurrent_step
-from .moe import linear
+from .moe import fuse_rows, linear, linear_multi
 
 
 def _empty(shape, dtype, like):
@@ -79,7 +79,10 @@ def gdn(hidden_states, residual, weights, temporal_state, conv_state, *, input_n
     R = B * T
     x2 = hidden_states.reshape(R, H)
     xs, base, xsqrt = rmsnorm(x2, w["input_norm_w"], residual=residual.reshape(R, H), eps=input_norm_eps, folded=True)
-    proj = {n: _proj(xs, w, n, row_div=xsqrt) for n in ("q", "k", "v", "z", "a", "b")}
+    if "w_qkvzab" in w:  # the six projections fused by rows at load time (fuse_layer): one pass over one weight
+        proj = dict(zip("qkvzab", linear_multi(xs, w["w_qkvzab"], w["s_qkvzab"], w["n_qkvzab"], row_div=xsqrt)))
+    else:
+        proj = {n: _proj(xs, w, n, row_div=xsqrt) for n in ("q", "k", "v", "z", "a", "b")}
     KD, VD = proj["q"].shape[1], proj["v"].shape[1]
     NV = w["a_log"].numel()
     DV = VD // NV
@@ -129,9 +132,13 @@ def attention(x, weights, cos, sin, cache, indptr, indices, last_page_len, *, he
     w = weights
     R, H = x.shape
     n, _, _ = rmsnorm(x, w["ln1"])
-    qg = _proj(n, w, "q")
-    k = _proj(n, w, "k")
-    v = _proj(n, w, "v").reshape(R, kv_heads, head_dim)
+    if "w_qkv" in w:
+        qg, k, v = linear_multi(n, w["w_qkv"], w["s_qkv"], w["n_qkv"])
+        v = v.reshape(R, kv_heads, head_dim)
+    else:
+        qg = _proj(n, w, "q")
+        k = _proj(n, w, "k")
+        v = _proj(n, w, "v").reshape(R, kv_heads, head_dim)
     q = _empty((R, heads, head_dim), torch.bfloat16, x)
     kr = _empty((R, kv_heads, head_dim), torch.bfloat16, x)
     kw = dict(qg=qg, k=k, q_norm=w["q_norm"], k_norm=w["k_norm"], cos=cos, sin=sin, q_out=q, k_out=kr)
@@ -161,13 +168,29 @@ def mlp_residual(x1, weights, reduce=None):
     split of the reference's multi-core form, models/qwen35_2b/whole/src/q35_layer_mc.py:129-136)."""
     w = weights
     h2, _, _ = rmsnorm(x1, w["ln2"])
-    g = _proj(h2, w, "gate")
-    u = _proj(h2, w, "up")
+    if "w_gateup" in w:
+        g, u = linear_multi(h2, w["w_gateup"], w["s_gateup"], w["n_gateup"])
+    else:
+        g = _proj(h2, w, "gate")
+        u = _proj(h2, w, "up")
     act = torch.empty_like(g)
     _lib.run("act.silu_mul", a=g, b=u, y=act)
     if reduce is None:
         return _proj(act, w, "down", residual=x1)
     return finish_residual(x1, reduce(_proj(act, w, "down", out_dtype=torch.float32)))
+
+
+def fuse_layer(weights, kind):
+    """A copy of one layer's weight dict with the projections that share an input concatenated by rows (GDN: q k v z a
+    b; attention: q+gate k v; MLP: gate up), so that a decode step reads each of them in one launch sequence.  Made once
+    at load time; costs one copy of those weights (the separate tensors are dropped from the copy, not from the
+    caller's dict).  Layers whose projections differ in format stay as they are."""
+    w = dict(weights)
+    if kind == "g":
+        fuse_rows(w, ("q", "k", "v", "z", "a", "b"), "qkvzab")
+    else:
+        fuse_rows(w, ("q", "k", "v"), "qkv")
+    return fuse_rows(w, ("gate", "up"), "gateup")
 
 
 class HybridStack:
@@ -239,8 +262,11 @@ class DecodeGroup:
     reduce: tensor parallel (layers = this rank's shards, heads / kv_heads its counts), as in gdn()."""
 
     def __init__(self, layers, kinds, *, batch, heads, kv_heads, head_dim, rot, theta, max_tokens, page_size=64,
-                 gated=True, reduce=None, kv_dtype=torch.bfloat16):
-        self.layers, self.kinds, self.B = layers, kinds, batch
+                 gated=True, reduce=None, kv_dtype=torch.bfloat16, fuse=True):
+        self.kinds, self.B = kinds, batch
+        # fuse: projections that share an input are concatenated by rows once, here (see fuse_layer)
+        self.layers = [fuse_layer(w, k) for w, k in zip(layers, kinds)] if fuse else layers
+        layers = self.layers
         self.reduce, self.gated = reduce, gated
         self.cfg = dict(heads=heads, kv_heads=kv_heads, head_dim=head_dim)
         self.rot, self.theta, self.P = rot, theta, page_size

@@ -192,6 +192,41 @@ def linear(x, w, s, out=None, bias=None, out_dtype=torch.bfloat16, row_div=None,
     return out
 
 
+def linear_multi(x, w, s, sizes, row_div=None, bias=None, out_dtype=torch.bfloat16):
+    """Several projections of one input as ONE launch sequence (one quantisation of x, one pass over the weights, one
+    reduction): w / s are the projections' weights and scales concatenated by rows, sizes their row counts in that
+    order.  Returns one [T, N_i] tensor per projection.  The reference fuses the same rows into one weight (w_qkv of
+    its GDN kernels, models/qwen35_35b_a3b/qwen35_35b_a3b.manifest.json `prefill64.gdn`)."""
+    if len(sizes) > 8 or sum(sizes) != w.shape[0]:
+        raise ValueError("linear_multi: at most 8 projections whose rows add up to the weight's")
+    T = x.shape[0]
+    outs = [torch.empty((T, n), dtype=out_dtype, device=x.device) for n in sizes]
+    kw = dict(x=x, w=w, s=s if s.dtype == torch.float32 else _u8(s))
+    kw.update({f"out{i}": o for i, o in enumerate(outs)})
+    if row_div is not None:
+        kw["row_div"] = row_div
+    if bias is not None:
+        kw["bias"] = bias
+    _lib.run("linear.multi", **kw)
+    return outs
+
+
+def fuse_rows(weights, names, fused):
+    """adds `w_<fused>`, `s_<fused>` (rows of the projections `names` concatenated, one copy made at load time) and
+    `n_<fused>` (their row counts) to a weight dict and drops the separate entries.  No-op when the projections differ
+    in format or one is missing."""
+    ws, ss = [weights.get("w_" + n) for n in names], [weights.get("s_" + n) for n in names]
+    if any(t is None for t in ws + ss) or len({t.dtype for t in ws}) != 1 or len({t.dtype for t in ss}) != 1 or \
+            len({t.shape[1] for t in ws}) != 1 or len({t.dim() for t in ss}) != 1:
+        return weights
+    weights["w_" + fused] = torch.cat(ws, 0).contiguous()
+    weights["s_" + fused] = torch.cat(ss, 0).contiguous()
+    weights["n_" + fused] = [int(t.shape[0]) for t in ws]
+    for n in names:
+        del weights["w_" + n], weights["s_" + n]
+    return weights
+
+
 def lm_head(x, w, s, logits=None, token=None, want_logits=True, want_token=True):
     """MXFP4 output projection: fp32 logits [T, N] and / or the greedy token [T] (first index of the row maximum).
     Reference: mul_mat_mx4 (models/qwen35_2b/whole/src/q35_layer_mc.py:741-758), golden torch_logits

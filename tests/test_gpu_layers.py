@@ -350,3 +350,22 @@ def test_decode_group_bound_through_packs_and_banks(q35):
         outs.append(torch.stack(y))
     assert torch.isfinite(outs[0].float()).all()
     assert torch.equal(outs[0], outs[1])
+
+
+def test_decode_group_fused_projections_match_separate_ones(q35):
+    """DecodeGroup concatenates the projections that share an input (q k v z a b; q+gate k v; gate up) at load time;
+    two steps of the fused group against the group that keeps them separate"""
+    kinds = "gga"
+    kw, _ = stack_case(kinds, seed=33)
+    cfg = dict(heads=4, kv_heads=1, head_dim=128, rot=64, theta=1e7)
+    B, H = 5, 512
+    outs = []
+    for fuse in (True, False):
+        grp = q35.layers.DecodeGroup(to_dev(kw), kinds, batch=B, max_tokens=128, fuse=fuse, **cfg)
+        assert ("w_qkvzab" in grp.layers[0]) == fuse and ("w_gateup" in grp.layers[2]) == fuse
+        grp.set_context([0, 1, 63, 64, 100])
+        gx = torch.Generator().manual_seed(8)
+        outs.append(torch.stack([grp.step((torch.randn((B, H), generator=gx) * 0.5).to(torch.bfloat16).cuda()).cpu()
+                                 for _ in range(2)]))
+    assert rel_rms_err(outs[0], outs[1]) <= 2e-2
+    assert cosine(outs[0], outs[1]) >= 0.9995

@@ -241,6 +241,33 @@ def test_linear_contraction_multiple_of_128_only(q35, fmt):
                 out=torch.empty((T, N), device="cuda"), workspace=torch.empty(0, dtype=torch.uint8, device="cuda"))
 
 
+@pytest.mark.parametrize("fmt", ["mxfp4", "mxfp8", "fp8row"])
+@pytest.mark.parametrize("T", [1, 8, 70])
+def test_linear_multi_fused_rows(q35, fmt, T):
+    """linear.multi: projections of one input with their weights concatenated by rows (the GDN sublayer's q k v z a b
+    at a reduced width: 256 + 256 + 512 + 512 + 6 + 6 rows), one launch sequence, every segment in its own tensor;
+    against the golden product and against the one-projection role"""
+    K, sizes = 1024, [256, 256, 512, 512, 6, 6]
+    g = torch.Generator().manual_seed(T)
+    x = torch.randn((T, K), generator=g).to(torch.bfloat16)
+    wf = torch.randn((sum(sizes), K), generator=g) * 0.05
+    quant, dequant = {"mxfp4": (codecs.quant_mxfp4, codecs.dequant_mxfp4), "mxfp8": (codecs.quant_mxfp8, codecs.dequant_mxfp8),
+                      "fp8row": (codecs.quant_fp8_rowwise, codecs.dequant_fp8_rowwise)}[fmt]
+    w, s = quant(wf)
+    rdiv = torch.rand(T, generator=g) + 0.5
+    ref = ((x.float() @ dequant(w, s).T).to(torch.bfloat16).float() / rdiv[:, None]).to(torch.bfloat16)
+    outs = q35.moe.linear_multi(x.cuda(), w.cuda(), s.cuda(), sizes, row_div=rdiv.cuda())
+    assert [tuple(o.shape) for o in outs] == [(T, n) for n in sizes]
+    n0 = 0
+    for o, n in zip(outs, sizes):
+        assert rel_rms_err(o.cpu(), ref[:, n0:n0 + n]) <= TOL
+        one = q35.linear(x.cuda(), w[n0:n0 + n].cuda().contiguous(), s[n0:n0 + n].cuda().contiguous(), row_div=rdiv.cuda())
+        assert rel_rms_err(o.cpu(), one.cpu()) <= 1e-2
+        n0 += n
+    f32 = q35.moe.linear_multi(x.cuda(), w.cuda(), s.cuda(), [sum(sizes[:3]), sum(sizes[3:])], out_dtype=torch.float32)
+    assert rel_rms_err(torch.cat([t.cpu() for t in f32], 1), x.float() @ dequant(w, s).T) <= 2e-3
+
+
 # ------------------------------------------------------------------------------------------------ attention
 def _attn_check(q35, ctxs, P=64, HKV=2, HQ=16, D=256, fp8=False, per_head=True, sm_scale=None, seed=1):
     q, cache, indptr, indices, last, kvs = paged_case(ctxs, P=P, HKV=HKV, HQ=HQ, D=D, seed=seed, fp8=fp8,
