@@ -201,7 +201,7 @@ static const RoleDef kRoles[] = {
      R"({"in":[["q","bf16","[B,T,NK,128]"],["k","bf16","[B,T,NK,128]"],["v","bf16","[B,T,NV,128]"],["g","f32","[B,T,NV]"],["beta","bf16","[B,T,NV]"],["state_in","f32","[B,NV,128,128]"],["workspace","u8","[*]"]],"out":[["o","bf16","[B,T,NV,128]"],["state_out","f32","[B,NV,128,128]"]]})",
      run_gdn_chunk_prefill},
     {"linear",
-     R"({"in":[["x","bf16","[T,K]"],["w","u8|e4m3|bf16","[N,K/2]|[N,K]"],["s","u8|f32","[N,K/32]|[N] optional"],["bias","f32","[N] optional"],["row_div","f32","[T] optional"],["residual","bf16","[T,N] optional"],["workspace","u8","[*] optional: with it (and K a multiple of 512) the tensor-core path runs"]],"out":[["out","bf16|f32","[T,N]"]]})",
+     R"({"in":[["x","bf16","[T,K]"],["w","u8|e4m3|bf16","[N,K/2]|[N,K]"],["s","u8|f32|e4m3","[N,K/32]|[N]|[N,K/16], the last with E4M3 scales per 16 inputs: NVFP4"],["s2","f32","[1] optional: tensor scale of an NVFP4 weight"],["bias","f32","[N] optional"],["row_div","f32","[T] optional"],["residual","bf16","[T,N] optional"],["workspace","u8","[*] optional: with it (and K a multiple of 512) the tensor-core path runs"]],"out":[["out","bf16|f32","[T,N]"]]})",
      run_linear},
     {"linear.multi",
      R"({"in":[["x","bf16","[T,K]"],["w","u8|e4m3","[N,K/2]|[N,K]: the projections' weights, rows concatenated"],["s","u8|f32","[N,K/32]|[N]"],["bias","f32","[N] optional"],["row_div","f32","[T] optional"],["workspace","u8","[*]"]],"out":[["out0","bf16|f32","[T,N_0]"],["out1","bf16|f32","[T,N_1] optional, and so on up to out7; the N_i add up to N"],["out2","bf16|f32","optional"],["out3","bf16|f32","optional"],["out4","bf16|f32","optional"],["out5","bf16|f32","optional"],["out6","bf16|f32","optional"],["out7","bf16|f32","optional"]]})",

@@ -583,6 +583,7 @@ static int weight_format(const Tensor& w, const Tensor& s, int64_t K, int* fmt) 
   if (s.present && s.dtype == Q35_F32) { *fmt = W_FP8ROW; return 0; }
   Q35_REQUIRE(s.present, Q35_ERR_MISSING, "quantised weight without scales");
   const int64_t inner = w.s[w.nd - 1];
+  if (s.dtype == Q35_E4M3 && inner == K / 2) { *fmt = W_NVFP4; return 0; }  // E4M3 scales per 16 inputs
   if (inner == K / 2 && w.dtype == Q35_U8) { *fmt = W_MXFP4; return 0; }
   if (inner == K) { *fmt = W_MXFP8; return 0; }
   return fail(Q35_ERR_SHAPE, "weight inner dim %lld matches neither K/2 (MXFP4) nor K (FP8) for K=%lld",
@@ -633,7 +634,7 @@ static int moe_pre_impl(Call& c, int mode) {
     Q35_TRY(weight_format(wg, sg, H, &f1));
     Q35_TRY(weight_format(wu, su, H, &f2));
     Q35_TRY(weight_format(wd, sd, FS, &f3));
-    Q35_REQUIRE(f1 == f2 && f1 == f3 && f1 != W_FP8ROW, Q35_ERR_UNSUPPORTED,
+    Q35_REQUIRE(f1 == f2 && f1 == f3 && f1 != W_FP8ROW && f1 != W_NVFP4, Q35_ERR_UNSUPPORTED,
                 "moe.pre: shared expert must be MXFP4 or MXFP8");
     Q35_REQUIRE(sg.numel() == FS * (H / 32) && su.numel() == FS * (H / 32) && sd.numel() == H * (FS / 32),
                 Q35_ERR_SHAPE, "moe.pre: scale shapes");
@@ -767,7 +768,9 @@ int run_linear(Call& c) {
   Q35_TRY(c.get("residual", M(Q35_BF16), &resid, false));
   Q35_TRY(c.get("x", M(Q35_BF16), &x));
   Q35_TRY(c.get("w", M_BYTES | M(Q35_E4M3), &w));
-  Q35_TRY(c.get("s", M(Q35_U8) | M(Q35_F32), &s));
+  Q35_TRY(c.get("s", M(Q35_U8) | M(Q35_F32) | M(Q35_E4M3), &s));
+  Tensor s2;
+  Q35_TRY(c.get("s2", M(Q35_F32), &s2, false));
   Q35_TRY(c.get("bias", M(Q35_F32), &bias, false));
   Q35_TRY(c.get("out", M(Q35_BF16) | M(Q35_F32), &out));
   Q35_REQUIRE(x.nd >= 2 && w.nd == 2, Q35_ERR_SHAPE, "linear: x [T, K], w [N, K or K/2]");
@@ -775,7 +778,10 @@ int run_linear(Call& c) {
   int fmt;
   Q35_TRY(weight_format(w, s, K, &fmt));
   Q35_REQUIRE(out.numel() == T * N, Q35_ERR_SHAPE, "linear: out must be [T, N]");
-  Q35_REQUIRE(fmt == W_FP8ROW ? s.numel() == N : s.numel() == N * (K / 32), Q35_ERR_SHAPE, "linear: scale shape");
+  Q35_REQUIRE(fmt == W_FP8ROW ? s.numel() == N : fmt == W_NVFP4 ? s.numel() == N * (K / 16) : s.numel() == N * (K / 32),
+              Q35_ERR_SHAPE, "linear: scale shape");
+  Q35_REQUIRE(!s2.present || (fmt == W_NVFP4 && s2.numel() == 1), Q35_ERR_SHAPE,
+              "linear: s2 [1] is the tensor scale of an NVFP4 weight (E4M3 scales [N, K/16])");
   Q35_REQUIRE(!bias.present || bias.numel() == N, Q35_ERR_SHAPE, "linear: bias [N]");
   Q35_REQUIRE((!rdiv.present || rdiv.numel() == T) && (!resid.present || resid.numel() == T * N), Q35_ERR_SHAPE,
               "linear: row_div [T], residual [T, N]");
@@ -783,8 +789,8 @@ int run_linear(Call& c) {
   // With a workspace bound, the projection runs on the tensor cores (tcgen05 block-scaled MMA:
   // E2M1 or E4M3 weights straight from TMA, activations as two E4M3 terms); without a workspace on the CUDA-core
   // weight-streaming kernel, which takes K in multiples of 256 only.  Same results within the tolerance of the role.
-  const bool tc_shape = true;
-  const int64_t need = tc_linear_bytes(T, N, K);
+  const bool tc_shape = fmt != W_NVFP4;  // the block-scaled MMA kind used here takes E8M0 scales per 32 only
+  const int64_t need = tc_shape ? tc_linear_bytes(T, N, K) : 0;
   Tensor ws;
   c.ws_need = need;
   if (!c.dry) Q35_TRY(c.get("workspace", M(Q35_U8), &ws, false));
@@ -819,6 +825,10 @@ int run_linear(Call& c) {
   const int nt = pick_nt(T), tiles = int((N + 127) / 128);
   if (fmt == W_MXFP4) return launch_skinny<W_MXFP4, EPI_PLAIN>(d, nt, tiles, 1, c.stream);
   if (fmt == W_MXFP8) return launch_skinny<W_MXFP8, EPI_PLAIN>(d, nt, tiles, 1, c.stream);
+  if (fmt == W_NVFP4) {
+    d.tensor_scale = s2.present ? s2.as<float>() : nullptr;
+    return launch_skinny<W_NVFP4, EPI_PLAIN>(d, nt, tiles, 1, c.stream);
+  }
   return launch_skinny<W_FP8ROW, EPI_PLAIN>(d, nt, tiles, 1, c.stream);
 }
 
@@ -837,6 +847,7 @@ int run_linear_multi(Call& c) {
   const int64_t K = x.s[x.nd - 1], T = x.numel() / K, N = w.s[0];
   int fmt;
   Q35_TRY(weight_format(w, s, K, &fmt));
+  Q35_REQUIRE(fmt != W_NVFP4, Q35_ERR_UNSUPPORTED, "linear.multi: NVFP4 weights take the one-projection role");
   Q35_REQUIRE(fmt == W_FP8ROW ? s.numel() == N : s.numel() == N * (K / 32), Q35_ERR_SHAPE, "linear.multi: scale shape");
   Q35_REQUIRE((!bias.present || bias.numel() == N) && (!rdiv.present || rdiv.numel() == T), Q35_ERR_SHAPE,
               "linear.multi: bias [N], row_div [T]");

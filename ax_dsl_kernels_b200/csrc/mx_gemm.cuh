@@ -10,7 +10,10 @@
 
 namespace q35 {
 
-enum : int { W_MXFP4 = 0, W_MXFP8 = 1, W_FP8ROW = 2 };
+enum : int { W_MXFP4 = 0, W_MXFP8 = 1, W_FP8ROW = 2, W_NVFP4 = 3 };
+// NVFP4: E2M1 pairs as MXFP4, one E4M3 scale per 16 inputs, one fp32 scale for the tensor
+// (quantize_nvfp4, models/qwen35_35b_a3b/sgl/python/sgl_kernel_axera/quantization.py:8-37)
+constexpr bool fmt_is_fp4(int f) { return f == W_MXFP4 || f == W_NVFP4; }
 enum : int { EPI_SILU_MUL = 0, EPI_ROW_SCALE = 1, EPI_SHARED_DOWN = 2, EPI_PLAIN = 3 };
 
 struct SkinnyArgs {
@@ -40,6 +43,7 @@ struct SkinnyArgs {
   const __nv_bfloat16* resid;  // EPI_SHARED_DOWN: residual [T, out_stride]
   const float* gate;       // EPI_SHARED_DOWN: pre-sigmoid gate per token
   const float* bias;       // EPI_PLAIN: optional per-row bias
+  const float* tensor_scale;  // W_NVFP4: the weight's fp32 scale [1]
   const float* row_div;    // EPI_PLAIN: optional per-token divisor applied to the bf16-rounded product (folded RMSNorm)
   const __nv_bfloat16* resid2;  // EPI_PLAIN: optional residual [T, out_stride] added to the bf16-rounded product
   int* status;
@@ -51,6 +55,7 @@ template <int FMT> struct WTraits;
 template <> struct WTraits<W_MXFP4> { static constexpr int KIT = 256, PAD_UNITS = 4, BIAS = 63; };
 template <> struct WTraits<W_MXFP8> { static constexpr int KIT = 128, PAD_UNITS = 1, BIAS = 57; };
 template <> struct WTraits<W_FP8ROW> { static constexpr int KIT = 128, PAD_UNITS = 1, BIAS = 57; };
+template <> struct WTraits<W_NVFP4> { static constexpr int KIT = 256, PAD_UNITS = 4, BIAS = 63; };
 
 __device__ __forceinline__ uint32_t bf16x2_mul(uint32_t a, uint32_t b) {
   uint32_t d;
@@ -61,7 +66,7 @@ __device__ __forceinline__ uint32_t bf16x2_mul(uint32_t a, uint32_t b) {
 // physical 16-byte unit of logical unit u inside an activation row (bank-conflict-free fragment reads)
 template <int FMT>
 __device__ __forceinline__ int swz_unit(int u) {
-  if constexpr (FMT == W_MXFP4) return u ^ ((u >> 3) & 3);
+  if constexpr (fmt_is_fp4(FMT)) return u ^ ((u >> 3) & 3);
   else return u ^ (((u >> 3) & 1) << 1);
 }
 
@@ -91,8 +96,8 @@ __global__ void __launch_bounds__(128) skinny_gemm_kernel(const SkinnyArgs a) {
   if (n <= 0) return;
 
   const int row_base = blockIdx.x * a.tile_rows + warp * a.warp_rows;
-  const int wrow_bytes = FMT == W_MXFP4 ? a.K / 2 : a.K;
-  const int srow = a.K / 32;
+  const int wrow_bytes = fmt_is_fp4(FMT) ? a.K / 2 : a.K;
+  const int srow = FMT == W_NVFP4 ? a.K / 16 : a.K / 32;
   // rows this lane streams: [stream][half]; out-of-range rows are clamped for loads and masked at the end
   int rows_l[2][2];
   bool rok[2][2];
@@ -110,6 +115,7 @@ __global__ void __launch_bounds__(128) skinny_gemm_kernel(const SkinnyArgs a) {
       const int rr = rok[st][h] ? rows_l[st][h] : 0;
       wptr[st][h] = wp + (long long)rr * wrow_bytes + c * 32;
       if constexpr (FMT == W_MXFP4) sptr[st][h] = sp[st] + (long long)rr * srow + c * 2;
+      else if constexpr (FMT == W_NVFP4) sptr[st][h] = sp[st] + (long long)rr * srow + c * 4;
       else if constexpr (FMT == W_MXFP8) sptr[st][h] = sp[st] + (long long)rr * srow + c;
       else sptr[st][h] = sp[st];
     }
@@ -138,6 +144,7 @@ __global__ void __launch_bounds__(128) skinny_gemm_kernel(const SkinnyArgs a) {
           wd[st][h][0] = ldg_nc_16(p);
           wd[st][h][1] = ldg_nc_16(p + 16);
           if constexpr (FMT == W_MXFP4) sd[st][h] = *reinterpret_cast<const unsigned short*>(sptr[st][h] + it * 8);
+          else if constexpr (FMT == W_NVFP4) sd[st][h] = *reinterpret_cast<const uint32_t*>(sptr[st][h] + it * 16);
           else if constexpr (FMT == W_MXFP8) sd[st][h] = *(sptr[st][h] + it * 4);
           else sd[st][h] = 127;
         }
@@ -158,7 +165,7 @@ __global__ void __launch_bounds__(128) skinny_gemm_kernel(const SkinnyArgs a) {
           const long long xr = a.src ? a.src[dst] : dst;
           v = *reinterpret_cast<const uint4*>(a.x + xr * a.x_stride + kc + u * 8);
           uint4 o;
-          if constexpr (FMT == W_MXFP4) {
+          if constexpr (fmt_is_fp4(FMT)) {
             o.x = __byte_perm(v.x, v.z, 0x5410); o.y = __byte_perm(v.x, v.z, 0x7632);
             o.z = __byte_perm(v.y, v.w, 0x5410); o.w = __byte_perm(v.y, v.w, 0x7632);
           } else {
@@ -177,12 +184,20 @@ __global__ void __launch_bounds__(128) skinny_gemm_kernel(const SkinnyArgs a) {
       for (int it = it0; it < it1; ++it) {
         if (it + 1 < n_it) load_w(it + 1, wnxt, snxt);
         // per-block multipliers: 2^(s - 127) folded with the exponent re-bias of the bit trick
-        uint32_t mult[2][2][2];
+        uint32_t mult[2][2][FMT == W_NVFP4 ? 4 : 2];
 #pragma unroll
         for (int st = 0; st < 2; ++st)
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
-            if constexpr (FMT == W_MXFP4) {
+            if constexpr (FMT == W_NVFP4) {
+              // four E4M3 scales (k 0-15, 16-31, 32-47, 48-63 of this lane's 64 inputs) times the 2^63 of the bit trick
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const __half_raw hr = __nv_cvt_fp8_to_halfraw(__nv_fp8_storage_t((scur[st][h] >> (8 * j)) & 0xff), __NV_E4M3);
+                const float f = __half2float(*reinterpret_cast<const __half*>(&hr)) * 9223372036854775808.f;
+                mult[st][h][j] = uint32_t(__bfloat16_as_ushort(__float2bfloat16_rn(f))) * 0x00010001u;
+              }
+            } else if constexpr (FMT == W_MXFP4) {
               mult[st][h][0] = (((scur[st][h] & 0xff) + TR::BIAS) << 7) * 0x00010001u;
               mult[st][h][1] = (((scur[st][h] >> 8) + TR::BIAS) << 7) * 0x00010001u;
             } else {
@@ -194,7 +209,7 @@ __global__ void __launch_bounds__(128) skinny_gemm_kernel(const SkinnyArgs a) {
         for (int q = 0; q < 2; ++q) {          // the two 16-byte loads of this iteration
 #pragma unroll
           for (int wi = 0; wi < 4; ++wi) {     // words of the load
-            if constexpr (FMT == W_MXFP4) {
+            if constexpr (fmt_is_fp4(FMT)) {
               const int j = q * 4 + wi;        // activation unit of this word (8 nibbles = 8 k)
               uint4 bx[NT];
 #pragma unroll
@@ -203,7 +218,8 @@ __global__ void __launch_bounds__(128) skinny_gemm_kernel(const SkinnyArgs a) {
               for (int st = 0; st < 2; ++st) {
                 const uint32_t w0 = reinterpret_cast<const uint32_t*>(&wcur[st][0][q])[wi];
                 const uint32_t w1 = reinterpret_cast<const uint32_t*>(&wcur[st][1][q])[wi];
-                const uint32_t m0 = mult[st][0][q], m1 = mult[st][1][q];
+                const int mi = FMT == W_NVFP4 ? q * 2 + (wi >> 1) : q;  // NVFP4: a scale per 16 inputs = two words
+                const uint32_t m0 = mult[st][0][mi], m1 = mult[st][1][mi];
                 const uint32_t p0 = bf16x2_mul(((w0 << 6) & 0x01C001C0u) | ((w0 << 12) & 0x80008000u), m0);
                 const uint32_t p1 = bf16x2_mul(((w0 << 2) & 0x01C001C0u) | ((w0 << 8) & 0x80008000u), m0);
                 const uint32_t p2 = bf16x2_mul(((w0 >> 2) & 0x01C001C0u) | ((w0 << 4) & 0x80008000u), m0);
@@ -275,6 +291,7 @@ __global__ void __launch_bounds__(128) skinny_gemm_kernel(const SkinnyArgs a) {
             const int row = rows_l[st][h];
             float v = acc[st][nt][i];
             if constexpr (FMT == W_FP8ROW) v *= reinterpret_cast<const float*>(sp[st])[row];
+            if constexpr (FMT == W_NVFP4) v *= a.tensor_scale ? a.tensor_scale[0] : 1.f;
             if constexpr (EPI == EPI_ROW_SCALE) {
               v *= a.rw_row[dst];
               if (a.f_out) a.f_out[(long long)dst * a.out_stride + row] = v;

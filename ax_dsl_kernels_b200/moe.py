@@ -175,13 +175,16 @@ def moe_block(x1, w, top_k, out=None, overlap=True):
     return out, ids, rw, logits
 
 
-def linear(x, w, s, out=None, bias=None, out_dtype=torch.bfloat16, row_div=None, residual=None):
+def linear(x, w, s, out=None, bias=None, out_dtype=torch.bfloat16, row_div=None, residual=None, s2=None):
     """x [T, K] bf16 times a quantised weight [N, K]: MXFP4 (uint8 [N, K/2] + E8M0 [N, K/32]), MXFP8 (e4m3 [N, K] +
-    E8M0) or FP8 per-row (e4m3 [N, K] + fp32 [N]; fp8_gemm with scale_a = 1,
-    models/qwen35_35b_a3b/sgl/python/sgl_kernel_axera/gemm.py:457-466)."""
+    E8M0), FP8 per-row (e4m3 [N, K] + fp32 [N]; fp8_gemm with scale_a = 1,
+    models/qwen35_35b_a3b/sgl/python/sgl_kernel_axera/gemm.py:457-466) or NVFP4 (uint8 [N, K/2] + float8_e4m3fn scales
+    [N, K/16] + the fp32 tensor scale s2 [1]; quantize_nvfp4, .../sgl_kernel_axera/quantization.py:8-37)."""
     T, N = x.shape[0], w.shape[0]
     out = torch.empty((T, N), dtype=out_dtype, device=x.device) if out is None else out
-    kw = dict(x=x, w=w, s=s if s.dtype == torch.float32 else _u8(s), out=out)
+    kw = dict(x=x, w=w, s=s if s.dtype in (torch.float32, torch.float8_e4m3fn) else _u8(s), out=out)
+    if s2 is not None:
+        kw["s2"] = s2
     if bias is not None:
         kw["bias"] = bias
     if row_div is not None:  # per-token divisor applied to the bf16-rounded product (folded RMSNorm of the GDN sublayer)
@@ -201,7 +204,7 @@ def linear_multi(x, w, s, sizes, row_div=None, bias=None, out_dtype=torch.bfloat
         raise ValueError("linear_multi: at most 8 projections whose rows add up to the weight's")
     T = x.shape[0]
     outs = [torch.empty((T, n), dtype=out_dtype, device=x.device) for n in sizes]
-    kw = dict(x=x, w=w, s=s if s.dtype == torch.float32 else _u8(s))
+    kw = dict(x=x, w=w, s=s if s.dtype in (torch.float32, torch.float8_e4m3fn) else _u8(s))
     kw.update({f"out{i}": o for i, o in enumerate(outs)})
     if row_div is not None:
         kw["row_div"] = row_div

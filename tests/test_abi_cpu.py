@@ -128,3 +128,15 @@ def test_reference_manifest_roles_bind_to_library_roles():
         manifest.check_role(bad, "lm_head")
     with pytest.raises(KeyError):
         manifest.check_role(m, "decode.group")
+
+
+def test_every_role_table_is_valid_json_with_named_typed_entries():
+    """q35_io_table(role) for every role: parses, and every entry is [name, dtype alternatives, shape text]"""
+    import json
+    from ax_dsl_kernels_b200 import _lib
+    for role in _lib.roles():
+        t = json.loads(_lib.io_table(role)) if isinstance(_lib.io_table(role), str) else _lib.io_table(role)
+        assert set(t) == {"in", "out"} and t["out"], role
+        for e in t["in"] + t["out"]:
+            assert len(e) == 3 and all(isinstance(v, str) and v for v in e), (role, e)
+            assert set(e[1].split("|")) <= {"u8", "f32", "i32", "bf16", "f16", "e4m3", "fp4"}, (role, e)

@@ -268,6 +268,24 @@ def test_linear_multi_fused_rows(q35, fmt, T):
     assert rel_rms_err(torch.cat([t.cpu() for t in f32], 1), x.float() @ dequant(w, s).T) <= 2e-3
 
 
+@pytest.mark.parametrize("T,N,K", [(1, 48, 512), (8, 256, 2048), (33, 130, 1024)])
+def test_linear_nvfp4_weights(q35, T, N, K):
+    """NVFP4 weights (E2M1 pairs, E4M3 scale per 16 inputs, fp32 tensor scale) in the `linear` role, against the
+    reference's quantiser / dequantiser restated in the oracle (pinned to the reference's own output by the fixture)"""
+    g = torch.Generator().manual_seed(N + K + 1)
+    x = torch.randn((T, K), generator=g).to(torch.bfloat16)
+    wf = torch.randn((N, K), generator=g) * 0.05 * torch.exp2(torch.randint(-4, 3, (N, 1), generator=g).float())
+    pk, sc, s2 = codecs.quant_nvfp4(wf)
+    ref = x.float() @ codecs.dequant_nvfp4(pk, sc, s2).T
+    out = q35.linear(x.cuda(), pk.cuda(), sc.cuda(), s2=s2.cuda(), out_dtype=torch.float32)
+    assert rel_rms_err(out.cpu(), ref) <= 2e-3
+    bias = torch.randn(N, generator=g)
+    outb = q35.linear(x.cuda(), pk.cuda(), sc.cuda(), s2=s2.cuda(), bias=bias.cuda())
+    assert rel_rms_err(outb.cpu(), (ref + bias).to(torch.bfloat16)) <= TOL
+    with pytest.raises(q35.Q35Error):  # the fused form is tensor-core only, which has no NVFP4 kind for bf16-class inputs
+        q35.moe.linear_multi(x.cuda(), pk.cuda(), sc.cuda(), [N])
+
+
 # ------------------------------------------------------------------------------------------------ attention
 def _attn_check(q35, ctxs, P=64, HKV=2, HQ=16, D=256, fp8=False, per_head=True, sm_scale=None, seed=1):
     q, cache, indptr, indices, last, kvs = paged_case(ctxs, P=P, HKV=HKV, HQ=HQ, D=D, seed=seed, fp8=fp8,
