@@ -33,6 +33,56 @@ __global__ void __launch_bounds__(256) rms_kernel(const __nv_bfloat16* __restric
                                                   float* xsqrt_out, int H, const float* eps_ptr, int folded) {
   __shared__ float red[32];
   const int t = blockIdx.x;
+  // rows of up to 8192 channels in multiples of 8, 16-byte aligned: every thread keeps its (at most four) 16-byte
+  // pieces of the row in registers, so the row is read once and all loads of a thread are in flight together -- a
+  // decode step normalises a handful of rows and the latency of a load chain is all this kernel costs
+  const bool vec = (H & 7) == 0 && H <= 8 * 256 * RMS_MAX_PIECES && blockDim.x == 256 &&
+                   ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(residual) |
+                     reinterpret_cast<uintptr_t>(base_out) | reinterpret_cast<uintptr_t>(w)) & 15) == 0;
+  if (vec) {
+    RmsPieces p, r;
+    rms_load(x + size_t(t) * H, H, threadIdx.x, p);
+    if (residual) {
+      rms_load(residual + size_t(t) * H, H, threadIdx.x, r);
+#pragma unroll
+      for (int c = 0; c < RMS_MAX_PIECES; ++c) {
+        uint32_t* pv = reinterpret_cast<uint32_t*>(&p.v[c]);
+        const uint32_t* rv = reinterpret_cast<const uint32_t*>(&r.v[c]);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) pv[u] = pack_bf16(bf16lo(pv[u]) + bf16lo(rv[u]), bf16hi(pv[u]) + bf16hi(rv[u]));
+      }
+    }
+    const float tot = block_sum(rms_sumsq(p), red);
+    const float var = tot / float(H) + (eps_ptr ? eps_ptr[0] : 1e-6f);
+    const float rs = folded ? 1.f : rsqrtf(var);
+    if (folded && threadIdx.x == 0) xsqrt_out[t] = sqrtf(var);
+#pragma unroll
+    for (int c = 0; c < RMS_MAX_PIECES; ++c) {
+      const int i = (threadIdx.x + 256 * c) * 8;
+      if (i >= H) break;
+      if (base_out) *reinterpret_cast<uint4*>(base_out + size_t(t) * H + i) = p.v[c];
+      float wv[8];
+      if (w_bf16) {
+        const uint4 wq = *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(w) + i);
+        const uint32_t ww[4] = {wq.x, wq.y, wq.z, wq.w};
+#pragma unroll
+        for (int u = 0; u < 4; ++u) { wv[2 * u] = bf16lo(ww[u]); wv[2 * u + 1] = bf16hi(ww[u]); }
+      } else {
+        const float4 w0 = *reinterpret_cast<const float4*>(static_cast<const float*>(w) + i);
+        const float4 w1 = *reinterpret_cast<const float4*>(static_cast<const float*>(w) + i + 4);
+        wv[0] = w0.x; wv[1] = w0.y; wv[2] = w0.z; wv[3] = w0.w; wv[4] = w1.x; wv[5] = w1.y; wv[6] = w1.z; wv[7] = w1.w;
+      }
+      const uint32_t pv[4] = {p.v[c].x, p.v[c].y, p.v[c].z, p.v[c].w};
+      uint32_t o[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const float a = bf16lo(pv[u]), b = bf16hi(pv[u]);
+        o[u] = folded ? pack_bf16(a * wv[2 * u], b * wv[2 * u + 1]) : pack_bf16(a * rs * wv[2 * u], b * rs * wv[2 * u + 1]);
+      }
+      *reinterpret_cast<uint4*>(y + size_t(t) * H + i) = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+    return;
+  }
   float ss = 0.f;
   for (int i = threadIdx.x; i < H; i += blockDim.x) {
     float v = __bfloat162float(x[size_t(t) * H + i]);
@@ -93,7 +143,8 @@ __global__ void __launch_bounds__(128) gdn_prep_kernel(const __nv_bfloat16* __re
   const int row = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const float qscale = rsqrtf(float(DK));
-  for (int h = warp; h < 2 * NK; h += 4) {  // heads of q then heads of k
+  // heads of q then heads of k, one per warp: blockIdx.y spreads them over CTAs (a decode step has few rows)
+  for (int h = warp + 4 * blockIdx.y; h < 2 * NK; h += 4 * gridDim.y) {
     const bool is_k = h >= NK;
     const __nv_bfloat16* src = (is_k ? k : q) + (size_t(row) * NK + (is_k ? h - NK : h)) * DK;
     __nv_bfloat16* dst = (is_k ? kn : qn) + (size_t(row) * NK + (is_k ? h - NK : h)) * DK;
@@ -107,6 +158,7 @@ __global__ void __launch_bounds__(128) gdn_prep_kernel(const __nv_bfloat16* __re
       dst[i] = __float2bfloat16_rn(v);
     }
   }
+  if (blockIdx.y != 0) return;
   for (int h = threadIdx.x; h < NV; h += blockDim.x) {
     const float av = __bfloat162float(a[size_t(row) * NV + h]) + load_w(dt_bias, dt_bf16, h);
     const float sp = av > 20.f ? av : log1pf(expf(av));
@@ -134,7 +186,7 @@ int run_gdn_prep(Call& c) {
                   dtb.numel() == NV, Q35_ERR_SHAPE, "gdn.prep: a / b / g / beta [R, NV], dt_bias [NV]");
   c.ws_need = 0;
   if (c.dry || R == 0) return 0;
-  gdn_prep_kernel<<<unsigned(R), 128, 0, c.stream>>>(q.as<__nv_bfloat16>(), k.as<__nv_bfloat16>(), a.as<__nv_bfloat16>(),
+  gdn_prep_kernel<<<dim3(unsigned(R), unsigned((2 * NK + 3) / 4)), 128, 0, c.stream>>>(q.as<__nv_bfloat16>(), k.as<__nv_bfloat16>(), a.as<__nv_bfloat16>(),
                                                      b.as<__nv_bfloat16>(), alog.as<float>(), dtb.p, dtb.dtype == Q35_BF16,
                                                      qn.as<__nv_bfloat16>(), kn.as<__nv_bfloat16>(), g.as<float>(),
                                                      beta.as<__nv_bfloat16>(), int(NK), int(NV), int(DK));
@@ -149,7 +201,7 @@ __global__ void __launch_bounds__(128) gdn_out_norm_kernel(const __nv_bfloat16* 
                                                            __nv_bfloat16* __restrict__ y, int heads, int DV, const float* eps_ptr) {
   const int row = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const float eps = eps_ptr ? eps_ptr[0] : 1e-6f;
-  for (int h = warp; h < heads; h += 4) {
+  for (int h = warp + 4 * blockIdx.y; h < heads; h += 4 * gridDim.y) {  // one head per warp, heads over blockIdx.y
     const size_t o = (size_t(row) * heads + h) * DV;
     float ss = 0.f;
     for (int i = lane; i < DV; i += 32) { const float v = __bfloat162float(core[o + i]); ss += v * v; }
@@ -175,7 +227,7 @@ int run_gdn_out_norm(Call& c) {
   Q35_REQUIRE(z.numel() == core.numel() && y.numel() == core.numel() && w.numel() == DV, Q35_ERR_SHAPE, "gdn.out_norm: shapes");
   c.ws_need = 0;
   if (c.dry || R == 0) return 0;
-  gdn_out_norm_kernel<<<unsigned(R), 128, 0, c.stream>>>(core.as<__nv_bfloat16>(), z.as<__nv_bfloat16>(), w.p,
+  gdn_out_norm_kernel<<<dim3(unsigned(R), unsigned((NV + 3) / 4)), 128, 0, c.stream>>>(core.as<__nv_bfloat16>(), z.as<__nv_bfloat16>(), w.p,
                                                          w.dtype == Q35_BF16, y.as<__nv_bfloat16>(), int(NV), int(DV),
                                                          eps.present ? eps.as<float>() : nullptr);
   Q35_CUDA_LAUNCH_CHECK("gdn.out_norm");
@@ -195,7 +247,7 @@ __global__ void __launch_bounds__(256) attn_qk_prep_kernel(const __nv_bfloat16* 
   const int row = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int half = rot / 2;
   const float eps = eps_ptr ? eps_ptr[0] : 1e-6f;
-  for (int h = warp; h < HQ + HKV; h += 8) {
+  for (int h = warp + 8 * blockIdx.y; h < HQ + HKV; h += 8 * gridDim.y) {  // one head per warp, heads over blockIdx.y
     const bool is_k = h >= HQ;
     const int hh = is_k ? h - HQ : h;
     const __nv_bfloat16* src = is_k ? k + (size_t(row) * HKV + hh) * D : qg + (size_t(row) * HQ + hh) * (gated ? 2 * D : D);
@@ -245,7 +297,7 @@ int run_attn_qk_prep(Call& c) {
   Q35_REQUIRE(rot <= D && rot % 2 == 0 && (!gated || go.numel() == R * HQ * D), Q35_ERR_SHAPE, "attn.qk_prep: rot / gate_out");
   c.ws_need = 0;
   if (c.dry || R == 0) return 0;
-  attn_qk_prep_kernel<<<unsigned(R), 256, 0, c.stream>>>(
+  attn_qk_prep_kernel<<<dim3(unsigned(R), unsigned((HQ + HKV + 7) / 8)), 256, 0, c.stream>>>(
       qg.as<__nv_bfloat16>(), k.as<__nv_bfloat16>(), qw.as<float>(), kw.as<float>(), cs.as<float>(), sn.as<float>(),
       qo.as<__nv_bfloat16>(), ko.as<__nv_bfloat16>(), gated ? go.as<__nv_bfloat16>() : nullptr, int(HQ), int(HKV),
       int(D), int(rot), gated, eps.present ? eps.as<float>() : nullptr);
