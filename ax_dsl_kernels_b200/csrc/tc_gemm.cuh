@@ -186,33 +186,7 @@ __global__ void __launch_bounds__(TcCfg<NB>::THREADS, TcCfg<NB>::CTAS_PER_SM) tc
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *g_slot;
-  // Everything above touches only this CTA's shared and tensor memory and may overlap the previous kernel's tail.  So
-  // may the first weight tiles of a dense launch: its work items are plain arithmetic and its weights are not written
-  // by any kernel of the step, so the producer puts the weight halves of its first stages in flight BEFORE the
-  // dependency wait (their barriers already expect the whole stage) and adds the activation halves after it.  A
-  // decode-sized projection is a launch of some ten microseconds; this takes the ramp out of each.
-  uint32_t pre = 0;
-  if (warp == 0) {
-    if (lane == 0 && a.g_n == nullptr) {
-      const int n_dense_items = (a.n_dense + a.dense_rows - 1) / a.dense_rows * a.n_tiles * a.k_slices;
-      TcItem f;
-      if (int(blockIdx.x) < n_dense_items) {
-        tc_load_item(a, int(blockIdx.x), &f);
-        if (f.n > 0) {
-          const int ks0 = f.slice * a.slice_stages, ks1 = min(KS, (f.slice + 1) * a.slice_stages);
-          const int r0 = f.tile * a.tile_rows + a.roff[0], r1 = f.tile * a.tile_rows + a.roff[1];
-          pre = uint32_t(min(C::STAGES, ks1 - ks0));
-          for (uint32_t j = 0; j < pre; ++j) {
-            mbar_expect_tx(full_bar(int(j)), uint32_t(a.stage_tx));
-            const uint32_t sa = s_stage + j * C::STAGE_BYTES;
-            tma_load_2d(sa, &wmap0, full_bar(int(j)), (ks0 + int(j)) * 128, r0);
-            tma_load_2d(sa + 8192, &wmap1, full_bar(int(j)), (ks0 + int(j)) * 128, r1);
-          }
-        }
-      }
-    }
-    pre = __shfl_sync(0xffffffffu, pre, 0);
-  }
+  // everything above touches only this CTA's shared and tensor memory and may overlap the previous kernel's tail
   pdl_wait();
   pdl_launch();
   // a CTA without work walks empty loops and falls through to the release of its tensor memory
@@ -234,13 +208,11 @@ __global__ void __launch_bounds__(TcCfg<NB>::THREADS, TcCfg<NB>::CTAS_PER_SM) tc
         for (int t0 = 0; t0 < im.n && !dead; t0 += NB) {
           for (int ks = ks0; ks < ks1; ++ks, ++it) {
             const uint32_t s = it % C::STAGES, ph = (it / C::STAGES) & 1;
+            if (!mbar_wait(empty_bar(s), ph ^ 1)) { atomicOr(a.status, DS_WAIT_TIMEOUT | 0x10); dead = true; break; }
+            mbar_expect_tx(full_bar(s), uint32_t(a.stage_tx));
             const uint32_t sa = s_stage + s * C::STAGE_BYTES, sb = sa + C::A_BYTES;
-            if (it >= pre) {  // (the first `pre` stages got their barrier set up and their weights before the wait)
-              if (!mbar_wait(empty_bar(s), ph ^ 1)) { atomicOr(a.status, DS_WAIT_TIMEOUT | 0x10); dead = true; break; }
-              mbar_expect_tx(full_bar(s), uint32_t(a.stage_tx));
-              tma_load_2d(sa, &wmap0, full_bar(s), ks * 128, im.plane * a.plane_rows[0] + r0);
-              tma_load_2d(sa + 8192, &wmap1, full_bar(s), ks * 128, im.plane * a.plane_rows[1] + r1);
-            }
+            tma_load_2d(sa, &wmap0, full_bar(s), ks * 128, im.plane * a.plane_rows[0] + r0);
+            tma_load_2d(sa + 8192, &wmap1, full_bar(s), ks * 128, im.plane * a.plane_rows[1] + r1);
             tma_load_2d(sb, &xmap_hi, full_bar(s), ks * 128, im.row0 + t0);
             tma_load_2d(sb + NB * 128, &xmap_lo, full_bar(s), ks * 128, im.row0 + t0);
           }
