@@ -48,6 +48,7 @@ struct AttnArgs {
   float* lse_m; float* lse_l; float* lse_o;   // [B, HQ], [B, HQ], [B, HQ, D] -- or one packed [B, HQ, D + 2] block
   int lse_os, lse_ms;                         // floats between rows of lse_o, between entries of lse_m / lse_l
   int B, HQ, HKV, G, P, num_pages, n_indices, n_cta;
+  int wpc;              // warps per CTA of the decode kernel = partial slots per (segment, CTA)
   // workspace
   AttnPlan* plan;
   int* seg_start;   // [B * HKV + 1]
@@ -102,17 +103,21 @@ __global__ void __launch_bounds__(1024) attn_plan_kernel(AttnArgs a) {
 // KVF: cache element format.  0 = bf16, 1 = FP8 E4M3 (one scale per head or the constant 1 / 8), 2 = int8 with a bf16
 // scale per cached row and head (kv_quant_row, models/qwen38_27b/decode/q35_group.py:198-205).  The two one-byte
 // formats share the byte-wise fragment paths; they differ in the conversion to f16 and in where the scale enters.
-template <int D, int KVF>
+// WARPS: 4, or 8 = two groups of four warps that take alternate tiles of the CTA's range.  One warp per scheduler is
+// enough while a tile's bytes take longer to arrive than its dependent chain (load fragments, convert, MMA, softmax,
+// MMA) takes to run; with one-byte elements the tile arrives in half the time and the chain becomes the limit, so
+// those formats run two warps per scheduler with half the stages each (the same bytes in flight).
+template <int D, int KVF, int WARPS>
 struct AttnCfg {
   static constexpr bool FP8 = KVF != 0;
   static constexpr int ELT = FP8 ? 1 : 2;
-  static constexpr int STAGES = FP8 ? 6 : 3;    // same bytes in flight for both cache types
+  static constexpr int STAGES = (FP8 && WARPS == 4) ? 6 : 3;    // same bytes in flight in every variant
   static constexpr int ROWB = D * ELT;            // bytes of one key row of one head
   static constexpr int CPR = ROWB / 16;           // 16-byte chunks per row
   static constexpr int KV_BYTES = AT_WKEYS * ROWB;  // K (or V) bytes per warp per stage
   static constexpr int STAGE_BYTES = 2 * KV_BYTES;
   static constexpr int WARP_BYTES = STAGES * STAGE_BYTES;
-  static constexpr int SMEM = 4 * WARP_BYTES;
+  static constexpr int SMEM = WARPS * WARP_BYTES;
   static constexpr int LD_PER_LANE = AT_WKEYS * CPR / 32;
 };
 
@@ -139,15 +144,17 @@ __device__ __forceinline__ uint32_t cvt_s8x2_bf16x2(uint32_t xs, float s0, float
   return pack_bf16(fmaf(f0, s0, -8388736.f * s0), fmaf(f1, s1, -8388736.f * s1));
 }
 
-template <int D, int KVF>
-__global__ void __launch_bounds__(128, 1) attn_decode_kernel(const AttnArgs a) {
+template <int D, int KVF, int WARPS>
+__global__ void __launch_bounds__(32 * WARPS, 1) attn_decode_kernel(const AttnArgs a) {
   pdl_wait();
   pdl_launch();
-  using C = AttnCfg<D, KVF>;
+  using C = AttnCfg<D, KVF, WARPS>;
+  constexpr int TG = WARPS / 4;  // tiles in flight per CTA: warp group wg takes tiles t_begin + wg, + TG, ...
   constexpr bool FP8 = C::FP8;
   constexpr int AT_STAGES = C::STAGES;
   extern __shared__ __align__(128) uint8_t smem[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int wk = warp & 3, wg = warp >> 2;  // key quarter of a tile, tile group
   const int r = lane >> 2, c = lane & 3;
   const uint32_t sbase = smem_u32(smem) + warp * C::WARP_BYTES;
 
@@ -173,6 +180,7 @@ __global__ void __launch_bounds__(128, 1) attn_decode_kernel(const AttnArgs a) {
     const int seg0 = a.seg_start[s];
     const int t_begin = g - seg0;
     const int t_end = min(g_end, a.seg_start[s + 1]) - seg0;
+    const int t_first = t_begin + wg;  // this warp group's first tile
     const int ctx = a.ctx[b];
     const int page0 = a.indptr[b];
 
@@ -215,7 +223,7 @@ __global__ void __launch_bounds__(128, 1) attn_decode_kernel(const AttnArgs a) {
     auto load_scales = [&](int t) -> uint3 {
       uint3 v = make_uint3(0u, 0u, 0u);
       if constexpr (KVF == 2) {
-        const int kk = t * AT_TILE + warp * AT_WKEYS;
+        const int kk = t * AT_TILE + wk * AT_WKEYS;
         if (t < t_end && kk < ctx) {
           const int pl = kk / a.P, ro = kk % a.P, valid = ctx - kk;
           int page = a.indices[page0 + pl];
@@ -238,7 +246,7 @@ __global__ void __launch_bounds__(128, 1) attn_decode_kernel(const AttnArgs a) {
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
 
     auto issue = [&](int t) {  // t: tile index inside the sequence
-      const int kk = t * AT_TILE + warp * AT_WKEYS;
+      const int kk = t * AT_TILE + wk * AT_WKEYS;
       if (t < t_end && kk < ctx) {
         const int pl = kk / a.P, ro = kk % a.P;
         int page = a.indices[page0 + pl];
@@ -248,7 +256,7 @@ __global__ void __launch_bounds__(128, 1) attn_decode_kernel(const AttnArgs a) {
         }
         const uint8_t* kb = cache + ((size_t(page) * 2 + 0) * a.P + ro) * row_stride + size_t(kvh) * C::ROWB;
         const uint8_t* vb = cache + ((size_t(page) * 2 + 1) * a.P + ro) * row_stride + size_t(kvh) * C::ROWB;
-        const uint32_t st = sbase + ((t - t_begin) % AT_STAGES) * C::STAGE_BYTES;
+        const uint32_t st = sbase + (((t - t_first) / TG) % AT_STAGES) * C::STAGE_BYTES;
 #pragma unroll
         for (int j = 0; j < C::LD_PER_LANE; ++j) {
           const int ci = lane + 32 * j;
@@ -262,18 +270,18 @@ __global__ void __launch_bounds__(128, 1) attn_decode_kernel(const AttnArgs a) {
     };
 
 #pragma unroll
-    for (int p = 0; p < AT_STAGES - 1; ++p) issue(t_begin + p);
-    uint3 rs_cur = load_scales(t_begin), rs_n1 = load_scales(t_begin + 1), rs_n2 = make_uint3(0u, 0u, 0u);
+    for (int p = 0; p < AT_STAGES - 1; ++p) issue(t_first + p * TG);
+    uint3 rs_cur = load_scales(t_first), rs_n1 = load_scales(t_first + TG), rs_n2 = make_uint3(0u, 0u, 0u);
 
-    for (int t = t_begin; t < t_end; ++t) {
-      issue(t + AT_STAGES - 1);
-      rs_n2 = load_scales(t + 2);
+    for (int t = t_first; t < t_end; t += TG) {
+      issue(t + (AT_STAGES - 1) * TG);
+      rs_n2 = load_scales(t + 2 * TG);
       cp_async_wait<AT_STAGES - 1>();
       __syncwarp();
-      const int kk = t * AT_TILE + warp * AT_WKEYS;
+      const int kk = t * AT_TILE + wk * AT_WKEYS;
       if (kk < ctx) {
         const int valid = min(AT_WKEYS, ctx - kk);
-        const uint32_t st = sbase + ((t - t_begin) % AT_STAGES) * C::STAGE_BYTES;
+        const uint32_t st = sbase + (((t - t_first) / TG) % AT_STAGES) * C::STAGE_BYTES;
         if (valid < AT_WKEYS) {  // rows past the context may hold anything (NaN bits included): clear V
           for (int idx = lane; idx < (AT_WKEYS - valid) * C::CPR; idx += 32) {
             const uint32_t addr = st + C::KV_BYTES + (valid + idx / C::CPR) * C::ROWB + ((idx % C::CPR) << 4);
@@ -415,14 +423,14 @@ __global__ void __launch_bounds__(128, 1) attn_decode_kernel(const AttnArgs a) {
     }
     cp_async_wait<0>();
 
-    // partial of this (segment, CTA, warp): slot = (s + cta) * 4 + warp
+    // partial of this (segment, CTA, warp): slot = (s + cta) * WARPS + warp (a warp group without a tile leaves l = 0)
     {
 #pragma unroll
       for (int o = 4; o < 32; o <<= 1) {
         l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], o);
         l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], o);
       }
-      const size_t slot = size_t(s + blockIdx.x) * 4 + warp;
+      const size_t slot = size_t(s + blockIdx.x) * WARPS + warp;
       float* ml = a.part_ml + slot * 16;
       if (r == 0) {
         ml[2 * c] = m_run[0]; ml[2 * c + 1] = m_run[1];
@@ -459,8 +467,8 @@ __global__ void __launch_bounds__(D / 2) attn_merge_kernel(const AttnArgs a) {
   if (seg1 > seg0) {
     // Two passes so that no load waits for arithmetic on the previous one: first the maximum over the segment's
     // partials, then every partial scaled by exp2(m - M) and added (slots: 4 warps of each CTA that touched it).
-    const size_t slot0 = (size_t(s) + seg0 / q_per) * 4;
-    const int ns = ((seg1 - 1) / q_per - seg0 / q_per + 1) * 4;
+    const size_t slot0 = (size_t(s) + seg0 / q_per) * a.wpc;
+    const int ns = ((seg1 - 1) / q_per - seg0 / q_per + 1) * a.wpc;
 #pragma unroll 4
     for (int j = 0; j < ns; ++j) {
       const float m = a.part_ml[(slot0 + j) * 16 + gq];
@@ -681,14 +689,15 @@ int run_attn_kv_write(Call& c) {
   return 0;
 }
 
-template <int D, int KVF>
+template <int D, int KVF, int WARPS = 4>
 static int launch_attn(const AttnArgs& a, cudaStream_t stream) {
-  using C = AttnCfg<D, KVF>;
-  Q35_TRY(ensure_dynamic_smem(reinterpret_cast<const void*>(attn_decode_kernel<D, KVF>), C::SMEM));
+  using C = AttnCfg<D, KVF, WARPS>;
+  Q35_REQUIRE(a.wpc == WARPS, Q35_ERR_CUDA, "attention decode: partial slots sized for %d warps, kernel has %d", a.wpc, WARPS);
+  Q35_TRY(ensure_dynamic_smem(reinterpret_cast<const void*>(attn_decode_kernel<D, KVF, WARPS>), C::SMEM));
   Q35_REQUIRE(a.status != nullptr, Q35_ERR_CUDA, "attention decode: no device status word");
   launch_pdl(attn_plan_kernel, dim3(1), dim3(1024), 0, stream, a);
   Q35_CUDA_LAUNCH_CHECK("attn plan");
-  launch_pdl(attn_decode_kernel<D, KVF>, dim3(unsigned(a.n_cta)), dim3(128), C::SMEM, stream, a);
+  launch_pdl(attn_decode_kernel<D, KVF, WARPS>, dim3(unsigned(a.n_cta)), dim3(32 * WARPS), C::SMEM, stream, a);
   Q35_CUDA_LAUNCH_CHECK("attn decode");
   launch_pdl(attn_merge_kernel<D>, dim3(unsigned(a.B * a.HQ)), dim3(D / 2), 0, stream, a);
   Q35_CUDA_LAUNCH_CHECK("attn merge");
@@ -743,7 +752,8 @@ int run_attn_paged_decode(Call& c) {
               "attn.paged_decode: paged_kv_scale [pages, 2, P, HKV] bf16 goes with an int8 cache (bound as bytes)");
   Q35_REQUIRE(!fp8 || D == 256 || D == 128, Q35_ERR_UNSUPPORTED, "attn.paged_decode: FP8 cache needs head_dim 128/256");
   const int n_cta = sm_count();
-  const int64_t S = B * HKV, slots = (S + n_cta) * 4;
+  const int wpc = fp8 ? 8 : 4;  // one-byte formats run two warps per scheduler (see AttnCfg)
+  const int64_t S = B * HKV, slots = (S + n_cta) * wpc;
   int64_t off = 0;
   auto take = [&](int64_t bytes) { const int64_t o = off; off = (off + bytes + 255) / 256 * 256; return o; };
   const int64_t o_plan = take(sizeof(AttnPlan)), o_seg = take((S + 1) * 4), o_ctx = take(B * 4),
@@ -777,11 +787,12 @@ int run_attn_paged_decode(Call& c) {
   a.part_ml = reinterpret_cast<float*>(w + o_ml);
   a.part_o = reinterpret_cast<float*>(w + o_po);
   a.status = device_status_ptr();
+  a.wpc = wpc;
   if (rsc.present) {
     a.row_scale = rsc.as<__nv_bfloat16>();
-    return D == 128 ? launch_attn<128, 2>(a, c.stream) : launch_attn<256, 2>(a, c.stream);
+    return D == 128 ? launch_attn<128, 2, 8>(a, c.stream) : launch_attn<256, 2, 8>(a, c.stream);
   }
-  if (fp8) return D == 128 ? launch_attn<128, 1>(a, c.stream) : launch_attn<256, 1>(a, c.stream);
+  if (fp8) return D == 128 ? launch_attn<128, 1, 8>(a, c.stream) : launch_attn<256, 1, 8>(a, c.stream);
   if (D == 64) return launch_attn<64, 0>(a, c.stream);
   if (D == 128) return launch_attn<128, 0>(a, c.stream);
   return launch_attn<256, 0>(a, c.stream);
@@ -872,6 +883,7 @@ extern "C" int q35_attn_paged_decode_static(const void* q, const void* paged_kv_
   a.out = static_cast<__nv_bfloat16*>(out);
   a.B = B; a.HQ = HQ; a.HKV = HKV; a.G = HQ / HKV; a.P = P;
   a.num_pages = num_pages; a.n_indices = n_indices; a.n_cta = n_cta;
+  a.wpc = 4;  // every format on four warps here: the built-in scratch holds four partial slots per (segment, CTA)
   a.plan = reinterpret_cast<AttnPlan*>(w + o_plan);
   a.seg_start = reinterpret_cast<int*>(w + o_seg);
   a.ctx = reinterpret_cast<int*>(w + o_ctx);
