@@ -131,6 +131,9 @@ int run_act_silu_mul(Call&);
 int run_act_sigmoid_gate(Call&);
 int run_linear_tc(Call&);
 int run_linear_multi(Call&);
+int run_ep_publish(Call&);
+int run_ep_wait(Call&);
+int run_ep_reduce(Call&);
 int run_lm_head(Call&);
 int run_debug_wait_probe(Call&);
 int run_debug_tc_peak(Call&);

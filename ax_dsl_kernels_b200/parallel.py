@@ -38,7 +38,12 @@ class ExpertParallelMoE:
     """w: the block's weights with FULL-size expert planes e_gw / e_gs / e_dw / e_ds [NE, ...]; only this rank's
     slice is kept (as a view when already on the device)."""
 
-    def __init__(self, w, top_k, group=None, n_experts=None):
+    def __init__(self, w, top_k, group=None, n_experts=None, exchange="auto"):
+        """exchange: "peer" = the two exchanges of forward() through this library's peer-memory kernels (roles
+        ep.publish / ep.wait / ep.reduce over a symmetric buffer every rank maps), "nccl" = all-gather + reduce-scatter,
+        "auto" = peer when the ranks are GPUs of one node and symmetric memory can be set up, else nccl."""
+        self.exchange = exchange
+        self._peer = None
         self.group = group if group is not None else dist.group.WORLD
         self.rank, self.world = dist.get_rank(self.group), dist.get_world_size(self.group)
         self.top_k = top_k
@@ -119,6 +124,68 @@ class ExpertParallelMoE:
         for dst, src in pairs:
             dist.all_gather_into_tensor(dst, src.contiguous(), group=self.group)
 
+    # -- the exchanges through peer memory -----------------------------------------------------------------------
+    def _peer_setup(self, x1):
+        """One symmetric buffer per rank (torch's symmetric memory: cuMem allocations every rank of the node maps),
+        laid out as ep_exchange expects: 1 KB header, then h2_all, ids_all, rw_all, partial.  Returns None when it
+        cannot be had (CPU tensors, no symmetric memory): the caller then takes the NCCL exchange."""
+        if self._peer is not None:
+            return self._peer or None
+        self._peer = False
+        if self.exchange == "nccl" or not x1.is_cuda:
+            return None
+        try:
+            import torch.distributed._symmetric_memory as symm_mem
+            T, H = x1.shape
+            N, K = self.world, self.top_k
+            al = lambda n: (n + 255) // 256 * 256  # noqa: E731
+            o_h2 = 1024
+            o_ids = o_h2 + al(N * T * H * 2)
+            o_rw = o_ids + al(N * T * K * 4)
+            o_par = o_rw + al(N * T * K * 4)
+            total = o_par + al(N * T * H * 4)
+            buf = symm_mem.empty(total, dtype=torch.uint8, device=x1.device)
+            name = self.group.group_name if hasattr(self.group, "group_name") else self.group
+            hdl = symm_mem.rendezvous(buf, name)
+            buf.zero_()
+            torch.cuda.synchronize(x1.device)
+            dist.barrier(group=self.group)  # nobody publishes into a buffer that is still being cleared
+            view = lambda off, n, dt, shape: buf[off:off + n].view(dt).view(shape)  # noqa: E731
+            self._peer = dict(
+                T=T, buf=buf, hdl=hdl,
+                peers=torch.tensor([int(p) for p in hdl.buffer_ptrs], dtype=torch.int64, device=x1.device).view(torch.uint8),
+                rank=torch.tensor([self.rank], dtype=torch.int32, device=x1.device),
+                h2_all=view(o_h2, N * T * H * 2, torch.bfloat16, (N * T, H)),
+                ids_all=view(o_ids, N * T * K * 4, torch.int32, (N * T, K)),
+                rw_all=view(o_rw, N * T * K * 4, torch.float32, (N * T, K)),
+                partial=view(o_par, N * T * H * 4, torch.float32, (N * T, H)))
+            # the gathered-token buffers of the step ARE the regions of the exchange buffer
+            self._buf[("partial", (N * T, H), torch.float32)] = self._peer["partial"]
+        except Exception as e:  # noqa: BLE001  (any failure of the optional path: fall back, but say so once)
+            if self.exchange == "peer":
+                raise
+            import warnings
+            warnings.warn(f"expert-parallel exchange falls back to NCCL: {type(e).__name__}: {e}")
+            self._peer = False
+        return self._peer or None
+
+    def _forward_peer(self, x1, out, px, mark):
+        from . import _lib
+        base, h2, ids, rw, ready = self._dense_part(x1)
+        mark("norm + router + route (shared expert on a second stream)")
+        common = dict(exchange=px["buf"], peers=px["peers"], rank=px["rank"])
+        _lib.run("ep.publish", h2=h2, ids=ids, rw=rw, h2_all=px["h2_all"], ids_all=px["ids_all"], rw_all=px["rw_all"],
+                 **common)  # returns in stream order once every rank's rows are here
+        mark("rows, ids, weights to every rank (peer stores) and the wait for everybody's")
+        partial = self._local_experts(px["h2_all"], px["ids_all"], px["rw_all"])
+        assert partial.data_ptr() == px["partial"].data_ptr()
+        mark("moe.experts on the gathered tokens, local experts")
+        if ready is not None:
+            torch.cuda.current_stream(base.device).wait_event(ready)
+        _lib.run("ep.reduce", base=base, partial=partial, out=out, **common)
+        mark("partial sums of my tokens from every rank (peer loads) + closing sum")
+        return out
+
     def forward(self, x1, out=None, marks=None):
         """marks: a list; when given, a (phase name, CUDA event) pair is appended after every phase of the step, so a
         caller can time the phases on the device (the first entry marks the start)."""
@@ -131,6 +198,9 @@ class ExpertParallelMoE:
         T, H = x1.shape
         N, K = self.world, self.top_k
         mark("start")
+        px = self._peer_setup(x1)
+        if px is not None and px["T"] == T:
+            return self._forward_peer(x1, torch.empty_like(x1) if out is None else out, px, mark)
         base, h2, ids, rw, ready = self._dense_part(x1)
         mark("norm + router + route (shared expert on a second stream)")
         h2_all = self._get("h2_all", (N * T, H), h2.dtype, h2.device)
@@ -147,6 +217,63 @@ class ExpertParallelMoE:
         out = self._finish(base, mine, out, ready)
         mark("closing sum (waits for the shared expert)")
         return out
+
+    def phases(self, x1, out):
+        """[(name, callable)]: the pieces of forward() on the same buffers, each callable on its own (a benchmark
+        captures each into a CUDA graph and times its replays; events cannot be placed inside one replayed graph).
+        The first piece joins the second stream at its end, so the shared expert's time shows in it instead of
+        hiding behind the exchange as it does in forward()."""
+        T, H = x1.shape
+        N, K = self.world, self.top_k
+        st = {}
+
+        def dense():
+            st["base"], st["h2"], st["ids"], st["rw"], ready = self._dense_part(x1)
+            if ready is not None:
+                torch.cuda.current_stream(x1.device).wait_event(ready)
+
+        dense()
+        px = self._peer_setup(x1)
+        if px is not None and px["T"] == T:
+            from . import _lib
+            common = dict(exchange=px["buf"], peers=px["peers"], rank=px["rank"])
+
+            def publish():
+                _lib.run("ep.publish", h2=st["h2"], ids=st["ids"], rw=st["rw"], h2_all=px["h2_all"],
+                         ids_all=px["ids_all"], rw_all=px["rw_all"], **common)
+
+            def experts_p():
+                self._local_experts(px["h2_all"], px["ids_all"], px["rw_all"])
+
+            def reduce():
+                _lib.run("ep.reduce", base=st["base"], partial=px["partial"], out=out, **common)
+
+            publish(); experts_p(); reduce()  # noqa: E702
+            return [("norm + router + route + shared expert (joined)", dense),
+                    ("rows, ids, weights to every rank (peer stores) + wait for everybody's", publish),
+                    ("moe.experts on the gathered tokens, local experts", experts_p),
+                    ("partial sums of my tokens from every rank (peer loads) + closing sum", reduce)]
+        h2_all = self._get("h2_all", (N * T, H), st["h2"].dtype, x1.device)
+        ids_all = self._get("ids_all", (N * T, K), st["ids"].dtype, x1.device)
+        rw_all = self._get("rw_all", (N * T, K), st["rw"].dtype, x1.device)
+        mine = self._get("mine", (T, H), torch.float32, x1.device)
+
+        def gather():
+            self._gather(((h2_all, st["h2"]), (ids_all, st["ids"]), (rw_all, st["rw"])))
+
+        def experts():
+            st["partial"] = self._local_experts(h2_all, ids_all, rw_all)
+
+        def scatter():
+            dist.reduce_scatter_tensor(mine, st["partial"], op=dist.ReduceOp.SUM, group=self.group)
+
+        def finish():
+            self._finish(st["base"], mine, out, None)
+
+        gather(); experts(); scatter(); finish()  # noqa: E702  (every buffer exists before anything is captured)
+        return [("norm + router + route + shared expert (joined)", dense), ("all-gather of rows, ids, weights", gather),
+                ("moe.experts on the gathered tokens, local experts", experts),
+                ("reduce-scatter of the fp32 partial sums", scatter), ("closing sum", finish)]
 
     # -- prefill-sized batches: a true all-to-all ---------------------------------------------------------------------
     def _combine(self, base, loc, rows, out):

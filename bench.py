@@ -88,7 +88,9 @@ class Workload:
     """all tensors of one rank, generated on the device from a seed; the per-step activations and results live in two
     packed buffers"""
 
-    def __init__(self, dev, seed, n_experts_local=NE, attn=True):
+    def __init__(self, dev, seed, n_experts_local=NE, attn=True, weight_seed=None):
+        """weight_seed: the MoE weights from a seed of their own (several ranks: the same model on every rank, different
+        tokens and caches per rank)"""
         g = torch.Generator(device=dev).manual_seed(seed)
         bf = torch.bfloat16
         rn = lambda *s: torch.randn(s, generator=g, device=dev)  # noqa: E731
@@ -121,6 +123,8 @@ class Workload:
         # MoE block
         rb = lambda lo, hi, *s: torch.randint(lo, hi, s, generator=g, device=dev, dtype=torch.int32).to(torch.uint8)  # noqa: E731
         self.x1.copy_(rn(B, H).to(bf))
+        if weight_seed is not None:
+            g = torch.Generator(device=dev).manual_seed(weight_seed)  # rn / rb below draw from this one
         self.w = dict(
             ln2=torch.ones(H, device=dev), w_router=(rn(NE, H) / H ** 0.5).to(bf), w_shg=(rn(H) / H ** 0.5).to(bf),
             e_gw=rb(0, 256, n_experts_local, 2 * FE, H // 2), e_gs=rb(119, 128, n_experts_local, 2 * FE, H // 32),
@@ -254,11 +258,11 @@ def run_ours(args):
         import torch.distributed as dist
         import datetime
         dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=120))
-    wl = Workload(dev, seed=1000 + rank)
+    wl = Workload(dev, seed=1000 + rank, weight_seed=999 if world > 1 else None)
     L = q35._lib.lib()
     if world > 1:
         from ax_dsl_kernels_b200 import parallel
-        ep = parallel.ExpertParallelMoE(wl.w, TOPK, dist.group.WORLD)
+        ep = parallel.ExpertParallelMoE(wl.w, TOPK, dist.group.WORLD, exchange=args.ep_exchange)
         moe_step = lambda x: ep.forward(x, wl.moe_out)  # noqa: E731
     else:
         q35.prepare_moe_weights(wl.w)  # load-time re-layout of the E8M0 scales for the one-call decode block
@@ -325,18 +329,25 @@ def run_ours(args):
         parts["attn.paged_decode (plan + decode + merge)"] = median(
             timed_rounds(gph.replay if gph else attn_only, args.steps, barrier, min_seconds=0.2, agree=agree)) / args.steps
     attn_ms = parts["attn.paged_decode (plan + decode + merge)"]
+    ep_check = None
+    if world > 1:  # the expert-parallel block against the one-GPU block on this rank's tokens (every rank holds all weights)
+        ref = q35.moe_block(wl.x1, q35.prepare_moe_weights(wl.w), TOPK)[0].float()
+        got = ep.forward(wl.x1, wl.moe_out).float()
+        worst = ((got - ref).abs().max() / ref.square().mean().sqrt()).reshape(1)
+        dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+        ep_check = {"max_err_over_rms_vs_one_gpu_block": float(worst.item()),
+                    "exchange": "peer memory" if getattr(ep, "_peer", None) else "nccl"}
     ep_phases = None
-    if world > 1:  # the expert-parallel MoE step phase by phase: eager launches bracketed by events, median over steps
-        per = {}
-        for it in range(40):
-            marks = []
-            ep.forward(wl.x1, wl.moe_out, marks=marks)
-            torch.cuda.synchronize()
-            if it >= 8:
-                for (_, a), (name, b) in zip(marks[:-1], marks[1:]):
-                    per.setdefault(name, []).append(a.elapsed_time(b))
-                per.setdefault("whole MoE step (eager)", []).append(marks[0][1].elapsed_time(marks[-1][1]))
-        ep_phases = {name: round(median(v) * 1e3, 1) for name, v in per.items()}
+    if world > 1:  # the expert-parallel MoE step piece by piece: each piece captured as a graph of its own and replayed
+        ep_phases = {}
+        for name, fn in ep.phases(wl.x1, wl.moe_out):
+            gph = capture(fn) if not args.no_graph else None
+            ep_phases[name] = round(median(timed_rounds(gph.replay if gph else fn, args.steps, barrier, min_seconds=0.1,
+                                                        agree=agree)) / args.steps * 1e3, 1)
+        gph = capture(lambda: ep.forward(wl.x1, wl.moe_out)) if not args.no_graph else None
+        ep_phases["whole MoE step (shared expert overlapped)"] = round(median(timed_rounds(
+            gph.replay if gph else (lambda: ep.forward(wl.x1, wl.moe_out)), args.steps, barrier, min_seconds=0.1,
+            agree=agree)) / args.steps * 1e3, 1)
 
     # end to end: the per-step activations start in ONE pinned host block and the results come back into one
     host_in = torch.empty(wl.inputs.nbytes, dtype=torch.uint8).pin_memory()
@@ -403,6 +414,7 @@ def run_ours(args):
         }
         if ep_phases is not None:
             line["ep_phases_us_rank0"] = ep_phases
+            line["ep_check"] = ep_check
         if world == 1:
             ids = q35.moe_block(wl.x1, wl.w, TOPK, wl.moe_out)[1]
             distinct = int(torch.unique(ids).numel())
@@ -653,6 +665,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="headline")
     ap.add_argument("--layers", type=int, default=16, help="layers of the --config c5 decode group")
+    ap.add_argument("--ep-exchange", default="auto", choices=["auto", "peer", "nccl"],
+                    help="several GPUs: the expert-parallel exchange through this library's peer-memory kernels or NCCL")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
     ap.add_argument("--no-full-layer", action="store_true", help="skip the full-layer variant of the step")
     ap.add_argument("--no-graph", action="store_true", help="launch the timed steps eagerly instead of replaying a CUDA graph")

@@ -414,6 +414,61 @@ def test_qwen3_moe_one_call_contract_by_the_reference_names(q35):
                            w_norm=(w["ln2"] - 1).cuda().clone()))
 
 
+def test_expert_parallel_exchange_kernels_two_ranks_emulated_on_one_gpu(q35):
+    """ep.publish / ep.wait / ep.reduce with two ranks' exchange buffers in this one GPU's memory, the ranks run one
+    after the other: rows, ids and weights land in slice `rank` of BOTH buffers, the flags carry the exchange count,
+    and every rank's output is its dense part plus both ranks' partial sums of its tokens.  No kernel is made to wait
+    here: a rank publishes with no_wait, ep.wait runs once both have published, and the test raises the done flags the
+    other rank's reduce would raise (it plays that rank) before each reduce."""
+    N, T, H, K = 2, 8, 512, 4
+    g = torch.Generator().manual_seed(41)
+    al = lambda n: (n + 255) // 256 * 256  # noqa: E731
+    o_h2 = 1024
+    o_ids = o_h2 + al(N * T * H * 2)
+    o_rw = o_ids + al(N * T * K * 4)
+    o_par = o_rw + al(N * T * K * 4)
+    total = o_par + al(N * T * H * 4)
+    bufs = [torch.zeros(total, dtype=torch.uint8, device="cuda") for _ in range(N)]
+    peers = torch.tensor([b.data_ptr() for b in bufs], dtype=torch.int64, device="cuda").view(torch.uint8)
+    view = lambda b, off, n, dt, shape: b[off:off + n].view(dt).view(shape)  # noqa: E731
+    regs = [dict(h2_all=view(b, o_h2, N * T * H * 2, torch.bfloat16, (N * T, H)),
+                 ids_all=view(b, o_ids, N * T * K * 4, torch.int32, (N * T, K)),
+                 rw_all=view(b, o_rw, N * T * K * 4, torch.float32, (N * T, K)),
+                 partial=view(b, o_par, N * T * H * 4, torch.float32, (N * T, H))) for b in bufs]
+    ranks = [torch.tensor([r], dtype=torch.int32, device="cuda") for r in range(N)]
+    flag = torch.ones(1, dtype=torch.int32, device="cuda")
+    for step in (1, 2):  # two exchanges: the flags count them
+        h2 = [torch.randn((T, H), generator=g).to(torch.bfloat16).cuda() for _ in range(N)]
+        ids = [torch.randint(0, 64, (T, K), generator=g, dtype=torch.int32).cuda() for _ in range(N)]
+        rw = [torch.rand((T, K), generator=g).cuda() for _ in range(N)]
+        for r in range(N):
+            q35.run("ep.publish", h2=h2[r], ids=ids[r], rw=rw[r], peers=peers, rank=ranks[r], exchange=bufs[r],
+                    no_wait=flag, h2_all=regs[r]["h2_all"], ids_all=regs[r]["ids_all"], rw_all=regs[r]["rw_all"])
+        for r in range(N):
+            q35.run("ep.wait", peers=peers, rank=ranks[r], exchange=bufs[r])
+        for r in range(N):
+            hdr = bufs[r][:1024].view(torch.int32)
+            assert int(hdr[0]) == step and hdr[64:64 + N].tolist() == [step] * N  # epoch, gather flags
+            assert torch.equal(regs[r]["h2_all"], torch.cat(h2)) and torch.equal(regs[r]["ids_all"], torch.cat(ids))
+            assert torch.equal(regs[r]["rw_all"], torch.cat(rw))
+        part = [torch.randn((N * T, H), generator=g).cuda() for _ in range(N)]
+        base = [torch.randn((T, H), generator=g).to(torch.bfloat16).cuda() for _ in range(N)]
+        for r in range(N):
+            regs[r]["partial"].copy_(part[r])
+            bufs[r][:1024].view(torch.int32)[128:128 + N] = step  # the done flags the ranks' reduces would raise
+        for r in range(N):
+            out = torch.full((T, H), float("nan"), dtype=torch.bfloat16, device="cuda")
+            q35.run("ep.reduce", base=base[r], partial=regs[r]["partial"], peers=peers, rank=ranks[r], exchange=bufs[r],
+                    out=out)
+            ref = base[r].float()
+            for p in range(N):
+                ref = ref + part[p][r * T:(r + 1) * T]
+            assert torch.equal(out, ref.to(torch.bfloat16))
+    assert q35.device_status() == 0
+    with pytest.raises(q35.Q35Error):  # peers[rank] must be this rank's own buffer
+        q35.run("ep.wait", peers=peers, rank=ranks[1], exchange=bufs[0])
+
+
 # ------------------------------------------------------------------------------------------------ robustness
 def test_bounded_wait_reports_instead_of_hanging(q35):
     """a device-side wait that can never complete (a barrier nothing arrives at, 4096 polls) gives up, sets the
