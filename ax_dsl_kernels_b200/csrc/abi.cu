@@ -215,6 +215,9 @@ static const RoleDef kRoles[] = {
     {"ep.reduce",
      R"({"in":[["base","bf16","[T,H]"],["partial","f32","[N T,H] region of exchange: this rank's sums for every rank's tokens"],["peers","u8","[8 N]"],["rank","i32","[1]"],["exchange","u8","[*]"]],"out":[["out","bf16","[T,H]: base + the ranks' partial sums of this rank's tokens, added in rank order"]]})",
      run_ep_reduce},
+    {"ar.oneshot",
+     R"({"in":[["x","f32","[*]: this rank's addend, a multiple of 4 elements"],["peers","u8","[8 N]"],["rank","i32","[1]"],["exchange","u8","[1024 + 2 N slot]: slot = bytes of x rounded up to 256"]],"out":[["out","f32","like x: the sum over the ranks, added in rank order"]]})",
+     run_ar_oneshot},
     {"norm.rms",
      R"({"in":[["x","bf16","[T,H]"],["residual","bf16","[T,H] optional"],["w","f32|bf16","[H]"],["eps","f32","[1] optional"]],"out":[["y","bf16","[T,H]"],["base_out","bf16","[T,H] optional"],["xsqrt_out","f32","[T] optional: folded form"]]})",
      run_norm_rms},

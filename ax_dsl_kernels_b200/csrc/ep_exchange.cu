@@ -158,6 +158,56 @@ __global__ void __launch_bounds__(256) ep_reduce_kernel(const __nv_bfloat16* __r
   }
 }
 
+// ar.oneshot: sum over the ranks of an fp32 tensor of a few hundred kilobytes -- the all-reduce after every sublayer's
+// output projection in the tensor-parallel decode group (reduce(), models/qwen38_27b/decode/q35_group.py:128-137; the
+// NPU cores add their partial sums through shared memory) -- in ONE kernel: every rank stores its tensor into slot
+// `rank` of every rank's buffer, raises its flag everywhere, waits for everybody's flag and adds the N slots in rank
+// order (the same order on every rank: bit-identical results).  Slots are double-buffered by the parity of the exchange
+// count: a rank can be at most one exchange ahead of another (it cannot finish exchange e + 1 without the other's flag
+// of e + 1, raised after that rank is done reading exchange e).  Layout: the 1 KB header as above (epoch, counter, flags
+// at 256), then [2 parities][N ranks][bytes of the tensor, rounded up to 256].
+__global__ void __launch_bounds__(256) ar_oneshot_kernel(const float4* __restrict__ x, EpPeers peers, int N, int rank,
+                                                         int n_vec, long long slot_bytes, float4* __restrict__ out,
+                                                         int* status) {
+  pdl_wait();
+  pdl_launch();
+  uint8_t* mine = peers.base[rank];
+  uint32_t* hdr = reinterpret_cast<uint32_t*>(mine);
+  const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(hdr) + 1;  // (updated by the last CTA, after every CTA read it)
+  const long long par = (long long)(epoch & 1u) * N * slot_bytes;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n_vec; i += gridDim.x * blockDim.x) {
+    const float4 v = x[i];
+#pragma unroll
+    for (int q = 0; q < EP_MAX_RANKS; ++q)
+      if (q < N) reinterpret_cast<float4*>(peers.base[q] + EP_HDR_BYTES + par + rank * slot_bytes)[i] = v;
+  }
+  __threadfence_system();
+  __syncthreads();
+  __shared__ bool last;
+  if (threadIdx.x == 0) last = atomicAdd(hdr + 1, 1u) == gridDim.x - 1;
+  __syncthreads();
+  if (last) {
+    __threadfence_system();
+    if (threadIdx.x < N) st_release_sys(reinterpret_cast<uint32_t*>(peers.base[threadIdx.x] + 256) + rank, epoch);
+    if (threadIdx.x == 0) { hdr[1] = 0; hdr[0] = epoch; }
+  }
+  if (threadIdx.x < N && !ep_wait_flags(reinterpret_cast<const uint32_t*>(mine + 256) + threadIdx.x, 1, epoch))
+    atomicOr(status, DS_WAIT_TIMEOUT | 0x2000);
+  __syncthreads();
+  const uint8_t* slots = mine + EP_HDR_BYTES + par;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n_vec; i += gridDim.x * blockDim.x) {
+    float4 v[EP_MAX_RANKS];
+#pragma unroll
+    for (int p = 0; p < EP_MAX_RANKS; ++p)
+      if (p < N) v[p] = __ldcv(reinterpret_cast<const float4*>(slots + p * slot_bytes) + i);  // written by peers: not cached
+    float4 acc = v[0];
+#pragma unroll
+    for (int p = 1; p < EP_MAX_RANKS; ++p)
+      if (p < N) { acc.x += v[p].x; acc.y += v[p].y; acc.z += v[p].z; acc.w += v[p].w; }
+    out[i] = acc;
+  }
+}
+
 // ---------------------------------------------------------------------------------------------------------------
 static int ep_common(Call& c, const char* role, Tensor* ex, EpPeers* peers, int* N, int* rank) {
   Tensor pt, rk;
@@ -274,6 +324,29 @@ int run_ep_reduce(Call& c) {
   launch_pdl(ep_reduce_kernel, dim3(grid), dim3(256), 0, c.stream, base.as<__nv_bfloat16>(), peers, N, rank, off,
              int(T), int(H), out.as<__nv_bfloat16>(), device_status_ptr());
   Q35_CUDA_LAUNCH_CHECK("ep.reduce");
+  return 0;
+}
+
+int run_ar_oneshot(Call& c) {
+  Tensor ex, x, out;
+  EpPeers peers{};
+  int N = 0, rank = 0;
+  Q35_TRY(c.get("x", M(Q35_F32), &x));
+  Q35_TRY(c.get("out", M(Q35_F32), &out));
+  Q35_TRY(ep_common(c, "ar.oneshot", &ex, &peers, &N, &rank));
+  Q35_REQUIRE(out.numel() == x.numel() && x.numel() % 4 == 0, Q35_ERR_SHAPE, "ar.oneshot: out like x, a multiple of 4 elements");
+  const long long slot = (long long)(x.bytes + 255) / 256 * 256;
+  Q35_REQUIRE((long long)ex.bytes >= EP_HDR_BYTES + 2 * N * slot, Q35_ERR_WORKSPACE,
+              "ar.oneshot: exchange must hold the 1 KB header and 2 x %d slots of %lld bytes", N, slot);
+  c.ws_need = 0;
+  if (c.dry || x.numel() == 0) return 0;
+  Q35_REQUIRE(aligned16(x.p) && aligned16(out.p), Q35_ERR_ALIGN, "ar.oneshot: x, out 16-byte aligned");
+  const int n_vec = int(x.numel() / 4);
+  // every CTA waits for the peers' flags: the grid must be resident at once
+  const unsigned grid = unsigned(std::min<long long>((n_vec + 255) / 256, sm_count()));
+  launch_pdl(ar_oneshot_kernel, dim3(grid), dim3(256), 0, c.stream, static_cast<const float4*>(x.p), peers, N, rank, n_vec,
+             slot, static_cast<float4*>(out.p), device_status_ptr());
+  Q35_CUDA_LAUNCH_CHECK("ar.oneshot");
   return 0;
 }
 

@@ -441,6 +441,57 @@ def all_reduce_sum(group=None):
     return reduce
 
 
+class PeerAllReduce:
+    """The `reduce` hook through this library's one-kernel all-reduce over peer memory (role ar.oneshot): every rank
+    stores its fp32 partial into a slot of every rank's symmetric buffer, flags, waits, and adds the slots in rank
+    order.  Made for the few hundred kilobytes a decode step reduces after each output projection, where a collective's
+    latency is the cost.  Tensors of another size than the first one seen, CPU tensors and hosts without symmetric
+    memory take dist.all_reduce."""
+
+    def __init__(self, group=None, mode="auto"):
+        self.group = group if group is not None else dist.group.WORLD
+        self.rank, self.world = dist.get_rank(self.group), dist.get_world_size(self.group)
+        self.mode = mode
+        self._px = None
+
+    def _setup(self, partial):
+        if self._px is not None:
+            return self._px or None
+        self._px = False
+        if self.mode == "nccl" or not partial.is_cuda or partial.numel() % 4 or partial.dtype != torch.float32:
+            return None
+        try:
+            import torch.distributed._symmetric_memory as symm_mem
+            slot = (partial.numel() * 4 + 255) // 256 * 256
+            buf = symm_mem.empty(1024 + 2 * self.world * slot, dtype=torch.uint8, device=partial.device)
+            name = self.group.group_name if hasattr(self.group, "group_name") else self.group
+            hdl = symm_mem.rendezvous(buf, name)
+            buf.zero_()
+            torch.cuda.synchronize(partial.device)
+            dist.barrier(group=self.group)
+            self._px = dict(numel=partial.numel(), buf=buf, hdl=hdl, out=torch.empty_like(partial),
+                            peers=torch.tensor([int(p) for p in hdl.buffer_ptrs], dtype=torch.int64,
+                                               device=partial.device).view(torch.uint8),
+                            rank=torch.tensor([self.rank], dtype=torch.int32, device=partial.device))
+        except Exception as e:  # noqa: BLE001
+            if self.mode == "peer":
+                raise
+            import warnings
+            warnings.warn(f"tensor-parallel all-reduce falls back to NCCL: {type(e).__name__}: {e}")
+            self._px = False
+        return self._px or None
+
+    def __call__(self, partial):
+        px = self._setup(partial)
+        if px is None or px["numel"] != partial.numel():
+            dist.all_reduce(partial, op=dist.ReduceOp.SUM, group=self.group)
+            return partial
+        from . import _lib
+        out = px["out"].view(partial.shape)
+        _lib.run("ar.oneshot", x=partial.contiguous(), peers=px["peers"], rank=px["rank"], exchange=px["buf"], out=out)
+        return out
+
+
 def tensor_parallel_stack(layers, kinds, *, heads, kv_heads, head_dim, group=None, gated=True, **stack_kw):
     """layers.HybridStack over this rank's shards with an all-reduce after each of the two sublayers of a layer"""
     from .layers import HybridStack
@@ -452,7 +503,8 @@ def tensor_parallel_stack(layers, kinds, *, heads, kv_heads, head_dim, group=Non
                        **stack_kw)
 
 
-def tensor_parallel_decode_group(layers, kinds, *, batch, heads, kv_heads, head_dim, group=None, gated=True, **group_kw):
+def tensor_parallel_decode_group(layers, kinds, *, batch, heads, kv_heads, head_dim, group=None, gated=True,
+                                 reduce="auto", **group_kw):
     """layers.DecodeGroup (B sequences, one token each per step) over this rank's shards: heads, GDN value heads and FFN
     columns split over the group, one all-reduce of the fp32 partial [B, H] after each sublayer's output projection --
     the split of the 27B-class decode group over 2 / 4 / 8 devices (models/qwen38_27b/decode/q35_group.py:128-137)."""
@@ -461,8 +513,10 @@ def tensor_parallel_decode_group(layers, kinds, *, batch, heads, kv_heads, head_
     rank, world = dist.get_rank(g), dist.get_world_size(g)
     shards, hl, kl = shard_stack_weights(layers, kinds, rank, world, heads=heads, kv_heads=kv_heads, head_dim=head_dim,
                                          gated=gated)
+    # reduce: "auto" / "peer" = the one-kernel all-reduce over peer memory (PeerAllReduce), "nccl" = dist.all_reduce
+    hook = all_reduce_sum(g) if reduce == "nccl" else PeerAllReduce(g, reduce)
     return DecodeGroup(shards, kinds, batch=batch, heads=hl, kv_heads=kl, head_dim=head_dim, gated=gated,
-                       reduce=all_reduce_sum(g), **group_kw)
+                       reduce=hook, **group_kw)
 
 
 # ----------------------------------------------------------------------------------------------------------------

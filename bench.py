@@ -666,7 +666,8 @@ def main():
     ap.add_argument("--config", default="headline")
     ap.add_argument("--layers", type=int, default=16, help="layers of the --config c5 decode group")
     ap.add_argument("--ep-exchange", default="auto", choices=["auto", "peer", "nccl"],
-                    help="several GPUs: the expert-parallel exchange through this library's peer-memory kernels or NCCL")
+                    help="several GPUs: the expert-parallel exchange (headline) and the tensor-parallel all-reduce (c5) through this "
+                    "library's peer-memory kernels or through NCCL")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
     ap.add_argument("--no-full-layer", action="store_true", help="skip the full-layer variant of the step")
     ap.add_argument("--no-graph", action="store_true", help="launch the timed steps eagerly instead of replaying a CUDA graph")

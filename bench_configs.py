@@ -379,7 +379,7 @@ def run_c5(args, fp8):
     kw = dict(batch=B, heads=heads, kv_heads=kvh, head_dim=hd, rot=64, theta=1e7, max_tokens=CTX + PAGE, page_size=PAGE,
               kv_dtype=torch.float8_e4m3fn if fp8 else torch.bfloat16)
     if world > 1:
-        grp = parallel.tensor_parallel_decode_group(ws, kinds, **kw)
+        grp = parallel.tensor_parallel_decode_group(ws, kinds, reduce=args.ep_exchange, **kw)
         del ws
         torch.cuda.empty_cache()
     else:

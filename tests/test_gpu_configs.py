@@ -511,3 +511,32 @@ def test_two_host_threads_own_streams_bitwise_equal(q35):
     assert not errs, errs
     for o in outs:
         assert torch.equal(o.view(torch.int16), ref.view(torch.int16))
+
+
+def test_oneshot_all_reduce_two_ranks_emulated_on_one_gpu(q35):
+    """ar.oneshot with two ranks' exchange buffers in this GPU's memory.  A rank's kernel waits for the other's flag, so
+    the ranks cannot run one after the other for real; the test plays the other rank instead: before rank r's launch it
+    writes the other rank's addend into r's slot and raises that flag by hand.  Checked: the sum (rank order), the
+    store of r's addend into BOTH buffers, the flags, and the alternation of the two slot sets."""
+    N, n = 2, 8 * 512
+    slot = (n * 4 + 255) // 256 * 256
+    bufs = [torch.zeros(1024 + 2 * N * slot, dtype=torch.uint8, device="cuda") for _ in range(N)]
+    peers = torch.tensor([b.data_ptr() for b in bufs], dtype=torch.int64, device="cuda").view(torch.uint8)
+    ranks = [torch.tensor([r], dtype=torch.int32, device="cuda") for r in range(N)]
+    g = torch.Generator().manual_seed(3)
+    for epoch in (1, 2, 3):
+        par = (epoch & 1) * N * slot
+        xs = [torch.randn(n, generator=g).cuda() for _ in range(N)]
+        for r in range(N):
+            o = 1 - r
+            # the other rank's part of this exchange, as its kernel would have left it in r's buffer
+            bufs[r][1024 + par + o * slot:1024 + par + o * slot + n * 4].view(torch.float32).copy_(xs[o])
+            bufs[r][:1024].view(torch.int32)[64 + o] = epoch
+            out = torch.full((n,), float("nan"), device="cuda")
+            q35.run("ar.oneshot", x=xs[r], peers=peers, rank=ranks[r], exchange=bufs[r], out=out)
+            assert torch.equal(out, xs[0] + xs[1])
+            hdr = bufs[r][:1024].view(torch.int32)
+            assert int(hdr[0]) == epoch and int(hdr[64 + r]) == epoch
+            for b in bufs:  # r's addend reached both buffers
+                assert torch.equal(b[1024 + par + r * slot:1024 + par + r * slot + n * 4].view(torch.float32), xs[r])
+    assert q35.device_status() == 0
