@@ -378,7 +378,23 @@ def run_c5(args, fp8):
     ws, kinds = c5_weights(dev, layers=n_layers)  # the same full weights on every rank, then this rank's shard
     kw = dict(batch=B, heads=heads, kv_heads=kvh, head_dim=hd, rot=64, theta=1e7, max_tokens=CTX + PAGE, page_size=PAGE,
               kv_dtype=torch.float8_e4m3fn if fp8 else torch.bfloat16)
+    tp_check = None
     if world > 1:
+        # the first four layers (g g g a), short context, one step: this rank's tensor-parallel output against the whole
+        # layers on this GPU alone (every rank holds the full weights at this point)
+        small = dict(kw, max_tokens=256 + PAGE)
+        xs = (torch.randn((B, H), generator=torch.Generator(device=dev).manual_seed(5), device=dev) * 0.5).to(torch.bfloat16)
+        one = L.DecodeGroup(ws[:4], kinds[:4], **small)
+        tp4 = parallel.tensor_parallel_decode_group(ws[:4], kinds[:4], reduce=args.ep_exchange, **small)
+        outs = []
+        for grp4 in (one, tp4):
+            grp4.set_context([100] * B)
+            outs.append(grp4.step(xs, advance=False).float())
+        worst = ((outs[1] - outs[0]).abs().max() / outs[0].square().mean().sqrt()).reshape(1)
+        dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+        tp_check = {"layers": 4, "max_err_over_rms_vs_one_gpu": float(worst.item()),
+                    "all_reduce": "peer memory (ar.oneshot)" if getattr(tp4.reduce, "_px", None) else "nccl"}
+        del one, tp4, outs
         grp = parallel.tensor_parallel_decode_group(ws, kinds, reduce=args.ep_exchange, **kw)
         del ws
         torch.cuda.empty_cache()
@@ -408,7 +424,9 @@ def run_c5(args, fp8):
              f"({wb / 1e9:.2f} GB), batch {B}, context {CTX}, page {PAGE}, {'FP8 E4M3' if fp8 else 'bf16'} KV "
              f"({kvb / 1e9:.2f} GB read per step), fp32 GDN state ({stb / 1e9:.2f} GB read + written)",
              "parallelism": "1 GPU" if world == 1 else f"tensor parallel x{world}: heads, GDN value heads and FFN columns "
-             "split, one NCCL all-reduce of the fp32 partial [8, 5120] per sublayer"}, dist=dist, dev=dev, scaling="strong")
+             "split, one all-reduce of the fp32 partial [8, 5120] per sublayer (this library's one-kernel all-reduce over "
+             "peer memory, or NCCL with --ep-exchange nccl)"}, dist=dist, dev=dev, scaling="strong",
+            extra=(lambda _ms: {"tp_check": tp_check}) if tp_check else None)
 
 
 def run(args):
