@@ -206,6 +206,9 @@ static const RoleDef kRoles[] = {
     {"linear.multi",
      R"({"in":[["x","bf16","[T,K]"],["w","u8|e4m3","[N,K/2]|[N,K]: the projections' weights, rows concatenated"],["s","u8|f32","[N,K/32]|[N]"],["bias","f32","[N] optional"],["row_div","f32","[T] optional"],["workspace","u8","[*]"]],"out":[["out0","bf16|f32","[T,N_0]"],["out1","bf16|f32","[T,N_1] optional, and so on up to out7; the N_i add up to N"],["out2","bf16|f32","optional"],["out3","bf16|f32","optional"],["out4","bf16|f32","optional"],["out5","bf16|f32","optional"],["out6","bf16|f32","optional"],["out7","bf16|f32","optional"]]})",
      run_linear_multi},
+    {"moe.front",
+     R"({"in":[["x1","bf16","[T,H]"],["ln2","f32","[H]"],["w_router","bf16","[NE,H]"],["w_shg","bf16","[H] optional: shared-expert gate vector"],["workspace","u8","[*]"]],"out":[["h2_out","bf16","[T,H]"],["logits_out","f32","[T,NE]"],["gate_out","f32","[T] with w_shg"],["ids","i32","[T,K]"],["rw","f32","[T,K]"]]})",
+     run_moe_front},
     {"ep.publish",
      R"({"in":[["h2","bf16","[T,H]"],["ids","i32","[T,K]"],["rw","f32","[T,K]"],["peers","u8","[8 N]: the ranks' exchange buffer addresses as mapped here"],["rank","i32","[1]"],["no_wait","i32","[1] optional: return after publishing instead of waiting for every rank's rows; ep.wait does that later"]],"out":[["exchange","u8","[*]: this rank's exchange buffer, 1 KB header first"],["h2_all","bf16","[N,T,H] region of exchange"],["ids_all","i32","[N,T,K] region of exchange"],["rw_all","f32","[N,T,K] region of exchange"]]})",
      run_ep_publish},

@@ -135,6 +135,7 @@ int run_ep_publish(Call&);
 int run_ep_wait(Call&);
 int run_ep_reduce(Call&);
 int run_ar_oneshot(Call&);
+int run_moe_front(Call&);
 int run_lm_head(Call&);
 int run_debug_wait_probe(Call&);
 int run_debug_tc_peak(Call&);

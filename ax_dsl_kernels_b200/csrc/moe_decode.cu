@@ -1043,6 +1043,69 @@ int moe_experts_tiled(Call& c, const Tensor& h2, const Tensor& base, const Tenso
   return 0;
 }
 
+// moe.front: the head of the block on a decode-sized batch in ONE launch -- RMSNorm, router logits, shared-expert gate
+// dot, softmax, top-k, routing weights (moe_pre's first half + route, models/qwen35_2b/whole/src/q35_moe.py:123-137,
+// 293-297) -- for hosts that put something of their own between routing and the experts (the expert-parallel step
+// exchanges rows between GPUs there).  The same kernel as moe.block's first launch; its slot plan goes to scratch.
+int run_moe_front(Call& c) {
+  Tensor x1, ln2, wr, wshg, h2o, lg, gt, ids, rw, ws;
+  Q35_TRY(c.get("x1", M(Q35_BF16), &x1));
+  Q35_TRY(c.get("ln2", M(Q35_F32), &ln2));
+  Q35_TRY(c.get("w_router", M(Q35_BF16), &wr));
+  Q35_TRY(c.get("w_shg", M(Q35_BF16), &wshg, false));
+  Q35_TRY(c.get("h2_out", M(Q35_BF16), &h2o));
+  Q35_TRY(c.get("logits_out", M(Q35_F32), &lg));
+  Q35_TRY(c.get("gate_out", M(Q35_F32), &gt, false));
+  Q35_TRY(c.get("ids", M(Q35_I32), &ids));
+  Q35_TRY(c.get("rw", M(Q35_F32), &rw));
+  Q35_REQUIRE(x1.nd == 2 && wr.nd == 2 && ids.nd == 2, Q35_ERR_SHAPE, "moe.front: x1 [T, H], w_router [NE, H], ids [T, K]");
+  const int64_t T = x1.s[0], H = x1.s[1], NE = wr.s[0], K = ids.s[1];
+  const bool has_shared = wshg.present;
+  Q35_REQUIRE(wr.s[1] == H && ln2.numel() == H && h2o.numel() == T * H && lg.numel() == T * NE && ids.s[0] == T &&
+                  rw.numel() == T * K && (!has_shared || (wshg.numel() == H && gt.present && gt.numel() == T)),
+              Q35_ERR_SHAPE, "moe.front: shapes (w_shg [H] goes with gate_out [T])");
+  Q35_REQUIRE(H % 512 == 0 && H <= NR_MAX_H && K >= 1 && K <= 32 && K <= NE && NE + 1 <= 1024, Q35_ERR_UNSUPPORTED,
+              "moe.front: H a multiple of 512 up to 8192, K <= 32, NE < 1024");
+  const int64_t P = T * K, W = (T + 31) / 32;
+  Q35_REQUIRE(T >= 1 && P <= MD_MAX_PAIRS && NE * W <= MD_MAX_WORDS, Q35_ERR_UNSUPPORTED,
+              "moe.front: decode-sized batches only (T * K <= 4096)");
+  const int64_t groups = NE + (T + MD_NB - 1) / MD_NB;
+  WsCut cut{nullptr};
+  int *counters, *g_plane, *g_n, *g_row0, *active, *ready, *loc;
+  float* gate;
+  auto carve = [&](WsCut& w) {
+    counters = w.take<int>(T + 1);
+    g_plane = w.take<int>(groups); g_n = w.take<int>(groups); g_row0 = w.take<int>(groups);
+    active = w.take<int>(groups + 1); ready = w.take<int>(groups); loc = w.take<int>((K + 1) * T);
+    gate = w.take<float>(T);
+  };
+  carve(cut);
+  Q35_TRY(c.workspace(cut.off, &ws));
+  if (c.dry) return 0;
+  Q35_REQUIRE(aligned16(x1.p) && aligned16(wr.p) && aligned16(ln2.p) && aligned16(h2o.p) &&
+                  (!has_shared || aligned16(wshg.p)), Q35_ERR_ALIGN, "moe.front: pointers must be 16-byte aligned");
+  WsCut wc{ws.as<uint8_t>()};
+  carve(wc);
+  if (gt.present) gate = gt.as<float>();
+  const int tok_per = NR_TOK / int((H + 2047) / 2048);
+  const int tgroups = int((T + tok_per - 1) / tok_per);
+  cudaMemsetAsync(counters, 0, size_t(tgroups + 1) * sizeof(int), c.stream);
+  const int max_slices = int((NE + 1 + 7) / 8);
+  int slices = (4 * sm_count() + tgroups - 1) / tgroups;
+  slices = slices < 1 ? 1 : slices > max_slices ? max_slices : slices;
+#define Q35_FRONT(PER)                                                                                                \
+  launch_pdl(moe_front_kernel<PER>, dim3(unsigned(tgroups), unsigned(slices)), dim3(256), 0, c.stream,                 \
+             x1.as<__nv_bfloat16>(), ln2.as<float>(), wr.as<__nv_bfloat16>(),                                          \
+             has_shared ? wshg.as<__nv_bfloat16>() : wr.as<__nv_bfloat16>(), h2o.as<__nv_bfloat16>(), lg.as<float>(),  \
+             gate, int(H), int(NE), 1e-6f, int(T), int(K), int(has_shared), tok_per, ids.as<int>(), rw.as<float>(),    \
+             counters, g_plane, g_n, g_row0, active, ready, loc)
+  if (NE <= 256) Q35_FRONT(8);
+  else Q35_FRONT(32);
+#undef Q35_FRONT
+  Q35_CUDA_LAUNCH_CHECK("moe.front");
+  return 0;
+}
+
 // moe.block: the whole block on a decode-sized batch.  Needs the tiled scale tensors (mx.tile_scales.*) of the routed
 // and, when bound, the shared expert; MXFP4 everywhere; H and FE multiples of 512; shared intermediate size == FE.
 int run_moe_block(Call& c) {

@@ -67,16 +67,26 @@ class ExpertParallelMoE:
         base, h2 = self._get("base", (T, H), x1.dtype, dev), self._get("h2", (T, H), x1.dtype, dev)
         logits = self._get("logits", (T, self.n_experts), torch.float32, dev)
         gate = self._get("gate", (T,), torch.float32, dev)
-        _lib.run("moe.norm_router", x1=x1, ln2=w["ln2"], w_router=w["w_router"], w_shg=w["w_shg"].reshape(-1), h2_out=h2,
-                 logits_out=logits, gate_out=gate)
+        ids = self._get("ids", (T, self.top_k), torch.int32, dev)
+        rw = self._get("rw", (T, self.top_k), torch.float32, dev)
+        # (role moe.front does norm, router, gate dot, softmax and top-k in one launch; measured here it is the slower
+        # choice: the shared expert on the second stream can only start once that whole kernel is through, 47 us
+        # against 33 us for this part at 2 GPUs, so the short norm + router kernel stays in front of the fork)
+        one_launch = False
+        if one_launch:
+            _lib.run("moe.front", x1=x1, ln2=w["ln2"], w_router=w["w_router"], w_shg=w["w_shg"].reshape(-1), h2_out=h2,
+                     logits_out=logits, gate_out=gate, ids=ids, rw=rw)
+        else:
+            _lib.run("moe.norm_router", x1=x1, ln2=w["ln2"], w_router=w["w_router"], w_shg=w["w_shg"].reshape(-1),
+                     h2_out=h2, logits_out=logits, gate_out=gate)
         main, side = torch.cuda.current_stream(dev), moe._side_stream(dev)
         side.wait_stream(main)
         with torch.cuda.stream(side):
             _lib.run("moe.shared", x1=x1, h2=h2, gate=gate, w_gate=w["w_gate"], s_gate=moe._u8(w["s_gate"]),
                      w_up=w["w_up"], s_up=moe._u8(w["s_up"]), w_down=w["w_down"], s_down=moe._u8(w["s_down"]), out=base)
             ready = side.record_event()
-        ids, rw = moe.route(logits, self.top_k, self._get("ids", (T, self.top_k), torch.int32, dev),
-                            self._get("rw", (T, self.top_k), torch.float32, dev))
+        if not one_launch:
+            moe.route(logits, self.top_k, ids, rw)
         return base, h2, ids, rw, ready
 
     def _local_experts(self, h2_all, ids_all, rw_all):

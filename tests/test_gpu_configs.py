@@ -414,6 +414,34 @@ def test_qwen3_moe_one_call_contract_by_the_reference_names(q35):
                            w_norm=(w["ln2"] - 1).cuda().clone()))
 
 
+@pytest.mark.parametrize("T", [1, 64, 200])
+def test_moe_front_one_launch_head_of_the_block(q35, T):
+    """moe.front (RMSNorm + router + gate dot + softmax + top-k in one launch) against the role sequence
+    moe.norm_router -> moe.route and against the oracle's routing: ids bit-exact, rows and weights equal or within
+    fp32 rounding of the sum order"""
+    x1, w = moe_case(T, NE=256, seed=50 + T)
+    w["ln2"] = 1 + 0.05 * torch.randn(2048, generator=torch.Generator().manual_seed(T))
+    d = {k: v.cuda() for k, v in w.items()}
+    x = x1.cuda()
+    mk = lambda *s, dt=torch.float32: torch.full(s, float("nan") if dt != torch.int32 else -7, dtype=dt, device="cuda")  # noqa: E731
+    h2a, lga, gta = mk(T, 2048, dt=torch.bfloat16), mk(T, 256), mk(T)
+    q35.run("moe.norm_router", x1=x, ln2=d["ln2"], w_router=d["w_router"], w_shg=d["w_shg"].reshape(-1), h2_out=h2a,
+            logits_out=lga, gate_out=gta)
+    ida, rwa = q35.route(lga, 8)
+    h2b, lgb, gtb, idb, rwb = mk(T, 2048, dt=torch.bfloat16), mk(T, 256), mk(T), mk(T, 8, dt=torch.int32), mk(T, 8)
+    q35.run("moe.front", x1=x, ln2=d["ln2"], w_router=d["w_router"], w_shg=d["w_shg"].reshape(-1), h2_out=h2b,
+            logits_out=lgb, gate_out=gtb, ids=idb, rw=rwb)
+    assert torch.equal(h2a, h2b)
+    assert (lga - lgb).abs().max().item() <= 1e-4 * lga.abs().max().item()
+    assert (gta - gtb).abs().max().item() <= 1e-4 * max(1.0, gta.abs().max().item())
+    oids, orw = omoe.route(lgb.cpu(), 8)
+    assert torch.equal(idb.cpu(), oids)
+    assert (rwb.cpu() - orw).abs().max().item() <= 1e-5
+    same = (ida == idb).all(1)
+    assert same.float().mean().item() >= 0.98  # (the two kernels' logits differ in the last bits: a near-tie may flip)
+    assert (rwa[same] - rwb[same]).abs().max().item() <= 1e-4
+
+
 def test_expert_parallel_exchange_kernels_two_ranks_emulated_on_one_gpu(q35):
     """ep.publish / ep.wait / ep.reduce with two ranks' exchange buffers in this one GPU's memory, the ranks run one
     after the other: rows, ids and weights land in slice `rank` of BOTH buffers, the flags carry the exchange count,
