@@ -50,7 +50,7 @@ def kv_write(paged_kv_cache, cache_location, k_new, v_new, kv_scale=None, paged_
 
 
 def paged_attention_prefill(q, paged_kv_cache, qo_indptr, indptr, indices, last_page_len, out=None, *, sm_scale=None,
-                            k_new=None, v_new=None, kv_scale=None):
+                            k_new=None, v_new=None, kv_scale=None, paged_kv_scale=None):
     """Causal attention of T new tokens per sequence over the paged cache.  q [Ttot, HQ, D] bf16 with the sequences
     delimited by qo_indptr [B + 1]; the page table (indptr / indices / last_page_len) describes each sequence INCLUDING
     its new tokens.  k_new / v_new [Ttot, HKV, D], when given, are first written into the cache at the new tokens'
@@ -61,6 +61,8 @@ def paged_attention_prefill(q, paged_kv_cache, qo_indptr, indptr, indices, last_
               last_page_len=last_page_len, out=out)
     if kv_scale is not None:
         kw["kv_scale"] = kv_scale
+    if paged_kv_scale is not None:  # int8 cache: [pages, 2, P, HKV] bf16 row scales (read, and written for new rows)
+        kw["paged_kv_scale"] = paged_kv_scale
     if sm_scale is not None:
         kw["sm_scale"] = sm_scale if isinstance(sm_scale, torch.Tensor) else torch.tensor(
             [float(sm_scale)], dtype=torch.float32, device=q.device)

@@ -189,7 +189,7 @@ static const RoleDef kRoles[] = {
      R"({"in":[["k_new","bf16","[B,HKV,D]"],["v_new","bf16","[B,HKV,D]"],["cache_location","i32","[B,2]"],["kv_scale","f32","[2,HKV] optional"]],"out":[["paged_kv_cache","bf16|e4m3","[pages,2,P,HKV,D]"],["paged_kv_scale","bf16","[pages,2,P,HKV] optional: int8 cache bound as bytes, the rows' scales land here"]]})",
      run_attn_kv_write},
     {"attn.paged_prefill",
-     R"({"in":[["q","bf16","[T,HQ,D]"],["paged_kv_cache","bf16|e4m3","[pages,2,P,HKV,D]"],["qo_indptr","i32","[B+1]"],["indptr","i32","[B+1]"],["indices","i32","[N]"],["last_page_len","i32","[B]"],["sm_scale","f32","[1] optional"],["kv_scale","f32","[2,HKV] optional: FP8 cache with per-head scales; absent: the stored x 8 form"],["k_new","bf16","[T,HKV,D] optional: written into the cache first"],["v_new","bf16","[T,HKV,D] optional"]],"out":[["out","bf16","[T,HQ,D]"]]})",
+     R"({"in":[["q","bf16","[T,HQ,D]"],["paged_kv_cache","bf16|e4m3","[pages,2,P,HKV,D]"],["qo_indptr","i32","[B+1]"],["indptr","i32","[B+1]"],["indices","i32","[N]"],["last_page_len","i32","[B]"],["sm_scale","f32","[1] optional"],["kv_scale","f32","[2,HKV] optional: FP8 cache with per-head scales; absent: the stored x 8 form"],["paged_kv_scale","bf16","[pages,2,P,HKV] optional: int8 cache bound as bytes, one scale per row and head; new rows' scales are written"],["k_new","bf16","[T,HKV,D] optional: written into the cache first"],["v_new","bf16","[T,HKV,D] optional"]],"out":[["out","bf16","[T,HQ,D]"]]})",
      run_attn_paged_prefill},
     {"gdn.step",
      R"({"in":[["q","bf16","[B,NK,DK]"],["k","bf16","[B,NK,DK]"],["v","bf16","[B,NV,DV]"],["g","f32","[B,NV]"],["beta","bf16","[B,NV]"],["state_in","f32","[B,NV,DK,DV]"]],"out":[["o","bf16","[B,NV,DV]"],["state_out","f32","[B,NV,DK,DV]"]]})",

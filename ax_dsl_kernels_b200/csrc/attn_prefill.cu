@@ -30,6 +30,7 @@ struct PrefillArgs {
   const __nv_bfloat16* q;      // [Ttot, HQ, D]
   const void* cache;           // [pages, 2, P, HKV, D] bf16 or e4m3
   const float* kv_scale;       // FP8 cache: [2, HKV] per-head scales, or null = the constant form (stored x * 8)
+  const __nv_bfloat16* row_scale;  // int8 cache: [pages, 2, P, HKV], one scale per cached row and head
   const int* qo_indptr;        // [B + 1] token ranges of the sequences inside q
   const int* indptr; const int* indices; const int* last_page_len;  // page table incl. the new tokens
   const float* sm_scale;
@@ -38,8 +39,12 @@ struct PrefillArgs {
   int* status;
 };
 
-template <int D, bool FP8>
+// KVF: 0 bf16 cache, 1 FP8 E4M3, 2 int8 with a bf16 scale per row and head (kv_quant_row,
+// models/qwen38_27b/decode/q35_group.py:198-222): the one-byte formats share the staging ring; int8 rows become
+// bf16(int8 x scale) element by element, the reference's page dequantisation, on their way into the MMA tile.
+template <int D, int KVF>
 __global__ void __launch_bounds__(256, 1) attn_prefill_kernel(const PrefillArgs a) {
+  constexpr bool FP8 = KVF != 0;
   constexpr int ROWB = D * 2, CPR = ROWB / 16, TILE_BYTES = PF_KEYS * ROWB;
   // FP8: [K tile | V tile] bf16 work tiles, then two staging stages of raw bytes (K rows then V rows, D bytes each)
   constexpr int RAWB = D, RCPR = RAWB / 16, RAW_TILE = PF_KEYS * RAWB;
@@ -60,8 +65,8 @@ __global__ void __launch_bounds__(256, 1) attn_prefill_kernel(const PrefillArgs 
   }
   const int hist = kv_len - tq;                 // tokens before this call
   const int page0 = a.indptr[b];
-  const float k_deq = !FP8 ? 1.f : a.kv_scale ? a.kv_scale[kvh] : 0.125f;
-  const float v_deq = !FP8 ? 1.f : a.kv_scale ? a.kv_scale[a.HKV + kvh] : 0.125f;
+  const float k_deq = KVF != 1 ? 1.f : a.kv_scale ? a.kv_scale[kvh] : 0.125f;
+  const float v_deq = KVF != 1 ? 1.f : a.kv_scale ? a.kv_scale[a.HKV + kvh] : 0.125f;
   const float scale_log2 = (a.sm_scale ? a.sm_scale[0] : rsqrtf(float(D))) * PF_LOG2E * k_deq;
 
   // this thread's two rows: row m = warp * 16 + r (+ 8); token = m / 8, head = m % 8
@@ -135,11 +140,40 @@ __global__ void __launch_bounds__(256, 1) attn_prefill_kernel(const PrefillArgs 
     const int kk = t * PF_KEYS;
     if constexpr (FP8) {  // raw bytes -> the swizzled bf16 tiles (16 bytes in, two 16-byte chunks out)
       const uint8_t* raw = smem + 2 * TILE_BYTES + (t & 1) * 2 * RAW_TILE;
+      float* s_rs = reinterpret_cast<float*>(smem + 2 * TILE_BYTES + 4 * RAW_TILE);  // int8: [2][64] row scales
+      if constexpr (KVF == 2) {
+        if (tid < 2 * PF_KEYS) {  // this tile's K and V row scales; rows past the cached length count as 0
+          const int kv = tid / PF_KEYS, key = tid % PF_KEYS, pos = kk + key;
+          float sc = 0.f;
+          if (pos < kv_len) {
+            int page = a.indices[page0 + min(pos / a.P, np - 1)];
+            if (page < 0 || page >= a.num_pages) page = 0;
+            sc = __bfloat162float(a.row_scale[((size_t(page) * 2 + kv) * a.P + pos % a.P) * a.HKV + kvh]);
+          }
+          s_rs[tid] = sc;
+        }
+        __syncthreads();
+      }
       for (int idx = tid; idx < 2 * PF_KEYS * RCPR; idx += 256) {
         const int kv = idx / (PF_KEYS * RCPR), rem = idx % (PF_KEYS * RCPR), key = rem / RCPR, ch = rem % RCPR;
         const uint4 in = *reinterpret_cast<const uint4*>(raw + kv * RAW_TILE + key * RAWB + ch * 16);
         const uint32_t w[4] = {in.x, in.y, in.z, in.w};
         uint32_t o8[8];
+        if constexpr (KVF == 2) {
+          // bf16(int8 x scale), exact: 0x4B000000 | (b ^ 0x80) is the float 2^23 + 128 + b; the fused multiply-add
+          // leaves b x scale (a 15-bit product), one rounding to bf16 follows
+          const float sc = s_rs[kv * PF_KEYS + key], off = -8388736.f * sc;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const uint32_t xs = w[j] ^ 0x80808080u;
+            const float f0 = __uint_as_float(__byte_perm(xs, 0x4B000000u, 0x7540));
+            const float f1 = __uint_as_float(__byte_perm(xs, 0x4B000000u, 0x7541));
+            const float f2 = __uint_as_float(__byte_perm(xs, 0x4B000000u, 0x7542));
+            const float f3 = __uint_as_float(__byte_perm(xs, 0x4B000000u, 0x7543));
+            o8[2 * j] = pack_bf16(fmaf(f0, sc, off), fmaf(f1, sc, off));
+            o8[2 * j + 1] = pack_bf16(fmaf(f2, sc, off), fmaf(f3, sc, off));
+          }
+        } else {
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           const __half2_raw lo = __nv_cvt_fp8x2_to_halfraw2(__nv_fp8x2_storage_t(w[j] & 0xffffu), __NV_E4M3);
@@ -148,6 +182,7 @@ __global__ void __launch_bounds__(256, 1) attn_prefill_kernel(const PrefillArgs 
           const float2 fh = __half22float2(*reinterpret_cast<const __half2*>(&hi));
           o8[2 * j] = pack_bf16(fl.x, fl.y);
           o8[2 * j + 1] = pack_bf16(fh.x, fh.y);
+        }
         }
         const uint32_t dst = sK + kv * TILE_BYTES + key * ROWB;
         asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst + (((2 * ch) ^ (key & 7)) << 4)), "r"(o8[0]),
@@ -267,8 +302,8 @@ __global__ void __launch_bounds__(256, 1) attn_prefill_kernel(const PrefillArgs 
 __global__ void attn_kv_write_rows_kernel(const __nv_bfloat16* __restrict__ k_new, const __nv_bfloat16* __restrict__ v_new,
                                           const int* __restrict__ qo_indptr, const int* __restrict__ indptr,
                                           const int* __restrict__ indices, const int* __restrict__ last_page_len,
-                                          void* cache, const float* kv_scale, int fp8, int B, int HKV, int D, int P,
-                                          int num_pages, int* status) {
+                                          void* cache, const float* kv_scale, __nv_bfloat16* row_scale, int fp8, int B,
+                                          int HKV, int D, int P, int num_pages, int* status) {
   const int tok = blockIdx.x;  // global token index
   int b = 0;
   while (b + 1 < B && qo_indptr[b + 1] <= tok) ++b;
@@ -282,6 +317,26 @@ __global__ void attn_kv_write_rows_kernel(const __nv_bfloat16* __restrict__ k_ne
   if (page < 0 || page >= num_pages) { if (threadIdx.x == 0) atomicOr(status, DS_BAD_PAGE); return; }
   const int n = HKV * D;
   const size_t krow = ((size_t(page) * 2 + 0) * P + pos % P) * n, vrow = ((size_t(page) * 2 + 1) * P + pos % P) * n;
+  if (row_scale) {  // int8 rows with a bf16 scale per row and head: the arithmetic of attn.kv_write's int8 form
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    int8_t* c8 = static_cast<int8_t*>(cache);
+    for (int item = warp; item < 2 * HKV; item += blockDim.x >> 5) {
+      const int kv = item / HKV, h = item % HKV;
+      const __nv_bfloat16* src = (kv ? v_new : k_new) + size_t(tok) * n + size_t(h) * D;
+      float amax = 0.f;
+      for (int i = lane; i < D; i += 32) amax = fmaxf(amax, fabsf(__bfloat162float(src[i])));
+      for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+      amax = fmaxf(amax, round_bf16(1e-5f));
+      const float sc = round_bf16(amax * round_bf16(1.f / 127.f)), inv = round_bf16(1.f / sc);
+      const size_t row = (size_t(page) * 2 + kv) * P + pos % P;
+      for (int i = lane; i < D; i += 32) {
+        const float qv = rintf(round_bf16(__bfloat162float(src[i]) * inv));
+        c8[(row * HKV + h) * D + i] = int8_t(fminf(fmaxf(qv, -127.f), 127.f));
+      }
+      if (lane == 0) row_scale[row * HKV + h] = __float2bfloat16_rn(sc);
+    }
+    return;
+  }
   if (fp8) {  // e4m3(x * 8), or e4m3(x / scale_h) with per-head scales: the arithmetic of attn.kv_write
     __nv_fp8_e4m3* c8 = static_cast<__nv_fp8_e4m3*>(cache);
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
@@ -298,11 +353,11 @@ __global__ void attn_kv_write_rows_kernel(const __nv_bfloat16* __restrict__ k_ne
   }
 }
 
-template <int D, bool FP8>
+template <int D, int KVF>
 static int launch_prefill(const PrefillArgs& a, dim3 grid, cudaStream_t stream) {
-  constexpr int smem = FP8 ? 2 * PF_KEYS * D * 2 + 4 * PF_KEYS * D : 4 * PF_KEYS * D * 2;
-  Q35_TRY(ensure_dynamic_smem(reinterpret_cast<const void*>(attn_prefill_kernel<D, FP8>), smem));
-  attn_prefill_kernel<D, FP8><<<grid, 256, smem, stream>>>(a);
+  constexpr int smem = KVF ? 2 * PF_KEYS * D * 2 + 4 * PF_KEYS * D + 2 * PF_KEYS * 4 : 4 * PF_KEYS * D * 2;
+  Q35_TRY(ensure_dynamic_smem(reinterpret_cast<const void*>(attn_prefill_kernel<D, KVF>), smem));
+  attn_prefill_kernel<D, KVF><<<grid, 256, smem, stream>>>(a);
   Q35_CUDA_LAUNCH_CHECK("attn.paged_prefill");
   return 0;
 }
@@ -334,14 +389,19 @@ int run_attn_paged_prefill(Call& c) {
               Q35_ERR_SHAPE, "attn.paged_prefill: k_new / v_new [T, HKV, D]");
   Q35_REQUIRE(!kvs.present || (fp8 && kvs.numel() == 2 * HKV), Q35_ERR_SHAPE,
               "attn.paged_prefill: kv_scale [2, HKV] goes with an FP8 cache");
+  Tensor rsc;
+  Q35_TRY(c.get("paged_kv_scale", M(Q35_BF16), &rsc, false));
+  Q35_REQUIRE(!rsc.present || (fp8 && !kvs.present && rsc.numel() == cache.s[0] * 2 * P * HKV), Q35_ERR_SHAPE,
+              "attn.paged_prefill: paged_kv_scale [pages, 2, P, HKV] bf16 goes with an int8 cache (bound as bytes)");
   c.ws_need = 0;
   if (c.dry || T == 0) return 0;
   Q35_REQUIRE(aligned16(q.p) && aligned16(cache.p) && aligned16(out.p), Q35_ERR_ALIGN, "attn.paged_prefill: alignment");
   if (kn.present) {
     attn_kv_write_rows_kernel<<<unsigned(T), 128, 0, c.stream>>>(
         kn.as<__nv_bfloat16>(), vn.as<__nv_bfloat16>(), qo.as<int>(), indptr.as<int>(), indices.as<int>(),
-        lpl.as<int>(), cache.p, kvs.present ? kvs.as<float>() : nullptr, fp8, int(B), int(HKV), int(D), int(P),
-        int(cache.s[0]), device_status_ptr());
+        lpl.as<int>(), cache.p, kvs.present ? kvs.as<float>() : nullptr,
+        rsc.present ? rsc.as<__nv_bfloat16>() : nullptr, fp8, int(B), int(HKV), int(D), int(P), int(cache.s[0]),
+        device_status_ptr());
     Q35_CUDA_LAUNCH_CHECK("attn.kv_write_rows");
   }
   PrefillArgs a{};
@@ -356,8 +416,12 @@ int run_attn_paged_prefill(Call& c) {
   // the longest sequence is not known on the host: the grid covers T tokens for every sequence, CTAs past a
   // sequence's own length leave at once
   const dim3 grid{unsigned((T + PF_TOK - 1) / PF_TOK), unsigned(HKV), unsigned(B)};
-  if (D == 256) return fp8 ? launch_prefill<256, true>(a, grid, c.stream) : launch_prefill<256, false>(a, grid, c.stream);
-  return fp8 ? launch_prefill<128, true>(a, grid, c.stream) : launch_prefill<128, false>(a, grid, c.stream);
+  if (rsc.present) {
+    a.row_scale = rsc.as<__nv_bfloat16>();
+    return D == 256 ? launch_prefill<256, 2>(a, grid, c.stream) : launch_prefill<128, 2>(a, grid, c.stream);
+  }
+  if (D == 256) return fp8 ? launch_prefill<256, 1>(a, grid, c.stream) : launch_prefill<256, 0>(a, grid, c.stream);
+  return fp8 ? launch_prefill<128, 1>(a, grid, c.stream) : launch_prefill<128, 0>(a, grid, c.stream);
 }
 
 }  // namespace q35

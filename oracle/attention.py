@@ -100,7 +100,7 @@ def lse_merge(pm, pl, po):
     return torch.where(L[..., None] > 0, o / L[..., None].clamp_min(1e-38), torch.zeros_like(o)).to(torch.bfloat16)
 
 
-def paged_prefill(q, cache, qo_indptr, indptr, indices, last_page_len, sm_scale=None, kv_scale=None):
+def paged_prefill(q, cache, qo_indptr, indptr, indices, last_page_len, sm_scale=None, kv_scale=None, row_scale=None):
     """T new tokens per sequence against the paged cache that already holds their K / V rows, causal:
     token i of a sequence with `hist` earlier tokens sees keys 0 .. hist + i (prefill form of the decode golden;
     reference kernels: flash_attn.py:471-610, models/qwen35_2b/whole/src/q35_prefill.py:250-318).
@@ -116,7 +116,7 @@ def paged_prefill(q, cache, qo_indptr, indptr, indices, last_page_len, sm_scale=
         q0, q1 = int(qo_indptr[b]), int(qo_indptr[b + 1])
         if q1 == q0:
             continue
-        k, v = gather_kv(cache, indptr, indices, last_page_len, b, kv_scale)
+        k, v = gather_kv(cache, indptr, indices, last_page_len, b, kv_scale, row_scale)
         hist = k.shape[0] - (q1 - q0)
         qb = q[q0:q1].float().reshape(q1 - q0, HKV, G, D)
         s = torch.einsum("thgd,lhd->thgl", qb, k) * scale

@@ -642,6 +642,40 @@ def test_paged_prefill_fp8_cache(q35, per_head, D, HKV, HQ):
                   bf16_step=True)
 
 
+@pytest.mark.parametrize("D,HKV,HQ", [(256, 2, 16), (128, 4, 8)])
+def test_paged_prefill_int8_cache(q35, D, HKV, HQ):
+    """int8 KV rows with a bf16 scale per row and head in the prefill role: history rows from the cache, the call's own
+    rows quantised as they are written (rows and scales bit-identical to the oracle's kv_quant_row restatement),
+    attention over bf16(int8 x scale), and a decode step over the resulting cache"""
+    hist, T, P = [70, 0, 200], [33, 64, 130], 64
+    g = torch.Generator().manual_seed(77 + D)
+    ctxs = [h + t for h, t in zip(hist, T)]
+    _, kv, indptr, indices, last, _ = paged_case(ctxs, P=P, HKV=HKV, HQ=HQ, D=D, seed=9)
+    cache, scales = codecs.kv_quant_int8_rows(kv.to(torch.bfloat16))
+    qo = torch.tensor([0, *torch.tensor(T).cumsum(0).tolist()], dtype=torch.int32)
+    n = sum(T)
+    q = torch.randn((n, HQ, D), generator=g).to(torch.bfloat16)
+    k_new = torch.randn((n, HKV, D), generator=g).to(torch.bfloat16)
+    v_new = (torch.randn((n, HKV, D), generator=g) * 2).to(torch.bfloat16)
+    ref_cache, ref_scales = cache.clone(), scales.clone()
+    for b in range(len(T)):
+        for i in range(T[b]):
+            pos = hist[b] + i
+            page = int(indices[int(indptr[b]) + pos // P])
+            oattn.store_paged_kv(ref_cache, torch.tensor([[page, pos % P]]), k_new[int(qo[b]) + i][None],
+                                 v_new[int(qo[b]) + i][None], row_scale=ref_scales)
+    ref = oattn.paged_prefill(q, ref_cache, qo, indptr, indices, last, row_scale=ref_scales)
+    gc, gs = cache.cuda(), scales.cuda()
+    out = q35.paged_attention_prefill(q.cuda(), gc, qo.cuda(), indptr.cuda(), indices.cuda(), last.cuda(),
+                                      k_new=k_new.cuda(), v_new=v_new.cuda(), paged_kv_scale=gs)
+    assert torch.equal(gc.cpu(), ref_cache) and torch.equal(gs.cpu().view(torch.int16), ref_scales.view(torch.int16))
+    assert_parity(out.cpu(), ref, per_seq=True, bf16_step=True)  # (0.9 M elements per token RMS: see the FP8 test)
+    qd = torch.randn((3, HQ, D), generator=g).to(torch.bfloat16)
+    dec = q35.paged_attention_decode(qd.cuda(), gc, indptr.cuda(), indices.cuda(), last.cuda(), paged_kv_scale=gs)
+    assert_parity(dec.cpu(), oattn.paged_decode(qd, ref_cache, indptr, indices, last, row_scale=ref_scales), per_seq=True,
+                  bf16_step=True)
+
+
 def test_lm_head_golden_fixture_and_vocabulary_sized(q35, golden):
     """MXFP4 output projection (mul_mat_mx4 / torch_logits): the reference fixture, then a vocabulary-sized matrix"""
     from ax_dsl_kernels_b200.moe import lm_head
