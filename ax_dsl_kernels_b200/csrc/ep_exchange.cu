@@ -33,7 +33,7 @@ namespace q35 {
 
 constexpr int EP_MAX_RANKS = 16;
 constexpr int EP_HDR_BYTES = 1024;
-constexpr uint32_t EP_WAIT_POLLS = 1u << 21;
+constexpr uint32_t EP_WAIT_POLLS = 1u << 20;  // about a second of polling
 
 struct EpPeers { uint8_t* base[EP_MAX_RANKS]; };
 
@@ -46,10 +46,14 @@ __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
-// waits until every one of the first n flags has reached `epoch`; false when the poll budget ran out
-__device__ __forceinline__ bool ep_wait_flags(const uint32_t* flags, int n, uint32_t epoch) {
+// waits until every one of the first n flags has reached `epoch`; false when the poll budget ran out.  Once a wait has
+// run out on this GPU (the bit stays in the status word until the host reads it) later waits give up at once: a rank
+// that is gone costs the others one timeout, not one per kernel of every following step.
+__device__ __forceinline__ bool ep_wait_flags(const uint32_t* flags, int n, uint32_t epoch, const int* status) {
   for (int p = 0; p < n; ++p) {
     uint32_t polls = 0;
+    if (int32_t(ld_acquire_sys(flags + p) - epoch) >= 0) continue;
+    if (*reinterpret_cast<const volatile int*>(status) & DS_WAIT_TIMEOUT) return false;
     // (epochs wrap after 2^32 exchanges; the signed difference keeps the comparison right across the wrap)
     while (int32_t(ld_acquire_sys(flags + p) - epoch) < 0) {
       if (++polls > EP_WAIT_POLLS) return false;
@@ -101,7 +105,7 @@ __global__ void __launch_bounds__(256) ep_publish_kernel(const uint4* __restrict
     // ... and waits for everybody's rows of this exchange (one thread per source rank), so that the kernels that follow
     // in the stream find the gather regions complete
     if (wait_all && threadIdx.x < N &&
-        !ep_wait_flags(reinterpret_cast<const uint32_t*>(mine + 256) + threadIdx.x, 1, epoch))
+        !ep_wait_flags(reinterpret_cast<const uint32_t*>(mine + 256) + threadIdx.x, 1, epoch, status))
       atomicOr(status, DS_WAIT_TIMEOUT | 0x800);
   }
 }
@@ -112,7 +116,7 @@ __global__ void ep_wait_gather_kernel(uint8_t* mine, int N, int* status) {
   pdl_launch();
   if (threadIdx.x < N) {  // one thread per source rank
     const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(mine);
-    if (!ep_wait_flags(reinterpret_cast<const uint32_t*>(mine + 256) + threadIdx.x, 1, epoch))
+    if (!ep_wait_flags(reinterpret_cast<const uint32_t*>(mine + 256) + threadIdx.x, 1, epoch, status))
       atomicOr(status, DS_WAIT_TIMEOUT | 0x800);
   }
 }
@@ -133,7 +137,7 @@ __global__ void __launch_bounds__(256) ep_reduce_kernel(const __nv_bfloat16* __r
   // ... and one thread per peer waits for that peer's flag here
   if (threadIdx.x == 0) ok = true;
   __syncthreads();
-  if (threadIdx.x < N && !ep_wait_flags(reinterpret_cast<const uint32_t*>(mine + 512) + threadIdx.x, 1, epoch)) {
+  if (threadIdx.x < N && !ep_wait_flags(reinterpret_cast<const uint32_t*>(mine + 512) + threadIdx.x, 1, epoch, status)) {
     ok = false;
     atomicOr(status, DS_WAIT_TIMEOUT | 0x1000);
   }
@@ -191,7 +195,7 @@ __global__ void __launch_bounds__(256) ar_oneshot_kernel(const float4* __restric
     if (threadIdx.x < N) st_release_sys(reinterpret_cast<uint32_t*>(peers.base[threadIdx.x] + 256) + rank, epoch);
     if (threadIdx.x == 0) { hdr[1] = 0; hdr[0] = epoch; }
   }
-  if (threadIdx.x < N && !ep_wait_flags(reinterpret_cast<const uint32_t*>(mine + 256) + threadIdx.x, 1, epoch))
+  if (threadIdx.x < N && !ep_wait_flags(reinterpret_cast<const uint32_t*>(mine + 256) + threadIdx.x, 1, epoch, status))
     atomicOr(status, DS_WAIT_TIMEOUT | 0x2000);
   __syncthreads();
   const uint8_t* slots = mine + EP_HDR_BYTES + par;

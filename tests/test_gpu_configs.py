@@ -568,3 +568,42 @@ def test_oneshot_all_reduce_two_ranks_emulated_on_one_gpu(q35):
             for b in bufs:  # r's addend reached both buffers
                 assert torch.equal(b[1024 + par + r * slot:1024 + par + r * slot + n * 4].view(torch.float32), xs[r])
     assert q35.device_status() == 0
+
+
+def test_exchange_wait_runs_out_and_reports_instead_of_hanging(q35):
+    """A rank whose peer never publishes: ep.wait polls a flag that nothing raises, gives up after its poll budget
+    (about a second), records the wait site in the status word and returns; the next wait gives up at once while the
+    bit is still set, and after the host has read (and cleared) the status the exchange works again."""
+    import time
+    N, T, H, K = 2, 8, 512, 4
+    al = lambda n: (n + 255) // 256 * 256  # noqa: E731
+    o_h2, o_ids = 1024, 1024 + al(N * T * H * 2)
+    o_rw = o_ids + al(N * T * K * 4)
+    total = o_rw + al(N * T * K * 4)
+    bufs = [torch.zeros(total, dtype=torch.uint8, device="cuda") for _ in range(N)]
+    peers = torch.tensor([b.data_ptr() for b in bufs], dtype=torch.int64, device="cuda").view(torch.uint8)
+    rank0 = torch.tensor([0], dtype=torch.int32, device="cuda")
+    rank1 = torch.tensor([1], dtype=torch.int32, device="cuda")
+    flag = torch.ones(1, dtype=torch.int32, device="cuda")
+    view = lambda b, off, n, dt, shape: b[off:off + n].view(dt).view(shape)  # noqa: E731
+    regs = lambda b: dict(h2_all=view(b, o_h2, N * T * H * 2, torch.bfloat16, (N * T, H)),  # noqa: E731
+                          ids_all=view(b, o_ids, N * T * K * 4, torch.int32, (N * T, K)),
+                          rw_all=view(b, o_rw, N * T * K * 4, torch.float32, (N * T, K)))
+    h2 = torch.zeros((T, H), dtype=torch.bfloat16, device="cuda")
+    ids = torch.zeros((T, K), dtype=torch.int32, device="cuda")
+    rw = torch.zeros((T, K), device="cuda")
+    assert q35.device_status() == 0
+    q35.run("ep.publish", h2=h2, ids=ids, rw=rw, peers=peers, rank=rank0, exchange=bufs[0], no_wait=flag, **regs(bufs[0]))
+    q35.run("ep.wait", peers=peers, rank=rank0, exchange=bufs[0])  # rank 1 never publishes
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    q35.run("ep.wait", peers=peers, rank=rank0, exchange=bufs[0])
+    torch.cuda.synchronize()
+    assert time.perf_counter() - t0 < 0.5  # gives up at once while the timeout is on record
+    st = q35.device_status()
+    assert st & 0x4 and st & 0x800, hex(st)
+    assert q35.device_status() == 0
+    q35.run("ep.publish", h2=h2, ids=ids, rw=rw, peers=peers, rank=rank1, exchange=bufs[1], no_wait=flag, **regs(bufs[1]))
+    q35.run("ep.wait", peers=peers, rank=rank0, exchange=bufs[0])  # now both have published exchange 1
+    torch.cuda.synchronize()
+    assert q35.device_status() == 0
