@@ -589,6 +589,8 @@ def run_profile_case(name, reps):
     torch.cuda.set_device(0)
     if name == "attn":
         B, CTX = 16, 8192  # 268 MB of bf16 KV
+    if name == "attn_fp8":
+        B, CTX = 32, 8192  # 268 MB of FP8 KV
     g = torch.Generator(device=dev).manual_seed(1)
     rn = lambda *s: torch.randn(s, generator=g, device=dev)  # noqa: E731
     bf = torch.bfloat16
@@ -634,9 +636,14 @@ def run_profile_case(name, reps):
         fn = lambda: lm_head(x, pk, sc, logits, token)  # noqa: E731
         units = 1
     else:
-        wl = Workload(dev, seed=1, attn=(name == "attn"))
+        wl = Workload(dev, seed=1, attn=name in ("attn", "attn_fp8"))
         units = B
-        if name == "attn":
+        if name == "attn_fp8":  # the same launch over an FP8 E4M3 cache with per-head scales
+            kvs = (wl.cache.float().abs().amax((0, 2, 4)) / 448.0).contiguous()
+            c8 = (wl.cache.float() / kvs.reshape(1, 2, 1, HKV, 1)).to(torch.float8_e4m3fn)
+            fn = lambda: q35.paged_attention_decode(wl.q, c8, wl.indptr, wl.indices, wl.last, wl.attn_out,  # noqa: E731
+                                                    sm_scale=wl.sm_scale, kv_scale=kvs)
+        elif name == "attn":
             fn = lambda: q35.paged_attention_decode(wl.q, wl.cache, wl.indptr, wl.indices, wl.last, wl.attn_out,  # noqa: E731
                                                     sm_scale=wl.sm_scale)
         elif name == "gdn":
@@ -674,7 +681,7 @@ def main():
     ap.add_argument("--attn-read-ratio", type=float, default=268.70 / 268.44,
                     help="DRAM bytes read per K/V byte by the attention kernel, from an ncu capture (default: the capture "
                          "of the 16 x 8192 case, 268.70 MB read for 268.44 MB of K/V)")
-    ap.add_argument("--profile-case", choices=["attn", "gdn", "moe", "gdn_prefill", "attn_prefill", "moe_prefill", "lm_head"], help="run one kernel on a capture-sized case")
+    ap.add_argument("--profile-case", choices=["attn", "attn_fp8", "gdn", "moe", "gdn_prefill", "attn_prefill", "moe_prefill", "lm_head"], help="run one kernel on a capture-sized case")
     args = ap.parse_args()
     if args.profile_case:
         run_profile_case(args.profile_case, max(1, min(args.steps, 5)))
