@@ -210,7 +210,7 @@ static const RoleDef kRoles[] = {
      R"({"in":[["x1","bf16","[T,H]"],["ln2","f32","[H]"],["w_router","bf16","[NE,H]"],["w_shg","bf16","[H] optional: shared-expert gate vector"],["workspace","u8","[*]"]],"out":[["h2_out","bf16","[T,H]"],["logits_out","f32","[T,NE]"],["gate_out","f32","[T] with w_shg"],["ids","i32","[T,K]"],["rw","f32","[T,K]"]]})",
      run_moe_front},
     {"ep.publish",
-     R"({"in":[["h2","bf16","[T,H]"],["ids","i32","[T,K]"],["rw","f32","[T,K]"],["peers","u8","[8 N]: the ranks' exchange buffer addresses as mapped here"],["rank","i32","[1]"],["no_wait","i32","[1] optional: return after publishing instead of waiting for every rank's rows; ep.wait does that later"]],"out":[["exchange","u8","[*]: this rank's exchange buffer, 1 KB header first"],["h2_all","bf16","[N,T,H] region of exchange"],["ids_all","i32","[N,T,K] region of exchange"],["rw_all","f32","[N,T,K] region of exchange"]]})",
+     R"({"in":[["h2","bf16","[T,H]"],["ids","i32","[T,K]"],["rw","f32","[T,K]"],["peers","u8","[8 N]: the ranks' exchange buffer addresses as mapped here, peers[rank] = exchange; the kernels read the table"],["rank","i32","[1]: read by the kernels"],["no_wait","i32","[1] optional: return after publishing instead of waiting for every rank's rows; ep.wait does that later"]],"out":[["exchange","u8","[*]: this rank's exchange buffer, 1 KB header first"],["h2_all","bf16","[N,T,H] region of exchange"],["ids_all","i32","[N,T,K] region of exchange"],["rw_all","f32","[N,T,K] region of exchange"]]})",
      run_ep_publish},
     {"ep.wait",
      R"({"in":[["peers","u8","[8 N]"],["rank","i32","[1]"]],"out":[["exchange","u8","[*]: returns when every rank's rows of the current exchange have arrived, or records a wait timeout"]]})",

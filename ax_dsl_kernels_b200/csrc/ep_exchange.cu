@@ -23,8 +23,6 @@
 // status word and lets the kernel finish (the output of that step is then wrong and the host sees the status).
 // Plain loads and stores only: no multimem, no TMA on peer memory.
 #include <algorithm>
-#include <mutex>
-#include <vector>
 
 #include "abi.h"
 #include "common.cuh"
@@ -35,7 +33,22 @@ constexpr int EP_MAX_RANKS = 16;
 constexpr int EP_HDR_BYTES = 1024;
 constexpr uint32_t EP_WAIT_POLLS = 1u << 20;  // about a second of polling
 
-struct EpPeers { uint8_t* base[EP_MAX_RANKS]; };
+// the ranks' exchange buffer addresses as this process maps them: a table in device memory, read by the kernels
+// (nothing of it is read on the host, so a call can be captured from its first use on)
+struct EpPeers {
+  const unsigned long long* tab;
+  const int* rank_ptr;
+  uint8_t* self;  // the `exchange` argument of the call: must be entry `rank` of the table
+  // a table that does not name `self` at `rank` (a stale or foreign table) is recorded and the kernel does nothing
+  __device__ __forceinline__ bool bound(int N, int* status) const {
+    const int r = rank_ptr[0];
+    if (r >= 0 && r < N && reinterpret_cast<uint8_t*>(tab[r]) == self) return true;
+    if (threadIdx.x == 0 && blockIdx.x == 0) atomicOr(status, 0x4000);
+    return false;
+  }
+  __device__ __forceinline__ uint8_t* base(int p) const { return reinterpret_cast<uint8_t*>(tab[p]); }
+  __device__ __forceinline__ int rank() const { return rank_ptr[0]; }
+};
 
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
   uint32_t v;
@@ -66,19 +79,21 @@ __device__ __forceinline__ bool ep_wait_flags(const uint32_t* flags, int n, uint
 // ep.publish: my rows -> slice `rank` of every rank's gather regions; the last CTA raises my gather flag everywhere
 // and (wait_all) waits for everybody else's, which saves the launch of ep.wait.
 __global__ void __launch_bounds__(256) ep_publish_kernel(const uint4* __restrict__ h2, const uint4* __restrict__ ids,
-                                                         const uint4* __restrict__ rw, EpPeers peers, int N, int rank,
+                                                         const uint4* __restrict__ rw, EpPeers peers, int N,
                                                          long long off_h2, long long off_ids, long long off_rw,
                                                          int n_h2, int n_ids, int n_rw,  // counts of 16-byte units
                                                          int wait_all, int* status) {
   pdl_wait();
   pdl_launch();
-  uint8_t* mine = peers.base[rank];
+  if (!peers.bound(N, status)) return;
+  const int rank = peers.rank();
+  uint8_t* mine = peers.base(rank);
   const int per_peer = n_h2 + n_ids + n_rw;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < (long long)N * per_peer;
        i += (long long)gridDim.x * blockDim.x) {
     const int q = int(i / per_peer);
     int j = int(i % per_peer);
-    uint8_t* dst = peers.base[q];
+    uint8_t* dst = peers.base(q);
     if (j < n_h2) {
       reinterpret_cast<uint4*>(dst + off_h2)[(long long)rank * n_h2 + j] = h2[j];
     } else if ((j -= n_h2) < n_ids) {
@@ -99,7 +114,7 @@ __global__ void __launch_bounds__(256) ep_publish_kernel(const uint4* __restrict
     const uint32_t epoch = hdr[0] + 1;  // only this CTA touches the epoch, once per launch
     __threadfence_system();
     if (threadIdx.x < N)
-      st_release_sys(reinterpret_cast<uint32_t*>(peers.base[threadIdx.x] + 256) + rank, epoch);
+      st_release_sys(reinterpret_cast<uint32_t*>(peers.base(threadIdx.x) + 256) + rank, epoch);
     __syncthreads();
     if (threadIdx.x == 0) { hdr[0] = epoch; __threadfence(); }
     // ... and waits for everybody's rows of this exchange (one thread per source rank), so that the kernels that follow
@@ -111,9 +126,11 @@ __global__ void __launch_bounds__(256) ep_publish_kernel(const uint4* __restrict
 }
 
 // ep.wait: until every rank's rows of the current exchange are in my gather regions
-__global__ void ep_wait_gather_kernel(uint8_t* mine, int N, int* status) {
+__global__ void ep_wait_gather_kernel(EpPeers peers, int N, int* status) {
   pdl_wait();
   pdl_launch();
+  if (!peers.bound(N, status)) return;
+  uint8_t* mine = peers.self;
   if (threadIdx.x < N) {  // one thread per source rank
     const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(mine);
     if (!ep_wait_flags(reinterpret_cast<const uint32_t*>(mine + 256) + threadIdx.x, 1, epoch, status))
@@ -124,16 +141,18 @@ __global__ void ep_wait_gather_kernel(uint8_t* mine, int N, int* status) {
 // ep.reduce: raise my done flag everywhere (my partial sums were written by the previous kernel of this stream), wait
 // for everybody's, then out[t] = bf16(base[t] + sum over ranks p, in rank order, of partial_p[rank * T + t]).
 __global__ void __launch_bounds__(256) ep_reduce_kernel(const __nv_bfloat16* __restrict__ base, EpPeers peers, int N,
-                                                        int rank, long long off_partial, int T, int H,
+                                                        long long off_partial, int T, int H,
                                                         __nv_bfloat16* __restrict__ out, int* status) {
   pdl_wait();
   pdl_launch();
-  uint8_t* mine = peers.base[rank];
+  if (!peers.bound(N, status)) return;
+  const int rank = peers.rank();
+  uint8_t* mine = peers.base(rank);
   __shared__ bool ok;
   const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(mine);
   // one thread per peer raises my done flag there (N round trips side by side, not one after the other) ...
   if (blockIdx.x == 0 && threadIdx.x < N)
-    st_release_sys(reinterpret_cast<uint32_t*>(peers.base[threadIdx.x] + 512) + rank, epoch);
+    st_release_sys(reinterpret_cast<uint32_t*>(peers.base(threadIdx.x) + 512) + rank, epoch);
   // ... and one thread per peer waits for that peer's flag here
   if (threadIdx.x == 0) ok = true;
   __syncthreads();
@@ -154,7 +173,7 @@ __global__ void __launch_bounds__(256) ep_reduce_kernel(const __nv_bfloat16* __r
     const size_t o = off_partial + (size_t(rank) * T + t) * H * 4 + size_t(c) * 16;
 #pragma unroll
     for (int p = 0; p < EP_MAX_RANKS; ++p)
-      if (p < N) v[p] = __ldcv(reinterpret_cast<const float4*>(peers.base[p] + o));
+      if (p < N) v[p] = __ldcv(reinterpret_cast<const float4*>(peers.base(p) + o));
 #pragma unroll
     for (int p = 0; p < EP_MAX_RANKS; ++p)
       if (p < N) { acc.x += v[p].x; acc.y += v[p].y; acc.z += v[p].z; acc.w += v[p].w; }
@@ -170,12 +189,14 @@ __global__ void __launch_bounds__(256) ep_reduce_kernel(const __nv_bfloat16* __r
 // count: a rank can be at most one exchange ahead of another (it cannot finish exchange e + 1 without the other's flag
 // of e + 1, raised after that rank is done reading exchange e).  Layout: the 1 KB header as above (epoch, counter, flags
 // at 256), then [2 parities][N ranks][bytes of the tensor, rounded up to 256].
-__global__ void __launch_bounds__(256) ar_oneshot_kernel(const float4* __restrict__ x, EpPeers peers, int N, int rank,
+__global__ void __launch_bounds__(256) ar_oneshot_kernel(const float4* __restrict__ x, EpPeers peers, int N,
                                                          int n_vec, long long slot_bytes, float4* __restrict__ out,
                                                          int* status) {
   pdl_wait();
   pdl_launch();
-  uint8_t* mine = peers.base[rank];
+  if (!peers.bound(N, status)) return;
+  const int rank = peers.rank();
+  uint8_t* mine = peers.base(rank);
   uint32_t* hdr = reinterpret_cast<uint32_t*>(mine);
   const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(hdr) + 1;  // (updated by the last CTA, after every CTA read it)
   const long long par = (long long)(epoch & 1u) * N * slot_bytes;
@@ -183,7 +204,7 @@ __global__ void __launch_bounds__(256) ar_oneshot_kernel(const float4* __restric
     const float4 v = x[i];
 #pragma unroll
     for (int q = 0; q < EP_MAX_RANKS; ++q)
-      if (q < N) reinterpret_cast<float4*>(peers.base[q] + EP_HDR_BYTES + par + rank * slot_bytes)[i] = v;
+      if (q < N) reinterpret_cast<float4*>(peers.base(q) + EP_HDR_BYTES + par + rank * slot_bytes)[i] = v;
   }
   __threadfence_system();
   __syncthreads();
@@ -192,7 +213,7 @@ __global__ void __launch_bounds__(256) ar_oneshot_kernel(const float4* __restric
   __syncthreads();
   if (last) {
     __threadfence_system();
-    if (threadIdx.x < N) st_release_sys(reinterpret_cast<uint32_t*>(peers.base[threadIdx.x] + 256) + rank, epoch);
+    if (threadIdx.x < N) st_release_sys(reinterpret_cast<uint32_t*>(peers.base(threadIdx.x) + 256) + rank, epoch);
     if (threadIdx.x == 0) { hdr[1] = 0; hdr[0] = epoch; }
   }
   if (threadIdx.x < N && !ep_wait_flags(reinterpret_cast<const uint32_t*>(mine + 256) + threadIdx.x, 1, epoch, status))
@@ -213,45 +234,22 @@ __global__ void __launch_bounds__(256) ar_oneshot_kernel(const float4* __restric
 }
 
 // ---------------------------------------------------------------------------------------------------------------
-static int ep_common(Call& c, const char* role, Tensor* ex, EpPeers* peers, int* N, int* rank) {
+static int ep_common(Call& c, const char* role, Tensor* ex, EpPeers* peers, int* N) {
   Tensor pt, rk;
   Q35_TRY(c.get("exchange", M(Q35_U8), ex));
   Q35_TRY(c.get("peers", M(Q35_U8), &pt));
   Q35_TRY(c.get("rank", M(Q35_I32), &rk));
-  // `peers` and `rank` are HOST-side values of the call (a table of addresses and an index), passed as tensors whose
-  // bytes are read here: they are bound once and never change, so reading them at enqueue time is exact
   Q35_REQUIRE(pt.bytes % 8 == 0 && pt.bytes >= 8 && pt.bytes <= 8 * EP_MAX_RANKS, Q35_ERR_SHAPE,
               "%s: peers = one 8-byte address per rank (at most %d ranks)", role, EP_MAX_RANKS);
   *N = int(pt.bytes / 8);
   Q35_REQUIRE(rk.numel() >= 1, Q35_ERR_SHAPE, "%s: rank [1]", role);
-  Q35_REQUIRE(ex->bytes >= EP_HDR_BYTES && (reinterpret_cast<uintptr_t>(ex->p) & 255) == 0, Q35_ERR_ALIGN,
-              "%s: exchange must be 256-byte aligned and hold the 1 KB header", role);
-  if (c.dry) return 0;
-  // read once per (peers, rank) binding and remembered: the first call with a binding must come outside a stream
-  // capture (it copies 8 N + 4 bytes to the host), every later call only looks the table up
-  struct Bound { const void* peers; const void* rank; uint64_t table[EP_MAX_RANKS]; int n, r; };
-  static std::mutex mu;
-  static std::vector<Bound> bound;
-  const Bound* hit = nullptr;
-  {
-    std::lock_guard<std::mutex> lock(mu);
-    for (const Bound& b : bound)
-      if (b.peers == pt.p && b.rank == rk.p && b.n == *N) hit = &b;
-    if (!hit) {
-      Bound b{};
-      b.peers = pt.p; b.rank = rk.p; b.n = *N;
-      Q35_REQUIRE(cudaMemcpy(b.table, pt.p, pt.bytes, cudaMemcpyDefault) == cudaSuccess &&
-                      cudaMemcpy(&b.r, rk.p, 4, cudaMemcpyDefault) == cudaSuccess, Q35_ERR_CUDA,
-                  "%s: reading the peer table failed (the first call with a binding must not be inside a stream capture)",
-                  role);
-      bound.push_back(b);
-      hit = &bound.back();
-    }
-    Q35_REQUIRE(hit->r >= 0 && hit->r < *N && hit->table[hit->r] == reinterpret_cast<uint64_t>(ex->p), Q35_ERR_SHAPE,
-                "%s: peers[rank] must be the address of `exchange`", role);
-    for (int i = 0; i < *N; ++i) peers->base[i] = reinterpret_cast<uint8_t*>(hit->table[i]);
-    *rank = hit->r;
-  }
+  Q35_REQUIRE(ex->bytes >= EP_HDR_BYTES && (reinterpret_cast<uintptr_t>(ex->p) & 255) == 0 &&
+                  (reinterpret_cast<uintptr_t>(pt.p) & 7) == 0, Q35_ERR_ALIGN,
+              "%s: exchange must be 256-byte aligned and hold the 1 KB header; peers 8-byte aligned", role);
+  // peers[rank] must be this rank's own buffer, `exchange`: the kernels check it and record 0x4000 otherwise
+  peers->tab = static_cast<const unsigned long long*>(pt.p);
+  peers->rank_ptr = rk.as<int>();
+  peers->self = ex->as<uint8_t>();
   return 0;
 }
 
@@ -266,7 +264,7 @@ static int region_offset(const char* role, const Tensor& ex, const Tensor& t, co
 int run_ep_publish(Call& c) {
   Tensor ex, h2, ids, rw, h2a, idsa, rwa;
   EpPeers peers{};
-  int N = 0, rank = 0;
+  int N = 0;
   Q35_TRY(c.get("h2", M(Q35_BF16), &h2));
   Q35_TRY(c.get("ids", M(Q35_I32), &ids));
   Q35_TRY(c.get("rw", M(Q35_F32), &rw));
@@ -275,7 +273,7 @@ int run_ep_publish(Call& c) {
   Q35_TRY(c.get("rw_all", M(Q35_F32), &rwa));
   Tensor nowait;  // bound (any i32 [1]): return after publishing; the host calls ep.wait later, with work in between
   Q35_TRY(c.get("no_wait", M(Q35_I32), &nowait, false));
-  Q35_TRY(ep_common(c, "ep.publish", &ex, &peers, &N, &rank));
+  Q35_TRY(ep_common(c, "ep.publish", &ex, &peers, &N));
   Q35_REQUIRE(h2a.bytes == h2.bytes * N && idsa.bytes == ids.bytes * N && rwa.bytes == rw.bytes * N, Q35_ERR_SHAPE,
               "ep.publish: the *_all regions hold one slice per rank");
   Q35_REQUIRE(h2.bytes % 16 == 0 && ids.bytes % 16 == 0 && rw.bytes % 16 == 0 && aligned16(h2.p) && aligned16(ids.p) &&
@@ -290,7 +288,7 @@ int run_ep_publish(Call& c) {
   const long long units = (long long)N * (n1 + n2 + n3);
   const unsigned grid = unsigned(std::min<long long>((units + 255) / 256, 2 * sm_count()));
   launch_pdl(ep_publish_kernel, dim3(grid), dim3(256), 0, c.stream, static_cast<const uint4*>(h2.p),
-             static_cast<const uint4*>(ids.p), static_cast<const uint4*>(rw.p), peers, N, rank, o1, o2, o3, n1, n2, n3,
+             static_cast<const uint4*>(ids.p), static_cast<const uint4*>(rw.p), peers, N, o1, o2, o3, n1, n2, n3,
              nowait.present ? 0 : 1, device_status_ptr());
   Q35_CUDA_LAUNCH_CHECK("ep.publish");
   return 0;
@@ -299,11 +297,11 @@ int run_ep_publish(Call& c) {
 int run_ep_wait(Call& c) {
   Tensor ex;
   EpPeers peers{};
-  int N = 0, rank = 0;
-  Q35_TRY(ep_common(c, "ep.wait", &ex, &peers, &N, &rank));
+  int N = 0;
+  Q35_TRY(ep_common(c, "ep.wait", &ex, &peers, &N));
   c.ws_need = 0;
   if (c.dry) return 0;
-  launch_pdl(ep_wait_gather_kernel, dim3(1), dim3(32), 0, c.stream, ex.as<uint8_t>(), N, device_status_ptr());
+  launch_pdl(ep_wait_gather_kernel, dim3(1), dim3(32), 0, c.stream, peers, N, device_status_ptr());
   Q35_CUDA_LAUNCH_CHECK("ep.wait");
   return 0;
 }
@@ -311,11 +309,11 @@ int run_ep_wait(Call& c) {
 int run_ep_reduce(Call& c) {
   Tensor ex, base, partial, out;
   EpPeers peers{};
-  int N = 0, rank = 0;
+  int N = 0;
   Q35_TRY(c.get("base", M(Q35_BF16), &base));
   Q35_TRY(c.get("partial", M(Q35_F32), &partial));
   Q35_TRY(c.get("out", M(Q35_BF16), &out));
-  Q35_TRY(ep_common(c, "ep.reduce", &ex, &peers, &N, &rank));
+  Q35_TRY(ep_common(c, "ep.reduce", &ex, &peers, &N));
   Q35_REQUIRE(base.nd == 2 && out.numel() == base.numel(), Q35_ERR_SHAPE, "ep.reduce: base, out [T, H]");
   const int64_t T = base.s[0], H = base.s[1];
   Q35_REQUIRE(partial.numel() == int64_t(N) * T * H && H % 4 == 0, Q35_ERR_SHAPE, "ep.reduce: partial [N * T, H], H % 4 == 0");
@@ -325,7 +323,7 @@ int run_ep_reduce(Call& c) {
   Q35_TRY(region_offset("ep.reduce", ex, partial, "partial", &off));
   Q35_REQUIRE(aligned16(base.p) && aligned16(out.p), Q35_ERR_ALIGN, "ep.reduce: base, out 16-byte aligned");
   const unsigned grid = unsigned(std::min<int64_t>((T * (H / 4) + 255) / 256, 2 * sm_count()));
-  launch_pdl(ep_reduce_kernel, dim3(grid), dim3(256), 0, c.stream, base.as<__nv_bfloat16>(), peers, N, rank, off,
+  launch_pdl(ep_reduce_kernel, dim3(grid), dim3(256), 0, c.stream, base.as<__nv_bfloat16>(), peers, N, off,
              int(T), int(H), out.as<__nv_bfloat16>(), device_status_ptr());
   Q35_CUDA_LAUNCH_CHECK("ep.reduce");
   return 0;
@@ -334,10 +332,10 @@ int run_ep_reduce(Call& c) {
 int run_ar_oneshot(Call& c) {
   Tensor ex, x, out;
   EpPeers peers{};
-  int N = 0, rank = 0;
+  int N = 0;
   Q35_TRY(c.get("x", M(Q35_F32), &x));
   Q35_TRY(c.get("out", M(Q35_F32), &out));
-  Q35_TRY(ep_common(c, "ar.oneshot", &ex, &peers, &N, &rank));
+  Q35_TRY(ep_common(c, "ar.oneshot", &ex, &peers, &N));
   Q35_REQUIRE(out.numel() == x.numel() && x.numel() % 4 == 0, Q35_ERR_SHAPE, "ar.oneshot: out like x, a multiple of 4 elements");
   const long long slot = (long long)(x.bytes + 255) / 256 * 256;
   Q35_REQUIRE((long long)ex.bytes >= EP_HDR_BYTES + 2 * N * slot, Q35_ERR_WORKSPACE,
@@ -348,7 +346,7 @@ int run_ar_oneshot(Call& c) {
   const int n_vec = int(x.numel() / 4);
   // every CTA waits for the peers' flags: the grid must be resident at once
   const unsigned grid = unsigned(std::min<long long>((n_vec + 255) / 256, sm_count()));
-  launch_pdl(ar_oneshot_kernel, dim3(grid), dim3(256), 0, c.stream, static_cast<const float4*>(x.p), peers, N, rank, n_vec,
+  launch_pdl(ar_oneshot_kernel, dim3(grid), dim3(256), 0, c.stream, static_cast<const float4*>(x.p), peers, N, n_vec,
              slot, static_cast<float4*>(out.p), device_status_ptr());
   Q35_CUDA_LAUNCH_CHECK("ar.oneshot");
   return 0;

@@ -94,6 +94,7 @@ const char* q35_last_error(void);
  *   0x400 a work item waiting for the rows another item produces
  *   0x800 ep.wait: another rank's rows did not arrive   0x1000 ep.reduce: another rank's partial sums did not
  *   0x2000 ar.oneshot: another rank's addend did not arrive
+ *   0x4000 ep.* / ar.oneshot: entry `rank` of `peers` is not `exchange` (the call did nothing)
  * The role "debug.wait_probe" makes one such wait run out on purpose (a barrier nobody arrives at, a poll limit the
  * caller gives) so that a host can check this reporting path; it touches nothing else. */
 int q35_device_status(void* stream);
