@@ -178,4 +178,51 @@ __device__ __forceinline__ int e8m0_for(float amax) {
   return max(-127, min(127, e));
 }
 
+// 2^e as a float for the exponents a UE8M0 scale can name (-127 is the subnormal 2^-127): no special-function unit
+__device__ __forceinline__ float pow2_int(int e) {
+  return __uint_as_float(e > -127 ? uint32_t(e + 127) << 23 : 0x00400000u);
+}
+
+// Eight consecutive values of a block of 32 that four neighbouring lanes hold -> two E4M3 terms with UE8M0 block
+// exponents: v = hi * 2^eh + lo * 2^el up to 2^-9 of the block's maximum.  Every lane of the warp calls (shuffles).
+// Conversions go two at a time (cvt.rn.satfinite.e4m3x2.f32 and cvt.rn.f16x2.e4m3x2): the conversion unit is the
+// narrow one, and a prefill-sized quantisation is bound by it.
+struct TwoTerm8 {
+  uint2 hi, lo;  // eight E4M3 bytes each, element u in byte u
+  int eh, el;
+};
+__device__ __forceinline__ TwoTerm8 quant_two_terms8(const float (&v)[8]) {
+  TwoTerm8 t;
+  float amax = 0.f;
+#pragma unroll
+  for (int u = 0; u < 8; ++u) amax = fmaxf(amax, fabsf(v[u]));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+  t.eh = e8m0_for(amax);
+  const float dn = pow2_int(-t.eh), up = pow2_int(t.eh);
+  uint32_t hw[4], lw[4];
+  float rem[8];
+  float rmax = 0.f;
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    const __nv_fp8x2_storage_t h2 =
+        __nv_cvt_float2_to_fp8x2(make_float2(v[2 * u] * dn, v[2 * u + 1] * dn), __NV_SATFINITE, __NV_E4M3);
+    const float2 back = __half22float2(__half2(__nv_cvt_fp8x2_to_halfraw2(h2, __NV_E4M3)));
+    hw[u] = h2;
+    rem[2 * u] = v[2 * u] - back.x * up;
+    rem[2 * u + 1] = v[2 * u + 1] - back.y * up;
+    rmax = fmaxf(rmax, fmaxf(fabsf(rem[2 * u]), fabsf(rem[2 * u + 1])));
+  }
+  rmax = fmaxf(rmax, __shfl_xor_sync(0xffffffffu, rmax, 1));
+  rmax = fmaxf(rmax, __shfl_xor_sync(0xffffffffu, rmax, 2));
+  t.el = e8m0_for(rmax);
+  const float dl = pow2_int(-t.el);
+#pragma unroll
+  for (int u = 0; u < 4; ++u)
+    lw[u] = __nv_cvt_float2_to_fp8x2(make_float2(rem[2 * u] * dl, rem[2 * u + 1] * dl), __NV_SATFINITE, __NV_E4M3);
+  t.hi = make_uint2(hw[0] | hw[1] << 16, hw[2] | hw[3] << 16);
+  t.lo = make_uint2(lw[0] | lw[1] << 16, lw[2] | lw[3] << 16);
+  return t;
+}
+
 }  // namespace q35

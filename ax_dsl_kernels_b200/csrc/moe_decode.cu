@@ -307,10 +307,10 @@ moe_decode_kernel(const __grid_constant__ CUtensorMap m_wg, const __grid_constan
               const float act = round_bf16(g / (1.0f + expf(-g)) * u);
               // two E4M3 terms with UE8M0 scales over the warp's 32 consecutive inputs (same split as launch 2)
               const int eh = e8m0_for(warp_max(fabsf(act)));
-              const __nv_fp8_e4m3 hq(act * exp2f(float(-eh)));
-              const float rem = act - float(hq) * exp2f(float(eh));
+              const __nv_fp8_e4m3 hq(act * pow2_int(-eh));
+              const float rem = act - float(hq) * pow2_int(eh);
               const int el = e8m0_for(warp_max(fabsf(rem)));
-              const __nv_fp8_e4m3 lq(rem * exp2f(float(-el)));
+              const __nv_fp8_e4m3 lq(rem * pow2_int(-el));
               const long long row = im.y + t0 + t;
               a.q2h[row * a.FE + col_fe] = *reinterpret_cast<const uint8_t*>(&hq);
               a.q2l[row * a.FE + col_fe] = *reinterpret_cast<const uint8_t*>(&lq);
@@ -632,48 +632,18 @@ __global__ void __launch_bounds__(256) moe_decode_quant_kernel(const __nv_bfloat
   if (on) raw = *reinterpret_cast<const uint4*>(x + size_t(pair % T) * H + c8 * 8);
   const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
   float v[8];
-  float amax = 0.f;
 #pragma unroll
-  for (int u = 0; u < 4; ++u) {
-    v[2 * u] = bf16lo(w[u]); v[2 * u + 1] = bf16hi(w[u]);
-    amax = fmaxf(amax, fmaxf(fabsf(v[2 * u]), fabsf(v[2 * u + 1])));
-  }
-  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-  const int eh = e8m0_for(amax);
-  const float dn = exp2f(float(-eh)), up = exp2f(float(eh));
-  uint8_t hb[8], lb[8];
-  float rem[8];
-  float rmax = 0.f;
-#pragma unroll
-  for (int u = 0; u < 8; ++u) {
-    const __nv_fp8_e4m3 hq(v[u] * dn);
-    hb[u] = *reinterpret_cast<const uint8_t*>(&hq);
-    rem[u] = v[u] - float(hq) * up;
-    rmax = fmaxf(rmax, fabsf(rem[u]));
-  }
-  rmax = fmaxf(rmax, __shfl_xor_sync(0xffffffffu, rmax, 1));
-  rmax = fmaxf(rmax, __shfl_xor_sync(0xffffffffu, rmax, 2));
-  const int el = e8m0_for(rmax);
-  const float dl = exp2f(float(-el));
-#pragma unroll
-  for (int u = 0; u < 8; ++u) {
-    const __nv_fp8_e4m3 lq(rem[u] * dl);
-    lb[u] = *reinterpret_cast<const uint8_t*>(&lq);
-  }
+  for (int u = 0; u < 4; ++u) { v[2 * u] = bf16lo(w[u]); v[2 * u + 1] = bf16hi(w[u]); }
+  const TwoTerm8 t = quant_two_terms8(v);
   if (!on) return;
-  auto pack = [](const uint8_t* b) {
-    return make_uint2(uint32_t(b[0]) | uint32_t(b[1]) << 8 | uint32_t(b[2]) << 16 | uint32_t(b[3]) << 24,
-                      uint32_t(b[4]) | uint32_t(b[5]) << 8 | uint32_t(b[6]) << 16 | uint32_t(b[7]) << 24);
-  };
   const long long o = (long long)row * H + c8 * 8;
-  *reinterpret_cast<uint2*>(qh + o) = pack(hb);
-  *reinterpret_cast<uint2*>(ql + o) = pack(lb);
+  *reinterpret_cast<uint2*>(qh + o) = t.hi;
+  *reinterpret_cast<uint2*>(ql + o) = t.lo;
   if ((c8 & 3) == 0) {
     uint8_t* blk = sfb + (size_t(row >> 4) * (H / 128) + (c8 >> 4)) * MD_SF_BYTES;
     const int n = row & 15, kb = (c8 >> 2) & 3;
-    blk[n * 16 + kb] = uint8_t(eh + 127);
-    blk[(MD_NB + n) * 16 + kb] = uint8_t(el + 127);
+    blk[n * 16 + kb] = uint8_t(t.eh + 127);
+    blk[(MD_NB + n) * 16 + kb] = uint8_t(t.el + 127);
   }
 }
 

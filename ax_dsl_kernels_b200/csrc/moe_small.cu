@@ -97,6 +97,8 @@ int run_moe_route(Call& c) {
 // the ids in token order and compacts the pairs that chose it, so the result does not depend on scheduling.
 // counts[e] = number of pairs, list[e * T + j] = pair index t * K + k of the j-th token (ascending t) of expert e.
 // base (optional): first global expert id of this rank's planes; ids outside [base, base + NE) belong to other ranks.
+// A thread takes four consecutive tokens of every 1024 (their ids as 16-byte loads when K allows, all in flight), so
+// a prefill-sized call pays one block-wide hand-over per 1024 tokens.
 __global__ void __launch_bounds__(256) moe_group_count_kernel(const int* __restrict__ ids, const int* __restrict__ base,
                                                               int T, int K, int NE, int* __restrict__ counts,
                                                               int* __restrict__ list, int* status) {
@@ -107,22 +109,47 @@ __global__ void __launch_bounds__(256) moe_group_count_kernel(const int* __restr
   __shared__ int s_base;
   if (tid == 0) s_base = 0;
   __syncthreads();
-  for (int t0 = 0; t0 < T; t0 += 256) {
-    const int t = t0 + tid;
-    int hit = -1;
-    if (t < T) {
-      for (int k = 0; k < K; ++k) {
-        const int id = ids[size_t(t) * K + k] - first;
-        if (id == e && hit < 0) hit = k;
-        if (e == 0 && !base && id >= NE) atomicOr(status, DS_BAD_EXPERT);  // negative ids mean "not on this rank"
+  const bool vec = (K & 3) == 0 && (reinterpret_cast<uintptr_t>(ids) & 15) == 0;
+  bool bad = false;
+  for (int t0 = 0; t0 < T; t0 += 1024) {
+    int hit[4] = {-1, -1, -1, -1};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int t = t0 + tid * 4 + j;
+      if (t >= T) continue;
+      const int* row = ids + size_t(t) * K;
+      if (vec) {
+        for (int k = 0; k < K; k += 4) {
+          const int4 v = *reinterpret_cast<const int4*>(row + k);
+          const int id4[4] = {v.x - first, v.y - first, v.z - first, v.w - first};
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            if (id4[u] == e && hit[j] < 0) hit[j] = k + u;
+            bad |= id4[u] >= NE;
+          }
+        }
+      } else {
+        for (int k = 0; k < K; ++k) {
+          const int id = row[k] - first;
+          if (id == e && hit[j] < 0) hit[j] = k;
+          bad |= id >= NE;
+        }
       }
     }
-    const unsigned m = __ballot_sync(0xffffffffu, hit >= 0);
-    if (lane == 0) s_warp[wid] = __popc(m);
+    const int cnt = (hit[0] >= 0) + (hit[1] >= 0) + (hit[2] >= 0) + (hit[3] >= 0);
+    int inc = cnt;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int n = __shfl_up_sync(0xffffffffu, inc, o);
+      if (lane >= o) inc += n;
+    }
+    if (lane == 31) s_warp[wid] = inc;
     __syncthreads();
-    int before = s_base;
-    for (int w = 0; w < wid; ++w) before += s_warp[w];
-    if (hit >= 0) list[size_t(e) * T + before + __popc(m & ((1u << lane) - 1))] = t * K + hit;
+    int at = s_base + inc - cnt;
+    for (int w = 0; w < wid; ++w) at += s_warp[w];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      if (hit[j] >= 0) list[size_t(e) * T + at++] = (t0 + tid * 4 + j) * K + hit[j];
     __syncthreads();
     if (tid == 0) {
       int tot = 0;
@@ -131,6 +158,7 @@ __global__ void __launch_bounds__(256) moe_group_count_kernel(const int* __restr
     }
     __syncthreads();
   }
+  if (e == 0 && !base && bad) atomicOr(status, DS_BAD_EXPERT);  // with a base, foreign ids mean "not on this rank"
   if (tid == 0) counts[e] = s_base;
 }
 

@@ -87,66 +87,55 @@ static int encode_map(CUtensorMap* m, bool fp4, const void* base, uint64_t rows,
 // ---------------------------------------------------------------------------------------------------------------
 // x (bf16) -> two E4M3 terms with UE8M0 block-32 scales: x = hi * 2^eh + lo * 2^el;
 // rows gathered through `src` (destination row -> source row; nullptr = identity).
-// Eight elements per thread (one 16-byte load), four threads per 32-block.
+// Eight elements per piece (one 16-byte load), four threads per 32-block.  A thread takes PP pieces, 256 apart, and
+// has the row ids and then the 16-byte loads of all of them in flight before it converts the first: with one piece per
+// thread a prefill-sized call (millions of pieces, two dependent loads each) ran at the loads' latency, not at the
+// bandwidth of its stores.
+template <int PP>
 __global__ void __launch_bounds__(256) tc_quant_kernel(const __nv_bfloat16* __restrict__ x, int x_stride,
                                                        const int* __restrict__ src, int x_rows, int R, int K,
                                                        uint8_t* __restrict__ qh, uint8_t* __restrict__ ql,
                                                        uint8_t* __restrict__ sh, uint8_t* __restrict__ sl) {
   pdl_wait();
   pdl_launch();
-  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;  // index of the 8-element piece
   const int per_row = K / 8;
-  const bool on = i < (long long)R * per_row;  // whole quads are on or off together (K is a multiple of 32)
-  const int row = on ? int(i / per_row) : 0, c8 = on ? int(i % per_row) : 0;
-  long long srow = row;
-  if (src) {  // rows past the filled part of a grouped list hold stale ids: read row 0 instead, nobody uses the result
-    srow = src[row];
-    if (srow < 0 || srow >= x_rows) srow = 0;
-  }
-  uint4 raw = make_uint4(0u, 0u, 0u, 0u);
-  if (on) raw = *reinterpret_cast<const uint4*>(x + srow * x_stride + c8 * 8);
-  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-  float v[8];
-  float amax = 0.f;
+  const long long n_pieces = (long long)R * per_row;
+  const long long i0 = (long long)blockIdx.x * (256 * PP) + threadIdx.x;  // index of the first 8-element piece
+  bool on[PP];
+  int row[PP], c8[PP];
+  long long srow[PP];
 #pragma unroll
-  for (int u = 0; u < 4; ++u) {
-    v[2 * u] = bf16lo(w[u]); v[2 * u + 1] = bf16hi(w[u]);
-    amax = fmaxf(amax, fmaxf(fabsf(v[2 * u]), fabsf(v[2 * u + 1])));
+  for (int j = 0; j < PP; ++j) {
+    const long long i = i0 + j * 256;
+    on[j] = i < n_pieces;  // whole quads are on or off together (K is a multiple of 32)
+    row[j] = on[j] ? int(i / per_row) : 0;
+    c8[j] = on[j] ? int(i % per_row) : 0;
+    srow[j] = row[j];
+    if (src) srow[j] = src[row[j]];
   }
-  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-  const int eh = e8m0_for(amax);
-  const float dn = exp2f(float(-eh)), up = exp2f(float(eh));
-  uint8_t hb[8], lb[8];
-  float rem[8];
-  float rmax = 0.f;
+  uint4 raw[PP];
 #pragma unroll
-  for (int u = 0; u < 8; ++u) {
-    const __nv_fp8_e4m3 h(v[u] * dn);
-    hb[u] = *reinterpret_cast<const uint8_t*>(&h);
-    rem[u] = v[u] - float(h) * up;
-    rmax = fmaxf(rmax, fabsf(rem[u]));
+  for (int j = 0; j < PP; ++j) {
+    // rows past the filled part of a grouped list hold stale ids: read row 0 instead, nobody uses the result
+    if (srow[j] < 0 || srow[j] >= x_rows) srow[j] = 0;
+    raw[j] = make_uint4(0u, 0u, 0u, 0u);
+    if (on[j]) raw[j] = *reinterpret_cast<const uint4*>(x + srow[j] * x_stride + c8[j] * 8);
   }
-  rmax = fmaxf(rmax, __shfl_xor_sync(0xffffffffu, rmax, 1));
-  rmax = fmaxf(rmax, __shfl_xor_sync(0xffffffffu, rmax, 2));
-  const int el = e8m0_for(rmax);
-  const float dl = exp2f(float(-el));
 #pragma unroll
-  for (int u = 0; u < 8; ++u) {
-    const __nv_fp8_e4m3 l(rem[u] * dl);
-    lb[u] = *reinterpret_cast<const uint8_t*>(&l);
-  }
-  if (!on) return;
-  auto pack = [](const uint8_t* b) {
-    return make_uint2(uint32_t(b[0]) | uint32_t(b[1]) << 8 | uint32_t(b[2]) << 16 | uint32_t(b[3]) << 24,
-                      uint32_t(b[4]) | uint32_t(b[5]) << 8 | uint32_t(b[6]) << 16 | uint32_t(b[7]) << 24);
-  };
-  const long long o = (long long)row * K + c8 * 8;
-  *reinterpret_cast<uint2*>(qh + o) = pack(hb);
-  *reinterpret_cast<uint2*>(ql + o) = pack(lb);
-  if ((c8 & 3) == 0) {
-    sh[(long long)row * (K / 32) + c8 / 4] = uint8_t(eh + 127);
-    sl[(long long)row * (K / 32) + c8 / 4] = uint8_t(el + 127);
+  for (int j = 0; j < PP; ++j) {
+    const uint32_t w[4] = {raw[j].x, raw[j].y, raw[j].z, raw[j].w};
+    float v[8];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) { v[2 * u] = bf16lo(w[u]); v[2 * u + 1] = bf16hi(w[u]); }
+    const TwoTerm8 t = quant_two_terms8(v);
+    if (!on[j]) continue;
+    const long long o = (long long)row[j] * K + c8[j] * 8;
+    *reinterpret_cast<uint2*>(qh + o) = t.hi;
+    *reinterpret_cast<uint2*>(ql + o) = t.lo;
+    if ((c8[j] & 3) == 0) {
+      sh[(long long)row[j] * (K / 32) + c8[j] / 4] = uint8_t(t.eh + 127);
+      sl[(long long)row[j] * (K / 32) + c8[j] / 4] = uint8_t(t.el + 127);
+    }
   }
 }
 
@@ -156,8 +145,13 @@ int tc_quantize(const __nv_bfloat16* x, int x_stride, const int* src, int x_rows
   if (pieces == 0) return 0;
   Q35_REQUIRE(K % 32 == 0 && x_stride % 8 == 0 && (uintptr_t(x) & 15) == 0, Q35_ERR_ALIGN,
               "tc quantize: rows must start on 16-byte boundaries");
-  launch_pdl(tc_quant_kernel, dim3(unsigned((pieces + 255) / 256)), dim3(256), 0, stream, x, x_stride, src, x_rows, R, K,
-             q.qh, q.ql, q.sh, q.sl);
+  // several pieces per thread once there are enough pieces to fill every SM several times over
+  if (pieces >= 4ll * 256 * 8 * sm_count())
+    launch_pdl(tc_quant_kernel<4>, dim3(unsigned((pieces + 1023) / 1024)), dim3(256), 0, stream, x, x_stride, src, x_rows,
+               R, K, q.qh, q.ql, q.sh, q.sl);
+  else
+    launch_pdl(tc_quant_kernel<1>, dim3(unsigned((pieces + 255) / 256)), dim3(256), 0, stream, x, x_stride, src, x_rows, R,
+               K, q.qh, q.ql, q.sh, q.sl);
   Q35_CUDA_LAUNCH_CHECK("tc quantize");
   return 0;
 }
