@@ -625,6 +625,20 @@ def run_profile_case(name, reps):
         out = torch.empty_like(x1)
         fn = lambda: q35.moe_block(x1, wl.w, TOPK, out)  # noqa: E731
         units = T
+    elif name == "moe_ep8":  # what one of 8 expert-parallel ranks runs per decode step: 512 gathered tokens, 32 local experts
+        from ax_dsl_kernels_b200 import _lib, moe as qmoe
+        wl = Workload(dev, seed=1, attn=False)
+        T, lo, hi = 8 * B, 0, NE // 8
+        h2 = (rn(T, H) * 0.5).to(bf)
+        ids, rw = q35.route(rn(T, NE), TOPK)
+        w = {k: wl.w[k][lo:hi].contiguous() for k in ("e_gw", "e_gs", "e_dw", "e_ds")}
+        gs_t, ds_t = qmoe.tile_scales(w["e_gs"], True), qmoe.tile_scales(w["e_ds"], False)
+        base = torch.tensor([lo], dtype=torch.int32, device=dev)
+        partial = torch.empty((T, H), dtype=torch.float32, device=dev)
+        fn = lambda: _lib.run("moe.experts", h2=h2, ids=ids, rw=rw, e_gw=qmoe._u8(w["e_gw"]), e_gs=qmoe._u8(w["e_gs"]),  # noqa: E731
+                              e_dw=qmoe._u8(w["e_dw"]), e_ds=qmoe._u8(w["e_ds"]), expert_base=base, partial_out=partial,
+                              e_gs_tiled=gs_t, e_ds_tiled=ds_t)
+        units = T
     elif name == "lm_head":  # MXFP4 output projection 248320 x 2048 (254 MB codes + 16 MB scales) on one token row
         from ax_dsl_kernels_b200.moe import lm_head
         N = 248320
@@ -681,7 +695,7 @@ def main():
     ap.add_argument("--attn-read-ratio", type=float, default=268.70 / 268.44,
                     help="DRAM bytes read per K/V byte by the attention kernel, from an ncu capture (default: the capture "
                          "of the 16 x 8192 case, 268.70 MB read for 268.44 MB of K/V)")
-    ap.add_argument("--profile-case", choices=["attn", "attn_fp8", "gdn", "moe", "gdn_prefill", "attn_prefill", "moe_prefill", "lm_head"], help="run one kernel on a capture-sized case")
+    ap.add_argument("--profile-case", choices=["attn", "attn_fp8", "gdn", "moe", "moe_ep8", "gdn_prefill", "attn_prefill", "moe_prefill", "lm_head"], help="run one kernel on a capture-sized case")
     args = ap.parse_args()
     if args.profile_case:
         run_profile_case(args.profile_case, max(1, min(args.steps, 5)))
