@@ -218,7 +218,7 @@ static int launch_nb(const CUtensorMap& w0, const CUtensorMap& w1, const CUtenso
   const long long items = (long long)tiles * (a.g_n ? groups : (a.n_dense + a.dense_rows - 1) / a.dense_rows * a.k_slices);
   const long long slots = (long long)sm_count() * TcCfg<NB>::CTAS_PER_SM;
   const unsigned grid = unsigned(items < slots ? items : slots);
-  launch_pdl(tc_gemm_kernel<NB, EPI>, dim3(grid), dim3(TcCfg<NB>::THREADS), size_t(smem), stream, w0, w1, xh, xl, a);
+  launch_pdl(tc_gemm_kernel<NB, EPI>, dim3(grid), dim3(tc_threads<NB, EPI>()), size_t(smem), stream, w0, w1, xh, xl, a);
   Q35_CUDA_LAUNCH_CHECK("tc gemm");
   return 0;
 }

@@ -7,12 +7,13 @@
 // Why two terms: the reference multiplies bf16 activations by the dequantised weights (golden
 // models/qwen35_2b/whole/src/q35_moe.py:235-238); a single E4M3 term misses the 2e-2 tolerance by a factor 6.
 //
-// Work item = (group, 128-row weight tile, NB-token tile).  Persistent kernel (320 threads, two CTAs per SM for small
+// Work item = (group, 128-row weight tile, NB-token tile).  Persistent kernel (320 or 448 threads, two CTAs per SM for small
 // token tiles), items dealt round-robin over the compacted list of non-empty groups.  Warp-specialised and decoupled:
 //   warp 0    TMA producer: weight and activation tiles into a ring of stages (K = 128 per stage), running ahead
 //             across item boundaries;
 //   warp 1    owns tensor memory, copies the stage's scale blocks into TMEM (tcgen05.cp) and issues 4 MMAs of K = 32;
-//   warps 2-5 epilogue: tcgen05.ld of a finished accumulator while the next item accumulates into the other buffer;
+//   warps 2-5 epilogue: tcgen05.ld of a finished accumulator while the next item accumulates into the other buffer
+//             (prefill-sized MoE tiles: a second epilogue group, warps 10-13, one group per accumulator buffer);
 //   warps 6-9 gather the E8M0 scales from global memory into 32 x 16-byte blocks (the layout tcgen05.cp wants), four
 //             stages (K = 512, 16 scale bytes of a row) at a time, in a two-deep ring of their own, with the loads of
 //             four granules in flight in registers.  Measured alternatives, all slower: the same per stage (a proxy
@@ -81,15 +82,24 @@ struct TcCfg {
   static constexpr int STAGE_TX = 128 * 64 + B_BYTES;
   static constexpr int CTAS_PER_SM = NB <= 32 ? 2 : 1;
   static constexpr int STAGES = NB <= 16 ? 5 : NB <= 32 ? 4 : 6;
-  static constexpr int THREADS = 320;
   static constexpr int TMEM_COLS = (2 * N + 8) <= 128 ? 128 : (2 * N + 8) <= 256 ? 256 : 512;
   static constexpr int SFA_COL = 2 * N, SFB_COL = 2 * N + 4;
-  static constexpr int XCH_BYTES = 16 * 64 * 2;            // gate/up exchange of one 16-column chunk (bf16)
+  static constexpr int EPI_GROUPS = NB == 64 ? 2 : 1;      // epilogue warpgroups the shared memory is laid out for
+  static constexpr int XCH_BYTES = 16 * 64 * 2 * EPI_GROUPS;  // per group: gate/up exchange of one 16-column chunk (bf16)
   static constexpr int smem_bytes(int) {                   // + 1024 for manual alignment
     return 1024 + STAGES * STAGE_BYTES + SF_RING * SF_BYTES + XCH_BYTES + 256;
   }
 };
 
+
+// Threads of a CTA.  Prefill-sized token tiles (NB = 64) of the MoE epilogues run TWO epilogue warpgroups, one per
+// accumulator buffer (warps 2-5 take the even token tiles, warps 10-13 the odd ones): with the whole pipeline
+// switched off part by part, the epilogue alone accounted for 0.47 ms of a 1.55 ms prefill block -- a tile's
+// tcgen05.ld round trips, exchange through shared memory and stores are a chain of latencies that one warp per
+// scheduler cannot hide, and a second accumulator in flight only helps if somebody is free to drain it.  (The plain
+// epilogue of the `linear` role keeps one group: its 168 registers do not fit 448 threads.)
+template <int NB, int EPI>
+__host__ __device__ constexpr int tc_threads() { return (NB == 64 && EPI != TC_EPI_PLAIN) ? 448 : 320; }
 
 struct TcItem {
   int plane, row0, n, tile, slice;
@@ -145,7 +155,7 @@ struct TcItemWalk {
 };
 
 template <int NB, int EPI>
-__global__ void __launch_bounds__(TcCfg<NB>::THREADS, TcCfg<NB>::CTAS_PER_SM) tc_gemm_kernel(const __grid_constant__ CUtensorMap wmap0,
+__global__ void __launch_bounds__(tc_threads<NB, EPI>(), TcCfg<NB>::CTAS_PER_SM) tc_gemm_kernel(const __grid_constant__ CUtensorMap wmap0,
                                                          const __grid_constant__ CUtensorMap wmap1,
                                                          const __grid_constant__ CUtensorMap xmap_hi,
                                                          const __grid_constant__ CUtensorMap xmap_lo, const TcArgs a) {
@@ -263,7 +273,7 @@ __global__ void __launch_bounds__(TcCfg<NB>::THREADS, TcCfg<NB>::CTAS_PER_SM) tc
       }
     }
     __syncwarp();
-  } else if (warp >= 6) {
+  } else if (warp >= 6 && warp < 10) {
     // ---------------------------------------------------------------- scale gather (128 threads: one tile row each)
     // A unit = one granule (four stages, K = 512) of one (item, token tile): 16 scale bytes of weight row gt and of
     // activation column gt.  Four units are kept in flight in registers, so the loads' latency is off the chain.
@@ -352,7 +362,13 @@ __global__ void __launch_bounds__(TcCfg<NB>::THREADS, TcCfg<NB>::CTAS_PER_SM) tc
       }
     }
   } else {
-    // ---------------------------------------------------------------- epilogue: warps 2..5 own lane quadrant warp % 4
+    // ---------------------------------------------------------------- epilogue: warps 2..5 (and 10..13) own lane
+    // quadrant warp % 4; with two groups, group eg drains accumulator buffer eg (token tiles of that parity)
+    constexpr bool TWO = tc_threads<NB, EPI>() == 448;
+    const int eg = TWO && warp >= 10 ? 1 : 0;
+    const int ebase = eg ? 320 : 64;                 // first thread of this group
+    const uint32_t bar_x = eg ? 4u : 1u, bar_acc = eg ? 5u : 3u;  // named barriers of this group
+    __nv_bfloat16* const xch = g_xch + eg * (16 * 64);
     const int qd = warp & 3;
     const int r = qd * 32 + lane;  // row of the 128-row tile
     const int h = r >> 6;
@@ -366,6 +382,7 @@ __global__ void __launch_bounds__(TcCfg<NB>::THREADS, TcCfg<NB>::CTAS_PER_SM) tc
       const int row = im.tile * a.tile_rows + a.roff[h] + (r & 63);
       const bool rvalid = row < a.lim[h];
       for (int t0 = 0; t0 < im.n; t0 += NB, ++q) {
+        if (TWO && int(q & 1) != eg) continue;
         const uint32_t b = q & 1, bph = (q >> 1) & 1;
         if (!dead && !mbar_wait(acc_full(b), bph)) {
           if (lane == 0) atomicOr(a.status, DS_WAIT_TIMEOUT | 0x100);
@@ -382,8 +399,8 @@ __global__ void __launch_bounds__(TcCfg<NB>::THREADS, TcCfg<NB>::CTAS_PER_SM) tc
             // the last columns are in registers: hand the accumulator back before the global loads and stores below,
             // so that the MMA warp is never held up by their latency
             tc_fence_before();
-            asm volatile("bar.sync 3, 128;" ::: "memory");
-            if (tid == 64) mbar_arrive(acc_empty(b));
+            asm volatile("bar.sync %0, 128;" ::"r"(bar_acc) : "memory");
+            if (tid == ebase) mbar_arrive(acc_empty(b));
           }
 #pragma unroll
           for (int jj = 0; jj < 16; ++jj) hi[jj] += lo[jj];
@@ -406,20 +423,20 @@ __global__ void __launch_bounds__(TcCfg<NB>::THREADS, TcCfg<NB>::CTAS_PER_SM) tc
 #pragma unroll
             for (int jj = 0; jj < 8; ++jj) {
               const int col = h ? jj : jj + 8;
-              g_xch[col * 64 + p] = __float2bfloat16_rn(h ? hi[jj] : hi[jj + 8]);  // static indices: hi stays in registers
+              xch[col * 64 + p] = __float2bfloat16_rn(h ? hi[jj] : hi[jj + 8]);  // static indices: hi stays in registers
             }
-            asm volatile("bar.sync 1, 128;" ::: "memory");
+            asm volatile("bar.sync %0, 128;" ::"r"(bar_x) : "memory");
 #pragma unroll
             for (int jj = 0; jj < 8; ++jj) {
               const int col = h ? jj + 8 : jj;
               const int t = t0 + c0 + col;
               if (t < im.n && ovalid) {
-                const float mine = round_bf16(h ? hi[jj + 8] : hi[jj]), other = __bfloat162float(g_xch[col * 64 + p]);
+                const float mine = round_bf16(h ? hi[jj + 8] : hi[jj]), other = __bfloat162float(xch[col * 64 + p]);
                 const float g = h ? other : mine, u = h ? mine : other;
                 a.act_out[(long long)(im.row0 + t) * a.act_rows + orow] = __float2bfloat16_rn(g / (1.0f + expf(-g)) * u);
               }
             }
-            asm volatile("bar.sync 1, 128;" ::: "memory");
+            asm volatile("bar.sync %0, 128;" ::"r"(bar_x) : "memory");
           } else {
             // every global load of the chunk goes out before the first store: the output may alias the residual, so
             // the compiler cannot move a load above a store, and one round trip per column would be paid otherwise
@@ -471,15 +488,15 @@ __global__ void __launch_bounds__(TcCfg<NB>::THREADS, TcCfg<NB>::CTAS_PER_SM) tc
 #pragma unroll
               for (int half = 0; half < 2; ++half) {
 #pragma unroll
-                for (int jj = 0; jj < 8; ++jj) g_xch[jj * 128 + r] = __float2bfloat16_rn(o[half * 8 + jj]);
-                asm volatile("bar.sync 1, 128;" ::: "memory");
-                const int e = tid - 64, tt = e >> 4, part = e & 15;
+                for (int jj = 0; jj < 8; ++jj) xch[jj * 128 + r] = __float2bfloat16_rn(o[half * 8 + jj]);
+                asm volatile("bar.sync %0, 128;" ::"r"(bar_x) : "memory");
+                const int e = tid - ebase, tt = e >> 4, part = e & 15;
                 const int t = t0 + c0 + half * 8 + tt;
                 const int rowg = im.tile * 128 + a.roff[0] + part * 8;
                 if (t < im.n && rowg < a.lim[0])
                   *reinterpret_cast<uint4*>(a.b_out + (long long)(im.row0 + t) * a.out_stride + rowg) =
-                      *reinterpret_cast<const uint4*>(g_xch + tt * 128 + part * 8);
-                asm volatile("bar.sync 1, 128;" ::: "memory");
+                      *reinterpret_cast<const uint4*>(xch + tt * 128 + part * 8);
+                asm volatile("bar.sync %0, 128;" ::"r"(bar_x) : "memory");
               }
             } else {
 #pragma unroll
