@@ -349,6 +349,24 @@ class ExpertParallelMoE:
         return out
 
 
+    def forward_prefill(self, x1, out=None, form="auto", marks=None, gather_limit_bytes=4 << 30):
+        """A prefill-sized call through one of the two exchanges.  form "all_gather": forward() -- every rank receives
+        every rank's rows and returns fp32 partial sums of all of them; fixed sizes, no counts, no host round trip, and
+        on the peer-memory kernels two launches.  form "all_to_all": forward_all_to_all() -- at most min(K, N) rows per
+        token each way, but a count exchange, a host round trip and the index building in front of it.  Inside one
+        NVSwitch node the first is the faster one as long as the gathered rows fit (measured at 8192 tokens over 2-8
+        GPUs); "auto" takes it while the N * T gathered rows with their fp32 partial sums (6 bytes per element) stay
+        under gather_limit_bytes, and the all-to-all beyond."""
+        if form == "auto":
+            T, H = x1.shape
+            form = "all_gather" if self.world * T * H * 6 <= gather_limit_bytes else "all_to_all"
+        if form == "all_gather":
+            return self.forward(x1, out, marks)
+        if form == "all_to_all":
+            return self.forward_all_to_all(x1, out, marks)
+        raise ValueError(f"form {form!r}: 'auto', 'all_gather' or 'all_to_all'")
+
+
 # ----------------------------------------------------------------------------------------------------------------
 # Tensor parallelism of the dense hybrid stack (27B-class decode group: heads split across 2 / 4 / 8 GPUs).
 # The reference splits the same way across its 4 NPU cores: projection rows by head, FFN rows by column block,

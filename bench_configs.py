@@ -222,7 +222,8 @@ def run_c3_prefill(args):
 
 
 def run_c4_prefill_ep(args):
-    """MoE prefill over several GPUs: experts sharded, the 8192 tokens split evenly, routed rows exchanged all-to-all"""
+    """MoE prefill over several GPUs: experts sharded, the 8192 tokens split evenly; both exchange forms are timed and
+    compared, the timed step runs the one `ExpertParallelMoE.forward_prefill` picks"""
     import datetime
     import torch.distributed as dist
     import ax_dsl_kernels_b200 as q35
@@ -237,7 +238,6 @@ def run_c4_prefill_ep(args):
     g = torch.Generator(device=dev).manual_seed(3 + rank)
     x1 = torch.randn((T, hb.H), generator=g, device=dev).to(torch.bfloat16)
     out = torch.empty_like(x1)
-    step = lambda: ep.forward_all_to_all(x1, out)  # noqa: E731
     flop = 8192 * hb.TOPK * 6 * hb.H * hb.FE + 8192 * 6 * hb.H * hb.FS + 8192 * 2 * hb.H * hb.NE
     _, tf, src = hb.measured_peaks()
 
@@ -245,25 +245,41 @@ def run_c4_prefill_ep(args):
         t = flop / (ms * 1e-3) / 1e12
         return {"bound": "tensor", "kernel": "tc_gemm_kernel (routed gate-up, down on the received rows; shared expert)",
                 "achieved": t, "peak": tf * world, "unit": "TFLOP/s", "frac": t / (tf * world),
-                "peak_source": src + " (bf16 GEMM) x GPUs", "traffic": None, "algorithmic_flop": flop,
-                "exchange_rows_per_token_upper_bound": min(hb.TOPK, world) - 1}
+                "peak_source": src + " (bf16 GEMM) x GPUs", "traffic": None, "algorithmic_flop": flop}
 
-    per = {}  # phase times, every rank takes part (the step holds collectives); rank 0's medians are reported
-    for it in range(12):
-        marks = []
-        ep.forward_all_to_all(x1, out, marks=marks)
-        torch.cuda.synchronize()
-        if it >= 4:
-            for (_, a), (nm, b) in zip(marks[:-1], marks[1:]):
-                per.setdefault(nm, []).append(a.elapsed_time(b))
-    phases = {nm: round(hb.median(v) * 1e3, 1) for nm, v in per.items()}
-    extra = lambda _ms: {"ep_phases_us_rank0": phases}  # noqa: E731
+    # Both exchanges on the same tokens: phase times of each (every rank takes part: the steps hold collectives; rank
+    # 0's medians are reported), their whole-step times, and how far their results are apart.  The timed step is the
+    # library's own choice (forward_prefill, form "auto").
+    forms, outs = {}, {}
+    for form in ("all_to_all", "all_gather"):
+        o = torch.empty_like(x1)
+        per, whole = {}, []
+        for it in range(12):
+            marks = []
+            ep.forward_prefill(x1, o, form=form, marks=marks)
+            torch.cuda.synchronize()
+            if it >= 4:
+                for (_, a), (nm, b) in zip(marks[:-1], marks[1:]):
+                    per.setdefault(nm, []).append(a.elapsed_time(b))
+                whole.append(marks[0][1].elapsed_time(marks[-1][1]))
+        t = torch.tensor([hb.median(whole)], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        forms[form] = {"ms_max_over_ranks": round(float(t.item()), 4),
+                       "phases_us_rank0": {nm: round(hb.median(v) * 1e3, 1) for nm, v in per.items()}}
+        outs[form] = o
+    diff = (outs["all_to_all"].float() - outs["all_gather"].float()).abs().max() / outs["all_gather"].float().square().mean().sqrt()
+    d = torch.tensor([float(diff)], device=dev)
+    dist.all_reduce(d, op=dist.ReduceOp.MAX)
+    chosen = "all_gather" if world * T * hb.H * 6 <= (4 << 30) else "all_to_all"
+    step = lambda: ep.forward_prefill(x1, out)  # noqa: E731
+    extra = lambda _ms: {"ep_forms": forms, "ep_forms_max_diff_over_rms": float(d.item()), "ep_form_timed": chosen}  # noqa: E731
     _finish(args, "c4_prefill", "MoE block prefill tok/s (8192 tokens, 256 experts top-8); % of FP4/FP8 TC peak", 8192, step,
             [x1], [out], roof,
             {"workload": f"MoE block, 8192 tokens ({T} per GPU), {hb.NE} experts top-{hb.TOPK} MXFP4 + shared expert, "
-             f"hidden {hb.H}", "parallelism": f"experts sharded x{world}, tokens split x{world}, every token's row sent once to each rank "
-             "that owns one of its experts and one weighted partial sum returned per row (NCCL all-to-all both ways), "
-             "row counts through the host once per step"},
+             f"hidden {hb.H}", "parallelism": f"experts sharded x{world}, tokens split x{world}; exchange form '{chosen}' "
+             "(all_gather: every rank's rows to every rank and fp32 partial sums back, through peer memory or NCCL; "
+             "all_to_all: every token's row once to each rank that owns one of its experts, one weighted sum back per "
+             "row, row counts through the host); both are timed in ep_forms"},
             dist=dist, dev=dev, scaling="strong", graph_ok=False, extra=extra)
 
 

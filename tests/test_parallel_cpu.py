@@ -113,7 +113,12 @@ def _worker(rank, world, port, ret):
         ref, _, _, _ = omoe.moe_block(x1, w["ln2"], *deq, w["w_router"], w["w_shg"], w["e_gw"], w["e_gs"], w["e_dw"],
                                       w["e_ds"], 3)
         err = (out.float() - ref.float()).abs().max() / ref.float().square().mean().sqrt()
-        ret[rank] = float(err)
+        # the prefill entry: the same exchange under "auto" while the gathered rows fit, the all-to-all beyond
+        same = ep.forward_prefill(x1)
+        a2a = ep.forward_prefill(x1, gather_limit_bytes=0)
+        assert torch.equal(same, out)
+        err2 = (a2a.float() - ref.float()).abs().max() / ref.float().square().mean().sqrt()
+        ret[rank] = float(max(err, err2))
     finally:
         dist.destroy_process_group()
 
