@@ -123,7 +123,8 @@ def kv_quant_fp8(x, scale=None):
 def kv_quant_int8_rows(x):
     """[..., HKV, D] bf16 -> (int8 [..., HKV, D], bf16 scale [..., HKV]): amax per head (at least 1e-5), s = bf16(amax *
     bf16(1 / 127)), q = round(bf16(x * bf16(1 / s))) -- kv_quant_row (models/qwen38_27b/decode/q35_group.py:198-205),
-    every product rounded to bf16 as the reference's bf16 ops do."""
+    every product rounded to bf16 as the reference's bf16 ops do.  Parity unpinned: the reference has these lines only
+    as kernel DSL (no torch function to import, no inline golden), so this restates their operation sequence."""
     bf = lambda t: t.to(torch.bfloat16).float()  # noqa: E731
     xb = x.to(torch.bfloat16).float()
     amax = torch.maximum(xb.abs().amax(-1, keepdim=True), bf(torch.tensor(1e-5)))
