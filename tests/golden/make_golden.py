@@ -147,7 +147,81 @@ def mtp():
     save("mtp", d)
 
 
+def hf_layer():
+    """The end-to-end ground truth the reference checks its layer kernels against: transformers'
+    Qwen3_5MoeDecoderLayer in fp32, eager attention, with the routed experts' weights passed through the MXFP4 round
+    trip (hf_layer / hf_out, models/qwen35_2b/whole/src/q35_moe.py:300-324).  A small configuration of the same
+    architecture, seeded random weights rounded to bf16, one GDN layer and one attention layer on a 6-token prefill.
+    Needs the `transformers` package (no reference source)."""
+    from transformers.models.qwen3_5_moe.configuration_qwen3_5_moe import Qwen3_5MoeTextConfig
+    from transformers.models.qwen3_5_moe.modeling_qwen3_5_moe import (Qwen3_5MoeDecoderLayer,
+                                                                       Qwen3_5MoeTextRotaryEmbedding)
+    sys.path.insert(0, os.path.join(HERE, "..", ".."))
+    from oracle import codecs
+    dims = dict(hidden_size=256, num_experts=8, num_experts_per_tok=2, moe_intermediate_size=64,
+                shared_expert_intermediate_size=64, num_attention_heads=4, num_key_value_heads=2, head_dim=64,
+                layer_types=["linear_attention", "full_attention"], num_hidden_layers=2, linear_num_key_heads=2,
+                linear_num_value_heads=4, linear_key_head_dim=32, linear_value_head_dim=32, linear_conv_kernel_dim=4,
+                rms_norm_eps=1e-6, vocab_size=1000)
+    hc = Qwen3_5MoeTextConfig(**dims)
+    hc._attn_implementation = "eager"
+    rot = Qwen3_5MoeTextRotaryEmbedding(hc)
+    g = torch.Generator().manual_seed(77)
+    P, H, NE, FE = 6, dims["hidden_size"], dims["num_experts"], dims["moe_intermediate_size"]
+    out = dict(rope_theta=float(hc.rope_parameters["rope_theta"]),
+               partial_rotary_factor=float(hc.rope_parameters["partial_rotary_factor"]))
+    for kind, il in (("gdn", 0), ("attn", 1)):
+        layer = Qwen3_5MoeDecoderLayer(hc, il).float().eval()
+        sd = {}
+        for name, t in layer.state_dict().items():
+            if name.endswith("layernorm.weight") or name.endswith("_norm.weight"):  # stored as w - 1
+                v = torch.randn(t.shape, generator=g) * 0.1
+            elif name.endswith("linear_attn.norm.weight"):
+                v = 1.0 + torch.randn(t.shape, generator=g) * 0.1
+            elif name.endswith("A_log"):
+                v = torch.randn(t.shape, generator=g) * 0.5
+            elif name.endswith("dt_bias"):
+                v = torch.randn(t.shape, generator=g) * 0.5
+            elif name.endswith("conv1d.weight"):
+                v = torch.randn(t.shape, generator=g) * 0.3
+            else:
+                v = torch.randn(t.shape, generator=g) * (t.shape[-1] ** -0.5)
+            sd[name] = v.to(torch.bfloat16).float()
+        packs = {}
+        for name in ("mlp.experts.gate_up_proj", "mlp.experts.down_proj"):  # the MXFP4 round trip, expert by expert
+            w = sd[name]
+            pk, sc = zip(*[codecs.quant_mxfp4(w[e]) for e in range(NE)])
+            packs[name] = (torch.stack(pk), torch.stack(sc))
+            sd[name] = torch.stack([codecs.dequant_mxfp4(a, b) for a, b in zip(pk, sc)])
+        layer.load_state_dict(sd, strict=True)
+        x = (torch.randn((1, P, H), generator=g) * 0.5).to(torch.bfloat16)
+        pos = torch.arange(P)[None]
+        mask = torch.full((1, 1, P, P), float("-inf")).triu(1) if layer.layer_type == "full_attention" else None
+        probs = []
+        hook = layer.mlp.gate.register_forward_hook(lambda m, i, o: probs.append(o[0]))
+        with torch.no_grad():
+            y = layer(x.float(), position_embeddings=rot(x.float(), pos), attention_mask=mask, position_ids=pos)
+        hook.remove()
+        y = y[0] if isinstance(y, tuple) else y
+        out[kind + ".x"] = x
+        out[kind + ".y"] = y.reshape(P, H).float()
+        out[kind + ".router_probs"] = probs[0].reshape(P, NE).float()
+        for name, t in sd.items():
+            if name in packs:
+                out[f"{kind}.{name}.packed"], out[f"{kind}.{name}.scale"] = packs[name]
+            else:
+                out[f"{kind}.{name}"] = t.to(torch.bfloat16)
+    cos, sin = rot(torch.zeros((1, P, H)), torch.arange(P)[None])
+    out["rope_cos"], out["rope_sin"] = cos.reshape(P, -1).float(), sin.reshape(P, -1).float()
+    for k, v in dims.items():
+        if isinstance(v, (int, float)):
+            out["cfg." + k] = v
+    save("hf_layer", out)
+
+
 def main():
+    if "--only-hf-layer" in sys.argv:
+        return hf_layer()
     if not os.path.isdir(REF):
         sys.exit("set REF to the reference checkout")
     if "--only-lm-head" in sys.argv:
@@ -238,6 +312,7 @@ def main():
     manifest_roles()
     mrope()
     mtp()
+    hf_layer()
 
 
 if __name__ == "__main__":
