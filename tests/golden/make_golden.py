@@ -219,9 +219,68 @@ def hf_layer():
     save("hf_layer", out)
 
 
+def hf_stack():
+    """The dense hybrid stack (layers g g g a, SwiGLU block after every token mixer) as transformers' Qwen3_5TextModel
+    runs it in fp32 with its own cache: a 7-token prefill, then two single-token decode steps; the hidden state after
+    every decoder layer of each call.  The layer loop this stands for:
+    models/qwen35_2b/whole/src/q35_step.py:438-470.  Needs the `transformers` package (no reference source)."""
+    from transformers.models.qwen3_5.configuration_qwen3_5 import Qwen3_5TextConfig
+    from transformers.models.qwen3_5.modeling_qwen3_5 import Qwen3_5TextModel
+    dims = dict(hidden_size=128, intermediate_size=256, num_attention_heads=4, num_key_value_heads=2, head_dim=32,
+                layer_types=["linear_attention"] * 3 + ["full_attention"], num_hidden_layers=4, linear_num_key_heads=2,
+                linear_num_value_heads=4, linear_key_head_dim=16, linear_value_head_dim=16, linear_conv_kernel_dim=4,
+                rms_norm_eps=1e-6, vocab_size=64)
+    hc = Qwen3_5TextConfig(**dims)
+    hc._attn_implementation = "eager"
+    model = Qwen3_5TextModel(hc).float().eval()
+    g = torch.Generator().manual_seed(91)
+    sd = {}
+    for name, t in model.state_dict().items():
+        if name.endswith("layernorm.weight") or name.endswith("_norm.weight") or name == "norm.weight":
+            v = torch.randn(t.shape, generator=g) * 0.1  # stored as w - 1
+        elif name.endswith("linear_attn.norm.weight"):
+            v = 1.0 + torch.randn(t.shape, generator=g) * 0.1
+        elif name.endswith("A_log") or name.endswith("dt_bias"):
+            v = torch.randn(t.shape, generator=g) * 0.5
+        elif name.endswith("conv1d.weight"):
+            v = torch.randn(t.shape, generator=g) * 0.3
+        else:
+            v = torch.randn(t.shape, generator=g) * (t.shape[-1] ** -0.5)
+        sd[name] = v.to(torch.bfloat16).float()
+    model.load_state_dict(sd, strict=True)
+    T, H = 7, dims["hidden_size"]
+    xs = (torch.randn((1, T + 2, H), generator=g) * 0.5).to(torch.bfloat16)
+    seen = []
+    hooks = [layer.register_forward_hook(lambda m, i, o: seen.append(o[0] if isinstance(o, tuple) else o))
+             for layer in model.layers]
+    with torch.no_grad():
+        r = model(inputs_embeds=xs[:, :T].float(), use_cache=True)
+        cache = r.past_key_values
+        for t in range(T, T + 2):
+            r = model(inputs_embeds=xs[:, t:t + 1].float(), past_key_values=cache, use_cache=True)
+            cache = r.past_key_values
+    for h in hooks:
+        h.remove()
+    L = len(model.layers)  # seen: the L layers' outputs of the prefill, then of each decode step
+    out = dict(x=xs, y_prefill=torch.stack([t.reshape(T, H) for t in seen[:L]]).float(),
+               y_decode0=torch.stack([t.reshape(1, H) for t in seen[L:2 * L]]).float(),
+               y_decode1=torch.stack([t.reshape(1, H) for t in seen[2 * L:3 * L]]).float(),
+               rope_theta=float(hc.rope_parameters["rope_theta"]),
+               partial_rotary_factor=float(hc.rope_parameters["partial_rotary_factor"]))
+    for name, t in sd.items():
+        if name.startswith("layers."):
+            out[name] = t.to(torch.bfloat16)
+    for k, v in dims.items():
+        if isinstance(v, (int, float)):
+            out["cfg." + k] = v
+    save("hf_stack", out)
+
+
 def main():
     if "--only-hf-layer" in sys.argv:
         return hf_layer()
+    if "--only-hf-stack" in sys.argv:
+        return hf_stack()
     if not os.path.isdir(REF):
         sys.exit("set REF to the reference checkout")
     if "--only-lm-head" in sys.argv:
@@ -313,6 +372,7 @@ def main():
     mrope()
     mtp()
     hf_layer()
+    hf_stack()
 
 
 if __name__ == "__main__":

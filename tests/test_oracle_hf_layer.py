@@ -44,13 +44,13 @@ def _finish(f, kind, x1, top_k):
     return out
 
 
-def _check(out, ref):
+def _check(out, ref, worst_limit=0.1):
     """bf16 rounding at every step of the oracle against no rounding at all: error of the whole output against its RMS
-    within 2e-2, cosine above 0.9998 (the reference logs the cosine, q35_moe.py:353-355), no element off by 0.1 RMS"""
+    within 2e-2, cosine above 0.9998 (the reference logs the cosine, q35_moe.py:353-355), no element off by worst_limit RMS"""
     rms = ref.square().mean().sqrt()
     d = out.float() - ref
     rel, worst = float(d.square().mean().sqrt() / rms), float(d.abs().max() / rms)
-    assert _cos(out, ref) > 0.9998 and rel < 2e-2 and worst < 0.1, (_cos(out, ref), rel, worst)
+    assert _cos(out, ref) > 0.9998 and rel < 2e-2 and worst < worst_limit, (_cos(out, ref), rel, worst)
 
 
 def test_gdn_layer_with_moe_block_matches_the_transformers_layer(golden):
@@ -96,3 +96,49 @@ def test_attention_layer_with_moe_block_matches_the_transformers_layer(golden):
     out = _finish(f, "attn", x1, int(f["cfg.num_experts_per_tok"]))
     _check(out, g("y"))
     assert codecs.GROUP == 32
+
+
+def test_dense_hybrid_stack_prefill_then_decode_matches_the_transformers_model(golden):
+    """oracle.stack.HybridStack (g g g a with a SwiGLU block per layer; the stack the GPU stack drivers are checked
+    against) on a 7-token prefill and two decode steps, against transformers' Qwen3_5TextModel with its own cache
+    (tests/golden/hf_stack.npz, make_golden.py --only-hf-stack): the decode steps go through the recurrent state, the
+    conv state and the paged KV cache the prefill left behind."""
+    f = golden("hf_stack")
+    NK, NV = int(f["cfg.linear_num_key_heads"]), int(f["cfg.linear_num_value_heads"])
+    DK, DV = int(f["cfg.linear_key_head_dim"]), int(f["cfg.linear_value_head_dim"])
+    kd, vd = NK * DK, NV * DV
+    heads, kv_heads, hd = int(f["cfg.num_attention_heads"]), int(f["cfg.num_key_value_heads"]), int(f["cfg.head_dim"])
+    rot = int(round(hd * float(f["partial_rotary_factor"])))
+    kinds, layers = ["g", "g", "g", "a"], []
+    for i, kind in enumerate(kinds):
+        g = lambda n: f[f"layers.{i}.{n}"]  # noqa: E731,B023
+        w = dict(ln2=1.0 + g("post_attention_layernorm.weight").float(), w_gate=g("mlp.gate_proj.weight"),
+                 w_up=g("mlp.up_proj.weight"), w_down=g("mlp.down_proj.weight"))
+        if kind == "g":
+            qkv = g("linear_attn.in_proj_qkv.weight")
+            conv = g("linear_attn.conv1d.weight").reshape(2 * kd + vd, -1)
+            w.update(input_norm_w=1.0 + g("input_layernorm.weight").float(), w_q=qkv[:kd], w_k=qkv[kd:2 * kd],
+                     w_v=qkv[2 * kd:], w_z=g("linear_attn.in_proj_z.weight"), w_a=g("linear_attn.in_proj_a.weight"),
+                     w_b=g("linear_attn.in_proj_b.weight"), w_q_conv=conv[:kd], w_k_conv=conv[kd:2 * kd],
+                     w_v_conv=conv[2 * kd:], a_log=g("linear_attn.A_log").float(), dt_bias=g("linear_attn.dt_bias"),
+                     o_norm_w=g("linear_attn.norm.weight").float(), w_o=g("linear_attn.out_proj.weight"))
+        else:
+            w.update(ln1=1.0 + g("input_layernorm.weight").float(), w_q=g("self_attn.q_proj.weight"),
+                     w_k=g("self_attn.k_proj.weight"), w_v=g("self_attn.v_proj.weight"), w_o=g("self_attn.o_proj.weight"),
+                     q_norm=1.0 + g("self_attn.q_norm.weight").float(), k_norm=1.0 + g("self_attn.k_norm.weight").float())
+        layers.append(w)
+    cfg = dict(heads=heads, kv_heads=kv_heads, head_dim=hd, rot=rot, theta=float(f["rope_theta"]), page_size=4, max_tokens=16,
+               gated=True)
+    x = f["x"][0]
+    T = f["y_prefill"].shape[1]
+    calls = [(x[:T], f["y_prefill"]), (x[T:T + 1], f["y_decode0"]), (x[T + 1:T + 2], f["y_decode1"])]
+    # every layer by itself, fed what the transformers layer was fed, its own state carried from call to call
+    for i, kind in enumerate(kinds):
+        one = stack.HybridStack(layers[i:i + 1], [kind], **cfg)
+        for xin, ys in calls:
+            _check(one.forward(xin if i == 0 else ys[i - 1].to(torch.bfloat16)), ys[i], worst_limit=0.15)
+    # the four layers chained: the rounding of one layer is the input noise of the next
+    st = stack.HybridStack(layers, kinds, **cfg)
+    for xin, ys in calls:
+        out, ref = st.forward(xin), ys[-1]
+        assert _cos(out, ref) > 0.999 and float((out.float() - ref).square().mean().sqrt() / ref.square().mean().sqrt()) < 5e-2
