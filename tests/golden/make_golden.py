@@ -6,7 +6,9 @@ The reference's kernels need its NPU DSL package `axnn`, which is not installabl
 not, so `axnn` (and `onnx`, imported by a board helper) are replaced by inert stub modules and the golden functions
 are imported and called unchanged.  Outputs: small .npz files (bf16 tensors stored as their int16 bit patterns with a
 `__bf16` suffix, fp8 as uint8 with `__e4m3`).  The tests only read the .npz files; nothing reads the reference at
-test time.
+test time.  Two fixtures need no reference source but the `transformers` package, whose Qwen3.5 decoder layers are the
+ground truth the reference compares its layer kernels with: `--only-hf-layer` (MoE decoder layers) and
+`--only-hf-stack` (the dense text model with its cache).
 """
 import importlib.abc
 import importlib.machinery
