@@ -197,14 +197,22 @@ def hf_layer():
             sd[name] = torch.stack([codecs.dequant_mxfp4(a, b) for a, b in zip(pk, sc)])
         layer.load_state_dict(sd, strict=True)
         x = (torch.randn((1, P, H), generator=g) * 0.5).to(torch.bfloat16)
-        pos = torch.arange(P)[None]
-        mask = torch.full((1, 1, P, P), float("-inf")).triu(1) if layer.layer_type == "full_attention" else None
+        pos = torch.arange(P).reshape(1, P)
+        mask = None
+        if kind == "attn":  # additive causal mask: key j is visible to query i when j <= i
+            visible = pos.reshape(P, 1) >= pos.reshape(1, P)
+            mask = torch.zeros((P, P)).masked_fill(~visible, float("-inf")).reshape(1, 1, P, P)
         probs = []
-        hook = layer.mlp.gate.register_forward_hook(lambda m, i, o: probs.append(o[0]))
+
+        def keep_router_output(module, args, output):
+            probs.append(output[0])  # the router's first output: softmax over all experts, fp32
+
+        handle = layer.mlp.gate.register_forward_hook(keep_router_output)
         with torch.no_grad():
             y = layer(x.float(), position_embeddings=rot(x.float(), pos), attention_mask=mask, position_ids=pos)
-        hook.remove()
-        y = y[0] if isinstance(y, tuple) else y
+        handle.remove()
+        if isinstance(y, tuple):
+            y = y[0]
         out[kind + ".x"] = x
         out[kind + ".y"] = y.reshape(P, H).float()
         out[kind + ".router_probs"] = probs[0].reshape(P, NE).float()
