@@ -4,7 +4,9 @@ checks its layer kernels with: transformers' Qwen3_5MoeDecoderLayer in fp32, exp
 tests/golden/make_golden.py --only-hf-layer) holds a small configuration of the same architecture with seeded weights.
 The oracle rounds to bf16 where the reference's kernels do and the Hugging Face layer does not round at all, so the
 comparison is the reference's own kind -- cosine and error against RMS -- not bit for bit: it pins the structure (norm
-convention, projection splits, head order, RoPE pairing, gates, residuals, router rule, expert layout)."""
+convention, projection splits, head order, RoPE pairing, gates, residuals, router rule, expert layout).  Checkpoint
+weights become kernel inputs as the reference's loader makes them: the layer norms and the q / k norms as 1 + w, the
+gated norm of the GDN output as it is (models/qwen35_2b/whole/src/q35_step.py:347, 370-401)."""
 import torch
 
 from oracle import attention as oattn
